@@ -1,0 +1,183 @@
+/*
+ * b200_lut.h — C ABI of the B200 (sm_100a) LUT-palettized linear library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream) and returns
+ * an integer status (B200LUT_OK = 0). No function allocates device memory unless
+ * its comment says so; the caller owns every buffer. After a non-zero status,
+ * b200lut_last_error() returns a message for the calling thread.
+ *
+ * Each declaration names the interface of the reference project
+ * (pkhairkh/rag-cache-engineering-qwen35-9b-flute) that it replaces.
+ *
+ * Semantics shared by all compute entry points
+ *   W[n, k] = LUT[min(n / group_size, n_groups - 1)][code(n, k)]   (exact lookup)
+ *   y[m, n] = sum_k x[m, k] * W[n, k]   accumulated in fp32, rounded once
+ * dtype: element type of x, LUT entries and outputs (B200LUT_BF16 / B200LUT_F16).
+ */
+#ifndef B200_LUT_H_
+#define B200_LUT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  B200LUT_OK = 0,
+  B200LUT_ERR_INVALID = 1,      /* bad argument (shape, null pointer, range) */
+  B200LUT_ERR_UNSUPPORTED = 2,  /* valid request outside the compiled kernel table */
+  B200LUT_ERR_CUDA = 3,         /* a CUDA runtime call or launch failed */
+  B200LUT_ERR_WORKSPACE = 4,    /* caller's workspace is too small */
+  B200LUT_ERR_ALIGN = 5,        /* a pointer misses its required alignment */
+  B200LUT_ERR_DEVICE = 6        /* a kernel reported a device-side status (bounded wait ran out) */
+};
+
+enum { B200LUT_BF16 = 0, B200LUT_F16 = 1 };
+
+/* Epilogue selector of b200lut_gemv_multi / b200lut_gemm. */
+enum {
+  B200LUT_EPI_NONE = 0,
+  B200LUT_EPI_SILU_MUL = 1      /* segments come in (gate, up) pairs: out = silu(gate) * up */
+};
+
+/* Library version (major * 100 + minor). */
+int b200lut_version(void);
+
+/* Message of the calling thread's last failure ("" if none). Replaces the
+ * TORCH_CHECK exception text of the reference's host wrappers
+ * (src/flute_extended/src/kernel_gemv.cu:338-454). */
+const char* b200lut_last_error(void);
+
+/* Number of SMs of the current device (used by the split policy). */
+int b200lut_sm_count(void);
+
+/* ------------------------------------------------------------------------- *
+ * Weight layout
+ * ------------------------------------------------------------------------- */
+
+/* Bytes of the slab-layout code buffer for an [N, K] matrix at `bits` per code
+ * (= N*K*bits/8, the same count as the idxN blob; reference:
+ * src/flute_extended/flute_extended/idxN.py:111-114). 0 on invalid shape. */
+size_t b200lut_packed_bytes(int N, int K, int bits);
+
+/* One-time conversion of an idxN blob (device) into this library's slab layout
+ * (device, 16-byte aligned, b200lut_packed_bytes long). Replaces the consumer
+ * side of the idxN format: src/flute_extended/flute_extended/idxN.py:37-55,
+ * 267-291 (unpack_idxn) and the fragment-direct readers of
+ * src/flute_extended/include/flute/gemv.cuh:50-96. Requires N % 128 == 0,
+ * K % 64 == 0, bits in 1..4. */
+int b200lut_repack_from_idxn(const void* idxn_blob, void* packed, int N, int K, int bits,
+                             void* stream);
+
+/* Inverse conversion (slab layout -> idxN blob), for artifact export and
+ * round-trip checks. Reference: idxN.py:235-264 (pack_idxn). */
+int b200lut_repack_to_idxn(const void* packed, void* idxn_blob, int N, int K, int bits,
+                           void* stream);
+
+/* Logical code matrix [N, K] uint8 from the slab layout. Reference:
+ * src/scripts/palettized_modules.py:658-666 (_logical_indices_numpy). */
+int b200lut_unpack_codes(const void* packed, uint8_t* codes, int N, int K, int bits, void* stream);
+
+/* Dequantised weight export: out[n*K + k] = the 16-bit LUT entry of W[n, k]
+ * (raw bits, dtype of the LUT). Replaces reference_dequant
+ * (src/scripts/palettized_modules.py:125-162) as the bit-exactness probe. */
+int b200lut_dequant(const void* packed, const void* lut, int n_groups, void* out,
+                    int N, int K, int bits, int group_size, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Decode GEMV (M <= 16)
+ * ------------------------------------------------------------------------- */
+
+/* One palettized projection ("segment") of a decode launch. Replaces one row
+ * of the reference's CPU int64 [count, 15] segment table
+ * (src/flute_extended/include/flute/entrypoints.h:105-122). */
+typedef struct b200lut_segment {
+  const void* packed;    /* stream-1 codes, slab layout */
+  const void* lut;       /* stream-1 palette [n_groups, 2^bits], dtype */
+  const void* packed2;   /* stream-2 codes or NULL */
+  const void* lut2;      /* stream-2 palette [n_groups, 2^bits2] or NULL */
+  const void* bias;      /* [N] dtype or NULL; added in fp32 before the one rounding */
+  void* out;             /* [M, ldo] dtype; with EPI_SILU_MUL only the gate segment's out is written */
+  int64_t ldo;           /* elements between consecutive rows of out */
+  int N;                 /* output features of this segment (multiple of 128) */
+  int group_size;        /* rows per palette (power of two >= 32, or any multiple of 128) */
+  int n_groups;          /* palette rows actually present (row-group index is clamped) */
+  int bits;              /* stream-1 width (1..4) */
+  int bits2;             /* stream-2 width, 0 if absent */
+  int reserved;
+} b200lut_segment;
+
+/* Scratch bytes b200lut_gemv_multi needs for (segments, M, split): zero when the
+ * split is reduced through thread-block-cluster shared memory (split <= 8),
+ * else the fp32 partial buffer + tickets of the workspace fold. Reference:
+ * gemv_workspace_for, src/flute_extended/src/gemv_host.cpp:45-78. */
+size_t b200lut_gemv_workspace_bytes(int total_rows, int M, int split);
+
+/* Split-K factor the library would pick for `tiles` 128-row tiles over K.
+ * Reference: gemv_pick_split, src/flute_extended/src/gemv_host.cpp:29-38
+ * (re-derived for 148 SMs x 2 resident blocks). */
+int b200lut_gemv_pick_split(int tiles, int K);
+
+/* y_s = x @ W_s^T for 1..8 segments that share the activation rows x [M, K]
+ * (row stride ldx elements), M <= 16. Replaces qgemm_cutlass_gemv_stream,
+ * qgemm_cutlass_gemv_splitk_stream, qgemm_cutlass_gemv_multi and (with
+ * B200LUT_EPI_SILU_MUL) qgemm_cutlass_gemv_mlp
+ * (src/flute_extended/include/flute/entrypoints.h:49-122).
+ * split: 0 = library policy, else 1..16. workspace: needed only when
+ * b200lut_gemv_workspace_bytes(...) > 0; must be zero-filled once before first
+ * use (tickets reset themselves) and is used by one launch at a time.
+ * flags bit 0: launch with programmatic dependent launch, so the weight
+ * prefetch overlaps the tail of the previous kernel in the stream. */
+int b200lut_gemv_multi(const void* x, int64_t ldx, int M, int K, int dtype,
+                       const b200lut_segment* segs, int nseg, int epilogue, int split,
+                       void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/* Single-projection convenience form of b200lut_gemv_multi (one stream, no bias).
+ * Replaces qgemm_cutlass_gemv_stream (entrypoints.h:49-60). */
+int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out,
+                 int M, int N, int K, int bits, int group_size, int n_groups, int dtype,
+                 int split, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Prefill GEMM (M > 16), tcgen05 / TMEM
+ * ------------------------------------------------------------------------- */
+
+/* out[M, N] = x[M, K] @ W^T (+ bias). Replaces qgemm_cutlass_streaming
+ * (src/flute_extended/include/flute/entrypoints.h:31-37, kernels
+ * src/flute_extended/src/kernel_streaming.cu:987-1108). x rows must be
+ * 16-byte aligned (K % 8 == 0 and ldx % 8 == 0). With B200LUT_EPI_SILU_MUL,
+ * packed/lut are the gate projection and packed2/lut2 the up projection of the
+ * same shape and out = silu(x Wg^T) * (x Wu^T); otherwise a non-NULL packed2 is
+ * a second stream summed into the same accumulator. */
+int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
+                 const b200lut_segment* seg, int epilogue, int flags, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Hadamard rotation of the activations
+ * ------------------------------------------------------------------------- */
+
+enum {
+  B200LUT_FHT_FORWARD = 0,   /* ((x H) * signs) / sqrt(b)         per segment */
+  B200LUT_FHT_ADJOINT = 1,   /* ((x * signs) H) / sqrt(b)         per segment */
+  B200LUT_FHT_AWQ = 2        /* (((x * scale) H) * signs / sqrt(b)) / scale   */
+};
+
+/* Row-wise transform of x [M, K] into out [M, K] (out may equal x: in place).
+ * block == 0: descending power-of-two segments of K (4096 -> one 4096-point
+ * transform; 12288 -> 8192 + 4096); block > 0 (power of two dividing K, <= 8192):
+ * independent `block`-point transforms. signs: (K,) fp32 +-1 or NULL (= all +1);
+ * scale: (K,) fp32, AWQ mode only. fp32 butterfly whatever the I/O dtype.
+ * dtype: B200LUT_BF16, B200LUT_F16 or 2 = fp32.
+ * Replaces fht_forward / fht_backward / fht_inplace_ / fht_forward_awq
+ * (src/flute_extended/src/kernel_fht.cu:70-255, src/flute_extended/fht.py:206-238). */
+int b200lut_fht(const void* x, void* out, const float* signs, const float* scale,
+                int M, int K, int64_t ldx, int64_t ldo, int dtype, int mode, int block,
+                void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* B200_LUT_H_ */

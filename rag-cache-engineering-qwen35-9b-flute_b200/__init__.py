@@ -1,0 +1,13 @@
+"""B200-native idxN LUT-palettized linear layer (decode GEMV, prefill GEMM, FHT).
+
+Host side: PyTorch modules mirroring the reference's PalettizedLinear /
+SplitQKV / FusedPalettizedMLP; compute: libb200lut.so (hand-written sm_100a CUDA
+behind a C ABI, see include/b200_lut.h). Import of this package does not load
+the library; the first compute call does, and fails loudly if it is not built.
+"""
+from . import _lib, fht, idxN, synthetic                                    # noqa: F401
+from .palettized_modules import (FusedPalettizedMLP, PalettizedLinear, SplitQKV,  # noqa: F401
+                                 reference_dequant, set_programmatic_launch)
+
+__all__ = ["PalettizedLinear", "SplitQKV", "FusedPalettizedMLP", "reference_dequant",
+           "set_programmatic_launch", "fht", "idxN", "synthetic"]

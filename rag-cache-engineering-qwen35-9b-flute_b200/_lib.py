@@ -1,0 +1,240 @@
+"""ctypes binding of libb200lut.so (the C ABI declared in include/b200_lut.h).
+
+The library is the only compute path of this package: if it is missing or a
+call fails, an exception is raised — nothing falls back to torch or the CPU.
+Tensors are passed as raw device pointers; launches go to torch's current CUDA
+stream so they order with the surrounding torch work.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Sequence
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200lut.so")
+
+OK = 0
+BF16, F16, F32 = 0, 1, 2
+EPI_NONE, EPI_SILU_MUL = 0, 1
+FHT_FORWARD, FHT_ADJOINT, FHT_AWQ = 0, 1, 2
+FLAG_PDL = 1
+
+EXPORTS = (
+    "b200lut_version", "b200lut_last_error", "b200lut_sm_count", "b200lut_packed_bytes",
+    "b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes",
+    "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
+    "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
+)
+
+
+class Segment(ctypes.Structure):
+    """struct b200lut_segment."""
+    _fields_ = [
+        ("packed", ctypes.c_void_p), ("lut", ctypes.c_void_p),
+        ("packed2", ctypes.c_void_p), ("lut2", ctypes.c_void_p),
+        ("bias", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("ldo", ctypes.c_int64),
+        ("N", ctypes.c_int), ("group_size", ctypes.c_int), ("n_groups", ctypes.c_int),
+        ("bits", ctypes.c_int), ("bits2", ctypes.c_int), ("reserved", ctypes.c_int),
+    ]
+
+
+class LibraryError(RuntimeError):
+    """A b200lut_* call returned a non-zero status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"b200lut status {code}: {message}")
+        self.code = code
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load the shared library once; loud failure when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python {os.path.join(_HERE, 'build.py')}` "
+            "(nvcc, sm_100a). This package has no other compute path.")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, i32, i64, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
+    L.b200lut_version.restype = i32
+    L.b200lut_last_error.restype = ctypes.c_char_p
+    L.b200lut_sm_count.restype = i32
+    L.b200lut_packed_bytes.restype = sz
+    L.b200lut_packed_bytes.argtypes = [i32, i32, i32]
+    for name in ("b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes"):
+        getattr(L, name).restype = i32
+        getattr(L, name).argtypes = [vp, vp, i32, i32, i32, vp]
+    L.b200lut_dequant.restype = i32
+    L.b200lut_dequant.argtypes = [vp, vp, i32, vp, i32, i32, i32, i32, vp]
+    L.b200lut_gemv_workspace_bytes.restype = sz
+    L.b200lut_gemv_workspace_bytes.argtypes = [i32, i32, i32]
+    L.b200lut_gemv_pick_split.restype = i32
+    L.b200lut_gemv_pick_split.argtypes = [i32, i32]
+    L.b200lut_gemv_multi.restype = i32
+    L.b200lut_gemv_multi.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32,
+                                     i32, vp, sz, i32, vp]
+    L.b200lut_gemv.restype = i32
+    L.b200lut_gemv.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, sz, vp]
+    L.b200lut_gemm.restype = i32
+    L.b200lut_gemm.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32, vp]
+    L.b200lut_fht.restype = i32
+    L.b200lut_fht.argtypes = [vp, vp, vp, vp, i32, i32, i64, i64, i32, i32, i32, vp]
+    _lib = L
+    return L
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise LibraryError(code, lib().b200lut_last_error().decode("utf-8", "replace"))
+
+
+def dtype_id(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return BF16
+    if dtype == torch.float16:
+        return F16
+    if dtype == torch.float32:
+        return F32
+    raise TypeError(f"unsupported dtype {dtype}")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what} must be a CUDA tensor: this package computes on the GPU only")
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+# --------------------------------------------------------------------------- #
+# layout
+# --------------------------------------------------------------------------- #
+
+def packed_bytes(N: int, K: int, bits: int) -> int:
+    n = lib().b200lut_packed_bytes(N, K, bits)
+    if n == 0:
+        raise ValueError(f"idxN layout requires N%128==0 and K%64==0 and bits in 1..4, got "
+                         f"N={N}, K={K}, bits={bits}")
+    return n
+
+
+def repack_from_idxn(blob: torch.Tensor, N: int, K: int, bits: int) -> torch.Tensor:
+    """idxN blob (uint8, CUDA) -> slab-layout codes (uint8, CUDA)."""
+    _need_cuda(blob, "blob")
+    blob = blob.contiguous().view(torch.uint8).reshape(-1)
+    n = packed_bytes(N, K, bits)
+    if blob.numel() != n:
+        raise ValueError(f"idx{bits} blob numel {blob.numel()} != N*K*{bits}/8 {n} (N={N}, K={K})")
+    if blob.data_ptr() % 16:
+        blob = blob.clone()
+    out = torch.empty(n, dtype=torch.uint8, device=blob.device)
+    with torch.cuda.device(blob.device):
+        check(lib().b200lut_repack_from_idxn(blob.data_ptr(), out.data_ptr(), N, K, bits, _stream(blob)))
+    return out
+
+
+def repack_to_idxn(packed: torch.Tensor, N: int, K: int, bits: int) -> torch.Tensor:
+    _need_cuda(packed, "packed")
+    out = torch.empty(packed_bytes(N, K, bits), dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(lib().b200lut_repack_to_idxn(packed.data_ptr(), out.data_ptr(), N, K, bits, _stream(packed)))
+    return out
+
+
+def unpack_codes(packed: torch.Tensor, N: int, K: int, bits: int) -> torch.Tensor:
+    _need_cuda(packed, "packed")
+    out = torch.empty(N, K, dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(lib().b200lut_unpack_codes(packed.data_ptr(), out.data_ptr(), N, K, bits, _stream(packed)))
+    return out
+
+
+def dequant(packed: torch.Tensor, lut: torch.Tensor, N: int, K: int, bits: int,
+            group_size: int) -> torch.Tensor:
+    """[N, K] tensor of the palette entries (dtype of the LUT, exact)."""
+    _need_cuda(packed, "packed")
+    lut = lut.contiguous()
+    if lut.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"LUT dtype must be bfloat16 or float16, got {lut.dtype}")
+    out = torch.empty(N, K, dtype=lut.dtype, device=packed.device)
+    n_groups = lut.numel() >> bits
+    with torch.cuda.device(packed.device):
+        check(lib().b200lut_dequant(packed.data_ptr(), lut.data_ptr(), n_groups, out.data_ptr(),
+                                    N, K, bits, group_size, _stream(packed)))
+    return out
+
+
+# --------------------------------------------------------------------------- #
+# compute
+# --------------------------------------------------------------------------- #
+
+def make_segments(descs: Sequence[dict]):
+    """Build a ctypes array of b200lut_segment from dicts of tensors/ints."""
+    arr = (Segment * len(descs))()
+    for s, d in zip(arr, descs):
+        s.packed, s.lut = ptr(d["packed"]), ptr(d["lut"])
+        s.packed2, s.lut2 = ptr(d.get("packed2")), ptr(d.get("lut2"))
+        s.bias, s.out = ptr(d.get("bias")), ptr(d.get("out"))
+        s.ldo = int(d.get("ldo", d["N"]))
+        s.N, s.group_size, s.n_groups = int(d["N"]), int(d["group_size"]), int(d["n_groups"])
+        s.bits, s.bits2 = int(d["bits"]), int(d.get("bits2") or 0)
+    return arr
+
+
+def gemv_workspace_bytes(total_rows: int, M: int, split: int) -> int:
+    return lib().b200lut_gemv_workspace_bytes(total_rows, M, split)
+
+
+def gemv_multi(x: torch.Tensor, segs, nseg: int, epilogue: int = EPI_NONE, split: int = 0,
+               workspace: Optional[torch.Tensor] = None, flags: int = 0) -> None:
+    """Launch the decode GEMV over a prepared segment array (outputs are the
+    tensors whose pointers the segments carry)."""
+    _need_cuda(x, "x")
+    M, K = x.shape
+    ws_ptr = None if workspace is None else workspace.data_ptr()
+    ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    with torch.cuda.device(x.device):
+        check(lib().b200lut_gemv_multi(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), segs,
+                                       nseg, epilogue, split, ws_ptr, ws_bytes, flags, _stream(x)))
+
+
+def gemm(x: torch.Tensor, seg, epilogue: int = EPI_NONE, flags: int = 0) -> None:
+    _need_cuda(x, "x")
+    M, K = x.shape
+    with torch.cuda.device(x.device):
+        check(lib().b200lut_gemm(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), seg,
+                                 epilogue, flags, _stream(x)))
+
+
+def fht(x: torch.Tensor, signs: Optional[torch.Tensor], mode: int = FHT_FORWARD,
+        scale: Optional[torch.Tensor] = None, block: int = 0,
+        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-wise Hadamard transform of a 2-D CUDA tensor (last dim contiguous)."""
+    _need_cuda(x, "x")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("fht expects a 2-D tensor with a contiguous last dim")
+    M, K = x.shape
+    if out is None:
+        out = torch.empty(M, K, dtype=x.dtype, device=x.device)
+    for name, v in (("signs", signs), ("scale", scale)):
+        if v is not None and (v.dtype != torch.float32 or not v.is_contiguous()
+                              or v.numel() != K or v.device != x.device):
+            raise ValueError(f"{name} must be a contiguous (K,) float32 tensor on x's device")
+    with torch.cuda.device(x.device):
+        check(lib().b200lut_fht(x.data_ptr(), out.data_ptr(), ptr(signs), ptr(scale), M, K,
+                                x.stride(0), out.stride(0), dtype_id(x.dtype), mode, block,
+                                _stream(x)))
+    return out

@@ -1,0 +1,159 @@
+// Row-wise fast Hadamard transform of the activations (the rotation in front of
+// the palettized GEMV / GEMM). Replaces the reference's FHT kernels
+// (src/flute_extended/src/kernel_fht.cu:70-255, include/flute/fht.cuh:84-178) and
+// follows the arithmetic of its torch twin (src/flute_extended/fht.py:174-238):
+// fp32 butterfly with stage length doubling from 1, each stage writing (a + b)
+// to the low and (a - b) to the high element of a pair; forward applies
+// * signs then * (1/sqrt(b)); adjoint applies * signs on load; the AWQ form
+// multiplies by the scale on load and truly divides by it on store. Every output
+// element is a fixed expression tree of fp32 adds, so results do not depend on
+// the thread schedule and match the torch twin bit for bit.
+//
+// One block per (row, segment). In block mode (independent `block`-point
+// transforms) the same butterfly simply stops after log2(block) stages.
+#include "common.cuh"
+
+namespace b200lut {
+namespace {
+
+constexpr int kMaxSegments = 16;
+constexpr int kMaxPoints = 16384;   // 64 KB of fp32 per block
+
+struct FhtParams {
+  const void* x;
+  void* out;
+  const float* signs;
+  const float* scale;
+  long long ldx, ldo;
+  int dtype, mode, nseg;
+  int seg_off[kMaxSegments];
+  int seg_len[kMaxSegments];     // points held by the block
+  int seg_stages[kMaxSegments];  // butterfly stages to run (log2 of the transform size)
+  float seg_inv[kMaxSegments];   // 1 / sqrt(transform size)
+};
+
+__device__ __forceinline__ float load_elem(const void* p, long long i, int dtype) {
+  if (dtype == B200LUT_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  if (dtype == B200LUT_F16) return __half2float(static_cast<const __half*>(p)[i]);
+  return static_cast<const float*>(p)[i];
+}
+
+__device__ __forceinline__ void store_elem(void* p, long long i, int dtype, float v) {
+  if (dtype == B200LUT_BF16) static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  else if (dtype == B200LUT_F16) static_cast<__half*>(p)[i] = __float2half_rn(v);
+  else static_cast<float*>(p)[i] = v;
+}
+
+__global__ void __launch_bounds__(1024) fht_kernel(const FhtParams p) {
+  extern __shared__ float buf[];
+  const int row = blockIdx.x, sg = blockIdx.y;
+  const int off = p.seg_off[sg], n = p.seg_len[sg], stages = p.seg_stages[sg];
+  const float inv = p.seg_inv[sg];
+  const long long xin = (long long)row * p.ldx + off;
+  const long long xout = (long long)row * p.ldo + off;
+
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = load_elem(p.x, xin + i, p.dtype);
+    if (p.mode == B200LUT_FHT_AWQ) v = v * p.scale[off + i];
+    else if (p.mode == B200LUT_FHT_ADJOINT && p.signs) v = v * p.signs[off + i];
+    buf[i] = v;
+  }
+  __syncthreads();
+  for (int st = 0; st < stages; ++st) {
+    const int len = 1 << st;
+    for (int i = threadIdx.x; i < n / 2; i += blockDim.x) {
+      const int lo = ((i >> st) << (st + 1)) + (i & (len - 1));
+      const float a = buf[lo], b = buf[lo + len];
+      buf[lo] = a + b;
+      buf[lo + len] = a - b;
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = buf[i];
+    if (p.mode == B200LUT_FHT_ADJOINT) {
+      v = v * inv;
+    } else {
+      if (p.signs) v = v * p.signs[off + i];
+      v = v * inv;
+      if (p.mode == B200LUT_FHT_AWQ) v = __fdiv_rn(v, p.scale[off + i]);
+    }
+    store_elem(p.out, xout + i, p.dtype, v);
+  }
+}
+
+}  // namespace
+}  // namespace b200lut
+
+using namespace b200lut;
+
+extern "C" int b200lut_fht(const void* x, void* out, const float* signs, const float* scale,
+                           int M, int K, int64_t ldx, int64_t ldo, int dtype, int mode, int block,
+                           void* stream) {
+  B200LUT_REQUIRE(x && out, B200LUT_ERR_INVALID, "null x or out");
+  B200LUT_REQUIRE(M >= 0 && K >= 1, B200LUT_ERR_INVALID, "bad shape M=%d K=%d", M, K);
+  B200LUT_REQUIRE(dtype >= 0 && dtype <= 2, B200LUT_ERR_INVALID, "dtype must be 0 (bf16), 1 (f16) or 2 (f32)");
+  B200LUT_REQUIRE(mode >= B200LUT_FHT_FORWARD && mode <= B200LUT_FHT_AWQ, B200LUT_ERR_INVALID,
+                  "unknown mode %d", mode);
+  B200LUT_REQUIRE(mode != B200LUT_FHT_AWQ || scale, B200LUT_ERR_INVALID,
+                  "the AWQ form needs a scale vector");
+  B200LUT_REQUIRE(ldx >= K && ldo >= K, B200LUT_ERR_INVALID, "row strides must be >= K");
+  if (M == 0) return B200LUT_OK;
+
+  FhtParams p = {};
+  p.x = x; p.out = out; p.signs = signs; p.scale = scale;
+  p.ldx = ldx; p.ldo = ldo; p.dtype = dtype; p.mode = mode;
+  int max_len = 0;
+  if (block > 0) {
+    B200LUT_REQUIRE((block & (block - 1)) == 0 && K % block == 0, B200LUT_ERR_INVALID,
+                    "block must be a power of two dividing K (block=%d, K=%d)", block, K);
+    int stages = 0;
+    while ((1 << stages) < block) ++stages;
+    // a block of threads takes as many whole transforms as fit 8192 points
+    int span = block;
+    while (span * 2 <= 8192 && K % (span * 2) == 0) span *= 2;
+    B200LUT_REQUIRE(span <= kMaxPoints && K / span <= kMaxSegments, B200LUT_ERR_UNSUPPORTED,
+                    "K=%d with block=%d needs more than %d row pieces", K, block, kMaxSegments);
+    p.nseg = K / span;
+    for (int i = 0; i < p.nseg; ++i) {
+      p.seg_off[i] = i * span;
+      p.seg_len[i] = span;
+      p.seg_stages[i] = stages;
+      p.seg_inv[i] = float(1.0 / sqrt(double(block)));
+    }
+    max_len = span;
+  } else {
+    int off = 0;
+    while (off < K) {
+      int b = 1;
+      while (b * 2 <= K - off) b *= 2;
+      B200LUT_REQUIRE(p.nseg < kMaxSegments && b <= kMaxPoints, B200LUT_ERR_UNSUPPORTED,
+                      "K=%d: segment of %d points or more than %d segments is not served", K, b,
+                      kMaxSegments);
+      int stages = 0;
+      while ((1 << stages) < b) ++stages;
+      p.seg_off[p.nseg] = off;
+      p.seg_len[p.nseg] = b;
+      p.seg_stages[p.nseg] = stages;
+      p.seg_inv[p.nseg] = float(1.0 / sqrt(double(b)));
+      ++p.nseg;
+      if (b > max_len) max_len = b;
+      off += b;
+    }
+  }
+  const size_t smem = size_t(max_len) * sizeof(float);
+  static bool configured[64] = {false};
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    B200LUT_CUDA_OK(cudaFuncSetAttribute(fht_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kMaxPoints * int(sizeof(float))));
+    configured[dev] = true;
+  }
+  int threads = max_len / 2;
+  if (threads > 1024) threads = 1024;
+  if (threads < 32) threads = 32;
+  fht_kernel<<<dim3(unsigned(M), unsigned(p.nseg)), threads, smem, cudaStream_t(stream)>>>(p);
+  B200LUT_CUDA_OK(cudaGetLastError());
+  return B200LUT_OK;
+}

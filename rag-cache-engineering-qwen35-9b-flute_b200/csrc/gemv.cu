@@ -1,0 +1,604 @@
+// Decode-time LUT GEMV (M <= 16) for sm_100a.
+//
+// y[m, n] = sum_k x[m, k] * LUT[n / gs][code(n, k)], fp32 accumulation, one rounding.
+// Replaces the reference's M = 1 streamers and their split-K / merged variants
+// (src/flute_extended/src/kernel_gemv.cu:92-253, kernel_gemv_splitk.cu:135-409,
+// kernel_gemv_multi.cu:101-334, kernel_gemv_mlp.cu:92-450).
+//
+// Design (one block per (128-row tile, K split), one block per SM):
+//  * The packed codes are streamed once from HBM with 256-bit loads per lane, fully
+//    coalesced (a warp reads 1 KB contiguous per instruction), straight into
+//    registers, one 128-row x 64-k chunk (4 KB at 4 bits) ahead of the math.
+//  * A pair of codes (2*bits bits) is turned into a packed pair of 16-bit palette
+//    entries by ONE shared-memory load from a "pair table" (4^bits entries). The
+//    table is replicated 32 times so that lane L only ever touches bank L: entry e
+//    of slot s lives at table + e*256 + s*128 + 4*L. The table is 64 KB aligned in
+//    the shared window, so the load address is formed by a single byte permute of
+//    (code word, lane base) — no shift, mask or add per lookup.
+//  * The looked-up pairs ARE the A fragments of mma.m16n8k16 (the slab layout is
+//    that register order); x supplies the B fragment (batch rows in the n8 columns).
+//    Tensor-core math is far off the critical path; it removes the 16->32-bit
+//    conversions and FMAs a scalar GEMV would spend its issue slots on.
+//  * Warps split the block's K range chunk by chunk; partial sums meet in shared
+//    memory in a fixed order. K splits of one tile form a thread-block cluster and
+//    are folded through distributed shared memory in rank order (deterministic, no
+//    atomics on data, no scratch). Splits wider than a cluster (9..16) use an fp32
+//    workspace and a last-arrival ticket, also folded in index order.
+//  * The kernel is written for programmatic dependent launch: code prefetch and
+//    table build run before griddepcontrol.wait, so they overlap the previous
+//    kernel's tail; only x depends on the predecessor.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace b200lut {
+namespace {
+
+constexpr int kMaxSeg = 8;
+constexpr int kMaxM = 16;
+constexpr uint32_t kTableBytes = 65536;   // one pair table: 256 entries x 256 B (two slots)
+constexpr uint32_t kPartBytes = 2 * kMaxM * kTileRows * 4;  // two result planes (gate/up)
+constexpr int kMaxClusterSplit = 8;
+
+struct SegDev {
+  const uint8_t* packed;
+  const uint16_t* lut;
+  const uint8_t* packed2;
+  const uint16_t* lut2;
+  const uint16_t* bias;
+  uint16_t* out;
+  long long ldo;
+  int N, gs, n_groups, bits, bits2, tile_begin;
+};
+
+struct GemvParams {
+  const uint16_t* x;
+  long long ldx;
+  int M, K, G, nseg, split, epilogue, tiles_total, cluster;
+  float* ws;       // workspace fold: [split][tiles_total][planes][M][128] fp32
+  int* tickets;    // workspace fold: [tiles_total]
+  SegDev seg[kMaxSeg];
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// 256-bit streaming load: read-only path, no L1 allocation, first in line for L2 eviction
+__device__ __forceinline__ void ldg_stream256(uint32_t* r, const uint8_t* p) {
+  asm volatile(
+      "ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7])
+      : "l"(p));
+}
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4],
+                                                        uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&d)[4], const uint32_t (&a)[4],
+                                                 uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Shared-memory address of the pair-table entry of field i of slab s.
+// base = 64 KB-aligned table address + slot*128 + lane*4 (bits 8..15 zero).
+template <int BITS>
+__device__ __forceinline__ uint32_t field_addr(const uint32_t (&w)[8 * BITS], int s, int i,
+                                               uint32_t base) {
+  if constexpr (BITS == 4) {
+    // field = byte (i & 3) of word 4s + (i >> 2): place it in address bits 8..15
+    return __byte_perm(w[4 * s + (i >> 2)], base, 0x7604u | (uint32_t(i & 3) << 4));
+  } else {
+    constexpr uint32_t kMask = ((1u << (2 * BITS)) - 1u) << 8;
+    const int pos = 32 * BITS * s + 2 * BITS * i, m = pos >> 5, sh = pos & 31;
+    uint32_t v;
+    if (sh + 2 * BITS > 32) v = __funnelshift_r(w[m], w[(m + 1) % (8 * BITS)], sh - 8);
+    else if (sh >= 8) v = w[m] >> (sh - 8);
+    else v = w[m] << (8 - sh);
+    return (v & kMask) | base;
+  }
+}
+
+// Fill the pair table(s) of one pass: entry v -> LUT[v & mask] | LUT[v >> bits] << 16,
+// one table slot per distinct palette of the tile (nl = 1, 2 or 4 palettes per tile).
+__device__ void build_tables(uint8_t* tbl_ptr, const uint16_t* __restrict__ lut, int bits,
+                             int n_groups, int row0, int gs, int nl, int nthreads) {
+  const int entries = 1 << (2 * bits);
+  const uint32_t mask = (1u << bits) - 1u;
+  const int rows_per_lut = kTileRows / nl;
+  for (int idx = threadIdx.x; idx < nl * entries * 8; idx += nthreads) {
+    const int q = idx & 7, e = (idx >> 3) & (entries - 1), sl = idx >> (3 + 2 * bits);
+    int grp = (row0 + sl * rows_per_lut) / gs;
+    if (grp > n_groups - 1) grp = n_groups - 1;
+    const uint16_t* row = lut + (size_t(grp) << bits);
+    const uint32_t v = uint32_t(__ldg(row + (e & mask))) | (uint32_t(__ldg(row + (e >> bits))) << 16);
+    uint4* dst = reinterpret_cast<uint4*>(tbl_ptr + size_t(sl >> 1) * kTableBytes + e * 256 +
+                                          (sl & 1) * 128 + q * 16);
+    *dst = make_uint4(v, v, v, v);
+  }
+}
+
+template <int BITS>
+__device__ __forceinline__ void load_chunk(uint32_t (&w)[8 * BITS], const uint8_t* chunk_lane) {
+#pragma unroll
+  for (int p = 0; p < BITS; ++p) ldg_stream256(&w[8 * p], chunk_lane + p * 1024);
+}
+
+template <int NB>
+__device__ __forceinline__ void load_x(uint2 (&xf)[NB][4], const uint16_t* __restrict__ x,
+                                       long long ldx, int M, int k0, int gid, int tig) {
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+    const int m = gid + 8 * nb;
+#pragma unroll
+    for (int kt = 0; kt < 4; ++kt) {
+      xf[nb][kt] = make_uint2(0u, 0u);
+      if (m < M)
+        xf[nb][kt] = *reinterpret_cast<const uint2*>(x + size_t(m) * ldx + k0 + 16 * kt + 4 * tig);
+    }
+  }
+}
+
+// One pass: stream the codes of (segment stream, tile) over the block's chunk range
+// and leave the per-warp accumulators in acc (fragment layout).
+template <typename T, int BITS, int NB, int NWARPS>
+__device__ __forceinline__ void stream_pass(float (&acc)[NB][8][4], const uint8_t* __restrict__ packed,
+                                            int tile, int G, int c0, int c1,
+                                            const uint16_t* __restrict__ x, long long ldx, int M,
+                                            uint32_t tbl_lane, int slot_shift, bool first_pass) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const size_t chunk_bytes = size_t(1024) * BITS;
+  const uint8_t* lane_base = packed + (size_t(tile) * G) * chunk_bytes + lane * 32;
+
+  // Single register buffer, refilled plane by plane: as soon as the last field of a
+  // 1 KB plane (8 words per lane) has been looked up, the same registers receive the
+  // next chunk's plane, so a whole chunk per warp is always in flight.
+  uint32_t w[8 * BITS];
+  int c = c0 + warp;
+  if (c < c1) load_chunk<BITS>(w, lane_base + size_t(c) * chunk_bytes);
+  if (first_pass) {
+    // everything above is independent of the previous kernel in the stream
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
+  for (; c < c1; c += NWARPS) {
+    const bool more = c + NWARPS < c1;
+    const uint8_t* next = lane_base + size_t(c + NWARPS) * chunk_bytes;
+    uint2 xf[NB][4];
+    load_x<NB>(xf, x, ldx, M, c * kChunkK, gid, tig);
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      const int slot = s >> slot_shift;
+      const uint32_t base = tbl_lane + uint32_t(slot >> 1) * kTableBytes + uint32_t(slot & 1) * 128u;
+#pragma unroll
+      for (int kt = 0; kt < 4; ++kt) {
+        uint32_t a[4];
+#pragma unroll
+        for (int f = 0; f < 4; ++f) a[f] = lds32(field_addr<BITS>(w, s, 4 * kt + f, base));
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) mma16816<T>(acc[nb][s], a, xf[nb][kt].x, xf[nb][kt].y);
+      }
+#pragma unroll
+      for (int pl = (s * BITS) / 8; pl < ((s + 1) * BITS) / 8; ++pl)
+        if (more) ldg_stream256(&w[8 * pl], next + pl * 1024);
+    }
+  }
+}
+
+template <typename T, int NB, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  constexpr int NT = NWARPS * 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+
+  float* part = reinterpret_cast<float*>(smem);   // [plane][m][row]
+  const uint32_t part_addr = smem_u32(smem);
+  const uint32_t tbl_addr = (part_addr + kPartBytes + 0xFFFFu) & ~0xFFFFu;
+  uint8_t* tbl_ptr = smem + (tbl_addr - part_addr);
+  float* red = reinterpret_cast<float*>(tbl_ptr);  // aliases the tables after the pass
+
+  // which tile / split is this block
+  const int split = p.split;
+  const int tile_g = blockIdx.x / split, sp = blockIdx.x % split;
+  const int c0 = (p.G * sp) / split, c1 = (p.G * (sp + 1)) / split;
+
+  const bool silu = p.epilogue == B200LUT_EPI_SILU_MUL;
+  // plain: one segment per tile. silu-mul: segments come in (gate, up) pairs that
+  // share the tile index; both are computed by this block, one after the other.
+  int si = 0;
+  {
+    const int step = silu ? 2 : 1;
+    for (int s = 0; s < p.nseg; s += step)
+      if (tile_g >= p.seg[s].tile_begin) si = s;
+  }
+  const int tile = tile_g - p.seg[si].tile_begin;
+  const int nplanes = silu ? 2 : 1;
+
+  asm volatile("griddepcontrol.launch_dependents;");
+
+  const int M = p.M;
+  bool first = true;
+  for (int plane = 0; plane < nplanes; ++plane) {
+    const SegDev& sg = p.seg[si + plane];
+    const int npass = sg.packed2 ? 2 : 1;
+    for (int pass = 0; pass < npass; ++pass) {
+      const uint8_t* packed = pass ? sg.packed2 : sg.packed;
+      const uint16_t* lut = pass ? sg.lut2 : sg.lut;
+      const int bits = pass ? sg.bits2 : sg.bits;
+      int nl = kTileRows / sg.gs;
+      if (nl < 1) nl = 1;
+      const int slot_shift = nl == 1 ? 3 : (nl == 2 ? 2 : 1);
+      if (!first) __syncthreads();   // the reduction buffer aliases the tables
+      build_tables(tbl_ptr, lut, bits, sg.n_groups, tile * kTileRows, sg.gs, nl, NT);
+      __syncthreads();
+
+      float acc[NB][8][4];
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+#pragma unroll
+          for (int r = 0; r < 4; ++r) acc[nb][s][r] = 0.f;
+
+      const uint32_t tbl_lane = tbl_addr + lane * 4;
+      switch (bits) {   // block-uniform
+        case 4:
+          stream_pass<T, 4, NB, NWARPS>(acc, packed, tile, p.G, c0, c1, p.x, p.ldx, M, tbl_lane,
+                                        slot_shift, first);
+          break;
+        case 3:
+          stream_pass<T, 3, NB, NWARPS>(acc, packed, tile, p.G, c0, c1, p.x, p.ldx, M, tbl_lane,
+                                        slot_shift, first);
+          break;
+        case 2:
+          stream_pass<T, 2, NB, NWARPS>(acc, packed, tile, p.G, c0, c1, p.x, p.ldx, M, tbl_lane,
+                                        slot_shift, first);
+          break;
+        default:
+          stream_pass<T, 1, NB, NWARPS>(acc, packed, tile, p.G, c0, c1, p.x, p.ldx, M, tbl_lane,
+                                        slot_shift, first);
+          break;
+      }
+      first = false;
+      __syncthreads();   // all warps are done with the tables
+
+      // cross-warp fold, 8 batch columns at a time: red[warp][m & 7][row]
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        if (nb) __syncthreads();
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int row = 16 * s + gid + 8 * (r >> 1), mm = 2 * tig + (r & 1);
+            red[(warp * 8 + mm) * kTileRows + row] = acc[nb][s][r];
+          }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 8 * kTileRows; idx += NT) {
+          const int mm = idx >> 7, row = idx & 127, m = mm + 8 * nb;
+          if (m < M) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < NWARPS; ++w) v += red[(w * 8 + mm) * kTileRows + row];
+            float* dst = part + (plane * kMaxM + m) * kTileRows + row;
+            *dst = pass ? *dst + v : v;
+          }
+        }
+      }
+    }
+  }
+  // part[plane][m][row] now holds this block's K-range contribution.
+
+  const SegDev& s0 = p.seg[si];
+  const int n0 = tile * kTileRows;
+  auto finish = [&](int m, int row, float a, float b) {
+    const int n = n0 + row;
+    if (s0.bias) a += DType<T>::to_float(s0.bias[n]);
+    float v = a;
+    if (silu) {
+      const SegDev& s1 = p.seg[si + 1];
+      if (s1.bias) b += DType<T>::to_float(s1.bias[n]);
+      v = a / (1.f + __expf(-a)) * b;
+    }
+    s0.out[size_t(m) * s0.ldo + n] = DType<T>::from_float(v);
+  };
+
+  if (split == 1) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < M * kTileRows; idx += NT) {
+      const int m = idx >> 7, row = idx & 127;
+      finish(m, row, part[m * kTileRows + row],
+             silu ? part[(kMaxM + m) * kTileRows + row] : 0.f);
+    }
+    return;
+  }
+
+  if (p.cluster) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();   // every rank's part[] is complete and visible
+    const int rank = int(cluster.block_rank());
+    const int r0 = (kTileRows * rank) / split, r1 = (kTileRows * (rank + 1)) / split;
+    const int nrows = r1 - r0;
+    for (int idx = threadIdx.x; idx < M * nrows; idx += NT) {
+      const int m = idx / nrows, row = r0 + idx % nrows;
+      float a = 0.f, b = 0.f;
+      for (int q = 0; q < split; ++q) {   // fixed rank order
+        const float* peer = cluster.map_shared_rank(part, q);
+        a += peer[m * kTileRows + row];
+        if (silu) b += peer[(kMaxM + m) * kTileRows + row];
+      }
+      finish(m, row, a, b);
+    }
+    cluster.sync();   // keep shared memory alive until every peer has read it
+    return;
+  }
+
+  // workspace fold: partials to global, last-arrival block folds in split order
+  {
+    __syncthreads();
+    const size_t plane_elems = size_t(M) * kTileRows;
+    const size_t tile_elems = size_t(nplanes) * plane_elems;
+    float* mine = p.ws + (size_t(sp) * p.tiles_total + tile_g) * tile_elems;
+    for (int idx = threadIdx.x; idx < int(tile_elems); idx += NT) {
+      const int pl = idx / int(plane_elems), rem = idx % int(plane_elems);
+      mine[idx] = part[(pl * kMaxM + rem / kTileRows) * kTileRows + rem % kTileRows];
+    }
+    __threadfence();
+    __syncthreads();
+    __shared__ int is_last;
+    if (threadIdx.x == 0) {
+      const int old = atomicAdd(p.tickets + tile_g, 1);
+      is_last = (old == split - 1);
+      if (is_last) p.tickets[tile_g] = 0;   // self-resetting: ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < M * kTileRows; idx += NT) {
+      const int m = idx >> 7, row = idx & 127;
+      float a = 0.f, b = 0.f;
+      for (int q = 0; q < split; ++q) {
+        const float* src = p.ws + (size_t(q) * p.tiles_total + tile_g) * tile_elems;
+        a += __ldcg(src + m * kTileRows + row);
+        if (silu) b += __ldcg(src + plane_elems + m * kTileRows + row);
+      }
+      finish(m, row, a, b);
+    }
+  }
+}
+
+size_t smem_bytes_for(int max_tables) {
+  return size_t(kPartBytes) + 65536 + size_t(max_tables) * kTableBytes;
+}
+
+template <typename T, int NB, int NWARPS>
+int launch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t stream) {
+  auto kern = gemv_kernel<T, NB, NWARPS>;
+  const size_t smem = smem_bytes_for(max_tables);
+  static size_t configured[64] = {0};
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && configured[dev] < smem) {
+    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         int(smem_bytes_for(2))));
+    configured[dev] = smem_bytes_for(2);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(p.tiles_total * p.split), 1, 1);
+  cfg.blockDim = dim3(NWARPS * 32, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (p.cluster) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = unsigned(p.split);
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = unsigned(na);
+  B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
+  return B200LUT_OK;
+}
+
+int sm_count_cached() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+constexpr int kWarpsM8 = 16, kWarpsM16 = 8;
+
+// Split policy: one block per SM is resident. Cost of a candidate = waves of blocks
+// times the chunks the busiest warp streams, plus a small per-split fold charge.
+int pick_split(int tiles, int G, int sms, int warps) {
+  int best = 1;
+  long best_cost = -1;
+  for (int s = 1; s <= kMaxClusterSplit; ++s) {
+    if (s > G) break;
+    const long blocks = long(tiles) * s;
+    const long waves = (blocks + sms - 1) / sms;
+    const long per_block = (G + s - 1) / s;
+    const long per_warp = (per_block + warps - 1) / warps;
+    const long cost = waves * per_warp * 16 + (s > 1 ? 2 + s / 4 : 0);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+  }
+  return best;
+}
+
+}  // namespace
+}  // namespace b200lut
+
+using namespace b200lut;
+
+extern "C" int b200lut_sm_count(void) { return sm_count_cached(); }
+
+extern "C" int b200lut_gemv_pick_split(int tiles, int K) {
+  if (tiles <= 0 || K <= 0) return 1;
+  return pick_split(tiles, K / kChunkK, sm_count_cached(), kWarpsM8);
+}
+
+extern "C" size_t b200lut_gemv_workspace_bytes(int total_rows, int M, int split) {
+  if (split <= kMaxClusterSplit || total_rows <= 0 || M <= 0) return 0;
+  const size_t tiles = size_t(total_rows) / kTileRows;
+  // two planes (gate/up) of fp32 partials per split and tile, then the tickets
+  return size_t(split) * tiles * 2 * size_t(M) * kTileRows * 4 + tiles * 4;
+}
+
+extern "C" int b200lut_gemv_multi(const void* x, int64_t ldx, int M, int K, int dtype,
+                                  const b200lut_segment* segs, int nseg, int epilogue, int split,
+                                  void* workspace, size_t workspace_bytes, int flags,
+                                  void* stream) {
+  B200LUT_REQUIRE(x && segs, B200LUT_ERR_INVALID, "null x or segment table");
+  B200LUT_REQUIRE(M >= 1 && M <= kMaxM, B200LUT_ERR_UNSUPPORTED,
+                  "decode GEMV serves 1 <= M <= 16, got M=%d (use b200lut_gemm)", M);
+  B200LUT_REQUIRE(K > 0 && K % kChunkK == 0, B200LUT_ERR_INVALID,
+                  "K must be a positive multiple of 64, got %d", K);
+  B200LUT_REQUIRE(nseg >= 1 && nseg <= kMaxSeg, B200LUT_ERR_INVALID,
+                  "1..%d segments per launch, got %d", kMaxSeg, nseg);
+  B200LUT_REQUIRE(dtype == B200LUT_BF16 || dtype == B200LUT_F16, B200LUT_ERR_INVALID,
+                  "dtype must be B200LUT_BF16 or B200LUT_F16");
+  B200LUT_REQUIRE(epilogue == B200LUT_EPI_NONE || epilogue == B200LUT_EPI_SILU_MUL,
+                  B200LUT_ERR_INVALID, "unknown epilogue %d", epilogue);
+  B200LUT_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K, B200LUT_ERR_ALIGN,
+                  "x must be 16-byte aligned with a row stride that is a multiple of 8 and >= K");
+  const bool silu = epilogue == B200LUT_EPI_SILU_MUL;
+  B200LUT_REQUIRE(!silu || nseg % 2 == 0, B200LUT_ERR_INVALID,
+                  "the silu-mul epilogue needs (gate, up) segment pairs");
+
+  GemvParams p = {};
+  p.x = static_cast<const uint16_t*>(x);
+  p.ldx = ldx;
+  p.M = M;
+  p.K = K;
+  p.G = K / kChunkK;
+  p.nseg = nseg;
+  p.epilogue = epilogue;
+  int tiles = 0, max_tables = 1;
+  for (int i = 0; i < nseg; ++i) {
+    const b200lut_segment& s = segs[i];
+    B200LUT_REQUIRE(s.packed && s.lut, B200LUT_ERR_INVALID, "segment %d: null codes or palette", i);
+    B200LUT_REQUIRE(s.N > 0 && s.N % kTileRows == 0, B200LUT_ERR_INVALID,
+                    "segment %d: N must be a positive multiple of 128, got %d", i, s.N);
+    B200LUT_REQUIRE(s.bits >= 1 && s.bits <= 4, B200LUT_ERR_INVALID,
+                    "segment %d: stream-1 width must be 1..4, got %d", i, s.bits);
+    const bool has2 = s.packed2 != nullptr;
+    B200LUT_REQUIRE(!has2 || (s.lut2 && s.bits2 >= 1 && s.bits2 <= 4), B200LUT_ERR_INVALID,
+                    "segment %d: stream-2 needs a palette and a width of 1..4 (got %d)", i,
+                    s.bits2);
+    B200LUT_REQUIRE(s.group_size >= 32 && s.n_groups >= 1 &&
+                        ((s.group_size < 128 && (s.group_size & (s.group_size - 1)) == 0) ||
+                         s.group_size % 128 == 0),
+                    B200LUT_ERR_UNSUPPORTED,
+                    "segment %d: group_size %d not served (32, 64 or a multiple of 128)", i,
+                    s.group_size);
+    B200LUT_REQUIRE(aligned16(s.packed) && (!has2 || aligned16(s.packed2)), B200LUT_ERR_ALIGN,
+                    "segment %d: code buffers must be 16-byte aligned", i);
+    const bool writes = !silu || (i % 2 == 0);
+    B200LUT_REQUIRE(!writes || (s.out && s.ldo >= s.N), B200LUT_ERR_INVALID,
+                    "segment %d: null output or row stride < N", i);
+    if (silu && (i % 2 == 1))
+      B200LUT_REQUIRE(s.N == segs[i - 1].N, B200LUT_ERR_INVALID,
+                      "gate and up segments must have the same N (%d vs %d)", segs[i - 1].N, s.N);
+    SegDev& d = p.seg[i];
+    d.packed = static_cast<const uint8_t*>(s.packed);
+    d.lut = static_cast<const uint16_t*>(s.lut);
+    d.packed2 = static_cast<const uint8_t*>(s.packed2);
+    d.lut2 = static_cast<const uint16_t*>(s.lut2);
+    d.bias = static_cast<const uint16_t*>(s.bias);
+    d.out = static_cast<uint16_t*>(s.out);
+    d.ldo = s.ldo;
+    d.N = s.N;
+    d.gs = s.group_size;
+    d.n_groups = s.n_groups;
+    d.bits = s.bits;
+    d.bits2 = has2 ? s.bits2 : 0;
+    if (silu && (i % 2 == 1)) {
+      d.tile_begin = p.seg[i - 1].tile_begin;
+    } else {
+      d.tile_begin = tiles;
+      tiles += s.N / kTileRows;
+    }
+    const int nl = s.group_size >= 128 ? 1 : 128 / s.group_size;
+    if ((nl + 1) / 2 > max_tables) max_tables = (nl + 1) / 2;
+  }
+  p.tiles_total = tiles;
+  const int warps = M <= 8 ? kWarpsM8 : kWarpsM16;
+  if (split <= 0) split = pick_split(tiles, p.G, sm_count_cached(), warps);
+  B200LUT_REQUIRE(split >= 1 && split <= 16 && split <= p.G, B200LUT_ERR_INVALID,
+                  "split must be 1..16 and <= K/64, got %d", split);
+  p.split = split;
+  p.cluster = (split > 1 && split <= kMaxClusterSplit) ? 1 : 0;
+  if (split > kMaxClusterSplit) {
+    size_t rows = size_t(tiles) * kTileRows;
+    const size_t need = b200lut_gemv_workspace_bytes(int(rows), M, split);
+    B200LUT_REQUIRE(workspace && workspace_bytes >= need, B200LUT_ERR_WORKSPACE,
+                    "split %d needs %zu workspace bytes, got %zu", split, need, workspace_bytes);
+    B200LUT_REQUIRE(aligned16(workspace), B200LUT_ERR_ALIGN, "workspace must be 16-byte aligned");
+    p.ws = static_cast<float*>(workspace);
+    p.tickets = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) +
+                                       size_t(split) * tiles * 2 * size_t(M) * kTileRows * 4);
+  }
+  const bool pdl = (flags & 1) != 0;
+  cudaStream_t st = cudaStream_t(stream);
+  if (dtype == B200LUT_BF16) {
+    return M <= 8 ? launch<__nv_bfloat16, 1, kWarpsM8>(p, max_tables, pdl, st)
+                  : launch<__nv_bfloat16, 2, kWarpsM16>(p, max_tables, pdl, st);
+  }
+  return M <= 8 ? launch<__half, 1, kWarpsM8>(p, max_tables, pdl, st)
+                : launch<__half, 2, kWarpsM16>(p, max_tables, pdl, st);
+}
+
+extern "C" int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out, int M,
+                            int N, int K, int bits, int group_size, int n_groups, int dtype,
+                            int split, void* workspace, size_t workspace_bytes, void* stream) {
+  b200lut_segment s = {};
+  s.packed = packed;
+  s.lut = lut;
+  s.out = out;
+  s.ldo = N;
+  s.N = N;
+  s.group_size = group_size;
+  s.n_groups = n_groups;
+  s.bits = bits;
+  return b200lut_gemv_multi(x, K, M, K, dtype, &s, 1, B200LUT_EPI_NONE, split, workspace,
+                            workspace_bytes, 0, stream);
+}

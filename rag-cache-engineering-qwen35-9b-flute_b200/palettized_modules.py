@@ -1,0 +1,419 @@
+"""Runtime modules of the LUT-palettized linear layer on B200.
+
+Drop-in for the linear modules of the reference's
+src/scripts/palettized_modules.py: PalettizedLinear (:413-1369, same constructor
+signature and attribute names), SplitQKV (:1390-1466), FusedPalettizedMLP
+(:1643-1723) and reference_dequant (:125-162). Every forward runs on the CUDA
+library (libb200lut.so); there is no torch/CPU compute fallback:
+
+  M <= 16  -> b200lut_gemv_multi  (decode GEMV; split-K, merged QKV, fused gate/up)
+  M  > 16  -> b200lut_gemm        (prefill GEMM on tcgen05 / TMEM)
+  rotation -> b200lut_fht in front of either
+  reference=True -> the same arithmetic as the reference's torch route
+                    (dequantise exactly, fp32 matmul, one rounding), on the GPU.
+
+Weights: W[n, k] = LUT[min(n // group_size, G-1)][idx[n, k]] — groups run along
+the output rows, one palette row serves all of K. The module receives the idxN
+blob and converts it once, on the device, into the library's slab layout.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from . import _lib
+from . import fht as _fht
+from . import idxN as _idxn
+
+GEMV_MAX_M = 16
+_LAUNCH_FLAGS = {"pdl": os.environ.get("B200LUT_PDL", "0").strip() in ("1", "true", "True")}
+_workspaces = {}
+
+
+def set_programmatic_launch(enabled: bool) -> None:
+    """Launch decode kernels with programmatic dependent launch (their weight
+    prefetch then overlaps the previous kernel's tail)."""
+    _LAUNCH_FLAGS["pdl"] = bool(enabled)
+
+
+def _flags() -> int:
+    return _lib.FLAG_PDL if _LAUNCH_FLAGS["pdl"] else 0
+
+
+def _workspace(device, nbytes: int) -> Optional[torch.Tensor]:
+    """Per-device zero-initialised scratch for splits wider than a cluster."""
+    if nbytes == 0:
+        return None
+    ws = _workspaces.get(str(device))
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[str(device)] = ws
+    return ws
+
+
+def reference_dequant(indices_blob, lut, N: int, K: int, group_size: int,
+                      bitwidth: int = 4) -> torch.Tensor:
+    """W[n, k] = LUT[n // gs, idx(n, k)] as an (N, K) fp32 tensor on the LUT's
+    (CUDA) device, computed by the library's dequant export (exact lookups)."""
+    if bitwidth not in (1, 2, 3, 4):
+        raise ValueError(f"reference_dequant supports bitwidths 1-4, got {bitwidth}")
+    lut_t = lut if torch.is_tensor(lut) else torch.from_numpy(np.asarray(lut))
+    if not lut_t.is_cuda:
+        raise RuntimeError("reference_dequant: the LUT must live on a CUDA device")
+    blob = indices_blob if torch.is_tensor(indices_blob) else torch.from_numpy(np.asarray(indices_blob))
+    blob = blob.to(lut_t.device)
+    lut16 = lut_t if lut_t.dtype in (torch.float16, torch.bfloat16) else None
+    packed = _lib.repack_from_idxn(blob, N, K, bitwidth)
+    if lut16 is not None:
+        return _lib.dequant(packed, lut16.reshape(-1, 1 << bitwidth), N, K, bitwidth, group_size).float()
+    # fp32 palettes (training masters): gather with the exported codes
+    codes = _lib.unpack_codes(packed, N, K, bitwidth).long()
+    pal = lut_t.reshape(-1, 1 << bitwidth)
+    rg = (torch.arange(N, device=pal.device) // int(group_size)).clamp_(max=pal.shape[0] - 1)
+    return pal[rg].float().gather(1, codes)
+
+
+class PalettizedLinear(nn.Module):
+    """y = x @ W^T (+ second stream, + low-rank residual, + bias), W palettized.
+
+    Arguments as in the reference constructor (palettized_modules.py:413-417):
+    indices: idxN blob (uint8, N*K*bitwidth/8 bytes); lut: [ceil(N/gs), 2**bitwidth]
+    fp16 or bf16; optional second stream (indices2, lut2, bitwidth2), residual
+    factors resA [N, R] / resB [R, K], bias [N]; rotation_seed/rotation_k enable
+    the Hadamard input rotation (signs drawn as the palettizer does);
+    awq_scale + fold_order="rotate_then_awq" select the compensated rotation.
+    """
+
+    def __init__(self, indices, lut, bitwidth, group_size, N, K, bias=None,
+                 resA=None, resB=None, indices2=None, lut2=None,
+                 bitwidth2=None, reference: bool = False,
+                 rotation_seed: int = None, rotation_k: int = None,
+                 awq_scale=None, fold_order: str = None):
+        super().__init__()
+        self.bitwidth = int(bitwidth)
+        self.group_size = int(group_size)
+        self.bitwidth2 = int(bitwidth2) if bitwidth2 is not None else self.bitwidth
+        self.N, self.K = int(N), int(K)
+        self.reference = bool(reference)
+        if self.N % 128 != 0 or self.K % 64 != 0:
+            raise ValueError(f"idxN layout requires N%128==0 and K%64==0, got N={self.N}, K={self.K}")
+        for name, b in (("stream-1", self.bitwidth), ("stream-2", self.bitwidth2)):
+            if b not in (1, 2, 3, 4):
+                raise ValueError(f"PalettizedLinear: {name} bitwidth must be 1-4, got {b}")
+        indices = torch.as_tensor(indices)
+        expected = (self.N * self.K * self.bitwidth) // 8
+        if indices.numel() != expected:
+            raise ValueError(f"idx{self.bitwidth} blob numel {indices.numel()} != "
+                             f"N*K*{self.bitwidth}/8 {expected} (N={self.N}, K={self.K})")
+        self.register_buffer("indices", indices, persistent=False)
+        self.register_buffer("lut", self._lut2d(lut, self.bitwidth), persistent=False)
+        if resA is not None and resB is not None:
+            if resA.shape != (self.N, resB.shape[0]) or resB.shape[1] != self.K:
+                raise ValueError(f"residual factors shape mismatch: A {tuple(resA.shape)}, "
+                                 f"B {tuple(resB.shape)} for N={self.N}, K={self.K}")
+            self.register_buffer("resA", resA, persistent=False)
+            self.register_buffer("resB", resB, persistent=False)
+        else:
+            self.resA = self.resB = None
+        if indices2 is None and lut2 is None:
+            self.indices2 = self.lut2 = None
+        elif indices2 is None or lut2 is None:
+            raise ValueError("PalettizedLinear: a second stream needs BOTH indices2 and lut2; "
+                             "refusing a half-constructed two-stream module")
+        else:
+            indices2 = torch.as_tensor(indices2)
+            expected2 = (self.N * self.K * self.bitwidth2) // 8
+            if indices2.numel() != expected2:
+                raise ValueError(f"idx{self.bitwidth2} stream-2 blob numel {indices2.numel()} != "
+                                 f"N*K*{self.bitwidth2}/8 {expected2} (N={self.N}, K={self.K})")
+            lut2_t = self._lut2d(lut2, self.bitwidth2)
+            if lut2_t.shape[0] != self.lut.shape[0]:
+                raise ValueError(f"stream-2 LUT groups {lut2_t.shape[0]} != stream-1 "
+                                 f"{self.lut.shape[0]}; both streams must share the group grid")
+            self.register_buffer("indices2", indices2, persistent=False)
+            self.register_buffer("lut2", lut2_t, persistent=False)
+        if bias is not None:
+            self.bias = nn.Parameter(bias, requires_grad=False)
+        else:
+            self.register_parameter("bias", None)
+        # rotation (Hadamard boundary fold; None = unrotated)
+        self.rotation_seed = int(rotation_seed) if rotation_seed is not None else None
+        self.rotation_k = int(rotation_k) if rotation_k is not None else None
+        self.fold_order = fold_order if fold_order in ("awq_then_rotate", "rotate_then_awq") else None
+        self.rot_signs = None
+        self.awq_scale = None
+        self._dev_cache = {}
+        if self.rotation_seed is not None and self.rotation_k is not None:
+            if self.rotation_k != self.K:
+                raise ValueError(f"PalettizedLinear: rotation_k {self.rotation_k} != the input "
+                                 f"dim K {self.K} — the boundary fold is defined on the input axis")
+            self.rot_signs = _fht.rotation_signs(self.rotation_k, self.rotation_seed)
+            if awq_scale is not None:
+                st = torch.as_tensor(awq_scale, dtype=torch.float32).detach().cpu()
+                if st.dim() != 1 or st.numel() != self.K:
+                    raise ValueError(f"PalettizedLinear: awq_scale must be a (K,) vector for "
+                                     f"K={self.K}, got {tuple(st.shape)}")
+                if not torch.isfinite(st).all() or bool((st <= 0).any()):
+                    raise ValueError("PalettizedLinear: awq_scale must be finite and > 0 per channel")
+                self.awq_scale = st
+                if self.fold_order is None:
+                    self.fold_order = "rotate_then_awq"
+        elif awq_scale is not None:
+            raise ValueError("PalettizedLinear: awq_scale passed without rotation metadata")
+        self._packed = None
+        self._packed2 = None
+
+    @staticmethod
+    def _lut2d(lut, bits):
+        t = lut if torch.is_tensor(lut) else torch.from_numpy(np.asarray(lut))
+        if t.dim() != 2:
+            t = t.view(-1, 1 << bits)
+        if t.shape[1] != (1 << bits):
+            raise ValueError(f"LUT palette width {t.shape[1]} != 2**bitwidth {1 << bits}")
+        return t
+
+    # ------------------------------------------------------------------ state
+    def has_residual(self) -> bool:
+        return self.resA is not None and self.resB is not None
+
+    @property
+    def has_stream2(self) -> bool:
+        return self.indices2 is not None and self.lut2 is not None
+
+    def _logical_indices_numpy(self, blob=None, bits=None) -> np.ndarray:
+        """(N, K) uint8 logical codes of a stream's idxN blob (host, numpy)."""
+        b = int(bits) if bits is not None else self.bitwidth
+        blob = self.indices if blob is None else blob
+        arr = np.ascontiguousarray(blob.detach().cpu().numpy(), dtype=np.uint8).reshape(-1)
+        return _idxn.unpack_idxn(arr, self.N, self.K, b)
+
+    def _on(self, name: str, t: torch.Tensor, device) -> torch.Tensor:
+        key = (name, str(device))
+        v = self._dev_cache.get(key)
+        if v is None:
+            v = t.to(device=device, dtype=torch.float32).contiguous()
+            self._dev_cache[key] = v
+        return v
+
+    def _ensure_packed(self):
+        """One-time device conversion idxN blob -> slab layout (per stream)."""
+        dev = self.lut.device
+        if not self.lut.is_cuda:
+            raise RuntimeError("PalettizedLinear: move the module to a CUDA device first "
+                               "(this package has no CPU compute route)")
+        if self._packed is None or self._packed.device != dev:
+            self._packed = _lib.repack_from_idxn(self.indices.to(dev), self.N, self.K, self.bitwidth)
+            self._packed2 = None
+        if self.has_stream2 and self._packed2 is None:
+            self._packed2 = _lib.repack_from_idxn(self.indices2.to(dev), self.N, self.K, self.bitwidth2)
+
+    def drop_blob(self) -> "PalettizedLinear":
+        """Free the idxN blob(s) once the slab copy exists (halves weight memory)."""
+        self._ensure_packed()
+        self.indices = torch.empty(0, dtype=torch.uint8, device=self.lut.device)
+        if self.has_stream2:
+            self.indices2 = torch.empty(0, dtype=torch.uint8, device=self.lut.device)
+        return self
+
+    @classmethod
+    def from_packed(cls, packed, lut, bitwidth, group_size, N, K, **kw) -> "PalettizedLinear":
+        """Build a module around codes that are already in the slab layout
+        (used by the synthetic model stack, which draws random codes on the device)."""
+        mod = cls.__new__(cls)
+        nn.Module.__init__(mod)
+        blob = torch.empty(0, dtype=torch.uint8, device=packed.device)
+        mod.bitwidth, mod.bitwidth2, mod.group_size = int(bitwidth), int(bitwidth), int(group_size)
+        mod.N, mod.K, mod.reference = int(N), int(K), False
+        mod.register_buffer("indices", blob, persistent=False)
+        mod.register_buffer("lut", cls._lut2d(lut, int(bitwidth)), persistent=False)
+        mod.resA = mod.resB = mod.indices2 = mod.lut2 = None
+        bias = kw.get("bias")
+        mod.register_parameter("bias", None if bias is None else nn.Parameter(bias, requires_grad=False))
+        mod.rotation_seed = mod.rotation_k = mod.fold_order = None
+        mod.rot_signs = mod.awq_scale = None
+        mod._dev_cache = {}
+        mod._packed, mod._packed2 = packed, None
+        if packed.numel() != N * K * bitwidth // 8:
+            raise ValueError("from_packed: wrong code buffer size")
+        return mod
+
+    # ---------------------------------------------------------------- pieces
+    def _segment_desc(self, out: Optional[torch.Tensor], ldo: Optional[int] = None,
+                      with_bias: bool = True) -> dict:
+        self._ensure_packed()
+        d = dict(packed=self._packed, lut=self.lut, N=self.N, group_size=self.group_size,
+                 n_groups=self.lut.shape[0], bits=self.bitwidth, out=out,
+                 ldo=self.N if ldo is None else ldo)
+        if self.has_stream2:
+            d.update(packed2=self._packed2, lut2=self.lut2, bits2=self.bitwidth2)
+        if with_bias and self.bias is not None:
+            d["bias"] = self.bias.data
+        return d
+
+    def _compute_dtype(self) -> torch.dtype:
+        if self.lut.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError(f"PalettizedLinear(kernel path): LUT dtype must be float16 or "
+                             f"bfloat16, got lut ({self.lut.dtype})")
+        if self.has_stream2 and self.lut2.dtype != self.lut.dtype:
+            raise ValueError("PalettizedLinear(kernel path): both LUTs must share one dtype")
+        if self.bias is not None and self.bias.dtype != self.lut.dtype:
+            raise ValueError("PalettizedLinear(kernel path): bias dtype must equal the LUT dtype")
+        return self.lut.dtype
+
+    def _rotate_input(self, x: torch.Tensor) -> torch.Tensor:
+        signs = self._on("signs", self.rot_signs, x.device)
+        if self.awq_scale is not None and self.fold_order == "rotate_then_awq":
+            return _fht.fht_apply_awq(x, signs, self._on("awq", self.awq_scale, x.device))
+        return _fht.fht_apply(x, signs)
+
+    def _kernel_matmul(self, x2: torch.Tensor) -> torch.Tensor:
+        """x2 [M, K] in the compute dtype -> [M, N] (streams + bias)."""
+        M = x2.shape[0]
+        out = torch.empty(M, self.N, dtype=x2.dtype, device=x2.device)
+        if M == 0:
+            return out
+        segs = _lib.make_segments([self._segment_desc(out)])
+        if M <= GEMV_MAX_M:
+            _lib.gemv_multi(x2, segs, 1, flags=_flags())
+        else:
+            _lib.gemm(x2, segs, flags=_flags())
+        return out
+
+    def _reference_matmul(self, x2: torch.Tensor) -> torch.Tensor:
+        """The reference route's arithmetic on the GPU: exact dequant, fp32
+        matmul per stream, ordered fp32 add, one rounding; bias added after."""
+        self._ensure_packed()
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            xf = x2.float()
+            w1 = self._dequant_stream(self._packed, self.lut, self.bitwidth)
+            y = xf @ w1.t()
+            if self.has_stream2:
+                y = y + xf @ self._dequant_stream(self._packed2, self.lut2, self.bitwidth2).t()
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
+        return y.to(x2.dtype)
+
+    def _dequant_stream(self, packed, lut, bits) -> torch.Tensor:
+        if lut.dtype in (torch.float16, torch.bfloat16):
+            return _lib.dequant(packed, lut, self.N, self.K, bits, self.group_size).float()
+        codes = _lib.unpack_codes(packed, self.N, self.K, bits).long()
+        rg = (torch.arange(self.N, device=lut.device) // self.group_size).clamp_(max=lut.shape[0] - 1)
+        return lut[rg].float().gather(1, codes)
+
+    def _quantized_weight(self) -> torch.Tensor:
+        """Effective dequantised weight W1 (+ W2), fp32 [N, K], in the module's
+        (fold-space) basis."""
+        self._ensure_packed()
+        w = self._dequant_stream(self._packed, self.lut, self.bitwidth)
+        if self.has_stream2:
+            w = w + self._dequant_stream(self._packed2, self.lut2, self.bitwidth2)
+        return w
+
+    # --------------------------------------------------------------- forward
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not x.is_cuda:
+            raise RuntimeError("PalettizedLinear.forward: x must be a CUDA tensor")
+        shape = x.shape
+        if x.shape[-1] != self.K:
+            raise ValueError(f"PalettizedLinear: input feature dim {x.shape[-1]} != K {self.K}")
+        x2 = x.reshape(-1, self.K)
+        if self.rot_signs is not None:
+            x2 = self._rotate_input(x2)
+        if self.reference:
+            out = self._reference_matmul(x2)
+            bias_done = False
+        else:
+            cd = self._compute_dtype()
+            xc = x2 if x2.dtype == cd else x2.to(cd)
+            if xc.stride(-1) != 1 or xc.stride(0) % 8 or xc.data_ptr() % 16:
+                xc = xc.contiguous().clone() if xc.data_ptr() % 16 else xc.contiguous()
+            out = self._kernel_matmul(xc).to(x.dtype)
+            bias_done = True
+        if self.has_residual():
+            xr = x2.to(self.resA.dtype)
+            out = out + ((xr @ self.resB.t()) @ self.resA.t()).to(out.dtype)
+        if self.bias is not None and not bias_done:
+            out = out + self.bias
+        return out.reshape(*shape[:-1], self.N)
+
+
+def _mergeable(mods, x: torch.Tensor) -> bool:
+    """Decode-merge verdict: M <= 16, same K, unrotated, no residual, one dtype."""
+    if x.reshape(-1, x.shape[-1]).shape[0] > GEMV_MAX_M or not x.is_cuda:
+        return False
+    m0 = mods[0]
+    for m in mods:
+        if not isinstance(m, PalettizedLinear) or m.reference or m.K != m0.K:
+            return False
+        if m.rot_signs is not None or m.has_residual() or m.lut.dtype != m0.lut.dtype:
+            return False
+        if m.lut.dtype not in (torch.float16, torch.bfloat16):
+            return False
+    return True
+
+
+class SplitQKV(nn.Module):
+    """q/k/v projections sharing one input: one merged decode launch when
+    M <= 16, else the three modules (reference palettized_modules.py:1390-1466)."""
+
+    def __init__(self, q_proj, k_proj, v_proj):
+        super().__init__()
+        self.q_proj, self.k_proj, self.v_proj = q_proj, k_proj, v_proj
+
+    def forward(self, x):
+        mods = (self.q_proj, self.k_proj, self.v_proj)
+        if os.environ.get("FLUTE_NO_MERGE", "").strip() in ("1", "true", "True") \
+                or not _mergeable(mods, x):
+            return torch.cat([m(x) for m in mods], dim=-1)
+        cd = mods[0].lut.dtype
+        x2 = x.reshape(-1, x.shape[-1]).to(cd).contiguous()
+        total = sum(m.N for m in mods)
+        out = torch.empty(x2.shape[0], total, dtype=cd, device=x.device)
+        descs, off = [], 0
+        for m in mods:
+            descs.append(m._segment_desc(out[:, off:], ldo=total))
+            off += m.N
+        _lib.gemv_multi(x2, _lib.make_segments(descs), len(descs), flags=_flags())
+        return out.to(x.dtype).reshape(*x.shape[:-1], total)
+
+
+class FusedPalettizedMLP(nn.Module):
+    """down(act(gate(x)) * up(x)); at M <= 16 with a SiLU activation the gate and
+    up projections and the SiLU*mul run as ONE launch (fp32 silu on the fp32 sums,
+    one rounding) (reference palettized_modules.py:1643-1723)."""
+
+    def __init__(self, gate_proj, up_proj, down_proj, act_fn):
+        super().__init__()
+        self.gate_proj, self.up_proj, self.down_proj = gate_proj, up_proj, down_proj
+        self.act_fn = act_fn
+
+    def _is_silu(self) -> bool:
+        return isinstance(self.act_fn, nn.SiLU) or self.act_fn in (torch.nn.functional.silu,)
+
+    def fused_gate_up(self, x2: torch.Tensor) -> torch.Tensor:
+        g, u = self.gate_proj, self.up_proj
+        out = torch.empty(x2.shape[0], g.N, dtype=x2.dtype, device=x2.device)
+        descs = [g._segment_desc(out), u._segment_desc(None)]
+        epi = _lib.EPI_SILU_MUL
+        if x2.shape[0] <= GEMV_MAX_M:
+            _lib.gemv_multi(x2, _lib.make_segments(descs), 2, epilogue=epi, flags=_flags())
+        else:
+            raise RuntimeError("fused gate/up is a decode (M <= 16) route")
+        return out
+
+    def forward(self, x):
+        mods = (self.gate_proj, self.up_proj)
+        fusable = (self._is_silu() and _mergeable(mods, x) and mods[0].N == mods[1].N
+                   and os.environ.get("FLUTE_NO_MERGE", "").strip() not in ("1", "true", "True"))
+        if not fusable:
+            return self.down_proj(self.act_fn(self.gate_proj(x)) * self.up_proj(x))
+        cd = mods[0].lut.dtype
+        x2 = x.reshape(-1, x.shape[-1]).to(cd).contiguous()
+        y = self.fused_gate_up(x2).to(x.dtype)
+        return self.down_proj(y).reshape(*x.shape[:-1], self.down_proj.N)

@@ -1,0 +1,142 @@
+"""CPU-side checks: the C-ABI library loads and exports every symbol the header
+declares, argument validation answers without touching a GPU, the host idxN tool
+matches the reference-made golden blobs, and the Python surface mirrors the
+reference's constructor contracts."""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT, load_pkg
+
+pkg = load_pkg()
+HEADER = os.path.join(ROOT, "include", "b200_lut.h")
+
+
+def _declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200lut_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = pkg._lib.lib()
+    names = _declared_symbols()
+    assert len(names) >= 14
+    for name in names:
+        assert hasattr(L, name), f"{name} declared in include/b200_lut.h but not exported"
+    assert set(names) == set(pkg._lib.EXPORTS)
+    assert L.b200lut_version() >= 100
+
+
+def test_packed_bytes_and_shape_refusals():
+    L = pkg._lib.lib()
+    assert L.b200lut_packed_bytes(4096, 4096, 4) == 4096 * 4096 // 2
+    assert L.b200lut_packed_bytes(12288, 4096, 3) == 12288 * 4096 * 3 // 8
+    assert L.b200lut_packed_bytes(100, 64, 4) == 0
+    assert L.b200lut_packed_bytes(128, 60, 4) == 0
+    assert L.b200lut_packed_bytes(128, 64, 5) == 0
+    with pytest.raises(ValueError):
+        pkg._lib.packed_bytes(128, 64, 0)
+
+
+def test_validation_errors_carry_a_message():
+    L = pkg._lib.lib()
+    rc = L.b200lut_repack_from_idxn(None, None, 100, 64, 4, None)
+    assert rc == 1 and b"multiple of 128" in L.b200lut_last_error()
+    rc = L.b200lut_gemv(None, None, None, None, 1, 128, 64, 4, 128, 1, 0, 0, None, 0, None)
+    assert rc == 1 and b"null" in L.b200lut_last_error()
+    buf = ctypes.create_string_buffer(64)
+    seg = pkg._lib.Segment()
+    seg.packed = seg.lut = seg.out = ctypes.addressof(buf) & ~15
+    seg.N, seg.group_size, seg.n_groups, seg.bits, seg.ldo = 128, 128, 1, 4, 128
+    x = ctypes.addressof(buf) & ~15
+    rc = L.b200lut_gemv_multi(x, 64, 17, 64, 0, ctypes.byref(seg), 1, 0, 0, None, 0, 0, None)
+    assert rc == 2 and b"M <= 16" in L.b200lut_last_error() or b"16" in L.b200lut_last_error()
+    seg.group_size = 48
+    rc = L.b200lut_gemv_multi(x, 64, 1, 64, 0, ctypes.byref(seg), 1, 0, 0, None, 0, 0, None)
+    assert rc == 2 and b"group_size" in L.b200lut_last_error()
+    rc = L.b200lut_fht(x, x, None, None, 1, 96, 96, 96, 0, 0, 64, None)
+    assert rc == 1 and b"block" in L.b200lut_last_error()
+
+
+def test_workspace_query():
+    L = pkg._lib.lib()
+    assert L.b200lut_gemv_workspace_bytes(4096, 1, 8) == 0        # cluster fold: no scratch
+    n = L.b200lut_gemv_workspace_bytes(4096, 1, 16)
+    assert n == 16 * 32 * 2 * 1 * 128 * 4 + 32 * 4
+
+
+@pytest.mark.parametrize("bits", (1, 2, 3, 4))
+def test_host_idxn_matches_reference_blobs(golden, bits):
+    for (N, K) in ((128, 64), (256, 128)):
+        tag = f"idxn_b{bits}_{N}x{K}"
+        idx, blob = golden.np(tag + "_idx"), golden.np(tag + "_blob")
+        assert np.array_equal(pkg.idxN.pack_idxn(idx, bits), blob)
+        assert np.array_equal(pkg.idxN.unpack_idxn(blob, N, K, bits), idx)
+
+
+def test_host_idxn_self_test_and_refusals():
+    assert pkg.idxN.self_test()
+    with pytest.raises(ValueError):
+        pkg.idxN.pack_idxn(np.zeros((64, 64), np.uint8), 4)
+    with pytest.raises(ValueError):
+        pkg.idxN.pack_idxn(np.full((128, 64), 4, np.uint8), 2)
+    with pytest.raises(ValueError):
+        pkg.idxN.unpack_idxn(np.zeros(100, np.uint8), 128, 64, 4)
+    rows = np.random.default_rng(1).integers(0, 256, size=(128, 24), dtype=np.uint8)
+    blob = pkg.idxN.pack_idxn_from_packed(rows, 3)
+    idx = pkg.idxN.unpack_idxn(blob, 128, 64, 3)
+    assert np.array_equal(np.packbits(((idx[:, :, None] >> np.arange(3)) & 1).reshape(128, -1),
+                                      axis=1, bitorder="little"), rows)
+
+
+def test_signs_and_segments_match_golden(golden):
+    for (K, seed) in ((64, 0), (1024, 7), (4096, 0), (12288, 3)):
+        s = pkg.fht.rotation_signs(K, seed)
+        assert np.array_equal(s.to(torch.int8).numpy(), golden.np(f"signs_K{K}_s{seed}"))
+    assert pkg.fht.segments(12288) == [(0, 8192), (8192, 4096)]
+    assert pkg.fht.segments(3072) == [(0, 2048), (2048, 1024)]
+    T = pkg.fht.build_rotation_matrix(64, 0)
+    assert torch.allclose(T @ T.t(), torch.eye(64), atol=1e-6)
+
+
+def test_constructor_contracts():
+    PL = pkg.PalettizedLinear
+    blob = torch.zeros(128 * 64 // 2, dtype=torch.uint8)
+    lut = torch.zeros(1, 16, dtype=torch.bfloat16)
+    m = PL(blob, lut, 4, 128, 128, 64)
+    assert (m.N, m.K, m.bitwidth, m.group_size, m.bitwidth2) == (128, 64, 4, 128, 4)
+    assert not m.has_stream2 and not m.has_residual() and m.rot_signs is None
+    with pytest.raises(ValueError, match="N%128"):
+        PL(blob, lut, 4, 128, 100, 64)
+    with pytest.raises(ValueError, match="blob numel"):
+        PL(blob[:-1], lut, 4, 128, 128, 64)
+    with pytest.raises(ValueError, match="BOTH"):
+        PL(blob, lut, 4, 128, 128, 64, indices2=blob)
+    with pytest.raises(ValueError, match="rotation_k"):
+        PL(blob, lut, 4, 128, 128, 64, rotation_seed=1, rotation_k=128)
+    with pytest.raises(ValueError, match="without rotation"):
+        PL(blob, lut, 4, 128, 128, 64, awq_scale=torch.ones(64))
+    with pytest.raises(ValueError, match="finite"):
+        PL(blob, lut, 4, 128, 128, 64, rotation_seed=1, rotation_k=64, awq_scale=torch.zeros(64))
+    r = PL(blob, lut, 4, 128, 128, 64, rotation_seed=3, rotation_k=64, awq_scale=torch.ones(64))
+    assert r.fold_order == "rotate_then_awq"
+    assert torch.equal(r.rot_signs, pkg.fht.rotation_signs(64, 3))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        m(torch.zeros(1, 64, dtype=torch.bfloat16))       # no CPU compute route
+    codes = np.random.default_rng(0).integers(0, 16, size=(128, 64), dtype=np.uint8)
+    m2 = PL(torch.from_numpy(pkg.idxN.pack_idxn(codes, 4)), lut, 4, 128, 128, 64)
+    assert np.array_equal(m2._logical_indices_numpy(), codes)
+
+
+def test_missing_library_is_loud(monkeypatch):
+    monkeypatch.setattr(pkg._lib, "_lib", None)
+    monkeypatch.setattr(pkg._lib, "LIB_PATH", "/nonexistent/libb200lut.so")
+    with pytest.raises(RuntimeError, match="missing"):
+        pkg._lib.lib()
