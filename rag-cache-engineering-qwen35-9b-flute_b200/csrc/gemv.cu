@@ -75,9 +75,25 @@ __device__ __forceinline__ void ldg_stream256(uint32_t* r, const uint8_t* p) {
       : "l"(p));
 }
 
+// Same load, executed only when `on` is non-zero; the registers keep their old value
+// otherwise (read-write operands: no select or copy after the load, so nothing waits
+// on it until the data is actually used).
+__device__ __forceinline__ void ldg_stream256_if(uint32_t* r, const uint8_t* p, uint32_t on) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %9, 0;\n\t"
+      "@q ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n\t}"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+        "+r"(r[7])
+      : "l"(p), "r"(on));
+}
+
+// Pair-table lookup. Deliberately NOT volatile, so the scheduler may issue lookups of
+// later fragments ahead of the current mma. Ordering against the barriers around the
+// table's lifetime is carried by data: every address includes a token defined after
+// the build barrier, and the accumulators are pinned before the barrier that ends it.
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
 
@@ -87,7 +103,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
 template <>
 __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4],
                                                         uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
       "{%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -96,7 +112,7 @@ __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uin
 template <>
 __device__ __forceinline__ void mma16816<__half>(float (&d)[4], const uint32_t (&a)[4],
                                                  uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
       "{%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -147,12 +163,27 @@ __device__ __forceinline__ void load_chunk(uint32_t (&w)[8 * BITS], const uint8_
   for (int p = 0; p < BITS; ++p) ldg_stream256(&w[8 * p], chunk_lane + p * 1024);
 }
 
-template <int NB>
-__device__ __forceinline__ void load_x(uint2 (&xf)[NB][4], const uint16_t* __restrict__ x,
-                                       long long ldx, int M, int k0, int gid, int tig) {
+// Batch-column plan. The n8 columns of the m16n8k16 accumulator are shared between
+// batch rows and row slabs: with CP batch columns per slab (CP = 1, 2, 4, 8), one
+// accumulator fragment serves 8/CP slabs — slab j of the group accumulates into columns
+// [j*CP, (j+1)*CP), because its B fragment carries x only in those columns (zero
+// elsewhere). At M = 1 the whole 128-row tile lives in ONE fragment (4 registers),
+// which frees the register file for codes in flight. CP = 16 is the two-fragment
+// form for 9..16 batch rows.
+template <int CP> struct Plan {
+  static constexpr int kCols = CP > 8 ? 8 : CP;          // batch columns per slab and fragment
+  static constexpr int kNB = CP > 8 ? 2 : 1;             // B fragments (batch rows gid, gid + 8)
+  static constexpr int kSlabsPerAcc = 8 / kCols;
+  static constexpr int kAcc = kCols * kNB;               // accumulator fragments
+};
+
+template <int CP>
+__device__ __forceinline__ void load_x(uint2 (&xf)[Plan<CP>::kNB][4],
+                                       const uint16_t* __restrict__ x, long long ldx, int M,
+                                       int k0, int gid, int tig) {
 #pragma unroll
-  for (int nb = 0; nb < NB; ++nb) {
-    const int m = gid + 8 * nb;
+  for (int nb = 0; nb < Plan<CP>::kNB; ++nb) {
+    const int m = gid % Plan<CP>::kCols + 8 * nb;
 #pragma unroll
     for (int kt = 0; kt < 4; ++kt) {
       xf[nb][kt] = make_uint2(0u, 0u);
@@ -162,64 +193,150 @@ __device__ __forceinline__ void load_x(uint2 (&xf)[NB][4], const uint16_t* __res
   }
 }
 
-// One pass: stream the codes of (segment stream, tile) over the block's chunk range
-// and leave the per-warp accumulators in acc (fragment layout).
-template <typename T, int BITS, int NB, int NWARPS>
-__device__ __forceinline__ void stream_pass(float (&acc)[NB][8][4], const uint8_t* __restrict__ packed,
+// Look up and multiply one chunk held in w; refill each 1 KB plane of w from `next`
+// (when `more`) as soon as its last field has been used.
+template <typename T, int BITS, int CP>
+__device__ __forceinline__ void chunk_math(float (&acc)[Plan<CP>::kAcc][4], uint32_t (&w)[8 * BITS],
+                                           const uint2 (&xf)[Plan<CP>::kNB][4], uint32_t tbl_lane,
+                                           int slot_shift, int gid, const uint8_t* next,
+                                           uint32_t more) {
+  using P = Plan<CP>;
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    const int slot = s >> slot_shift;
+    const uint32_t base = tbl_lane + uint32_t(slot >> 1) * kTableBytes + uint32_t(slot & 1) * 128u;
+    const bool mine = (gid / P::kCols) == (s % P::kSlabsPerAcc);
+#pragma unroll
+    for (int kt = 0; kt < 4; ++kt) {
+      uint32_t a[4];
+#pragma unroll
+      for (int f = 0; f < 4; ++f) a[f] = lds32(field_addr<BITS>(w, s, 4 * kt + f, base));
+#pragma unroll
+      for (int nb = 0; nb < P::kNB; ++nb) {
+        const uint32_t b0 = (P::kSlabsPerAcc == 1 || mine) ? xf[nb][kt].x : 0u;
+        const uint32_t b1 = (P::kSlabsPerAcc == 1 || mine) ? xf[nb][kt].y : 0u;
+        mma16816<T>(acc[(s / P::kSlabsPerAcc) * P::kNB + nb], a, b0, b1);
+      }
+    }
+#pragma unroll
+    for (int pl = (s * BITS) / 8; pl < ((s + 1) * BITS) / 8; ++pl)
+      ldg_stream256_if(&w[8 * pl], next + pl * 1024, more);
+  }
+}
+
+// One pass: stream the codes of one (segment stream, tile) over the block's chunk
+// range, fold the warps' sums and add the result into part[m][row] (the block's
+// K-range contribution). Each warp keeps RC chunks in flight in registers; the
+// first ones are requested before the pair tables are built, so the palette fetch
+// and the first code fetches overlap.
+template <typename T, int BITS, int CP, int NWARPS, int RC>
+__device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, uint8_t* tbl_ptr,
+                                            uint32_t tbl_addr, const uint8_t* __restrict__ packed,
+                                            const uint16_t* __restrict__ lut, int n_groups, int gs,
                                             int tile, int G, int c0, int c1,
                                             const uint16_t* __restrict__ x, long long ldx, int M,
-                                            uint32_t tbl_lane, int slot_shift, bool first_pass) {
+                                            bool first_pass) {
+  using P = Plan<CP>;
+  constexpr int NT = NWARPS * 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   const size_t chunk_bytes = size_t(1024) * BITS;
+  const size_t hop = chunk_bytes * NWARPS;            // bytes between a warp's consecutive chunks
   const uint8_t* lane_base = packed + (size_t(tile) * G) * chunk_bytes + lane * 32;
+  float* red = reinterpret_cast<float*>(tbl_ptr);   // aliases the tables after the loop
 
-  // Single register buffer, refilled plane by plane: as soon as the last field of a
-  // 1 KB plane (8 words per lane) has been looked up, the same registers receive the
-  // next chunk's plane, so a whole chunk per warp is always in flight.
-  uint32_t w[8 * BITS];
+  uint32_t w[RC][8 * BITS];
   int c = c0 + warp;
-  if (c < c1) load_chunk<BITS>(w, lane_base + size_t(c) * chunk_bytes);
+#pragma unroll
+  for (int u = 0; u < RC; ++u) {
+#pragma unroll
+    for (int i = 0; i < 8 * BITS; ++i) w[u][i] = 0u;
+#pragma unroll
+    for (int pl = 0; pl < BITS; ++pl)
+      ldg_stream256_if(&w[u][8 * pl], lane_base + size_t(c) * chunk_bytes + u * hop + pl * 1024,
+                       c + u * NWARPS < c1 ? 1u : 0u);
+  }
+
+  int nl = kTileRows / gs;
+  if (nl < 1) nl = 1;
+  const int slot_shift = nl == 1 ? 3 : (nl == 2 ? 2 : 1);
+  if (!first_pass) __syncthreads();   // the previous pass's fold buffer aliases the tables
+  build_tables(tbl_ptr, lut, BITS, n_groups, tile * kTileRows, gs, nl, NT);
+  __syncthreads();
   if (first_pass) {
     // everything above is independent of the previous kernel in the stream
     asm volatile("griddepcontrol.wait;" ::: "memory");
   }
-  for (; c < c1; c += NWARPS) {
-    const bool more = c + NWARPS < c1;
-    const uint8_t* next = lane_base + size_t(c + NWARPS) * chunk_bytes;
-    uint2 xf[NB][4];
-    load_x<NB>(xf, x, ldx, M, c * kChunkK, gid, tig);
+
+  float acc[P::kAcc][4];
 #pragma unroll
-    for (int s = 0; s < 8; ++s) {
-      const int slot = s >> slot_shift;
-      const uint32_t base = tbl_lane + uint32_t(slot >> 1) * kTableBytes + uint32_t(slot & 1) * 128u;
+  for (int a = 0; a < P::kAcc; ++a)
 #pragma unroll
-      for (int kt = 0; kt < 4; ++kt) {
-        uint32_t a[4];
+    for (int r = 0; r < 4; ++r) acc[a][r] = 0.f;
+
+  uint32_t token;   // defined after the build barrier; part of every lookup address
+  asm volatile("mov.u32 %0, 0;" : "=r"(token));
+  const uint32_t tbl_lane = tbl_addr + lane * 4 + token;
+  // x fragments ride the same ring: the rows of a chunk are requested RC chunks ahead
+  // of their use (a first touch of x misses L1 and pays an L2 round trip).
+  uint2 xf[RC][P::kNB][4];
 #pragma unroll
-        for (int f = 0; f < 4; ++f) a[f] = lds32(field_addr<BITS>(w, s, 4 * kt + f, base));
+  for (int u = 0; u < RC; ++u)
+    load_x<CP>(xf[u], x, ldx, (c + u * NWARPS < c1) ? M : 0, (c + u * NWARPS) * kChunkK, gid, tig);
+  for (; c < c1; c += RC * NWARPS) {
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) mma16816<T>(acc[nb][s], a, xf[nb][kt].x, xf[nb][kt].y);
+    for (int u = 0; u < RC; ++u) {
+      const int cu = c + u * NWARPS;
+      if (cu < c1) {   // warp-uniform
+        const bool more = cu + RC * NWARPS < c1;
+        chunk_math<T, BITS, CP>(acc, w[u], xf[u], tbl_lane, slot_shift, gid,
+                                lane_base + size_t(cu) * chunk_bytes + RC * hop, more ? 1u : 0u);
+        load_x<CP>(xf[u], x, ldx, more ? M : 0, (cu + RC * NWARPS) * kChunkK, gid, tig);
       }
+    }
+  }
 #pragma unroll
-      for (int pl = (s * BITS) / 8; pl < ((s + 1) * BITS) / 8; ++pl)
-        if (more) ldg_stream256(&w[8 * pl], next + pl * 1024);
+  for (int a = 0; a < P::kAcc; ++a)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) asm volatile("" ::"f"(acc[a][r]));   // lookups end here
+  __syncthreads();   // all warps are done with the tables
+
+  // cross-warp fold, 8 batch columns at a time: red[warp][m & 7][row], fixed warp order
+#pragma unroll
+  for (int nb = 0; nb < P::kNB; ++nb) {
+    if (nb) __syncthreads();
+#pragma unroll
+    for (int a = 0; a < P::kCols; ++a)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int col = 2 * tig + (r & 1);
+        const int s = a * P::kSlabsPerAcc + col / P::kCols, mm = col % P::kCols;
+        const int row = 16 * s + gid + 8 * (r >> 1);
+        red[(warp * P::kCols + mm) * kTileRows + row] = acc[a * P::kNB + nb][r];
+      }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < P::kCols * kTileRows; idx += NT) {
+      const int mm = idx >> 7, row = idx & 127, m = mm + 8 * nb;
+      if (m < M) {
+        float v = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < NWARPS; ++wi) v += red[(wi * P::kCols + mm) * kTileRows + row];
+        float* dst = part_plane + m * kTileRows + row;
+        *dst = accumulate ? *dst + v : v;
+      }
     }
   }
 }
 
-template <typename T, int NB, int NWARPS>
+template <typename T, int CP, int NWARPS, int RC>
 __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   constexpr int NT = NWARPS * 32;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int gid = lane >> 2, tig = lane & 3;
 
   float* part = reinterpret_cast<float*>(smem);   // [plane][m][row]
   const uint32_t part_addr = smem_u32(smem);
   const uint32_t tbl_addr = (part_addr + kPartBytes + 0xFFFFu) & ~0xFFFFu;
   uint8_t* tbl_ptr = smem + (tbl_addr - part_addr);
-  float* red = reinterpret_cast<float*>(tbl_ptr);  // aliases the tables after the pass
 
   // which tile / split is this block
   const int split = p.split;
@@ -249,66 +366,18 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
       const uint8_t* packed = pass ? sg.packed2 : sg.packed;
       const uint16_t* lut = pass ? sg.lut2 : sg.lut;
       const int bits = pass ? sg.bits2 : sg.bits;
-      int nl = kTileRows / sg.gs;
-      if (nl < 1) nl = 1;
-      const int slot_shift = nl == 1 ? 3 : (nl == 2 ? 2 : 1);
-      if (!first) __syncthreads();   // the reduction buffer aliases the tables
-      build_tables(tbl_ptr, lut, bits, sg.n_groups, tile * kTileRows, sg.gs, nl, NT);
-      __syncthreads();
-
-      float acc[NB][8][4];
-#pragma unroll
-      for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-#pragma unroll
-          for (int r = 0; r < 4; ++r) acc[nb][s][r] = 0.f;
-
-      const uint32_t tbl_lane = tbl_addr + lane * 4;
+      float* dst = part + plane * kMaxM * kTileRows;
+#define B200LUT_PASS(B)                                                                       \
+  stream_pass<T, B, CP, NWARPS, RC>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups,  \
+                                sg.gs, tile, p.G, c0, c1, p.x, p.ldx, M, first)
       switch (bits) {   // block-uniform
-        case 4:
-          stream_pass<T, 4, NB, NWARPS>(acc, packed, tile, p.G, c0, c1, p.x, p.ldx, M, tbl_lane,
-                                        slot_shift, first);
-          break;
-        case 3:
-          stream_pass<T, 3, NB, NWARPS>(acc, packed, tile, p.G, c0, c1, p.x, p.ldx, M, tbl_lane,
-                                        slot_shift, first);
-          break;
-        case 2:
-          stream_pass<T, 2, NB, NWARPS>(acc, packed, tile, p.G, c0, c1, p.x, p.ldx, M, tbl_lane,
-                                        slot_shift, first);
-          break;
-        default:
-          stream_pass<T, 1, NB, NWARPS>(acc, packed, tile, p.G, c0, c1, p.x, p.ldx, M, tbl_lane,
-                                        slot_shift, first);
-          break;
+        case 4: B200LUT_PASS(4); break;
+        case 3: B200LUT_PASS(3); break;
+        case 2: B200LUT_PASS(2); break;
+        default: B200LUT_PASS(1); break;
       }
+#undef B200LUT_PASS
       first = false;
-      __syncthreads();   // all warps are done with the tables
-
-      // cross-warp fold, 8 batch columns at a time: red[warp][m & 7][row]
-#pragma unroll
-      for (int nb = 0; nb < NB; ++nb) {
-        if (nb) __syncthreads();
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-#pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            const int row = 16 * s + gid + 8 * (r >> 1), mm = 2 * tig + (r & 1);
-            red[(warp * 8 + mm) * kTileRows + row] = acc[nb][s][r];
-          }
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < 8 * kTileRows; idx += NT) {
-          const int mm = idx >> 7, row = idx & 127, m = mm + 8 * nb;
-          if (m < M) {
-            float v = 0.f;
-#pragma unroll
-            for (int w = 0; w < NWARPS; ++w) v += red[(w * 8 + mm) * kTileRows + row];
-            float* dst = part + (plane * kMaxM + m) * kTileRows + row;
-            *dst = pass ? *dst + v : v;
-          }
-        }
-      }
     }
   }
   // part[plane][m][row] now holds this block's K-range contribution.
@@ -391,13 +460,15 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
   }
 }
 
+constexpr int kWarpsM8 = 16, kWarpsM16 = 8;
+
 size_t smem_bytes_for(int max_tables) {
   return size_t(kPartBytes) + 65536 + size_t(max_tables) * kTableBytes;
 }
 
-template <typename T, int NB, int NWARPS>
+template <typename T, int CP, int NWARPS, int RC>
 int launch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t stream) {
-  auto kern = gemv_kernel<T, NB, NWARPS>;
+  auto kern = gemv_kernel<T, CP, NWARPS, RC>;
   const size_t smem = smem_bytes_for(max_tables);
   static size_t configured[64] = {0};
   int dev = 0;
@@ -432,6 +503,15 @@ int launch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t stream) {
   return B200LUT_OK;
 }
 
+template <typename T>
+int dispatch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t st) {
+  if (p.M == 1) return launch<T, 1, kWarpsM8, 2>(p, max_tables, pdl, st);
+  if (p.M == 2) return launch<T, 2, kWarpsM8, 2>(p, max_tables, pdl, st);
+  if (p.M <= 4) return launch<T, 4, kWarpsM8, 2>(p, max_tables, pdl, st);
+  if (p.M <= 8) return launch<T, 8, kWarpsM8, 1>(p, max_tables, pdl, st);
+  return launch<T, 16, kWarpsM16, 1>(p, max_tables, pdl, st);
+}
+
 int sm_count_cached() {
   static int cached[64] = {0};
   int dev = 0;
@@ -445,7 +525,6 @@ int sm_count_cached() {
   return cached[dev];
 }
 
-constexpr int kWarpsM8 = 16, kWarpsM16 = 8;
 
 // Split policy: one block per SM is resident. Cost of a candidate = waves of blocks
 // times the chunks the busiest warp streams, plus a small per-split fold charge.
@@ -579,12 +658,8 @@ extern "C" int b200lut_gemv_multi(const void* x, int64_t ldx, int M, int K, int 
   }
   const bool pdl = (flags & 1) != 0;
   cudaStream_t st = cudaStream_t(stream);
-  if (dtype == B200LUT_BF16) {
-    return M <= 8 ? launch<__nv_bfloat16, 1, kWarpsM8>(p, max_tables, pdl, st)
-                  : launch<__nv_bfloat16, 2, kWarpsM16>(p, max_tables, pdl, st);
-  }
-  return M <= 8 ? launch<__half, 1, kWarpsM8>(p, max_tables, pdl, st)
-                : launch<__half, 2, kWarpsM16>(p, max_tables, pdl, st);
+  if (dtype == B200LUT_BF16) return dispatch<__nv_bfloat16>(p, max_tables, pdl, st);
+  return dispatch<__half>(p, max_tables, pdl, st);
 }
 
 extern "C" int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out, int M,
