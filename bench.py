@@ -1,0 +1,407 @@
+#!/usr/bin/env python3
+"""Benchmark of the B200 LUT-palettized linear path.
+
+Workload (default): the Qwen3.5-9B-shaped linear stack — 248 palettized projections
+(6 912 212 992 4-bit weights, group 128, bf16 palettes), one decode step at batch M
+(default 1) = one pass of the activation rows through every projection. With N GPUs
+the output rows of every projection are sharded column-parallel and the MLP
+activation is all-gathered once per layer (strong scaling: total work is fixed).
+
+One JSON line on stdout (rank 0):
+  value      tok/s with inputs resident in HBM (CUDA-graph replay of the step)
+  e2e        tok/s through the host-facing call: pinned host x -> device, step, result -> host
+  roofline   the decode GEMV kernel against the measured HBM copy bandwidth
+  cpu_baseline  the CPU oracle (a port of the reference's forward="reference" route)
+             timed on this host on a bounded sample, which also checks the GPU outputs
+  extras     single-projection GEMV GB/s and (when built) the M=2048 prefill GEMM TFLOP/s
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--batch M] [--impl reference]
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+PKG = "rag-cache-engineering-qwen35-9b-flute_b200"
+METRIC = "9B linear-stack decode tok/s (LUT-GEMV, M=1 unless --batch)"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while a timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.rows, self.proc = gpu_index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx = max(mx, float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n_gpus: int):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    if world != n_gpus:
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    return rank, world, local
+
+
+def max_over_ranks(ms: float, world: int) -> float:
+    if world == 1:
+        return ms
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world: int):
+    import torch
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def make_gather(world: int, M: int):
+    """All-gather of the column-sharded MLP activation [M, world * n] over NCCL."""
+    if world == 1:
+        return None
+    import torch.distributed as dist
+
+    def gather(full, local):
+        if M == 1:
+            dist.all_gather_into_tensor(full.view(-1), local.reshape(-1))    # in place
+        else:
+            n = local.shape[1]
+            tmp = full.new_empty(world, M, n)
+            dist.all_gather_into_tensor(tmp.view(-1), local.contiguous().view(-1))
+            full.view(M, world, n).copy_(tmp.permute(1, 0, 2))
+    return gather
+
+
+def time_steps(fn, steps: int, world: int) -> float:
+    """Milliseconds for `steps` calls of fn, CUDA events on the current stream,
+    barrier + synchronize on both sides, max over ranks."""
+    import torch
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier(world)
+    return max_over_ranks(e0.elapsed_time(e1), world)
+
+
+def cpu_sample(pkg, stack, M: int, gpu_check: bool, threads: int):
+    """Time the CPU oracle on layers 0 (linear attention) and 3 (full attention) and
+    scale to the 24 + 8 layer stack; when gpu_check, compare the GPU outputs of those
+    layers with it (max relative error <= 1e-2)."""
+    import numpy as np
+    import torch
+    from oracle import lut_linear_oracle as orc
+    torch.set_num_threads(threads)
+    st = importlib.import_module(PKG + ".stack")
+    plan = stack._plan(M) if gpu_check else None
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(M, st.HIDDEN, generator=g).to(stack.dtype)
+    if gpu_check:
+        plan["x"].copy_(x)
+        stack.step(M)
+        torch.cuda.synchronize()
+    per_kind, worst = {}, 0.0
+    for li in (0, 3):
+        L = stack.layers[li]
+        mods = L.heads() + [L.out(), L.mlp.gate_proj, L.mlp.up_proj, L.mlp.down_proj]
+        blobs = [pkg._lib.repack_to_idxn(m._packed, m.N, m.K, m.bitwidth).cpu().numpy() for m in mods]
+        luts = [m.lut.cpu() for m in mods]
+        t0 = time.perf_counter()
+        ys = []
+        for m, blob, lut in zip(mods[:-3], blobs, luts):     # as shipped: unpack on every call
+            ys.append(orc.linear_forward(x, orc.dequant(blob, lut, m.N, m.K, m.group_size, m.bitwidth)))
+        wg, wu, wd = (orc.dequant(b, l, m.N, m.K, m.group_size, m.bitwidth)
+                      for m, b, l in zip(mods[-3:], blobs[-3:], luts[-3:]))
+        xf = x.float()
+        act = orc.silu_mul_fused(xf @ wg.t(), xf @ wu.t(), x.dtype)
+        y = orc.linear_forward(act, wd)
+        per_kind[L.kind] = time.perf_counter() - t0
+        if gpu_check:
+            bufs = plan["buffers"][4 * li:4 * li + 4]
+            want_heads = torch.cat(ys[:-1], dim=1)
+            for got, want in ((bufs[0], want_heads), (bufs[1], ys[-1]), (bufs[2], act), (bufs[3], y)):
+                worst = max(worst, orc.max_rel_err(got.cpu().float(), want.float()))
+    n_lin = sum(1 for L in stack.layers if L.kind == "linear")
+    n_full = len(stack.layers) - n_lin
+    step_s = n_lin * per_kind["linear"] + n_full * per_kind["full"]
+    return step_s, worst, per_kind
+
+
+def run_reference(args, rank: int):
+    """The reference arm: the CPU oracle (port of the reference's forward="reference"
+    route: numpy unpack of the idxN blob on every call, fp32 torch matmul) timed on
+    the host cores. One step = one 4096 x 4096 projection; tok/s is scaled to the
+    stack by the weight ratio."""
+    if rank != 0:
+        return
+    import numpy as np
+    import torch
+    from oracle import lut_linear_oracle as orc
+    pkg = importlib.import_module(PKG)
+    st = importlib.import_module(PKG + ".stack")
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    M, N, K, bits, gs = args.batch, 4096, 4096, 4, 128
+    codes, blob = pkg.synthetic.make_blob(N, K, bits, pkg.synthetic.BASE_SEED)
+    lut = pkg.synthetic.make_lut(N // gs, bits, torch.bfloat16, pkg.synthetic.BASE_SEED)
+    x = pkg.synthetic.make_x(M, K, torch.bfloat16, pkg.synthetic.BASE_SEED)
+    blob = blob.numpy()
+
+    def step():
+        return orc.linear_forward(x, orc.dequant(blob, lut, N, K, gs, bits))
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    scale = st.census()["weights"] / (N * K)
+    value = M / (dt * scale)
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt * scale * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "qwen3.5-9b linear stack, 248 projections, 4-bit group 128",
+                       "batch": M},
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port",
+                             "sample": f"one 4096x4096 projection per step ({dt * 1e3:.0f} ms), "
+                                       f"scaled x{scale:.0f} by weight count"},
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def single_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int, flags: int):
+    """Extra: one projection launched back to back over `sets` distinct weight sets
+    (their total exceeds L2), CUDA-graph replay; returns (GB/s, us per launch)."""
+    import torch
+    L = pkg._lib
+    bits, gs, dt = 4, 128, torch.bfloat16
+    x = torch.randn(M, K, device="cuda").to(dt)
+    out = torch.empty(M, N, dtype=dt, device="cuda")
+    keep, segs = [], []
+    for i in range(sets):
+        packed = L.repack_from_idxn(pkg.synthetic.random_blob_on_device(N, K, bits, 900 + i, "cuda"), N, K, bits)
+        lut = pkg.synthetic.make_lut(N // gs, bits, dt, 900 + i).cuda()
+        keep.append((packed, lut))
+        segs.append(L.make_segments([dict(packed=packed, lut=lut, N=N, group_size=gs,
+                                          n_groups=N // gs, bits=bits, out=out)]))
+
+    def run():
+        for s in segs:
+            L.gemv_multi(x, s, 1, flags=flags)
+    run()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run()
+    for _ in range(3):
+        g.replay()
+    ms = time_steps(g.replay, iters, 1)
+    us = ms * 1e3 / (iters * sets)
+    byts = N * K * bits // 8 + (N // gs) * 32 + M * K * 2 + M * N * 2
+    return byts / us / 1e3, us
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (1/0)")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args, int(os.environ.get("RANK", "0")))
+        return 0
+
+    import torch
+    rank, world, local = dist_setup(args.gpus)
+    pkg = importlib.import_module(PKG)
+    st = importlib.import_module(PKG + ".stack")
+    M = args.batch
+    flags = pkg._lib.FLAG_PDL if args.pdl else 0
+    peaks = measured_peaks()
+
+    stack = st.LinearStack(device=f"cuda:{local}", rank=rank, world=world)
+    gather = make_gather(world, M)
+    plan = stack._plan(M)
+    x_host = torch.randn(M, st.HIDDEN, generator=torch.Generator().manual_seed(1)).to(stack.dtype).pin_memory()
+    y_host = torch.empty(plan["y"].shape, dtype=stack.dtype).pin_memory()
+    plan["x"].copy_(x_host)
+
+    # eager run, then capture the step in a CUDA graph
+    stack.step(M, flags=flags, gather=gather)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        stack.step(M, flags=flags, gather=gather)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            stack.step(M, flags=flags, gather=gather)
+    torch.cuda.synchronize()
+
+    def step_resident():
+        graph.replay()
+
+    def step_e2e():
+        plan["x"].copy_(x_host, non_blocking=True)
+        graph.replay()
+        y_host.copy_(plan["y"], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(args.warmup):
+        step_resident()
+    with ClockSampler(local) as clk:
+        # run under load for ~1.5 s first so that the 200 ms sampler sees the timed state,
+        # then time exactly K steps
+        probe_ms = time_steps(step_resident, args.steps, world)
+        for _ in range(min(int(1500 / max(probe_ms, 1e-3)), 200)):
+            for _ in range(args.steps):
+                step_resident()
+        ms = time_steps(step_resident, args.steps, world)
+    clocks = clk.summary()
+    for _ in range(args.warmup):
+        step_e2e()
+    ms_e2e = time_steps(step_e2e, args.steps, world)
+
+    ms_step = ms / args.steps
+    tok_s = M * 1e3 / ms_step
+    launches = stack.launches_per_step(M)
+    bytes_rank = stack.algorithmic_bytes(M)
+    achieved = bytes_rank / (ms_step * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "qwen3.5-9b linear stack: 32 layers, 248 projections, "
+                               "6912212992 4-bit weights, group 128, bf16 palettes",
+                   "batch": M, "parallelism": f"column-parallel x{world}, all-gather per layer",
+                   "l2": "inputs (3.46 GB of codes per step) exceed the 126 MB L2",
+                   "launch": "CUDA graph replay" + (", programmatic dependent launch" if args.pdl else "")},
+        "e2e": {"value": M * 1e3 / (ms_e2e / args.steps), "unit": "tok/s",
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+        "gpu_launches": launches * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "gemv_kernel", "achieved": achieved,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                     "peak_source": peaks["source"], "traffic": None,
+                     "bytes_per_launch": bytes_rank / launches,
+                     "us_per_launch": ms_step * 1e3 / launches},
+    }
+    if rank == 0 and world == 1 and not args.no_extras:
+        extras = {}
+        try:
+            gbs, us = single_projection_gbs(pkg, 1, 4096, 4096, 40, 20, flags)
+            extras["gemv_4096x4096_m1"] = {"GB/s": gbs, "us_per_launch": us,
+                                           "frac_of_hbm": gbs / peaks["hbm_gbs"]}
+            gbs, us = single_projection_gbs(pkg, 1, 12288, 4096, 16, 20, flags)
+            extras["gemv_12288x4096_m1"] = {"GB/s": gbs, "us_per_launch": us,
+                                            "frac_of_hbm": gbs / peaks["hbm_gbs"]}
+        except Exception as e:       # an extra must not lose the main line
+            extras["error"] = repr(e)
+        line["extras"] = extras
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        step_s, worst, per_kind = cpu_sample(pkg, stack, M, True, threads)
+        line["cpu_baseline"] = {
+            "value": M / step_s, "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": f"layers 0 (linear-attention, {per_kind['linear']:.1f} s) and 3 "
+                      f"(full-attention, {per_kind['full']:.1f} s), scaled x24 + x8; blob unpacked "
+                      "on every call as the reference route does",
+            "gpu_max_rel_err_vs_cpu": worst}
+        if worst > 1e-2:
+            line["invalid"] = f"GPU outputs differ from the CPU oracle: max rel err {worst}"
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

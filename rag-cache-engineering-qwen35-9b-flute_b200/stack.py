@@ -1,0 +1,210 @@
+"""Synthetic Qwen3.5-9B-shaped linear stack: every palettized projection of the 32
+decoder layers, random-init, run as one decode (or prefill) step.
+
+The reference builds its model from a checkpoint (load_palettized_model,
+src/scripts/palettized_modules.py:3264-3398); no checkpoint travels with this
+package, so this module offers the constructor the reference lacks: the module
+census of src/docs/MODEL_GEOMETRY.md (24 linear-attention layers with in_proj_qkv
+as Q 2048 + K 2048 + V 4096 rows, in_proj_z 4096, out_proj 4096; 8 full-attention
+layers with q 8192, k 1024, v 1024, o 4096; every layer an MLP 4096 -> 12288 ->
+4096), 248 modules, 6 912 212 992 weights, 4-bit codes, group 128.
+
+Attention, recurrence, norms and residual adds are excluded (they are not part of
+the palettized linear path): every projection group of a step reads the step's
+activation rows x [M, 4096]; the MLP chain gate/up -> SiLU*mul -> down is real.
+
+Column-parallel sharding: rank r of G owns output rows [r*N/G, (r+1)*N/G) of every
+projection (contiguous bytes in the tile-major code buffer). Sharded outputs that
+feed a full-K consumer are recombined with an all-gather (the MLP's SiLU*mul
+output before down_proj, and the layer outputs).
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+
+from . import _lib, synthetic
+from .palettized_modules import FusedPalettizedMLP, PalettizedLinear, SplitQKV
+
+HIDDEN = 4096
+INTERMEDIATE = 12288
+N_LAYERS = 32
+FULL_ATTENTION_EVERY = 4          # layers 3, 7, ... are full attention (8 of 32)
+LINEAR_ATTN = (("q", 2048), ("k", 2048), ("v", 4096), ("z", 4096))
+FULL_ATTN = (("q", 8192), ("k", 1024), ("v", 1024))
+
+
+def layer_kind(i: int) -> str:
+    return "full" if (i + 1) % FULL_ATTENTION_EVERY == 0 else "linear"
+
+
+def census() -> dict:
+    """Module and weight counts of the stack (checked against the model geometry)."""
+    modules = weights = 0
+    for i in range(N_LAYERS):
+        heads = LINEAR_ATTN if layer_kind(i) == "linear" else FULL_ATTN
+        rows = [n for _, n in heads] + [HIDDEN]                # + out_proj / o_proj
+        modules += len(rows) + 3
+        weights += sum(rows) * HIDDEN + 3 * INTERMEDIATE * HIDDEN
+    return {"modules": modules, "weights": weights}
+
+
+class _Layer(nn.Module):
+    def __init__(self, kind: str, mods: dict):
+        super().__init__()
+        self.kind = kind
+        if kind == "linear":
+            self.in_proj_qkv = SplitQKV(mods["q"], mods["k"], mods["v"])
+            self.in_proj_z = mods["z"]
+            self.out_proj = mods["o"]
+        else:
+            self.qkv = SplitQKV(mods["q"], mods["k"], mods["v"])
+            self.o_proj = mods["o"]
+        self.mlp = FusedPalettizedMLP(mods["gate"], mods["up"], mods["down"], nn.SiLU())
+
+    def heads(self) -> List[PalettizedLinear]:
+        if self.kind == "linear":
+            q = self.in_proj_qkv
+            return [q.q_proj, q.k_proj, q.v_proj, self.in_proj_z]
+        return [self.qkv.q_proj, self.qkv.k_proj, self.qkv.v_proj]
+
+    def out(self) -> PalettizedLinear:
+        return self.out_proj if self.kind == "linear" else self.o_proj
+
+
+class LinearStack(nn.Module):
+    """The 32-layer projection stack, optionally one column-parallel shard of it."""
+
+    def __init__(self, device="cuda", dtype=torch.bfloat16, bits: int = 4, group_size: int = 128,
+                 n_layers: int = N_LAYERS, seed: int = synthetic.BASE_SEED + 5,
+                 rank: int = 0, world: int = 1):
+        super().__init__()
+        self.device, self.dtype = torch.device(device), dtype
+        self.bits, self.group_size = bits, group_size
+        self.rank, self.world = rank, world
+        self.layers = nn.ModuleList()
+        mod_id = 0
+        for i in range(n_layers):
+            kind = layer_kind(i)
+            heads = LINEAR_ATTN if kind == "linear" else FULL_ATTN
+            shapes = [(name, n, HIDDEN) for name, n in heads] + [
+                ("o", HIDDEN, HIDDEN), ("gate", INTERMEDIATE, HIDDEN),
+                ("up", INTERMEDIATE, HIDDEN), ("down", HIDDEN, INTERMEDIATE)]
+            mods = {}
+            for name, n, k in shapes:
+                mods[name] = self._make_module(n, k, seed * 1000 + mod_id)
+                mod_id += 1
+            self.layers.append(_Layer(kind, mods))
+        self._plans = {}
+
+    def _make_module(self, N: int, K: int, seed: int) -> PalettizedLinear:
+        """Full-size codes and palette are drawn from the seed (distinct bytes per
+        module); a shard keeps rows [rank*N/world, (rank+1)*N/world)."""
+        if N % (self.world * 128) or (N // self.world) % self.group_size:
+            raise ValueError(f"N={N} does not shard over {self.world} ranks in whole tiles and groups")
+        n_loc = N // self.world
+        blob = synthetic.random_blob_on_device(N, K, self.bits, seed, self.device)
+        shard_bytes = n_loc * K * self.bits // 8            # a row-tile range is contiguous
+        blob = blob[self.rank * shard_bytes:(self.rank + 1) * shard_bytes]
+        packed = _lib.repack_from_idxn(blob, n_loc, K, self.bits)
+        lut = synthetic.make_lut(N // self.group_size, self.bits, self.dtype, seed)
+        g_loc = n_loc // self.group_size
+        lut = lut[self.rank * g_loc:(self.rank + 1) * g_loc].contiguous().to(self.device)
+        return PalettizedLinear.from_packed(packed, lut, self.bits, self.group_size, n_loc, K)
+
+    # ------------------------------------------------------------------ census
+    def modules_list(self) -> List[PalettizedLinear]:
+        out = []
+        for L in self.layers:
+            out += L.heads() + [L.out(), L.mlp.gate_proj, L.mlp.up_proj, L.mlp.down_proj]
+        return out
+
+    def weight_count(self) -> int:
+        return sum(m.N * m.K for m in self.modules_list())
+
+    def algorithmic_bytes(self, M: int) -> int:
+        """Bytes one step must move on this rank: codes + palettes + activations in
+        and out of every launch (2 bytes per activation element)."""
+        total = 0
+        for m in self.modules_list():
+            total += m.N * m.K * m.bitwidth // 8 + m.lut.numel() * 2 + M * m.K * 2 + M * m.N * 2
+        return total
+
+    def flops(self, M: int) -> int:
+        return 2 * M * self.weight_count()
+
+    # -------------------------------------------------------------------- step
+    def _plan(self, M: int):
+        """Persistent buffers and prebuilt segment tables for batch M (stable
+        pointers, so a step can be captured in a CUDA graph)."""
+        plan = self._plans.get(M)
+        if plan is not None:
+            return plan
+        dev, dt = self.device, self.dtype
+        x = torch.zeros(M, HIDDEN, dtype=dt, device=dev)
+        launches = []
+        outs = []
+        for L in self.layers:
+            heads = L.heads()
+            total = sum(m.N for m in heads)
+            hbuf = torch.empty(M, total, dtype=dt, device=dev)
+            descs, off = [], 0
+            for m in heads:
+                descs.append(m._segment_desc(hbuf[:, off:], ldo=total))
+                off += m.N
+            launches.append(("heads", x, _lib.make_segments(descs), len(descs), _lib.EPI_NONE))
+            o = L.out()
+            obuf = torch.empty(M, o.N, dtype=dt, device=dev)
+            launches.append(("out", x, _lib.make_segments([o._segment_desc(obuf)]), 1, _lib.EPI_NONE))
+            g, u, d = L.mlp.gate_proj, L.mlp.up_proj, L.mlp.down_proj
+            act = torch.empty(M, g.N * self.world, dtype=dt, device=dev)   # full width after gather
+            act_loc = act[:, self.rank * g.N:(self.rank + 1) * g.N]
+            launches.append(("gate_up", x, _lib.make_segments(
+                [g._segment_desc(act_loc, ldo=act.shape[1]), u._segment_desc(None)]), 2,
+                _lib.EPI_SILU_MUL))
+            if self.world > 1:
+                launches.append(("gather", act, act_loc, None, None))
+            ybuf = torch.empty(M, d.N, dtype=dt, device=dev)
+            launches.append(("down", act, _lib.make_segments([d._segment_desc(ybuf)]), 1,
+                             _lib.EPI_NONE))
+            outs += [hbuf, obuf, act, ybuf]
+        plan = {"x": x, "launches": launches, "buffers": outs, "y": outs[-1]}
+        self._plans[M] = plan
+        return plan
+
+    def step(self, M: int, flags: int = 0, gather=None) -> torch.Tensor:
+        """Run every projection once on the plan's activation buffer; returns the
+        last layer's down_proj output (this rank's columns)."""
+        plan = self._plan(M)
+        for name, xin, segs, nseg, epi in plan["launches"]:
+            if name == "gather":
+                gather(xin, segs)
+                continue
+            if M <= 16:
+                _lib.gemv_multi(xin, segs, nseg, epilogue=epi, flags=flags)
+            else:
+                for i in range(0, nseg, 2 if epi == _lib.EPI_SILU_MUL else 1):
+                    _lib.gemm(xin, _pair(segs, i, epi), epilogue=epi, flags=flags)
+        return plan["y"]
+
+    def launches_per_step(self, M: int) -> int:
+        n = 0
+        for name, _, _, nseg, epi in self._plan(M)["launches"]:
+            if name == "gather":
+                continue
+            n += 1 if M <= 16 else (nseg // 2 if epi == _lib.EPI_SILU_MUL else nseg)
+        return n
+
+
+def _pair(segs, i, epi):
+    """Pointer to segment i of a ctypes segment array (the prefill GEMM takes one
+    projection, or one (gate, up) pair merged into a single descriptor)."""
+    import ctypes
+    if epi != _lib.EPI_SILU_MUL:
+        return ctypes.pointer(segs[i])
+    s = _lib.Segment()
+    ctypes.memmove(ctypes.byref(s), ctypes.byref(segs[i]), ctypes.sizeof(s))
+    s.packed2, s.lut2, s.bits2 = segs[i + 1].packed, segs[i + 1].lut, segs[i + 1].bits
+    return ctypes.pointer(s)
