@@ -51,6 +51,12 @@ int b200lut_version(void);
  * (src/flute_extended/src/kernel_gemv.cu:338-454). */
 const char* b200lut_last_error(void);
 
+/* Device-side status of the tensor-core kernels on the current device: 0 = none;
+ * non-zero = a bounded wait inside a kernel ran out (the kernel then returned early
+ * with its tensor memory freed and its output undefined). Synchronises the device
+ * read; clears the word. No counterpart in the reference (its kernels never wait). */
+int b200lut_device_status(void);
+
 /* Number of SMs of the current device (used by the split policy). */
 int b200lut_sm_count(void);
 

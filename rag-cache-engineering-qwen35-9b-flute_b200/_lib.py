@@ -23,7 +23,7 @@ FHT_FORWARD, FHT_ADJOINT, FHT_AWQ = 0, 1, 2
 FLAG_PDL = 1
 
 EXPORTS = (
-    "b200lut_version", "b200lut_last_error", "b200lut_sm_count", "b200lut_packed_bytes",
+    "b200lut_version", "b200lut_last_error", "b200lut_sm_count", "b200lut_device_status", "b200lut_packed_bytes",
     "b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes",
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
@@ -67,6 +67,7 @@ def lib() -> ctypes.CDLL:
     L.b200lut_version.restype = i32
     L.b200lut_last_error.restype = ctypes.c_char_p
     L.b200lut_sm_count.restype = i32
+    L.b200lut_device_status.restype = i32
     L.b200lut_packed_bytes.restype = sz
     L.b200lut_packed_bytes.argtypes = [i32, i32, i32]
     for name in ("b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes"):

@@ -29,6 +29,8 @@
 //    kernel's tail; only x depends on the predecessor.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -328,60 +330,17 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
   }
 }
 
-template <typename T, int CP, int NWARPS, int RC>
-__global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  constexpr int NT = NWARPS * 32;
-
-  float* part = reinterpret_cast<float*>(smem);   // [plane][m][row]
-  const uint32_t part_addr = smem_u32(smem);
-  const uint32_t tbl_addr = (part_addr + kPartBytes + 0xFFFFu) & ~0xFFFFu;
-  uint8_t* tbl_ptr = smem + (tbl_addr - part_addr);
-
-  // which tile / split is this block
-  const int split = p.split;
-  const int tile_g = blockIdx.x / split, sp = blockIdx.x % split;
-  const int c0 = (p.G * sp) / split, c1 = (p.G * (sp + 1)) / split;
-
+// Fold the K splits of one tile and write the outputs. part[plane][m][row] holds this
+// block's K-range contribution. split == 1: direct; cluster: ranks fold disjoint row
+// ranges through distributed shared memory in rank order; otherwise fp32 partials go
+// to the workspace and the last-arrival block (ticket) folds them in split order.
+// Deterministic in every mode. Returns to the caller with all of the block's threads.
+template <typename T, int NT>
+__device__ __forceinline__ void fold_and_store(const GemvParams& p, float* part, int si, int tile,
+                                               int tile_g, int sp) {
+  const int split = p.split, M = p.M;
   const bool silu = p.epilogue == B200LUT_EPI_SILU_MUL;
-  // plain: one segment per tile. silu-mul: segments come in (gate, up) pairs that
-  // share the tile index; both are computed by this block, one after the other.
-  int si = 0;
-  {
-    const int step = silu ? 2 : 1;
-    for (int s = 0; s < p.nseg; s += step)
-      if (tile_g >= p.seg[s].tile_begin) si = s;
-  }
-  const int tile = tile_g - p.seg[si].tile_begin;
   const int nplanes = silu ? 2 : 1;
-
-  asm volatile("griddepcontrol.launch_dependents;");
-
-  const int M = p.M;
-  bool first = true;
-  for (int plane = 0; plane < nplanes; ++plane) {
-    const SegDev& sg = p.seg[si + plane];
-    const int npass = sg.packed2 ? 2 : 1;
-    for (int pass = 0; pass < npass; ++pass) {
-      const uint8_t* packed = pass ? sg.packed2 : sg.packed;
-      const uint16_t* lut = pass ? sg.lut2 : sg.lut;
-      const int bits = pass ? sg.bits2 : sg.bits;
-      float* dst = part + plane * kMaxM * kTileRows;
-#define B200LUT_PASS(B)                                                                       \
-  stream_pass<T, B, CP, NWARPS, RC>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups,  \
-                                sg.gs, tile, p.G, c0, c1, p.x, p.ldx, M, first)
-      switch (bits) {   // block-uniform
-        case 4: B200LUT_PASS(4); break;
-        case 3: B200LUT_PASS(3); break;
-        case 2: B200LUT_PASS(2); break;
-        default: B200LUT_PASS(1); break;
-      }
-#undef B200LUT_PASS
-      first = false;
-    }
-  }
-  // part[plane][m][row] now holds this block's K-range contribution.
-
   const SegDev& s0 = p.seg[si];
   const int n0 = tile * kTileRows;
   auto finish = [&](int m, int row, float a, float b) {
@@ -460,6 +419,69 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
   }
 }
 
+template <typename T, int CP, int NWARPS, int RC>
+__global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  constexpr int NT = NWARPS * 32;
+
+  float* part = reinterpret_cast<float*>(smem);   // [plane][m][row]
+  const uint32_t part_addr = smem_u32(smem);
+  const uint32_t tbl_addr = (part_addr + kPartBytes + 0xFFFFu) & ~0xFFFFu;
+  uint8_t* tbl_ptr = smem + (tbl_addr - part_addr);
+
+  // which tile / split is this block
+  const int split = p.split;
+  const int tile_g = blockIdx.x / split, sp = blockIdx.x % split;
+  const int c0 = (p.G * sp) / split, c1 = (p.G * (sp + 1)) / split;
+
+  const bool silu = p.epilogue == B200LUT_EPI_SILU_MUL;
+  // plain: one segment per tile. silu-mul: segments come in (gate, up) pairs that
+  // share the tile index; both are computed by this block, one after the other.
+  int si = 0;
+  {
+    const int step = silu ? 2 : 1;
+    for (int s = 0; s < p.nseg; s += step)
+      if (tile_g >= p.seg[s].tile_begin) si = s;
+  }
+  const int tile = tile_g - p.seg[si].tile_begin;
+  const int nplanes = silu ? 2 : 1;
+
+  asm volatile("griddepcontrol.launch_dependents;");
+
+  const int M = p.M;
+  bool first = true;
+  for (int plane = 0; plane < nplanes; ++plane) {
+    const SegDev& sg = p.seg[si + plane];
+    const int npass = sg.packed2 ? 2 : 1;
+    for (int pass = 0; pass < npass; ++pass) {
+      const uint8_t* packed = pass ? sg.packed2 : sg.packed;
+      const uint16_t* lut = pass ? sg.lut2 : sg.lut;
+      const int bits = pass ? sg.bits2 : sg.bits;
+      float* dst = part + plane * kMaxM * kTileRows;
+#define B200LUT_PASS(B)                                                                       \
+  stream_pass<T, B, CP, NWARPS, RC>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups,  \
+                                sg.gs, tile, p.G, c0, c1, p.x, p.ldx, M, first)
+      switch (bits) {   // block-uniform
+        case 4: B200LUT_PASS(4); break;
+        case 3: B200LUT_PASS(3); break;
+        case 2: B200LUT_PASS(2); break;
+        default: B200LUT_PASS(1); break;
+      }
+#undef B200LUT_PASS
+      first = false;
+    }
+  }
+  fold_and_store<T, NT>(p, part, si, tile, tile_g, sp);
+}
+
+}  // namespace
+}  // namespace b200lut
+
+#include "gemv_tc.cuh"
+
+namespace b200lut {
+namespace {
+
 constexpr int kWarpsM8 = 16, kWarpsM16 = 8;
 
 size_t smem_bytes_for(int max_tables) {
@@ -503,8 +525,63 @@ int launch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t stream) {
   return B200LUT_OK;
 }
 
+constexpr size_t kMaxDynSmem = 232448 - 1024;   // 227 KB opt-in limit of sm_100, less static shared memory
+
+size_t tc_smem_bytes(int tables, int nblk) {
+  return size_t(kPartBytes) + kTcCtrlBytes + 65536 + size_t(tables) * kTableBytes +
+         size_t(nblk) * kChunkK * kTcTokens * 2;
+}
+
+int tc_max_blocks(int tables) {
+  const size_t fixed = tc_smem_bytes(tables, 0);
+  return fixed >= kMaxDynSmem ? 0 : int((kMaxDynSmem - fixed) / (kChunkK * kTcTokens * 2));
+}
+
+template <typename T>
+int launch_tc(const GemvParams& p, int tables, bool pdl, cudaStream_t stream) {
+  auto kern = gemv_tc_kernel<T>;
+  const int nblk = (p.G + p.split - 1) / p.split;
+  const size_t smem = tc_smem_bytes(tables, nblk);
+  static bool configured[64] = {false};
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         int(kMaxDynSmem)));
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(p.tiles_total * p.split), 1, 1);
+  cfg.blockDim = dim3(kTcThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (p.cluster) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = unsigned(p.split);
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = unsigned(na);
+  B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
+  return B200LUT_OK;
+}
+
 template <typename T>
 int dispatch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t st) {
+  static const int plan = [] { const char* e = getenv("B200LUT_GEMV_PLAN"); return e ? atoi(e) : 0; }();
+  if (p.M == 1 && plan == 81) return launch<T, 8, kWarpsM8, 1>(p, max_tables, pdl, st);
+  if (p.M == 1 && plan == 82) return launch<T, 8, kWarpsM8, 2>(p, max_tables, pdl, st);
+  if (p.M == 1 && plan == 42) return launch<T, 4, kWarpsM8, 2>(p, max_tables, pdl, st);
+  if (p.M == 1 && plan == 22) return launch<T, 2, kWarpsM8, 2>(p, max_tables, pdl, st);
   if (p.M == 1) return launch<T, 1, kWarpsM8, 2>(p, max_tables, pdl, st);
   if (p.M == 2) return launch<T, 2, kWarpsM8, 2>(p, max_tables, pdl, st);
   if (p.M <= 4) return launch<T, 4, kWarpsM8, 2>(p, max_tables, pdl, st);
@@ -538,6 +615,23 @@ int pick_split(int tiles, int G, int sms, int warps) {
     const long per_block = (G + s - 1) / s;
     const long per_warp = (per_block + warps - 1) / warps;
     const long cost = waves * per_warp * 16 + (s > 1 ? 2 + s / 4 : 0);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+  }
+  return best;
+}
+
+// Split policy of the tcgen05 kernel: the four stage groups of a block work on four
+// k-blocks at a time; a block may hold at most max_blocks k-blocks of activations.
+int pick_split_tc(int tiles, int G, int sms, int max_blocks) {
+  int best = 0;
+  long best_cost = -1;
+  for (int s = 1; s <= kMaxClusterSplit; ++s) {
+    if (s > G) break;
+    const long per_block = (G + s - 1) / s;
+    if (per_block > max_blocks) continue;
+    const long blocks = long(tiles) * s;
+    const long waves = (blocks + sms - 1) / sms;
+    const long cost = waves * ((per_block + 3) / 4 + 3) + (s > 1 ? 1 : 0);
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
   }
   return best;
@@ -640,6 +734,27 @@ extern "C" int b200lut_gemv_multi(const void* x, int64_t ldx, int M, int K, int 
     if ((nl + 1) / 2 > max_tables) max_tables = (nl + 1) / 2;
   }
   p.tiles_total = tiles;
+  // back end: the tcgen05 kernel serves 4-bit single-stream segments whose K range per
+  // block fits shared memory next to the pair tables; everything else (other widths, a
+  // second stream, palettes of 32 rows with the fused pair) runs on the mma.sync kernel.
+  static const int tc_enabled = [] {
+    const char* e = getenv("B200LUT_GEMV_TC");
+    return e ? atoi(e) : 1;
+  }();
+  bool use_tc = tc_enabled != 0;
+  int tc_tables = 1;
+  for (int i = 0; i < nseg && use_tc; ++i) {
+    if (segs[i].bits != 4 || segs[i].packed2) use_tc = false;
+    const int nl = segs[i].group_size >= 128 ? 1 : 128 / segs[i].group_size;
+    const int t = ((silu ? 2 : 1) * nl + 1) / 2;
+    if (t > tc_tables) tc_tables = t;
+  }
+  const int tc_blocks = use_tc ? tc_max_blocks(tc_tables) : 0;
+  if (use_tc && split > 0 && (p.G + split - 1) / split > tc_blocks) use_tc = false;
+  if (use_tc && split <= 0) {
+    split = pick_split_tc(tiles, p.G, sm_count_cached(), tc_blocks);
+    if (split <= 0) use_tc = false;
+  }
   const int warps = M <= 8 ? kWarpsM8 : kWarpsM16;
   if (split <= 0) split = pick_split(tiles, p.G, sm_count_cached(), warps);
   B200LUT_REQUIRE(split >= 1 && split <= 16 && split <= p.G, B200LUT_ERR_INVALID,
@@ -658,8 +773,21 @@ extern "C" int b200lut_gemv_multi(const void* x, int64_t ldx, int M, int K, int 
   }
   const bool pdl = (flags & 1) != 0;
   cudaStream_t st = cudaStream_t(stream);
+  if (use_tc) {
+    if (dtype == B200LUT_BF16) return launch_tc<__nv_bfloat16>(p, tc_tables, pdl, st);
+    return launch_tc<__half>(p, tc_tables, pdl, st);
+  }
   if (dtype == B200LUT_BF16) return dispatch<__nv_bfloat16>(p, max_tables, pdl, st);
   return dispatch<__half>(p, max_tables, pdl, st);
+}
+
+// Device-side status of the tcgen05 kernels on the current device (0 = none). A non-zero
+// value means a bounded wait ran out inside a kernel; it is cleared by this call.
+extern "C" int b200lut_device_status(void) {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+  return v;
 }
 
 extern "C" int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out, int M,
