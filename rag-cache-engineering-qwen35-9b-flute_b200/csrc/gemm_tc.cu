@@ -1,7 +1,406 @@
-// Prefill LUT GEMM (placeholder until the tcgen05 kernel lands in this file).
+// Prefill LUT GEMM (M > 16 tokens) on the Blackwell tensor-core path.
+//
+// out[m, n] = sum_k x[m, k] * LUT[n / gs][code(n, k)]: replaces the reference's streaming
+// tensor-core GEMM family (src/flute_extended/src/kernel_streaming.cu:987-1108, K7/K8).
+//
+// One block computes a 128 (weight rows) x NT (tokens, up to 256) output tile over all
+// of K with tcgen05.mma, weights on the M side:
+//   * A operand = dequantised weights, 128 rows x 64 k per stage, living in TENSOR MEMORY.
+//     Lookup warps stream the 4-bit codes from global memory into registers (256-bit
+//     loads), turn each code pair into two palette entries with one shared-memory
+//     lookup (pairtable.cuh) and write the result straight into TMEM with tcgen05.st —
+//     the slab layout's register order is the 16x256b store shape. The dequantised tile
+//     never passes through shared memory, which the B operand needs for itself.
+//   * B operand = activations, NT tokens x 64 k per stage, brought by TMA
+//     (cp.async.bulk.tensor, 128-byte swizzle, zero fill beyond M) into shared memory.
+//   * D = fp32 accumulators in TMEM (128 lanes x NT columns, a second plane for the
+//     fused gate/up form); the epilogue reads them with tcgen05.ld, adds bias, applies
+//     SiLU*mul when asked, rounds once and stores.
+// Warp roles: 0-7 lookup (TMEM lane quarter = warp % 4, two groups alternate k-blocks),
+// 8 = TMA producer, 9 = MMA issuer; warps 0-7 run the epilogue. All mbarrier waits are
+// bounded (tc05.cuh).
+#include <cuda.h>
+
+#include <cstdlib>
+
 #include "common.cuh"
+#include "pairtable.cuh"
+#include "tc05.cuh"
+
+namespace b200lut {
+namespace {
+
+constexpr int kLookupWarps = 8;
+constexpr int kThreads = (kLookupWarps + 2) * 32;
+constexpr int kAStages = 4;            // operand stages in TMEM, 32 columns each
+constexpr int kRing = 4;               // k-blocks of codes in flight per lookup warp
+constexpr int kMaxXStages = 6;
+constexpr uint32_t kCtrlBytes = 1024;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kACol = 256;        // operand stage s at columns [256 + 32 s, 288 + 32 s)
+constexpr size_t kMaxDynSmem = 232448 - 1024;
+
+__device__ int g_gemm_status = 0;
+
+struct GemmParams {
+  const uint8_t* packed[2];
+  const uint16_t* lut[2];
+  const uint16_t* bias[2];
+  uint16_t* out;
+  long long ldo;
+  int M, N, K, G, gs, n_groups;
+  int npass;        // 1, or 2 (second stream / up projection)
+  int plane[2];     // accumulator plane of each pass (0, or 1 for the up projection)
+  int silu;         // epilogue: out = silu(plane 0) * plane 1
+  int NT;           // token tile (multiple of 16, <= 256; <= 128 with two planes)
+  int m_tiles;
+  uint32_t smem_bytes;
+};
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t base = smem_u32(smem);
+  // control block: barriers, the TMEM base and the abort flag
+  const uint32_t bar_xfull = base, bar_xempty = base + 64, bar_afull = base + 128,
+                 bar_aempty = base + 192, bar_done = base + 256;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + 264);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 268);
+
+  int nl = kTileRows / p.gs;
+  if (nl < 1) nl = 1;
+  const int tables = (p.npass * nl + 1) / 2;
+  const uint32_t tbl_addr = (base + kCtrlBytes + 0xFFFFu) & ~0xFFFFu;
+  uint8_t* tbl_ptr = smem + (tbl_addr - base);
+  // activation stages fill the space below and above the 64 KB-aligned tables
+  const uint32_t stage_bytes = uint32_t(p.NT) * 128u;
+  volatile uint32_t* xaddr = reinterpret_cast<volatile uint32_t*>(smem + 512);   // [kMaxXStages]
+  volatile int* nxs_slot = reinterpret_cast<volatile int*>(smem + 544);
+  if (threadIdx.x == 0) {
+    int n = 0;
+    uint32_t a = (base + kCtrlBytes + 1023u) & ~1023u;
+    while (n < kMaxXStages && a + stage_bytes <= tbl_addr) { xaddr[n++] = a; a += stage_bytes; }
+    a = tbl_addr + uint32_t(tables) * kTableBytes;
+    while (n < kMaxXStages && a + stage_bytes <= base + p.smem_bytes) { xaddr[n++] = a; a += stage_bytes; }
+    *nxs_slot = n;
+  }
+
+  const int n_tile = blockIdx.x / p.m_tiles, m_tile = blockIdx.x % p.m_tiles;
+  const int m0 = m_tile * p.NT, n0 = n_tile * kTileRows;
+  const int total = p.G * p.npass;     // k-blocks streamed, pass-major
+
+  asm volatile("griddepcontrol.launch_dependents;");
+
+  // ---- code prefetch ---------------------------------------------------------------------
+  const int q = warp & 3, grp = warp >> 2;
+  uint32_t w[kRing][8];
+  auto block_ptr = [&](int i) -> const uint8_t* {
+    const int pass = i >= p.G ? 1 : 0, c = pass ? i - p.G : i;
+    return p.packed[pass] + (size_t(n_tile) * p.G + c) * 4096 + q * 1024 + lane * 32;
+  };
+  if (warp < kLookupWarps) {
+#pragma unroll
+    for (int u = 0; u < kRing; ++u) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[u][i] = 0u;
+      const int i = grp + 2 * u;
+      ldg_stream256_if(w[u], block_ptr(i < total ? i : 0), i < total ? 1u : 0u);
+    }
+  }
+
+  // ---- setup ----------------------------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kMaxXStages; ++s) {
+      tc::mbar_init(bar_xfull + 8 * s, 1);
+      tc::mbar_init(bar_xempty + 8 * s, 1);
+    }
+    for (int s = 0; s < kAStages; ++s) {
+      tc::mbar_init(bar_afull + 8 * s, 4);
+      tc::mbar_init(bar_aempty + 8 * s, 1);
+    }
+    tc::mbar_init(bar_done, 1);
+    *abort_flag = (*nxs_slot < 2) ? 1 : 0;   // cannot pipeline: drain at once (host prevents this)
+    tc::mbar_init_fence();
+  }
+  if (warp == kLookupWarps) tc::tmem_alloc(base + 264, kTmemCols);
+  for (int pass = 0; pass < p.npass; ++pass)
+    build_tables(tbl_ptr + size_t((pass * nl) >> 1) * kTableBytes + ((pass * nl) & 1) * 128,
+                 p.lut[pass], 4, p.n_groups, n0, p.gs, nl, kThreads);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const int nxs = *nxs_slot > 0 ? *nxs_slot : 1;
+
+  if (warp < kLookupWarps) {
+    // ---- lookup warps: codes -> palette pairs -> TMEM -------------------------------------------
+    uint32_t token;
+    asm volatile("mov.u32 %0, 0;" : "=r"(token));
+    const uint32_t lane_base = tbl_addr + lane * 4 + token;
+    for (int i0 = grp; i0 < total; i0 += 2 * kRing) {
+#pragma unroll
+      for (int u = 0; u < kRing; ++u) {
+        const int i = i0 + 2 * u;
+        if (i < total) {
+          const int stage = i % kAStages, use = i / kAStages;
+          const int pass = i >= p.G ? 1 : 0;
+          if (use > 0)
+            tc::mbar_wait(bar_aempty + 8 * stage, uint32_t(use - 1) & 1u, abort_flag,
+                          &g_gemm_status, tc::kStatusWaitEmpty);
+          tc::fence_after_sync();
+#pragma unroll
+          for (int sl = 0; sl < 2; ++sl) {
+            const int rowslab = 2 * q + sl;
+            const int pal = pass * nl + (nl == 1 ? 0 : (nl == 2 ? rowslab >> 2 : rowslab >> 1));
+            const uint32_t tb = lane_base + uint32_t(pal >> 1) * kTableBytes + uint32_t(pal & 1) * 128u;
+            uint32_t r[16];
+#pragma unroll
+            for (int kt = 0; kt < 4; ++kt) {
+              const uint32_t word = w[u][4 * sl + kt];
+              // slab fields (row g, k 0-1), (g+8, k 0-1), (g, k 2-3), (g+8, k 2-3); the store
+              // shape wants (g, c), (g, c+1), (g+8, c), (g+8, c+1): fields 0, 2, 1, 3
+              r[4 * kt + 0] = lds32(__byte_perm(word, tb, 0x7604u));
+              r[4 * kt + 1] = lds32(__byte_perm(word, tb, 0x7624u));
+              r[4 * kt + 2] = lds32(__byte_perm(word, tb, 0x7614u));
+              r[4 * kt + 3] = lds32(__byte_perm(word, tb, 0x7634u));
+            }
+            tc::tmem_st_16x256b_x4(tmem + (uint32_t(32 * q + 16 * sl) << 16) + kACol + 32u * stage, r);
+          }
+          const int in = i + 2 * kRing;
+          ldg_stream256_if(w[u], block_ptr(in < total ? in : 0), in < total ? 1u : 0u);
+          tc::wait_st();
+          tc::fence_before_sync();
+          if (lane == 0) tc::mbar_arrive(bar_afull + 8 * stage);
+        }
+      }
+    }
+  } else if (warp == kLookupWarps) {
+    // ---- TMA producer: activations of k-block c, tokens m0 .. m0 + NT ---------------------------
+    for (int i = 0; i < total; ++i) {
+      const int xs = i % nxs, use = i / nxs;
+      const int c = i >= p.G ? i - p.G : i;
+      if (use > 0)
+        tc::mbar_wait(bar_xempty + 8 * xs, uint32_t(use - 1) & 1u, abort_flag, &g_gemm_status,
+                      tc::kStatusWaitEmpty);
+      if (lane == 0 && !*abort_flag) {
+        tc::mbar_expect_tx(bar_xfull + 8 * xs, stage_bytes);
+        tma_load_2d(xaddr[xs], &xmap, bar_xfull + 8 * xs, c * kChunkK, m0);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ---- MMA issuer ---------------------------------------------------------------------------
+    constexpr uint32_t kFmt = DType<T>::id == B200LUT_BF16 ? 1u : 0u;
+    const uint32_t idesc = tc::instr_desc(kFmt, 128, uint32_t(p.NT));
+    for (int i = 0; i < total; ++i) {
+      const int stage = i % kAStages, ause = i / kAStages;
+      const int xs = i % nxs, xuse = i / nxs;
+      const int pass = i >= p.G ? 1 : 0, blk = pass ? i - p.G : i;
+      tc::mbar_wait(bar_xfull + 8 * xs, uint32_t(xuse) & 1u, abort_flag, &g_gemm_status,
+                    tc::kStatusWaitLoad);
+      tc::mbar_wait(bar_afull + 8 * stage, uint32_t(ause) & 1u, abort_flag, &g_gemm_status,
+                    tc::kStatusWaitFull);
+      tc::fence_after_sync();
+      if (lane == 0) {
+        // the first k-block that targets a plane overwrites it
+        const bool first_of_plane = blk == 0 && (pass == 0 || p.plane[1] != p.plane[0]);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t bdesc = tc::smem_desc(xaddr[xs] + 32u * ks, 16u, 1024u, 2u);
+          tc::mma_ts(tmem + uint32_t(p.plane[pass] * p.NT), tmem + kACol + 32u * stage + 8u * ks,
+                     bdesc, idesc, (first_of_plane && ks == 0) ? 0u : 1u);
+        }
+        tc::mma_commit(bar_xempty + 8 * xs);
+        tc::mma_commit(bar_aempty + 8 * stage);
+        if (i == total - 1) tc::mma_commit(bar_done);
+      }
+      __syncwarp();
+    }
+  }
+
+  // ---- epilogue: TMEM -> bias / SiLU*mul -> one rounding -> global -----------------------------
+  if (warp < kLookupWarps) {
+    tc::mbar_wait(bar_done, 0u, abort_flag, &g_gemm_status, tc::kStatusWaitDone);
+    tc::fence_after_sync();
+    const int n = n0 + 32 * q + lane;
+    const float b0 = p.bias[0] ? DType<T>::to_float(p.bias[0][n]) : 0.f;
+    const float b1 = (p.npass > 1 && p.bias[1]) ? DType<T>::to_float(p.bias[1][n]) : 0.f;
+    const int half_cols = p.NT / 2;
+    for (int cb = grp * half_cols; cb < (grp + 1) * half_cols; cb += 16) {
+      uint32_t r0[16], r1[16];
+      tc::tmem_ld_32x32b_x16(tmem + (uint32_t(32 * q) << 16) + uint32_t(cb), r0);
+      if (p.silu) tc::tmem_ld_32x32b_x16(tmem + (uint32_t(32 * q) << 16) + uint32_t(p.NT + cb), r1);
+      tc::wait_ld();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int tok = m0 + cb + j;
+        if (tok < p.M) {
+          float v = __uint_as_float(r0[j]) + b0;
+          if (p.silu) {
+            const float u = __uint_as_float(r1[j]) + b1;
+            v = v / (1.f + __expf(-v)) * u;
+          } else if (p.npass > 1) {
+            v += b1;     // second stream: both biases belong to the one output
+          }
+          p.out[size_t(tok) * p.ldo + n] = DType<T>::from_float(v);
+        }
+      }
+    }
+    tc::fence_before_sync();
+  }
+  __syncthreads();
+  if (warp == kLookupWarps) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+template <typename T>
+int launch(const CUtensorMap& map, const GemmParams& p, int n_tiles, bool pdl, cudaStream_t stream) {
+  auto kern = gemm_tc_kernel<T>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         int(kMaxDynSmem)));
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(n_tiles * p.m_tiles), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = p.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int na = 0;
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = unsigned(na);
+  B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map, p));
+  return B200LUT_OK;
+}
+
+}  // namespace
+
+}  // namespace b200lut
+
 using namespace b200lut;
-extern "C" int b200lut_gemm(const void*, int64_t, int, int, int, const b200lut_segment*, int, int,
-                            void*) {
-  return fail(B200LUT_ERR_UNSUPPORTED, "b200lut_gemm is not built yet");
+
+// Device-side status of the tensor-core kernel on the current device (0 = none). A
+// non-zero value means a bounded wait ran out inside a kernel; cleared by this call.
+extern "C" int b200lut_device_status(void) {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
+  return v;
+}
+
+extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
+                            const b200lut_segment* seg, int epilogue, int flags, void* stream) {
+  B200LUT_REQUIRE(x && seg, B200LUT_ERR_INVALID, "null x or segment");
+  B200LUT_REQUIRE(M >= 1, B200LUT_ERR_INVALID, "M must be >= 1, got %d", M);
+  B200LUT_REQUIRE(K > 0 && K % kChunkK == 0, B200LUT_ERR_INVALID,
+                  "K must be a positive multiple of 64, got %d", K);
+  B200LUT_REQUIRE(dtype == B200LUT_BF16 || dtype == B200LUT_F16, B200LUT_ERR_INVALID,
+                  "dtype must be B200LUT_BF16 or B200LUT_F16");
+  B200LUT_REQUIRE(epilogue == B200LUT_EPI_NONE || epilogue == B200LUT_EPI_SILU_MUL,
+                  B200LUT_ERR_INVALID, "unknown epilogue %d", epilogue);
+  B200LUT_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K, B200LUT_ERR_ALIGN,
+                  "x must be 16-byte aligned with a row stride that is a multiple of 8 and >= K");
+  const b200lut_segment& s = *seg;
+  B200LUT_REQUIRE(s.packed && s.lut && s.out, B200LUT_ERR_INVALID, "null codes, palette or output");
+  B200LUT_REQUIRE(s.N > 0 && s.N % kTileRows == 0 && s.ldo >= s.N, B200LUT_ERR_INVALID,
+                  "N must be a positive multiple of 128 and ldo >= N (N=%d)", s.N);
+  const bool silu = epilogue == B200LUT_EPI_SILU_MUL;
+  const bool two = s.packed2 != nullptr;
+  B200LUT_REQUIRE(!silu || two, B200LUT_ERR_INVALID,
+                  "the silu-mul epilogue needs the up projection in packed2 / lut2");
+  B200LUT_REQUIRE(s.bits == 4 && (!two || (s.lut2 && s.bits2 == 4)), B200LUT_ERR_UNSUPPORTED,
+                  "the prefill GEMM serves 4-bit codes (got %d / %d)", s.bits, s.bits2);
+  B200LUT_REQUIRE(s.group_size >= 32 && s.n_groups >= 1 &&
+                      ((s.group_size < 128 && (s.group_size & (s.group_size - 1)) == 0) ||
+                       s.group_size % 128 == 0),
+                  B200LUT_ERR_UNSUPPORTED, "group_size %d not served (32, 64 or a multiple of 128)",
+                  s.group_size);
+  B200LUT_REQUIRE(aligned16(s.packed) && (!two || aligned16(s.packed2)), B200LUT_ERR_ALIGN,
+                  "code buffers must be 16-byte aligned");
+
+  GemmParams p = {};
+  p.packed[0] = static_cast<const uint8_t*>(s.packed);
+  p.lut[0] = static_cast<const uint16_t*>(s.lut);
+  p.bias[0] = static_cast<const uint16_t*>(s.bias);
+  p.packed[1] = static_cast<const uint8_t*>(s.packed2);
+  p.lut[1] = static_cast<const uint16_t*>(s.lut2);
+  p.out = static_cast<uint16_t*>(s.out);
+  p.ldo = s.ldo;
+  p.M = M; p.N = s.N; p.K = K; p.G = K / kChunkK;
+  p.gs = s.group_size; p.n_groups = s.n_groups;
+  p.npass = two ? 2 : 1;
+  p.plane[0] = 0;
+  p.plane[1] = silu ? 1 : 0;
+  p.silu = silu ? 1 : 0;
+  const int nt_max = silu ? 128 : 256;
+  int NT = ((M + 31) / 32) * 32;           // even halves of whole 16-column epilogue chunks
+  if (NT > nt_max) NT = nt_max;
+  p.NT = NT;
+  p.m_tiles = (M + NT - 1) / NT;
+  const int nl = s.group_size >= 128 ? 1 : 128 / s.group_size;
+  const int tables = (p.npass * nl + 1) / 2;
+  // control + alignment slack + tables + as many activation stages as fit (at least two)
+  const size_t fixed = kCtrlBytes + size_t(tables) * kTableBytes;
+  B200LUT_REQUIRE(fixed + 65536 + 2 * size_t(NT) * 128 <= kMaxDynSmem, B200LUT_ERR_UNSUPPORTED,
+                  "group_size %d with two code streams needs more shared memory than an SM has",
+                  s.group_size);
+  p.smem_bytes = uint32_t(kMaxDynSmem);
+
+  EncodeTiledFn enc = encode_fn();
+  B200LUT_REQUIRE(enc != nullptr, B200LUT_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(M)};
+  const cuuint64_t strides[1] = {cuuint64_t(ldx) * 2};
+  const cuuint32_t box[2] = {cuuint32_t(kChunkK), cuuint32_t(NT)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(&map, dtype == B200LUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         2, const_cast<void*>(x), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200LUT_REQUIRE(r == CUDA_SUCCESS, B200LUT_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", int(r));
+  const bool pdl = (flags & 1) != 0;
+  if (dtype == B200LUT_BF16)
+    return launch<__nv_bfloat16>(map, p, s.N / kTileRows, pdl, cudaStream_t(stream));
+  return launch<__half>(map, p, s.N / kTileRows, pdl, cudaStream_t(stream));
 }

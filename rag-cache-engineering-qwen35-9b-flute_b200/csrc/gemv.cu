@@ -32,6 +32,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "pairtable.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -40,7 +41,6 @@ namespace {
 
 constexpr int kMaxSeg = 8;
 constexpr int kMaxM = 16;
-constexpr uint32_t kTableBytes = 65536;   // one pair table: 256 entries x 256 B (two slots)
 constexpr uint32_t kPartBytes = 2 * kMaxM * kTileRows * 4;  // two result planes (gate/up)
 constexpr int kMaxClusterSplit = 8;
 
@@ -63,41 +63,6 @@ struct GemvParams {
   int* tickets;    // workspace fold: [tiles_total]
   SegDev seg[kMaxSeg];
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-// 256-bit streaming load: read-only path, no L1 allocation, first in line for L2 eviction
-__device__ __forceinline__ void ldg_stream256(uint32_t* r, const uint8_t* p) {
-  asm volatile(
-      "ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7])
-      : "l"(p));
-}
-
-// Same load, executed only when `on` is non-zero; the registers keep their old value
-// otherwise (read-write operands: no select or copy after the load, so nothing waits
-// on it until the data is actually used).
-__device__ __forceinline__ void ldg_stream256_if(uint32_t* r, const uint8_t* p, uint32_t on) {
-  asm volatile(
-      "{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %9, 0;\n\t"
-      "@q ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n\t}"
-      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
-        "+r"(r[7])
-      : "l"(p), "r"(on));
-}
-
-// Pair-table lookup. Deliberately NOT volatile, so the scheduler may issue lookups of
-// later fragments ahead of the current mma. Ordering against the barriers around the
-// table's lifetime is carried by data: every address includes a token defined after
-// the build barrier, and the accumulators are pinned before the barrier that ends it.
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
 
 template <typename T>
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
@@ -137,25 +102,6 @@ __device__ __forceinline__ uint32_t field_addr(const uint32_t (&w)[8 * BITS], in
     else if (sh >= 8) v = w[m] >> (sh - 8);
     else v = w[m] << (8 - sh);
     return (v & kMask) | base;
-  }
-}
-
-// Fill the pair table(s) of one pass: entry v -> LUT[v & mask] | LUT[v >> bits] << 16,
-// one table slot per distinct palette of the tile (nl = 1, 2 or 4 palettes per tile).
-__device__ void build_tables(uint8_t* tbl_ptr, const uint16_t* __restrict__ lut, int bits,
-                             int n_groups, int row0, int gs, int nl, int nthreads) {
-  const int entries = 1 << (2 * bits);
-  const uint32_t mask = (1u << bits) - 1u;
-  const int rows_per_lut = kTileRows / nl;
-  for (int idx = threadIdx.x; idx < nl * entries * 8; idx += nthreads) {
-    const int q = idx & 7, e = (idx >> 3) & (entries - 1), sl = idx >> (3 + 2 * bits);
-    int grp = (row0 + sl * rows_per_lut) / gs;
-    if (grp > n_groups - 1) grp = n_groups - 1;
-    const uint16_t* row = lut + (size_t(grp) << bits);
-    const uint32_t v = uint32_t(__ldg(row + (e & mask))) | (uint32_t(__ldg(row + (e >> bits))) << 16);
-    uint4* dst = reinterpret_cast<uint4*>(tbl_ptr + size_t(sl >> 1) * kTableBytes + e * 256 +
-                                          (sl & 1) * 128 + q * 16);
-    *dst = make_uint4(v, v, v, v);
   }
 }
 
@@ -474,14 +420,6 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
   fold_and_store<T, NT>(p, part, si, tile, tile_g, sp);
 }
 
-}  // namespace
-}  // namespace b200lut
-
-#include "gemv_tc.cuh"
-
-namespace b200lut {
-namespace {
-
 constexpr int kWarpsM8 = 16, kWarpsM16 = 8;
 
 size_t smem_bytes_for(int max_tables) {
@@ -503,56 +441,6 @@ int launch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(unsigned(p.tiles_total * p.split), 1, 1);
   cfg.blockDim = dim3(NWARPS * 32, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  int na = 0;
-  if (p.cluster) {
-    attr[na].id = cudaLaunchAttributeClusterDimension;
-    attr[na].val.clusterDim.x = unsigned(p.split);
-    attr[na].val.clusterDim.y = 1;
-    attr[na].val.clusterDim.z = 1;
-    ++na;
-  }
-  if (pdl) {
-    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[na].val.programmaticStreamSerializationAllowed = 1;
-    ++na;
-  }
-  cfg.attrs = attr;
-  cfg.numAttrs = unsigned(na);
-  B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
-  return B200LUT_OK;
-}
-
-constexpr size_t kMaxDynSmem = 232448 - 1024;   // 227 KB opt-in limit of sm_100, less static shared memory
-
-size_t tc_smem_bytes(int tables, int nblk) {
-  return size_t(kPartBytes) + kTcCtrlBytes + 65536 + size_t(tables) * kTableBytes +
-         size_t(nblk) * kChunkK * kTcTokens * 2;
-}
-
-int tc_max_blocks(int tables) {
-  const size_t fixed = tc_smem_bytes(tables, 0);
-  return fixed >= kMaxDynSmem ? 0 : int((kMaxDynSmem - fixed) / (kChunkK * kTcTokens * 2));
-}
-
-template <typename T>
-int launch_tc(const GemvParams& p, int tables, bool pdl, cudaStream_t stream) {
-  auto kern = gemv_tc_kernel<T>;
-  const int nblk = (p.G + p.split - 1) / p.split;
-  const size_t smem = tc_smem_bytes(tables, nblk);
-  static bool configured[64] = {false};
-  int dev = 0;
-  B200LUT_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
-    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         int(kMaxDynSmem)));
-    configured[dev] = true;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(unsigned(p.tiles_total * p.split), 1, 1);
-  cfg.blockDim = dim3(kTcThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -615,23 +503,6 @@ int pick_split(int tiles, int G, int sms, int warps) {
     const long per_block = (G + s - 1) / s;
     const long per_warp = (per_block + warps - 1) / warps;
     const long cost = waves * per_warp * 16 + (s > 1 ? 2 + s / 4 : 0);
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
-  }
-  return best;
-}
-
-// Split policy of the tcgen05 kernel: the four stage groups of a block work on four
-// k-blocks at a time; a block may hold at most max_blocks k-blocks of activations.
-int pick_split_tc(int tiles, int G, int sms, int max_blocks) {
-  int best = 0;
-  long best_cost = -1;
-  for (int s = 1; s <= kMaxClusterSplit; ++s) {
-    if (s > G) break;
-    const long per_block = (G + s - 1) / s;
-    if (per_block > max_blocks) continue;
-    const long blocks = long(tiles) * s;
-    const long waves = (blocks + sms - 1) / sms;
-    const long cost = waves * ((per_block + 3) / 4 + 3) + (s > 1 ? 1 : 0);
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
   }
   return best;
@@ -734,27 +605,6 @@ extern "C" int b200lut_gemv_multi(const void* x, int64_t ldx, int M, int K, int 
     if ((nl + 1) / 2 > max_tables) max_tables = (nl + 1) / 2;
   }
   p.tiles_total = tiles;
-  // back end: the tcgen05 kernel serves 4-bit single-stream segments whose K range per
-  // block fits shared memory next to the pair tables; everything else (other widths, a
-  // second stream, palettes of 32 rows with the fused pair) runs on the mma.sync kernel.
-  static const int tc_enabled = [] {
-    const char* e = getenv("B200LUT_GEMV_TC");
-    return e ? atoi(e) : 1;
-  }();
-  bool use_tc = tc_enabled != 0;
-  int tc_tables = 1;
-  for (int i = 0; i < nseg && use_tc; ++i) {
-    if (segs[i].bits != 4 || segs[i].packed2) use_tc = false;
-    const int nl = segs[i].group_size >= 128 ? 1 : 128 / segs[i].group_size;
-    const int t = ((silu ? 2 : 1) * nl + 1) / 2;
-    if (t > tc_tables) tc_tables = t;
-  }
-  const int tc_blocks = use_tc ? tc_max_blocks(tc_tables) : 0;
-  if (use_tc && split > 0 && (p.G + split - 1) / split > tc_blocks) use_tc = false;
-  if (use_tc && split <= 0) {
-    split = pick_split_tc(tiles, p.G, sm_count_cached(), tc_blocks);
-    if (split <= 0) use_tc = false;
-  }
   const int warps = M <= 8 ? kWarpsM8 : kWarpsM16;
   if (split <= 0) split = pick_split(tiles, p.G, sm_count_cached(), warps);
   B200LUT_REQUIRE(split >= 1 && split <= 16 && split <= p.G, B200LUT_ERR_INVALID,
@@ -773,21 +623,8 @@ extern "C" int b200lut_gemv_multi(const void* x, int64_t ldx, int M, int K, int 
   }
   const bool pdl = (flags & 1) != 0;
   cudaStream_t st = cudaStream_t(stream);
-  if (use_tc) {
-    if (dtype == B200LUT_BF16) return launch_tc<__nv_bfloat16>(p, tc_tables, pdl, st);
-    return launch_tc<__half>(p, tc_tables, pdl, st);
-  }
   if (dtype == B200LUT_BF16) return dispatch<__nv_bfloat16>(p, max_tables, pdl, st);
   return dispatch<__half>(p, max_tables, pdl, st);
-}
-
-// Device-side status of the tcgen05 kernels on the current device (0 = none). A non-zero
-// value means a bounded wait ran out inside a kernel; it is cleared by this call.
-extern "C" int b200lut_device_status(void) {
-  int v = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
-  if (v != 0) cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
-  return v;
 }
 
 extern "C" int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out, int M,

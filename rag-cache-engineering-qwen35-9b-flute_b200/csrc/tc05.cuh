@@ -21,7 +21,7 @@ enum : int {
   kStatusWaitLoad = 4     // a consumer gave up waiting for a bulk (TMA) load
 };
 
-constexpr uint32_t kMaxPolls = 1u << 22;   // ~ a second of polling at most
+constexpr long long kWaitCycles = 20000000;   // ~10 ms at 2 GHz: far beyond any healthy wait
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -41,11 +41,12 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// Non-blocking phase test.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -53,15 +54,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. `abort_flag` is a shared-memory word: once any waiter times out it is
-// set, and every later wait in the block returns at once. Returns false on abort.
+// Bounded wait. `abort_flag` is a shared-memory word: once any waiter in the block has
+// timed out it is set, and every later wait returns at once, so a block that lost a
+// signal drains in microseconds. The deadline is in SM clock cycles. Returns false on
+// abort.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int why) {
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u) {
+  if (mbar_test(bar, parity)) return true;
+  if (*abort_flag) return false;
+  const long long t0 = clock64();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if ((i & 15u) == 0u) {
       if (*abort_flag) return false;
-      __nanosleep(64);
+      if (clock64() - t0 > kWaitCycles) break;
     }
   }
   *abort_flag = 1;

@@ -279,8 +279,14 @@ class PalettizedLinear(nn.Module):
         segs = _lib.make_segments([self._segment_desc(out)])
         if M <= GEMV_MAX_M:
             _lib.gemv_multi(x2, segs, 1, flags=_flags())
-        else:
+        elif self.bitwidth == 4 and (not self.has_stream2 or self.bitwidth2 == 4):
             _lib.gemm(x2, segs, flags=_flags())
+        else:
+            # widths the tensor-core GEMM does not serve yet: decode kernel, 16 rows at a time
+            for r0 in range(0, M, GEMV_MAX_M):
+                rows = slice(r0, min(M, r0 + GEMV_MAX_M))
+                _lib.gemv_multi(x2[rows], _lib.make_segments([self._segment_desc(out[rows])]), 1,
+                                flags=_flags())
         return out
 
     def _reference_matmul(self, x2: torch.Tensor) -> torch.Tensor:

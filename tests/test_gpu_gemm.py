@@ -1,0 +1,99 @@
+"""GPU parity of the prefill GEMM (M > 16, tcgen05 / TMEM) against the CPU oracle.
+
+Tolerance: max |got - want| / max |want| <= 1e-2 (16-bit output, fp32 accumulate).
+Dequantised weights are checked BIT-EXACT through the same kernel with one-hot
+activations (1.0 * w + zeros is exact in fp32 and in the 16-bit output)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, Case, pkg, rel_err
+from oracle import lut_linear_oracle as orc
+
+pytestmark = pytest.mark.gpu
+L = pkg._lib
+
+
+@pytest.fixture(autouse=True)
+def _no_device_error():
+    yield
+    torch.cuda.synchronize()
+    assert L.lib().b200lut_device_status() == 0, "a bounded wait ran out inside a kernel"
+
+
+@pytest.mark.parametrize("N,K,gs,dtype,M", (
+    (128, 64, 128, torch.bfloat16, 17),
+    (256, 256, 128, torch.bfloat16, 32),
+    (512, 1024, 64, torch.float16, 100),
+    (1024, 4096, 128, torch.bfloat16, 128),
+    (384, 512, 32, torch.bfloat16, 64),
+    (1024, 1024, 128, torch.float16, 300),
+    (256, 2048, 128, torch.bfloat16, 513),
+))
+def test_gemm_matches_oracle(N, K, gs, dtype, M):
+    case = Case(N, K, gs, 4, dtype, seed=N + K + M)
+    x = case.x(M)
+    got = case.module()(x.cuda())
+    assert got.shape == (M, N) and not torch.isnan(got.float()).any()
+    assert rel_err(got, case.oracle(x)) <= TOL
+
+
+@pytest.mark.parametrize("gs,dtype", ((128, torch.bfloat16), (64, torch.float16), (32, torch.bfloat16)))
+def test_weights_through_the_gemm_are_bit_exact(gs, dtype):
+    N, K = 256, 192
+    case = Case(N, K, gs, 4, dtype, seed=gs)
+    x = torch.zeros(K, K, dtype=dtype)
+    x[torch.arange(K), torch.arange(K)] = 1.0
+    W = case.module()(x.cuda()).cpu().t()          # [N, K]
+    assert torch.equal(W.float(), case.w1)
+
+
+def test_bias_second_stream_and_token_tail():
+    case = Case(256, 512, 128, 4, torch.bfloat16, seed=9, bits2=4, bias=True)
+    for M in (33, 257):
+        x = case.x(M)
+        assert rel_err(case.module()(x.cuda()), case.oracle(x)) <= TOL
+
+
+def test_fused_gate_up_prefill():
+    dt = torch.bfloat16
+    gate, up = Case(512, 256, 128, 4, dt, seed=4, lut_std=0.05), Case(512, 256, 128, 4, dt, seed=5)
+    M = 200
+    x = gate.x(M).cuda()
+    g, u = gate.module(), up.module()
+    out = torch.empty(M, 512, dtype=dt, device="cuda")
+    d = g._segment_desc(out)
+    d.update(packed2=u._packed, lut2=u.lut, bits2=4)
+    L.gemm(x, L.make_segments([d]), epilogue=L.EPI_SILU_MUL)
+    want = orc.silu_mul_fused(x.cpu().float() @ gate.w1.t(), x.cpu().float() @ up.w1.t(), dt)
+    assert rel_err(out, want) <= TOL
+
+
+def test_other_widths_route_through_the_decode_kernel():
+    case = Case(256, 256, 64, 3, torch.float16, seed=12)
+    x = case.x(40)
+    assert rel_err(case.module()(x.cuda()), case.oracle(x)) <= TOL
+
+
+def test_prefill_shape_of_the_9b_model_sampled():
+    # M = 2048, K = 4096, N = 12288 (gate/up shape): every token, 512 sampled weight rows
+    N, K, M, gs = 12288, 4096, 2048, 128
+    blob = pkg.synthetic.random_blob_on_device(N, K, 4, 77, "cuda")
+    lut = pkg.synthetic.make_lut(N // gs, 4, torch.bfloat16, 77)
+    mod = pkg.PalettizedLinear(blob, lut.cuda(), 4, gs, N, K).cuda()
+    x = pkg.synthetic.make_x(M, K, torch.bfloat16, 78)
+    got = mod(x.cuda())
+    rows = torch.cat([torch.arange(t * 128, t * 128 + 128) for t in (0, 37, 70, 95)])
+    codes = L.unpack_codes(mod._packed, N, K, 4)[rows.cuda()].cpu().numpy()
+    w = torch.empty(len(rows), K)
+    for j, r in enumerate(rows.tolist()):
+        w[j] = lut[r // gs].float()[torch.from_numpy(codes[j].astype(np.int64))]
+    want = (x.float() @ w.t()).to(torch.bfloat16)
+    assert rel_err(got[:, rows.cuda()], want) <= TOL
+    # the block-rotated variant: same GEMM behind a 128-point Hadamard of the activations
+    xr = pkg.fht.fht_block(x.cuda(), 128)
+    got_r = mod(xr)
+    want_r = (orc.fht_block(x, 128).float() @ w.t()).to(torch.bfloat16)
+    assert rel_err(got_r[:, rows.cuda()], want_r) <= TOL
