@@ -379,11 +379,19 @@ extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
   p.m_tiles = (M + NT - 1) / NT;
   const int nl = s.group_size >= 128 ? 1 : 128 / s.group_size;
   const int tables = (p.npass * nl + 1) / 2;
-  // control + alignment slack + tables + as many activation stages as fit (at least two)
-  const size_t fixed = kCtrlBytes + size_t(tables) * kTableBytes;
-  B200LUT_REQUIRE(fixed + 65536 + 2 * size_t(NT) * 128 <= kMaxDynSmem, B200LUT_ERR_UNSUPPORTED,
-                  "group_size %d with two code streams needs more shared memory than an SM has",
-                  s.group_size);
+  // Activation stages fill what the control block and the 64 KB-aligned tables leave
+  // free. The dynamic window starts 1 KB into the shared window on sm_100; the kernel
+  // recomputes the stage count from its real base and drains with a status if fewer
+  // than two fit.
+  {
+    const size_t stage = size_t(NT) * 128, win0 = 1024, tbl0 = 65536;
+    const size_t below = (tbl0 - ((win0 + kCtrlBytes + 1023) & ~size_t(1023))) / stage;
+    const size_t top = win0 + kMaxDynSmem, tbl1 = tbl0 + size_t(tables) * kTableBytes;
+    const size_t above = top > tbl1 ? (top - tbl1) / stage : 0;
+    B200LUT_REQUIRE(tbl1 <= top && below + above >= 2, B200LUT_ERR_UNSUPPORTED,
+                    "group_size %d with %d code stream(s) leaves no room for two activation "
+                    "stages in shared memory", s.group_size, p.npass);
+  }
   p.smem_bytes = uint32_t(kMaxDynSmem);
 
   EncodeTiledFn enc = encode_fn();

@@ -63,6 +63,7 @@ def test_fused_gate_up_prefill():
     M = 200
     x = gate.x(M).cuda()
     g, u = gate.module(), up.module()
+    u._ensure_packed()
     out = torch.empty(M, 512, dtype=dt, device="cuda")
     d = g._segment_desc(out)
     d.update(packed2=u._packed, lut2=u.lut, bits2=4)
