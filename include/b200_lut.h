@@ -147,6 +147,35 @@ int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out,
                  int M, int N, int K, int bits, int group_size, int n_groups, int dtype,
                  int split, void* workspace, size_t workspace_bytes, void* stream);
 
+/* One decode GEMV launch inside a persistent plan: what b200lut_gemv_multi takes, plus
+ * the index of the earlier job that produces this job's activation rows (-1: none). */
+typedef struct b200lut_job {
+  const void* x;          /* [M, ldx] activation rows (device) */
+  int64_t ldx;
+  int K;
+  int nseg;               /* 1..8 */
+  int epilogue;           /* B200LUT_EPI_* */
+  int dep;                /* producer job index (< this job's index) or -1 */
+  b200lut_segment segs[8];
+} b200lut_job;
+
+/* A plan runs a whole list of decode jobs (all projections of a model step) in ONE
+ * cooperative launch with one block per SM: code bytes stay in flight across job
+ * boundaries, and a job starts its math when the job it depends on has finished
+ * (bounded wait on a completion counter). Replaces the reference's per-module launch
+ * chain under CUDA-graph replay (src/docs/ARCHITECTURE.md section 3,
+ * src/scripts/palettized_modules.py:870-983).
+ * b200lut_plan_bytes: size of the caller-owned device buffer that holds the job table,
+ * counters and the split-fold workspace (0 on invalid input).
+ * b200lut_plan_build: validates and uploads the jobs (synchronises the stream).
+ * b200lut_plan_run: one launch; may be captured in a CUDA graph; launches of one plan
+ * must not overlap. b200lut_plan_status: B200LUT_ERR_DEVICE if a wait ever ran out. */
+size_t b200lut_plan_bytes(const b200lut_job* jobs, int njobs, int M, int dtype);
+int b200lut_plan_build(void* plan, size_t plan_bytes, const b200lut_job* jobs, int njobs, int M,
+                       int dtype, void* stream);
+int b200lut_plan_run(void* plan, int M, int dtype, void* stream);
+int b200lut_plan_status(const void* plan);
+
 /* ------------------------------------------------------------------------- *
  * Prefill GEMM (M > 16), tcgen05 / TMEM
  * ------------------------------------------------------------------------- */

@@ -27,6 +27,7 @@ EXPORTS = (
     "b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes",
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
+    "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
 
@@ -39,6 +40,15 @@ class Segment(ctypes.Structure):
         ("ldo", ctypes.c_int64),
         ("N", ctypes.c_int), ("group_size", ctypes.c_int), ("n_groups", ctypes.c_int),
         ("bits", ctypes.c_int), ("bits2", ctypes.c_int), ("reserved", ctypes.c_int),
+    ]
+
+
+class Job(ctypes.Structure):
+    """struct b200lut_job."""
+    _fields_ = [
+        ("x", ctypes.c_void_p), ("ldx", ctypes.c_int64),
+        ("K", ctypes.c_int), ("nseg", ctypes.c_int), ("epilogue", ctypes.c_int),
+        ("dep", ctypes.c_int), ("segs", Segment * 8),
     ]
 
 
@@ -88,6 +98,14 @@ def lib() -> ctypes.CDLL:
     L.b200lut_gemm.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32, vp]
     L.b200lut_fht.restype = i32
     L.b200lut_fht.argtypes = [vp, vp, vp, vp, i32, i32, i64, i64, i32, i32, i32, vp]
+    L.b200lut_plan_bytes.restype = sz
+    L.b200lut_plan_bytes.argtypes = [ctypes.POINTER(Job), i32, i32, i32]
+    L.b200lut_plan_build.restype = i32
+    L.b200lut_plan_build.argtypes = [vp, sz, ctypes.POINTER(Job), i32, i32, i32, vp]
+    L.b200lut_plan_run.restype = i32
+    L.b200lut_plan_run.argtypes = [vp, i32, i32, vp]
+    L.b200lut_plan_status.restype = i32
+    L.b200lut_plan_status.argtypes = [vp]
     _lib = L
     return L
 
@@ -239,3 +257,43 @@ def fht(x: torch.Tensor, signs: Optional[torch.Tensor], mode: int = FHT_FORWARD,
                                 x.stride(0), out.stride(0), dtype_id(x.dtype), mode, block,
                                 _stream(x)))
     return out
+
+
+class DecodePlan:
+    """A persistent decode plan: a list of decode GEMV jobs run by ONE cooperative
+    launch (b200lut_plan_*). jobs: dicts with x (CUDA tensor [M, K]), segs (list of
+    segment dicts as for make_segments), epilogue and dep (index of the producing job
+    or -1). The plan keeps references to every tensor it points to."""
+
+    def __init__(self, jobs: Sequence[dict], M: int, dtype: torch.dtype, device):
+        self.M, self.dtype, self.device = int(M), dtype, torch.device(device)
+        self._keep = list(jobs)
+        arr = (Job * len(jobs))()
+        for j, d in zip(arr, jobs):
+            x = d["x"]
+            _need_cuda(x, "x")
+            if x.shape[0] != M or x.stride(1) != 1:
+                raise ValueError("every job's x must be [M, K] with a contiguous last dim")
+            j.x, j.ldx, j.K = x.data_ptr(), x.stride(0), x.shape[1]
+            segs = make_segments(d["segs"])
+            j.nseg, j.epilogue, j.dep = len(d["segs"]), int(d.get("epilogue", EPI_NONE)), int(d.get("dep", -1))
+            for i in range(len(d["segs"])):
+                j.segs[i] = segs[i]
+        did = dtype_id(dtype)
+        with torch.cuda.device(self.device):
+            nbytes = lib().b200lut_plan_bytes(arr, len(jobs), self.M, did)
+            if nbytes == 0:
+                check(lib().b200lut_plan_build(None, 0, arr, len(jobs), self.M, did, None) or 1)
+            self.buffer = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            check(lib().b200lut_plan_build(self.buffer.data_ptr(), nbytes, arr, len(jobs), self.M, did,
+                                           torch.cuda.current_stream(self.device).cuda_stream))
+        self.njobs = len(jobs)
+
+    def run(self) -> None:
+        with torch.cuda.device(self.device):
+            check(lib().b200lut_plan_run(self.buffer.data_ptr(), self.M, dtype_id(self.dtype),
+                                         torch.cuda.current_stream(self.device).cuda_stream))
+
+    def check_status(self) -> None:
+        with torch.cuda.device(self.device):
+            check(lib().b200lut_plan_status(self.buffer.data_ptr()))

@@ -30,6 +30,7 @@
 #include <cooperative_groups.h>
 
 #include <cstdlib>
+#include <vector>
 
 #include "common.cuh"
 #include "pairtable.cuh"
@@ -111,6 +112,39 @@ __device__ __forceinline__ void load_chunk(uint32_t (&w)[8 * BITS], const uint8_
   for (int p = 0; p < BITS; ++p) ldg_stream256(&w[8 * p], chunk_lane + p * 1024);
 }
 
+// What a pass must wait for before it may read the activation rows: nothing, the previous
+// kernel in the stream (programmatic dependent launch), or a completion counter of the
+// producing job inside a persistent launch.
+struct DepWait {
+  int mode;                 // 0 none, 1 griddepcontrol.wait, 2 counter
+  const int* counter;       // mode 2: tiles of the producer finished so far
+  int target;               // mode 2: proceed when *counter >= target
+  int* abort_word;          // mode 2: global word set when any block gave up waiting
+};
+
+constexpr long long kDepWaitCycles = 40000000;   // ~20 ms: far beyond any healthy wait
+
+__device__ __forceinline__ int ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded wait on a producer's completion counter (one thread polls). Gives up after a
+// fixed number of cycles, or at once when another block already gave up, and records it.
+__device__ __forceinline__ void dep_poll(const DepWait& dep) {
+  if (ld_acquire(dep.counter) >= dep.target) return;
+  const long long t0 = clock64();
+  for (uint32_t i = 1;; ++i) {
+    if (ld_acquire(dep.counter) >= dep.target) return;
+    if ((i & 15u) == 0u) {
+      if (ld_acquire(dep.abort_word) != 0) return;
+      if (clock64() - t0 > kDepWaitCycles) break;
+    }
+  }
+  atomicExch(dep.abort_word, 1);
+}
+
 // Batch-column plan. The n8 columns of the m16n8k16 accumulator are shared between
 // batch rows and row slabs: with CP batch columns per slab (CP = 1, 2, 4, 8), one
 // accumulator fragment serves 8/CP slabs — slab j of the group accumulates into columns
@@ -136,7 +170,7 @@ __device__ __forceinline__ void load_x(uint2 (&xf)[Plan<CP>::kNB][4],
     for (int kt = 0; kt < 4; ++kt) {
       xf[nb][kt] = make_uint2(0u, 0u);
       if (m < M)
-        xf[nb][kt] = *reinterpret_cast<const uint2*>(x + size_t(m) * ldx + k0 + 16 * kt + 4 * tig);
+        xf[nb][kt] = __ldcg(reinterpret_cast<const uint2*>(x + size_t(m) * ldx + k0 + 16 * kt + 4 * tig));
     }
   }
 }
@@ -183,7 +217,7 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
                                             const uint16_t* __restrict__ lut, int n_groups, int gs,
                                             int tile, int G, int c0, int c1,
                                             const uint16_t* __restrict__ x, long long ldx, int M,
-                                            bool first_pass) {
+                                            bool sync_before, DepWait dep) {
   using P = Plan<CP>;
   constexpr int NT = NWARPS * 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -208,10 +242,11 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
   int nl = kTileRows / gs;
   if (nl < 1) nl = 1;
   const int slot_shift = nl == 1 ? 3 : (nl == 2 ? 2 : 1);
-  if (!first_pass) __syncthreads();   // the previous pass's fold buffer aliases the tables
+  if (sync_before) __syncthreads();   // the previous pass's fold buffer aliases the tables
   build_tables(tbl_ptr, lut, BITS, n_groups, tile * kTileRows, gs, nl, NT);
+  if (dep.mode == 2 && threadIdx.x == 0) dep_poll(dep);   // producer job's tiles, bounded
   __syncthreads();
-  if (first_pass) {
+  if (dep.mode == 1) {
     // everything above is independent of the previous kernel in the stream
     asm volatile("griddepcontrol.wait;" ::: "memory");
   }
@@ -406,7 +441,8 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
       float* dst = part + plane * kMaxM * kTileRows;
 #define B200LUT_PASS(B)                                                                       \
   stream_pass<T, B, CP, NWARPS, RC>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups,  \
-                                sg.gs, tile, p.G, c0, c1, p.x, p.ldx, M, first)
+                                    sg.gs, tile, p.G, c0, c1, p.x, p.ldx, M, !first,              \
+                                    DepWait{first ? 1 : 0, nullptr, 0, nullptr})
       switch (bits) {   // block-uniform
         case 4: B200LUT_PASS(4); break;
         case 3: B200LUT_PASS(3); break;
@@ -421,6 +457,14 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
 }
 
 constexpr int kWarpsM8 = 16, kWarpsM16 = 8;
+
+}  // namespace
+}  // namespace b200lut
+
+#include "gemv_plan.cuh"
+
+namespace b200lut {
+namespace {
 
 size_t smem_bytes_for(int max_tables) {
   return size_t(kPartBytes) + 65536 + size_t(max_tables) * kTableBytes;
@@ -460,6 +504,60 @@ int launch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t stream) {
   cfg.attrs = attr;
   cfg.numAttrs = unsigned(na);
   B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
+  return B200LUT_OK;
+}
+
+// Validate the caller's segments and convert them to the device form. Shared by the
+// per-launch entry and the plan builder.
+int convert_segments(const b200lut_segment* segs, int nseg, bool silu, SegDev* out, int* tiles,
+                     int* max_tables) {
+  for (int i = 0; i < nseg; ++i) {
+    const b200lut_segment& s = segs[i];
+    B200LUT_REQUIRE(s.packed && s.lut, B200LUT_ERR_INVALID, "segment %d: null codes or palette", i);
+    B200LUT_REQUIRE(s.N > 0 && s.N % kTileRows == 0, B200LUT_ERR_INVALID,
+                    "segment %d: N must be a positive multiple of 128, got %d", i, s.N);
+    B200LUT_REQUIRE(s.bits >= 1 && s.bits <= 4, B200LUT_ERR_INVALID,
+                    "segment %d: stream-1 width must be 1..4, got %d", i, s.bits);
+    const bool has2 = s.packed2 != nullptr;
+    B200LUT_REQUIRE(!has2 || (s.lut2 && s.bits2 >= 1 && s.bits2 <= 4), B200LUT_ERR_INVALID,
+                    "segment %d: stream-2 needs a palette and a width of 1..4 (got %d)", i,
+                    s.bits2);
+    B200LUT_REQUIRE(s.group_size >= 32 && s.n_groups >= 1 &&
+                        ((s.group_size < 128 && (s.group_size & (s.group_size - 1)) == 0) ||
+                         s.group_size % 128 == 0),
+                    B200LUT_ERR_UNSUPPORTED,
+                    "segment %d: group_size %d not served (32, 64 or a multiple of 128)", i,
+                    s.group_size);
+    B200LUT_REQUIRE(aligned16(s.packed) && (!has2 || aligned16(s.packed2)), B200LUT_ERR_ALIGN,
+                    "segment %d: code buffers must be 16-byte aligned", i);
+    const bool writes = !silu || (i % 2 == 0);
+    B200LUT_REQUIRE(!writes || (s.out && s.ldo >= s.N), B200LUT_ERR_INVALID,
+                    "segment %d: null output or row stride < N", i);
+    if (silu && (i % 2 == 1))
+      B200LUT_REQUIRE(s.N == segs[i - 1].N, B200LUT_ERR_INVALID,
+                      "gate and up segments must have the same N (%d vs %d)", segs[i - 1].N, s.N);
+    SegDev& d = out[i];
+    d.packed = static_cast<const uint8_t*>(s.packed);
+    d.lut = static_cast<const uint16_t*>(s.lut);
+    d.packed2 = static_cast<const uint8_t*>(s.packed2);
+    d.lut2 = static_cast<const uint16_t*>(s.lut2);
+    d.bias = static_cast<const uint16_t*>(s.bias);
+    d.out = static_cast<uint16_t*>(s.out);
+    d.ldo = s.ldo;
+    d.N = s.N;
+    d.gs = s.group_size;
+    d.n_groups = s.n_groups;
+    d.bits = s.bits;
+    d.bits2 = has2 ? s.bits2 : 0;
+    if (silu && (i % 2 == 1)) {
+      d.tile_begin = out[i - 1].tile_begin;
+    } else {
+      d.tile_begin = *tiles;
+      *tiles += s.N / kTileRows;
+    }
+    const int nl = s.group_size >= 128 ? 1 : 128 / s.group_size;
+    if ((nl + 1) / 2 > *max_tables) *max_tables = (nl + 1) / 2;
+  }
   return B200LUT_OK;
 }
 
@@ -557,53 +655,7 @@ extern "C" int b200lut_gemv_multi(const void* x, int64_t ldx, int M, int K, int 
   p.nseg = nseg;
   p.epilogue = epilogue;
   int tiles = 0, max_tables = 1;
-  for (int i = 0; i < nseg; ++i) {
-    const b200lut_segment& s = segs[i];
-    B200LUT_REQUIRE(s.packed && s.lut, B200LUT_ERR_INVALID, "segment %d: null codes or palette", i);
-    B200LUT_REQUIRE(s.N > 0 && s.N % kTileRows == 0, B200LUT_ERR_INVALID,
-                    "segment %d: N must be a positive multiple of 128, got %d", i, s.N);
-    B200LUT_REQUIRE(s.bits >= 1 && s.bits <= 4, B200LUT_ERR_INVALID,
-                    "segment %d: stream-1 width must be 1..4, got %d", i, s.bits);
-    const bool has2 = s.packed2 != nullptr;
-    B200LUT_REQUIRE(!has2 || (s.lut2 && s.bits2 >= 1 && s.bits2 <= 4), B200LUT_ERR_INVALID,
-                    "segment %d: stream-2 needs a palette and a width of 1..4 (got %d)", i,
-                    s.bits2);
-    B200LUT_REQUIRE(s.group_size >= 32 && s.n_groups >= 1 &&
-                        ((s.group_size < 128 && (s.group_size & (s.group_size - 1)) == 0) ||
-                         s.group_size % 128 == 0),
-                    B200LUT_ERR_UNSUPPORTED,
-                    "segment %d: group_size %d not served (32, 64 or a multiple of 128)", i,
-                    s.group_size);
-    B200LUT_REQUIRE(aligned16(s.packed) && (!has2 || aligned16(s.packed2)), B200LUT_ERR_ALIGN,
-                    "segment %d: code buffers must be 16-byte aligned", i);
-    const bool writes = !silu || (i % 2 == 0);
-    B200LUT_REQUIRE(!writes || (s.out && s.ldo >= s.N), B200LUT_ERR_INVALID,
-                    "segment %d: null output or row stride < N", i);
-    if (silu && (i % 2 == 1))
-      B200LUT_REQUIRE(s.N == segs[i - 1].N, B200LUT_ERR_INVALID,
-                      "gate and up segments must have the same N (%d vs %d)", segs[i - 1].N, s.N);
-    SegDev& d = p.seg[i];
-    d.packed = static_cast<const uint8_t*>(s.packed);
-    d.lut = static_cast<const uint16_t*>(s.lut);
-    d.packed2 = static_cast<const uint8_t*>(s.packed2);
-    d.lut2 = static_cast<const uint16_t*>(s.lut2);
-    d.bias = static_cast<const uint16_t*>(s.bias);
-    d.out = static_cast<uint16_t*>(s.out);
-    d.ldo = s.ldo;
-    d.N = s.N;
-    d.gs = s.group_size;
-    d.n_groups = s.n_groups;
-    d.bits = s.bits;
-    d.bits2 = has2 ? s.bits2 : 0;
-    if (silu && (i % 2 == 1)) {
-      d.tile_begin = p.seg[i - 1].tile_begin;
-    } else {
-      d.tile_begin = tiles;
-      tiles += s.N / kTileRows;
-    }
-    const int nl = s.group_size >= 128 ? 1 : 128 / s.group_size;
-    if ((nl + 1) / 2 > max_tables) max_tables = (nl + 1) / 2;
-  }
+  if (int rc = convert_segments(segs, nseg, silu, p.seg, &tiles, &max_tables)) return rc;
   p.tiles_total = tiles;
   const int warps = M <= 8 ? kWarpsM8 : kWarpsM16;
   if (split <= 0) split = pick_split(tiles, p.G, sm_count_cached(), warps);
@@ -641,4 +693,150 @@ extern "C" int b200lut_gemv(const void* x, const void* packed, const void* lut, 
   s.bits = bits;
   return b200lut_gemv_multi(x, K, M, K, dtype, &s, 1, B200LUT_EPI_NONE, split, workspace,
                             workspace_bytes, 0, stream);
+}
+
+// ------------------------------------------------------------------------------------------
+// Persistent decode plan
+// ------------------------------------------------------------------------------------------
+namespace {
+
+struct PlanLayout {
+  PlanHeader hdr;
+  std::vector<JobDev> jobs;
+};
+
+int plan_layout(const b200lut_job* jobs, int njobs, int M, int dtype, int grid, PlanLayout* out) {
+  B200LUT_REQUIRE(jobs && njobs >= 1 && njobs <= 4096, B200LUT_ERR_INVALID,
+                  "a plan holds 1..4096 jobs, got %d", njobs);
+  B200LUT_REQUIRE(M >= 1 && M <= kMaxM, B200LUT_ERR_UNSUPPORTED,
+                  "a decode plan serves 1 <= M <= 16, got M=%d", M);
+  B200LUT_REQUIRE(dtype == B200LUT_BF16 || dtype == B200LUT_F16, B200LUT_ERR_INVALID,
+                  "dtype must be B200LUT_BF16 or B200LUT_F16");
+  out->jobs.assign(size_t(njobs), JobDev{});
+  long long ws_floats = 0;
+  int ntickets = 0;
+  for (int j = 0; j < njobs; ++j) {
+    const b200lut_job& src = jobs[j];
+    JobDev& d = out->jobs[size_t(j)];
+    B200LUT_REQUIRE(src.x && src.K > 0 && src.K % kChunkK == 0, B200LUT_ERR_INVALID,
+                    "job %d: null x or K not a positive multiple of 64", j);
+    B200LUT_REQUIRE(aligned16(src.x) && src.ldx % 8 == 0 && src.ldx >= src.K, B200LUT_ERR_ALIGN,
+                    "job %d: x must be 16-byte aligned, row stride a multiple of 8 and >= K", j);
+    B200LUT_REQUIRE(src.nseg >= 1 && src.nseg <= kMaxSeg, B200LUT_ERR_INVALID,
+                    "job %d: 1..%d segments, got %d", j, kMaxSeg, src.nseg);
+    B200LUT_REQUIRE(src.epilogue == B200LUT_EPI_NONE || src.epilogue == B200LUT_EPI_SILU_MUL,
+                    B200LUT_ERR_INVALID, "job %d: unknown epilogue %d", j, src.epilogue);
+    B200LUT_REQUIRE(src.dep >= -1 && src.dep < j, B200LUT_ERR_INVALID,
+                    "job %d: dep must name an earlier job or be -1 (got %d)", j, src.dep);
+    const bool silu = src.epilogue == B200LUT_EPI_SILU_MUL;
+    B200LUT_REQUIRE(!silu || src.nseg % 2 == 0, B200LUT_ERR_INVALID,
+                    "job %d: the silu-mul epilogue needs (gate, up) segment pairs", j);
+    int tiles = 0, max_tables = 1;
+    if (int rc = convert_segments(src.segs, src.nseg, silu, d.seg, &tiles, &max_tables)) return rc;
+    B200LUT_REQUIRE(max_tables <= 2, B200LUT_ERR_UNSUPPORTED, "job %d: palette grid too fine", j);
+    d.x = static_cast<const uint16_t*>(src.x);
+    d.ldx = src.ldx;
+    d.K = src.K;
+    d.G = src.K / kChunkK;
+    d.nseg = src.nseg;
+    d.epilogue = src.epilogue;
+    d.tiles_total = tiles;
+    d.planes = silu ? 2 : 1;
+    d.dep = src.dep;
+    d.dep_target = src.dep >= 0 ? out->jobs[size_t(src.dep)].tiles_total : 0;
+    const long long total = (long long)tiles * d.G;
+    d.per = int((total + grid - 1) / grid);
+    d.maxc = (d.G + d.per - 1) / d.per + 1;
+    d.ws_off = ws_floats;
+    d.ticket_off = ntickets;
+    ws_floats += (long long)tiles * d.maxc * d.planes * M * kTileRows;
+    ntickets += tiles;
+  }
+  PlanHeader& h = out->hdr;
+  h.magic = kPlanMagic;
+  h.njobs = njobs; h.M = M; h.dtype = dtype; h.grid = grid;
+  long long off = (sizeof(PlanHeader) + 255) & ~255ll;
+  h.jobs_off = off;      off += ((long long)njobs * sizeof(JobDev) + 255) & ~255ll;
+  h.done_off = off;      off += ((long long)njobs * 4 + 255) & ~255ll;
+  h.tickets_off = off;   off += ((long long)ntickets * 4 + 255) & ~255ll;
+  h.misc_off = off;      off += 256;
+  h.ws_off = off;        off += (ws_floats * 4 + 255) & ~255ll;
+  h.total_bytes = off;
+  h.ntickets = ntickets;
+  return B200LUT_OK;
+}
+
+template <typename T, int CP, int NWARPS, int RC>
+int launch_plan(void* plan, int grid, cudaStream_t stream) {
+  auto kern = gemv_plan_kernel<T, CP, NWARPS, RC>;
+  const size_t smem = smem_bytes_for(2);
+  static bool configured[64] = {false};
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         int(smem)));
+    configured[dev] = true;
+  }
+  uint8_t* arg = static_cast<uint8_t*>(plan);
+  void* args[] = {&arg};
+  B200LUT_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kern), dim3(unsigned(grid)),
+                                              dim3(NWARPS * 32), args, smem, stream));
+  return B200LUT_OK;
+}
+
+template <typename T>
+int dispatch_plan(void* plan, int M, int grid, cudaStream_t st) {
+  if (M == 1) return launch_plan<T, 1, kWarpsM8, 2>(plan, grid, st);
+  if (M == 2) return launch_plan<T, 2, kWarpsM8, 2>(plan, grid, st);
+  if (M <= 4) return launch_plan<T, 4, kWarpsM8, 2>(plan, grid, st);
+  if (M <= 8) return launch_plan<T, 8, kWarpsM8, 1>(plan, grid, st);
+  return launch_plan<T, 16, kWarpsM16, 1>(plan, grid, st);
+}
+
+}  // namespace
+
+extern "C" size_t b200lut_plan_bytes(const b200lut_job* jobs, int njobs, int M, int dtype) {
+  PlanLayout lay;
+  if (plan_layout(jobs, njobs, M, dtype, sm_count_cached(), &lay) != B200LUT_OK) return 0;
+  return size_t(lay.hdr.total_bytes);
+}
+
+extern "C" int b200lut_plan_build(void* plan, size_t plan_bytes, const b200lut_job* jobs, int njobs,
+                                  int M, int dtype, void* stream) {
+  B200LUT_REQUIRE(plan && aligned16(plan), B200LUT_ERR_ALIGN, "plan buffer must be 16-byte aligned");
+  PlanLayout lay;
+  if (int rc = plan_layout(jobs, njobs, M, dtype, sm_count_cached(), &lay)) return rc;
+  B200LUT_REQUIRE(plan_bytes >= size_t(lay.hdr.total_bytes), B200LUT_ERR_WORKSPACE,
+                  "plan needs %lld bytes, got %zu", lay.hdr.total_bytes, plan_bytes);
+  cudaStream_t st = cudaStream_t(stream);
+  uint8_t* base = static_cast<uint8_t*>(plan);
+  // counters, tickets and the abort word start at zero; partials need no initial value
+  B200LUT_CUDA_OK(cudaMemsetAsync(base, 0, size_t(lay.hdr.ws_off), st));
+  B200LUT_CUDA_OK(cudaMemcpyAsync(base, &lay.hdr, sizeof(PlanHeader), cudaMemcpyHostToDevice, st));
+  B200LUT_CUDA_OK(cudaMemcpyAsync(base + lay.hdr.jobs_off, lay.jobs.data(),
+                                  lay.jobs.size() * sizeof(JobDev), cudaMemcpyHostToDevice, st));
+  B200LUT_CUDA_OK(cudaStreamSynchronize(st));   // the host staging dies with this call
+  return B200LUT_OK;
+}
+
+extern "C" int b200lut_plan_run(void* plan, int M, int dtype, void* stream) {
+  B200LUT_REQUIRE(plan, B200LUT_ERR_INVALID, "null plan");
+  B200LUT_REQUIRE(M >= 1 && M <= kMaxM && (dtype == B200LUT_BF16 || dtype == B200LUT_F16),
+                  B200LUT_ERR_INVALID, "M and dtype must be those the plan was built with");
+  const int grid = sm_count_cached();
+  if (dtype == B200LUT_BF16) return dispatch_plan<__nv_bfloat16>(plan, M, grid, cudaStream_t(stream));
+  return dispatch_plan<__half>(plan, M, grid, cudaStream_t(stream));
+}
+
+extern "C" int b200lut_plan_status(const void* plan) {
+  B200LUT_REQUIRE(plan, B200LUT_ERR_INVALID, "null plan");
+  PlanHeader h;
+  B200LUT_CUDA_OK(cudaMemcpy(&h, plan, sizeof(h), cudaMemcpyDeviceToHost));
+  B200LUT_REQUIRE(h.magic == kPlanMagic, B200LUT_ERR_INVALID, "not a plan buffer");
+  int misc[2] = {0, 0};
+  B200LUT_CUDA_OK(cudaMemcpy(misc, static_cast<const uint8_t*>(plan) + h.misc_off, sizeof(misc),
+                             cudaMemcpyDeviceToHost));
+  if (misc[1] != 0) return fail(B200LUT_ERR_DEVICE, "a dependency wait inside the plan ran out");
+  return B200LUT_OK;
 }

@@ -154,21 +154,21 @@ class LinearStack(nn.Module):
             for m in heads:
                 descs.append(m._segment_desc(hbuf[:, off:], ldo=total))
                 off += m.N
-            launches.append(("heads", x, _lib.make_segments(descs), len(descs), _lib.EPI_NONE))
+            launches.append(("heads", x, _lib.make_segments(descs), len(descs), _lib.EPI_NONE, descs))
             o = L.out()
             obuf = torch.empty(M, o.N, dtype=dt, device=dev)
-            launches.append(("out", x, _lib.make_segments([o._segment_desc(obuf)]), 1, _lib.EPI_NONE))
+            od = [o._segment_desc(obuf)]
+            launches.append(("out", x, _lib.make_segments(od), 1, _lib.EPI_NONE, od))
             g, u, d = L.mlp.gate_proj, L.mlp.up_proj, L.mlp.down_proj
             act = torch.empty(M, g.N * self.world, dtype=dt, device=dev)   # full width after gather
             act_loc = act[:, self.rank * g.N:(self.rank + 1) * g.N]
-            launches.append(("gate_up", x, _lib.make_segments(
-                [g._segment_desc(act_loc, ldo=act.shape[1]), u._segment_desc(None)]), 2,
-                _lib.EPI_SILU_MUL))
+            gd = [g._segment_desc(act_loc, ldo=act.shape[1]), u._segment_desc(None)]
+            launches.append(("gate_up", x, _lib.make_segments(gd), 2, _lib.EPI_SILU_MUL, gd))
             if self.world > 1:
-                launches.append(("gather", act, act_loc, None, None))
+                launches.append(("gather", act, act_loc, None, None, None))
             ybuf = torch.empty(M, d.N, dtype=dt, device=dev)
-            launches.append(("down", act, _lib.make_segments([d._segment_desc(ybuf)]), 1,
-                             _lib.EPI_NONE))
+            dd = [d._segment_desc(ybuf)]
+            launches.append(("down", act, _lib.make_segments(dd), 1, _lib.EPI_NONE, dd))
             outs += [hbuf, obuf, act, ybuf]
         plan = {"x": x, "launches": launches, "buffers": outs, "y": outs[-1]}
         self._plans[M] = plan
@@ -178,7 +178,7 @@ class LinearStack(nn.Module):
         """Run every projection once on the plan's activation buffer; returns the
         last layer's down_proj output (this rank's columns)."""
         plan = self._plan(M)
-        for name, xin, segs, nseg, epi in plan["launches"]:
+        for name, xin, segs, nseg, epi, _ in plan["launches"]:
             if name == "gather":
                 gather(xin, segs)
                 continue
@@ -189,9 +189,36 @@ class LinearStack(nn.Module):
                     _lib.gemm(xin, _pair(segs, i, epi), epilogue=epi, flags=flags)
         return plan["y"]
 
+    def decode_plans(self, M: int):
+        """Persistent-launch form of the step (M <= 16): the launches between two
+        all-gathers become one plan each (a single plan on one GPU). Inside a plan every
+        job depends on the one before it — the order a real decoder layer imposes."""
+        plan = self._plan(M)
+        if "plans" not in plan:
+            groups, cur = [], []
+            for name, xin, segs, nseg, epi, descs in plan["launches"]:
+                if name == "gather":
+                    groups.append(("plan", cur))
+                    groups.append(("gather", (xin, segs)))
+                    cur = []
+                else:
+                    cur.append(dict(x=xin, segs=descs, epilogue=epi, dep=len(cur) - 1))
+            groups.append(("plan", cur))
+            plan["plans"] = [(k, _lib.DecodePlan(v, M, self.dtype, self.device) if k == "plan" else v)
+                             for k, v in groups if k == "gather" or v]
+        return plan["plans"]
+
+    def step_persistent(self, M: int, gather=None) -> torch.Tensor:
+        for kind, item in self.decode_plans(M):
+            if kind == "plan":
+                item.run()
+            else:
+                gather(*item)
+        return self._plan(M)["y"]
+
     def launches_per_step(self, M: int) -> int:
         n = 0
-        for name, _, _, nseg, epi in self._plan(M)["launches"]:
+        for name, _, _, nseg, epi, _ in self._plan(M)["launches"]:
             if name == "gather":
                 continue
             n += 1 if M <= 16 else (nseg // 2 if epi == _lib.EPI_SILU_MUL else nseg)

@@ -147,3 +147,44 @@ def test_mlp_block_shapes_of_the_9b_model():
         want = orc.mlp_block_fused(x, gate.w1, up.w1, down.w1)
         assert rel_err(y, want) <= 2 * TOL
         assert orc.cosine(y.cpu().float(), want.float()) >= 0.999
+
+
+def test_persistent_plan_matches_per_launch_results():
+    # a chain of jobs (merged heads, plain, fused gate/up, down on the fused output) in one
+    # cooperative launch gives the same bits as the separate launches, run after run
+    dt = torch.bfloat16
+    for M in (1, 4, 16):
+        q, k, o = (Case(n, 1024, 128, 4, dt, seed=s) for n, s in ((512, 1), (128, 2), (1024, 3)))
+        gate, up = Case(2048, 1024, 128, 4, dt, seed=4, lut_std=0.05), Case(2048, 1024, 128, 4, dt, seed=5)
+        down = Case(1024, 2048, 64, 3, dt, seed=6)
+        mods = {n: c.module() for n, c in dict(q=q, k=k, o=o, gate=gate, up=up, down=down).items()}
+        for m in mods.values():
+            m._ensure_packed()
+        x = q.x(M).cuda()
+        heads = torch.empty(M, 640, dtype=dt, device="cuda")
+        obuf = torch.empty(M, 1024, dtype=dt, device="cuda")
+        act = torch.empty(M, 2048, dtype=dt, device="cuda")
+        y = torch.empty(M, 1024, dtype=dt, device="cuda")
+        jobs = [
+            dict(x=x, segs=[mods["q"]._segment_desc(heads, ldo=640), mods["k"]._segment_desc(heads[:, 512:], ldo=640)], dep=-1),
+            dict(x=x, segs=[mods["o"]._segment_desc(obuf)], dep=0),
+            dict(x=x, segs=[mods["gate"]._segment_desc(act), mods["up"]._segment_desc(None)],
+                 epilogue=L.EPI_SILU_MUL, dep=1),
+            dict(x=act, segs=[mods["down"]._segment_desc(y)], dep=2),
+        ]
+        want = []
+        for j in jobs:
+            L.gemv_multi(j["x"], L.make_segments(j["segs"]), len(j["segs"]), epilogue=j.get("epilogue", 0))
+        torch.cuda.synchronize()
+        want = [t.clone() for t in (heads, obuf, act, y)]
+        plan = L.DecodePlan(jobs, M, dt, "cuda")
+        for rep in range(3):
+            for t in (heads, obuf, act, y):
+                t.fill_(float("nan"))
+            plan.run()
+            torch.cuda.synchronize()
+            plan.check_status()
+            for got, w in zip((heads, obuf, act, y), want):
+                assert rel_err(got, w) <= 2e-3         # same math, different K split points
+        assert rel_err(obuf, o.oracle(x.cpu())) <= TOL
+        assert rel_err(y, down.oracle(act.cpu())) <= TOL
