@@ -291,6 +291,9 @@ def main() -> int:
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (1/0)")
+    ap.add_argument("--executor", default="plan", choices=("plan", "graph"),
+                    help="plan: persistent cooperative launch(es) per step; graph: one kernel per "
+                         "projection group under CUDA-graph replay")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -314,14 +317,21 @@ def main() -> int:
     plan["x"].copy_(x_host)
 
     # eager run, then capture the step in a CUDA graph
-    stack.step(M, flags=flags, gather=gather)
+    use_plan = args.executor == "plan" and M <= 16
+
+    def run_step():
+        if use_plan:
+            stack.step_persistent(M, gather=gather)
+        else:
+            stack.step(M, flags=flags, gather=gather)
+    run_step()
     torch.cuda.synchronize()
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
-        stack.step(M, flags=flags, gather=gather)
+        run_step()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
-            stack.step(M, flags=flags, gather=gather)
+            run_step()
     torch.cuda.synchronize()
 
     def step_resident():
@@ -351,6 +361,7 @@ def main() -> int:
     ms_step = ms / args.steps
     tok_s = M * 1e3 / ms_step
     launches = stack.launches_per_step(M)
+    kernel_launches = sum(1 for k, _ in stack.decode_plans(M) if k == "plan") if use_plan else launches
     bytes_rank = stack.algorithmic_bytes(M)
     achieved = bytes_rank / (ms_step * 1e-3) / 1e9
     line = {
@@ -361,16 +372,20 @@ def main() -> int:
                                "6912212992 4-bit weights, group 128, bf16 palettes",
                    "batch": M, "parallelism": f"column-parallel x{world}, all-gather per layer",
                    "l2": "inputs (3.46 GB of codes per step) exceed the 126 MB L2",
-                   "launch": "CUDA graph replay" + (", programmatic dependent launch" if args.pdl else "")},
+                   "launch": ("persistent cooperative launch per step (jobs chained by completion counters), "
+                              "CUDA graph replay" if use_plan else
+                              "one kernel per projection group, CUDA graph replay"
+                              + (", programmatic dependent launch" if args.pdl else ""))},
         "e2e": {"value": M * 1e3 / (ms_e2e / args.steps), "unit": "tok/s",
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
-        "gpu_launches": launches * args.steps,
+        "gpu_launches": kernel_launches * args.steps,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "gemv_kernel", "achieved": achieved,
+        "roofline": {"bound": "hbm", "kernel": "gemv_plan_kernel" if use_plan else "gemv_kernel", "achieved": achieved,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                      "peak_source": peaks["source"], "traffic": None,
-                     "bytes_per_launch": bytes_rank / launches,
-                     "us_per_launch": ms_step * 1e3 / launches},
+                     "bytes_per_launch": bytes_rank / kernel_launches,
+                     "us_per_launch": ms_step * 1e3 / kernel_launches,
+                     "projection_groups_per_step": launches},
     }
     if rank == 0 and world == 1 and not args.no_extras:
         extras = {}
