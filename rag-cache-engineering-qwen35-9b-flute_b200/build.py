@@ -36,10 +36,11 @@ def _stale(target: str, deps) -> bool:
 
 def _compile(src: str, force: bool) -> str:
     obj = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
-    deps = [os.path.join(CSRC, src), os.path.join(CSRC, "common.cuh"),
-            os.path.join(HERE, "..", "include", "b200_lut.h")]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh") or f == src]
+    deps.append(os.path.join(HERE, "..", "include", "b200_lut.h"))
     if force or _stale(obj, deps):
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        extra = os.environ.get("B200LUT_NVCC_EXTRA", "").split()
+        cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         with open(obj + ".log", "w") as f:
             f.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)

@@ -564,11 +564,17 @@ int convert_segments(const b200lut_segment* segs, int nseg, bool silu, SegDev* o
 template <typename T>
 int dispatch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t st) {
   static const int plan = [] { const char* e = getenv("B200LUT_GEMV_PLAN"); return e ? atoi(e) : 0; }();
+  if (p.M == 1 && plan == 122) return launch<T, 1, 12, 2>(p, max_tables, pdl, st);
+  if (p.M == 1 && plan == 121) return launch<T, 1, 12, 1>(p, max_tables, pdl, st);
+  if (p.M == 1 && plan == 83) return launch<T, 1, 8, 3>(p, max_tables, pdl, st);
+  if (p.M == 1 && plan == 84) return launch<T, 1, 8, 2>(p, max_tables, pdl, st);
+  if (p.M == 1 && plan == 11) return launch<T, 1, kWarpsM8, 1>(p, max_tables, pdl, st);
+  if (p.M == 1 && plan == 21) return launch<T, 2, kWarpsM8, 1>(p, max_tables, pdl, st);
   if (p.M == 1 && plan == 81) return launch<T, 8, kWarpsM8, 1>(p, max_tables, pdl, st);
   if (p.M == 1 && plan == 82) return launch<T, 8, kWarpsM8, 2>(p, max_tables, pdl, st);
   if (p.M == 1 && plan == 42) return launch<T, 4, kWarpsM8, 2>(p, max_tables, pdl, st);
   if (p.M == 1 && plan == 22) return launch<T, 2, kWarpsM8, 2>(p, max_tables, pdl, st);
-  if (p.M == 1) return launch<T, 1, kWarpsM8, 2>(p, max_tables, pdl, st);
+  if (p.M == 1) return launch<T, 1, kWarpsM8, 1>(p, max_tables, pdl, st);
   if (p.M == 2) return launch<T, 2, kWarpsM8, 2>(p, max_tables, pdl, st);
   if (p.M <= 4) return launch<T, 4, kWarpsM8, 2>(p, max_tables, pdl, st);
   if (p.M <= 8) return launch<T, 8, kWarpsM8, 1>(p, max_tables, pdl, st);
@@ -787,7 +793,7 @@ int launch_plan(void* plan, int grid, cudaStream_t stream) {
 
 template <typename T>
 int dispatch_plan(void* plan, int M, int grid, cudaStream_t st) {
-  if (M == 1) return launch_plan<T, 1, kWarpsM8, 2>(plan, grid, st);
+  if (M == 1) return launch_plan<T, 1, kWarpsM8, 1>(plan, grid, st);
   if (M == 2) return launch_plan<T, 2, kWarpsM8, 2>(plan, grid, st);
   if (M <= 4) return launch_plan<T, 4, kWarpsM8, 2>(plan, grid, st);
   if (M <= 8) return launch_plan<T, 8, kWarpsM8, 1>(plan, grid, st);

@@ -74,8 +74,17 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
   const uint32_t tbl_addr = (part_addr + kPartBytes + 0xFFFFu) & ~0xFFFFu;
   uint8_t* tbl_ptr = smem + (tbl_addr - part_addr);
   const int b = blockIdx.x, M = hdr.M;
+#ifdef B200LUT_PLAN_TIMING
+  long long tm_copy = 0, tm_pass = 0, tm_fold = 0, tm_total0 = clock64(), tm_mark;
+#define TM_MARK() tm_mark = clock64()
+#define TM_ADD(v) v += clock64() - tm_mark
+#else
+#define TM_MARK()
+#define TM_ADD(v)
+#endif
 
   for (int j = 0; j < hdr.njobs; ++j) {
+    TM_MARK();
     __syncthreads();
     {
       const uint32_t* src = reinterpret_cast<const uint32_t*>(jobs + j);
@@ -83,6 +92,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
       for (int i = threadIdx.x; i < int(sizeof(JobDev) / 4); i += NT) dst[i] = __ldcg(src + i);
     }
     __syncthreads();
+    TM_ADD(tm_copy);
     const int G = job.G, total = job.tiles_total * G;
     const int lin0 = b * job.per;
     int lin1 = lin0 + job.per;
@@ -98,6 +108,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
         if (tile_g >= job.seg[s].tile_begin) si = s;
       const int tile = tile_g - job.seg[si].tile_begin;
 
+      TM_MARK();
       for (int plane = 0; plane < job.planes; ++plane) {
         const SegDev& sg = job.seg[si + plane];
         const int npass = sg.packed2 ? 2 : 1;
@@ -122,6 +133,8 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
         }
       }
 
+      TM_ADD(tm_pass);
+      TM_MARK();
       // ---- fold the shares of this tile and store ------------------------------------------
       const SegDev& s0 = job.seg[si];
       const SegDev* s1 = silu ? &job.seg[si + 1] : nullptr;
@@ -174,9 +187,16 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
           atomicAdd(done + j, 1);
         }
       }
+      TM_ADD(tm_fold);
       lin += c1 - c0;
     }
   }
+#ifdef B200LUT_PLAN_TIMING
+  if (threadIdx.x == 0 && b < 4) {
+    long long* t = reinterpret_cast<long long*>(misc + 16) + b * 4;
+    t[0] = tm_copy; t[1] = tm_pass; t[2] = tm_fold; t[3] = clock64() - tm_total0;
+  }
+#endif
 
   // the last block out resets the completion counters for the next launch
   __syncthreads();
