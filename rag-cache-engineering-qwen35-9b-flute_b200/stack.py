@@ -51,6 +51,28 @@ def census() -> dict:
     return {"modules": modules, "weights": weights}
 
 
+def shard_rows(N: int, group_size: int, rank: int, world: int):
+    """Output rows [lo, hi) of rank `rank`: whole 128-row tiles and whole palette groups."""
+    n_loc = N // world
+    if N % (world * 128) or (n_loc % group_size and group_size % n_loc):
+        raise ValueError(f"N={N} does not shard over {world} ranks in whole tiles and groups")
+    return rank * n_loc, (rank + 1) * n_loc
+
+
+def shard_blob(blob, N: int, K: int, bits: int, rank: int, world: int):
+    """Column-parallel shard of an idxN blob: the blob is tile-major over 128-row tiles,
+    so the rows of a rank are one contiguous byte range."""
+    lo, hi = shard_rows(N, 128, rank, world)
+    row_bytes = K * bits // 8
+    return blob[lo * row_bytes:hi * row_bytes]
+
+
+def shard_lut(lut, N: int, group_size: int, rank: int, world: int):
+    """Palette rows that serve the rank's output rows."""
+    lo, hi = shard_rows(N, group_size, rank, world)
+    return lut[lo // group_size:max(hi // group_size, lo // group_size + 1)]
+
+
 class _Layer(nn.Module):
     def __init__(self, kind: str, mods: dict):
         super().__init__()
@@ -102,16 +124,12 @@ class LinearStack(nn.Module):
     def _make_module(self, N: int, K: int, seed: int) -> PalettizedLinear:
         """Full-size codes and palette are drawn from the seed (distinct bytes per
         module); a shard keeps rows [rank*N/world, (rank+1)*N/world)."""
-        if N % (self.world * 128) or (N // self.world) % self.group_size:
-            raise ValueError(f"N={N} does not shard over {self.world} ranks in whole tiles and groups")
         n_loc = N // self.world
         blob = synthetic.random_blob_on_device(N, K, self.bits, seed, self.device)
-        shard_bytes = n_loc * K * self.bits // 8            # a row-tile range is contiguous
-        blob = blob[self.rank * shard_bytes:(self.rank + 1) * shard_bytes]
+        blob = shard_blob(blob, N, K, self.bits, self.rank, self.world)
         packed = _lib.repack_from_idxn(blob, n_loc, K, self.bits)
         lut = synthetic.make_lut(N // self.group_size, self.bits, self.dtype, seed)
-        g_loc = n_loc // self.group_size
-        lut = lut[self.rank * g_loc:(self.rank + 1) * g_loc].contiguous().to(self.device)
+        lut = shard_lut(lut, N, self.group_size, self.rank, self.world).contiguous().to(self.device)
         return PalettizedLinear.from_packed(packed, lut, self.bits, self.group_size, n_loc, K)
 
     # ------------------------------------------------------------------ census
