@@ -739,7 +739,8 @@ int plan_layout(const b200lut_job* jobs, int njobs, int M, int dtype, int grid, 
                     "job %d: the silu-mul epilogue needs (gate, up) segment pairs", j);
     int tiles = 0, max_tables = 1;
     if (int rc = convert_segments(src.segs, src.nseg, silu, d.seg, &tiles, &max_tables)) return rc;
-    B200LUT_REQUIRE(max_tables <= 2, B200LUT_ERR_UNSUPPORTED, "job %d: palette grid too fine", j);
+    B200LUT_REQUIRE(max_tables <= 1, B200LUT_ERR_UNSUPPORTED,
+                    "job %d: a plan serves group sizes >= 64 (two palettes per tile at most)", j);
     d.x = static_cast<const uint16_t*>(src.x);
     d.ldx = src.ldx;
     d.K = src.K;
@@ -765,16 +766,16 @@ int plan_layout(const b200lut_job* jobs, int njobs, int M, int dtype, int grid, 
   h.jobs_off = off;      off += ((long long)njobs * sizeof(JobDev) + 255) & ~255ll;
   h.done_off = off;      off += ((long long)njobs * 4 + 255) & ~255ll;
   h.tickets_off = off;   off += ((long long)ntickets * 4 + 255) & ~255ll;
-  h.misc_off = off;      off += 256;
+  h.misc_off = off;      off += 65536;   // exit count, abort word; profiling builds log here
   h.ws_off = off;        off += (ws_floats * 4 + 255) & ~255ll;
   h.total_bytes = off;
   h.ntickets = ntickets;
   return B200LUT_OK;
 }
 
-template <typename T, int CP, int NWARPS, int RC>
+template <typename T, int CP, int NWARPS>
 int launch_plan(void* plan, int grid, cudaStream_t stream) {
-  auto kern = gemv_plan_kernel<T, CP, NWARPS, RC>;
+  auto kern = gemv_plan_kernel<T, CP, NWARPS>;
   const size_t smem = smem_bytes_for(2);
   static bool configured[64] = {false};
   int dev = 0;
@@ -793,11 +794,11 @@ int launch_plan(void* plan, int grid, cudaStream_t stream) {
 
 template <typename T>
 int dispatch_plan(void* plan, int M, int grid, cudaStream_t st) {
-  if (M == 1) return launch_plan<T, 1, kWarpsM8, 1>(plan, grid, st);
-  if (M == 2) return launch_plan<T, 2, kWarpsM8, 2>(plan, grid, st);
-  if (M <= 4) return launch_plan<T, 4, kWarpsM8, 2>(plan, grid, st);
-  if (M <= 8) return launch_plan<T, 8, kWarpsM8, 1>(plan, grid, st);
-  return launch_plan<T, 16, kWarpsM16, 1>(plan, grid, st);
+  if (M == 1) return launch_plan<T, 1, kWarpsM8>(plan, grid, st);
+  if (M == 2) return launch_plan<T, 2, kWarpsM8>(plan, grid, st);
+  if (M <= 4) return launch_plan<T, 4, kWarpsM8>(plan, grid, st);
+  if (M <= 8) return launch_plan<T, 8, kWarpsM8>(plan, grid, st);
+  return launch_plan<T, 16, kWarpsM16>(plan, grid, st);
 }
 
 }  // namespace

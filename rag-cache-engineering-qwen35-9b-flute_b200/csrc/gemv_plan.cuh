@@ -8,7 +8,10 @@
 // takes an equal, contiguous share of the job's (tile, k-chunk) space (so all SMs stream
 // the same number of bytes whatever the tile count), requests its first codes, builds its
 // pair table, and only then waits — on a completion counter — for the job that produces
-// its activation rows. Code bytes are therefore in flight across the dependency.
+// its activation rows. Code bytes are therefore in flight across the dependency. The walk
+// is a flat sequence of passes (one code stream of one tile share) pipelined one ahead:
+// while a pass folds, the first codes of the next pass — of the next tile or the next job —
+// are already requested and its pair table is already built in the other table region.
 //
 // Shares of one tile held by different blocks are folded through an fp32 workspace: each
 // contributor writes its partial tile, takes a ticket, and the last arrival sums the
@@ -55,11 +58,146 @@ __device__ __forceinline__ void plan_store(const SegDev& s0, const SegDev* s1, i
   s0.out[size_t(m) * s0.ldo + n] = DType<T>::from_float(v);
 }
 
-template <typename T, int CP, int NWARPS, int RC>
+// ---- pieces of one pass (one code stream of one tile share) --------------------------------
+
+// Palette entries this thread will write into the pair table of a pass: fetched early (one
+// pass ahead), stored late (table_store), so the palette's DRAM round trip is off the path.
+// registers per thread: nl (<= 2) * 256 entries * 8 sixteen-byte copies / threads
+template <int NT> struct LutRegs { static constexpr int n = 4096 / NT; };
+
+template <int NT>
+__device__ __forceinline__ void table_fetch(uint32_t (&v)[LutRegs<NT>::n], const uint16_t* __restrict__ lut,
+                                            int bits, int n_groups, int row0, int gs, int nl) {
+  const int entries = 1 << (2 * bits);
+  const uint32_t mask = (1u << bits) - 1u;
+  const int rows_per_lut = kTileRows / nl;
+#pragma unroll
+  for (int k = 0; k < LutRegs<NT>::n; ++k) {
+    const int idx = threadIdx.x + k * NT;
+    v[k] = 0u;
+    if (idx < nl * entries * 8) {
+      const int e = (idx >> 3) & (entries - 1), sl = idx >> (3 + 2 * bits);
+      int grp = (row0 + sl * rows_per_lut) / gs;
+      if (grp > n_groups - 1) grp = n_groups - 1;
+      const uint16_t* row = lut + (size_t(grp) << bits);
+      v[k] = uint32_t(__ldg(row + (e & mask))) | (uint32_t(__ldg(row + (e >> bits))) << 16);
+    }
+  }
+}
+
+template <int NT>
+__device__ __forceinline__ void table_store(uint8_t* tbl_ptr, const uint32_t (&v)[LutRegs<NT>::n], int bits,
+                                            int nl) {
+  const int entries = 1 << (2 * bits);
+#pragma unroll
+  for (int k = 0; k < LutRegs<NT>::n; ++k) {
+    const int idx = threadIdx.x + k * NT;
+    if (idx < nl * entries * 8) {
+      const int q = idx & 7, e = (idx >> 3) & (entries - 1), sl = idx >> (3 + 2 * bits);
+      *reinterpret_cast<uint4*>(tbl_ptr + e * 256 + (sl & 1) * 128 + q * 16) =
+          make_uint4(v[k], v[k], v[k], v[k]);
+    }
+  }
+}
+
+// First chunk of a pass into the (width-agnostic) register buffer.
+__device__ __forceinline__ void first_chunk(uint32_t (&w)[32], const uint8_t* __restrict__ packed,
+                                            int bits, int tile, int G, int c, int c1, int lane) {
+  const size_t chunk_bytes = size_t(1024) * bits;
+  const uint8_t* p = packed + (size_t(tile) * G + c) * chunk_bytes + lane * 32;
+#pragma unroll
+  for (int pl = 0; pl < 4; ++pl)
+    ldg_stream256_if(&w[8 * pl], p + pl * 1024, (pl < bits && c < c1) ? 1u : 0u);
+}
+
+// The chunk loop of a pass: one chunk of codes in flight per warp, activations one chunk ahead.
+template <typename T, int BITS, int CP, int NWARPS>
+__device__ __forceinline__ void plan_kloop(float (&acc)[Plan<CP>::kAcc][4], uint32_t (&w32)[32],
+                                           const uint8_t* __restrict__ packed, int tile, int G,
+                                           int c0, int c1, const uint16_t* __restrict__ x,
+                                           long long ldx, int M, uint32_t tbl_lane, int slot_shift) {
+  using P = Plan<CP>;
+  uint32_t(&w)[8 * BITS] = reinterpret_cast<uint32_t(&)[8 * BITS]>(w32);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const size_t chunk_bytes = size_t(1024) * BITS;
+  const uint8_t* lane_base = packed + (size_t(tile) * G) * chunk_bytes + lane * 32;
+  int c = c0 + warp;
+  uint2 xa[P::kNB][4], xb[P::kNB][4];
+  load_x<CP>(xa, x, ldx, c < c1 ? M : 0, c * kChunkK, gid, tig);
+  for (; c < c1; c += 2 * NWARPS) {
+    {
+      const bool more = c + NWARPS < c1;
+      load_x<CP>(xb, x, ldx, more ? M : 0, (c + NWARPS) * kChunkK, gid, tig);
+      chunk_math<T, BITS, CP>(acc, w, xa, tbl_lane, slot_shift, gid,
+                              lane_base + size_t(c + NWARPS) * chunk_bytes, more ? 1u : 0u);
+    }
+    if (c + NWARPS < c1) {
+      const bool more = c + 2 * NWARPS < c1;
+      load_x<CP>(xa, x, ldx, more ? M : 0, (c + 2 * NWARPS) * kChunkK, gid, tig);
+      chunk_math<T, BITS, CP>(acc, w, xb, tbl_lane, slot_shift, gid,
+                              lane_base + size_t(c + 2 * NWARPS) * chunk_bytes, more ? 1u : 0u);
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < P::kAcc; ++a)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) asm volatile("" ::"f"(acc[a][r]));   // lookups end here
+}
+
+// Cross-warp fold of the accumulator fragments through `red`, fixed warp order, into
+// part_plane[m][row] (+= when accumulate). Caller guarantees `red` is free (a barrier after
+// the last lookup of the table it aliases).
+template <int CP, int NWARPS>
+__device__ __forceinline__ void plan_warp_fold(const float (&acc)[Plan<CP>::kAcc][4], float* red,
+                                               float* part_plane, bool accumulate, int M) {
+  using P = Plan<CP>;
+  constexpr int NT = NWARPS * 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+#pragma unroll
+  for (int nb = 0; nb < P::kNB; ++nb) {
+    if (nb) __syncthreads();
+#pragma unroll
+    for (int a = 0; a < P::kCols; ++a)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int col = 2 * tig + (r & 1);
+        const int s = a * P::kSlabsPerAcc + col / P::kCols, mm = col % P::kCols;
+        const int row = 16 * s + gid + 8 * (r >> 1);
+        red[(warp * P::kCols + mm) * kTileRows + row] = acc[a * P::kNB + nb][r];
+      }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < P::kCols * kTileRows; idx += NT) {
+      const int mm = idx >> 7, row = idx & 127, m = mm + 8 * nb;
+      if (m < M) {
+        float v = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < NWARPS; ++wi) v += red[(wi * P::kCols + mm) * kTileRows + row];
+        float* dst = part_plane + m * kTileRows + row;
+        *dst = accumulate ? *dst + v : v;
+      }
+    }
+  }
+}
+
+// One pass of a block's walk through the plan (block-uniform values).
+struct PassDesc {
+  bool valid;
+  int j, slot;                 // job index and the shared-memory copy that holds it
+  int tile_g, tile, si, c0, c1, plane, pass;
+  bool first_of_job, last_of_tile;
+  const uint8_t* packed;
+  const uint16_t* lut;
+  int bits, gs, n_groups, nl;
+};
+
+template <typename T, int CP, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan_bytes) {
   extern __shared__ __align__(16) uint8_t smem[];
   constexpr int NT = NWARPS * 32;
-  __shared__ JobDev job;
+  using P = Plan<CP>;
+  __shared__ JobDev jobbuf[2];
   __shared__ int is_last;
 
   const PlanHeader& hdr = *reinterpret_cast<const PlanHeader*>(plan_bytes);
@@ -71,74 +209,153 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
 
   float* part = reinterpret_cast<float*>(smem);
   const uint32_t part_addr = smem_u32(smem);
-  const uint32_t tbl_addr = (part_addr + kPartBytes + 0xFFFFu) & ~0xFFFFu;
+  const uint32_t tbl_addr = (part_addr + kPartBytes + 0xFFFFu) & ~0xFFFFu;   // two regions follow
   uint8_t* tbl_ptr = smem + (tbl_addr - part_addr);
-  const int b = blockIdx.x, M = hdr.M;
+  const int b = blockIdx.x, M = hdr.M, njobs = hdr.njobs;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  // ---- the walk: jobs in order, this block's share of each, its tiles, planes, streams -------
+  int it_j = 0, it_lin = 0, it_lin1 = 0, it_plane = 0, it_pass = 0;
+  bool it_loaded = false, it_first = false;
+  auto advance = [&](PassDesc& d) {
+    d.valid = false;
+    for (;;) {
+      if (it_j >= njobs) return;
+      JobDev& job = jobbuf[it_j & 1];
+      if (!it_loaded) {
+        __syncthreads();   // nobody still reads the copy this one replaces
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(jobs + it_j);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&job);
+        for (int i = threadIdx.x; i < int(sizeof(JobDev) / 4); i += NT) dst[i] = __ldcg(src + i);
+        __syncthreads();
+        const int total = job.tiles_total * job.G;
+        it_lin = b * job.per;
+        it_lin1 = it_lin + job.per;
+        if (it_lin1 > total) it_lin1 = total;
+        it_plane = it_pass = 0;
+        it_loaded = true;
+        it_first = true;
+      }
+      if (it_lin >= it_lin1) { ++it_j; it_loaded = false; continue; }
+      const int G = job.G;
+      const bool silu = job.epilogue == B200LUT_EPI_SILU_MUL;
+      d.j = it_j; d.slot = it_j & 1;
+      d.tile_g = it_lin / G;
+      d.c0 = it_lin - d.tile_g * G;
+      d.c1 = d.c0 + (it_lin1 - it_lin);
+      if (d.c1 > G) d.c1 = G;
+      int si = 0;
+      for (int s = 0; s < job.nseg; s += silu ? 2 : 1)
+        if (d.tile_g >= job.seg[s].tile_begin) si = s;
+      d.si = si;
+      d.tile = d.tile_g - job.seg[si].tile_begin;
+      d.plane = it_plane; d.pass = it_pass;
+      const SegDev& sg = job.seg[si + it_plane];
+      const int npass = sg.packed2 ? 2 : 1;
+      d.packed = it_pass ? sg.packed2 : sg.packed;
+      d.lut = it_pass ? sg.lut2 : sg.lut;
+      d.bits = it_pass ? sg.bits2 : sg.bits;
+      d.gs = sg.gs; d.n_groups = sg.n_groups;
+      d.nl = sg.gs >= kTileRows ? 1 : kTileRows / sg.gs;
+      d.first_of_job = it_first;
+      it_first = false;
+      // step
+      d.last_of_tile = false;
+      if (++it_pass >= npass) {
+        it_pass = 0;
+        if (++it_plane >= job.planes) {
+          it_plane = 0;
+          d.last_of_tile = true;
+          it_lin += d.c1 - d.c0;
+        }
+      }
+      d.valid = true;
+      return;
+    }
+  };
+
 #ifdef B200LUT_PLAN_TIMING
-  long long tm_copy = 0, tm_pass = 0, tm_fold = 0, tm_total0 = clock64(), tm_mark;
+  long long tm_head = 0, tm_loop = 0, tm_fold = 0, tm_tile = 0, tm_total0 = clock64(), tm_mark;
 #define TM_MARK() tm_mark = clock64()
 #define TM_ADD(v) v += clock64() - tm_mark
 #else
 #define TM_MARK()
 #define TM_ADD(v)
 #endif
+  PassDesc cur, nxt;
+  uint32_t w[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) w[i] = 0u;
+  uint32_t lutv[LutRegs<NT>::n];
+  advance(cur);
+  int region = 0;
+  if (cur.valid) {
+    first_chunk(w, cur.packed, cur.bits, cur.tile, jobbuf[cur.slot].G, cur.c0 + warp, cur.c1, lane);
+    table_fetch<NT>(lutv, cur.lut, cur.bits, cur.n_groups, cur.tile * kTileRows, cur.gs, cur.nl);
+    table_store<NT>(tbl_ptr, lutv, cur.bits, cur.nl);
+  }
 
-  for (int j = 0; j < hdr.njobs; ++j) {
+  while (cur.valid) {
+    const JobDev& job = jobbuf[cur.slot];
+    uint8_t* my_tbl = tbl_ptr + size_t(region) * kTableBytes;
+    const uint32_t my_tbl_addr = tbl_addr + uint32_t(region) * kTableBytes;
     TM_MARK();
-    __syncthreads();
-    {
-      const uint32_t* src = reinterpret_cast<const uint32_t*>(jobs + j);
-      uint32_t* dst = reinterpret_cast<uint32_t*>(&job);
-      for (int i = threadIdx.x; i < int(sizeof(JobDev) / 4); i += NT) dst[i] = __ldcg(src + i);
+    // look one pass ahead first (may load the next job's descriptor; block-uniform) and
+    // request that pass's palette: none of it depends on the producer of this job's rows
+    advance(nxt);
+    if (nxt.valid)
+      table_fetch<NT>(lutv, nxt.lut, nxt.bits, nxt.n_groups, nxt.tile * kTileRows, nxt.gs, nxt.nl);
+    // the producer of this job's activation rows must have finished (bounded poll)
+    if (cur.first_of_job && job.dep >= 0 && threadIdx.x == 0)
+      dep_poll(DepWait{2, done + job.dep, job.dep_target, misc + 1});
+    __syncthreads();                       // table of this pass is complete; dependency met
+    TM_ADD(tm_head);
+    TM_MARK();
+#ifdef B200LUT_PLAN_TIMING
+    if (threadIdx.x == 0 && b == 0 && cur.first_of_job) reinterpret_cast<long long*>(misc + 64)[4 * cur.j + 0] = clock64() - tm_total0;
+#endif
+    float acc[P::kAcc][4];
+#pragma unroll
+    for (int a = 0; a < P::kAcc; ++a)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) acc[a][r] = 0.f;
+    uint32_t token;
+    asm volatile("mov.u32 %0, 0;" : "=r"(token));
+    const uint32_t tbl_lane = my_tbl_addr + lane * 4 + token;
+    const int slot_shift = cur.nl == 1 ? 3 : 2;
+#define B200LUT_KLOOP(B)                                                                        \
+  plan_kloop<T, B, CP, NWARPS>(acc, w, cur.packed, cur.tile, job.G, cur.c0, cur.c1, job.x, job.ldx, \
+                               M, tbl_lane, slot_shift)
+    switch (cur.bits) {   // block-uniform
+      case 4: B200LUT_KLOOP(4); break;
+      case 3: B200LUT_KLOOP(3); break;
+      case 2: B200LUT_KLOOP(2); break;
+      default: B200LUT_KLOOP(1); break;
     }
-    __syncthreads();
-    TM_ADD(tm_copy);
-    const int G = job.G, total = job.tiles_total * G;
-    const int lin0 = b * job.per;
-    int lin1 = lin0 + job.per;
-    if (lin1 > total) lin1 = total;
-    const bool silu = job.epilogue == B200LUT_EPI_SILU_MUL;
-    bool waited = job.dep < 0;
-    for (int lin = lin0; lin < lin1;) {
-      const int tile_g = lin / G, c0 = lin - tile_g * G;
-      int c1 = c0 + (lin1 - lin);
-      if (c1 > G) c1 = G;
-      int si = 0;
-      for (int s = 0; s < job.nseg; s += silu ? 2 : 1)
-        if (tile_g >= job.seg[s].tile_begin) si = s;
-      const int tile = tile_g - job.seg[si].tile_begin;
+#undef B200LUT_KLOOP
 
-      TM_MARK();
-      for (int plane = 0; plane < job.planes; ++plane) {
-        const SegDev& sg = job.seg[si + plane];
-        const int npass = sg.packed2 ? 2 : 1;
-        for (int pass = 0; pass < npass; ++pass) {
-          const uint8_t* packed = pass ? sg.packed2 : sg.packed;
-          const uint16_t* lut = pass ? sg.lut2 : sg.lut;
-          const int bits = pass ? sg.bits2 : sg.bits;
-          float* dst = part + plane * kMaxM * kTileRows;
-          const DepWait dep{waited ? 0 : 2, done + (job.dep < 0 ? 0 : job.dep), job.dep_target,
-                            misc + 1};
-#define B200LUT_PASS(B)                                                                          \
-  stream_pass<T, B, CP, NWARPS, RC>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups, \
-                                    sg.gs, tile, G, c0, c1, job.x, job.ldx, M, true, dep)
-          switch (bits) {   // block-uniform
-            case 4: B200LUT_PASS(4); break;
-            case 3: B200LUT_PASS(3); break;
-            case 2: B200LUT_PASS(2); break;
-            default: B200LUT_PASS(1); break;
-          }
-#undef B200LUT_PASS
-          waited = true;
-        }
-      }
+    TM_ADD(tm_loop);
+    TM_MARK();
+#ifdef B200LUT_PLAN_TIMING
+    if (threadIdx.x == 0 && b == 0) reinterpret_cast<long long*>(misc + 64)[4 * cur.j + 1] = clock64() - tm_total0;
+#endif
+    // codes and table of the next pass go out before this pass folds
+    if (nxt.valid) {
+      first_chunk(w, nxt.packed, nxt.bits, nxt.tile, jobbuf[nxt.slot].G, nxt.c0 + warp, nxt.c1, lane);
+      table_store<NT>(tbl_ptr + size_t(region ^ 1) * kTableBytes, lutv, nxt.bits, nxt.nl);
+    }
+    __syncthreads();                       // every warp is done with this pass's table
+    plan_warp_fold<CP, NWARPS>(acc, reinterpret_cast<float*>(my_tbl),
+                               part + cur.plane * kMaxM * kTileRows, cur.pass != 0, M);
 
-      TM_ADD(tm_pass);
-      TM_MARK();
-      // ---- fold the shares of this tile and store ------------------------------------------
-      const SegDev& s0 = job.seg[si];
-      const SegDev* s1 = silu ? &job.seg[si + 1] : nullptr;
-      const int n0 = tile * kTileRows;
+    TM_ADD(tm_fold);
+    TM_MARK();
+    if (cur.last_of_tile) {
+      // ---- fold the shares of this tile across blocks and store -----------------------------
+      const bool silu = job.epilogue == B200LUT_EPI_SILU_MUL;
+      const SegDev& s0 = job.seg[cur.si];
+      const SegDev* s1 = silu ? &job.seg[cur.si + 1] : nullptr;
+      const int G = job.G, n0 = cur.tile * kTileRows, tile_g = cur.tile_g;
       const int first = (tile_g * G) / job.per, last = (tile_g * G + G - 1) / job.per;
       const int nctr = last - first + 1, ci = b - first;
       const int plane_elems = M * kTileRows, tile_elems = job.planes * plane_elems;
@@ -184,17 +401,25 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
         __syncthreads();
         if (threadIdx.x == 0) {
           __threadfence();
-          atomicAdd(done + j, 1);
+          atomicAdd(done + cur.j, 1);
         }
       }
-      TM_ADD(tm_fold);
-      lin += c1 - c0;
     }
+    TM_ADD(tm_tile);
+#ifdef B200LUT_PLAN_TIMING
+    if (threadIdx.x == 0 && b == 0) reinterpret_cast<long long*>(misc + 64)[4 * cur.j + 2] = clock64() - tm_total0;
+    if (threadIdx.x == 0 && cur.j >= 8 && cur.j < 12) {
+      long long* q = reinterpret_cast<long long*>(misc + 2048) + ((cur.j - 8) * 160 + b) * 4;
+      q[0] = clock64(); q[1] = tm_mark; q[2] = cur.last_of_tile ? 1 : 0; q[3] = cur.c1 - cur.c0;
+    }
+#endif
+    cur = nxt;
+    region ^= 1;
   }
 #ifdef B200LUT_PLAN_TIMING
   if (threadIdx.x == 0 && b < 4) {
-    long long* t = reinterpret_cast<long long*>(misc + 16) + b * 4;
-    t[0] = tm_copy; t[1] = tm_pass; t[2] = tm_fold; t[3] = clock64() - tm_total0;
+    long long* t = reinterpret_cast<long long*>(misc + 16) + b * 5;
+    t[0] = tm_head; t[1] = tm_loop; t[2] = tm_fold; t[3] = tm_tile; t[4] = clock64() - tm_total0;
   }
 #endif
 
@@ -204,7 +429,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
     __threadfence();
     const int old = atomicAdd(misc, 1);
     if (old == int(gridDim.x) - 1) {
-      for (int j = 0; j < hdr.njobs; ++j) done[j] = 0;
+      for (int j = 0; j < njobs; ++j) done[j] = 0;
       misc[0] = 0;
       __threadfence();
     }
