@@ -147,6 +147,22 @@ int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out,
                  int M, int N, int K, int bits, int group_size, int n_groups, int dtype,
                  int split, void* workspace, size_t workspace_bytes, void* stream);
 
+/* b200lut_gemv for callers that cannot hand the library any memory — a host whose device
+ * pool is carved up once at start-up, a plug-in invoked where cudaMalloc is forbidden, a
+ * process without an allocator. Same arithmetic as b200lut_gemv, but the split-K fold always
+ * goes through scratch, and that scratch is an 8 MiB array built into the library image
+ * (every device that loads the library holds it until exit); the call allocates and frees
+ * nothing. Limit: split * (N/128) * M * 1024 bytes of partial tiles must fit 8 MiB - 4 KiB
+ * and N <= 131072; larger requests return B200LUT_ERR_WORKSPACE with the sizes in the
+ * message. split: 0 = library policy, else 1..16. The first call on each device looks up
+ * the array's device address (make that call before any stream capture). All calls share
+ * the array: launches that overlap on the GPU race; stream-ordered calls are safe (partials
+ * are fully rewritten by each call, tickets return to zero by themselves).
+ * This entry point has no counterpart in the reference. */
+int b200lut_gemv_noalloc(const void* x, const void* packed, const void* lut, void* out,
+                         int M, int N, int K, int bits, int group_size, int n_groups, int dtype,
+                         int split, void* stream);
+
 /* One decode GEMV launch inside a persistent plan: what b200lut_gemv_multi takes, plus
  * the index of the earlier job that produces this job's activation rows (-1: none). */
 typedef struct b200lut_job {

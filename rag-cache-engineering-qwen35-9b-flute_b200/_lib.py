@@ -27,7 +27,7 @@ EXPORTS = (
     "b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes",
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
-    "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
+    "b200lut_gemv_noalloc", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
 
@@ -98,6 +98,8 @@ def lib() -> ctypes.CDLL:
     L.b200lut_gemm.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32, vp]
     L.b200lut_fht.restype = i32
     L.b200lut_fht.argtypes = [vp, vp, vp, vp, i32, i32, i64, i64, i32, i32, i32, vp]
+    L.b200lut_gemv_noalloc.restype = i32
+    L.b200lut_gemv_noalloc.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
     L.b200lut_plan_bytes.restype = sz
     L.b200lut_plan_bytes.argtypes = [ctypes.POINTER(Job), i32, i32, i32]
     L.b200lut_plan_build.restype = i32

@@ -847,3 +847,83 @@ extern "C" int b200lut_plan_status(const void* plan) {
   if (misc[1] != 0) return fail(B200LUT_ERR_DEVICE, "a dependency wait inside the plan ran out");
   return B200LUT_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free entry point
+// ------------------------------------------------------------------------------------------
+// Some hosts of this library cannot give it memory: a runtime that hands out its device
+// pool once at start-up and forbids cudaMalloc afterwards, a plug-in called from inside a
+// region where allocation is banned, an embedding in a process that has no allocator of
+// its own. For them the split-K fold's scratch (fp32 partial tiles + tickets) lives in a
+// fixed array inside the library image instead of a caller buffer. Every device that loads
+// the library holds these 8 MiB until the process exits.
+namespace {
+constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;
+constexpr size_t kNoAllocTicketBytes = 4096;   // 1024 tiles
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+}  // namespace
+
+extern "C" int b200lut_gemv_noalloc(const void* x, const void* packed, const void* lut, void* out,
+                                    int M, int N, int K, int bits, int group_size, int n_groups,
+                                    int dtype, int split, void* stream) {
+  B200LUT_REQUIRE(x && packed && lut && out, B200LUT_ERR_INVALID, "null x, codes, palette or output");
+  B200LUT_REQUIRE(M >= 1 && M <= kMaxM, B200LUT_ERR_UNSUPPORTED,
+                  "decode GEMV serves 1 <= M <= 16, got M=%d", M);
+  B200LUT_REQUIRE(K > 0 && K % kChunkK == 0, B200LUT_ERR_INVALID,
+                  "K must be a positive multiple of 64, got %d", K);
+  B200LUT_REQUIRE(dtype == B200LUT_BF16 || dtype == B200LUT_F16, B200LUT_ERR_INVALID,
+                  "dtype must be B200LUT_BF16 or B200LUT_F16");
+  B200LUT_REQUIRE(aligned16(x), B200LUT_ERR_ALIGN, "x must be 16-byte aligned");
+  b200lut_segment seg = {};
+  seg.packed = packed;
+  seg.lut = lut;
+  seg.out = out;
+  seg.ldo = N;
+  seg.N = N;
+  seg.group_size = group_size;
+  seg.n_groups = n_groups;
+  seg.bits = bits;
+
+  GemvParams p = {};
+  p.x = static_cast<const uint16_t*>(x);
+  p.ldx = K;
+  p.M = M;
+  p.K = K;
+  p.G = K / kChunkK;
+  p.nseg = 1;
+  p.epilogue = B200LUT_EPI_NONE;
+  int tiles = 0, max_tables = 1;
+  if (int rc = convert_segments(&seg, 1, false, p.seg, &tiles, &max_tables)) return rc;
+  p.tiles_total = tiles;
+  if (split <= 0) split = pick_split(tiles, p.G, sm_count_cached(), M <= 8 ? kWarpsM8 : kWarpsM16);
+  B200LUT_REQUIRE(split >= 1 && split <= 16 && split <= p.G, B200LUT_ERR_INVALID,
+                  "split must be 1..16 and <= K/64, got %d", split);
+  // the built-in scratch bounds the problem: partial tiles of every split, plus tickets
+  const size_t need = size_t(split) * size_t(tiles) * 2 * size_t(M) * kTileRows * sizeof(float);
+  B200LUT_REQUIRE(size_t(tiles) * sizeof(int) <= kNoAllocTicketBytes &&
+                      need <= kNoAllocScratchBytes - kNoAllocTicketBytes,
+                  B200LUT_ERR_WORKSPACE,
+                  "N=%d, M=%d, split=%d needs %zu bytes of fold scratch; the allocation-free entry "
+                  "has %zu (lower split, or use b200lut_gemv with a caller workspace)",
+                  N, M, split, need, kNoAllocScratchBytes - kNoAllocTicketBytes);
+
+  // set-up, once per device, with that device current: the array's name is only a host-side
+  // handle; the kernel needs the device address behind it
+  static unsigned char* scratch_addr[64] = {nullptr};
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  B200LUT_REQUIRE(dev >= 0 && dev < 64, B200LUT_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  if (!scratch_addr[dev]) {
+    void* ptr = nullptr;
+    B200LUT_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    B200LUT_REQUIRE(ptr != nullptr, B200LUT_ERR_CUDA, "no device address for the built-in scratch");
+    scratch_addr[dev] = static_cast<unsigned char*>(ptr);
+  }
+  p.split = split;
+  p.cluster = 0;     // always the scratch fold: partials to the array, last arrival sums them
+  p.tickets = reinterpret_cast<int*>(scratch_addr[dev]);            // zero at load, self-resetting
+  p.ws = reinterpret_cast<float*>(scratch_addr[dev] + kNoAllocTicketBytes);   // fully rewritten per call
+  cudaStream_t st = cudaStream_t(stream);
+  if (dtype == B200LUT_BF16) return dispatch<__nv_bfloat16>(p, max_tables, false, st);
+  return dispatch<__half>(p, max_tables, false, st);
+}
