@@ -291,7 +291,7 @@ def main() -> int:
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (1/0)")
-    ap.add_argument("--executor", default="plan", choices=("plan", "graph"),
+    ap.add_argument("--executor", default="graph", choices=("plan", "graph"),
                     help="plan: persistent cooperative launch(es) per step; graph: one kernel per "
                          "projection group under CUDA-graph replay")
     args = ap.parse_args()
