@@ -34,13 +34,16 @@ constexpr int kLookupWarps = 8;
 constexpr int kThreads = (kLookupWarps + 2) * 32;
 constexpr int kAStages = 4;            // operand stages in TMEM, 32 columns each
 constexpr int kRing = 4;               // k-blocks of codes in flight per lookup warp
-constexpr int kMaxXStages = 6;
+constexpr int kMaxXStages = kAStages;   // activation stage s pairs with operand stage s
 constexpr uint32_t kCtrlBytes = 1024;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kACol = 256;        // operand stage s at columns [256 + 32 s, 288 + 32 s)
 constexpr size_t kMaxDynSmem = 232448 - 1024;
 
 __device__ int g_gemm_status = 0;
+#ifdef B200LUT_GEMM_TIMING
+__device__ long long g_gemm_timing[64];
+#endif
 
 struct GemmParams {
   const uint8_t* packed[2];
@@ -55,6 +58,7 @@ struct GemmParams {
   int NT;           // token tile (multiple of 16, <= 256; <= 128 with two planes)
   int m_tiles;
   uint32_t smem_bytes;
+  int debug;
 };
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -73,8 +77,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t base = smem_u32(smem);
   // control block: barriers, the TMEM base and the abort flag
-  const uint32_t bar_xfull = base, bar_xempty = base + 64, bar_afull = base + 128,
-                 bar_aempty = base + 192, bar_done = base + 256;
+  const uint32_t bar_xfull = base, bar_afull = base + 128, bar_empty = base + 192,
+                 bar_done = base + 256;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + 264);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 268);
 
@@ -121,13 +125,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
 
   // ---- setup ----------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kMaxXStages; ++s) {
-      tc::mbar_init(bar_xfull + 8 * s, 1);
-      tc::mbar_init(bar_xempty + 8 * s, 1);
-    }
     for (int s = 0; s < kAStages; ++s) {
-      tc::mbar_init(bar_afull + 8 * s, 4);
-      tc::mbar_init(bar_aempty + 8 * s, 1);
+      tc::mbar_init(bar_xfull + 8 * s, 1);    // TMA transaction bytes
+      tc::mbar_init(bar_afull + 8 * s, 4);    // the four lookup warps that filled the stage
+      tc::mbar_init(bar_empty + 8 * s, 1);    // tcgen05.commit: both operands of the stage consumed
     }
     tc::mbar_init(bar_done, 1);
     *abort_flag = (*nxs_slot < 2) ? 1 : 0;   // cannot pipeline: drain at once (host prevents this)
@@ -142,23 +143,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const int nxs = *nxs_slot > 0 ? *nxs_slot : 1;
+  const int nst = *nxs_slot > 0 ? *nxs_slot : 1;   // pipeline depth: 2..4 stages of both operands
 
   if (warp < kLookupWarps) {
     // ---- lookup warps: codes -> palette pairs -> TMEM -------------------------------------------
     uint32_t token;
     asm volatile("mov.u32 %0, 0;" : "=r"(token));
     const uint32_t lane_base = tbl_addr + lane * 4 + token;
+#ifdef B200LUT_GEMM_TIMING
+    long long t_wait = 0, t_all = clock64();
+#endif
     for (int i0 = grp; i0 < total; i0 += 2 * kRing) {
 #pragma unroll
       for (int u = 0; u < kRing; ++u) {
         const int i = i0 + 2 * u;
         if (i < total) {
-          const int stage = i % kAStages, use = i / kAStages;
+          const int stage = i % nst, use = i / nst;
           const int pass = i >= p.G ? 1 : 0;
+#ifdef B200LUT_GEMM_TIMING
+          long long ta = clock64();
+#endif
           if (use > 0)
-            tc::mbar_wait(bar_aempty + 8 * stage, uint32_t(use - 1) & 1u, abort_flag,
+            tc::mbar_wait(bar_empty + 8 * stage, uint32_t(use - 1) & 1u, abort_flag,
                           &g_gemm_status, tc::kStatusWaitEmpty);
+#ifdef B200LUT_GEMM_TIMING
+          t_wait += clock64() - ta;
+#endif
           tc::fence_after_sync();
 #pragma unroll
           for (int sl = 0; sl < 2; ++sl) {
@@ -169,6 +179,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
 #pragma unroll
             for (int kt = 0; kt < 4; ++kt) {
               const uint32_t word = w[u][4 * sl + kt];
+#ifdef B200LUT_GEMM_TIMING
+              if (p.debug & 1) { r[4 * kt] = word; r[4 * kt + 1] = word; r[4 * kt + 2] = word; r[4 * kt + 3] = word; continue; }
+#endif
               // slab fields (row g, k 0-1), (g+8, k 0-1), (g, k 2-3), (g+8, k 2-3); the store
               // shape wants (g, c), (g, c+1), (g+8, c), (g+8, c+1): fields 0, 2, 1, 3
               r[4 * kt + 0] = lds32(__byte_perm(word, tb, 0x7604u));
@@ -186,14 +199,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
         }
       }
     }
+#ifdef B200LUT_GEMM_TIMING
+    if (blockIdx.x == 0 && lane == 0) { g_gemm_timing[warp * 2] = t_wait; g_gemm_timing[warp * 2 + 1] = clock64() - t_all; }
+#endif
   } else if (warp == kLookupWarps) {
     // ---- TMA producer: activations of k-block c, tokens m0 .. m0 + NT ---------------------------
     for (int i = 0; i < total; ++i) {
-      const int xs = i % nxs, use = i / nxs;
+      const int xs = i % nst, use = i / nst;
       const int c = i >= p.G ? i - p.G : i;
       if (use > 0)
-        tc::mbar_wait(bar_xempty + 8 * xs, uint32_t(use - 1) & 1u, abort_flag, &g_gemm_status,
+        tc::mbar_wait(bar_empty + 8 * xs, uint32_t(use - 1) & 1u, abort_flag, &g_gemm_status,
                       tc::kStatusWaitEmpty);
+#ifdef B200LUT_GEMM_TIMING
+      if (lane == 0 && (p.debug & 2) && use > 0) { tc::mbar_arrive(bar_xfull + 8 * xs); } else
+#endif
       if (lane == 0 && !*abort_flag) {
         tc::mbar_expect_tx(bar_xfull + 8 * xs, stage_bytes);
         tma_load_2d(xaddr[xs], &xmap, bar_xfull + 8 * xs, c * kChunkK, m0);
@@ -204,30 +223,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     // ---- MMA issuer ---------------------------------------------------------------------------
     constexpr uint32_t kFmt = DType<T>::id == B200LUT_BF16 ? 1u : 0u;
     const uint32_t idesc = tc::instr_desc(kFmt, 128, uint32_t(p.NT));
+#ifdef B200LUT_GEMM_TIMING
+    long long t_x = 0, t_a = 0, t_all = clock64();
+#endif
+    // One thread issues; its instruction stream is the limit (an MMA must leave every 128
+    // cycles), so everything per-MMA is precomputed: descriptor templates per stage, a
+    // 64-bit add per K step, one commit per k-block.
+    const uint64_t dtemplate = tc::smem_desc(0u, 16u, 1024u, 2u);
     for (int i = 0; i < total; ++i) {
-      const int stage = i % kAStages, ause = i / kAStages;
-      const int xs = i % nxs, xuse = i / nxs;
+      const int stage = i % nst, use = i / nst;
       const int pass = i >= p.G ? 1 : 0, blk = pass ? i - p.G : i;
-      tc::mbar_wait(bar_xfull + 8 * xs, uint32_t(xuse) & 1u, abort_flag, &g_gemm_status,
+      const uint64_t bdesc0 = dtemplate + uint64_t(xaddr[stage] >> 4);
+      const uint32_t a0 = tmem + kACol + 32u * uint32_t(stage);
+      const uint32_t d0 = tmem + uint32_t(p.plane[pass] * p.NT);
+      const uint32_t first_acc = (blk == 0 && (pass == 0 || p.plane[1] != p.plane[0])) ? 0u : 1u;
+#ifdef B200LUT_GEMM_TIMING
+      long long ta = clock64();
+#endif
+      tc::mbar_wait(bar_xfull + 8 * stage, uint32_t(use) & 1u, abort_flag, &g_gemm_status,
                     tc::kStatusWaitLoad);
-      tc::mbar_wait(bar_afull + 8 * stage, uint32_t(ause) & 1u, abort_flag, &g_gemm_status,
+#ifdef B200LUT_GEMM_TIMING
+      long long tb = clock64(); t_x += tb - ta;
+#endif
+      tc::mbar_wait(bar_afull + 8 * stage, uint32_t(use) & 1u, abort_flag, &g_gemm_status,
                     tc::kStatusWaitFull);
+#ifdef B200LUT_GEMM_TIMING
+      t_a += clock64() - tb;
+#endif
       tc::fence_after_sync();
       if (lane == 0) {
-        // the first k-block that targets a plane overwrites it
-        const bool first_of_plane = blk == 0 && (pass == 0 || p.plane[1] != p.plane[0]);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t bdesc = tc::smem_desc(xaddr[xs] + 32u * ks, 16u, 1024u, 2u);
-          tc::mma_ts(tmem + uint32_t(p.plane[pass] * p.NT), tmem + kACol + 32u * stage + 8u * ks,
-                     bdesc, idesc, (first_of_plane && ks == 0) ? 0u : 1u);
-        }
-        tc::mma_commit(bar_xempty + 8 * xs);
-        tc::mma_commit(bar_aempty + 8 * stage);
+        tc::mma_ts(d0, a0, bdesc0, idesc, first_acc);        // the first k-block of a plane overwrites it
+        tc::mma_ts(d0, a0 + 8u, bdesc0 + 2u, idesc, 1u);     // +32 bytes of K per step
+        tc::mma_ts(d0, a0 + 16u, bdesc0 + 4u, idesc, 1u);
+        tc::mma_ts(d0, a0 + 24u, bdesc0 + 6u, idesc, 1u);
+        tc::mma_commit(bar_empty + 8 * stage);
         if (i == total - 1) tc::mma_commit(bar_done);
       }
       __syncwarp();
     }
+#ifdef B200LUT_GEMM_TIMING
+    if (blockIdx.x == 0 && lane == 0) { g_gemm_timing[40] = t_x; g_gemm_timing[41] = t_a; g_gemm_timing[42] = clock64() - t_all; g_gemm_timing[43] = nst; }
+#endif
   }
 
   // ---- epilogue: TMEM -> bias / SiLU*mul -> one rounding -> global -----------------------------
@@ -319,6 +355,12 @@ int launch(const CUtensorMap& map, const GemmParams& p, int n_tiles, bool pdl, c
 
 using namespace b200lut;
 
+#ifdef B200LUT_GEMM_TIMING
+extern "C" int b200lut_gemm_timing(long long* out64) {
+  return cudaMemcpyFromSymbol(out64, g_gemm_timing, sizeof(long long) * 64) == cudaSuccess ? 0 : 3;
+}
+#endif
+
 // Device-side status of the tensor-core kernel on the current device (0 = none). A
 // non-zero value means a bounded wait ran out inside a kernel; cleared by this call.
 extern "C" int b200lut_device_status(void) {
@@ -393,6 +435,7 @@ extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
                     "stages in shared memory", s.group_size, p.npass);
   }
   p.smem_bytes = uint32_t(kMaxDynSmem);
+  { const char* e = getenv("B200LUT_GEMM_DEBUG"); p.debug = e ? atoi(e) : 0; }
 
   EncodeTiledFn enc = encode_fn();
   B200LUT_REQUIRE(enc != nullptr, B200LUT_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
