@@ -59,6 +59,7 @@ struct GemmParams {
   int m_tiles;
   uint32_t smem_bytes;
   int debug;
+  int out_aligned;   // out rows are 16-byte aligned: staged, vectorised epilogue
 };
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -100,6 +101,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     *nxs_slot = n;
   }
 
+#ifdef B200LUT_GEMM_TIMING
+  const long long t_kernel0 = clock64();
+#endif
   const int n_tile = blockIdx.x / p.m_tiles, m_tile = blockIdx.x % p.m_tiles;
   const int m0 = m_tile * p.NT, n0 = n_tile * kTileRows;
   const int total = p.G * p.npass;     // k-blocks streamed, pass-major
@@ -142,6 +146,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
+#ifdef B200LUT_GEMM_TIMING
+  if (threadIdx.x == 0 && blockIdx.x == 0) g_gemm_timing[48] = clock64() - t_kernel0;
+#endif
   const uint32_t tmem = *tmem_slot;
   const int nst = *nxs_slot > 0 ? *nxs_slot : 1;   // pipeline depth: 2..4 stages of both operands
 
@@ -227,39 +234,55 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     long long t_x = 0, t_a = 0, t_all = clock64();
 #endif
     // One thread issues; its instruction stream is the limit (an MMA must leave every 128
-    // cycles), so everything per-MMA is precomputed: descriptor templates per stage, a
-    // 64-bit add per K step, one commit per k-block.
+    // cycles), so nothing is computed per MMA: stage descriptors sit in registers, stage
+    // and phase advance by increment, a K step is a 64-bit add, one commit per k-block.
     const uint64_t dtemplate = tc::smem_desc(0u, 16u, 1024u, 2u);
-    for (int i = 0; i < total; ++i) {
-      const int stage = i % nst, use = i / nst;
-      const int pass = i >= p.G ? 1 : 0, blk = pass ? i - p.G : i;
-      const uint64_t bdesc0 = dtemplate + uint64_t(xaddr[stage] >> 4);
-      const uint32_t a0 = tmem + kACol + 32u * uint32_t(stage);
-      const uint32_t d0 = tmem + uint32_t(p.plane[pass] * p.NT);
-      const uint32_t first_acc = (blk == 0 && (pass == 0 || p.plane[1] != p.plane[0])) ? 0u : 1u;
+    uint64_t xd[kAStages];
+#pragma unroll
+    for (int s = 0; s < kAStages; ++s) xd[s] = dtemplate + uint64_t(xaddr[s < nst ? s : 0] >> 4);
+    const uint32_t dcol[2] = {tmem + uint32_t(p.plane[0] * p.NT), tmem + uint32_t(p.plane[1] * p.NT)};
+    const bool two_planes = p.plane[1] != p.plane[0];
+    const int G = p.G;
+    auto block = [&](int i, int stage, uint32_t phase, uint64_t bdesc0) {
+      const int pass = i >= G ? 1 : 0;
+      const bool first = (i == 0) || (two_planes && i == G);
 #ifdef B200LUT_GEMM_TIMING
       long long ta = clock64();
 #endif
-      tc::mbar_wait(bar_xfull + 8 * stage, uint32_t(use) & 1u, abort_flag, &g_gemm_status,
-                    tc::kStatusWaitLoad);
+      tc::mbar_wait(bar_xfull + 8 * stage, phase, abort_flag, &g_gemm_status, tc::kStatusWaitLoad);
 #ifdef B200LUT_GEMM_TIMING
       long long tb = clock64(); t_x += tb - ta;
 #endif
-      tc::mbar_wait(bar_afull + 8 * stage, uint32_t(use) & 1u, abort_flag, &g_gemm_status,
-                    tc::kStatusWaitFull);
+      tc::mbar_wait(bar_afull + 8 * stage, phase, abort_flag, &g_gemm_status, tc::kStatusWaitFull);
 #ifdef B200LUT_GEMM_TIMING
       t_a += clock64() - tb;
 #endif
       tc::fence_after_sync();
       if (lane == 0) {
-        tc::mma_ts(d0, a0, bdesc0, idesc, first_acc);        // the first k-block of a plane overwrites it
-        tc::mma_ts(d0, a0 + 8u, bdesc0 + 2u, idesc, 1u);     // +32 bytes of K per step
+        const uint32_t a0 = tmem + kACol + 32u * uint32_t(stage), d0 = pass ? dcol[1] : dcol[0];
+        tc::mma_ts(d0, a0, bdesc0, idesc, first ? 0u : 1u);   // first k-block of a plane overwrites
+        tc::mma_ts(d0, a0 + 8u, bdesc0 + 2u, idesc, 1u);      // +32 bytes of K per step
         tc::mma_ts(d0, a0 + 16u, bdesc0 + 4u, idesc, 1u);
         tc::mma_ts(d0, a0 + 24u, bdesc0 + 6u, idesc, 1u);
         tc::mma_commit(bar_empty + 8 * stage);
         if (i == total - 1) tc::mma_commit(bar_done);
       }
       __syncwarp();
+    };
+    if (nst == kAStages) {
+      uint32_t phase = 0;
+      for (int i0 = 0; i0 < total; i0 += kAStages, phase ^= 1u) {
+#pragma unroll
+        for (int s = 0; s < kAStages; ++s)
+          if (i0 + s < total) block(i0 + s, s, phase, xd[s]);
+      }
+    } else {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < total; ++i) {
+        block(i, stage, phase, dtemplate + uint64_t(xaddr[stage] >> 4));
+        if (++stage == nst) { stage = 0; phase ^= 1u; }
+      }
     }
 #ifdef B200LUT_GEMM_TIMING
     if (blockIdx.x == 0 && lane == 0) { g_gemm_timing[40] = t_x; g_gemm_timing[41] = t_a; g_gemm_timing[42] = clock64() - t_all; g_gemm_timing[43] = nst; }
@@ -270,10 +293,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
   if (warp < kLookupWarps) {
     tc::mbar_wait(bar_done, 0u, abort_flag, &g_gemm_status, tc::kStatusWaitDone);
     tc::fence_after_sync();
+#ifdef B200LUT_GEMM_TIMING
+    if (threadIdx.x == 0 && blockIdx.x == 0) g_gemm_timing[49] = clock64() - t_kernel0;
+#endif
     const int n = n0 + 32 * q + lane;
     const float b0 = p.bias[0] ? DType<T>::to_float(p.bias[0][n]) : 0.f;
     const float b1 = (p.npass > 1 && p.bias[1]) ? DType<T>::to_float(p.bias[1][n]) : 0.f;
     const int half_cols = p.NT / 2;
+    // The output tile is staged in the (now idle) pair-table region as [token][128 rows] and
+    // then written with 16-byte stores, 256 contiguous bytes per token row; a thread-per-
+    // element store would issue 2-byte writes at a stride of ldo.
+    uint16_t* stage_out = reinterpret_cast<uint16_t*>(tbl_ptr);
+    const bool staged = p.out_aligned != 0;
     for (int cb = grp * half_cols; cb < (grp + 1) * half_cols; cb += 16) {
       uint32_t r0[16], r1[16];
       tc::tmem_ld_32x32b_x16(tmem + (uint32_t(32 * q) << 16) + uint32_t(cb), r0);
@@ -282,21 +313,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const int tok = m0 + cb + j;
-        if (tok < p.M) {
-          float v = __uint_as_float(r0[j]) + b0;
-          if (p.silu) {
-            const float u = __uint_as_float(r1[j]) + b1;
-            v = v / (1.f + __expf(-v)) * u;
-          } else if (p.npass > 1) {
-            v += b1;     // second stream: both biases belong to the one output
-          }
-          p.out[size_t(tok) * p.ldo + n] = DType<T>::from_float(v);
+        float v = __uint_as_float(r0[j]) + b0;
+        if (p.silu) {
+          const float u = __uint_as_float(r1[j]) + b1;
+          v = v / (1.f + __expf(-v)) * u;
+        } else if (p.npass > 1) {
+          v += b1;     // second stream: both biases belong to the one output
         }
+        if (staged) stage_out[(cb + j) * kTileRows + 32 * q + lane] = DType<T>::from_float(v);
+        else if (tok < p.M) p.out[size_t(tok) * p.ldo + n] = DType<T>::from_float(v);
+      }
+    }
+    if (staged) {
+      asm volatile("bar.sync 1, %0;" ::"r"(kLookupWarps * 32) : "memory");   // the eight epilogue warps
+      const uint4* src = reinterpret_cast<const uint4*>(stage_out);
+      for (int idx = threadIdx.x; idx < p.NT * 16; idx += kLookupWarps * 32) {
+        const int r = idx >> 4, c = idx & 15;
+        if (m0 + r < p.M)
+          *reinterpret_cast<uint4*>(p.out + size_t(m0 + r) * p.ldo + n0 + 8 * c) = src[idx];
       }
     }
     tc::fence_before_sync();
   }
   __syncthreads();
+#ifdef B200LUT_GEMM_TIMING
+  if (threadIdx.x == 0 && blockIdx.x == 0) g_gemm_timing[50] = clock64() - t_kernel0;
+#endif
   if (warp == kLookupWarps) {
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem, kTmemCols);
@@ -408,6 +450,7 @@ extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
   p.lut[1] = static_cast<const uint16_t*>(s.lut2);
   p.out = static_cast<uint16_t*>(s.out);
   p.ldo = s.ldo;
+  p.out_aligned = (aligned16(s.out) && s.ldo % 8 == 0) ? 1 : 0;
   p.M = M; p.N = s.N; p.K = K; p.G = K / kChunkK;
   p.gs = s.group_size; p.n_groups = s.n_groups;
   p.npass = two ? 2 : 1;
