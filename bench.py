@@ -281,6 +281,35 @@ def single_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int, fl
     return byts / us / 1e3, us
 
 
+def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool):
+    """Extra: the M=2048 prefill GEMM (optionally behind the 128-point block Hadamard of the
+    activations, timed together), CUDA events, inputs 16 MB + 24 MB + 48 MB out per call."""
+    import torch
+    L = pkg._lib
+    bits, gs, dt = 4, 128, torch.bfloat16
+    packed = L.repack_from_idxn(pkg.synthetic.random_blob_on_device(N, K, bits, 700, "cuda"), N, K, bits)
+    lut = pkg.synthetic.make_lut(N // gs, bits, dt, 700).cuda()
+    x = torch.randn(M, K, device="cuda").to(dt)
+    xr = torch.empty_like(x)
+    out = torch.empty(M, N, dtype=dt, device="cuda")
+    seg = L.make_segments([dict(packed=packed, lut=lut, N=N, group_size=gs, n_groups=N // gs,
+                                bits=bits, out=out)])
+
+    def run():
+        if rotate:
+            L.fht(x, None, block=128, out=xr)
+            L.gemm(xr, seg)
+        else:
+            L.gemm(x, seg)
+    for _ in range(3):
+        run()
+    ms = time_steps(run, iters, 1)
+    if L.lib().b200lut_device_status() != 0:
+        raise RuntimeError("a bounded wait ran out inside the GEMM kernel")
+    us = ms * 1e3 / iters
+    return 2.0 * M * N * K / us / 1e6, us
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -396,6 +425,13 @@ def main() -> int:
             gbs, us = single_projection_gbs(pkg, 1, 12288, 4096, 16, 20, flags)
             extras["gemv_12288x4096_m1"] = {"GB/s": gbs, "us_per_launch": us,
                                             "frac_of_hbm": gbs / peaks["hbm_gbs"]}
+            tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, 20, False)
+            extras["prefill_gemm_m2048_k4096_n12288"] = {
+                "TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"],
+                "peak": peaks["bf16_tflops"], "peak_kind": "burst, " + peaks["source"]}
+            tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, 20, True)
+            extras["prefill_gemm_with_block128_fht"] = {
+                "TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
         except Exception as e:       # an extra must not lose the main line
             extras["error"] = repr(e)
         line["extras"] = extras
