@@ -310,6 +310,25 @@ def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool):
     return 2.0 * M * N * K / us / 1e6, us
 
 
+def run_case(args) -> int:
+    """A few eager launches of one kernel on a profiling-sized case. gemv: 12288 x 4096
+    4-bit projection at M = 1 over 8 distinct weight sets (192 MB of codes, larger than L2);
+    gemm: M = 2048, K = 4096, N = 12288."""
+    import torch
+    torch.cuda.set_device(0)
+    pkg = importlib.import_module(PKG)
+    peaks = measured_peaks()
+    if args.case == "gemv":
+        gbs, us = single_projection_gbs(pkg, args.batch, 12288, 4096, 8, max(args.steps, 1), 0)
+        print(json.dumps({"case": "gemv 12288x4096 M=%d, 8 weight sets" % args.batch, "GB/s": gbs,
+                          "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}))
+    else:
+        tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, max(args.steps, 1), False)
+        print(json.dumps({"case": "gemm M=2048 K=4096 N=12288", "TFLOP/s": tf, "us": us,
+                          "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -320,6 +339,9 @@ def main() -> int:
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (1/0)")
+    ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemm"),
+                    help="stack: the benchmark; gemv / gemm: a few launches of one kernel on a "
+                         "small case (the workloads the ncu captures in profiles/ use)")
     ap.add_argument("--executor", default="graph", choices=("plan", "graph"),
                     help="plan: persistent cooperative launch(es) per step; graph: one kernel per "
                          "projection group under CUDA-graph replay")
@@ -331,6 +353,8 @@ def main() -> int:
         return 0
 
     import torch
+    if args.case != "stack":
+        return run_case(args)
     rank, world, local = dist_setup(args.gpus)
     pkg = importlib.import_module(PKG)
     st = importlib.import_module(PKG + ".stack")
