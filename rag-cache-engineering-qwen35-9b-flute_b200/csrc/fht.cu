@@ -82,6 +82,54 @@ __global__ void __launch_bounds__(1024) fht_kernel(const FhtParams p) {
   }
 }
 
+// 128-point block transform, one block of 128 elements per warp, entirely in registers:
+// lane L holds elements 4L .. 4L+3; stages of length 1 and 2 pair elements inside the lane,
+// stages 4 .. 64 pair lanes L and L ^ (len / 4) through shuffles. Each output is the same
+// expression tree of fp32 adds as in the shared-memory kernel (low element a + b, high
+// element a - b), so the bits are identical; the kernel is a pure stream (HBM bound).
+__global__ void __launch_bounds__(256) fht_block128_kernel(const FhtParams p, long long nblocks,
+                                                          int blocks_per_row) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+  const float inv = p.seg_inv[0];
+  for (long long blk = warp0; blk < nblocks; blk += stride) {
+    const long long row = blk / blocks_per_row;
+    const int off = int(blk - row * blocks_per_row) * 128 + 4 * lane;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[j] = load_elem(p.x, row * p.ldx + off + j, p.dtype);
+      if (p.mode == B200LUT_FHT_AWQ) v[j] = v[j] * p.scale[off + j];
+      else if (p.mode == B200LUT_FHT_ADJOINT && p.signs) v[j] = v[j] * p.signs[off + j];
+    }
+    {   // len 1, then len 2
+      const float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
+      v[0] = a0 + a2; v[1] = a1 + a3; v[2] = a0 - a2; v[3] = a1 - a3;
+    }
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {   // len = 4 * m
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], m);
+        v[j] = (lane & m) ? other - v[j] : v[j] + other;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float r = v[j];
+      if (p.mode == B200LUT_FHT_ADJOINT) {
+        r = r * inv;
+      } else {
+        if (p.signs) r = r * p.signs[off + j];
+        r = r * inv;
+        if (p.mode == B200LUT_FHT_AWQ) r = __fdiv_rn(r, p.scale[off + j]);
+      }
+      store_elem(p.out, row * p.ldo + off + j, p.dtype, r);
+    }
+  }
+}
+
 }  // namespace
 }  // namespace b200lut
 
@@ -112,8 +160,10 @@ extern "C" int b200lut_fht(const void* x, void* out, const float* signs, const f
     // a block of threads takes as many whole transforms as fit 8192 points
     int span = block;
     while (span * 2 <= 8192 && K % (span * 2) == 0) span *= 2;
-    B200LUT_REQUIRE(span <= kMaxPoints && K / span <= kMaxSegments, B200LUT_ERR_UNSUPPORTED,
-                    "K=%d with block=%d needs more than %d row pieces", K, block, kMaxSegments);
+    B200LUT_REQUIRE(block == 128 || (span <= kMaxPoints && K / span <= kMaxSegments),
+                    B200LUT_ERR_UNSUPPORTED, "K=%d with block=%d needs more than %d row pieces", K,
+                    block, kMaxSegments);
+    if (block == 128) span = K;
     p.nseg = K / span;
     for (int i = 0; i < p.nseg; ++i) {
       p.seg_off[i] = i * span;
@@ -140,6 +190,14 @@ extern "C" int b200lut_fht(const void* x, void* out, const float* signs, const f
       if (b > max_len) max_len = b;
       off += b;
     }
+  }
+  if (block == 128) {
+    const long long nblocks = (long long)M * (K / 128);
+    long long grid = (nblocks + 7) / 8;
+    if (grid > 148 * 8) grid = 148 * 8;
+    fht_block128_kernel<<<unsigned(grid), 256, 0, cudaStream_t(stream)>>>(p, nblocks, K / 128);
+    B200LUT_CUDA_OK(cudaGetLastError());
+    return B200LUT_OK;
   }
   const size_t smem = size_t(max_len) * sizeof(float);
   static bool configured[64] = {false};

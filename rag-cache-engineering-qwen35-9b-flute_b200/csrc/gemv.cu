@@ -595,18 +595,23 @@ int sm_count_cached() {
 }
 
 
-// Split policy: one block per SM is resident. Cost of a candidate = waves of blocks
-// times the chunks the busiest warp streams, plus a small per-split fold charge.
+// Split policy: one block per SM is resident. A wave of blocks costs a fixed part (launch
+// ramp, palette fetch and table build, first code fetch, cluster fold: about three chunk
+// rounds of time, measured) plus the chunk rounds of its busiest warp; clusters of `s`
+// blocks place a little under one block per SM.
 int pick_split(int tiles, int G, int sms, int warps) {
+  constexpr long kWaveFixed = 3;
   int best = 1;
   long best_cost = -1;
   for (int s = 1; s <= kMaxClusterSplit; ++s) {
     if (s > G) break;
     const long blocks = long(tiles) * s;
-    const long waves = (blocks + sms - 1) / sms;
+    long cap = s == 1 ? sms : long(sms / s) * s * 9 / 10;
+    if (cap < s) cap = s;
+    const long waves = (blocks + cap - 1) / cap;
     const long per_block = (G + s - 1) / s;
     const long per_warp = (per_block + warps - 1) / warps;
-    const long cost = waves * per_warp * 16 + (s > 1 ? 2 + s / 4 : 0);
+    const long cost = waves * (per_warp + kWaveFixed) * 8 + s;   // ties: the smaller split
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
   }
   return best;
