@@ -339,6 +339,8 @@ def main() -> int:
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (1/0)")
+    ap.add_argument("--layers", type=int, default=32, help="decoder layers of the stack (32 = the model)")
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
     ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemm"),
                     help="stack: the benchmark; gemv / gemm: a few launches of one kernel on a "
                          "small case (the workloads the ncu captures in profiles/ use)")
@@ -362,7 +364,11 @@ def main() -> int:
     flags = pkg._lib.FLAG_PDL if args.pdl else 0
     peaks = measured_peaks()
 
-    stack = st.LinearStack(device=f"cuda:{local}", rank=rank, world=world)
+    def trace(msg):
+        if os.environ.get("B200LUT_BENCH_TRACE"):
+            print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
+    trace("building the stack")
+    stack = st.LinearStack(device=f"cuda:{local}", rank=rank, world=world, n_layers=args.layers)
     gather = make_gather(world, M)
     plan = stack._plan(M)
     x_host = torch.randn(M, st.HIDDEN, generator=torch.Generator().manual_seed(1)).to(stack.dtype).pin_memory()
@@ -377,27 +383,38 @@ def main() -> int:
             stack.step_persistent(M, gather=gather)
         else:
             stack.step(M, flags=flags, gather=gather)
+    trace("first eager step")
     run_step()
     torch.cuda.synchronize()
-    side = torch.cuda.Stream()
-    with torch.cuda.stream(side):
-        run_step()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
+    trace("eager step done")
+    graph = None
+    if not args.no_graph:
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
             run_step()
-    torch.cuda.synchronize()
+            torch.cuda.synchronize()
+            trace("capturing")
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                run_step()
+        torch.cuda.synchronize()
+        trace("captured")
 
     def step_resident():
-        graph.replay()
+        if graph is not None:
+            graph.replay()
+        else:
+            run_step()
 
     def step_e2e():
         plan["x"].copy_(x_host, non_blocking=True)
-        graph.replay()
+        step_resident()
         y_host.copy_(plan["y"], non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(args.warmup):
         step_resident()
+    trace("warm-up done")
     with ClockSampler(local) as clk:
         # run under load for ~1.5 s first so that the 200 ms sampler sees the timed state,
         # then time exactly K steps
@@ -407,6 +424,7 @@ def main() -> int:
                 step_resident()
         ms = time_steps(step_resident, args.steps, world)
     clocks = clk.summary()
+    trace("timed")
     for _ in range(args.warmup):
         step_e2e()
     ms_e2e = time_steps(step_e2e, args.steps, world)
