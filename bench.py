@@ -395,7 +395,8 @@ def main() -> int:
             torch.cuda.synchronize()
             trace("capturing")
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
+            # thread-local capture: the NCCL watchdog thread keeps making CUDA calls of its own
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
                 run_step()
         torch.cuda.synchronize()
         trace("captured")
@@ -491,8 +492,16 @@ def main() -> int:
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        # A captured graph that holds NCCL work keeps the communicator busy; tearing the
+        # process group down under it can block. Everything is reported: drop the graph,
+        # meet the other ranks once more and leave without the teardown.
         import torch.distributed as dist
-        dist.destroy_process_group()
+        del graph
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 
