@@ -340,6 +340,9 @@ def main() -> int:
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (1/0)")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the stack (32 = the model)")
+    ap.add_argument("--gather", choices=("push", "nccl"), default="push",
+                    help="N > 1: how the sharded MLP activation is recombined (push: peer stores "
+                         "from the GEMV epilogue; nccl: an all-gather call between the launches)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
     ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemm"),
                     help="stack: the benchmark; gemv / gemm: a few launches of one kernel on a "
@@ -368,7 +371,9 @@ def main() -> int:
         if os.environ.get("B200LUT_BENCH_TRACE"):
             print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
     trace("building the stack")
-    stack = st.LinearStack(device=f"cuda:{local}", rank=rank, world=world, n_layers=args.layers)
+    push = world > 1 and args.gather == "push" and M <= 16 and args.executor != "plan"
+    stack = st.LinearStack(device=f"cuda:{local}", rank=rank, world=world, n_layers=args.layers,
+                           gather="push" if push else "nccl")
     gather = make_gather(world, M)
     plan = stack._plan(M)
     x_host = torch.randn(M, st.HIDDEN, generator=torch.Generator().manual_seed(1)).to(stack.dtype).pin_memory()
@@ -430,6 +435,10 @@ def main() -> int:
         step_e2e()
     ms_e2e = time_steps(step_e2e, args.steps, world)
 
+    status = pkg._lib.lib().b200lut_device_status()
+    if status != 0:
+        raise RuntimeError(f"rank {rank}: a bounded device wait ran out (status {status:#x}); "
+                           "the timings are void")
     ms_step = ms / args.steps
     tok_s = M * 1e3 / ms_step
     launches = stack.launches_per_step(M)
@@ -442,7 +451,11 @@ def main() -> int:
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "qwen3.5-9b linear stack: 32 layers, 248 projections, "
                                "6912212992 4-bit weights, group 128, bf16 palettes",
-                   "batch": M, "parallelism": f"column-parallel x{world}, all-gather per layer",
+                   "batch": M,
+                   "parallelism": f"column-parallel x{world}, all-gather per layer" + (
+                       "" if world == 1 else
+                       " folded into the GEMV launches (peer stores over NVLink + flag wait)" if push
+                       else " (NCCL)"),
                    "l2": "inputs (3.46 GB of codes per step) exceed the 126 MB L2",
                    "launch": ("persistent cooperative launch per step (jobs chained by completion counters), "
                               "CUDA graph replay" if use_plan else

@@ -163,6 +163,64 @@ int b200lut_gemv_noalloc(const void* x, const void* packed, const void* lut, voi
                          int M, int N, int K, int bits, int group_size, int n_groups, int dtype,
                          int split, void* stream);
 
+/* ---- column-parallel exchange: the all-gather folded into the GEMV ---------------------
+ *
+ * On G GPUs of one box every rank owns N/G output rows of a projection; a consumer with a
+ * full-K input (down_proj after the SiLU*mul of gate/up) needs all ranks' slices. The
+ * reference has no multi-GPU path; the plain form of this step is an NCCL all-gather between
+ * two launches. The fused form removes that launch: the producing GEMV stores every output
+ * element into its own buffer AND, over NVLink, at the same position of every peer's buffer;
+ * every block of the grid then writes this rank's push count into its own flag word in every
+ * rank's flag array (one system-wide fence per block, no serialisation behind a last
+ * block); the consuming GEMV waits (bounded, about 20 ms; on expiry the launch carries on
+ * and b200lut_device_status() turns nonzero) until all world x producer_blocks flags have
+ * reached the number of waits done on the channel plus one, and only then reads its
+ * activation rows. With programmatic dependent launch the waiting launch does not wait for
+ * the previous grid to drain — the flags (its own rank's included) are its whole dependency,
+ * so its code prefetch and table build overlap the producer's tail and the NVLink latency.
+ *
+ * Contract: all ranks issue the same sequence of pushes and waits on the same exchange
+ * words; a buffer that is pushed into must not be pushed into again before every rank's
+ * consumer of the previous contents has finished (two or more layers with a buffer each
+ * give that for free, because a rank cannot get a step ahead of a peer's consumer).
+ * peer memory is only ever written with plain stores by this library's own kernels. */
+#define B200LUT_MAX_PEERS 8
+
+typedef struct b200lut_exchange {
+  int world, rank;        /* 1 <= world <= 8 */
+  int push;               /* nonzero: mirror outputs to the peers and signal them */
+  int wait;               /* nonzero: wait for all ranks' signals before reading x */
+  int producer_blocks;    /* blocks of the pushing launch (tiles x split: pass an explicit split,
+                             b200lut_gemv_pick_split gives the library's choice); the same on
+                             every rank; push: checked against the launch; wait: flags per rank */
+  int reserved;
+  int64_t peer_delta[B200LUT_MAX_PEERS];  /* bytes from a local output address to the same
+                                             element of rank q's buffer (entry `rank` unused) */
+  void* peer_flag[B200LUT_MAX_PEERS];     /* rank q's flag array u32[world][producer_blocks]
+                                             (entry `rank`: the local one) */
+  void* ticket;           /* local u32, zero before first use (push) */
+  void* epoch;            /* local u32, zero before first use: pushes done (push) */
+  const void* flags;      /* the local flag array, zero before first use (wait) */
+  void* wait_ticket;      /* local u32, zero before first use (wait) */
+  void* wait_count;       /* local u32, zero before first use: waits done (wait) */
+} b200lut_exchange;
+
+/* b200lut_gemv_multi with the exchange described above (ex == NULL: identical to it).
+ * No counterpart in the reference. */
+int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, int dtype,
+                          const b200lut_segment* segs, int nseg, int epilogue, int split,
+                          void* workspace, size_t workspace_bytes, int flags,
+                          const b200lut_exchange* ex, void* stream);
+
+/* Sharing a device buffer between the ranks (processes) of one box. export: fills a 64-byte
+ * handle for the allocation that contains ptr and the offset of ptr inside it (the buffer
+ * must come from cudaMalloc, directly or through a caching allocator). open: maps another
+ * process's allocation into this one (peer access over NVLink) and returns its base; close
+ * unmaps it. Handles travel between the processes by any host channel. */
+int b200lut_peer_export(const void* ptr, unsigned char handle[64], int64_t* offset);
+int b200lut_peer_open(const unsigned char handle[64], void** base);
+int b200lut_peer_close(void* base);
+
 /* One decode GEMV launch inside a persistent plan: what b200lut_gemv_multi takes, plus
  * the index of the earlier job that produces this job's activation rows (-1: none). */
 typedef struct b200lut_job {

@@ -27,6 +27,7 @@ EXPORTS = (
     "b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes",
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
+    "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
     "b200lut_gemv_noalloc", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
@@ -49,6 +50,21 @@ class Job(ctypes.Structure):
         ("x", ctypes.c_void_p), ("ldx", ctypes.c_int64),
         ("K", ctypes.c_int), ("nseg", ctypes.c_int), ("epilogue", ctypes.c_int),
         ("dep", ctypes.c_int), ("segs", Segment * 8),
+    ]
+
+
+MAX_PEERS = 8
+
+
+class Exchange(ctypes.Structure):
+    """struct b200lut_exchange."""
+    _fields_ = [
+        ("world", ctypes.c_int), ("rank", ctypes.c_int),
+        ("push", ctypes.c_int), ("wait", ctypes.c_int),
+        ("producer_blocks", ctypes.c_int), ("reserved", ctypes.c_int),
+        ("peer_delta", ctypes.c_int64 * MAX_PEERS), ("peer_flag", ctypes.c_void_p * MAX_PEERS),
+        ("ticket", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("flags", ctypes.c_void_p),
+        ("wait_ticket", ctypes.c_void_p), ("wait_count", ctypes.c_void_p),
     ]
 
 
@@ -92,6 +108,15 @@ def lib() -> ctypes.CDLL:
     L.b200lut_gemv_multi.restype = i32
     L.b200lut_gemv_multi.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32,
                                      i32, vp, sz, i32, vp]
+    L.b200lut_gemv_exchange.restype = i32
+    L.b200lut_gemv_exchange.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32,
+                                        i32, vp, sz, i32, ctypes.POINTER(Exchange), vp]
+    L.b200lut_peer_export.restype = i32
+    L.b200lut_peer_export.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(i64)]
+    L.b200lut_peer_open.restype = i32
+    L.b200lut_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+    L.b200lut_peer_close.restype = i32
+    L.b200lut_peer_close.argtypes = [vp]
     L.b200lut_gemv.restype = i32
     L.b200lut_gemv.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, sz, vp]
     L.b200lut_gemm.restype = i32
@@ -230,6 +255,41 @@ def gemv_multi(x: torch.Tensor, segs, nseg: int, epilogue: int = EPI_NONE, split
     with torch.cuda.device(x.device):
         check(lib().b200lut_gemv_multi(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), segs,
                                        nseg, epilogue, split, ws_ptr, ws_bytes, flags, _stream(x)))
+
+
+def gemv_pick_split(tiles: int, K: int) -> int:
+    return int(lib().b200lut_gemv_pick_split(tiles, K))
+
+
+def gemv_exchange(x: torch.Tensor, segs, nseg: int, ex: "Exchange", epilogue: int = EPI_NONE,
+                  split: int = 0, flags: int = 0) -> None:
+    """gemv_multi with the column-parallel exchange folded in (push after, wait before)."""
+    _need_cuda(x, "x")
+    M, K = x.shape
+    with torch.cuda.device(x.device):
+        check(lib().b200lut_gemv_exchange(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), segs,
+                                          nseg, epilogue, split, None, 0, flags,
+                                          ctypes.byref(ex), _stream(x)))
+
+
+def peer_export(t: torch.Tensor):
+    """(64-byte handle, offset) of the device allocation that holds tensor t."""
+    _need_cuda(t, "buffer")
+    handle = ctypes.create_string_buffer(64)
+    off = ctypes.c_int64(0)
+    with torch.cuda.device(t.device):
+        check(lib().b200lut_peer_export(t.data_ptr(), handle, ctypes.byref(off)))
+    return bytes(handle.raw), int(off.value)
+
+
+def peer_open(handle: bytes) -> int:
+    base = ctypes.c_void_p(0)
+    check(lib().b200lut_peer_open(ctypes.c_char_p(handle), ctypes.byref(base)))
+    return int(base.value)
+
+
+def peer_close(base: int) -> None:
+    check(lib().b200lut_peer_close(ctypes.c_void_p(base)))
 
 
 def gemm(x: torch.Tensor, seg, epilogue: int = EPI_NONE, flags: int = 0) -> None:

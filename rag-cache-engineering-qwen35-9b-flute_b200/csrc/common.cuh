@@ -89,4 +89,7 @@ template <> struct DType<__half> {
   __device__ static uint16_t from_float(float v) { return __half_as_ushort(__float2half_rn(v)); }
 };
 
+// Status word of the decode kernels' exchange waits (defined with the GEMV): value and clear.
+int exchange_status_take();
+
 }  // namespace b200lut

@@ -403,13 +403,15 @@ extern "C" int b200lut_gemm_timing(long long* out64) {
 }
 #endif
 
-// Device-side status of the tensor-core kernel on the current device (0 = none). A
-// non-zero value means a bounded wait ran out inside a kernel; cleared by this call.
+// Device-side status of the library's kernels on the current device (0 = none). A
+// non-zero value means a bounded wait ran out inside a kernel (tensor-core pipeline codes,
+// or 0x7000 + rank for an exchange wait on that rank's push); cleared by this call.
 extern "C" int b200lut_device_status(void) {
   int v = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
   if (v != 0) cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
-  return v;
+  const int e = b200lut::exchange_status_take();
+  return v != 0 ? v : e;
 }
 
 extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,

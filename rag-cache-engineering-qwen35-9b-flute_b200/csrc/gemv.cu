@@ -40,6 +40,8 @@ namespace cg = cooperative_groups;
 namespace b200lut {
 namespace {
 
+__device__ int g_exchange_status = 0;
+
 constexpr int kMaxSeg = 8;
 constexpr int kMaxM = 16;
 constexpr uint32_t kPartBytes = 2 * kMaxM * kTileRows * 4;  // two result planes (gate/up)
@@ -56,6 +58,21 @@ struct SegDev {
   int N, gs, n_groups, bits, bits2, tile_begin;
 };
 
+// Column-parallel exchange (see b200lut_exchange): where to mirror outputs, whom to signal,
+// what to wait for.
+struct ExchangeDev {
+  int world, rank, push, wait;
+  int blocks;           // blocks of the producing grid = flags per rank
+  long long delta[B200LUT_MAX_PEERS];
+  uint32_t* peer_flag[B200LUT_MAX_PEERS];
+  uint32_t* ticket;
+  uint32_t* epoch;
+  const uint32_t* flags;
+  uint32_t* wait_ticket;
+  uint32_t* wait_count;
+  int* status;          // device status word of the library (set when a wait runs out)
+};
+
 struct GemvParams {
   const uint16_t* x;
   long long ldx;
@@ -63,6 +80,7 @@ struct GemvParams {
   float* ws;       // workspace fold: [split][tiles_total][planes][M][128] fp32
   int* tickets;    // workspace fold: [tiles_total]
   SegDev seg[kMaxSeg];
+  ExchangeDev ex;
 };
 
 template <typename T>
@@ -120,6 +138,7 @@ struct DepWait {
   const int* counter;       // mode 2: tiles of the producer finished so far
   int target;               // mode 2: proceed when *counter >= target
   int* abort_word;          // mode 2: global word set when any block gave up waiting
+  const ExchangeDev* ex;    // mode 1: also wait for the peers' pushes (null: no exchange)
 };
 
 constexpr long long kDepWaitCycles = 40000000;   // ~20 ms: far beyond any healthy wait
@@ -143,6 +162,31 @@ __device__ __forceinline__ void dep_poll(const DepWait& dep) {
     }
   }
   atomicExch(dep.abort_word, 1);
+}
+
+// Bounded wait for one block of one rank's push: its flag (written over NVLink by that
+// block of that rank's producer) must have reached the number of waits this rank has completed on the channel, plus one (that
+// count is bumped by the last block of the waiting grid, after every block has read it).
+// On expiry the status word is set and the launch
+// carries on, so the context stays usable and the host can see what happened.
+__device__ __forceinline__ void peer_poll(const ExchangeDev& ex, int idx) {
+  const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(ex.wait_count) + 1u;
+  const uint32_t* f = ex.flags + idx;
+  auto arrived = [&]() {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    return int(v - want) >= 0;
+  };
+  if (arrived()) return;
+  const long long t0 = clock64();
+  for (uint32_t i = 1;; ++i) {
+    if (arrived()) return;
+    if ((i & 15u) == 0u) {
+      if (*reinterpret_cast<volatile int*>(ex.status) != 0) return;
+      if (clock64() - t0 > kDepWaitCycles) break;
+    }
+  }
+  atomicExch(ex.status, 0x7000 + idx / ex.blocks);
 }
 
 // Batch-column plan. The n8 columns of the m16n8k16 accumulator are shared between
@@ -248,7 +292,16 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
   __syncthreads();
   if (dep.mode == 1) {
     // everything above is independent of the previous kernel in the stream
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (dep.ex) {   // block-uniform
+      // The activation rows come from this and the other ranks' producers: their flags are
+      // the whole dependency (they also order this rank's own slice), so the launch does
+      // not wait for the previous grid to drain.
+      for (int i = int(threadIdx.x); i < dep.ex->world * dep.ex->blocks; i += int(blockDim.x))
+        peer_poll(*dep.ex, i);
+      __syncthreads();
+    } else {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
   }
 
   float acc[P::kAcc][4];
@@ -333,7 +386,14 @@ __device__ __forceinline__ void fold_and_store(const GemvParams& p, float* part,
       if (s1.bias) b += DType<T>::to_float(s1.bias[n]);
       v = a / (1.f + __expf(-a)) * b;
     }
-    s0.out[size_t(m) * s0.ldo + n] = DType<T>::from_float(v);
+    uint16_t* dst = s0.out + size_t(m) * s0.ldo + n;
+    const uint16_t bits16 = DType<T>::from_float(v);
+    *dst = bits16;
+    if (p.ex.push) {   // the same element of every peer's buffer, over NVLink
+      for (int q = 0; q < p.ex.world; ++q)
+        if (q != p.ex.rank)
+          *reinterpret_cast<uint16_t*>(reinterpret_cast<char*>(dst) + p.ex.delta[q]) = bits16;
+    }
   };
 
   if (split == 1) {
@@ -442,7 +502,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
 #define B200LUT_PASS(B)                                                                       \
   stream_pass<T, B, CP, NWARPS, RC>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups,  \
                                     sg.gs, tile, p.G, c0, c1, p.x, p.ldx, M, !first,              \
-                                    DepWait{first ? 1 : 0, nullptr, 0, nullptr})
+                                    DepWait{first ? 1 : 0, nullptr, 0, nullptr, (first && p.ex.wait) ? &p.ex : nullptr})
       switch (bits) {   // block-uniform
         case 4: B200LUT_PASS(4); break;
         case 3: B200LUT_PASS(3); break;
@@ -454,6 +514,41 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
     }
   }
   fold_and_store<T, NT>(p, part, si, tile, tile_g, sp);
+
+  if (p.ex.wait) {
+    // The last block of a waiting grid counts the wait as done (every block read the count
+    // when it polled, before it came here).
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t old = atomicAdd(p.ex.wait_ticket, 1u);
+      if (old == gridDim.x - 1) {
+        *reinterpret_cast<volatile uint32_t*>(p.ex.wait_ticket) = 0u;
+        *reinterpret_cast<volatile uint32_t*>(p.ex.wait_count) += 1u;
+      }
+    }
+  }
+  if (p.ex.push) {
+    // Every block signals for itself: the barrier orders its threads' (remote) stores before
+    // thread 0, whose single system-wide fence makes them visible everywhere before it writes
+    // this block's flag into every rank's flag array. System-wide fences are slow (several
+    // microseconds), so there is exactly one per block, all blocks pay it in parallel, and
+    // nothing is serialised behind a last block. The ticket only maintains the push count
+    // for the next launch and is off the peers' critical path.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t e = *reinterpret_cast<volatile uint32_t*>(p.ex.epoch) + 1u;
+      __threadfence_system();
+      const uint32_t slot = uint32_t(p.ex.rank) * gridDim.x + blockIdx.x;
+      for (int q = 0; q < p.ex.world; ++q)
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.ex.peer_flag[q] + slot), "r"(e)
+                     : "memory");
+      const uint32_t old = atomicAdd(p.ex.ticket, 1u);
+      if (old == gridDim.x - 1) {   // every block has read the count by now
+        *reinterpret_cast<volatile uint32_t*>(p.ex.ticket) = 0u;
+        *reinterpret_cast<volatile uint32_t*>(p.ex.epoch) = e;
+      }
+    }
+  }
 }
 
 constexpr int kWarpsM8 = 16, kWarpsM16 = 8;
@@ -636,10 +731,83 @@ extern "C" size_t b200lut_gemv_workspace_bytes(int total_rows, int M, int split)
   return size_t(split) * tiles * 2 * size_t(M) * kTileRows * 4 + tiles * 4;
 }
 
+namespace b200lut {
+int exchange_status_take() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_exchange_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_exchange_status, &zero, sizeof(int));
+  return v;
+}
+}  // namespace b200lut
+
+namespace {
+
+// Validate an exchange descriptor and turn it into the device form.
+int convert_exchange(const b200lut_exchange* ex, ExchangeDev* out) {
+  *out = ExchangeDev{};
+  if (!ex || (!ex->push && !ex->wait)) return B200LUT_OK;
+  B200LUT_REQUIRE(ex->world >= 1 && ex->world <= B200LUT_MAX_PEERS && ex->rank >= 0 &&
+                      ex->rank < ex->world,
+                  B200LUT_ERR_INVALID, "exchange: world must be 1..%d and rank inside it (got %d, %d)",
+                  B200LUT_MAX_PEERS, ex->world, ex->rank);
+  B200LUT_REQUIRE(ex->producer_blocks >= 1 && ex->producer_blocks <= 4096, B200LUT_ERR_INVALID,
+                  "exchange: producer_blocks must be 1..4096, got %d", ex->producer_blocks);
+  out->world = ex->world;
+  out->rank = ex->rank;
+  out->blocks = ex->producer_blocks;
+  if (ex->push) {
+    B200LUT_REQUIRE(ex->ticket && ex->epoch && ((uintptr_t(ex->ticket) | uintptr_t(ex->epoch)) & 3) == 0,
+                    B200LUT_ERR_INVALID, "exchange: push needs its ticket and count words");
+    out->epoch = static_cast<uint32_t*>(ex->epoch);
+    for (int q = 0; q < ex->world; ++q) {
+      B200LUT_REQUIRE(ex->peer_flag[q] && (uintptr_t(ex->peer_flag[q]) & 3) == 0,
+                      B200LUT_ERR_INVALID, "exchange: null or misaligned flag of rank %d", q);
+      B200LUT_REQUIRE(ex->peer_delta[q] % 2 == 0, B200LUT_ERR_ALIGN,
+                      "exchange: odd buffer offset to rank %d", q);
+      out->delta[q] = ex->peer_delta[q];
+      out->peer_flag[q] = static_cast<uint32_t*>(ex->peer_flag[q]);
+    }
+    out->ticket = static_cast<uint32_t*>(ex->ticket);
+    out->push = 1;
+  }
+  if (ex->wait) {
+    B200LUT_REQUIRE(ex->flags && (uintptr_t(ex->flags) & 3) == 0, B200LUT_ERR_INVALID,
+                    "exchange: wait needs the local flag array");
+    B200LUT_REQUIRE(ex->wait_ticket && ex->wait_count &&
+                        ((uintptr_t(ex->wait_ticket) | uintptr_t(ex->wait_count)) & 3) == 0,
+                    B200LUT_ERR_INVALID, "exchange: wait needs its ticket and count words");
+    out->flags = static_cast<const uint32_t*>(ex->flags);
+    out->wait_ticket = static_cast<uint32_t*>(ex->wait_ticket);
+    out->wait_count = static_cast<uint32_t*>(ex->wait_count);
+    out->wait = 1;
+  }
+  static int* status_addr[64] = {nullptr};
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  B200LUT_REQUIRE(dev < 64, B200LUT_ERR_UNSUPPORTED, "device index %d not served", dev);
+  if (!status_addr[dev]) {
+    void* a = nullptr;
+    B200LUT_CUDA_OK(cudaGetSymbolAddress(&a, g_exchange_status));
+    status_addr[dev] = static_cast<int*>(a);
+  }
+  out->status = status_addr[dev];
+  return B200LUT_OK;
+}
+
+}  // namespace
+
 extern "C" int b200lut_gemv_multi(const void* x, int64_t ldx, int M, int K, int dtype,
                                   const b200lut_segment* segs, int nseg, int epilogue, int split,
                                   void* workspace, size_t workspace_bytes, int flags,
                                   void* stream) {
+  return b200lut_gemv_exchange(x, ldx, M, K, dtype, segs, nseg, epilogue, split, workspace,
+                               workspace_bytes, flags, nullptr, stream);
+}
+
+extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, int dtype,
+                                     const b200lut_segment* segs, int nseg, int epilogue,
+                                     int split, void* workspace, size_t workspace_bytes, int flags,
+                                     const b200lut_exchange* ex, void* stream) {
   B200LUT_REQUIRE(x && segs, B200LUT_ERR_INVALID, "null x or segment table");
   B200LUT_REQUIRE(M >= 1 && M <= kMaxM, B200LUT_ERR_UNSUPPORTED,
                   "decode GEMV serves 1 <= M <= 16, got M=%d (use b200lut_gemm)", M);
@@ -665,6 +833,7 @@ extern "C" int b200lut_gemv_multi(const void* x, int64_t ldx, int M, int K, int 
   p.G = K / kChunkK;
   p.nseg = nseg;
   p.epilogue = epilogue;
+  if (int rc = convert_exchange(ex, &p.ex)) return rc;
   int tiles = 0, max_tables = 1;
   if (int rc = convert_segments(segs, nseg, silu, p.seg, &tiles, &max_tables)) return rc;
   p.tiles_total = tiles;
@@ -684,6 +853,9 @@ extern "C" int b200lut_gemv_multi(const void* x, int64_t ldx, int M, int K, int 
     p.tickets = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) +
                                        size_t(split) * tiles * 2 * size_t(M) * kTileRows * 4);
   }
+  B200LUT_REQUIRE(!p.ex.push || p.ex.blocks == tiles * split, B200LUT_ERR_INVALID,
+                  "exchange: producer_blocks is %d but this launch has %d tiles x split %d blocks",
+                  p.ex.blocks, tiles, split);
   const bool pdl = (flags & 1) != 0;
   cudaStream_t st = cudaStream_t(stream);
   if (dtype == B200LUT_BF16) return dispatch<__nv_bfloat16>(p, max_tables, pdl, st);

@@ -16,7 +16,9 @@ activation rows x [M, 4096]; the MLP chain gate/up -> SiLU*mul -> down is real.
 Column-parallel sharding: rank r of G owns output rows [r*N/G, (r+1)*N/G) of every
 projection (contiguous bytes in the tile-major code buffer). Sharded outputs that
 feed a full-K consumer are recombined with an all-gather (the MLP's SiLU*mul
-output before down_proj, and the layer outputs).
+output before down_proj): either an NCCL call between the two launches, or — decode,
+`gather="push"` — folded into them (exchange.py: the gate/up launch stores its slice
+into every rank's buffer over NVLink, the down launch waits for the flags).
 """
 from __future__ import annotations
 
@@ -25,7 +27,7 @@ from typing import List, Optional
 import torch
 import torch.nn as nn
 
-from . import _lib, synthetic
+from . import _lib, exchange, synthetic
 from .palettized_modules import FusedPalettizedMLP, PalettizedLinear, SplitQKV
 
 HIDDEN = 4096
@@ -101,8 +103,15 @@ class LinearStack(nn.Module):
 
     def __init__(self, device="cuda", dtype=torch.bfloat16, bits: int = 4, group_size: int = 128,
                  n_layers: int = N_LAYERS, seed: int = synthetic.BASE_SEED + 5,
-                 rank: int = 0, world: int = 1):
+                 rank: int = 0, world: int = 1, gather: str = "nccl", arenas=None):
         super().__init__()
+        if gather not in ("nccl", "push"):
+            raise ValueError(f"gather must be 'nccl' or 'push', got {gather!r}")
+        if gather == "push" and world > 1 and n_layers < 2:
+            # with one buffer a peer's next push could overtake this rank's reader
+            raise ValueError("gather='push' needs at least two layers")
+        self.gather_mode = gather if world > 1 else "nccl"
+        self._arenas = arenas        # test form: pre-built emulated arenas (this rank's one)
         self.device, self.dtype = torch.device(device), dtype
         self.bits, self.group_size = bits, group_size
         self.rank, self.world = rank, world
@@ -164,6 +173,13 @@ class LinearStack(nn.Module):
         x = torch.zeros(M, HIDDEN, dtype=dt, device=dev)
         launches = []
         outs = []
+        push = self.gather_mode == "push" and M <= 16
+        arena = None
+        if push:
+            width = self.layers[0].mlp.gate_proj.N * self.world
+            need = len(self.layers) * (((M * width * 2 + 255) // 256 + 2) * 256 + self.world * 4096 * 4)
+            arena = self._arenas if self._arenas is not None else exchange.PeerArena(
+                need, self.rank, self.world, dev)
         for L in self.layers:
             heads = L.heads()
             total = sum(m.N for m in heads)
@@ -172,39 +188,50 @@ class LinearStack(nn.Module):
             for m in heads:
                 descs.append(m._segment_desc(hbuf[:, off:], ldo=total))
                 off += m.N
-            launches.append(("heads", x, _lib.make_segments(descs), len(descs), _lib.EPI_NONE, descs))
+            launches.append(("heads", x, _lib.make_segments(descs), len(descs), _lib.EPI_NONE, descs, None))
             o = L.out()
             obuf = torch.empty(M, o.N, dtype=dt, device=dev)
             od = [o._segment_desc(obuf)]
-            launches.append(("out", x, _lib.make_segments(od), 1, _lib.EPI_NONE, od))
+            launches.append(("out", x, _lib.make_segments(od), 1, _lib.EPI_NONE, od, None))
             g, u, d = L.mlp.gate_proj, L.mlp.up_proj, L.mlp.down_proj
-            act = torch.empty(M, g.N * self.world, dtype=dt, device=dev)   # full width after gather
-            act_loc = act[:, self.rank * g.N:(self.rank + 1) * g.N]
+            chan = exchange.Channel(arena, M, g.N * self.world, dt, g.N // 128, g.K) if push else None
+            act = chan.act if push else torch.empty(M, g.N * self.world, dtype=dt, device=dev)
+            act_loc = act[:, self.rank * g.N:(self.rank + 1) * g.N]   # full width after gather
             gd = [g._segment_desc(act_loc, ldo=act.shape[1]), u._segment_desc(None)]
-            launches.append(("gate_up", x, _lib.make_segments(gd), 2, _lib.EPI_SILU_MUL, gd))
-            if self.world > 1:
-                launches.append(("gather", act, act_loc, None, None, None))
+            launches.append(("gate_up", x, _lib.make_segments(gd), 2, _lib.EPI_SILU_MUL, gd,
+                             chan.push if push else None))
+            if self.world > 1 and not push:
+                launches.append(("gather", act, act_loc, None, None, None, None))
             ybuf = torch.empty(M, d.N, dtype=dt, device=dev)
             dd = [d._segment_desc(ybuf)]
-            launches.append(("down", act, _lib.make_segments(dd), 1, _lib.EPI_NONE, dd))
+            launches.append(("down", act, _lib.make_segments(dd), 1, _lib.EPI_NONE, dd,
+                             chan.wait if push else None))
             outs += [hbuf, obuf, act, ybuf]
-        plan = {"x": x, "launches": launches, "buffers": outs, "y": outs[-1]}
+        plan = {"x": x, "launches": launches, "buffers": outs, "y": outs[-1], "arena": arena}
         self._plans[M] = plan
         return plan
+
+    def run_launch(self, entry, M: int, flags: int = 0, gather=None) -> None:
+        """Issue one entry of the plan's launch list on the current stream."""
+        name, xin, segs, nseg, epi, _, ex = entry
+        if name == "gather":
+            gather(xin, segs)
+        elif ex is not None:
+            # the pushing launch runs with the split its flag array was sized for
+            split = ex.producer_blocks // (segs[0].N // 128) if ex.push else 0
+            _lib.gemv_exchange(xin, segs, nseg, ex, epilogue=epi, split=split, flags=flags)
+        elif M <= 16:
+            _lib.gemv_multi(xin, segs, nseg, epilogue=epi, flags=flags)
+        else:
+            for i in range(0, nseg, 2 if epi == _lib.EPI_SILU_MUL else 1):
+                _lib.gemm(xin, _pair(segs, i, epi), epilogue=epi, flags=flags)
 
     def step(self, M: int, flags: int = 0, gather=None) -> torch.Tensor:
         """Run every projection once on the plan's activation buffer; returns the
         last layer's down_proj output (this rank's columns)."""
         plan = self._plan(M)
-        for name, xin, segs, nseg, epi, _ in plan["launches"]:
-            if name == "gather":
-                gather(xin, segs)
-                continue
-            if M <= 16:
-                _lib.gemv_multi(xin, segs, nseg, epilogue=epi, flags=flags)
-            else:
-                for i in range(0, nseg, 2 if epi == _lib.EPI_SILU_MUL else 1):
-                    _lib.gemm(xin, _pair(segs, i, epi), epilogue=epi, flags=flags)
+        for entry in plan["launches"]:
+            self.run_launch(entry, M, flags, gather)
         return plan["y"]
 
     def decode_plans(self, M: int):
@@ -214,7 +241,7 @@ class LinearStack(nn.Module):
         plan = self._plan(M)
         if "plans" not in plan:
             groups, cur = [], []
-            for name, xin, segs, nseg, epi, descs in plan["launches"]:
+            for name, xin, segs, nseg, epi, descs, _ in plan["launches"]:
                 if name == "gather":
                     groups.append(("plan", cur))
                     groups.append(("gather", (xin, segs)))
@@ -236,7 +263,7 @@ class LinearStack(nn.Module):
 
     def launches_per_step(self, M: int) -> int:
         n = 0
-        for name, _, _, nseg, epi, _ in self._plan(M)["launches"]:
+        for name, _, _, nseg, epi, _, _ in self._plan(M)["launches"]:
             if name == "gather":
                 continue
             n += 1 if M <= 16 else (nseg // 2 if epi == _lib.EPI_SILU_MUL else nseg)

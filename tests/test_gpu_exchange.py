@@ -1,0 +1,121 @@
+"""Column-parallel exchange folded into the decode GEMV (push all-gather).
+
+Single GPU: two "ranks" live on one device, each with its own arena; their launches are
+issued in the order gate_up(0), gate_up(1), down(0), down(1), ..., so every flag a launch
+waits for has been raised by a launch that completed before it started (nothing waits on
+a later launch). The recombined activation and the outputs must equal, bit for bit, a
+manual gather of the same shards, and match the unsharded stack within the output
+tolerance. Two GPUs (skipped on fewer): the same through real peer mappings, one process
+per GPU, against the NCCL all-gather.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import pytest
+import torch
+
+from helpers import TOL, pkg, rel_err
+
+pytestmark = pytest.mark.gpu
+stack_mod = __import__("importlib").import_module(pkg.__name__ + ".stack")
+exchange = __import__("importlib").import_module(pkg.__name__ + ".exchange")
+
+
+def _emulated_step(stacks, M, x):
+    plans = [s._plan(M) for s in stacks]
+    for p in plans:
+        p["x"].copy_(x)
+    for entries in zip(*[p["launches"] for p in plans]):
+        for s, e in zip(stacks, entries):
+            s.run_launch(e, M)
+    torch.cuda.synchronize()
+    return plans
+
+
+@pytest.mark.parametrize("M", (1, 5))
+def test_emulated_two_rank_push_equals_manual_gather(M):
+    world, layers = 2, 2
+    arenas = exchange.PeerArena.emulated(1 << 20, world, "cuda")
+    pushed = [stack_mod.LinearStack(n_layers=layers, rank=r, world=world, gather="push",
+                                    arenas=arenas[r]) for r in range(world)]
+    manual = [stack_mod.LinearStack(n_layers=layers, rank=r, world=world, gather="nccl")
+              for r in range(world)]
+    x = torch.randn(M, stack_mod.HIDDEN, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
+
+    for rep in range(3):      # the flags and tickets must be reusable step after step
+        plans = _emulated_step(pushed, M, x)
+        assert pkg._lib.lib().b200lut_device_status() == 0
+
+        # manual gather: run both shards launch by launch, copying slices at the gather entries
+        mplans = [s._plan(M) for s in manual]
+        for p in mplans:
+            p["x"].copy_(x)
+        for entries in zip(*[p["launches"] for p in mplans]):
+            if entries[0][0] == "gather":
+                for r, e in enumerate(entries):
+                    n = e[2].shape[1]
+                    for q in range(world):
+                        if q != r:
+                            entries[q][1][:, r * n:(r + 1) * n].copy_(e[2])
+                continue
+            for s, e in zip(manual, entries):
+                s.run_launch(e, M)
+        torch.cuda.synchronize()
+        for r in range(world):
+            for got, want in zip(plans[r]["buffers"], mplans[r]["buffers"]):
+                assert torch.equal(got, want), f"rank {r}, repetition {rep}"
+
+    full = stack_mod.LinearStack(n_layers=layers)
+    fp = full._plan(M)
+    fp["x"].copy_(x)
+    y = full.step(M)
+    torch.cuda.synchronize()
+    n = y.shape[1] // world
+    for r in range(world):
+        assert rel_err(plans[r]["y"].float().cpu(), y[:, r * n:(r + 1) * n].float().cpu()) <= TOL
+
+
+def test_push_needs_two_layers():
+    with pytest.raises(ValueError):
+        stack_mod.LinearStack(n_layers=1, rank=0, world=2, gather="push")
+
+
+def _two_gpu_worker(rank, world, port, ok):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    M, layers = 1, 3
+    a = stack_mod.LinearStack(device=f"cuda:{rank}", n_layers=layers, rank=rank, world=world, gather="push")
+    b = stack_mod.LinearStack(device=f"cuda:{rank}", n_layers=layers, rank=rank, world=world, gather="nccl")
+    x = torch.randn(M, stack_mod.HIDDEN, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
+
+    def gather(full, local):
+        parts = [torch.empty_like(local.contiguous()) for _ in range(world)]
+        dist.all_gather(parts, local.contiguous())
+        full.copy_(torch.cat(parts, dim=1))
+    same = True
+    for _ in range(4):
+        a._plan(M)["x"].copy_(x)
+        b._plan(M)["x"].copy_(x)
+        ya = a.step(M, flags=pkg._lib.FLAG_PDL)
+        yb = b.step(M, gather=gather)
+        torch.cuda.synchronize()
+        same = same and all(torch.equal(p, q) for p, q in zip(a._plan(M)["buffers"], b._plan(M)["buffers"]))
+        same = same and torch.equal(ya, yb)
+    same = same and pkg._lib.lib().b200lut_device_status() == 0
+    dist.barrier()
+    ok[rank] = 1 if same else 0
+    a._plan(M)["arena"].close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs of one box")
+def test_two_gpu_push_equals_nccl_gather():
+    import torch.multiprocessing as mp
+    world = 2
+    ok = mp.get_context("spawn").Array("i", [0] * world)
+    mp.spawn(_two_gpu_worker, args=(world, 29531, ok), nprocs=world, join=True)
+    assert list(ok) == [1] * world

@@ -65,6 +65,35 @@ def test_validation_errors_carry_a_message():
     assert rc == 1 and b"block" in L.b200lut_last_error()
 
 
+def test_exchange_descriptor_is_validated_before_any_launch():
+    L = pkg._lib.lib()
+    buf = ctypes.create_string_buffer(256)
+    a = (ctypes.addressof(buf) + 15) & ~15
+    seg = pkg._lib.Segment()
+    seg.packed = seg.lut = seg.out = a
+    seg.N, seg.group_size, seg.n_groups, seg.bits, seg.ldo = 128, 128, 1, 4, 128
+    ex = pkg._lib.Exchange()
+    ex.world, ex.rank, ex.push, ex.producer_blocks = 9, 0, 1, 1
+    call = lambda: L.b200lut_gemv_exchange(a, 64, 1, 64, 0, ctypes.byref(seg), 1, 0, 0, None, 0, 0,
+                                           ctypes.byref(ex), None)
+    assert call() == 1 and b"world" in L.b200lut_last_error()
+    ex.world, ex.rank = 2, 2
+    assert call() == 1 and b"rank" in L.b200lut_last_error()
+    ex.rank, ex.producer_blocks = 1, 0
+    assert call() == 1 and b"producer_blocks" in L.b200lut_last_error()
+    ex.producer_blocks = 3
+    assert call() == 1 and b"ticket and count" in L.b200lut_last_error()
+    ex.ticket, ex.epoch = a + 64, a + 96
+    assert call() == 1 and b"flag of rank 0" in L.b200lut_last_error()
+    ex.push, ex.wait = 0, 1
+    assert call() == 1 and b"flag array" in L.b200lut_last_error()
+    ex.flags = a
+    assert call() == 1 and b"wait needs its ticket" in L.b200lut_last_error()
+    assert L.b200lut_peer_export(None, None, None) == 1
+    assert L.b200lut_peer_open(None, None) == 1
+    assert L.b200lut_peer_close(None) == 1
+
+
 def test_workspace_query():
     L = pkg._lib.lib()
     assert L.b200lut_gemv_workspace_bytes(4096, 1, 8) == 0        # cluster fold: no scratch
