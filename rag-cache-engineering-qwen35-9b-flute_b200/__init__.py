@@ -8,6 +8,10 @@ the library; the first compute call does, and fails loudly if it is not built.
 from . import _lib, fht, idxN, synthetic                                    # noqa: F401
 from .palettized_modules import (FusedPalettizedMLP, PalettizedLinear, SplitQKV,  # noqa: F401
                                  reference_dequant, set_programmatic_launch)
+from .artifacts import (load_metadata, load_palettized_weight,                     # noqa: F401
+                        replace_linear_with_palettized)
+from .loader import load_quant_model                                             # noqa: F401
 
-__all__ = ["PalettizedLinear", "SplitQKV", "FusedPalettizedMLP", "reference_dequant",
+__all__ = ["load_quant_model", "load_palettized_weight", "replace_linear_with_palettized",
+           "load_metadata", "PalettizedLinear", "SplitQKV", "FusedPalettizedMLP", "reference_dequant",
            "set_programmatic_launch", "fht", "idxN", "synthetic"]
