@@ -345,6 +345,346 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Persistent form for one code stream (no second plane): a block walks a contiguous range of
+// (row tile, token tile) output tiles of 128 x 256 and never tears its pipeline down.
+// Measured on B200: a tcgen05.mma with the A operand in tensor memory costs the issuing
+// thread about 70 cycles whatever N is, and 128 cycles of tensor pipe at N = 256, so N = 256
+// is the only efficient tile width; the accumulator then fills 256 of the 512 TMEM columns and
+// cannot be double-buffered next to the operand stages. What the persistent form removes is
+// everything around the main loop: no block launch, TMEM allocation or barrier set-up per
+// tile, the pair table is rebuilt only when the row tile changes, and while eight dedicated
+// epilogue warps drain tile i (tcgen05.ld -> bias -> one rounding -> staged, 16-byte global
+// stores) the lookup warps and the TMA producer already refill all operand stages of tile
+// i + 1, so its MMAs start the moment the accumulator is free.
+// Per k-block the lookup warps (codes -> pair lookups -> tcgen05.st) and the TMA producer
+// arrive on ONE "full" barrier; the MMA issuer — a single thread, its loop flat over the
+// block's k-blocks and unrolled by the ring size: one barrier test, one fence, one four-MMA
+// instruction group, one commit — commits to one "done" barrier that frees the stage.
+// Warps 0-7 lookup, 8 TMA producer, 9 MMA issuer, 10-17 epilogue.
+constexpr int kPEpiWarps = 8;
+constexpr int kPThreads = (kLookupWarps + 2 + kPEpiWarps) * 32;
+constexpr int kPMaxNT = 256;
+constexpr int kPStages = 4;             // ring depth of both operands
+constexpr uint32_t kPACol = 256;        // operand stage s at columns [256 + 32 s, 288 + 32 s)
+constexpr int kPStageTokens = 48;       // tokens per staged epilogue slice (12 KB per column half)
+
+struct PersistParams {
+  const uint8_t* packed;
+  const uint16_t* lut;
+  const uint16_t* bias;
+  uint16_t* out;
+  long long ldo;
+  int M, N, K, G, gs, n_groups;
+  int NT;            // token tile (multiple of 32, <= 256)
+  int m_tiles;       // token tiles per row tile
+  int n_tiles;       // row tiles
+  int W;             // token columns of a row of tiles (the last tile rounded up to 32)
+  uint32_t smem_bytes;
+  int out_aligned;
+  int debug;
+};
+
+// First tile of block b when the tile list is cut into gridDim.x ranges of equal cost
+// (cost of a tile = its token columns).
+__device__ __forceinline__ int persist_first_tile(const PersistParams& p, long long b, long long nb) {
+  const long long total = (long long)p.n_tiles * p.W;
+  const long long target = b * total / nb;
+  long long r = target / p.W;
+  const long long rem = target - r * p.W;
+  long long j = (rem + p.NT - 1) / p.NT;
+  if (j >= p.m_tiles) { ++r; j = 0; }
+  return int(r * p.m_tiles + j);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kPThreads, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const PersistParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef B200LUT_GEMM_TIMING
+#define PT_DECL long long pt_acc[4] = {0, 0, 0, 0}; const long long pt_start = clock64(); long long pt_t0 = 0;
+#define PT_BEGIN pt_t0 = clock64();
+#define PT_END(k) pt_acc[k] += clock64() - pt_t0;
+#define PT_STORE(slot) if (blockIdx.x == 0 && lane == 0) { for (int z = 0; z < 4; ++z) g_gemm_timing[slot + z] = pt_acc[z]; g_gemm_timing[slot + 4] = clock64() - pt_start; }
+#else
+#define PT_DECL
+#define PT_BEGIN
+#define PT_END(k)
+#define PT_STORE(slot)
+#endif
+  PT_DECL
+  const uint32_t base = smem_u32(smem);
+  const uint32_t bar_full = base, bar_done = base + 64, bar_dfull = base + 128,
+                 bar_dempty = base + 144;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + 264);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 268);
+
+  int nl = kTileRows / p.gs;
+  if (nl < 1) nl = 1;
+  const uint32_t tbl_addr = (base + kCtrlBytes + 0xFFFFu) & ~0xFFFFu;
+  uint8_t* tbl_ptr = smem + (tbl_addr - base);
+  const uint32_t stage_bytes = uint32_t(p.NT) * 128u;
+  // below the table: control block, the epilogue's two staging slices, one activation stage;
+  // above it: three more
+  uint16_t* stage_out = reinterpret_cast<uint16_t*>(smem + kCtrlBytes);   // 2 x [token][128 rows]
+  const uint32_t xlow = (base + kCtrlBytes + 2u * kPStageTokens * 256u + 1023u) & ~1023u;
+  const uint32_t xhigh = tbl_addr + kTableBytes;
+  auto xstage = [&](int s) { return s < 1 ? xlow : xhigh + uint32_t(s - 1) * stage_bytes; };
+  const bool fits = xhigh + (kPStages - 1) * stage_bytes <= base + p.smem_bytes &&
+                    xlow + stage_bytes <= tbl_addr;
+
+  const int t0 = persist_first_tile(p, blockIdx.x, gridDim.x);
+  const int t1 = persist_first_tile(p, blockIdx.x + 1, gridDim.x);
+  const int ntile = t1 - t0;
+  const int G = p.G;
+
+  asm volatile("griddepcontrol.launch_dependents;");
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPStages; ++s) {
+      tc::mbar_init(bar_full + 8 * s, 5);    // four lookup warps + the TMA producer (and its bytes)
+      tc::mbar_init(bar_done + 8 * s, 1);    // tcgen05.commit of the k-block that used the stage
+    }
+    tc::mbar_init(bar_dfull, 1);              // tcgen05.commit: the tile's last MMA
+    tc::mbar_init(bar_dempty, kPEpiWarps);    // the epilogue warps have read the accumulator
+    *abort_flag = fits ? 0 : 1;
+    if (!fits) atomicCAS(&g_gemm_status, tc::kStatusOk, tc::kStatusWaitLoad);
+    tc::mbar_init_fence();
+  }
+  if (warp == kLookupWarps) tc::tmem_alloc(base + 264, kTmemCols);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp < kLookupWarps) {
+    // ---- lookup warps ---------------------------------------------------------------------------
+    const int q = warp & 3, grp = warp >> 2;
+    // this warp's k-blocks are the global iterations grp, grp + 2, ... of the block's flat
+    // (tile, k-block) sequence; `load` runs kRing of them ahead of `use`
+    const int iters = ntile * G;
+    int lt = 0, lc = grp;            // load cursor: tile offset, k-block
+    auto code_ptr = [&](int t, int c) -> const uint8_t* {
+      const int row = (t0 + t) / p.m_tiles;
+      return p.packed + (size_t(row) * G + c) * 4096 + q * 1024 + lane * 32;
+    };
+    auto advance = [&](int& t, int& c) {
+      c += 2;
+      while (c >= G) { c -= G; ++t; }
+    };
+    while (lc >= G) { lc -= G; ++lt; }
+    uint32_t w[kRing][8];
+#pragma unroll
+    for (int u = 0; u < kRing; ++u) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[u][i] = 0u;
+      const bool on = lt < ntile;
+      ldg_stream256_if(w[u], code_ptr(on ? lt : 0, on ? lc : 0), on ? 1u : 0u);
+      advance(lt, lc);
+    }
+    int ut = 0, uc = grp;            // use cursor
+    while (uc >= G) { uc -= G; ++ut; }
+    int table_row = -1, table_tile = -1;
+    uint32_t lane_base = 0;
+    for (int it = grp; it < iters; it += 2 * kRing) {
+#pragma unroll
+      for (int u = 0; u < kRing; ++u) {
+        if (it + 2 * u < iters) {     // warp-uniform
+          if (ut != table_tile) {
+            // a new tile: all eight lookup warps pass here once per tile (block-uniform), and
+            // rebuild the pair table together when the row tile has changed
+            const int row = (t0 + ut) / p.m_tiles;
+            if (row != table_row) {
+              PT_BEGIN
+              asm volatile("bar.sync 1, %0;" ::"r"(kLookupWarps * 32) : "memory");
+              build_tables(tbl_ptr, p.lut, 4, p.n_groups, row * kTileRows, p.gs, nl, kLookupWarps * 32);
+              asm volatile("bar.sync 1, %0;" ::"r"(kLookupWarps * 32) : "memory");
+              uint32_t token;
+              asm volatile("mov.u32 %0, 0;" : "=r"(token));
+              lane_base = tbl_addr + lane * 4 + token;
+              table_row = row;
+              PT_END(1)
+            }
+            table_tile = ut;
+          }
+          const int i = it + 2 * u;
+          const int stage = i % kPStages;
+          PT_BEGIN
+          if (i >= kPStages)        // the k-block that last used this operand stage has been consumed
+            tc::mbar_wait(bar_done + 8 * stage, uint32_t(i / kPStages - 1) & 1u, abort_flag,
+                          &g_gemm_status, tc::kStatusWaitEmpty);
+          PT_END(0)
+          PT_BEGIN
+          tc::fence_after_sync();
+#pragma unroll
+          for (int sl = 0; sl < 2; ++sl) {
+            const int rowslab = 2 * q + sl;
+            const int pal = nl == 1 ? 0 : (nl == 2 ? rowslab >> 2 : rowslab >> 1);
+            const uint32_t tb = lane_base + uint32_t(pal >> 1) * kTableBytes + uint32_t(pal & 1) * 128u;
+            uint32_t r[16];
+#pragma unroll
+            for (int kt = 0; kt < 4; ++kt) {
+              const uint32_t word = w[u][4 * sl + kt];
+              r[4 * kt + 0] = lds32(__byte_perm(word, tb, 0x7604u));
+              r[4 * kt + 1] = lds32(__byte_perm(word, tb, 0x7624u));
+              r[4 * kt + 2] = lds32(__byte_perm(word, tb, 0x7614u));
+              r[4 * kt + 3] = lds32(__byte_perm(word, tb, 0x7634u));
+            }
+            tc::tmem_st_16x256b_x4(tmem + (uint32_t(32 * q + 16 * sl) << 16) + kPACol + 32u * stage, r);
+          }
+          {
+            const bool on = lt < ntile;
+            ldg_stream256_if(w[u], code_ptr(on ? lt : 0, on ? lc : 0), on ? 1u : 0u);
+            advance(lt, lc);
+          }
+          PT_END(2)
+          PT_BEGIN
+          tc::wait_st();
+          PT_END(3)
+          tc::fence_before_sync();
+          if (lane == 0) tc::mbar_arrive(bar_full + 8 * stage);
+          advance(ut, uc);
+        }
+      }
+    }
+    PT_STORE(warp * 5)
+  } else if (warp == kLookupWarps) {
+    // ---- TMA producer ---------------------------------------------------------------------------
+    int i = 0;
+    for (int t = 0; t < ntile; ++t) {
+      const int m0 = ((t0 + t) % p.m_tiles) * p.NT;
+      for (int c = 0; c < G; ++c, ++i) {
+        const int xs = i % kPStages;
+        if (i >= kPStages)
+          tc::mbar_wait(bar_done + 8 * xs, uint32_t(i / kPStages - 1) & 1u, abort_flag,
+                        &g_gemm_status, tc::kStatusWaitEmpty);
+        if (lane == 0 && !*abort_flag) {
+          tc::mbar_expect_tx(bar_full + 8 * xs, stage_bytes);
+          tma_load_2d(xstage(xs), &xmap, bar_full + 8 * xs, c * kChunkK, m0);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == kLookupWarps + 1) {
+    // ---- MMA issuer -----------------------------------------------------------------------------
+    constexpr uint32_t kFmt = DType<T>::id == B200LUT_BF16 ? 1u : 0u;
+    const uint64_t dtemplate = tc::smem_desc(0u, 16u, 1024u, 2u);
+    uint32_t xlo[kPStages];
+#pragma unroll
+    for (int s = 0; s < kPStages; ++s) xlo[s] = uint32_t(dtemplate) + (xstage(s) >> 4);
+    const uint32_t xhi = uint32_t(dtemplate >> 32);
+    if (lane == 0) {
+      const int iters = ntile * G;
+      int t = -1, c = G;             // tile offset and k-block inside it; c == G: start the next tile
+      uint32_t idesc = 0;
+      const uint32_t d0 = tmem;
+      uint32_t phase = 0;            // (i / ring size) & 1
+      for (int i0 = 0; i0 < iters; i0 += kPStages, phase ^= 1u) {
+#pragma unroll
+        for (int u = 0; u < kPStages; ++u) {
+          if (i0 + u < iters) {
+            if (c == G) {            // a new tile: its accumulator buffer must have been drained
+              ++t;
+              c = 0;
+              const int m0 = ((t0 + t) % p.m_tiles) * p.NT;
+              int nt = p.M - m0;                          // the row's last tile may be narrower
+              nt = nt >= p.NT ? p.NT : ((nt + 31) & ~31);
+              idesc = tc::instr_desc(kFmt, 128, uint32_t(nt));
+              PT_BEGIN
+              if (t >= 1)
+                tc::mbar_wait(bar_dempty, uint32_t(t - 1) & 1u, abort_flag, &g_gemm_status,
+                              tc::kStatusWaitDone);
+              PT_END(2)
+            }
+            PT_BEGIN
+            tc::mbar_wait(bar_full + 8 * u, phase, abort_flag, &g_gemm_status, tc::kStatusWaitFull);
+            PT_END(0)
+            tc::fence_after_sync();
+            tc::mma_ts_kblock(d0, tmem + kPACol + 32u * uint32_t(u), xlo[u], xhi, idesc, c == 0 ? 0u : 1u);
+            tc::mma_commit(bar_done + 8 * u);
+            if (++c == G) tc::mma_commit(bar_dfull);
+          }
+        }
+      }
+      PT_STORE(45)
+    }
+    __syncwarp();
+  } else {
+    // ---- epilogue warps: TMEM -> bias -> one rounding -> staged slice -> global -----------------
+    const int q = warp & 3;                              // TMEM lane quarter this warp may read
+    const int h = (warp - (kLookupWarps + 2)) >> 2;      // column half of the tile it drains
+    const int et = threadIdx.x - (kLookupWarps + 2 + 4 * h) * 32;   // 0..127 inside the half
+    uint16_t* stg = stage_out + h * (kPStageTokens * kTileRows);
+    for (int t = 0; t < ntile; ++t) {
+      const int tile = t0 + t;
+      const int n0 = (tile / p.m_tiles) * kTileRows, m0 = (tile % p.m_tiles) * p.NT;
+      int nt = p.M - m0;
+      nt = nt >= p.NT ? p.NT : ((nt + 31) & ~31);
+      const int half = nt >> 1, col0 = h * half;
+      const int n = n0 + 32 * q + lane;
+      const float b0 = p.bias ? DType<T>::to_float(p.bias[n]) : 0.f;
+      PT_BEGIN
+      tc::mbar_wait(bar_dfull, uint32_t(t) & 1u, abort_flag, &g_gemm_status, tc::kStatusWaitDone);
+      PT_END(0)
+      tc::fence_after_sync();
+      const uint32_t d0 = tmem + (uint32_t(32 * q) << 16) + uint32_t(col0);
+      // slices of up to 48 tokens: three loads in flight, one wait, staging, 16-byte stores
+      for (int s0 = 0; s0 < half; s0 += kPStageTokens) {
+        const int sn = half - s0 < kPStageTokens ? half - s0 : kPStageTokens;
+        uint32_t r[3][16];
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch)
+          if (16 * ch < sn) tc::tmem_ld_32x32b_x16(d0 + uint32_t(s0 + 16 * ch), r[ch]);
+        tc::wait_ld();
+        if (s0 + sn >= half) {   // the accumulator is free as soon as it has been read
+          tc::fence_before_sync();
+          if (lane == 0) tc::mbar_arrive(bar_dempty);
+        }
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) {
+          if (16 * ch < sn) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float v = __uint_as_float(r[ch][j]) + b0;
+              const int tok = s0 + 16 * ch + j;
+              if (p.out_aligned) stg[(16 * ch + j) * kTileRows + 32 * q + lane] = DType<T>::from_float(v);
+              else if (m0 + col0 + tok < p.M)
+                p.out[size_t(m0 + col0 + tok) * p.ldo + n] = DType<T>::from_float(v);
+            }
+          }
+        }
+        if (p.out_aligned) {
+          asm volatile("bar.sync %0, 128;" ::"r"(2 + h) : "memory");
+          const uint4* src = reinterpret_cast<const uint4*>(stg);
+          for (int idx = et; idx < sn * 16; idx += 128) {
+            const int r_ = col0 + s0 + (idx >> 4), c = idx & 15;
+            if (m0 + r_ < p.M)
+              *reinterpret_cast<uint4*>(p.out + size_t(m0 + r_) * p.ldo + n0 + 8 * c) = src[idx];
+          }
+          asm volatile("bar.sync %0, 128;" ::"r"(2 + h) : "memory");   // the slice is reused
+        }
+      }
+    }
+  }
+
+  if (warp == kLookupWarps + 2) { PT_STORE(52) }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == kLookupWarps) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem, kTmemCols);
+  }
+#ifdef B200LUT_GEMM_TIMING
+  if (threadIdx.x == 0 && blockIdx.x == 0) { g_gemm_timing[60] = clock64() - pt_start; g_gemm_timing[61] = ntile; }
+#endif
+#undef PT_DECL
+#undef PT_BEGIN
+#undef PT_END
+#undef PT_STORE
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -388,6 +728,52 @@ int launch(const CUtensorMap& map, const GemmParams& p, int n_tiles, bool pdl, c
   cfg.attrs = attr;
   cfg.numAttrs = unsigned(na);
   B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map, p));
+  return B200LUT_OK;
+}
+
+template <typename T>
+int launch_persistent(const CUtensorMap& map, const PersistParams& p, int grid, bool pdl,
+                      cudaStream_t stream) {
+  auto kern = gemm_tc_persistent_kernel<T>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         int(kMaxDynSmem)));
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(grid), 1, 1);
+  cfg.blockDim = dim3(kPThreads, 1, 1);
+  cfg.dynamicSmemBytes = p.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int na = 0;
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = unsigned(na);
+  B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map, p));
+  return B200LUT_OK;
+}
+
+int encode_x_map(CUtensorMap* map, const void* x, int64_t ldx, int M, int K, int dtype, int NT) {
+  EncodeTiledFn enc = encode_fn();
+  B200LUT_REQUIRE(enc != nullptr, B200LUT_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(M)};
+  const cuuint64_t strides[1] = {cuuint64_t(ldx) * 2};
+  const cuuint32_t box[2] = {cuuint32_t(kChunkK), cuuint32_t(NT)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, dtype == B200LUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         2, const_cast<void*>(x), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200LUT_REQUIRE(r == CUDA_SUCCESS, B200LUT_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", int(r));
   return B200LUT_OK;
 }
 
@@ -444,6 +830,42 @@ extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
   B200LUT_REQUIRE(aligned16(s.packed) && (!two || aligned16(s.packed2)), B200LUT_ERR_ALIGN,
                   "code buffers must be 16-byte aligned");
 
+  const bool pdl = (flags & 1) != 0;
+  int debug = 0;
+  { const char* e = getenv("B200LUT_GEMM_DEBUG"); debug = e ? atoi(e) : 0; }
+  const int nl = s.group_size >= 128 ? 1 : 128 / s.group_size;
+  if (!two && nl <= 2 && K / kChunkK >= 2 && !(debug & 4)) {
+    // one code stream whose palettes fit one table: the persistent, double-buffered kernel
+    PersistParams pp = {};
+    pp.packed = static_cast<const uint8_t*>(s.packed);
+    pp.lut = static_cast<const uint16_t*>(s.lut);
+    pp.bias = static_cast<const uint16_t*>(s.bias);
+    pp.out = static_cast<uint16_t*>(s.out);
+    pp.ldo = s.ldo;
+    pp.out_aligned = (aligned16(s.out) && s.ldo % 8 == 0) ? 1 : 0;
+    pp.M = M; pp.N = s.N; pp.K = K; pp.G = K / kChunkK;
+    pp.gs = s.group_size; pp.n_groups = s.n_groups;
+    pp.NT = M >= kPMaxNT ? kPMaxNT : ((M + 31) / 32) * 32;
+    pp.m_tiles = (M + pp.NT - 1) / pp.NT;
+    pp.n_tiles = s.N / kTileRows;
+    pp.W = (pp.m_tiles - 1) * pp.NT + ((M - (pp.m_tiles - 1) * pp.NT + 31) / 32) * 32;
+    pp.smem_bytes = uint32_t(kMaxDynSmem);
+    pp.debug = debug;
+    CUtensorMap pmap;
+    if (int rc = encode_x_map(&pmap, x, ldx, M, K, dtype, pp.NT)) return rc;
+    int sms = 148;
+    {
+      int dev = 0;
+      B200LUT_CUDA_OK(cudaGetDevice(&dev));
+      B200LUT_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    const long long tiles = (long long)pp.n_tiles * pp.m_tiles;
+    const int grid = int(tiles < sms ? tiles : sms);
+    if (dtype == B200LUT_BF16)
+      return launch_persistent<__nv_bfloat16>(pmap, pp, grid, pdl, cudaStream_t(stream));
+    return launch_persistent<__half>(pmap, pp, grid, pdl, cudaStream_t(stream));
+  }
+
   GemmParams p = {};
   p.packed[0] = static_cast<const uint8_t*>(s.packed);
   p.lut[0] = static_cast<const uint16_t*>(s.lut);
@@ -464,7 +886,6 @@ extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
   if (NT > nt_max) NT = nt_max;
   p.NT = NT;
   p.m_tiles = (M + NT - 1) / NT;
-  const int nl = s.group_size >= 128 ? 1 : 128 / s.group_size;
   const int tables = (p.npass * nl + 1) / 2;
   // Activation stages fill what the control block and the 64 KB-aligned tables leave
   // free. The dynamic window starts 1 KB into the shared window on sm_100; the kernel
@@ -480,22 +901,10 @@ extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
                     "stages in shared memory", s.group_size, p.npass);
   }
   p.smem_bytes = uint32_t(kMaxDynSmem);
-  { const char* e = getenv("B200LUT_GEMM_DEBUG"); p.debug = e ? atoi(e) : 0; }
+  p.debug = debug;
 
-  EncodeTiledFn enc = encode_fn();
-  B200LUT_REQUIRE(enc != nullptr, B200LUT_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
   CUtensorMap map;
-  const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(M)};
-  const cuuint64_t strides[1] = {cuuint64_t(ldx) * 2};
-  const cuuint32_t box[2] = {cuuint32_t(kChunkK), cuuint32_t(NT)};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(&map, dtype == B200LUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                         2, const_cast<void*>(x), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  B200LUT_REQUIRE(r == CUDA_SUCCESS, B200LUT_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", int(r));
-  const bool pdl = (flags & 1) != 0;
+  if (int rc = encode_x_map(&map, x, ldx, M, K, dtype, NT)) return rc;
   if (dtype == B200LUT_BF16)
     return launch<__nv_bfloat16>(map, p, s.N / kTileRows, pdl, cudaStream_t(stream));
   return launch<__half>(map, p, s.N / kTileRows, pdl, cudaStream_t(stream));

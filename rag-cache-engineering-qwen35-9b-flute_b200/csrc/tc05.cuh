@@ -163,6 +163,28 @@ __device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_
       : "memory");
 }
 
+// The four K = 16 steps of one 64-wide k-block in one instruction group: D (+)= A[a0 + 8 j] *
+// B[desc + 32 j bytes], j = 0..3. The descriptor is passed as its two words (only the low
+// one, which holds the start address in 16-byte units, changes between steps); the first
+// step overwrites D when accumulate == 0. One thread issues.
+__device__ __forceinline__ void mma_ts_kblock(uint32_t tmem_d, uint32_t a0, uint32_t desc_lo,
+                                              uint32_t desc_hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 b0, b1, b2, b3;\n\t.reg .b32 l1, l2, l3, a1, a2, a3;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 q, %6, %6;\n\t"
+      "add.u32 l1, %2, 2;\n\tadd.u32 l2, %2, 4;\n\tadd.u32 l3, %2, 6;\n\t"
+      "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\t"
+      "mov.b64 b0, {%2, %3};\n\tmov.b64 b1, {l1, %3};\n\tmov.b64 b2, {l2, %3};\n\tmov.b64 b3, {l3, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], b0, %4, {%6, %6, %6, %6}, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %4, {%6, %6, %6, %6}, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %4, {%6, %6, %6, %6}, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %4, {%6, %6, %6, %6}, q;\n\t}"
+      :
+      : "r"(tmem_d), "r"(a0), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
 // All MMAs issued so far by this thread arrive on `bar` when they complete.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
