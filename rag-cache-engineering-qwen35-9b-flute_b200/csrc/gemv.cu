@@ -42,6 +42,21 @@ namespace {
 
 __device__ int g_exchange_status = 0;
 
+#ifdef B200LUT_GEMV_TRACE
+// Debug build only: wall-clock stamps (ns) of the first and the last block of each launch.
+__device__ unsigned long long g_trace[8192 * 8];
+__device__ unsigned int g_trace_launch = 0;
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE_STAMP(k)                                                             \
+  if (trace_row && threadIdx.x == 0) trace_row[k] = trace_now();
+#else
+#define TRACE_STAMP(k)
+#endif
+
 constexpr int kMaxSeg = 8;
 constexpr int kMaxM = 16;
 constexpr uint32_t kPartBytes = 2 * kMaxM * kTileRows * 4;  // two result planes (gate/up)
@@ -139,6 +154,9 @@ struct DepWait {
   int target;               // mode 2: proceed when *counter >= target
   int* abort_word;          // mode 2: global word set when any block gave up waiting
   const ExchangeDev* ex;    // mode 1: also wait for the peers' pushes (null: no exchange)
+#ifdef B200LUT_GEMV_TRACE
+  unsigned long long* trace;
+#endif
 };
 
 constexpr long long kDepWaitCycles = 40000000;   // ~20 ms: far beyond any healthy wait
@@ -266,6 +284,9 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
   constexpr int NT = NWARPS * 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
+#ifdef B200LUT_GEMV_TRACE
+  unsigned long long* trace_row = dep.trace;
+#endif
   const size_t chunk_bytes = size_t(1024) * BITS;
   const size_t hop = chunk_bytes * NWARPS;            // bytes between a warp's consecutive chunks
   const uint8_t* lane_base = packed + (size_t(tile) * G) * chunk_bytes + lane * 32;
@@ -287,9 +308,17 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
   if (nl < 1) nl = 1;
   const int slot_shift = nl == 1 ? 3 : (nl == 2 ? 2 : 1);
   if (sync_before) __syncthreads();   // the previous pass's fold buffer aliases the tables
-  build_tables(tbl_ptr, lut, BITS, n_groups, tile * kTileRows, gs, nl, NT);
-  if (dep.mode == 2 && threadIdx.x == 0) dep_poll(dep);   // producer job's tiles, bounded
-  __syncthreads();
+  // Palette entries are requested now and written into the table only after the activation
+  // rows have been requested too: the two global round trips overlap, and both sit behind
+  // the code fetches issued above.
+  const bool split_build = nl <= 2;
+  uint32_t lutv = 0u;
+  if (split_build) lutv = palette_fetch(lut, BITS, n_groups, tile * kTileRows, gs, nl);
+  else build_tables(tbl_ptr, lut, BITS, n_groups, tile * kTileRows, gs, nl, NT);
+  if (dep.mode == 2) {
+    if (threadIdx.x == 0) dep_poll(dep);   // producer job's tiles, bounded
+    __syncthreads();
+  }
   if (dep.mode == 1) {
     // everything above is independent of the previous kernel in the stream
     if (dep.ex) {   // block-uniform
@@ -300,9 +329,20 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
         peer_poll(*dep.ex, i);
       __syncthreads();
     } else {
+      TRACE_STAMP(1)
       asm volatile("griddepcontrol.wait;" ::: "memory");
+      TRACE_STAMP(2)
     }
   }
+  // x fragments ride the code ring: the rows of a chunk are requested RC chunks ahead of their
+  // use (a first touch of x misses L1 and pays an L2 round trip).
+  uint2 xf[RC][P::kNB][4];
+#pragma unroll
+  for (int u = 0; u < RC; ++u)
+    load_x<CP>(xf[u], x, ldx, (c + u * NWARPS < c1) ? M : 0, (c + u * NWARPS) * kChunkK, gid, tig);
+  if (split_build) table_store_shfl<NT>(tbl_ptr, lutv, BITS, nl);
+  __syncthreads();
+  TRACE_STAMP(3)
 
   float acc[P::kAcc][4];
 #pragma unroll
@@ -313,12 +353,6 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
   uint32_t token;   // defined after the build barrier; part of every lookup address
   asm volatile("mov.u32 %0, 0;" : "=r"(token));
   const uint32_t tbl_lane = tbl_addr + lane * 4 + token;
-  // x fragments ride the same ring: the rows of a chunk are requested RC chunks ahead
-  // of their use (a first touch of x misses L1 and pays an L2 round trip).
-  uint2 xf[RC][P::kNB][4];
-#pragma unroll
-  for (int u = 0; u < RC; ++u)
-    load_x<CP>(xf[u], x, ldx, (c + u * NWARPS < c1) ? M : 0, (c + u * NWARPS) * kChunkK, gid, tig);
   for (; c < c1; c += RC * NWARPS) {
 #pragma unroll
     for (int u = 0; u < RC; ++u) {
@@ -335,7 +369,9 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
   for (int a = 0; a < P::kAcc; ++a)
 #pragma unroll
     for (int r = 0; r < 4; ++r) asm volatile("" ::"f"(acc[a][r]));   // lookups end here
+  if (warp == 0) { TRACE_STAMP(4) }
   __syncthreads();   // all warps are done with the tables
+  TRACE_STAMP(5)
 
   // cross-warp fold, 8 batch columns at a time: red[warp][m & 7][row], fixed warp order
 #pragma unroll
@@ -488,6 +524,22 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
   const int nplanes = silu ? 2 : 1;
 
   asm volatile("griddepcontrol.launch_dependents;");
+#ifdef B200LUT_GEMV_TRACE
+  __shared__ unsigned long long* trace_row_s;
+  if (threadIdx.x == 0) {
+    trace_row_s = nullptr;
+    if (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) {
+      unsigned int id = 0;
+      if (blockIdx.x == 0) id = atomicAdd(&g_trace_launch, 1u);
+      else id = *reinterpret_cast<volatile unsigned int*>(&g_trace_launch);   // approximate pairing
+      const unsigned int slot = (blockIdx.x == 0 ? 2 * id : 2 * id + 1) % 8192;
+      trace_row_s = g_trace + size_t(slot) * 8;
+      trace_row_s[0] = trace_now();
+    }
+  }
+  __syncthreads();
+  unsigned long long* trace_row = trace_row_s;
+#endif
 
   const int M = p.M;
   bool first = true;
@@ -499,10 +551,15 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
       const uint16_t* lut = pass ? sg.lut2 : sg.lut;
       const int bits = pass ? sg.bits2 : sg.bits;
       float* dst = part + plane * kMaxM * kTileRows;
+#ifdef B200LUT_GEMV_TRACE
+#define TRACE_ARG , (first ? trace_row : nullptr)
+#else
+#define TRACE_ARG
+#endif
 #define B200LUT_PASS(B)                                                                       \
   stream_pass<T, B, CP, NWARPS, RC>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups,  \
                                     sg.gs, tile, p.G, c0, c1, p.x, p.ldx, M, !first,              \
-                                    DepWait{first ? 1 : 0, nullptr, 0, nullptr, (first && p.ex.wait) ? &p.ex : nullptr})
+                                    DepWait{first ? 1 : 0, nullptr, 0, nullptr, (first && p.ex.wait) ? &p.ex : nullptr TRACE_ARG})
       switch (bits) {   // block-uniform
         case 4: B200LUT_PASS(4); break;
         case 3: B200LUT_PASS(3); break;
@@ -513,7 +570,9 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
       first = false;
     }
   }
+  TRACE_STAMP(6)
   fold_and_store<T, NT>(p, part, si, tile, tile_g, sp);
+  TRACE_STAMP(7)
 
   if (p.ex.wait) {
     // The last block of a waiting grid counts the wait as done (every block read the count
@@ -718,6 +777,16 @@ int pick_split(int tiles, int G, int sms, int warps) {
 using namespace b200lut;
 
 extern "C" int b200lut_sm_count(void) { return sm_count_cached(); }
+
+#ifdef B200LUT_GEMV_TRACE
+extern "C" int b200lut_gemv_trace(unsigned long long* out, int rows, unsigned int* launches) {
+  if (cudaMemcpyFromSymbol(out, g_trace, size_t(rows) * 64) != cudaSuccess) return 3;
+  if (cudaMemcpyFromSymbol(launches, g_trace_launch, 4) != cudaSuccess) return 3;
+  unsigned int zero = 0;
+  cudaMemcpyToSymbol(g_trace_launch, &zero, 4);
+  return 0;
+}
+#endif
 
 extern "C" int b200lut_gemv_pick_split(int tiles, int K) {
   if (tiles <= 0 || K <= 0) return 1;

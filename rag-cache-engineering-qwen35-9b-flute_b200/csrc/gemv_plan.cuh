@@ -60,46 +60,6 @@ __device__ __forceinline__ void plan_store(const SegDev& s0, const SegDev* s1, i
 
 // ---- pieces of one pass (one code stream of one tile share) --------------------------------
 
-// Palette entries this thread will write into the pair table of a pass: fetched early (one
-// pass ahead), stored late (table_store), so the palette's DRAM round trip is off the path.
-// registers per thread: nl (<= 2) * 256 entries * 8 sixteen-byte copies / threads
-template <int NT> struct LutRegs { static constexpr int n = 4096 / NT; };
-
-template <int NT>
-__device__ __forceinline__ void table_fetch(uint32_t (&v)[LutRegs<NT>::n], const uint16_t* __restrict__ lut,
-                                            int bits, int n_groups, int row0, int gs, int nl) {
-  const int entries = 1 << (2 * bits);
-  const uint32_t mask = (1u << bits) - 1u;
-  const int rows_per_lut = kTileRows / nl;
-#pragma unroll
-  for (int k = 0; k < LutRegs<NT>::n; ++k) {
-    const int idx = threadIdx.x + k * NT;
-    v[k] = 0u;
-    if (idx < nl * entries * 8) {
-      const int e = (idx >> 3) & (entries - 1), sl = idx >> (3 + 2 * bits);
-      int grp = (row0 + sl * rows_per_lut) / gs;
-      if (grp > n_groups - 1) grp = n_groups - 1;
-      const uint16_t* row = lut + (size_t(grp) << bits);
-      v[k] = uint32_t(__ldg(row + (e & mask))) | (uint32_t(__ldg(row + (e >> bits))) << 16);
-    }
-  }
-}
-
-template <int NT>
-__device__ __forceinline__ void table_store(uint8_t* tbl_ptr, const uint32_t (&v)[LutRegs<NT>::n], int bits,
-                                            int nl) {
-  const int entries = 1 << (2 * bits);
-#pragma unroll
-  for (int k = 0; k < LutRegs<NT>::n; ++k) {
-    const int idx = threadIdx.x + k * NT;
-    if (idx < nl * entries * 8) {
-      const int q = idx & 7, e = (idx >> 3) & (entries - 1), sl = idx >> (3 + 2 * bits);
-      *reinterpret_cast<uint4*>(tbl_ptr + e * 256 + (sl & 1) * 128 + q * 16) =
-          make_uint4(v[k], v[k], v[k], v[k]);
-    }
-  }
-}
-
 // First chunk of a pass into the (width-agnostic) register buffer.
 __device__ __forceinline__ void first_chunk(uint32_t (&w)[32], const uint8_t* __restrict__ packed,
                                             int bits, int tile, int G, int c, int c1, int lane) {

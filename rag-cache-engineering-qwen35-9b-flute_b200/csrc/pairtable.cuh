@@ -69,5 +69,78 @@ __device__ void build_tables(uint8_t* tbl_ptr, const uint16_t* __restrict__ lut,
   }
 }
 
+// The same fill in two halves with ONE register in between, for tiles with at most two
+// palettes (one table): lane L of every warp fetches entry L % 16 of palette L / 16
+// (palette_fetch, a single 2-byte load), and the pair entries are later assembled from
+// warp shuffles (table_store_shfl). All threads of the block must call both.
+__device__ __forceinline__ uint32_t palette_fetch(const uint16_t* __restrict__ lut, int bits,
+                                                  int n_groups, int row0, int gs, int nl) {
+  const int lane = threadIdx.x & 31;
+  const int sl = (lane >> 4) < nl ? (lane >> 4) : 0;
+  int grp = (row0 + sl * (kTileRows / nl)) / gs;
+  if (grp > n_groups - 1) grp = n_groups - 1;
+  const int e = lane & 15;
+  return e < (1 << bits) ? uint32_t(__ldg(lut + (size_t(grp) << bits) + e)) : 0u;
+}
+
+template <int NT>
+__device__ __forceinline__ void table_store_shfl(uint8_t* tbl_ptr, uint32_t lv, int bits, int nl) {
+  const int entries = 1 << (2 * bits);
+  const int mask = (1 << bits) - 1;
+  constexpr int kIters = (4096 + NT - 1) / NT;
+#pragma unroll
+  for (int k = 0; k < kIters; ++k) {
+    const int idx = threadIdx.x + k * NT;
+    if (idx < nl * entries * 8) {   // warp-uniform: the bound is a multiple of 32
+      const int q = idx & 7, e = (idx >> 3) & (entries - 1), sl = idx >> (3 + 2 * bits);
+      const uint32_t lo = __shfl_sync(0xffffffffu, lv, 16 * sl + (e & mask));
+      const uint32_t hi = __shfl_sync(0xffffffffu, lv, 16 * sl + (e >> bits));
+      const uint32_t v = lo | (hi << 16);
+      *reinterpret_cast<uint4*>(tbl_ptr + e * 256 + (sl & 1) * 128 + q * 16) = make_uint4(v, v, v, v);
+    }
+  }
+}
+
+// The same fill in two halves, for tiles with at most two palettes (one table):
+// Palette entries this thread will write into the pair table of a pass: fetched early (one
+// pass ahead), stored late (table_store), so the palette's DRAM round trip is off the path.
+// registers per thread: nl (<= 2) * 256 entries * 8 sixteen-byte copies / threads
+template <int NT> struct LutRegs { static constexpr int n = (4096 + NT - 1) / NT; };
+
+template <int NT>
+__device__ __forceinline__ void table_fetch(uint32_t (&v)[LutRegs<NT>::n], const uint16_t* __restrict__ lut,
+                                            int bits, int n_groups, int row0, int gs, int nl) {
+  const int entries = 1 << (2 * bits);
+  const uint32_t mask = (1u << bits) - 1u;
+  const int rows_per_lut = kTileRows / nl;
+#pragma unroll
+  for (int k = 0; k < LutRegs<NT>::n; ++k) {
+    const int idx = threadIdx.x + k * NT;
+    v[k] = 0u;
+    if (idx < nl * entries * 8) {
+      const int e = (idx >> 3) & (entries - 1), sl = idx >> (3 + 2 * bits);
+      int grp = (row0 + sl * rows_per_lut) / gs;
+      if (grp > n_groups - 1) grp = n_groups - 1;
+      const uint16_t* row = lut + (size_t(grp) << bits);
+      v[k] = uint32_t(__ldg(row + (e & mask))) | (uint32_t(__ldg(row + (e >> bits))) << 16);
+    }
+  }
+}
+
+template <int NT>
+__device__ __forceinline__ void table_store(uint8_t* tbl_ptr, const uint32_t (&v)[LutRegs<NT>::n], int bits,
+                                            int nl) {
+  const int entries = 1 << (2 * bits);
+#pragma unroll
+  for (int k = 0; k < LutRegs<NT>::n; ++k) {
+    const int idx = threadIdx.x + k * NT;
+    if (idx < nl * entries * 8) {
+      const int q = idx & 7, e = (idx >> 3) & (entries - 1), sl = idx >> (3 + 2 * bits);
+      *reinterpret_cast<uint4*>(tbl_ptr + e * 256 + (sl & 1) * 128 + q * 16) =
+          make_uint4(v[k], v[k], v[k], v[k]);
+    }
+  }
+}
+
 }  // namespace
 }  // namespace b200lut
