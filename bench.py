@@ -304,8 +304,9 @@ def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool):
     for _ in range(3):
         run()
     ms = time_steps(run, iters, 1)
-    if L.lib().b200lut_device_status() != 0:
-        raise RuntimeError("a bounded wait ran out inside the GEMM kernel")
+    status = L.lib().b200lut_device_status()
+    if status != 0:
+        raise RuntimeError(f"a bounded wait ran out inside the GEMM kernel (device status {status})")
     us = ms * 1e3 / iters
     return 2.0 * M * N * K / us / 1e6, us
 

@@ -383,6 +383,7 @@ struct PersistParams {
   uint32_t smem_bytes;
   int out_aligned;
   int debug;
+  long long wait_cycles;   // bound of every in-kernel wait, in SM clock cycles
 };
 
 // First tile of block b when the tile list is cut into gridDim.x ranges of equal cost
@@ -514,7 +515,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
           PT_BEGIN
           if (i >= kPStages)        // the k-block that last used this operand stage has been consumed
             tc::mbar_wait(bar_done + 8 * stage, uint32_t(i / kPStages - 1) & 1u, abort_flag,
-                          &g_gemm_status, tc::kStatusWaitEmpty);
+                          &g_gemm_status, tc::kStatusWaitEmpty, p.wait_cycles);
           PT_END(0)
           PT_BEGIN
           tc::fence_after_sync();
@@ -559,7 +560,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
         const int xs = i % kPStages;
         if (i >= kPStages)
           tc::mbar_wait(bar_done + 8 * xs, uint32_t(i / kPStages - 1) & 1u, abort_flag,
-                        &g_gemm_status, tc::kStatusWaitEmpty);
+                        &g_gemm_status, tc::kStatusWaitEmpty, p.wait_cycles);
         if (lane == 0 && !*abort_flag) {
           tc::mbar_expect_tx(bar_full + 8 * xs, stage_bytes);
           tma_load_2d(xstage(xs), &xmap, bar_full + 8 * xs, c * kChunkK, m0);
@@ -595,11 +596,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
               PT_BEGIN
               if (t >= 1)
                 tc::mbar_wait(bar_dempty, uint32_t(t - 1) & 1u, abort_flag, &g_gemm_status,
-                              tc::kStatusWaitDone);
+                              tc::kStatusWaitDone, p.wait_cycles);
               PT_END(2)
             }
             PT_BEGIN
-            tc::mbar_wait(bar_full + 8 * u, phase, abort_flag, &g_gemm_status, tc::kStatusWaitFull);
+            tc::mbar_wait(bar_full + 8 * u, phase, abort_flag, &g_gemm_status, tc::kStatusWaitFull, p.wait_cycles);
             PT_END(0)
             tc::fence_after_sync();
             tc::mma_ts_kblock(d0, tmem + kPACol + 32u * uint32_t(u), xlo[u], xhi, idesc, c == 0 ? 0u : 1u);
@@ -626,7 +627,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
       const int n = n0 + 32 * q + lane;
       const float b0 = p.bias ? DType<T>::to_float(p.bias[n]) : 0.f;
       PT_BEGIN
-      tc::mbar_wait(bar_dfull, uint32_t(t) & 1u, abort_flag, &g_gemm_status, tc::kStatusWaitDone);
+      tc::mbar_wait(bar_dfull, uint32_t(t) & 1u, abort_flag, &g_gemm_status, tc::kStatusWaitDone, p.wait_cycles);
       PT_END(0)
       tc::fence_after_sync();
       const uint32_t d0 = tmem + (uint32_t(32 * q) << 16) + uint32_t(col0);
@@ -851,6 +852,16 @@ extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
     pp.W = (pp.m_tiles - 1) * pp.NT + ((M - (pp.m_tiles - 1) * pp.NT + 31) / 32) * 32;
     pp.smem_bytes = uint32_t(kMaxDynSmem);
     pp.debug = debug;
+    // Waits inside the kernel give up after ~10 ms. A profiler that replays the kernel with
+    // heavy instrumentation can stretch a healthy wait beyond that; B200LUT_WAIT_MS raises the
+    // bound for such runs (capped at one second).
+    pp.wait_cycles = tc::kWaitCycles;
+    if (const char* e = getenv("B200LUT_WAIT_MS")) {
+      long ms = atol(e);
+      if (ms < 1) ms = 1;
+      if (ms > 1000) ms = 1000;
+      pp.wait_cycles = (long long)ms * 2000000ll;
+    }
     CUtensorMap pmap;
     if (int rc = encode_x_map(&pmap, x, ldx, M, K, dtype, pp.NT)) return rc;
     int sms = 148;

@@ -59,7 +59,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // signal drains in microseconds. The deadline is in SM clock cycles. Returns false on
 // abort.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int why) {
+                                          int* status, int why, long long limit = kWaitCycles) {
   if (mbar_test(bar, parity)) return true;
   if (*abort_flag) return false;
   const long long t0 = clock64();
@@ -67,7 +67,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_test(bar, parity)) return true;
     if ((i & 15u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) break;
+      if (clock64() - t0 > limit) break;
     }
   }
   *abort_flag = 1;
