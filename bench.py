@@ -482,6 +482,11 @@ def main() -> int:
             gbs, us = single_projection_gbs(pkg, 1, 12288, 4096, 16, 20, flags)
             extras["gemv_12288x4096_m1"] = {"GB/s": gbs, "us_per_launch": us,
                                             "frac_of_hbm": gbs / peaks["hbm_gbs"]}
+            # the model's lm_head (248 320 x 4096, 1940 tiles, 0.51 GB of codes): the steady-state
+            # streaming rate of the kernel, with the per-launch cost amortised over 13 waves
+            gbs, us = single_projection_gbs(pkg, 1, 248320, 4096, 1, 10, flags)
+            extras["gemv_248320x4096_m1_lm_head"] = {"GB/s": gbs, "us_per_launch": us,
+                                                     "frac_of_hbm": gbs / peaks["hbm_gbs"]}
             tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, 20, False)
             extras["prefill_gemm_m2048_k4096_n12288"] = {
                 "TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"],

@@ -113,8 +113,23 @@ typedef struct b200lut_segment {
   int n_groups;          /* palette rows actually present (row-group index is clamped) */
   int bits;              /* stream-1 width (1..4) */
   int bits2;             /* stream-2 width, 0 if absent */
-  int reserved;
+  int res_rank;          /* R of the fused low-rank residual, 0 if absent (decode GEMV only) */
+  const void* resA;      /* [N, R] dtype, row-major: out[m, n] += sum_r res_t[m, r] * resA[n, r] */
+  const float* res_t;    /* [M, res_ldt] fp32 = x @ resB^T, from b200lut_residual_project */
+  int64_t res_ldt;       /* elements between consecutive rows of res_t */
 } b200lut_segment;
+
+/* First factor of the low-rank residual of the decode path: t[m, r] = sum_k x[m, k] *
+ * resB[r, k] in fp32, M <= 16. resB is [R, K] dtype, row-major; the rB factors of projections
+ * that share x (Q/K/V, gate/up) may be stacked along r so that one call serves a merged
+ * launch. The GEMV that follows adds sum_r t[m, r] * resA[n, r] to its fp32 sums before bias
+ * and the single rounding (segment fields res_rank / resA / res_t / res_ldt). Replaces the
+ * residual branch the reference's split-K GEMV computes inside its launch
+ * (src/flute_extended/src/kernel_gemv_splitk.cu:260-292, 340-349; R <= 256 there).
+ * flags bit 0: programmatic dependent launch. */
+int b200lut_residual_project(const void* x, int64_t ldx, int M, int K, int dtype,
+                             const void* resB, int R, float* t, int64_t ldt, int flags,
+                             void* stream);
 
 /* Scratch bytes b200lut_gemv_multi needs for (segments, M, split): zero when the
  * split is reduced through thread-block-cluster shared memory (split <= 8),

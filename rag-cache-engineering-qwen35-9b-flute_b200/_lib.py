@@ -27,7 +27,7 @@ EXPORTS = (
     "b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes",
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
-    "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
+    "b200lut_residual_project", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
     "b200lut_gemv_noalloc", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
@@ -40,7 +40,8 @@ class Segment(ctypes.Structure):
         ("bias", ctypes.c_void_p), ("out", ctypes.c_void_p),
         ("ldo", ctypes.c_int64),
         ("N", ctypes.c_int), ("group_size", ctypes.c_int), ("n_groups", ctypes.c_int),
-        ("bits", ctypes.c_int), ("bits2", ctypes.c_int), ("reserved", ctypes.c_int),
+        ("bits", ctypes.c_int), ("bits2", ctypes.c_int), ("res_rank", ctypes.c_int),
+        ("resA", ctypes.c_void_p), ("res_t", ctypes.c_void_p), ("res_ldt", ctypes.c_int64),
     ]
 
 
@@ -108,6 +109,8 @@ def lib() -> ctypes.CDLL:
     L.b200lut_gemv_multi.restype = i32
     L.b200lut_gemv_multi.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32,
                                      i32, vp, sz, i32, vp]
+    L.b200lut_residual_project.restype = i32
+    L.b200lut_residual_project.argtypes = [vp, i64, i32, i32, i32, vp, i32, vp, i64, i32, vp]
     L.b200lut_gemv_exchange.restype = i32
     L.b200lut_gemv_exchange.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32,
                                         i32, vp, sz, i32, ctypes.POINTER(Exchange), vp]
@@ -237,7 +240,26 @@ def make_segments(descs: Sequence[dict]):
         s.ldo = int(d.get("ldo", d["N"]))
         s.N, s.group_size, s.n_groups = int(d["N"]), int(d["group_size"]), int(d["n_groups"])
         s.bits, s.bits2 = int(d["bits"]), int(d.get("bits2") or 0)
+        if d.get("resA") is not None:
+            t = d["res_t"]
+            s.resA, s.res_t = ptr(d["resA"]), t.data_ptr()
+            s.res_rank, s.res_ldt = int(d["resA"].shape[1]), int(t.stride(0))
     return arr
+
+
+def residual_project(x: torch.Tensor, resB: torch.Tensor, flags: int = 0,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """t = x @ resB^T in fp32 ([M, R]); the first factor of the fused low-rank residual."""
+    _need_cuda(x, "x")
+    M, K = x.shape
+    R = resB.shape[0]
+    if out is None:
+        out = torch.empty(M, R, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().b200lut_residual_project(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype),
+                                             resB.data_ptr(), R, out.data_ptr(), out.stride(0),
+                                             flags, _stream(x)))
+    return out
 
 
 def gemv_workspace_bytes(total_rows: int, M: int, split: int) -> int:

@@ -331,8 +331,10 @@ def replace_linear_with_palettized(model, metadata, artifacts_dir: str, residual
                                    heads_dir: Optional[str] = None):
     """Swap every tensor of the metadata for its palettized module, then install
     the fused MLP wrappers (the reference's swap, palettized_modules.py:2921-3027).
-    Head tensors (lm_head / embed_tokens) are outside this package's path: they
-    are left untouched and reported."""
+    `model.lm_head.weight` is a linear layer like any other (248 320 rows on the 9B model)
+    and is swapped too unless it is tied to the embedding; `model.embed_tokens.weight` is
+    a gather, for which the reference has no kernel either: it is left untouched and
+    reported."""
     tensors = dict(metadata["tensors"])
     if heads_dir is not None:
         heads = load_metadata(heads_dir)["tensors"]
@@ -341,21 +343,26 @@ def replace_linear_with_palettized(model, metadata, artifacts_dir: str, residual
             if key in heads:
                 tensors[key] = heads[key]
     art = ArtifactDir(artifacts_dir, verify_sha)
+    head_art = None
     skipped = []
     for name, meta in tensors.items():
-        if name in HEAD_TENSORS:
+        if name == "model.embed_tokens.weight" or (name in HEAD_TENSORS and meta.get("tied") is True):
             skipped.append(name)
             continue
+        head_dir = heads_dir if (heads_dir is not None and name in HEAD_TENSORS) else None
+        if head_dir is not None and (head_art is None):
+            head_art = ArtifactDir(head_dir, verify_sha)
         holder, leaf = resolve_module(model, name)
         old = getattr(holder, leaf)
         bias = getattr(old, "bias", None)
-        new = art.load_weight(meta, bias=None if bias is None else bias.data, residual=residual,
+        src = head_art if head_dir is not None else art
+        new = src.load_weight(meta, bias=None if bias is None else bias.data, residual=residual,
                               reference=reference, awq_scales=awq_scales)
         setattr(holder, leaf, new)
         del old
     art.summarize_gs()
     if skipped:
-        print(f"  [heads] not swapped (embedding / lm_head path is not part of this package): "
+        print(f"  [heads] not swapped (embedding gather / tied head are not part of this package): "
               f"{', '.join(skipped)}", flush=True)
     install_fused_mlp(model)
     return model

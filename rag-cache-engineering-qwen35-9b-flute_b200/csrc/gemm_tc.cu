@@ -817,6 +817,8 @@ extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
   B200LUT_REQUIRE(s.packed && s.lut && s.out, B200LUT_ERR_INVALID, "null codes, palette or output");
   B200LUT_REQUIRE(s.N > 0 && s.N % kTileRows == 0 && s.ldo >= s.N, B200LUT_ERR_INVALID,
                   "N must be a positive multiple of 128 and ldo >= N (N=%d)", s.N);
+  B200LUT_REQUIRE(s.res_rank == 0, B200LUT_ERR_UNSUPPORTED,
+                  "the prefill GEMM does not fuse the low-rank residual (two dense GEMMs do it)");
   const bool silu = epilogue == B200LUT_EPI_SILU_MUL;
   const bool two = s.packed2 != nullptr;
   B200LUT_REQUIRE(!silu || two, B200LUT_ERR_INVALID,

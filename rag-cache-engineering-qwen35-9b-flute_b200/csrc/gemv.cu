@@ -71,6 +71,10 @@ struct SegDev {
   uint16_t* out;
   long long ldo;
   int N, gs, n_groups, bits, bits2, tile_begin;
+  const uint16_t* resA;     // fused low-rank residual: [N, res_rank], or null
+  const float* res_t;       // [M, res_ldt] fp32 = x @ resB^T
+  long long res_ldt;
+  int res_rank, pad;
 };
 
 // Column-parallel exchange (see b200lut_exchange): where to mirror outputs, whom to signal,
@@ -92,6 +96,7 @@ struct GemvParams {
   const uint16_t* x;
   long long ldx;
   int M, K, G, nseg, split, epilogue, tiles_total, cluster;
+  uint32_t smem_bytes;   // dynamic shared memory of the launch
   float* ws;       // workspace fold: [split][tiles_total][planes][M][128] fp32
   int* tickets;    // workspace fold: [tiles_total]
   SegDev seg[kMaxSeg];
@@ -239,7 +244,7 @@ __device__ __forceinline__ void load_x(uint2 (&xf)[Plan<CP>::kNB][4],
 
 // Look up and multiply one chunk held in w; refill each 1 KB plane of w from `next`
 // (when `more`) as soon as its last field has been used.
-template <typename T, int BITS, int CP>
+template <typename T, int BITS, int CP, uint32_t TOFF = 0>
 __device__ __forceinline__ void chunk_math(float (&acc)[Plan<CP>::kAcc][4], uint32_t (&w)[8 * BITS],
                                            const uint2 (&xf)[Plan<CP>::kNB][4], uint32_t tbl_lane,
                                            int slot_shift, int gid, const uint8_t* next,
@@ -254,7 +259,7 @@ __device__ __forceinline__ void chunk_math(float (&acc)[Plan<CP>::kAcc][4], uint
     for (int kt = 0; kt < 4; ++kt) {
       uint32_t a[4];
 #pragma unroll
-      for (int f = 0; f < 4; ++f) a[f] = lds32(field_addr<BITS>(w, s, 4 * kt + f, base));
+      for (int f = 0; f < 4; ++f) a[f] = lds32o<TOFF>(field_addr<BITS>(w, s, 4 * kt + f, base));
 #pragma unroll
       for (int nb = 0; nb < P::kNB; ++nb) {
         const uint32_t b0 = (P::kSlabsPerAcc == 1 || mine) ? xf[nb][kt].x : 0u;
@@ -273,7 +278,7 @@ __device__ __forceinline__ void chunk_math(float (&acc)[Plan<CP>::kAcc][4], uint
 // K-range contribution). Each warp keeps RC chunks in flight in registers; the
 // first ones are requested before the pair tables are built, so the palette fetch
 // and the first code fetches overlap.
-template <typename T, int BITS, int CP, int NWARPS, int RC>
+template <typename T, int BITS, int CP, int NWARPS, int RC, uint32_t TOFF = 0>
 __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, uint8_t* tbl_ptr,
                                             uint32_t tbl_addr, const uint8_t* __restrict__ packed,
                                             const uint16_t* __restrict__ lut, int n_groups, int gs,
@@ -352,15 +357,16 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
 
   uint32_t token;   // defined after the build barrier; part of every lookup address
   asm volatile("mov.u32 %0, 0;" : "=r"(token));
-  const uint32_t tbl_lane = tbl_addr + lane * 4 + token;
+  // TOFF != 0: the table sits at window offset TOFF, which the load instruction adds
+  const uint32_t tbl_lane = (TOFF ? 0u : tbl_addr) + lane * 4 + token;
   for (; c < c1; c += RC * NWARPS) {
 #pragma unroll
     for (int u = 0; u < RC; ++u) {
       const int cu = c + u * NWARPS;
       if (cu < c1) {   // warp-uniform
         const bool more = cu + RC * NWARPS < c1;
-        chunk_math<T, BITS, CP>(acc, w[u], xf[u], tbl_lane, slot_shift, gid,
-                                lane_base + size_t(cu) * chunk_bytes + RC * hop, more ? 1u : 0u);
+        chunk_math<T, BITS, CP, TOFF>(acc, w[u], xf[u], tbl_lane, slot_shift, gid,
+                                      lane_base + size_t(cu) * chunk_bytes + RC * hop, more ? 1u : 0u);
         load_x<CP>(xf[u], x, ldx, more ? M : 0, (cu + RC * NWARPS) * kChunkK, gid, tig);
       }
     }
@@ -400,6 +406,28 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
   }
 }
 
+// sum_r t[m, r] * resA[n, r]: the second factor of the low-rank residual, 8 ranks per step.
+template <typename T>
+__device__ __forceinline__ float residual_dot(const SegDev& sg, int m, int n) {
+  const uint16_t* a = sg.resA + size_t(n) * sg.res_rank;
+  const float* t = sg.res_t + size_t(m) * sg.res_ldt;
+  float v = 0.f;
+  for (int r = 0; r < sg.res_rank; r += 8) {
+    const uint4 aw = __ldg(reinterpret_cast<const uint4*>(a + r));
+    const float4 t0 = __ldcg(reinterpret_cast<const float4*>(t + r));
+    const float4 t1 = __ldcg(reinterpret_cast<const float4*>(t + r + 4));
+    v = fmaf(t0.x, DType<T>::to_float(uint16_t(aw.x & 0xFFFFu)), v);
+    v = fmaf(t0.y, DType<T>::to_float(uint16_t(aw.x >> 16)), v);
+    v = fmaf(t0.z, DType<T>::to_float(uint16_t(aw.y & 0xFFFFu)), v);
+    v = fmaf(t0.w, DType<T>::to_float(uint16_t(aw.y >> 16)), v);
+    v = fmaf(t1.x, DType<T>::to_float(uint16_t(aw.z & 0xFFFFu)), v);
+    v = fmaf(t1.y, DType<T>::to_float(uint16_t(aw.z >> 16)), v);
+    v = fmaf(t1.z, DType<T>::to_float(uint16_t(aw.w & 0xFFFFu)), v);
+    v = fmaf(t1.w, DType<T>::to_float(uint16_t(aw.w >> 16)), v);
+  }
+  return v;
+}
+
 // Fold the K splits of one tile and write the outputs. part[plane][m][row] holds this
 // block's K-range contribution. split == 1: direct; cluster: ranks fold disjoint row
 // ranges through distributed shared memory in rank order; otherwise fp32 partials go
@@ -415,10 +443,12 @@ __device__ __forceinline__ void fold_and_store(const GemvParams& p, float* part,
   const int n0 = tile * kTileRows;
   auto finish = [&](int m, int row, float a, float b) {
     const int n = n0 + row;
+    if (s0.res_rank) a += residual_dot<T>(s0, m, n);
     if (s0.bias) a += DType<T>::to_float(s0.bias[n]);
     float v = a;
     if (silu) {
       const SegDev& s1 = p.seg[si + 1];
+      if (s1.res_rank) b += residual_dot<T>(s1, m, n);
       if (s1.bias) b += DType<T>::to_float(s1.bias[n]);
       v = a / (1.f + __expf(-a)) * b;
     }
@@ -496,15 +526,30 @@ __device__ __forceinline__ void fold_and_store(const GemvParams& p, float* part,
   }
 }
 
-template <typename T, int CP, int NWARPS, int RC>
-__global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p) {
+// Compact form (COMPACT = true): the pair table sits at the fixed window offset kCompactTable
+// right behind the partial sums (lds32o folds the offset into the lookup), a block needs 84 KB
+// of shared memory instead of 144 KB, runs 8 warps, and TWO blocks share an SM. A launch then
+// has 296 block slots: 96-tile projections fill the machine with a K split of 3 instead of
+// leaving 52 SMs idle, and the blocks of the next launch in a programmatic chain can move in
+// beside a launch that does not fill every slot.
+constexpr uint32_t kCompactTable = 20480;   // window offset of the table in the compact form
+
+template <typename T, int CP, int NWARPS, int RC, bool COMPACT>
+__global__ void __launch_bounds__(NWARPS * 32, COMPACT ? 2 : 1) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   constexpr int NT = NWARPS * 32;
+  constexpr uint32_t TOFF = COMPACT ? kCompactTable : 0u;
 
   float* part = reinterpret_cast<float*>(smem);   // [plane][m][row]
   const uint32_t part_addr = smem_u32(smem);
-  const uint32_t tbl_addr = (part_addr + kPartBytes + 0xFFFFu) & ~0xFFFFu;
+  const uint32_t tbl_addr = COMPACT ? kCompactTable : ((part_addr + kPartBytes + 0xFFFFu) & ~0xFFFFu);
   uint8_t* tbl_ptr = smem + (tbl_addr - part_addr);
+  if (COMPACT && (part_addr + kPartBytes > kCompactTable ||
+                  kCompactTable + kTableBytes > part_addr + p.smem_bytes)) {
+    // the shared window does not start where the host assumed: leave loudly (block-uniform)
+    if (threadIdx.x == 0) atomicExch(&g_exchange_status, 0x6100);
+    return;
+  }
 
   // which tile / split is this block
   const int split = p.split;
@@ -557,7 +602,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
 #define TRACE_ARG
 #endif
 #define B200LUT_PASS(B)                                                                       \
-  stream_pass<T, B, CP, NWARPS, RC>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups,  \
+  stream_pass<T, B, CP, NWARPS, RC, TOFF>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups,  \
                                     sg.gs, tile, p.G, c0, c1, p.x, p.ldx, M, !first,              \
                                     DepWait{first ? 1 : 0, nullptr, 0, nullptr, (first && p.ex.wait) ? &p.ex : nullptr TRACE_ARG})
       switch (bits) {   // block-uniform
@@ -624,17 +669,21 @@ size_t smem_bytes_for(int max_tables) {
   return size_t(kPartBytes) + 65536 + size_t(max_tables) * kTableBytes;
 }
 
-template <typename T, int CP, int NWARPS, int RC>
-int launch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t stream) {
-  auto kern = gemv_kernel<T, CP, NWARPS, RC>;
-  const size_t smem = smem_bytes_for(max_tables);
+size_t compact_smem_bytes() { return size_t(kCompactTable) + kTableBytes; }   // from window offset 1 KB, with slack
+
+template <typename T, int CP, int NWARPS, int RC, bool COMPACT = false>
+int launch(const GemvParams& p_in, int max_tables, bool pdl, cudaStream_t stream) {
+  auto kern = gemv_kernel<T, CP, NWARPS, RC, COMPACT>;
+  const size_t smem = COMPACT ? compact_smem_bytes() : smem_bytes_for(max_tables);
+  GemvParams p = p_in;
+  p.smem_bytes = uint32_t(smem);
   static size_t configured[64] = {0};
   int dev = 0;
   B200LUT_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 64 && configured[dev] < smem) {
-    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         int(smem_bytes_for(2))));
-    configured[dev] = smem_bytes_for(2);
+    const size_t want = COMPACT ? compact_smem_bytes() : smem_bytes_for(2);
+    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(want)));
+    configured[dev] = want;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(unsigned(p.tiles_total * p.split), 1, 1);
@@ -703,6 +752,22 @@ int convert_segments(const b200lut_segment* segs, int nseg, bool silu, SegDev* o
     d.n_groups = s.n_groups;
     d.bits = s.bits;
     d.bits2 = has2 ? s.bits2 : 0;
+    B200LUT_REQUIRE(s.res_rank >= 0 && s.res_rank <= 4096 && s.res_rank % 8 == 0,
+                    B200LUT_ERR_UNSUPPORTED,
+                    "segment %d: residual rank must be a multiple of 8 up to 4096, got %d", i,
+                    s.res_rank);
+    if (s.res_rank > 0) {
+      B200LUT_REQUIRE(s.resA && s.res_t && s.res_ldt >= s.res_rank, B200LUT_ERR_INVALID,
+                      "segment %d: the residual needs resA, res_t and res_ldt >= rank", i);
+      B200LUT_REQUIRE(aligned16(s.resA) && aligned16(s.res_t) && s.res_ldt % 4 == 0,
+                      B200LUT_ERR_ALIGN,
+                      "segment %d: resA and res_t must be 16-byte aligned, res_ldt a multiple of 4", i);
+    }
+    d.resA = static_cast<const uint16_t*>(s.resA);
+    d.res_t = s.res_t;
+    d.res_ldt = s.res_ldt;
+    d.res_rank = s.res_rank;
+    d.pad = 0;
     if (silu && (i % 2 == 1)) {
       d.tile_begin = out[i - 1].tile_begin;
     } else {
@@ -716,18 +781,8 @@ int convert_segments(const b200lut_segment* segs, int nseg, bool silu, SegDev* o
 }
 
 template <typename T>
-int dispatch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t st) {
-  static const int plan = [] { const char* e = getenv("B200LUT_GEMV_PLAN"); return e ? atoi(e) : 0; }();
-  if (p.M == 1 && plan == 122) return launch<T, 1, 12, 2>(p, max_tables, pdl, st);
-  if (p.M == 1 && plan == 121) return launch<T, 1, 12, 1>(p, max_tables, pdl, st);
-  if (p.M == 1 && plan == 83) return launch<T, 1, 8, 3>(p, max_tables, pdl, st);
-  if (p.M == 1 && plan == 84) return launch<T, 1, 8, 2>(p, max_tables, pdl, st);
-  if (p.M == 1 && plan == 11) return launch<T, 1, kWarpsM8, 1>(p, max_tables, pdl, st);
-  if (p.M == 1 && plan == 21) return launch<T, 2, kWarpsM8, 1>(p, max_tables, pdl, st);
-  if (p.M == 1 && plan == 81) return launch<T, 8, kWarpsM8, 1>(p, max_tables, pdl, st);
-  if (p.M == 1 && plan == 82) return launch<T, 8, kWarpsM8, 2>(p, max_tables, pdl, st);
-  if (p.M == 1 && plan == 42) return launch<T, 4, kWarpsM8, 2>(p, max_tables, pdl, st);
-  if (p.M == 1 && plan == 22) return launch<T, 2, kWarpsM8, 2>(p, max_tables, pdl, st);
+int dispatch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t st, bool compact = false) {
+  if (compact && p.M == 1 && max_tables == 1) return launch<T, 1, 8, 1, true>(p, max_tables, pdl, st);
   if (p.M == 1) return launch<T, 1, kWarpsM8, 1>(p, max_tables, pdl, st);
   if (p.M == 2) return launch<T, 2, kWarpsM8, 2>(p, max_tables, pdl, st);
   if (p.M <= 4) return launch<T, 4, kWarpsM8, 2>(p, max_tables, pdl, st);
@@ -907,7 +962,14 @@ extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, i
   if (int rc = convert_segments(segs, nseg, silu, p.seg, &tiles, &max_tables)) return rc;
   p.tiles_total = tiles;
   const int warps = M <= 8 ? kWarpsM8 : kWarpsM16;
-  if (split <= 0) split = pick_split(tiles, p.G, sm_count_cached(), warps);
+  bool compact = false;
+  if (split <= 0) {
+    split = pick_split(tiles, p.G, sm_count_cached(), warps);
+    if (M == 1 && max_tables == 1) {
+      static const int force = [] { const char* e = getenv("B200LUT_GEMV_COMPACT"); return e ? atoi(e) : -1; }();
+      if (force > 0 && force <= kMaxClusterSplit && force <= p.G) { compact = true; split = force; }
+    }
+  }
   B200LUT_REQUIRE(split >= 1 && split <= 16 && split <= p.G, B200LUT_ERR_INVALID,
                   "split must be 1..16 and <= K/64, got %d", split);
   p.split = split;
@@ -927,8 +989,8 @@ extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, i
                   p.ex.blocks, tiles, split);
   const bool pdl = (flags & 1) != 0;
   cudaStream_t st = cudaStream_t(stream);
-  if (dtype == B200LUT_BF16) return dispatch<__nv_bfloat16>(p, max_tables, pdl, st);
-  return dispatch<__half>(p, max_tables, pdl, st);
+  if (dtype == B200LUT_BF16) return dispatch<__nv_bfloat16>(p, max_tables, pdl, st, compact);
+  return dispatch<__half>(p, max_tables, pdl, st, compact);
 }
 
 extern "C" int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out, int M,
@@ -985,6 +1047,9 @@ int plan_layout(const b200lut_job* jobs, int njobs, int M, int dtype, int grid, 
                     "job %d: the silu-mul epilogue needs (gate, up) segment pairs", j);
     int tiles = 0, max_tables = 1;
     if (int rc = convert_segments(src.segs, src.nseg, silu, d.seg, &tiles, &max_tables)) return rc;
+    for (int q = 0; q < src.nseg; ++q)
+      B200LUT_REQUIRE(src.segs[q].res_rank == 0, B200LUT_ERR_UNSUPPORTED,
+                      "job %d: the fused residual is served by b200lut_gemv_multi, not by a plan", j);
     B200LUT_REQUIRE(max_tables <= 1, B200LUT_ERR_UNSUPPORTED,
                     "job %d: a plan serves group sizes >= 64 (two palettes per tile at most)", j);
     d.x = static_cast<const uint16_t*>(src.x);

@@ -243,11 +243,13 @@ class PalettizedLinear(nn.Module):
 
     # ---------------------------------------------------------------- pieces
     def _segment_desc(self, out: Optional[torch.Tensor], ldo: Optional[int] = None,
-                      with_bias: bool = True) -> dict:
+                      with_bias: bool = True, res_t: Optional[torch.Tensor] = None) -> dict:
         self._ensure_packed()
         d = dict(packed=self._packed, lut=self.lut, N=self.N, group_size=self.group_size,
                  n_groups=self.lut.shape[0], bits=self.bitwidth, out=out,
                  ldo=self.N if ldo is None else ldo)
+        if res_t is not None:          # fused low-rank residual: t = x @ resB^T computed by the caller
+            d.update(resA=self.resA, res_t=res_t)
         if self.has_stream2:
             d.update(packed2=self._packed2, lut2=self.lut2, bits2=self.bitwidth2)
         if with_bias and self.bias is not None:
@@ -270,13 +272,24 @@ class PalettizedLinear(nn.Module):
             return _fht.fht_apply_awq(x, signs, self._on("awq", self.awq_scale, x.device))
         return _fht.fht_apply(x, signs)
 
-    def _kernel_matmul(self, x2: torch.Tensor) -> torch.Tensor:
-        """x2 [M, K] in the compute dtype -> [M, N] (streams + bias)."""
+    def _fusable_residual(self, x2: torch.Tensor) -> bool:
+        """Decode rows, rank a multiple of 8, factors in the compute dtype and 16-byte aligned:
+        the residual rides the GEMV (one projection launch + the epilogue)."""
+        return (self.has_residual() and 0 < x2.shape[0] <= GEMV_MAX_M
+                and self.resA.shape[1] % 8 == 0 and self.resA.dtype == x2.dtype
+                and self.resB.dtype == x2.dtype and self.resA.is_contiguous()
+                and self.resB.is_contiguous() and self.resA.data_ptr() % 16 == 0
+                and self.resB.data_ptr() % 16 == 0)
+
+    def _kernel_matmul(self, x2: torch.Tensor, fuse_residual: bool = False) -> torch.Tensor:
+        """x2 [M, K] in the compute dtype -> [M, N] (streams + bias, and the low-rank
+        residual when fuse_residual)."""
         M = x2.shape[0]
         out = torch.empty(M, self.N, dtype=x2.dtype, device=x2.device)
         if M == 0:
             return out
-        segs = _lib.make_segments([self._segment_desc(out)])
+        res_t = _lib.residual_project(x2, self.resB, flags=_flags()) if fuse_residual else None
+        segs = _lib.make_segments([self._segment_desc(out, res_t=res_t)])
         if M <= GEMV_MAX_M:
             _lib.gemv_multi(x2, segs, 1, flags=_flags())
         elif self.bitwidth == 4 and (not self.has_stream2 or self.bitwidth2 == 4):
@@ -339,9 +352,10 @@ class PalettizedLinear(nn.Module):
             xc = x2 if x2.dtype == cd else x2.to(cd)
             if xc.stride(-1) != 1 or xc.stride(0) % 8 or xc.data_ptr() % 16:
                 xc = xc.contiguous().clone() if xc.data_ptr() % 16 else xc.contiguous()
-            out = self._kernel_matmul(xc).to(x.dtype)
+            residual_done = self._fusable_residual(xc)
+            out = self._kernel_matmul(xc, fuse_residual=residual_done).to(x.dtype)
             bias_done = True
-        if self.has_residual():
+        if self.has_residual() and not (not self.reference and residual_done):
             xr = x2.to(self.resA.dtype)
             out = out + ((xr @ self.resB.t()) @ self.resA.t()).to(out.dtype)
         if self.bias is not None and not bias_done:

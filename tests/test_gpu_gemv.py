@@ -188,3 +188,55 @@ def test_persistent_plan_matches_per_launch_results():
                 assert rel_err(got, w) <= 5e-3     # same math, other K split points: one bf16 ulp
         assert rel_err(obuf, o.oracle(x.cpu())) <= TOL
         assert rel_err(y, down.oracle(act.cpu())) <= TOL
+
+
+# ---- fused low-rank residual ------------------------------------------------------------------
+@pytest.mark.parametrize("M,K,R,dtype", ((1, 4096, 32, torch.bfloat16), (16, 1024, 256, torch.float16),
+                                          (5, 192, 8, torch.bfloat16)))
+def test_residual_projection_is_the_fp32_product(M, K, R, dtype):
+    g = torch.Generator().manual_seed(K + R)
+    x = torch.randn(M, K, generator=g).to(dtype).cuda()
+    resB = (0.05 * torch.randn(R, K, generator=g)).to(dtype).cuda()
+    t = L.residual_project(x, resB)
+    torch.cuda.synchronize()
+    want = x.double() @ resB.double().t()
+    assert rel_err(t.double().cpu(), want.cpu()) <= 1e-5
+    t2 = L.residual_project(x, resB)
+    assert torch.equal(t, t2)                       # fixed summation order
+
+
+@pytest.mark.parametrize("N,K,gs,bits,dtype,M,R", (
+    (4096, 4096, 128, 4, torch.bfloat16, 1, 32),    # the deployed recipe: 4-bit + rank 32
+    (512, 1024, 64, 3, torch.float16, 16, 256),
+    (256, 256, 128, 4, torch.bfloat16, 3, 8),
+))
+def test_fused_residual_matches_oracle(N, K, gs, bits, dtype, M, R):
+    case = Case(N, K, gs, bits, dtype, seed=N + R, residual=R, bias=True)
+    x = case.x(M)
+    mod = case.module()
+    assert mod._fusable_residual(x.cuda())
+    got = mod(x.cuda())
+    torch.cuda.synchronize()
+    want = orc.linear_forward(x, case.w1, None, case.resA, case.resB, case.bias)
+    assert rel_err(got.float().cpu(), want.float()) <= TOL
+    # the residual really is in the kernel's output: without it the error is large
+    plain = orc.linear_forward(x, case.w1, None, None, None, case.bias)
+    assert rel_err(plain.float(), want.float()) > 5 * TOL
+
+
+def test_fused_residual_in_a_gate_up_pair():
+    N, K, R, M, dt = 512, 1024, 32, 2, torch.bfloat16
+    gate, up = Case(N, K, 128, 4, dt, seed=1, residual=R), Case(N, K, 128, 4, dt, seed=2, residual=R)
+    x = gate.x(M).cuda()
+    g, u = gate.module(), up.module()
+    resB = torch.cat([g.resB, u.resB], dim=0).contiguous()          # stacked first factors
+    t = L.residual_project(x, resB)
+    out = torch.empty(M, N, dtype=dt, device="cuda")
+    descs = [g._segment_desc(out, res_t=t[:, :R]), u._segment_desc(None, res_t=t[:, R:])]
+    L.gemv_multi(x, L.make_segments(descs), 2, epilogue=L.EPI_SILU_MUL)
+    torch.cuda.synchronize()
+    xf = x.float().cpu()
+    gf = xf @ gate.w1.t() + (xf @ gate.resB.float().t()) @ gate.resA.float().t()
+    uf = xf @ up.w1.t() + (xf @ up.resB.float().t()) @ up.resA.float().t()
+    want = orc.silu_mul_fused(gf, uf, dt)
+    assert rel_err(out.float().cpu(), want.float()) <= TOL

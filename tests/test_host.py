@@ -61,6 +61,19 @@ def test_validation_errors_carry_a_message():
     seg.group_size = 48
     rc = L.b200lut_gemv_multi(x, 64, 1, 64, 0, ctypes.byref(seg), 1, 0, 0, None, 0, 0, None)
     assert rc == 2 and b"group_size" in L.b200lut_last_error()
+    seg.group_size, seg.res_rank = 128, 12
+    rc = L.b200lut_gemv_multi(x, 64, 1, 64, 0, ctypes.byref(seg), 1, 0, 0, None, 0, 0, None)
+    assert rc == 2 and b"residual rank" in L.b200lut_last_error()
+    seg.res_rank = 16
+    rc = L.b200lut_gemv_multi(x, 64, 1, 64, 0, ctypes.byref(seg), 1, 0, 0, None, 0, 0, None)
+    assert rc == 1 and b"resA" in L.b200lut_last_error()
+    rc = L.b200lut_gemm(x, 64, 32, 64, 0, ctypes.byref(seg), 0, 0, None)
+    assert rc == 2 and b"residual" in L.b200lut_last_error()
+    seg.res_rank = 0
+    rc = L.b200lut_residual_project(x, 64, 17, 64, 0, x, 8, x, 8, 0, None)
+    assert rc == 2 and b"M=17" in L.b200lut_last_error()
+    rc = L.b200lut_residual_project(x, 64, 1, 64, 0, None, 8, x, 8, 0, None)
+    assert rc == 1 and b"null" in L.b200lut_last_error()
     rc = L.b200lut_fht(x, x, None, None, 1, 96, 96, 96, 0, 0, 64, None)
     assert rc == 1 and b"block" in L.b200lut_last_error()
 
