@@ -96,7 +96,6 @@ struct GemvParams {
   const uint16_t* x;
   long long ldx;
   int M, K, G, nseg, split, epilogue, tiles_total, cluster;
-  uint32_t smem_bytes;   // dynamic shared memory of the launch
   float* ws;       // workspace fold: [split][tiles_total][planes][M][128] fp32
   int* tickets;    // workspace fold: [tiles_total]
   SegDev seg[kMaxSeg];
@@ -244,7 +243,7 @@ __device__ __forceinline__ void load_x(uint2 (&xf)[Plan<CP>::kNB][4],
 
 // Look up and multiply one chunk held in w; refill each 1 KB plane of w from `next`
 // (when `more`) as soon as its last field has been used.
-template <typename T, int BITS, int CP, uint32_t TOFF = 0>
+template <typename T, int BITS, int CP>
 __device__ __forceinline__ void chunk_math(float (&acc)[Plan<CP>::kAcc][4], uint32_t (&w)[8 * BITS],
                                            const uint2 (&xf)[Plan<CP>::kNB][4], uint32_t tbl_lane,
                                            int slot_shift, int gid, const uint8_t* next,
@@ -259,7 +258,7 @@ __device__ __forceinline__ void chunk_math(float (&acc)[Plan<CP>::kAcc][4], uint
     for (int kt = 0; kt < 4; ++kt) {
       uint32_t a[4];
 #pragma unroll
-      for (int f = 0; f < 4; ++f) a[f] = lds32o<TOFF>(field_addr<BITS>(w, s, 4 * kt + f, base));
+      for (int f = 0; f < 4; ++f) a[f] = lds32(field_addr<BITS>(w, s, 4 * kt + f, base));
 #pragma unroll
       for (int nb = 0; nb < P::kNB; ++nb) {
         const uint32_t b0 = (P::kSlabsPerAcc == 1 || mine) ? xf[nb][kt].x : 0u;
@@ -278,7 +277,7 @@ __device__ __forceinline__ void chunk_math(float (&acc)[Plan<CP>::kAcc][4], uint
 // K-range contribution). Each warp keeps RC chunks in flight in registers; the
 // first ones are requested before the pair tables are built, so the palette fetch
 // and the first code fetches overlap.
-template <typename T, int BITS, int CP, int NWARPS, int RC, uint32_t TOFF = 0>
+template <typename T, int BITS, int CP, int NWARPS, int RC>
 __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, uint8_t* tbl_ptr,
                                             uint32_t tbl_addr, const uint8_t* __restrict__ packed,
                                             const uint16_t* __restrict__ lut, int n_groups, int gs,
@@ -357,16 +356,15 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
 
   uint32_t token;   // defined after the build barrier; part of every lookup address
   asm volatile("mov.u32 %0, 0;" : "=r"(token));
-  // TOFF != 0: the table sits at window offset TOFF, which the load instruction adds
-  const uint32_t tbl_lane = (TOFF ? 0u : tbl_addr) + lane * 4 + token;
+  const uint32_t tbl_lane = tbl_addr + lane * 4 + token;
   for (; c < c1; c += RC * NWARPS) {
 #pragma unroll
     for (int u = 0; u < RC; ++u) {
       const int cu = c + u * NWARPS;
       if (cu < c1) {   // warp-uniform
         const bool more = cu + RC * NWARPS < c1;
-        chunk_math<T, BITS, CP, TOFF>(acc, w[u], xf[u], tbl_lane, slot_shift, gid,
-                                      lane_base + size_t(cu) * chunk_bytes + RC * hop, more ? 1u : 0u);
+        chunk_math<T, BITS, CP>(acc, w[u], xf[u], tbl_lane, slot_shift, gid,
+                                lane_base + size_t(cu) * chunk_bytes + RC * hop, more ? 1u : 0u);
         load_x<CP>(xf[u], x, ldx, more ? M : 0, (cu + RC * NWARPS) * kChunkK, gid, tig);
       }
     }
@@ -473,6 +471,9 @@ __device__ __forceinline__ void fold_and_store(const GemvParams& p, float* part,
   }
 
   if (p.cluster) {
+    // Pull fold. (A push variant — every rank stores its partial rows into the owners' shared
+    // memory and ONE cluster barrier follows — was measured slower: 7.3 vs 6.6 us per launch
+    // of the 4096 x 4096 projection.)
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();   // every rank's part[] is complete and visible
     const int rank = int(cluster.block_rank());
@@ -526,30 +527,15 @@ __device__ __forceinline__ void fold_and_store(const GemvParams& p, float* part,
   }
 }
 
-// Compact form (COMPACT = true): the pair table sits at the fixed window offset kCompactTable
-// right behind the partial sums (lds32o folds the offset into the lookup), a block needs 84 KB
-// of shared memory instead of 144 KB, runs 8 warps, and TWO blocks share an SM. A launch then
-// has 296 block slots: 96-tile projections fill the machine with a K split of 3 instead of
-// leaving 52 SMs idle, and the blocks of the next launch in a programmatic chain can move in
-// beside a launch that does not fill every slot.
-constexpr uint32_t kCompactTable = 20480;   // window offset of the table in the compact form
-
-template <typename T, int CP, int NWARPS, int RC, bool COMPACT>
-__global__ void __launch_bounds__(NWARPS * 32, COMPACT ? 2 : 1) gemv_kernel(const GemvParams p) {
+template <typename T, int CP, int NWARPS, int RC>
+__global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   constexpr int NT = NWARPS * 32;
-  constexpr uint32_t TOFF = COMPACT ? kCompactTable : 0u;
 
   float* part = reinterpret_cast<float*>(smem);   // [plane][m][row]
   const uint32_t part_addr = smem_u32(smem);
-  const uint32_t tbl_addr = COMPACT ? kCompactTable : ((part_addr + kPartBytes + 0xFFFFu) & ~0xFFFFu);
+  const uint32_t tbl_addr = (part_addr + kPartBytes + 0xFFFFu) & ~0xFFFFu;
   uint8_t* tbl_ptr = smem + (tbl_addr - part_addr);
-  if (COMPACT && (part_addr + kPartBytes > kCompactTable ||
-                  kCompactTable + kTableBytes > part_addr + p.smem_bytes)) {
-    // the shared window does not start where the host assumed: leave loudly (block-uniform)
-    if (threadIdx.x == 0) atomicExch(&g_exchange_status, 0x6100);
-    return;
-  }
 
   // which tile / split is this block
   const int split = p.split;
@@ -602,7 +588,7 @@ __global__ void __launch_bounds__(NWARPS * 32, COMPACT ? 2 : 1) gemv_kernel(cons
 #define TRACE_ARG
 #endif
 #define B200LUT_PASS(B)                                                                       \
-  stream_pass<T, B, CP, NWARPS, RC, TOFF>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups,  \
+  stream_pass<T, B, CP, NWARPS, RC>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups,  \
                                     sg.gs, tile, p.G, c0, c1, p.x, p.ldx, M, !first,              \
                                     DepWait{first ? 1 : 0, nullptr, 0, nullptr, (first && p.ex.wait) ? &p.ex : nullptr TRACE_ARG})
       switch (bits) {   // block-uniform
@@ -669,21 +655,17 @@ size_t smem_bytes_for(int max_tables) {
   return size_t(kPartBytes) + 65536 + size_t(max_tables) * kTableBytes;
 }
 
-size_t compact_smem_bytes() { return size_t(kCompactTable) + kTableBytes; }   // from window offset 1 KB, with slack
-
-template <typename T, int CP, int NWARPS, int RC, bool COMPACT = false>
-int launch(const GemvParams& p_in, int max_tables, bool pdl, cudaStream_t stream) {
-  auto kern = gemv_kernel<T, CP, NWARPS, RC, COMPACT>;
-  const size_t smem = COMPACT ? compact_smem_bytes() : smem_bytes_for(max_tables);
-  GemvParams p = p_in;
-  p.smem_bytes = uint32_t(smem);
+template <typename T, int CP, int NWARPS, int RC>
+int launch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t stream) {
+  auto kern = gemv_kernel<T, CP, NWARPS, RC>;
+  const size_t smem = smem_bytes_for(max_tables);
   static size_t configured[64] = {0};
   int dev = 0;
   B200LUT_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 64 && configured[dev] < smem) {
-    const size_t want = COMPACT ? compact_smem_bytes() : smem_bytes_for(2);
-    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(want)));
-    configured[dev] = want;
+    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         int(smem_bytes_for(2))));
+    configured[dev] = smem_bytes_for(2);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(unsigned(p.tiles_total * p.split), 1, 1);
@@ -781,8 +763,7 @@ int convert_segments(const b200lut_segment* segs, int nseg, bool silu, SegDev* o
 }
 
 template <typename T>
-int dispatch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t st, bool compact = false) {
-  if (compact && p.M == 1 && max_tables == 1) return launch<T, 1, 8, 1, true>(p, max_tables, pdl, st);
+int dispatch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t st) {
   if (p.M == 1) return launch<T, 1, kWarpsM8, 1>(p, max_tables, pdl, st);
   if (p.M == 2) return launch<T, 2, kWarpsM8, 2>(p, max_tables, pdl, st);
   if (p.M <= 4) return launch<T, 4, kWarpsM8, 2>(p, max_tables, pdl, st);
@@ -962,14 +943,7 @@ extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, i
   if (int rc = convert_segments(segs, nseg, silu, p.seg, &tiles, &max_tables)) return rc;
   p.tiles_total = tiles;
   const int warps = M <= 8 ? kWarpsM8 : kWarpsM16;
-  bool compact = false;
-  if (split <= 0) {
-    split = pick_split(tiles, p.G, sm_count_cached(), warps);
-    if (M == 1 && max_tables == 1) {
-      static const int force = [] { const char* e = getenv("B200LUT_GEMV_COMPACT"); return e ? atoi(e) : -1; }();
-      if (force > 0 && force <= kMaxClusterSplit && force <= p.G) { compact = true; split = force; }
-    }
-  }
+  if (split <= 0) split = pick_split(tiles, p.G, sm_count_cached(), warps);
   B200LUT_REQUIRE(split >= 1 && split <= 16 && split <= p.G, B200LUT_ERR_INVALID,
                   "split must be 1..16 and <= K/64, got %d", split);
   p.split = split;
@@ -989,8 +963,8 @@ extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, i
                   p.ex.blocks, tiles, split);
   const bool pdl = (flags & 1) != 0;
   cudaStream_t st = cudaStream_t(stream);
-  if (dtype == B200LUT_BF16) return dispatch<__nv_bfloat16>(p, max_tables, pdl, st, compact);
-  return dispatch<__half>(p, max_tables, pdl, st, compact);
+  if (dtype == B200LUT_BF16) return dispatch<__nv_bfloat16>(p, max_tables, pdl, st);
+  return dispatch<__half>(p, max_tables, pdl, st);
 }
 
 extern "C" int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out, int M,

@@ -50,17 +50,6 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   return v;
 }
 
-// The same lookup with a compile-time byte offset folded into the load instruction: the table
-// may then sit at (64 KB multiple) + OFF in the shared window — the permute still delivers an
-// address whose bits 8..15 are the code byte — instead of on a 64 KB boundary, which costs
-// up to 64 KB of padding per block.
-template <uint32_t OFF>
-__device__ __forceinline__ uint32_t lds32o(uint32_t addr) {
-  uint32_t v;
-  asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
-  return v;
-}
-
 // Fill the pair table(s) of one pass: entry v -> LUT[v & mask] | LUT[v >> bits] << 16,
 // one table slot per distinct palette of the tile (nl = 1, 2 or 4 palettes per tile).
 __device__ void build_tables(uint8_t* tbl_ptr, const uint16_t* __restrict__ lut, int bits,

@@ -364,18 +364,42 @@ class PalettizedLinear(nn.Module):
 
 
 def _mergeable(mods, x: torch.Tensor) -> bool:
-    """Decode-merge verdict: M <= 16, same K, unrotated, no residual, one dtype."""
-    if x.reshape(-1, x.shape[-1]).shape[0] > GEMV_MAX_M or not x.is_cuda:
+    """Decode-merge verdict: M <= 16, same K, unrotated, one dtype, and every low-rank
+    residual of a kind the GEMV epilogue serves."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.shape[0] > GEMV_MAX_M or x2.shape[0] == 0 or not x.is_cuda:
         return False
     m0 = mods[0]
     for m in mods:
         if not isinstance(m, PalettizedLinear) or m.reference or m.K != m0.K:
             return False
-        if m.rot_signs is not None or m.has_residual() or m.lut.dtype != m0.lut.dtype:
+        if m.rot_signs is not None or m.lut.dtype != m0.lut.dtype:
             return False
         if m.lut.dtype not in (torch.float16, torch.bfloat16):
             return False
+        if m.has_residual() and not m._fusable_residual(x2.to(m.lut.dtype)):
+            return False
     return True
+
+
+def _stacked_residual(owner: nn.Module, mods, x2: torch.Tensor):
+    """One projection launch for all residuals of a merged launch: the rB factors are
+    stacked once (cached on the owner), t = x2 @ stack^T, and each module gets its slice."""
+    with_res = [m for m in mods if m.has_residual()]
+    if not with_res:
+        return {}
+    key = tuple(m.resB.data_ptr() for m in with_res)
+    cache = owner.__dict__.get("_resB_stack")
+    if cache is None or cache[0] != key:
+        cache = (key, torch.cat([m.resB for m in with_res], dim=0).contiguous())
+        owner.__dict__["_resB_stack"] = cache
+    t = _lib.residual_project(x2, cache[1], flags=_flags())
+    out, off = {}, 0
+    for m in with_res:
+        r = m.resB.shape[0]
+        out[id(m)] = t[:, off:off + r]
+        off += r
+    return out
 
 
 class SplitQKV(nn.Module):
@@ -395,9 +419,10 @@ class SplitQKV(nn.Module):
         x2 = x.reshape(-1, x.shape[-1]).to(cd).contiguous()
         total = sum(m.N for m in mods)
         out = torch.empty(x2.shape[0], total, dtype=cd, device=x.device)
+        res = _stacked_residual(self, mods, x2)
         descs, off = [], 0
         for m in mods:
-            descs.append(m._segment_desc(out[:, off:], ldo=total))
+            descs.append(m._segment_desc(out[:, off:], ldo=total, res_t=res.get(id(m))))
             off += m.N
         _lib.gemv_multi(x2, _lib.make_segments(descs), len(descs), flags=_flags())
         return out.to(x.dtype).reshape(*x.shape[:-1], total)
@@ -419,7 +444,8 @@ class FusedPalettizedMLP(nn.Module):
     def fused_gate_up(self, x2: torch.Tensor) -> torch.Tensor:
         g, u = self.gate_proj, self.up_proj
         out = torch.empty(x2.shape[0], g.N, dtype=x2.dtype, device=x2.device)
-        descs = [g._segment_desc(out), u._segment_desc(None)]
+        res = _stacked_residual(self, (g, u), x2)
+        descs = [g._segment_desc(out, res_t=res.get(id(g))), u._segment_desc(None, res_t=res.get(id(u)))]
         epi = _lib.EPI_SILU_MUL
         if x2.shape[0] <= GEMV_MAX_M:
             _lib.gemv_multi(x2, _lib.make_segments(descs), 2, epilogue=epi, flags=_flags())
