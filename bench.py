@@ -389,6 +389,12 @@ def main() -> int:
             stack.step_persistent(M, gather=gather)
         else:
             stack.step(M, flags=flags, gather=gather)
+    if world > 1:
+        # ranks reach this point at different times (allocation, page locking); the exchange
+        # waits inside the kernels are bounded, so line the ranks up before the first step
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier()
     trace("first eager step")
     run_step()
     torch.cuda.synchronize()

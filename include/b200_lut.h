@@ -187,7 +187,7 @@ int b200lut_gemv_noalloc(const void* x, const void* packed, const void* lut, voi
  * element into its own buffer AND, over NVLink, at the same position of every peer's buffer;
  * every block of the grid then writes this rank's push count into its own flag word in every
  * rank's flag array (one system-wide fence per block, no serialisation behind a last
- * block); the consuming GEMV waits (bounded, about 20 ms; on expiry the launch carries on
+ * block); the consuming GEMV waits (bounded, about one second; on expiry the launch carries on
  * and b200lut_device_status() turns nonzero) until all world x producer_blocks flags have
  * reached the number of waits done on the channel plus one, and only then reads its
  * activation rows. With programmatic dependent launch the waiting launch does not wait for

@@ -164,6 +164,9 @@ struct DepWait {
 };
 
 constexpr long long kDepWaitCycles = 40000000;   // ~20 ms: far beyond any healthy wait
+// Waits on OTHER processes' kernels get a second: ranks drift apart by host-side work
+// (allocation, page locking, a late start) far more than blocks of one launch do.
+constexpr long long kPeerWaitCycles = 2000000000;
 
 __device__ __forceinline__ int ld_acquire(const int* p) {
   int v;
@@ -205,7 +208,7 @@ __device__ __forceinline__ void peer_poll(const ExchangeDev& ex, int idx) {
     if (arrived()) return;
     if ((i & 15u) == 0u) {
       if (*reinterpret_cast<volatile int*>(ex.status) != 0) return;
-      if (clock64() - t0 > kDepWaitCycles) break;
+      if (clock64() - t0 > kPeerWaitCycles) break;
     }
   }
   atomicExch(ex.status, 0x7000 + idx / ex.blocks);
