@@ -474,7 +474,13 @@ def main() -> int:
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "gemv_plan_kernel" if use_plan else "gemv_kernel", "achieved": achieved,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                     "peak_source": peaks["source"], "traffic": None,
+                     "peak_source": peaks["source"],
+                     # DRAM bytes per launch: the ncu capture of this kernel on the 12288 x 4096
+                     # projection read 25.25 MB for 25.20 MB of algorithmic bytes and wrote none
+                     # (profiles/gemv_kernel_12288x4096_m1.md); traffic grows with the codes, so
+                     # the ratio is applied to the average launch of the step
+                     "traffic": None if use_plan else 1.002 * bytes_rank / kernel_launches,
+                     "traffic_source": "ncu dram__bytes ratio 1.002 of the 12288x4096 capture, scaled",
                      "bytes_per_launch": bytes_rank / kernel_launches,
                      "us_per_launch": ms_step * 1e3 / kernel_launches,
                      "projection_groups_per_step": launches},
