@@ -386,6 +386,50 @@ struct PersistParams {
   long long wait_cycles;   // bound of every in-kernel wait, in SM clock cycles
 };
 
+// 64-bit code load (two consecutive words of a lane's string), executed only when `on`.
+__device__ __forceinline__ void ldg64_if(uint32_t* r, const uint8_t* ptr, uint32_t on) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %3, 0;\n\t"
+      "@q ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];\n\t}"
+      : "+r"(r[0]), "+r"(r[1])
+      : "l"(ptr), "r"(on));
+}
+
+// The 2 * BITS words of lane-string that hold row slabs 2q and 2q + 1 of one chunk
+// (`chunk_lane` = chunk base + 32 * lane). At 4 bits they are one whole 256-bit plane; at
+// other widths they straddle planes and come as BITS 64-bit loads.
+template <int BITS>
+__device__ __forceinline__ void load_slab_pair(uint32_t (&w)[2 * BITS], const uint8_t* chunk_lane,
+                                               int q, uint32_t on) {
+  if constexpr (BITS == 4) {
+    ldg_stream256_if(w, chunk_lane + q * 1024, on);
+  } else {
+#pragma unroll
+    for (int j = 0; j < BITS; ++j) {
+      const int m = 2 * BITS * q + 2 * j;
+      ldg64_if(&w[2 * j], chunk_lane + (m >> 3) * 1024 + 4 * (m & 7), on);
+    }
+  }
+}
+
+// Pair-table address of field i (0..15) of local slab sl (0, 1): the field's 2 * BITS bits
+// moved to address bits 8.., joined with the lane base.
+template <int BITS>
+__device__ __forceinline__ uint32_t slab_field_addr(const uint32_t (&w)[2 * BITS], int sl, int i,
+                                                    uint32_t base) {
+  if constexpr (BITS == 4) {
+    return __byte_perm(w[4 * sl + (i >> 2)], base, 0x7604u | (uint32_t(i & 3) << 4));
+  } else {
+    constexpr uint32_t kMask = ((1u << (2 * BITS)) - 1u) << 8;
+    const int pos = 32 * BITS * sl + 2 * BITS * i, m = pos >> 5, sh = pos & 31;
+    uint32_t v;
+    if (sh + 2 * BITS > 32) v = __funnelshift_r(w[m], w[(m + 1) % (2 * BITS)], sh - 8);
+    else if (sh >= 8) v = w[m] >> (sh - 8);
+    else v = w[m] << (8 - sh);
+    return (v & kMask) | base;
+  }
+}
+
 // First tile of block b when the tile list is cut into gridDim.x ranges of equal cost
 // (cost of a tile = its token columns).
 __device__ __forceinline__ int persist_first_tile(const PersistParams& p, long long b, long long nb) {
@@ -398,7 +442,7 @@ __device__ __forceinline__ int persist_first_tile(const PersistParams& p, long l
   return int(r * p.m_tiles + j);
 }
 
-template <typename T>
+template <typename T, int BITS>
 __global__ void __launch_bounds__(kPThreads, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const PersistParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
@@ -469,20 +513,20 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
     int lt = 0, lc = grp;            // load cursor: tile offset, k-block
     auto code_ptr = [&](int t, int c) -> const uint8_t* {
       const int row = (t0 + t) / p.m_tiles;
-      return p.packed + (size_t(row) * G + c) * 4096 + q * 1024 + lane * 32;
+      return p.packed + (size_t(row) * G + c) * (1024 * BITS) + lane * 32;
     };
     auto advance = [&](int& t, int& c) {
       c += 2;
       while (c >= G) { c -= G; ++t; }
     };
     while (lc >= G) { lc -= G; ++lt; }
-    uint32_t w[kRing][8];
+    uint32_t w[kRing][2 * BITS];
 #pragma unroll
     for (int u = 0; u < kRing; ++u) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) w[u][i] = 0u;
+      for (int i = 0; i < 2 * BITS; ++i) w[u][i] = 0u;
       const bool on = lt < ntile;
-      ldg_stream256_if(w[u], code_ptr(on ? lt : 0, on ? lc : 0), on ? 1u : 0u);
+      load_slab_pair<BITS>(w[u], code_ptr(on ? lt : 0, on ? lc : 0), q, on ? 1u : 0u);
       advance(lt, lc);
     }
     int ut = 0, uc = grp;            // use cursor
@@ -500,7 +544,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
             if (row != table_row) {
               PT_BEGIN
               asm volatile("bar.sync 1, %0;" ::"r"(kLookupWarps * 32) : "memory");
-              build_tables(tbl_ptr, p.lut, 4, p.n_groups, row * kTileRows, p.gs, nl, kLookupWarps * 32);
+              build_tables(tbl_ptr, p.lut, BITS, p.n_groups, row * kTileRows, p.gs, nl, kLookupWarps * 32);
               asm volatile("bar.sync 1, %0;" ::"r"(kLookupWarps * 32) : "memory");
               uint32_t token;
               asm volatile("mov.u32 %0, 0;" : "=r"(token));
@@ -527,17 +571,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
             uint32_t r[16];
 #pragma unroll
             for (int kt = 0; kt < 4; ++kt) {
-              const uint32_t word = w[u][4 * sl + kt];
-              r[4 * kt + 0] = lds32(__byte_perm(word, tb, 0x7604u));
-              r[4 * kt + 1] = lds32(__byte_perm(word, tb, 0x7624u));
-              r[4 * kt + 2] = lds32(__byte_perm(word, tb, 0x7614u));
-              r[4 * kt + 3] = lds32(__byte_perm(word, tb, 0x7634u));
+              // slab fields (row g, k 0-1), (g+8, k 0-1), (g, k 2-3), (g+8, k 2-3); the store
+              // shape wants (g, c), (g, c+1), (g+8, c), (g+8, c+1): fields 0, 2, 1, 3
+              r[4 * kt + 0] = lds32(slab_field_addr<BITS>(w[u], sl, 4 * kt + 0, tb));
+              r[4 * kt + 1] = lds32(slab_field_addr<BITS>(w[u], sl, 4 * kt + 2, tb));
+              r[4 * kt + 2] = lds32(slab_field_addr<BITS>(w[u], sl, 4 * kt + 1, tb));
+              r[4 * kt + 3] = lds32(slab_field_addr<BITS>(w[u], sl, 4 * kt + 3, tb));
             }
             tc::tmem_st_16x256b_x4(tmem + (uint32_t(32 * q + 16 * sl) << 16) + kPACol + 32u * stage, r);
           }
           {
             const bool on = lt < ntile;
-            ldg_stream256_if(w[u], code_ptr(on ? lt : 0, on ? lc : 0), on ? 1u : 0u);
+            load_slab_pair<BITS>(w[u], code_ptr(on ? lt : 0, on ? lc : 0), q, on ? 1u : 0u);
             advance(lt, lc);
           }
           PT_END(2)
@@ -732,10 +777,10 @@ int launch(const CUtensorMap& map, const GemmParams& p, int n_tiles, bool pdl, c
   return B200LUT_OK;
 }
 
-template <typename T>
+template <typename T, int BITS>
 int launch_persistent(const CUtensorMap& map, const PersistParams& p, int grid, bool pdl,
                       cudaStream_t stream) {
-  auto kern = gemm_tc_persistent_kernel<T>;
+  auto kern = gemm_tc_persistent_kernel<T, BITS>;
   static bool configured[64] = {false};
   int dev = 0;
   B200LUT_CUDA_OK(cudaGetDevice(&dev));
@@ -823,8 +868,8 @@ extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
   const bool two = s.packed2 != nullptr;
   B200LUT_REQUIRE(!silu || two, B200LUT_ERR_INVALID,
                   "the silu-mul epilogue needs the up projection in packed2 / lut2");
-  B200LUT_REQUIRE(s.bits == 4 && (!two || (s.lut2 && s.bits2 == 4)), B200LUT_ERR_UNSUPPORTED,
-                  "the prefill GEMM serves 4-bit codes (got %d / %d)", s.bits, s.bits2);
+  B200LUT_REQUIRE(s.bits >= 1 && s.bits <= 4 && (!two || (s.lut2 && s.bits2 >= 1 && s.bits2 <= 4)),
+                  B200LUT_ERR_INVALID, "code widths must be 1..4 (got %d / %d)", s.bits, s.bits2);
   B200LUT_REQUIRE(s.group_size >= 32 && s.n_groups >= 1 &&
                       ((s.group_size < 128 && (s.group_size & (s.group_size - 1)) == 0) ||
                        s.group_size % 128 == 0),
@@ -874,11 +919,24 @@ extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
     }
     const long long tiles = (long long)pp.n_tiles * pp.m_tiles;
     const int grid = int(tiles < sms ? tiles : sms);
-    if (dtype == B200LUT_BF16)
-      return launch_persistent<__nv_bfloat16>(pmap, pp, grid, pdl, cudaStream_t(stream));
-    return launch_persistent<__half>(pmap, pp, grid, pdl, cudaStream_t(stream));
+#define B200LUT_PERSIST(B)                                                                      \
+  (dtype == B200LUT_BF16                                                                          \
+       ? launch_persistent<__nv_bfloat16, B>(pmap, pp, grid, pdl, cudaStream_t(stream))          \
+       : launch_persistent<__half, B>(pmap, pp, grid, pdl, cudaStream_t(stream)))
+    switch (s.bits) {
+      case 4: return B200LUT_PERSIST(4);
+      case 3: return B200LUT_PERSIST(3);
+      case 2: return B200LUT_PERSIST(2);
+      default: return B200LUT_PERSIST(1);
+    }
+#undef B200LUT_PERSIST
   }
 
+  // what is left for the one-tile kernel: two code streams, the fused gate/up form, four
+  // palettes per tile — it looks 4-bit codes up
+  B200LUT_REQUIRE(s.bits == 4 && (!two || s.bits2 == 4), B200LUT_ERR_UNSUPPORTED,
+                  "two-stream, gate/up-fused and group-size-32 prefill GEMMs serve 4-bit codes "
+                  "(got %d / %d)", s.bits, s.bits2);
   GemmParams p = {};
   p.packed[0] = static_cast<const uint8_t*>(s.packed);
   p.lut[0] = static_cast<const uint16_t*>(s.lut);

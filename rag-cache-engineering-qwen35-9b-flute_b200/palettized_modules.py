@@ -292,10 +292,13 @@ class PalettizedLinear(nn.Module):
         segs = _lib.make_segments([self._segment_desc(out, res_t=res_t)])
         if M <= GEMV_MAX_M:
             _lib.gemv_multi(x2, segs, 1, flags=_flags())
-        elif self.bitwidth == 4 and (not self.has_stream2 or self.bitwidth2 == 4):
+        elif (self.bitwidth == 4 and (not self.has_stream2 or self.bitwidth2 == 4)) or \
+                (not self.has_stream2 and self.group_size >= 64 and self.K >= 128):
+            # tensor-core GEMM: any width for one code stream with at most two palettes per
+            # tile; 4-bit codes for the two-stream and group-size-32 forms
             _lib.gemm(x2, segs, flags=_flags())
         else:
-            # widths the tensor-core GEMM does not serve yet: decode kernel, 16 rows at a time
+            # what the tensor-core GEMM does not serve: decode kernel, 16 rows at a time
             for r0 in range(0, M, GEMV_MAX_M):
                 rows = slice(r0, min(M, r0 + GEMV_MAX_M))
                 _lib.gemv_multi(x2[rows], _lib.make_segments([self._segment_desc(out[rows])]), 1,

@@ -50,6 +50,24 @@ def test_weights_through_the_gemm_are_bit_exact(gs, dtype):
     assert torch.equal(W.float(), case.w1)
 
 
+@pytest.mark.parametrize("bits,gs,dtype,N,K,M", (
+    (3, 128, torch.bfloat16, 512, 1024, 128),      # hybrid recipe: 3-bit codes, 8-entry palettes
+    (3, 64, torch.float16, 256, 192, 40),
+    (2, 128, torch.bfloat16, 256, 512, 257),
+    (1, 64, torch.bfloat16, 128, 128, 33),
+))
+def test_sub_4_bit_widths_on_the_tensor_core_gemm(bits, gs, dtype, N, K, M):
+    case = Case(N, K, gs, bits, dtype, seed=bits * 100 + gs, bias=True)
+    x = case.x(M)
+    assert rel_err(case.module()(x.cuda()), case.oracle(x)) <= TOL
+    # and the dequantised weights come through bit-exact
+    eye = torch.zeros(K, K, dtype=dtype)
+    eye[torch.arange(K), torch.arange(K)] = 1.0
+    plain = Case(N, K, gs, bits, dtype, seed=bits * 100 + gs)
+    W = plain.module()(eye.cuda()).cpu().t()
+    assert torch.equal(W.float(), plain.w1)
+
+
 def test_bias_second_stream_and_token_tail():
     case = Case(256, 512, 128, 4, torch.bfloat16, seed=9, bits2=4, bias=True)
     for M in (33, 257):
@@ -72,8 +90,8 @@ def test_fused_gate_up_prefill():
     assert rel_err(out, want) <= TOL
 
 
-def test_other_widths_route_through_the_decode_kernel():
-    case = Case(256, 256, 64, 3, torch.float16, seed=12)
+def test_two_stream_sub_4_bit_routes_through_the_decode_kernel():
+    case = Case(256, 256, 64, 3, torch.float16, seed=12, bits2=2)
     x = case.x(40)
     assert rel_err(case.module()(x.cuda()), case.oracle(x)) <= TOL
 
