@@ -279,6 +279,13 @@ int b200lut_plan_status(const void* plan);
 int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
                  const b200lut_segment* seg, int epilogue, int flags, void* stream);
 
+/* gate[m, n] = silu(gate[m, n]) * up[m, n] over 16-bit [M, N] matrices (fp32 inside, one
+ * rounding), in place on the gate buffer: the pass between two full-width prefill GEMMs (gate,
+ * up) and the down projection. Replaces the act_fn(gate) * up of the reference's MLP at M > 1
+ * (src/scripts/palettized_modules.py:1643-1723). N % 8 == 0; rows 16-byte aligned. */
+int b200lut_silu_mul(void* gate, const void* up, int M, int N, int64_t ld_gate, int64_t ld_up,
+                     int dtype, void* stream);
+
 /* ------------------------------------------------------------------------- *
  * Hadamard rotation of the activations
  * ------------------------------------------------------------------------- */

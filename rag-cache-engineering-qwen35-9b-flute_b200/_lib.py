@@ -27,7 +27,7 @@ EXPORTS = (
     "b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes",
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
-    "b200lut_residual_project", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
+    "b200lut_residual_project", "b200lut_silu_mul", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
     "b200lut_gemv_noalloc", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
@@ -109,6 +109,8 @@ def lib() -> ctypes.CDLL:
     L.b200lut_gemv_multi.restype = i32
     L.b200lut_gemv_multi.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32,
                                      i32, vp, sz, i32, vp]
+    L.b200lut_silu_mul.restype = i32
+    L.b200lut_silu_mul.argtypes = [vp, vp, i32, i32, i64, i64, i32, vp]
     L.b200lut_residual_project.restype = i32
     L.b200lut_residual_project.argtypes = [vp, i64, i32, i32, i32, vp, i32, vp, i64, i32, vp]
     L.b200lut_gemv_exchange.restype = i32
@@ -312,6 +314,16 @@ def peer_open(handle: bytes) -> int:
 
 def peer_close(base: int) -> None:
     check(lib().b200lut_peer_close(ctypes.c_void_p(base)))
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """gate <- silu(gate) * up, in place (2-D, last dim contiguous, 16-bit)."""
+    _need_cuda(gate, "gate")
+    M, N = gate.shape
+    with torch.cuda.device(gate.device):
+        check(lib().b200lut_silu_mul(gate.data_ptr(), up.data_ptr(), M, N, gate.stride(0), up.stride(0),
+                                     dtype_id(gate.dtype), _stream(gate)))
+    return gate
 
 
 def gemm(x: torch.Tensor, seg, epilogue: int = EPI_NONE, flags: int = 0) -> None:

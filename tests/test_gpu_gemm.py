@@ -116,3 +116,28 @@ def test_prefill_shape_of_the_9b_model_sampled():
     got_r = mod(xr)
     want_r = (orc.fht_block(x, 128).float() @ w.t()).to(torch.bfloat16)
     assert rel_err(got_r[:, rows.cuda()], want_r) <= TOL
+
+
+@pytest.mark.parametrize("M,N,dtype", ((200, 512, torch.bfloat16), (3, 12288, torch.float16)))
+def test_silu_mul_pass(M, N, dtype):
+    g = torch.Generator().manual_seed(M + N)
+    gate = torch.randn(M, N + 8, generator=g).to(dtype).cuda()[:, :N]      # strided rows
+    up = torch.randn(M, N, generator=g).to(dtype).cuda()
+    want = (torch.nn.functional.silu(gate.float()) * up.float()).to(dtype)
+    got = L.silu_mul(gate, up)
+    torch.cuda.synchronize()
+    assert rel_err(got, want) <= 2e-3                                       # __expf, one rounding
+
+
+def test_stack_prefill_step_matches_module_forwards():
+    st = __import__("importlib").import_module(pkg.__name__ + ".stack")
+    stack = st.LinearStack(n_layers=1)
+    M = 96
+    x = torch.randn(M, st.HIDDEN, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).cuda()
+    plan = stack._plan(M)
+    plan["x"].copy_(x)
+    y = stack.step(M)
+    torch.cuda.synchronize()
+    mlp = stack.layers[0].mlp
+    want = mlp.down_proj(torch.nn.functional.silu(mlp.gate_proj(x).float()).to(torch.bfloat16) * mlp.up_proj(x))
+    assert rel_err(y, want) <= TOL

@@ -74,6 +74,10 @@ def test_validation_errors_carry_a_message():
     assert rc == 2 and b"M=17" in L.b200lut_last_error()
     rc = L.b200lut_residual_project(x, 64, 1, 64, 0, None, 8, x, 8, 0, None)
     assert rc == 1 and b"null" in L.b200lut_last_error()
+    rc = L.b200lut_silu_mul(x, x, 4, 12, 16, 16, 0, None)
+    assert rc == 1 and b"multiple of 8" in L.b200lut_last_error()
+    rc = L.b200lut_silu_mul(x, x, 4, 16, 12, 16, 0, None)
+    assert rc == 5 and b"aligned" in L.b200lut_last_error()
     rc = L.b200lut_fht(x, x, None, None, 1, 96, 96, 96, 0, 0, 64, None)
     assert rc == 1 and b"block" in L.b200lut_last_error()
 
