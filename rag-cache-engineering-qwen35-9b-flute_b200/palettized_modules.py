@@ -461,7 +461,14 @@ class FusedPalettizedMLP(nn.Module):
         fusable = (self._is_silu() and _mergeable(mods, x) and mods[0].N == mods[1].N
                    and os.environ.get("FLUTE_NO_MERGE", "").strip() not in ("1", "true", "True"))
         if not fusable:
-            return self.down_proj(self.act_fn(self.gate_proj(x)) * self.up_proj(x))
+            g, u = self.gate_proj(x), self.up_proj(x)
+            if (self._is_silu() and g.is_cuda and g.dtype in (torch.float16, torch.bfloat16)
+                    and g.dtype == u.dtype and g.shape[-1] % 8 == 0 and g.is_contiguous()
+                    and u.is_contiguous() and not self.gate_proj.reference):
+                # prefill: one SiLU*mul pass over the two projections' outputs
+                _lib.silu_mul(g.view(-1, g.shape[-1]), u.view(-1, u.shape[-1]))
+                return self.down_proj(g)
+            return self.down_proj(self.act_fn(g) * u)
         cd = mods[0].lut.dtype
         x2 = x.reshape(-1, x.shape[-1]).to(cd).contiguous()
         y = self.fused_gate_up(x2).to(x.dtype)
