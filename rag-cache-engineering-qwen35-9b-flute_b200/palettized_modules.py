@@ -344,6 +344,11 @@ class PalettizedLinear(nn.Module):
         shape = x.shape
         if x.shape[-1] != self.K:
             raise ValueError(f"PalettizedLinear: input feature dim {x.shape[-1]} != K {self.K}")
+        if self.K == 0 or self.N == 0 or x.numel() == 0:
+            # degenerate shapes of the reference's kernels: K == 0 gives zeros (+ bias),
+            # N == 0 or no rows give an empty result (kernel_streaming.cu:2363-2368)
+            out = torch.zeros(*shape[:-1], self.N, dtype=x.dtype, device=x.device)
+            return out + self.bias.to(x.dtype) if self.bias is not None and self.N else out
         x2 = x.reshape(-1, self.K)
         if self.rot_signs is not None:
             x2 = self._rotate_input(x2)
@@ -367,8 +372,8 @@ class PalettizedLinear(nn.Module):
 
 
 def _mergeable(mods, x: torch.Tensor) -> bool:
-    """Decode-merge verdict: M <= 16, same K, unrotated, one dtype, and every low-rank
-    residual of a kind the GEMV epilogue serves."""
+    """Decode-merge verdict: M <= 16, same K, one dtype, unrotated or one shared rotation,
+    and every low-rank residual of a kind the GEMV epilogue serves."""
     x2 = x.reshape(-1, x.shape[-1])
     if x2.shape[0] > GEMV_MAX_M or x2.shape[0] == 0 or not x.is_cuda:
         return False
@@ -376,13 +381,27 @@ def _mergeable(mods, x: torch.Tensor) -> bool:
     for m in mods:
         if not isinstance(m, PalettizedLinear) or m.reference or m.K != m0.K:
             return False
-        if m.rot_signs is not None or m.lut.dtype != m0.lut.dtype:
+        if m.lut.dtype != m0.lut.dtype or not _same_rotation(m0, m):
             return False
         if m.lut.dtype not in (torch.float16, torch.bfloat16):
             return False
         if m.has_residual() and not m._fusable_residual(x2.to(m.lut.dtype)):
             return False
     return True
+
+
+def _same_rotation(a: "PalettizedLinear", b: "PalettizedLinear") -> bool:
+    """Both unrotated, or both rotated by the same fold (seed, length, order, AWQ scale): a
+    merged launch rotates the shared input row once. (The reference's merged kernels carry a
+    per-segment FHT prologue and so also merge different folds; here the rotation is a
+    launch of its own and only a shared fold can be merged.)"""
+    if a.rot_signs is None or b.rot_signs is None:
+        return a.rot_signs is None and b.rot_signs is None
+    if (a.rotation_seed, a.rotation_k, a.fold_order) != (b.rotation_seed, b.rotation_k, b.fold_order):
+        return False
+    if a.awq_scale is None or b.awq_scale is None:
+        return a.awq_scale is None and b.awq_scale is None
+    return a is b or torch.equal(a.awq_scale, b.awq_scale)
 
 
 def _stacked_residual(owner: nn.Module, mods, x2: torch.Tensor):
@@ -419,7 +438,10 @@ class SplitQKV(nn.Module):
                 or not _mergeable(mods, x):
             return torch.cat([m(x) for m in mods], dim=-1)
         cd = mods[0].lut.dtype
-        x2 = x.reshape(-1, x.shape[-1]).to(cd).contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        if mods[0].rot_signs is not None:          # one shared fold (see _same_rotation)
+            x2 = mods[0]._rotate_input(x2)
+        x2 = x2.to(cd).contiguous()
         total = sum(m.N for m in mods)
         out = torch.empty(x2.shape[0], total, dtype=cd, device=x.device)
         res = _stacked_residual(self, mods, x2)
@@ -470,6 +492,9 @@ class FusedPalettizedMLP(nn.Module):
                 return self.down_proj(g)
             return self.down_proj(self.act_fn(g) * u)
         cd = mods[0].lut.dtype
-        x2 = x.reshape(-1, x.shape[-1]).to(cd).contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        if mods[0].rot_signs is not None:          # one shared fold (see _same_rotation)
+            x2 = mods[0]._rotate_input(x2)
+        x2 = x2.to(cd).contiguous()
         y = self.fused_gate_up(x2).to(x.dtype)
         return self.down_proj(y).reshape(*x.shape[:-1], self.down_proj.N)

@@ -3,6 +3,8 @@ restatement of the reference route) against outputs of the reference's own
 forward stored in tests/golden/, and against the oracle on seeded cases."""
 from __future__ import annotations
 
+import importlib
+
 import pytest
 import torch
 
@@ -84,3 +86,37 @@ def test_logical_indices_and_weight_accessors():
     mod.drop_blob()
     x = case.x(1)
     assert rel_err(mod(x.cuda()), case.oracle(x)) <= TOL
+
+
+def test_degenerate_shapes_follow_the_reference():
+    # no rows: empty result; K == 0: zeros plus bias (kernel_streaming.cu:2363-2368)
+    case = Case(128, 64, 128, 4, torch.bfloat16, seed=3, bias=True)
+    mod = case.module()
+    assert mod(torch.zeros(0, 64, dtype=torch.bfloat16, device="cuda")).shape == (0, 128)
+    assert mod(torch.zeros(2, 0, 64, dtype=torch.bfloat16, device="cuda")).shape == (2, 0, 128)
+    lut = torch.zeros(1, 16, dtype=torch.bfloat16)
+    bias = torch.arange(128, dtype=torch.bfloat16)
+    k0 = pkg.PalettizedLinear(torch.zeros(0, dtype=torch.uint8), lut, 4, 128, 128, 0, bias=bias).cuda()
+    y = k0(torch.zeros(3, 0, dtype=torch.bfloat16, device="cuda"))
+    assert y.shape == (3, 128) and torch.equal(y.cpu(), bias.expand(3, 128))
+
+
+def test_merged_launch_with_one_shared_rotation_and_residuals():
+    K, dt = 512, torch.float16
+    cases = [Case(n, K, 128, 4, dt, seed=40 + i, rotation_seed=9, residual=16, bias=(i == 1))
+             for i, n in enumerate((256, 128, 384))]
+    mods = [c.module() for c in cases]
+    qkv = pkg.SplitQKV(*mods)
+    x = cases[0].x(3)
+    assert importlib.import_module(pkg.__name__ + ".palettized_modules")._mergeable(mods, x.cuda())
+    got = qkv(x.cuda())
+    torch.cuda.synchronize()
+    want = torch.cat([c.oracle(x) for c in cases], dim=-1)
+    assert got.shape == want.shape and rel_err(got, want) <= TOL
+    # a different fold on one member: no merge, same result through the three modules
+    odd = Case(128, K, 128, 4, dt, seed=50, rotation_seed=10)
+    mixed = [mods[0], odd.module(), mods[2]]
+    assert not importlib.import_module(pkg.__name__ + ".palettized_modules")._mergeable(mixed, x.cuda())
+    got = pkg.SplitQKV(*mixed)(x.cuda())
+    want = torch.cat([cases[0].oracle(x), odd.oracle(x), cases[2].oracle(x)], dim=-1)
+    assert rel_err(got, want) <= TOL
