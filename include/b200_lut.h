@@ -279,6 +279,20 @@ int b200lut_plan_status(const void* plan);
 int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
                  const b200lut_segment* seg, int epilogue, int flags, void* stream);
 
+/* b200lut_gemm with a caller-owned scratch buffer. When the tile count (N/128 x ceil(M/256))
+ * leaves a partly filled last round of SMs, each tile of that round is cut along K into 2..8
+ * parts, one per SM; the parts exchange fp32 partial tiles through the workspace and each
+ * finishes a share of the tile's columns, adding the partial sums in ascending-k order
+ * (deterministic). b200lut_gemm_workspace_bytes gives the size for a shape on the current
+ * device (0: the shape gains nothing); with a NULL or smaller buffer the whole-tile schedule
+ * runs. The buffer must be zero-filled once before first use (its first 4 KiB are counters
+ * that return to zero by themselves), 16-byte aligned, and serves one launch at a time; it may
+ * be reused across shapes. No counterpart in the reference (its GEMM is one tile per block). */
+size_t b200lut_gemm_workspace_bytes(int M, int N, int K);
+int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dtype,
+                    const b200lut_segment* seg, int epilogue, int flags,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
 /* gate[m, n] = silu(gate[m, n]) * up[m, n] over 16-bit [M, N] matrices (fp32 inside, one
  * rounding), in place on the gate buffer: the pass between two full-width prefill GEMMs (gate,
  * up) and the down projection. Replaces the act_fn(gate) * up of the reference's MLP at M > 1

@@ -27,7 +27,7 @@ EXPORTS = (
     "b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes",
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
-    "b200lut_residual_project", "b200lut_silu_mul", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
+    "b200lut_residual_project", "b200lut_silu_mul", "b200lut_gemm_workspace_bytes", "b200lut_gemm_ws", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
     "b200lut_gemv_noalloc", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
@@ -109,6 +109,10 @@ def lib() -> ctypes.CDLL:
     L.b200lut_gemv_multi.restype = i32
     L.b200lut_gemv_multi.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32,
                                      i32, vp, sz, i32, vp]
+    L.b200lut_gemm_workspace_bytes.restype = sz
+    L.b200lut_gemm_workspace_bytes.argtypes = [i32, i32, i32]
+    L.b200lut_gemm_ws.restype = i32
+    L.b200lut_gemm_ws.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32, vp, sz, vp]
     L.b200lut_silu_mul.restype = i32
     L.b200lut_silu_mul.argtypes = [vp, vp, i32, i32, i64, i64, i32, vp]
     L.b200lut_residual_project.restype = i32
@@ -326,12 +330,37 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return gate
 
 
-def gemm(x: torch.Tensor, seg, epilogue: int = EPI_NONE, flags: int = 0) -> None:
+_gemm_scratch = {}
+
+
+def _gemm_workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    """Scratch of the prefill GEMM's split schedule, one per device and stream (a buffer serves
+    one launch at a time, and launches of one stream are ordered): zero-filled when
+    (re)allocated, grown geometrically."""
+    key = (device, stream)
+    buf = _gemm_scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        size = max(nbytes, 2 * buf.numel() if buf is not None else 0)
+        buf = torch.zeros(size, dtype=torch.uint8, device=device)
+        _gemm_scratch[key] = buf
+    return buf
+
+
+def gemm(x: torch.Tensor, seg, epilogue: int = EPI_NONE, flags: int = 0, split: bool = True) -> None:
+    """Prefill GEMM over one segment; brings the scratch buffer of the split schedule when the
+    shape gains from it (split=False: whole-tile schedule)."""
     _need_cuda(x, "x")
     M, K = x.shape
     with torch.cuda.device(x.device):
-        check(lib().b200lut_gemm(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), seg,
-                                 epilogue, flags, _stream(x)))
+        s0 = seg[0]
+        need = lib().b200lut_gemm_workspace_bytes(M, int(s0.N), K) if (split and not s0.packed2) else 0
+        if need:
+            ws = _gemm_workspace(x.device, int(_stream(x) or 0), need)
+            check(lib().b200lut_gemm_ws(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), seg,
+                                        epilogue, flags, ws.data_ptr(), ws.numel(), _stream(x)))
+        else:
+            check(lib().b200lut_gemm(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), seg,
+                                     epilogue, flags, _stream(x)))
 
 
 def fht(x: torch.Tensor, signs: Optional[torch.Tensor], mode: int = FHT_FORWARD,

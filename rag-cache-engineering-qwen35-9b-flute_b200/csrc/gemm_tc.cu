@@ -384,6 +384,15 @@ struct PersistParams {
   int out_aligned;
   int debug;
   long long wait_cycles;   // bound of every in-kernel wait, in SM clock cycles
+  // Split mode (a workspace was given and the tile count leaves a partly filled last round):
+  // every block takes `full` whole tiles; each of the `left` tiles behind them is cut along K
+  // into `split` equal k-block ranges, one per block (blocks 0 .. left * split - 1 take one
+  // each, before their whole tiles). The `split` blocks of a cut tile exchange fp32 partial
+  // tiles through the workspace and each finishes its share of the tile's 16-column chunks,
+  // adding the partial sums in ascending-k order.
+  int split, full, left;
+  float* ws;               // [left tile][part < split][column 256][row 128] fp32
+  int* tickets;            // [left tile][2]: partial tiles stored, shares finished; zero between launches
 };
 
 // 64-bit code load (two consecutive words of a lane's string), executed only when `on`.
@@ -479,10 +488,32 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
   const bool fits = xhigh + (kPStages - 1) * stage_bytes <= base + p.smem_bytes &&
                     xlow + stage_bytes <= tbl_addr;
 
-  const int t0 = persist_first_tile(p, blockIdx.x, gridDim.x);
-  const int t1 = persist_first_tile(p, blockIdx.x + 1, gridDim.x);
-  const int ntile = t1 - t0;
+  // The block's work is a list of segments (tile, k-blocks [c0, c1)). Plain mode: the whole
+  // tiles of a cost-balanced contiguous range. Split mode: first the block's k-range of a cut
+  // tile (if it has one), then `full` whole tiles.
   const int G = p.G;
+  const int bid = int(blockIdx.x);
+  int t0, ntile, has_cut = 0, cut_tile = 0, cut_c0 = 0, cut_c1 = 0, cut_part = 0;
+  if (p.split) {
+    t0 = bid * p.full;
+    ntile = p.full;
+    if (bid < p.left * p.split) {
+      has_cut = 1;
+      cut_part = bid % p.split;
+      cut_tile = int(gridDim.x) * p.full + bid / p.split;
+      cut_c0 = (G * cut_part) / p.split;
+      cut_c1 = (G * (cut_part + 1)) / p.split;
+    }
+  } else {
+    t0 = persist_first_tile(p, bid, gridDim.x);
+    ntile = persist_first_tile(p, bid + 1, gridDim.x) - t0;
+  }
+  const int nseg = ntile + has_cut;
+  const int iters = ntile * G + (cut_c1 - cut_c0);
+  // segment s of this block
+  auto seg_tile = [&](int sg) { return (has_cut && sg == 0) ? cut_tile : t0 + sg - has_cut; };
+  auto seg_c0 = [&](int sg) { return (has_cut && sg == 0) ? cut_c0 : 0; };
+  auto seg_c1 = [&](int sg) { return (has_cut && sg == 0) ? cut_c1 : G; };
 
   asm volatile("griddepcontrol.launch_dependents;");
 
@@ -507,40 +538,52 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
   if (warp < kLookupWarps) {
     // ---- lookup warps ---------------------------------------------------------------------------
     const int q = warp & 3, grp = warp >> 2;
-    // this warp's k-blocks are the global iterations grp, grp + 2, ... of the block's flat
-    // (tile, k-block) sequence; `load` runs kRing of them ahead of `use`
-    const int iters = ntile * G;
-    int lt = 0, lc = grp;            // load cursor: tile offset, k-block
-    auto code_ptr = [&](int t, int c) -> const uint8_t* {
-      const int row = (t0 + t) / p.m_tiles;
-      return p.packed + (size_t(row) * G + c) * (1024 * BITS) + lane * 32;
+    // this warp's k-blocks are the iterations grp, grp + 2, ... of the block's flat sequence of
+    // k-blocks (segment after segment; every segment has at least two k-blocks, so both groups
+    // work in every segment); `load` runs kRing of them ahead of `use`
+    struct Cursor { int s, c, c1, row; };
+    auto enter = [&](Cursor& cu, int over) {
+      if (cu.s < nseg) {
+        cu.c = seg_c0(cu.s) + over;
+        cu.c1 = seg_c1(cu.s);
+        cu.row = seg_tile(cu.s) / p.m_tiles;
+      }
     };
-    auto advance = [&](int& t, int& c) {
-      c += 2;
-      while (c >= G) { c -= G; ++t; }
+    auto advance = [&](Cursor& cu) {
+      cu.c += 2;
+      while (cu.s < nseg && cu.c >= cu.c1) {
+        const int over = cu.c - cu.c1;
+        ++cu.s;
+        enter(cu, over);
+      }
     };
-    while (lc >= G) { lc -= G; ++lt; }
+    auto code_ptr = [&](const Cursor& cu) -> const uint8_t* {
+      return p.packed + (size_t(cu.row) * G + cu.c) * (1024 * BITS) + lane * 32;
+    };
+    Cursor ld = {0, 0, 0, 0}, use = {0, 0, 0, 0};
+    enter(ld, grp - 2);
+    advance(ld);
+    enter(use, grp - 2);
+    advance(use);
     uint32_t w[kRing][2 * BITS];
 #pragma unroll
     for (int u = 0; u < kRing; ++u) {
 #pragma unroll
       for (int i = 0; i < 2 * BITS; ++i) w[u][i] = 0u;
-      const bool on = lt < ntile;
-      load_slab_pair<BITS>(w[u], code_ptr(on ? lt : 0, on ? lc : 0), q, on ? 1u : 0u);
-      advance(lt, lc);
+      const bool on = ld.s < nseg;
+      load_slab_pair<BITS>(w[u], on ? code_ptr(ld) : p.packed, q, on ? 1u : 0u);
+      if (on) advance(ld);
     }
-    int ut = 0, uc = grp;            // use cursor
-    while (uc >= G) { uc -= G; ++ut; }
-    int table_row = -1, table_tile = -1;
+    int table_row = -1, table_seg = -1;
     uint32_t lane_base = 0;
     for (int it = grp; it < iters; it += 2 * kRing) {
 #pragma unroll
       for (int u = 0; u < kRing; ++u) {
         if (it + 2 * u < iters) {     // warp-uniform
-          if (ut != table_tile) {
-            // a new tile: all eight lookup warps pass here once per tile (block-uniform), and
-            // rebuild the pair table together when the row tile has changed
-            const int row = (t0 + ut) / p.m_tiles;
+          if (use.s != table_seg) {
+            // a new segment: all eight lookup warps pass here once per segment (block-uniform),
+            // and rebuild the pair table together when the row tile has changed
+            const int row = use.row;
             if (row != table_row) {
               PT_BEGIN
               asm volatile("bar.sync 1, %0;" ::"r"(kLookupWarps * 32) : "memory");
@@ -552,7 +595,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
               table_row = row;
               PT_END(1)
             }
-            table_tile = ut;
+            table_seg = use.s;
           }
           const int i = it + 2 * u;
           const int stage = i % kPStages;
@@ -581,9 +624,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
             tc::tmem_st_16x256b_x4(tmem + (uint32_t(32 * q + 16 * sl) << 16) + kPACol + 32u * stage, r);
           }
           {
-            const bool on = lt < ntile;
-            load_slab_pair<BITS>(w[u], code_ptr(on ? lt : 0, on ? lc : 0), q, on ? 1u : 0u);
-            advance(lt, lc);
+            const bool on = ld.s < nseg;
+            load_slab_pair<BITS>(w[u], on ? code_ptr(ld) : p.packed, q, on ? 1u : 0u);
+            if (on) advance(ld);
           }
           PT_END(2)
           PT_BEGIN
@@ -591,7 +634,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
           PT_END(3)
           tc::fence_before_sync();
           if (lane == 0) tc::mbar_arrive(bar_full + 8 * stage);
-          advance(ut, uc);
+          advance(use);
         }
       }
     }
@@ -599,9 +642,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
   } else if (warp == kLookupWarps) {
     // ---- TMA producer ---------------------------------------------------------------------------
     int i = 0;
-    for (int t = 0; t < ntile; ++t) {
-      const int m0 = ((t0 + t) % p.m_tiles) * p.NT;
-      for (int c = 0; c < G; ++c, ++i) {
+    for (int sg = 0; sg < nseg; ++sg) {
+      const int m0 = (seg_tile(sg) % p.m_tiles) * p.NT;
+      const int c_hi = seg_c1(sg);
+      for (int c = seg_c0(sg); c < c_hi; ++c, ++i) {
         const int xs = i % kPStages;
         if (i >= kPStages)
           tc::mbar_wait(bar_done + 8 * xs, uint32_t(i / kPStages - 1) & 1u, abort_flag,
@@ -622,8 +666,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
     for (int s = 0; s < kPStages; ++s) xlo[s] = uint32_t(dtemplate) + (xstage(s) >> 4);
     const uint32_t xhi = uint32_t(dtemplate >> 32);
     if (lane == 0) {
-      const int iters = ntile * G;
-      int t = -1, c = G;             // tile offset and k-block inside it; c == G: start the next tile
+      int t = -1, c = 0, c_first = 0, c_end = 0;   // segment, k-block, the segment's k range
       uint32_t idesc = 0;
       const uint32_t d0 = tmem;
       uint32_t phase = 0;            // (i / ring size) & 1
@@ -631,10 +674,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
 #pragma unroll
         for (int u = 0; u < kPStages; ++u) {
           if (i0 + u < iters) {
-            if (c == G) {            // a new tile: its accumulator buffer must have been drained
+            if (c == c_end) {        // a new segment: the accumulator must have been drained
               ++t;
-              c = 0;
-              const int m0 = ((t0 + t) % p.m_tiles) * p.NT;
+              c = c_first = seg_c0(t);
+              c_end = seg_c1(t);
+              const int m0 = (seg_tile(t) % p.m_tiles) * p.NT;
               int nt = p.M - m0;                          // the row's last tile may be narrower
               nt = nt >= p.NT ? p.NT : ((nt + 31) & ~31);
               idesc = tc::instr_desc(kFmt, 128, uint32_t(nt));
@@ -648,9 +692,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
             tc::mbar_wait(bar_full + 8 * u, phase, abort_flag, &g_gemm_status, tc::kStatusWaitFull, p.wait_cycles);
             PT_END(0)
             tc::fence_after_sync();
-            tc::mma_ts_kblock(d0, tmem + kPACol + 32u * uint32_t(u), xlo[u], xhi, idesc, c == 0 ? 0u : 1u);
+            tc::mma_ts_kblock(d0, tmem + kPACol + 32u * uint32_t(u), xlo[u], xhi, idesc,
+                              c == c_first ? 0u : 1u);   // a segment's first k-block overwrites
             tc::mma_commit(bar_done + 8 * u);
-            if (++c == G) tc::mma_commit(bar_dfull);
+            if (++c == c_end) tc::mma_commit(bar_dfull);
           }
         }
       }
@@ -663,8 +708,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
     const int h = (warp - (kLookupWarps + 2)) >> 2;      // column half of the tile it drains
     const int et = threadIdx.x - (kLookupWarps + 2 + 4 * h) * 32;   // 0..127 inside the half
     uint16_t* stg = stage_out + h * (kPStageTokens * kTileRows);
-    for (int t = 0; t < ntile; ++t) {
-      const int tile = t0 + t;
+    volatile int* cut_flag = reinterpret_cast<volatile int*>(smem + 272);
+    for (int t = 0; t < nseg; ++t) {
+      const int tile = seg_tile(t);
+      const bool cut = has_cut && t == 0;
       const int n0 = (tile / p.m_tiles) * kTileRows, m0 = (tile % p.m_tiles) * p.NT;
       int nt = p.M - m0;
       nt = nt >= p.NT ? p.NT : ((nt + 31) & ~31);
@@ -676,6 +723,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
       PT_END(0)
       tc::fence_after_sync();
       const uint32_t d0 = tmem + (uint32_t(32 * q) << 16) + uint32_t(col0);
+      float* wt = cut ? p.ws + size_t(tile - int(gridDim.x) * p.full) * p.split * (256 * kTileRows) : nullptr;
       // slices of up to 48 tokens: three loads in flight, one wait, staging, 16-byte stores
       for (int s0 = 0; s0 < half; s0 += kPStageTokens) {
         const int sn = half - s0 < kPStageTokens ? half - s0 : kPStageTokens;
@@ -687,6 +735,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
         if (s0 + sn >= half) {   // the accumulator is free as soon as it has been read
           tc::fence_before_sync();
           if (lane == 0) tc::mbar_arrive(bar_dempty);
+        }
+        if (cut) {   // this block's k-range of a cut tile: raw fp32 sums to its workspace slot
+          float* mine = wt + size_t(cut_part) * (256 * kTileRows) + 32 * q + lane;
+#pragma unroll
+          for (int ch = 0; ch < 3; ++ch)
+            if (16 * ch < sn)
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                __stcg(mine + size_t(col0 + s0 + 16 * ch + j) * kTileRows, __uint_as_float(r[ch][j]));
+          continue;
         }
 #pragma unroll
         for (int ch = 0; ch < 3; ++ch) {
@@ -710,6 +768,50 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
               *reinterpret_cast<uint4*>(p.out + size_t(m0 + r_) * p.ldo + n0 + 8 * c) = src[idx];
           }
           asm volatile("bar.sync %0, 128;" ::"r"(2 + h) : "memory");   // the slice is reused
+        }
+      }
+      if (cut) {
+        // All `split` blocks of the tile store their partial tiles, meet on a counter (bounded
+        // wait: the grid is one block per SM and every block does its cut piece first), and
+        // each finishes the 16-column chunks k with k % split == its part: the partial sums
+        // are added in part (= ascending k) order, bias, one rounding, element stores.
+        int* cnt = p.tickets + 2 * (tile - int(gridDim.x) * p.full);
+        __threadfence();
+        asm volatile("bar.sync 4, %0;" ::"r"(kPEpiWarps * 32) : "memory");
+        if (warp == kLookupWarps + 2 && lane == 0) {
+          atomicAdd(cnt, 1);
+          int ok = 1;
+          const long long w0 = clock64();
+          while (*reinterpret_cast<volatile int*>(cnt) < p.split) {
+            if (*abort_flag || clock64() - w0 > p.wait_cycles) { ok = 0; break; }
+          }
+          if (!ok) { *abort_flag = 1; atomicCAS(&g_gemm_status, tc::kStatusOk, tc::kStatusWaitDone); }
+          *cut_flag = ok;
+        }
+        asm volatile("bar.sync 4, %0;" ::"r"(kPEpiWarps * 32) : "memory");
+        if (*cut_flag) {
+          __threadfence();
+          const int nchunk = nt >> 4;
+          for (int k = cut_part + p.split * h; k < nchunk; k += 2 * p.split) {   // the two halves alternate
+            float acc[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+            for (int ci = 0; ci < p.split; ++ci) {
+              const float* src = wt + (size_t(ci) * 256 + 16 * k) * kTileRows + 32 * q + lane;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[j] += __ldcg(src + size_t(j) * kTileRows);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int tok = m0 + 16 * k + j;
+              if (tok < p.M) p.out[size_t(tok) * p.ldo + n] = DType<T>::from_float(acc[j] + b0);
+            }
+          }
+        }
+        asm volatile("bar.sync 4, %0;" ::"r"(kPEpiWarps * 32) : "memory");
+        if (warp == kLookupWarps + 2 && lane == 0) {
+          __threadfence();
+          if (atomicAdd(cnt + 1, 1) == p.split - 1) { cnt[0] = 0; cnt[1] = 0; }   // ready for the next launch
         }
       }
     }
@@ -775,6 +877,25 @@ int launch(const CUtensorMap& map, const GemmParams& p, int n_tiles, bool pdl, c
   cfg.numAttrs = unsigned(na);
   B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map, p));
   return B200LUT_OK;
+}
+
+// Split planning for `tiles` output tiles of G k-blocks on `sms` blocks: whole rounds of tiles
+// stay whole; each tile of the partly filled last round is cut along K into `split` parts.
+struct SplitPlan { int split, full, left; size_t bytes; };
+constexpr size_t kTicketBytes = 4096;   // counters first, at a fixed place: they outlive a shape change
+
+SplitPlan plan_split(long long tiles, int G, int sms) {
+  SplitPlan sp = {0, 0, 0, 0};
+  if (tiles <= 0 || sms <= 0) return sp;
+  const long long full = tiles / sms, left = tiles - full * sms;
+  if (left == 0 || left > (long long)(kTicketBytes / 8)) return sp;
+  long long S = sms / left;
+  if (S > 8) S = 8;
+  while (S >= 2 && G < 2 * S) --S;       // every part keeps at least two k-blocks
+  if (S < 2) return sp;
+  sp.split = int(S); sp.full = int(full); sp.left = int(left);
+  sp.bytes = kTicketBytes + size_t(left) * size_t(S) * 256 * kTileRows * sizeof(float);
+  return sp;
 }
 
 template <typename T, int BITS>
@@ -846,8 +967,24 @@ extern "C" int b200lut_device_status(void) {
   return v != 0 ? v : e;
 }
 
+extern "C" size_t b200lut_gemm_workspace_bytes(int M, int N, int K) {
+  if (M < 1 || N < kTileRows || K < 2 * kChunkK) return 0;
+  const int nt = M >= kPMaxNT ? kPMaxNT : ((M + 31) / 32) * 32;
+  const long long tiles = (long long)(N / kTileRows) * ((M + nt - 1) / nt);
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess)
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return plan_split(tiles, K / kChunkK, sms).bytes;
+}
+
 extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
                             const b200lut_segment* seg, int epilogue, int flags, void* stream) {
+  return b200lut_gemm_ws(x, ldx, M, K, dtype, seg, epilogue, flags, nullptr, 0, stream);
+}
+
+extern "C" int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dtype,
+                               const b200lut_segment* seg, int epilogue, int flags,
+                               void* workspace, size_t workspace_bytes, void* stream) {
   B200LUT_REQUIRE(x && seg, B200LUT_ERR_INVALID, "null x or segment");
   B200LUT_REQUIRE(M >= 1, B200LUT_ERR_INVALID, "M must be >= 1, got %d", M);
   B200LUT_REQUIRE(K > 0 && K % kChunkK == 0, B200LUT_ERR_INVALID,
@@ -918,7 +1055,14 @@ extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
       B200LUT_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     }
     const long long tiles = (long long)pp.n_tiles * pp.m_tiles;
-    const int grid = int(tiles < sms ? tiles : sms);
+    int grid = int(tiles < sms ? tiles : sms);
+    const SplitPlan sp = plan_split(tiles, pp.G, sms);
+    if (sp.split && workspace && workspace_bytes >= sp.bytes && aligned16(workspace) && !(debug & 32)) {
+      pp.split = sp.split; pp.full = sp.full; pp.left = sp.left;
+      pp.tickets = static_cast<int*>(workspace);
+      pp.ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kTicketBytes);
+      grid = sms;
+    }
 #define B200LUT_PERSIST(B)                                                                      \
   (dtype == B200LUT_BF16                                                                          \
        ? launch_persistent<__nv_bfloat16, B>(pmap, pp, grid, pdl, cudaStream_t(stream))          \

@@ -118,6 +118,76 @@ def test_prefill_shape_of_the_9b_model_sampled():
     assert rel_err(got_r[:, rows.cuda()], want_r) <= TOL
 
 
+def _raw_gemm(case, mod, x, split, out=None, ldo=None):
+    """One call of the C entry on the module's own codes and palettes."""
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty(M, case.N, dtype=case.dtype, device="cuda")
+    d = dict(packed=mod._packed, lut=mod.lut, N=case.N, group_size=case.gs,
+             n_groups=mod.lut.shape[0], bits=case.bits, out=out, ldo=ldo or out.stride(0))
+    if case.bias is not None:
+        d["bias"] = case.bias.cuda()
+    L.gemm(x, L.make_segments([d]), split=split)
+    return out
+
+
+@pytest.mark.parametrize("N,K,gs,bits,dtype,M,bias", (
+    (12288, 1024, 128, 4, torch.bfloat16, 512, True),    # 192 tiles: one full round + 44 cut in 3
+    (2560, 512, 128, 4, torch.float16, 300, False),      # 40 tiles, no full round, 108 SMs share them
+    (8192, 2048, 64, 4, torch.bfloat16, 513, True),      # token tail: the third tile row holds one token
+    (4096, 1024, 128, 3, torch.bfloat16, 1100, False),   # 3-bit codes
+    (1280, 256, 128, 2, torch.float16, 256, True),       # short K: parts of two k-blocks
+))
+def test_split_schedule_equals_the_whole_tile_schedule(N, K, gs, bits, dtype, M, bias):
+    assert L.lib().b200lut_gemm_workspace_bytes(M, N, K) > 0
+    case = Case(N, K, gs, bits, dtype, seed=N + M, bias=bias)
+    mod = case.module()
+    mod(case.x(17).cuda())                       # repacks the codes
+    x = case.x(M)
+    xd = x.cuda()
+    whole = _raw_gemm(case, mod, xd, split=False)
+    cut = _raw_gemm(case, mod, xd, split=True)
+    again = _raw_gemm(case, mod, xd, split=True)     # the counters returned to zero by themselves
+    assert torch.equal(cut, again)
+    # same products, summed in 2..8 fp32 pieces instead of one: within one rounding of the output
+    assert rel_err(cut, whole) <= 2.0 ** -7
+    want = case.oracle(x)
+    assert rel_err(cut, want) <= TOL and rel_err(whole, want) <= TOL
+
+
+def test_split_schedule_into_an_unaligned_strided_output():
+    N, K, M = 2560, 512, 260
+    case = Case(N, K, 128, 4, torch.bfloat16, seed=5, bias=True)
+    mod = case.module()
+    mod(case.x(17).cuda())
+    x = case.x(M)
+    buf = torch.full((M, N + 24), 7.0, dtype=torch.bfloat16, device="cuda")
+    view = buf[:, 3:3 + N]                       # 6 bytes off the 16-byte grid, row stride N + 24
+    _raw_gemm(case, mod, x.cuda(), split=True, out=view)
+    assert rel_err(view, case.oracle(x)) <= TOL
+    assert (buf[:, :3] == 7.0).all() and (buf[:, 3 + N:] == 7.0).all()
+
+
+def test_small_or_misaligned_workspace_falls_back_to_whole_tiles():
+    N, K, M = 2560, 512, 300
+    case = Case(N, K, 128, 4, torch.bfloat16, seed=6)
+    mod = case.module()
+    mod(case.x(17).cuda())
+    x = case.x(M).cuda()
+    whole = _raw_gemm(case, mod, x, split=False)
+    need = L.lib().b200lut_gemm_workspace_bytes(M, N, K)
+    ws = torch.zeros(need + 16, dtype=torch.uint8, device="cuda")
+    out = torch.empty_like(whole)
+    seg = L.make_segments([dict(packed=mod._packed, lut=mod.lut, N=N, group_size=128,
+                                n_groups=mod.lut.shape[0], bits=4, out=out)])
+    for ptr, size in ((ws.data_ptr(), need - 1), (ws.data_ptr() + 4, need)):
+        out.zero_()
+        L.check(L.lib().b200lut_gemm_ws(x.data_ptr(), x.stride(0), M, K, L.dtype_id(x.dtype), seg,
+                                        0, 0, ptr, size, L._stream(x)))
+        assert torch.equal(out, whole)
+    assert not ws.any()                          # the fallback never touched the buffer
+
+
 @pytest.mark.parametrize("M,N,dtype", ((200, 512, torch.bfloat16), (3, 12288, torch.float16)))
 def test_silu_mul_pass(M, N, dtype):
     g = torch.Generator().manual_seed(M + N)

@@ -70,6 +70,13 @@ def test_validation_errors_carry_a_message():
     rc = L.b200lut_gemm(x, 64, 32, 64, 0, ctypes.byref(seg), 0, 0, None)
     assert rc == 2 and b"residual" in L.b200lut_last_error()
     seg.res_rank = 0
+    # the split schedule's workspace: sized without a device (148 SMs assumed), validated like
+    # the plain entry
+    assert L.b200lut_gemm_workspace_bytes(2048, 4096, 4096) == 0   # 108 tiles left over: no SM to spare
+    assert L.b200lut_gemm_workspace_bytes(16, 64, 4096) == 0
+    assert L.b200lut_gemm_workspace_bytes(512, 12288, 4096) == 4096 + 44 * 3 * 256 * 128 * 4
+    rc = L.b200lut_gemm_ws(x, 64, 32, 60, 0, ctypes.byref(seg), 0, 0, x, 1 << 20, None)
+    assert rc == 1 and b"multiple of 64" in L.b200lut_last_error()
     rc = L.b200lut_residual_project(x, 64, 17, 64, 0, x, 8, x, 8, 0, None)
     assert rc == 2 and b"M=17" in L.b200lut_last_error()
     rc = L.b200lut_residual_project(x, 64, 1, 64, 0, None, 8, x, 8, 0, None)
