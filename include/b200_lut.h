@@ -54,7 +54,8 @@ const char* b200lut_last_error(void);
 /* Device-side status of the tensor-core kernels on the current device: 0 = none;
  * non-zero = a bounded wait inside a kernel ran out (the kernel then returned early
  * with its tensor memory freed and its output undefined). Synchronises the device
- * read; clears the word. No counterpart in the reference (its kernels never wait). */
+ * read; clears the word. No counterpart in the reference (its kernels never wait).
+ * 0x6000: an embedding gather met an id outside its table (that row was written as zeros). */
 int b200lut_device_status(void);
 
 /* Number of SMs of the current device (used by the split policy). */
@@ -292,6 +293,31 @@ size_t b200lut_gemm_workspace_bytes(int M, int N, int K);
 int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dtype,
                     const b200lut_segment* seg, int epilogue, int flags,
                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- embedding gather ----------------------------------------------------------------------
+ *
+ * out[t, :] = W[ids[t], :] for n_ids int64 ids on the device, W the palettized [N, K] table
+ * described by `table` (packed / lut / bits, optional packed2 / lut2 / bits2, group_size,
+ * n_groups, N; resA + res_rank with `resB` [R, K] for the low-rank residual; out / ldo; bias and
+ * res_t are ignored). Arithmetic of the reference's PalettizedEmbedding.forward
+ * (src/scripts/palettized_modules.py:2276-2335): stream 1 palette entry, plus the stream 2
+ * entry in ONE add rounded to the palette dtype (stream 1 first), widened to fp32, plus
+ * sum_r resA[id, r] * resB[r, k] in fp32 (ascending r), then one rounding to dtype — or no
+ * rounding with out_fp32 != 0 (fp32 rows, for the un-rotation of a tied table:
+ * b200lut_fht(mode ADJOINT, dtype fp32) then b200lut_round_rows). The rows are read out of the
+ * slab layout, so a tied lm_head / embedding pair shares one copy of the codes; the reference
+ * keeps an unpacked [N, K] uint8 cache instead (:2181-2205).
+ * An id outside [0, N) writes a row of zeros and raises the device status
+ * (b200lut_device_status() != 0); the reference aborts the context with a device-side
+ * assertion (:1957-1976). */
+int b200lut_embed_gather(const int64_t* ids, int64_t n_ids, int K, int dtype,
+                         const b200lut_segment* table, const void* resB, int out_fp32,
+                         void* stream);
+
+/* out[m, k] = round_to_dtype(in[m, k]) for fp32 rows (the `.to(lut.dtype)` that ends the
+ * reference's embedding forward, :2335). */
+int b200lut_round_rows(const float* in, int64_t ldi, void* out, int64_t ldo, int64_t M, int K,
+                       int dtype, void* stream);
 
 /* gate[m, n] = silu(gate[m, n]) * up[m, n] over 16-bit [M, N] matrices (fp32 inside, one
  * rounding), in place on the gate buffer: the pass between two full-width prefill GEMMs (gate,

@@ -8,8 +8,9 @@ It restates, in numpy / CPU torch, the arithmetic of the reference project
 (pkhairkh/rag-cache-engineering-qwen35-9b-flute). Each function cites the
 reference file:line it follows. Parity is PINNED: tests/golden/ holds outputs
 of the reference's own Python code (its idxN packer, its reference_dequant,
-its PalettizedLinear(reference=True).forward and its fht_reference), made by
-tests/golden/make_golden.py, and tests/test_oracle_golden.py checks every
+its PalettizedLinear(reference=True).forward, its PalettizedEmbedding.forward and its
+fht_reference), made by tests/golden/make_golden.py and
+tests/golden/make_embedding_golden.py, and tests/test_oracle_golden.py checks every
 function here against them bit for bit.
 
 Conventions: indices are the logical [N, K] uint8 code matrix; a "blob" is the
@@ -293,6 +294,40 @@ def fht_adjoint(v: torch.Tensor, signs: torch.Tensor) -> torch.Tensor:
         seg = _wht((g[:, off:off + b] * s[:, off:off + b]).contiguous())
         out[:, off:off + b] = seg * (1.0 / math.sqrt(b))
     return out.reshape(v.shape).to(v.dtype)
+
+
+def embedding_forward(ids: torch.Tensor, idx1: np.ndarray, lut1: torch.Tensor, group_size: int,
+                      idx2: Optional[np.ndarray] = None, lut2: Optional[torch.Tensor] = None,
+                      resA: Optional[torch.Tensor] = None, resB: Optional[torch.Tensor] = None,
+                      rot_signs: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows ids of a palettized table, the dtype ladder of PalettizedEmbedding.forward
+    (src/scripts/palettized_modules.py:2276-2335): per stream
+    lut[ids // gs].gather(-1, idx[ids]) in the palette dtype (:2293-2294), the second stream
+    added in that dtype with stream 1 first (:2313-2315), widened to fp32, plus
+    resA[ids].float() @ resB.float() (:2316-2319), un-rotated through the adjoint transform
+    when the table is a tied, rotated head (:2326-2334), one cast to the palette dtype
+    (:2335). ids: integer tensor of any shape with values in [0, N); idx*: logical [N, K]
+    uint8 codes."""
+    ids = ids.long()
+    N = idx1.shape[0]
+    if ids.numel() and (int(ids.min()) < 0 or int(ids.max()) >= N):
+        raise ValueError(f"ids out of range [0, {N})")
+
+    def stream(idx, lut):
+        assert lut.dim() == 2, "palettes are [n_groups, 2**bits]"
+        rows = torch.from_numpy(np.ascontiguousarray(idx))[ids].long()
+        return lut[ids // group_size].gather(-1, rows)
+
+    w = stream(idx1, lut1)
+    if idx2 is not None:
+        w = w + stream(idx2, lut2)
+    if resA is not None and resB is not None:
+        w = w.float() + (resA[ids].float() @ resB.float())
+    else:
+        w = w.float()
+    if rot_signs is not None:
+        w = fht_adjoint(w, rot_signs)
+    return w.to(lut1.dtype)
 
 
 def fht_forward_awq(x: torch.Tensor, signs: torch.Tensor, s: torch.Tensor) -> torch.Tensor:

@@ -6,12 +6,13 @@ behind a C ABI, see include/b200_lut.h). Import of this package does not load
 the library; the first compute call does, and fails loudly if it is not built.
 """
 from . import _lib, fht, idxN, synthetic                                    # noqa: F401
-from .palettized_modules import (FusedPalettizedMLP, PalettizedLinear, SplitQKV,  # noqa: F401
+from .palettized_modules import (FusedPalettizedMLP, PalettizedEmbedding, PalettizedLinear,  # noqa: F401
+                                 SplitQKV,
                                  reference_dequant, set_programmatic_launch)
 from .artifacts import (load_metadata, load_palettized_weight,                     # noqa: F401
                         replace_linear_with_palettized)
 from .loader import load_quant_model                                             # noqa: F401
 
 __all__ = ["load_quant_model", "load_palettized_weight", "replace_linear_with_palettized",
-           "load_metadata", "PalettizedLinear", "SplitQKV", "FusedPalettizedMLP", "reference_dequant",
+           "load_metadata", "PalettizedLinear", "PalettizedEmbedding", "SplitQKV", "FusedPalettizedMLP", "reference_dequant",
            "set_programmatic_launch", "fht", "idxN", "synthetic"]

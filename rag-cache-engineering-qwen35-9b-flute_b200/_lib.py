@@ -27,7 +27,8 @@ EXPORTS = (
     "b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes",
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
-    "b200lut_residual_project", "b200lut_silu_mul", "b200lut_gemm_workspace_bytes", "b200lut_gemm_ws", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
+    "b200lut_residual_project", "b200lut_silu_mul", "b200lut_gemm_workspace_bytes", "b200lut_gemm_ws",
+    "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
     "b200lut_gemv_noalloc", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
@@ -113,6 +114,10 @@ def lib() -> ctypes.CDLL:
     L.b200lut_gemm_workspace_bytes.argtypes = [i32, i32, i32]
     L.b200lut_gemm_ws.restype = i32
     L.b200lut_gemm_ws.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32, vp, sz, vp]
+    L.b200lut_embed_gather.restype = i32
+    L.b200lut_embed_gather.argtypes = [vp, i64, i32, i32, ctypes.POINTER(Segment), vp, i32, vp]
+    L.b200lut_round_rows.restype = i32
+    L.b200lut_round_rows.argtypes = [vp, i64, vp, i64, i64, i32, i32, vp]
     L.b200lut_silu_mul.restype = i32
     L.b200lut_silu_mul.argtypes = [vp, vp, i32, i32, i64, i64, i32, vp]
     L.b200lut_residual_project.restype = i32
@@ -328,6 +333,43 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
         check(lib().b200lut_silu_mul(gate.data_ptr(), up.data_ptr(), M, N, gate.stride(0), up.stride(0),
                                      dtype_id(gate.dtype), _stream(gate)))
     return gate
+
+
+def embed_gather(ids: torch.Tensor, table: dict, K: int, dtype: torch.dtype,
+                 out_fp32: bool = False) -> torch.Tensor:
+    """Rows ids (1-D int64 CUDA tensor) of a palettized [N, K] table -> [n, K] in `dtype`
+    (fp32 with out_fp32). table: packed, lut, bits, N, group_size, n_groups and optionally
+    packed2 / lut2 / bits2 and resA + resB (both or neither)."""
+    _need_cuda(ids, "ids")
+    if ids.dim() != 1 or ids.dtype != torch.int64 or not ids.is_contiguous():
+        raise ValueError("embed_gather expects a contiguous 1-D int64 id tensor")
+    n = ids.numel()
+    out = torch.empty(n, K, dtype=torch.float32 if out_fp32 else dtype, device=ids.device)
+    seg = (Segment * 1)()
+    s = seg[0]
+    s.packed, s.lut = ptr(table["packed"]), ptr(table["lut"])
+    s.packed2, s.lut2 = ptr(table.get("packed2")), ptr(table.get("lut2"))
+    s.out, s.ldo = out.data_ptr(), K
+    s.N, s.group_size, s.n_groups = int(table["N"]), int(table["group_size"]), int(table["n_groups"])
+    s.bits, s.bits2 = int(table["bits"]), int(table.get("bits2") or 0)
+    resA, resB = table.get("resA"), table.get("resB")
+    if resA is not None:
+        s.resA, s.res_rank = ptr(resA), int(resA.shape[1])
+    with torch.cuda.device(ids.device):
+        check(lib().b200lut_embed_gather(ids.data_ptr(), n, K, dtype_id(dtype), seg, ptr(resB),
+                                         1 if out_fp32 else 0, _stream(ids)))
+    return out
+
+
+def round_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """fp32 [M, K] rows -> `dtype` (one rounding)."""
+    _need_cuda(x, "x")
+    M, K = x.shape
+    out = torch.empty(M, K, dtype=dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().b200lut_round_rows(x.data_ptr(), x.stride(0), out.data_ptr(), K, M, K,
+                                       dtype_id(dtype), _stream(x)))
+    return out
 
 
 _gemm_scratch = {}

@@ -31,7 +31,8 @@ import numpy as np
 import torch
 import torch.nn as nn
 
-from .palettized_modules import FusedPalettizedMLP, PalettizedLinear, SplitQKV
+from .palettized_modules import (FusedPalettizedMLP, PalettizedEmbedding, PalettizedLinear,
+                                 SplitQKV)
 
 _IDX_NAME = re.compile(r"^(?P<stem>.*)\.idx(?P<bits>[1-4])(?P<tag>\.[^./]+)?$")
 HEAD_TENSORS = ("model.lm_head.weight", "model.embed_tokens.weight")
@@ -221,6 +222,61 @@ class ArtifactDir:
                                 rotation_k=rot["k"] if rot else None,
                                 awq_scale=awq_scale, fold_order=fold_order)
 
+    def load_embedding(self, meta: Dict, residual: bool = True) -> PalettizedEmbedding:
+        """PalettizedEmbedding of an embed_tokens entry: both declared streams, the residual
+        pair when present, the rotation record of a tied head set (reference
+        load_palettized_embedding, palettized_modules.py:2731-2768)."""
+        ctx = meta.get("var", "?")
+        if "components" in meta:
+            raise ValueError(f"{ctx}: an embedding meta carries no QKV components (embed_tokens is "
+                             f"a single matrix, never a fused projection); refusing to guess a "
+                             f"component split")
+        blob, lut, bits, gs, N, K = self.read_stream(meta, ctx)
+        resA = resB = None
+        if residual:
+            resA, resB = self.read_residual(meta, ctx, N, K)
+        blob2 = lut2 = bits2 = None
+        if meta.get("streams"):
+            blob2, lut2, bits2 = self.read_stream2(meta, ctx, N, K, bits, gs)
+        rot = meta.get("rotation")
+        return PalettizedEmbedding(blob, lut, bits, gs, N, K, indices2=blob2, lut2=lut2,
+                                   bitwidth2=bits2, resA=resA, resB=resB,
+                                   rotation_seed=rot["seed"] if rot else None,
+                                   rotation_k=rot["k"] if rot else None)
+
+    def load_tied_pair(self, lm_meta: Dict, embed_meta: Optional[Dict], residual: bool = True,
+                       reference: bool = False, awq_scales: Optional[Dict] = None):
+        """(PalettizedLinear, PalettizedEmbedding) over ONE artifact set: read once through
+        the lm_head's metadata, the embedding built on the same tensors; both metas must
+        describe the same member set (reference load_tied_pair, :2792-2872)."""
+        lm_var = str(lm_meta.get("var", "?"))
+        if embed_meta is None:
+            embed_meta, emb_var = lm_meta, f"{lm_var}(tied)"
+        else:
+            emb_var = str(embed_meta.get("var", "?"))
+        if lm_meta.get("tied") is not True:
+            raise ValueError(f"load_tied_pair({lm_var}, {emb_var}): the lm_head metadata does not "
+                             f"carry the writer's \"tied\": true record — this is not a "
+                             f"one-artifact-set tied entry; load each consumer separately")
+        if "components" in lm_meta:
+            raise ValueError(f"load_tied_pair({lm_var}, {emb_var}): a tied head is a single matrix, "
+                             f"never a QKV component split")
+        rows_l, rows_e = tied_member_rows(lm_meta), tied_member_rows(embed_meta)
+        if rows_l != rows_e:
+            detail = "the member sets differ"
+            for i in range(max(len(rows_l), len(rows_e))):
+                a = rows_l[i] if i < len(rows_l) else None
+                b = rows_e[i] if i < len(rows_e) else None
+                if a != b:
+                    detail = (f"member {a[0] if a else b[0]}: lm_head expects {a[1:] if a else None}, "
+                              f"embed expects {b[1:] if b else None}")
+                    break
+            raise ValueError(f"load_tied_pair({lm_var}, {emb_var}): the two consumers' metadata "
+                             f"describe different artifact sets — {detail}; refusing to serve one "
+                             f"artifact set to disagreeing consumers")
+        lm = self.load_weight(lm_meta, residual=residual, reference=reference, awq_scales=awq_scales)
+        return lm, PalettizedEmbedding.tied_to(lm)
+
     def load_weight(self, meta: Dict, bias=None, residual: bool = False, reference: bool = False,
                     awq_scales: Optional[Dict] = None):
         """PalettizedLinear, or SplitQKV for a fused QKV tensor (the original bias is
@@ -248,6 +304,22 @@ class ArtifactDir:
         return SplitQKV(*parts)
 
 
+def tied_member_rows(meta: Dict):
+    """(member, file, expected sha256) rows of every artifact member a consumer's metadata
+    describes; two consumers of one tied set must produce equal rows (reference
+    _tied_member_rows, palettized_modules.py:2771-2789)."""
+    rows = [("index_file", meta.get("index_file"), meta.get("sha256_idx")),
+            ("lut_file", meta.get("lut_file"), meta.get("sha256_lut"))]
+    for i, entry in enumerate(meta.get("streams") or []):
+        rows.append((f"streams[{i}].idxN", entry.get("file"), entry.get("sha256")))
+        rows.append((f"streams[{i}].lut_scalar", entry.get("file"), entry.get("sha256_lut")))
+    res = meta.get("residual")
+    if res:
+        rows.append(("resA_file", res.get("resA_file"), res.get("sha256_resA")))
+        rows.append(("resB_file", res.get("resB_file"), res.get("sha256_resB")))
+    return rows
+
+
 def _awq_for(meta: Dict, awq_scales: Optional[Dict]):
     """(K-vector scale, fold order) recorded for a tensor, (None, None) when unscaled."""
     if not awq_scales:
@@ -265,6 +337,20 @@ def load_palettized_weight(tensor_meta: Dict, artifacts_dir: str, bias=None, res
     """The reference's per-tensor entry (palettized_modules.py:2619-2724)."""
     return ArtifactDir(artifacts_dir, verify_sha).load_weight(tensor_meta, bias, residual, reference,
                                                              awq_scales)
+
+
+def load_palettized_embedding(tensor_meta: Dict, artifacts_dir: str, residual: bool = True,
+                              verify_sha: bool = True) -> PalettizedEmbedding:
+    """The reference's embedding entry (palettized_modules.py:2731-2768)."""
+    return ArtifactDir(artifacts_dir, verify_sha).load_embedding(tensor_meta, residual)
+
+
+def load_tied_pair(lm_head_meta: Dict, embed_meta: Optional[Dict], artifacts_dir: str,
+                   residual: bool = True, reference: bool = False, verify_sha: bool = True,
+                   awq_scales: Optional[Dict] = None):
+    """The reference's tied-pair entry (palettized_modules.py:2792-2872)."""
+    return ArtifactDir(artifacts_dir, verify_sha).load_tied_pair(lm_head_meta, embed_meta, residual,
+                                                                reference, awq_scales)
 
 
 # ------------------------------------------------------------------------- swap
@@ -331,10 +417,10 @@ def replace_linear_with_palettized(model, metadata, artifacts_dir: str, residual
                                    heads_dir: Optional[str] = None):
     """Swap every tensor of the metadata for its palettized module, then install
     the fused MLP wrappers (the reference's swap, palettized_modules.py:2921-3027).
-    `model.lm_head.weight` is a linear layer like any other (248 320 rows on the 9B model)
-    and is swapped too unless it is tied to the embedding; `model.embed_tokens.weight` is
-    a gather, for which the reference has no kernel either: it is left untouched and
-    reported."""
+    `model.lm_head.weight` is a linear layer like any other (248 320 rows on the 9B model);
+    `model.embed_tokens.weight` becomes a PalettizedEmbedding; an lm_head entry that carries
+    "tied": true serves both consumers from one artifact set (one copy of the codes on the
+    device)."""
     tensors = dict(metadata["tensors"])
     if heads_dir is not None:
         heads = load_metadata(heads_dir)["tensors"]
@@ -344,25 +430,29 @@ def replace_linear_with_palettized(model, metadata, artifacts_dir: str, residual
                 tensors[key] = heads[key]
     art = ArtifactDir(artifacts_dir, verify_sha)
     head_art = None
-    skipped = []
     for name, meta in tensors.items():
-        if name == "model.embed_tokens.weight" or (name in HEAD_TENSORS and meta.get("tied") is True):
-            skipped.append(name)
-            continue
         head_dir = heads_dir if (heads_dir is not None and name in HEAD_TENSORS) else None
         if head_dir is not None and (head_art is None):
             head_art = ArtifactDir(head_dir, verify_sha)
+        src = head_art if head_dir is not None else art
+        if name == "model.lm_head.weight" and meta.get("tied") is True:
+            lm, emb = src.load_tied_pair(meta, None, residual=residual, reference=reference,
+                                         awq_scales=awq_scales)
+            holder, leaf = resolve_module(model, name)
+            setattr(holder, leaf, lm)
+            holder, leaf = resolve_module(model, "model.embed_tokens.weight")
+            setattr(holder, leaf, emb)
+            continue
         holder, leaf = resolve_module(model, name)
         old = getattr(holder, leaf)
-        bias = getattr(old, "bias", None)
-        src = head_art if head_dir is not None else art
-        new = src.load_weight(meta, bias=None if bias is None else bias.data, residual=residual,
-                              reference=reference, awq_scales=awq_scales)
+        if name == "model.embed_tokens.weight":
+            new = src.load_embedding(meta, residual=residual)
+        else:
+            bias = getattr(old, "bias", None)
+            new = src.load_weight(meta, bias=None if bias is None else bias.data, residual=residual,
+                                  reference=reference, awq_scales=awq_scales)
         setattr(holder, leaf, new)
         del old
     art.summarize_gs()
-    if skipped:
-        print(f"  [heads] not swapped (embedding gather / tied head are not part of this package): "
-              f"{', '.join(skipped)}", flush=True)
     install_fused_mlp(model)
     return model

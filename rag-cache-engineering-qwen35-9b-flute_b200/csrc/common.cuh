@@ -91,5 +91,7 @@ template <> struct DType<__half> {
 
 // Status word of the decode kernels' exchange waits (defined with the GEMV): value and clear.
 int exchange_status_take();
+// Status word of the embedding gather (an id outside the table): value and clear.
+int embed_status_take();
 
 }  // namespace b200lut

@@ -964,7 +964,8 @@ extern "C" int b200lut_device_status(void) {
   if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
   if (v != 0) cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
   const int e = b200lut::exchange_status_take();
-  return v != 0 ? v : e;
+  const int g = b200lut::embed_status_take();
+  return v != 0 ? v : (e != 0 ? e : g);
 }
 
 extern "C" size_t b200lut_gemm_workspace_bytes(int M, int N, int K) {

@@ -498,3 +498,200 @@ class FusedPalettizedMLP(nn.Module):
         x2 = x2.to(cd).contiguous()
         y = self.fused_gate_up(x2).to(x.dtype)
         return self.down_proj(y).reshape(*x.shape[:-1], self.down_proj.N)
+
+
+class PalettizedEmbedding(nn.Module):
+    """Embedding over a palettized [N, K] table: forward(ids) gathers rows.
+
+    Drop-in for the reference's PalettizedEmbedding
+    (src/scripts/palettized_modules.py:1979-2335): same constructor signature,
+    attribute names and dtype ladder —
+        w   = lut1[id // gs][idx1[id]] (+ lut2[id // gs][idx2[id]], one add in the palette
+              dtype, stream 1 first)
+        out = (w.float() + resA[id].float() @ resB.float())  [-> adjoint Hadamard transform
+              when the table is a tied, rotated head]  -> palette dtype, ONE rounding.
+    The reference gathers through torch indexing over an unpacked [N, K] uint8 copy of the
+    codes; here one CUDA launch (b200lut_embed_gather) reads the rows out of the packed slab
+    layout, so a table tied to an lm_head (`tied_to`) shares that module's codes and nothing
+    is unpacked. There is no CPU route, and no trainable-palette mode.
+
+    Ids outside [0, N): CPU ids raise ValueError like the reference; for CUDA ids the
+    reference aborts the context with a device-side assertion, this module writes a row of
+    zeros and raises the library's device status (`_lib.lib().b200lut_device_status()`),
+    without a host synchronisation.
+    """
+
+    def __init__(self, indices, lut, bitwidth, group_size, N, K, indices2=None, lut2=None,
+                 bitwidth2=None, resA=None, resB=None, num_embeddings=None, embedding_dim=None,
+                 rotation_seed: int = None, rotation_k: int = None):
+        super().__init__()
+        self.bitwidth = int(bitwidth)
+        if self.bitwidth not in (1, 2, 3, 4):
+            raise ValueError(f"PalettizedEmbedding: bitwidth {self.bitwidth} not in 1..4 — the idxN "
+                             f"artifact family is the contract")
+        self.bitwidth2 = int(bitwidth2) if bitwidth2 is not None else self.bitwidth
+        if self.bitwidth2 not in (1, 2, 3, 4):
+            raise ValueError(f"PalettizedEmbedding: bitwidth2 {self.bitwidth2} not in 1..4 — the "
+                             f"idxN artifact family is the contract")
+        self.group_size = int(group_size)
+        self.N, self.K = int(N), int(K)
+        if num_embeddings is not None and int(num_embeddings) != self.N:
+            raise ValueError(f"PalettizedEmbedding: num_embeddings {num_embeddings} != N {self.N}; "
+                             f"the two spellings must agree")
+        if embedding_dim is not None and int(embedding_dim) != self.K:
+            raise ValueError(f"PalettizedEmbedding: embedding_dim {embedding_dim} != K {self.K}; "
+                             f"the two spellings must agree")
+        if self.N % 128 != 0 or self.K % 64 != 0:
+            raise ValueError(f"idxN layout requires N%128==0 and K%64==0, got N={self.N}, K={self.K}")
+        indices = torch.as_tensor(indices)
+        expected = (self.N * self.K * self.bitwidth) // 8
+        if indices.numel() != expected:
+            raise ValueError(f"idx{self.bitwidth} blob numel {indices.numel()} != "
+                             f"N*K*{self.bitwidth}/8 {expected} (N={self.N}, K={self.K})")
+        self.register_buffer("indices", indices, persistent=False)
+        self.register_buffer("lut", PalettizedLinear._lut2d(lut, self.bitwidth), persistent=False)
+        if resA is not None and resB is not None:
+            if resA.shape != (self.N, resB.shape[0]) or resB.shape[1] != self.K:
+                raise ValueError(f"residual factors shape mismatch: A {tuple(resA.shape)}, "
+                                 f"B {tuple(resB.shape)} for N={self.N}, K={self.K}")
+            self.register_buffer("resA", resA, persistent=False)
+            self.register_buffer("resB", resB, persistent=False)
+        else:
+            self.resA = self.resB = None
+        if indices2 is None and lut2 is None:
+            self.indices2 = self.lut2 = None
+        elif indices2 is None or lut2 is None:
+            raise ValueError("PalettizedEmbedding: a second stream needs BOTH indices2 and lut2; "
+                             "refusing a half-constructed two-stream module")
+        else:
+            indices2 = torch.as_tensor(indices2)
+            expected2 = (self.N * self.K * self.bitwidth2) // 8
+            if indices2.numel() != expected2:
+                raise ValueError(f"idx{self.bitwidth2} stream-2 blob numel {indices2.numel()} != "
+                                 f"N*K*{self.bitwidth2}/8 {expected2} (N={self.N}, K={self.K})")
+            lut2_t = PalettizedLinear._lut2d(lut2, self.bitwidth2)
+            if lut2_t.shape[0] != self.lut.shape[0]:
+                raise ValueError(f"stream-2 LUT groups {lut2_t.shape[0]} != stream-1 "
+                                 f"{self.lut.shape[0]}; both streams must share the group grid")
+            self.register_buffer("indices2", indices2, persistent=False)
+            self.register_buffer("lut2", lut2_t, persistent=False)
+        self.rotation_seed = int(rotation_seed) if rotation_seed is not None else None
+        self.rotation_k = int(rotation_k) if rotation_k is not None else None
+        self.rot_signs = None
+        self._signs_cache = {}
+        if self.rotation_seed is not None and self.rotation_k is not None:
+            if self.rotation_k != self.K:
+                raise ValueError(f"PalettizedEmbedding: rotation_k {self.rotation_k} != the embedding "
+                                 f"dim K {self.K} — corrupt rotation record on a tied artifact set")
+            self.rot_signs = _fht.rotation_signs(self.rotation_k, self.rotation_seed)
+        self._packed = None
+        self._packed2 = None
+        self._tied = []          # [PalettizedLinear] whose slab copies serve this table
+
+    @classmethod
+    def tied_to(cls, lm: PalettizedLinear) -> "PalettizedEmbedding":
+        """The embedding consumer of a tied head: the SAME buffers as `lm` (blobs, palettes,
+        residual factors) and the same slab copy of the codes; inherits the head's rotation
+        record, so gathered rows are un-rotated (reference load_tied_pair, :2792-2872)."""
+        emb = cls(lm.indices, lm.lut, lm.bitwidth, lm.group_size, lm.N, lm.K,
+                  indices2=lm.indices2, lut2=lm.lut2,
+                  bitwidth2=lm.bitwidth2 if lm.has_stream2 else None, resA=lm.resA, resB=lm.resB,
+                  rotation_seed=lm.rotation_seed, rotation_k=lm.rotation_k) \
+            if lm.indices.numel() else None
+        if emb is None:           # the head already dropped its blob: build around its slab copy
+            emb = cls.__new__(cls)
+            nn.Module.__init__(emb)
+            emb.bitwidth, emb.bitwidth2, emb.group_size = lm.bitwidth, lm.bitwidth2, lm.group_size
+            emb.N, emb.K = lm.N, lm.K
+            for name in ("indices", "lut", "resA", "resB", "indices2", "lut2"):
+                v = getattr(lm, name)
+                if v is None:
+                    setattr(emb, name, None)
+                else:
+                    emb.register_buffer(name, v, persistent=False)
+            emb.rotation_seed, emb.rotation_k = lm.rotation_seed, lm.rotation_k
+            emb.rot_signs, emb._signs_cache = lm.rot_signs, {}
+            emb._packed = emb._packed2 = None
+        emb._tied = [lm]
+        return emb
+
+    # the nn.Embedding spellings
+    @property
+    def num_embeddings(self) -> int:
+        return self.N
+
+    @property
+    def embedding_dim(self) -> int:
+        return self.K
+
+    def has_residual(self) -> bool:
+        return self.resA is not None and self.resB is not None
+
+    @property
+    def has_stream2(self) -> bool:
+        return self.indices2 is not None and self.lut2 is not None
+
+    def _logical_indices_numpy(self, blob=None, bits=None) -> np.ndarray:
+        """(N, K) uint8 logical codes of a stream's idxN blob (host, numpy)."""
+        b = int(bits) if bits is not None else self.bitwidth
+        blob = self.indices if blob is None else blob
+        arr = np.ascontiguousarray(blob.detach().cpu().numpy(), dtype=np.uint8).reshape(-1)
+        return _idxn.unpack_idxn(arr, self.N, self.K, b)
+
+    def _signs_on(self, device) -> torch.Tensor:
+        key = str(device)
+        v = self._signs_cache.get(key)
+        if v is None:
+            v = self.rot_signs.to(device=device, dtype=torch.float32).contiguous()
+            self._signs_cache[key] = v
+        return v
+
+    def _table(self) -> dict:
+        dev = self.lut.device
+        if not self.lut.is_cuda:
+            raise RuntimeError("PalettizedEmbedding: move the module to a CUDA device first "
+                               "(this package has no CPU compute route)")
+        if self.lut.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError(f"PalettizedEmbedding: LUT dtype must be float16 or bfloat16, got "
+                             f"{self.lut.dtype}")
+        if self._tied and self._tied[0].lut.device == dev:
+            lm = self._tied[0]
+            lm._ensure_packed()
+            p1, p2 = lm._packed, lm._packed2
+        else:
+            if self._packed is None or self._packed.device != dev:
+                self._packed = _lib.repack_from_idxn(self.indices.to(dev), self.N, self.K, self.bitwidth)
+                self._packed2 = None
+            if self.has_stream2 and self._packed2 is None:
+                self._packed2 = _lib.repack_from_idxn(self.indices2.to(dev), self.N, self.K,
+                                                      self.bitwidth2)
+            p1, p2 = self._packed, self._packed2
+        d = dict(packed=p1, lut=self.lut, bits=self.bitwidth, N=self.N, group_size=self.group_size,
+                 n_groups=self.lut.shape[0])
+        if self.has_stream2:
+            d.update(packed2=p2, lut2=self.lut2.to(self.lut.dtype), bits2=self.bitwidth2)
+        if self.has_residual():
+            d.update(resA=self.resA.to(self.lut.dtype).contiguous(),
+                     resB=self.resB.to(self.lut.dtype).contiguous())
+        return d
+
+    def forward(self, ids):
+        if not torch.is_tensor(ids):
+            ids = torch.as_tensor(ids)
+        if ids.dtype not in (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8):
+            raise ValueError(f"PalettizedEmbedding.forward: ids must be an integer tensor, got dtype "
+                             f"{ids.dtype}")
+        if not ids.is_cuda and ids.numel() and (int(ids.min()) < 0 or int(ids.max()) >= self.N):
+            raise ValueError(f"PalettizedEmbedding.forward: ids out of range [0, {self.N}) (min "
+                             f"{int(ids.min())}, max {int(ids.max())}); refusing a silent wrap")
+        table = self._table()
+        flat = ids.to(device=self.lut.device, dtype=torch.int64).reshape(-1).contiguous()
+        dtype = self.lut.dtype
+        if self.rot_signs is None:
+            out = _lib.embed_gather(flat, table, self.K, dtype)
+        else:
+            w = _lib.embed_gather(flat, table, self.K, dtype, out_fp32=True)
+            if flat.numel():
+                w = _lib.fht(w, self._signs_on(w.device), _lib.FHT_ADJOINT, out=w)
+            out = _lib.round_rows(w, dtype)
+        return out.view(*ids.shape, self.K)

@@ -69,3 +69,8 @@ class Golden:
 @pytest.fixture(scope="session")
 def golden():
     return Golden(os.path.join(ROOT, "tests", "golden", "reference_vectors.npz"))
+
+
+@pytest.fixture(scope="session")
+def golden_embedding():
+    return Golden(os.path.join(ROOT, "tests", "golden", "embedding_vectors.npz"))

@@ -56,3 +56,13 @@ def tiny_skeleton(hidden: int = 128, inter: int = 256, seed: int = 7) -> nn.Modu
         m.model.layers[0].linear_attn.in_proj_qkv.bias.copy_(
             0.1 * torch.randn(3 * hidden, generator=torch.Generator().manual_seed(seed)))
     return m
+
+
+def tiny_skeleton_with_heads(hidden: int = 128, inter: int = 256, vocab: int = 256,
+                             seed: int = 7) -> nn.Module:
+    """The same skeleton plus the two head modules the head artifacts address:
+    `lm_head` on the wrapper and `embed_tokens` on the text model."""
+    m = tiny_skeleton(hidden, inter, seed)
+    m.lm_head = nn.Linear(hidden, vocab, bias=False)
+    m.model.embed_tokens = nn.Embedding(vocab, hidden)
+    return m

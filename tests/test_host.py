@@ -81,6 +81,17 @@ def test_validation_errors_carry_a_message():
     assert rc == 2 and b"M=17" in L.b200lut_last_error()
     rc = L.b200lut_residual_project(x, 64, 1, 64, 0, None, 8, x, 8, 0, None)
     assert rc == 1 and b"null" in L.b200lut_last_error()
+    rc = L.b200lut_embed_gather(x, 4, 60, 0, ctypes.byref(seg), None, 0, None)
+    assert rc == 1 and b"K %% 64" in L.b200lut_last_error() or b"64" in L.b200lut_last_error()
+    rc = L.b200lut_embed_gather(x, -1, 64, 0, ctypes.byref(seg), None, 0, None)
+    assert rc == 1 and b"n_ids" in L.b200lut_last_error()
+    seg.res_rank = 4
+    rc = L.b200lut_embed_gather(x, 4, 64, 0, ctypes.byref(seg), None, 0, None)
+    assert rc == 1 and b"resA and resB" in L.b200lut_last_error()
+    seg.res_rank = 0
+    assert L.b200lut_embed_gather(None, 0, 64, 0, ctypes.byref(seg), None, 0, None) == 0   # no ids: no launch
+    rc = L.b200lut_round_rows(None, 8, None, 4, 2, 8, 0, None)
+    assert rc == 1 and b"strides" in L.b200lut_last_error()
     rc = L.b200lut_silu_mul(x, x, 4, 12, 16, 16, 0, None)
     assert rc == 1 and b"multiple of 8" in L.b200lut_last_error()
     rc = L.b200lut_silu_mul(x, x, 4, 16, 12, 16, 0, None)

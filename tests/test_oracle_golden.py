@@ -160,3 +160,28 @@ def test_fused_silu_mul_close_to_unfused():
     fused = orc.silu_mul_fused(a, b, torch.bfloat16)
     unfused = torch.nn.functional.silu(a.bfloat16()) * b.bfloat16()
     assert orc.max_rel_err(fused, unfused.float()) < 2e-2
+
+
+EMBED_CASES = ("e1", "e2", "e3", "e4", "e5", "e6", "e7")
+
+
+@pytest.mark.parametrize("name", EMBED_CASES)
+def test_embedding_forward_matches_reference_module(golden_embedding, name):
+    g = golden_embedding
+    N, K, gs, bits, bits2, rank, rot = (int(v) for v in g.np(name + "_meta"))
+    signs = orc.rotation_signs(K, rot) if rot >= 0 else None
+    got = orc.embedding_forward(
+        g.t(name + "_ids"), g.np(name + "_codes"), g.t(name + "_lut"), gs,
+        idx2=g.np(name + "_codes2") if bits2 else None, lut2=g.opt(name + "_lut2"),
+        resA=g.opt(name + "_resA"), resB=g.opt(name + "_resB"), rot_signs=signs)
+    want = g.t(name + "_out")
+    assert got.dtype == want.dtype and got.shape == want.shape
+    assert torch.equal(got, want)
+
+
+def test_embedding_forward_refuses_ids_outside_the_table(golden_embedding):
+    g = golden_embedding
+    with pytest.raises(ValueError):
+        orc.embedding_forward(torch.tensor([256]), g.np("e1_codes"), g.t("e1_lut"), 64)
+    with pytest.raises(ValueError):
+        orc.embedding_forward(torch.tensor([-1]), g.np("e1_codes"), g.t("e1_lut"), 64)
