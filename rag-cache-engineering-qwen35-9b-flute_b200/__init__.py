@@ -9,10 +9,12 @@ from . import _lib, fht, idxN, synthetic                                    # no
 from .palettized_modules import (FusedPalettizedMLP, PalettizedEmbedding, PalettizedLinear,  # noqa: F401
                                  SplitQKV,
                                  reference_dequant, set_programmatic_launch)
-from .artifacts import (load_metadata, load_palettized_weight,                     # noqa: F401
-                        replace_linear_with_palettized)
+from .artifacts import (load_metadata, load_palettized_embedding, load_palettized_weight,  # noqa: F401
+                        load_tied_pair, replace_linear_with_palettized)
+from .lut_export import export_luts, import_luts, iter_palettized_linears      # noqa: F401
 from .loader import load_quant_model                                             # noqa: F401
 
 __all__ = ["load_quant_model", "load_palettized_weight", "replace_linear_with_palettized",
-           "load_metadata", "PalettizedLinear", "PalettizedEmbedding", "SplitQKV", "FusedPalettizedMLP", "reference_dequant",
+           "load_palettized_embedding", "load_tied_pair", "export_luts", "import_luts",
+           "iter_palettized_linears", "load_metadata", "PalettizedLinear", "PalettizedEmbedding", "SplitQKV", "FusedPalettizedMLP", "reference_dequant",
            "set_programmatic_launch", "fht", "idxN", "synthetic"]
