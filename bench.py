@@ -323,6 +323,29 @@ def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool):
     return 2.0 * M * N * K / us / 1e6, us
 
 
+def embedding_gather_gbs(pkg, N: int, K: int, n_ids: int, iters: int):
+    """Extra: the embedding gather over an lm_head-sized 4-bit table (0.51 GB of codes, far
+    beyond L2), `n_ids` random rows per launch; returns (GB/s of algorithmic bytes, us).
+    Algorithmic bytes per row: K/2 of codes + 2K of output."""
+    import torch
+    L = pkg._lib
+    bits, gs, dt = 4, 128, torch.bfloat16
+    packed = L.repack_from_idxn(pkg.synthetic.random_blob_on_device(N, K, bits, 811, "cuda"), N, K, bits)
+    lut = pkg.synthetic.make_lut(N // gs, bits, dt, 811).cuda()
+    table = dict(packed=packed, lut=lut, bits=bits, N=N, group_size=gs, n_groups=N // gs)
+    ids = torch.randint(0, N, (n_ids,), device="cuda", generator=torch.Generator("cuda").manual_seed(5))
+
+    def run():
+        L.embed_gather(ids, table, K, dt)
+    for _ in range(3):
+        run()
+    ms = time_steps(run, iters, 1)
+    if L.lib().b200lut_device_status() != 0:
+        raise RuntimeError("the embedding gather met an id outside its table")
+    us = ms * 1e3 / iters
+    return n_ids * (K * bits // 8 + 2 * K) / us / 1e3, us
+
+
 def run_case(args) -> int:
     """A few eager launches of one kernel on a profiling-sized case. gemv: 12288 x 4096
     4-bit projection at M = 1 over 8 distinct weight sets (192 MB of codes, larger than L2);
@@ -518,6 +541,9 @@ def main() -> int:
             gbs, us = single_projection_gbs(pkg, 1, 248320, 4096, 1, 10, flags)
             extras["gemv_248320x4096_m1_lm_head"] = {"GB/s": gbs, "us_per_launch": us,
                                                      "frac_of_hbm": gbs / peaks["hbm_gbs"]}
+            gbs, us = embedding_gather_gbs(pkg, 248320, 4096, 2048, 20)
+            extras["embedding_gather_248320x4096_2048_ids"] = {
+                "GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}
             # the whole stack at prefill width: every projection as a tensor-core GEMM
             # (gate, then up multiplying silu of the gate's output), eager launches
             Mp = 2048
