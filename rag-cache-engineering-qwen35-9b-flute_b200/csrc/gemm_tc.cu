@@ -773,8 +773,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
       if (cut) {
         // All `split` blocks of the tile store their partial tiles, meet on a counter (bounded
         // wait: the grid is one block per SM and every block does its cut piece first), and
-        // each finishes the 16-column chunks k with k % split == its part: the partial sums
-        // are added in part (= ascending k) order, bias, one rounding, element stores.
+        // each finishes the token pairs g with g % split == its part: the partial sums are
+        // added in part (= ascending k) order, bias, one rounding, element stores.
         int* cnt = p.tickets + 2 * (tile - int(gridDim.x) * p.full);
         __threadfence();
         asm volatile("bar.sync 4, %0;" ::"r"(kPEpiWarps * 32) : "memory");
@@ -791,21 +791,26 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
         asm volatile("bar.sync 4, %0;" ::"r"(kPEpiWarps * 32) : "memory");
         if (*cut_flag) {
           __threadfence();
-          const int nchunk = nt >> 4;
-          for (int k = cut_part + p.split * h; k < nchunk; k += 2 * p.split) {   // the two halves alternate
-            float acc[16];
+          // pairs of tokens, dealt round-robin over the parts and the two column halves; all
+          // `split` partial values of a pair are requested before the first is used
+          const int ngrp = nt >> 1;
+          for (int g2 = cut_part + p.split * h; g2 < ngrp; g2 += 2 * p.split) {
+            float v[8][2];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-            for (int ci = 0; ci < p.split; ++ci) {
-              const float* src = wt + (size_t(ci) * 256 + 16 * k) * kTileRows + 32 * q + lane;
-#pragma unroll
-              for (int j = 0; j < 16; ++j) acc[j] += __ldcg(src + size_t(j) * kTileRows);
+            for (int ci = 0; ci < 8; ++ci) {
+              if (ci < p.split) {
+                const float* src = wt + (size_t(ci) * 256 + 2 * g2) * kTileRows + 32 * q + lane;
+                v[ci][0] = __ldcg(src);
+                v[ci][1] = __ldcg(src + kTileRows);
+              }
             }
+            float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int tok = m0 + 16 * k + j;
-              if (tok < p.M) p.out[size_t(tok) * p.ldo + n] = DType<T>::from_float(acc[j] + b0);
-            }
+            for (int ci = 0; ci < 8; ++ci)
+              if (ci < p.split) { a0 += v[ci][0]; a1 += v[ci][1]; }
+            const int tok = m0 + 2 * g2;
+            if (tok < p.M) p.out[size_t(tok) * p.ldo + n] = DType<T>::from_float(a0 + b0);
+            if (tok + 1 < p.M) p.out[size_t(tok + 1) * p.ldo + n] = DType<T>::from_float(a1 + b0);
           }
         }
         asm volatile("bar.sync 4, %0;" ::"r"(kPEpiWarps * 32) : "memory");
