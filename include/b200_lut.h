@@ -294,6 +294,18 @@ int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dtype,
                     const b200lut_segment* seg, int epilogue, int flags,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* Several projections that share x as ONE prefill launch: Q/K/V(/z) of an attention block, or
+ * gate and up of an MLP (out[i] = x @ W_i^T + bias_i, every projection into its own out / ldo).
+ * The row tiles of the projections are concatenated, so the launch fills the SMs like one wide
+ * projection (and the split schedule of b200lut_gemm_ws applies to the sum; size the workspace
+ * with b200lut_gemm_workspace_bytes(M, sum of N, K)). 1 <= nseg <= 4; one code stream per
+ * projection, one code width and one group size (>= 64) for all; K >= 128. Counterpart of
+ * the merged decode launch (b200lut_gemv_multi) at prefill width; the reference runs one
+ * streaming GEMM per projection (src/scripts/palettized_modules.py:1468-1641 at M > 16). */
+int b200lut_gemm_multi(const void* x, int64_t ldx, int M, int K, int dtype,
+                       const b200lut_segment* segs, int nseg, int flags,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- embedding gather ----------------------------------------------------------------------
  *
  * out[t, :] = W[ids[t], :] for n_ids int64 ids on the device, W the palettized [N, K] table

@@ -27,7 +27,7 @@ EXPORTS = (
     "b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes",
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
-    "b200lut_residual_project", "b200lut_silu_mul", "b200lut_gemm_workspace_bytes", "b200lut_gemm_ws",
+    "b200lut_residual_project", "b200lut_silu_mul", "b200lut_gemm_workspace_bytes", "b200lut_gemm_ws", "b200lut_gemm_multi",
     "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
     "b200lut_gemv_noalloc", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
@@ -114,6 +114,8 @@ def lib() -> ctypes.CDLL:
     L.b200lut_gemm_workspace_bytes.argtypes = [i32, i32, i32]
     L.b200lut_gemm_ws.restype = i32
     L.b200lut_gemm_ws.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32, vp, sz, vp]
+    L.b200lut_gemm_multi.restype = i32
+    L.b200lut_gemm_multi.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32, vp, sz, vp]
     L.b200lut_embed_gather.restype = i32
     L.b200lut_embed_gather.argtypes = [vp, i64, i32, i32, ctypes.POINTER(Segment), vp, i32, vp]
     L.b200lut_round_rows.restype = i32
@@ -403,6 +405,32 @@ def gemm(x: torch.Tensor, seg, epilogue: int = EPI_NONE, flags: int = 0, split: 
         else:
             check(lib().b200lut_gemm(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), seg,
                                      epilogue, flags, _stream(x)))
+
+
+GEMM_MULTI_MAX = 4
+
+
+def gemm_multi_ok(descs: Sequence[dict], K: int) -> bool:
+    """True when the projections described by `descs` (dicts as for make_segments) can run as
+    one merged prefill launch: at most four, one code stream each, one code width, one group
+    size >= 64, K >= 128."""
+    if not 1 <= len(descs) <= GEMM_MULTI_MAX or K < 128:
+        return False
+    d0 = descs[0]
+    return all(d.get("packed2") is None and d.get("resA") is None and d["bits"] == d0["bits"]
+               and d["group_size"] == d0["group_size"] and d["group_size"] >= 64 for d in descs)
+
+
+def gemm_multi(x: torch.Tensor, segs, nseg: int, flags: int = 0, split: bool = True) -> None:
+    """Prefill GEMM over `nseg` projections that share x, as one launch."""
+    _need_cuda(x, "x")
+    M, K = x.shape
+    with torch.cuda.device(x.device):
+        total = sum(int(segs[i].N) for i in range(nseg))
+        need = lib().b200lut_gemm_workspace_bytes(M, total, K) if split else 0
+        ws = _gemm_workspace(x.device, int(_stream(x) or 0), need) if need else None
+        check(lib().b200lut_gemm_multi(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), segs, nseg,
+                                       flags, ptr(ws), ws.numel() if ws is not None else 0, _stream(x)))
 
 
 def fht(x: torch.Tensor, signs: Optional[torch.Tensor], mode: int = FHT_FORWARD,

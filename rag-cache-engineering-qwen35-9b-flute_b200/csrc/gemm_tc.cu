@@ -369,19 +369,27 @@ constexpr int kPStages = 4;             // ring depth of both operands
 constexpr uint32_t kPACol = 256;        // operand stage s at columns [256 + 32 s, 288 + 32 s)
 constexpr int kPStageTokens = 48;       // tokens per staged epilogue slice (12 KB per column half)
 
-struct PersistParams {
+constexpr int kPMaxSeg = 4;             // projections that share x in one launch (Q/K/V/z, gate/up)
+
+// One projection of a launch: its row tiles are the global row tiles [row0, next row0).
+struct PersistSeg {
   const uint8_t* packed;
   const uint16_t* lut;
   const uint16_t* bias;
   uint16_t* out;
   long long ldo;
-  int M, N, K, G, gs, n_groups;
+  int row0, n_groups, out_aligned, pad;
+};
+
+struct PersistParams {
+  PersistSeg seg[kPMaxSeg];
+  int nsegs;
+  int M, K, G, gs;
   int NT;            // token tile (multiple of 32, <= 256)
   int m_tiles;       // token tiles per row tile
   int n_tiles;       // row tiles
   int W;             // token columns of a row of tiles (the last tile rounded up to 32)
   uint32_t smem_bytes;
-  int out_aligned;
   int debug;
   long long wait_cycles;   // bound of every in-kernel wait, in SM clock cycles
   // Split mode (a workspace was given and the tile count leaves a partly filled last round):
@@ -437,6 +445,16 @@ __device__ __forceinline__ uint32_t slab_field_addr(const uint32_t (&w)[2 * BITS
     else v = w[m] << (8 - sh);
     return (v & kMask) | base;
   }
+}
+
+// The projection that owns global row tile `row` (static indexing of the parameter block: a
+// chain of selects, no local copy).
+__device__ __forceinline__ PersistSeg segment_of_row(const PersistParams& p, int row) {
+  PersistSeg sd = p.seg[0];
+#pragma unroll
+  for (int i = 1; i < kPMaxSeg; ++i)
+    if (i < p.nsegs && row >= p.seg[i].row0) sd = p.seg[i];
+  return sd;
 }
 
 // First tile of block b when the tile list is cut into gridDim.x ranges of equal cost
@@ -541,12 +559,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
     // this warp's k-blocks are the iterations grp, grp + 2, ... of the block's flat sequence of
     // k-blocks (segment after segment; every segment has at least two k-blocks, so both groups
     // work in every segment); `load` runs kRing of them ahead of `use`
-    struct Cursor { int s, c, c1, row; };
+    struct Cursor { int s, c, c1, row; const uint8_t* base; };
     auto enter = [&](Cursor& cu, int over) {
       if (cu.s < nseg) {
         cu.c = seg_c0(cu.s) + over;
         cu.c1 = seg_c1(cu.s);
         cu.row = seg_tile(cu.s) / p.m_tiles;
+        const PersistSeg sd = segment_of_row(p, cu.row);
+        cu.base = sd.packed + size_t(cu.row - sd.row0) * G * (1024 * BITS);
       }
     };
     auto advance = [&](Cursor& cu) {
@@ -558,9 +578,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
       }
     };
     auto code_ptr = [&](const Cursor& cu) -> const uint8_t* {
-      return p.packed + (size_t(cu.row) * G + cu.c) * (1024 * BITS) + lane * 32;
+      return cu.base + size_t(cu.c) * (1024 * BITS) + lane * 32;
     };
-    Cursor ld = {0, 0, 0, 0}, use = {0, 0, 0, 0};
+    Cursor ld = {0, 0, 0, 0, p.seg[0].packed}, use = {0, 0, 0, 0, p.seg[0].packed};
     enter(ld, grp - 2);
     advance(ld);
     enter(use, grp - 2);
@@ -571,7 +591,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
 #pragma unroll
       for (int i = 0; i < 2 * BITS; ++i) w[u][i] = 0u;
       const bool on = ld.s < nseg;
-      load_slab_pair<BITS>(w[u], on ? code_ptr(ld) : p.packed, q, on ? 1u : 0u);
+      load_slab_pair<BITS>(w[u], on ? code_ptr(ld) : p.seg[0].packed, q, on ? 1u : 0u);
       if (on) advance(ld);
     }
     int table_row = -1, table_seg = -1;
@@ -587,7 +607,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
             if (row != table_row) {
               PT_BEGIN
               asm volatile("bar.sync 1, %0;" ::"r"(kLookupWarps * 32) : "memory");
-              build_tables(tbl_ptr, p.lut, BITS, p.n_groups, row * kTileRows, p.gs, nl, kLookupWarps * 32);
+              const PersistSeg sd = segment_of_row(p, row);
+              build_tables(tbl_ptr, sd.lut, BITS, sd.n_groups, (row - sd.row0) * kTileRows, p.gs, nl,
+                           kLookupWarps * 32);
               asm volatile("bar.sync 1, %0;" ::"r"(kLookupWarps * 32) : "memory");
               uint32_t token;
               asm volatile("mov.u32 %0, 0;" : "=r"(token));
@@ -625,7 +647,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
           }
           {
             const bool on = ld.s < nseg;
-            load_slab_pair<BITS>(w[u], on ? code_ptr(ld) : p.packed, q, on ? 1u : 0u);
+            load_slab_pair<BITS>(w[u], on ? code_ptr(ld) : p.seg[0].packed, q, on ? 1u : 0u);
             if (on) advance(ld);
           }
           PT_END(2)
@@ -712,12 +734,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
     for (int t = 0; t < nseg; ++t) {
       const int tile = seg_tile(t);
       const bool cut = has_cut && t == 0;
-      const int n0 = (tile / p.m_tiles) * kTileRows, m0 = (tile % p.m_tiles) * p.NT;
+      const PersistSeg sd = segment_of_row(p, tile / p.m_tiles);
+      const int n0 = (tile / p.m_tiles - sd.row0) * kTileRows, m0 = (tile % p.m_tiles) * p.NT;
       int nt = p.M - m0;
       nt = nt >= p.NT ? p.NT : ((nt + 31) & ~31);
       const int half = nt >> 1, col0 = h * half;
       const int n = n0 + 32 * q + lane;
-      const float b0 = p.bias ? DType<T>::to_float(p.bias[n]) : 0.f;
+      const float b0 = sd.bias ? DType<T>::to_float(sd.bias[n]) : 0.f;
       PT_BEGIN
       tc::mbar_wait(bar_dfull, uint32_t(t) & 1u, abort_flag, &g_gemm_status, tc::kStatusWaitDone, p.wait_cycles);
       PT_END(0)
@@ -753,19 +776,19 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
             for (int j = 0; j < 16; ++j) {
               const float v = __uint_as_float(r[ch][j]) + b0;
               const int tok = s0 + 16 * ch + j;
-              if (p.out_aligned) stg[(16 * ch + j) * kTileRows + 32 * q + lane] = DType<T>::from_float(v);
+              if (sd.out_aligned) stg[(16 * ch + j) * kTileRows + 32 * q + lane] = DType<T>::from_float(v);
               else if (m0 + col0 + tok < p.M)
-                p.out[size_t(m0 + col0 + tok) * p.ldo + n] = DType<T>::from_float(v);
+                sd.out[size_t(m0 + col0 + tok) * sd.ldo + n] = DType<T>::from_float(v);
             }
           }
         }
-        if (p.out_aligned) {
+        if (sd.out_aligned) {
           asm volatile("bar.sync %0, 128;" ::"r"(2 + h) : "memory");
           const uint4* src = reinterpret_cast<const uint4*>(stg);
           for (int idx = et; idx < sn * 16; idx += 128) {
             const int r_ = col0 + s0 + (idx >> 4), c = idx & 15;
             if (m0 + r_ < p.M)
-              *reinterpret_cast<uint4*>(p.out + size_t(m0 + r_) * p.ldo + n0 + 8 * c) = src[idx];
+              *reinterpret_cast<uint4*>(sd.out + size_t(m0 + r_) * sd.ldo + n0 + 8 * c) = src[idx];
           }
           asm volatile("bar.sync %0, 128;" ::"r"(2 + h) : "memory");   // the slice is reused
         }
@@ -809,8 +832,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
             for (int ci = 0; ci < 8; ++ci)
               if (ci < p.split) { a0 += v[ci][0]; a1 += v[ci][1]; }
             const int tok = m0 + 2 * g2;
-            if (tok < p.M) p.out[size_t(tok) * p.ldo + n] = DType<T>::from_float(a0 + b0);
-            if (tok + 1 < p.M) p.out[size_t(tok + 1) * p.ldo + n] = DType<T>::from_float(a1 + b0);
+            if (tok < p.M) sd.out[size_t(tok) * sd.ldo + n] = DType<T>::from_float(a0 + b0);
+            if (tok + 1 < p.M) sd.out[size_t(tok + 1) * sd.ldo + n] = DType<T>::from_float(a1 + b0);
           }
         }
         asm volatile("bar.sync 4, %0;" ::"r"(kPEpiWarps * 32) : "memory");
@@ -973,6 +996,95 @@ extern "C" int b200lut_device_status(void) {
   return v != 0 ? v : (e != 0 ? e : g);
 }
 
+namespace {
+// Host side of the persistent kernel: `nseg` projections that share x (one code stream each,
+// the same code width and group size, at most two palettes per 128-row tile) as one launch
+// whose row tiles are the concatenation of the projections' row tiles.
+int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b200lut_segment* segs,
+                    int nseg, bool pdl, int debug, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+  PersistParams pp = {};
+  int rows = 0;
+  for (int i = 0; i < nseg; ++i) {
+    const b200lut_segment& s = segs[i];
+    PersistSeg& d = pp.seg[i];
+    d.packed = static_cast<const uint8_t*>(s.packed);
+    d.lut = static_cast<const uint16_t*>(s.lut);
+    d.bias = static_cast<const uint16_t*>(s.bias);
+    d.out = static_cast<uint16_t*>(s.out);
+    d.ldo = s.ldo;
+    d.out_aligned = (aligned16(s.out) && s.ldo % 8 == 0) ? 1 : 0;
+    d.row0 = rows;
+    d.n_groups = s.n_groups;
+    rows += s.N / kTileRows;
+  }
+  pp.nsegs = nseg;
+  const b200lut_segment& s = segs[0];
+  pp.M = M; pp.K = K; pp.G = K / kChunkK;
+  pp.gs = s.group_size;
+  pp.NT = M >= kPMaxNT ? kPMaxNT : ((M + 31) / 32) * 32;
+  pp.m_tiles = (M + pp.NT - 1) / pp.NT;
+  pp.n_tiles = rows;
+  pp.W = (pp.m_tiles - 1) * pp.NT + ((M - (pp.m_tiles - 1) * pp.NT + 31) / 32) * 32;
+  pp.smem_bytes = uint32_t(kMaxDynSmem);
+  pp.debug = debug;
+  // Waits inside the kernel give up after ~10 ms. A profiler that replays the kernel with
+  // heavy instrumentation can stretch a healthy wait beyond that; B200LUT_WAIT_MS raises the
+  // bound for such runs (capped at one second).
+  pp.wait_cycles = tc::kWaitCycles;
+  if (const char* e = getenv("B200LUT_WAIT_MS")) {
+    long ms = atol(e);
+    if (ms < 1) ms = 1;
+    if (ms > 1000) ms = 1000;
+    pp.wait_cycles = (long long)ms * 2000000ll;
+  }
+  CUtensorMap pmap;
+  if (int rc = encode_x_map(&pmap, x, ldx, M, K, dtype, pp.NT)) return rc;
+  int sms = 148;
+  {
+    int dev = 0;
+    B200LUT_CUDA_OK(cudaGetDevice(&dev));
+    B200LUT_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const long long tiles = (long long)pp.n_tiles * pp.m_tiles;
+  int grid = int(tiles < sms ? tiles : sms);
+  const SplitPlan sp = plan_split(tiles, pp.G, sms);
+  if (sp.split && workspace && workspace_bytes >= sp.bytes && aligned16(workspace) && !(debug & 32)) {
+    pp.split = sp.split; pp.full = sp.full; pp.left = sp.left;
+    pp.tickets = static_cast<int*>(workspace);
+    pp.ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kTicketBytes);
+    grid = sms;
+  }
+#define B200LUT_PERSIST(B)                                                                      \
+  (dtype == B200LUT_BF16                                                                          \
+       ? launch_persistent<__nv_bfloat16, B>(pmap, pp, grid, pdl, cudaStream_t(stream))          \
+       : launch_persistent<__half, B>(pmap, pp, grid, pdl, cudaStream_t(stream)))
+  switch (s.bits) {
+    case 4: return B200LUT_PERSIST(4);
+    case 3: return B200LUT_PERSIST(3);
+    case 2: return B200LUT_PERSIST(2);
+    default: return B200LUT_PERSIST(1);
+  }
+#undef B200LUT_PERSIST
+}
+
+// the checks every projection of a prefill GEMM passes, whichever kernel serves it
+int check_gemm_segment(const b200lut_segment& s) {
+  B200LUT_REQUIRE(s.packed && s.lut && s.out, B200LUT_ERR_INVALID, "null codes, palette or output");
+  B200LUT_REQUIRE(s.N > 0 && s.N % kTileRows == 0 && s.ldo >= s.N, B200LUT_ERR_INVALID,
+                  "N must be a positive multiple of 128 and ldo >= N (N=%d)", s.N);
+  B200LUT_REQUIRE(s.res_rank == 0, B200LUT_ERR_UNSUPPORTED,
+                  "the prefill GEMM does not fuse the low-rank residual (two dense GEMMs do it)");
+  B200LUT_REQUIRE(s.group_size >= 32 && s.n_groups >= 1 &&
+                      ((s.group_size < 128 && (s.group_size & (s.group_size - 1)) == 0) ||
+                       s.group_size % 128 == 0),
+                  B200LUT_ERR_UNSUPPORTED, "group_size %d not served (32, 64 or a multiple of 128)",
+                  s.group_size);
+  return B200LUT_OK;
+}
+
+}  // namespace
+
 extern "C" size_t b200lut_gemm_workspace_bytes(int M, int N, int K) {
   if (M < 1 || N < kTileRows || K < 2 * kChunkK) return 0;
   const int nt = M >= kPMaxNT ? kPMaxNT : ((M + 31) / 32) * 32;
@@ -986,6 +1098,37 @@ extern "C" size_t b200lut_gemm_workspace_bytes(int M, int N, int K) {
 extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
                             const b200lut_segment* seg, int epilogue, int flags, void* stream) {
   return b200lut_gemm_ws(x, ldx, M, K, dtype, seg, epilogue, flags, nullptr, 0, stream);
+}
+
+extern "C" int b200lut_gemm_multi(const void* x, int64_t ldx, int M, int K, int dtype,
+                                  const b200lut_segment* segs, int nseg, int flags,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+  B200LUT_REQUIRE(x && segs, B200LUT_ERR_INVALID, "null x or segment table");
+  B200LUT_REQUIRE(nseg >= 1 && nseg <= kPMaxSeg, B200LUT_ERR_UNSUPPORTED,
+                  "1 <= nseg <= %d projections per launch, got %d", kPMaxSeg, nseg);
+  B200LUT_REQUIRE(M >= 1, B200LUT_ERR_INVALID, "M must be >= 1, got %d", M);
+  B200LUT_REQUIRE(K >= 2 * kChunkK && K % kChunkK == 0, B200LUT_ERR_INVALID,
+                  "K must be a multiple of 64 and at least 128, got %d", K);
+  B200LUT_REQUIRE(dtype == B200LUT_BF16 || dtype == B200LUT_F16, B200LUT_ERR_INVALID,
+                  "dtype must be B200LUT_BF16 or B200LUT_F16");
+  B200LUT_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K, B200LUT_ERR_ALIGN,
+                  "x must be 16-byte aligned with a row stride that is a multiple of 8 and >= K");
+  for (int i = 0; i < nseg; ++i) {
+    const b200lut_segment& s = segs[i];
+    if (int rc = check_gemm_segment(s)) return rc;
+    B200LUT_REQUIRE(!s.packed2, B200LUT_ERR_UNSUPPORTED,
+                    "a merged prefill launch serves one code stream per projection");
+    B200LUT_REQUIRE(s.bits >= 1 && s.bits <= 4 && s.bits == segs[0].bits &&
+                        s.group_size == segs[0].group_size && s.group_size >= 64,
+                    B200LUT_ERR_UNSUPPORTED,
+                    "the projections of a merged prefill launch share one code width (1..4) and "
+                    "one group size >= 64 (segment %d: %d bits, group %d)", i, s.bits, s.group_size);
+    B200LUT_REQUIRE(aligned16(s.packed), B200LUT_ERR_ALIGN, "code buffers must be 16-byte aligned");
+  }
+  int debug = 0;
+  { const char* e = getenv("B200LUT_GEMM_DEBUG"); debug = e ? atoi(e) : 0; }
+  return persistent_gemm(x, ldx, M, K, dtype, segs, nseg, (flags & 1) != 0, debug, workspace,
+                         workspace_bytes, stream);
 }
 
 extern "C" int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dtype,
@@ -1002,22 +1145,13 @@ extern "C" int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dty
   B200LUT_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K, B200LUT_ERR_ALIGN,
                   "x must be 16-byte aligned with a row stride that is a multiple of 8 and >= K");
   const b200lut_segment& s = *seg;
-  B200LUT_REQUIRE(s.packed && s.lut && s.out, B200LUT_ERR_INVALID, "null codes, palette or output");
-  B200LUT_REQUIRE(s.N > 0 && s.N % kTileRows == 0 && s.ldo >= s.N, B200LUT_ERR_INVALID,
-                  "N must be a positive multiple of 128 and ldo >= N (N=%d)", s.N);
-  B200LUT_REQUIRE(s.res_rank == 0, B200LUT_ERR_UNSUPPORTED,
-                  "the prefill GEMM does not fuse the low-rank residual (two dense GEMMs do it)");
+  if (int rc = check_gemm_segment(s)) return rc;
   const bool silu = epilogue == B200LUT_EPI_SILU_MUL;
   const bool two = s.packed2 != nullptr;
   B200LUT_REQUIRE(!silu || two, B200LUT_ERR_INVALID,
                   "the silu-mul epilogue needs the up projection in packed2 / lut2");
   B200LUT_REQUIRE(s.bits >= 1 && s.bits <= 4 && (!two || (s.lut2 && s.bits2 >= 1 && s.bits2 <= 4)),
                   B200LUT_ERR_INVALID, "code widths must be 1..4 (got %d / %d)", s.bits, s.bits2);
-  B200LUT_REQUIRE(s.group_size >= 32 && s.n_groups >= 1 &&
-                      ((s.group_size < 128 && (s.group_size & (s.group_size - 1)) == 0) ||
-                       s.group_size % 128 == 0),
-                  B200LUT_ERR_UNSUPPORTED, "group_size %d not served (32, 64 or a multiple of 128)",
-                  s.group_size);
   B200LUT_REQUIRE(aligned16(s.packed) && (!two || aligned16(s.packed2)), B200LUT_ERR_ALIGN,
                   "code buffers must be 16-byte aligned");
 
@@ -1026,60 +1160,7 @@ extern "C" int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dty
   { const char* e = getenv("B200LUT_GEMM_DEBUG"); debug = e ? atoi(e) : 0; }
   const int nl = s.group_size >= 128 ? 1 : 128 / s.group_size;
   if (!two && nl <= 2 && K / kChunkK >= 2 && !(debug & 4)) {
-    // one code stream whose palettes fit one table: the persistent, double-buffered kernel
-    PersistParams pp = {};
-    pp.packed = static_cast<const uint8_t*>(s.packed);
-    pp.lut = static_cast<const uint16_t*>(s.lut);
-    pp.bias = static_cast<const uint16_t*>(s.bias);
-    pp.out = static_cast<uint16_t*>(s.out);
-    pp.ldo = s.ldo;
-    pp.out_aligned = (aligned16(s.out) && s.ldo % 8 == 0) ? 1 : 0;
-    pp.M = M; pp.N = s.N; pp.K = K; pp.G = K / kChunkK;
-    pp.gs = s.group_size; pp.n_groups = s.n_groups;
-    pp.NT = M >= kPMaxNT ? kPMaxNT : ((M + 31) / 32) * 32;
-    pp.m_tiles = (M + pp.NT - 1) / pp.NT;
-    pp.n_tiles = s.N / kTileRows;
-    pp.W = (pp.m_tiles - 1) * pp.NT + ((M - (pp.m_tiles - 1) * pp.NT + 31) / 32) * 32;
-    pp.smem_bytes = uint32_t(kMaxDynSmem);
-    pp.debug = debug;
-    // Waits inside the kernel give up after ~10 ms. A profiler that replays the kernel with
-    // heavy instrumentation can stretch a healthy wait beyond that; B200LUT_WAIT_MS raises the
-    // bound for such runs (capped at one second).
-    pp.wait_cycles = tc::kWaitCycles;
-    if (const char* e = getenv("B200LUT_WAIT_MS")) {
-      long ms = atol(e);
-      if (ms < 1) ms = 1;
-      if (ms > 1000) ms = 1000;
-      pp.wait_cycles = (long long)ms * 2000000ll;
-    }
-    CUtensorMap pmap;
-    if (int rc = encode_x_map(&pmap, x, ldx, M, K, dtype, pp.NT)) return rc;
-    int sms = 148;
-    {
-      int dev = 0;
-      B200LUT_CUDA_OK(cudaGetDevice(&dev));
-      B200LUT_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    }
-    const long long tiles = (long long)pp.n_tiles * pp.m_tiles;
-    int grid = int(tiles < sms ? tiles : sms);
-    const SplitPlan sp = plan_split(tiles, pp.G, sms);
-    if (sp.split && workspace && workspace_bytes >= sp.bytes && aligned16(workspace) && !(debug & 32)) {
-      pp.split = sp.split; pp.full = sp.full; pp.left = sp.left;
-      pp.tickets = static_cast<int*>(workspace);
-      pp.ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kTicketBytes);
-      grid = sms;
-    }
-#define B200LUT_PERSIST(B)                                                                      \
-  (dtype == B200LUT_BF16                                                                          \
-       ? launch_persistent<__nv_bfloat16, B>(pmap, pp, grid, pdl, cudaStream_t(stream))          \
-       : launch_persistent<__half, B>(pmap, pp, grid, pdl, cudaStream_t(stream)))
-    switch (s.bits) {
-      case 4: return B200LUT_PERSIST(4);
-      case 3: return B200LUT_PERSIST(3);
-      case 2: return B200LUT_PERSIST(2);
-      default: return B200LUT_PERSIST(1);
-    }
-#undef B200LUT_PERSIST
+    return persistent_gemm(x, ldx, M, K, dtype, seg, 1, pdl, debug, workspace, workspace_bytes, stream);
   }
 
   // what is left for the one-tile kernel: two code streams, the fused gate/up form, four

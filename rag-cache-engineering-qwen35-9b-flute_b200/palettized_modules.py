@@ -390,6 +390,42 @@ def _mergeable(mods, x: torch.Tensor) -> bool:
     return True
 
 
+def _prefill_mergeable(mods, x: torch.Tensor) -> bool:
+    """Prefill-merge verdict (M > 16): projections that share x run as ONE tensor-core launch
+    when they have one code stream each, one code width, one group size >= 64, one dtype, no
+    low-rank residual, and are unrotated or share one rotation."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.shape[0] <= GEMV_MAX_M or not x.is_cuda or len(mods) > _lib.GEMM_MULTI_MAX:
+        return False
+    if os.environ.get("FLUTE_NO_MERGE", "").strip() in ("1", "true", "True"):
+        return False
+    m0 = mods[0]
+    for m in mods:
+        if not isinstance(m, PalettizedLinear) or m.reference or m.K != m0.K or m.K < 128:
+            return False
+        if m.lut.dtype != m0.lut.dtype or m.lut.dtype not in (torch.float16, torch.bfloat16):
+            return False
+        if m.has_stream2 or m.has_residual() or not _same_rotation(m0, m):
+            return False
+        if m.bitwidth != m0.bitwidth or m.group_size != m0.group_size or m.group_size < 64:
+            return False
+        if m.bias is not None and m.bias.dtype != m.lut.dtype:
+            return False
+    return True
+
+
+def _prefill_merged(mods, x: torch.Tensor, outs) -> None:
+    """One merged prefill launch of `mods` over x into the 2-D buffers `outs` (each [M, >= N]
+    with its own row stride)."""
+    m0 = mods[0]
+    x2 = x.reshape(-1, x.shape[-1])
+    if m0.rot_signs is not None:
+        x2 = m0._rotate_input(x2)
+    x2 = x2.to(m0.lut.dtype).contiguous()
+    descs = [m._segment_desc(o, ldo=o.stride(0)) for m, o in zip(mods, outs)]
+    _lib.gemm_multi(x2, _lib.make_segments(descs), len(descs), flags=_flags())
+
+
 def _same_rotation(a: "PalettizedLinear", b: "PalettizedLinear") -> bool:
     """Both unrotated, or both rotated by the same fold (seed, length, order, AWQ scale): a
     merged launch rotates the shared input row once. (The reference's merged kernels carry a
@@ -434,6 +470,13 @@ class SplitQKV(nn.Module):
 
     def forward(self, x):
         mods = (self.q_proj, self.k_proj, self.v_proj)
+        if _prefill_mergeable(mods, x):      # M > 16: one tensor-core launch for the three
+            total = sum(m.N for m in mods)
+            M = x.numel() // x.shape[-1]
+            out = torch.empty(M, total, dtype=mods[0].lut.dtype, device=x.device)
+            offs = [0, mods[0].N, mods[0].N + mods[1].N]
+            _prefill_merged(mods, x, [out[:, o:] for o in offs])
+            return out.to(x.dtype).reshape(*x.shape[:-1], total)
         if os.environ.get("FLUTE_NO_MERGE", "").strip() in ("1", "true", "True") \
                 or not _mergeable(mods, x):
             return torch.cat([m(x) for m in mods], dim=-1)
@@ -483,6 +526,15 @@ class FusedPalettizedMLP(nn.Module):
         fusable = (self._is_silu() and _mergeable(mods, x) and mods[0].N == mods[1].N
                    and os.environ.get("FLUTE_NO_MERGE", "").strip() not in ("1", "true", "True"))
         if not fusable:
+            if self._is_silu() and mods[0].N == mods[1].N and _prefill_mergeable(mods, x):
+                # prefill: gate and up as one tensor-core launch, one SiLU*mul pass, down
+                M = x.numel() // x.shape[-1]
+                g = torch.empty(M, mods[0].N, dtype=mods[0].lut.dtype, device=x.device)
+                u = torch.empty_like(g)
+                _prefill_merged(mods, x, [g, u])
+                _lib.silu_mul(g, u)
+                y = self.down_proj(g.to(x.dtype))
+                return y.reshape(*x.shape[:-1], self.down_proj.N)
             g, u = self.gate_proj(x), self.up_proj(x)
             if (self._is_silu() and g.is_cuda and g.dtype in (torch.float16, torch.bfloat16)
                     and g.dtype == u.dtype and g.shape[-1] % 8 == 0 and g.is_contiguous()

@@ -22,6 +22,7 @@ into every rank's buffer over NVLink, the down launch waits for the flags).
 """
 from __future__ import annotations
 
+import ctypes
 from typing import List, Optional
 
 import torch
@@ -111,6 +112,7 @@ class LinearStack(nn.Module):
             # with one buffer a peer's next push could overtake this rank's reader
             raise ValueError("gather='push' needs at least two layers")
         self.gather_mode = gather if world > 1 else "nccl"
+        self.merge_prefill = True    # M > 16: projections that share x run as one launch
         self._arenas = arenas        # test form: pre-built emulated arenas (this rank's one)
         self.device, self.dtype = torch.device(device), dtype
         self.bits, self.group_size = bits, group_size
@@ -223,20 +225,32 @@ class LinearStack(nn.Module):
         elif M <= 16:
             _lib.gemv_multi(xin, segs, nseg, epilogue=epi, flags=flags)
         elif epi == _lib.EPI_SILU_MUL:
-            # prefill: gate and up as two full-width tensor-core GEMMs, then one SiLU*mul pass
-            # (measured faster than the fused 128-token form and than folding the multiply
-            # into the second GEMM's epilogue)
+            # prefill: gate and up as full-width tensor-core tiles of ONE launch, then one
+            # SiLU*mul pass (measured faster than the fused 128-token form and than folding the
+            # multiply into the second projection's epilogue)
             descs = entry[5]
             for i in range(0, nseg, 2):
                 act = descs[i]["out"]
                 ubuf = self._scratch(act.shape, act.dtype)
-                up = dict(descs[i + 1], out=ubuf, ldo=ubuf.shape[1])
-                _lib.gemm(xin, _pair(segs, i, _lib.EPI_NONE), flags=flags)
-                _lib.gemm(xin, _lib.make_segments([up]), flags=flags)
+                pair = [dict(descs[i], ldo=act.stride(0)), dict(descs[i + 1], out=ubuf, ldo=ubuf.shape[1])]
+                if self.merge_prefill and _lib.gemm_multi_ok(pair, xin.shape[1]):
+                    _lib.gemm_multi(xin, _lib.make_segments(pair), 2, flags=flags)
+                else:
+                    _lib.gemm(xin, _pair(segs, i, _lib.EPI_NONE), flags=flags)
+                    _lib.gemm(xin, _lib.make_segments([pair[1]]), flags=flags)
                 _lib.silu_mul(act, ubuf)
         else:
-            for i in range(nseg):
-                _lib.gemm(xin, _pair(segs, i, epi), epilogue=epi, flags=flags)
+            descs = entry[5]
+            i = 0
+            while i < nseg:      # merged launches of up to four projections that share x
+                j = min(nseg, i + _lib.GEMM_MULTI_MAX) if self.merge_prefill else i + 1
+                if j - i > 1 and _lib.gemm_multi_ok(descs[i:j], xin.shape[1]):
+                    _lib.gemm_multi(xin, ctypes.cast(ctypes.byref(segs[i]), ctypes.POINTER(_lib.Segment)),
+                                    j - i, flags=flags)
+                else:
+                    j = i + 1
+                    _lib.gemm(xin, _pair(segs, i, epi), epilogue=epi, flags=flags)
+                i = j
 
     def _scratch(self, shape, dtype) -> torch.Tensor:
         buf = self.__dict__.get("_scratch_buf")
@@ -281,11 +295,27 @@ class LinearStack(nn.Module):
         return self._plan(M)["y"]
 
     def launches_per_step(self, M: int) -> int:
+        """Kernel launches of one step (the all-gathers of a multi-GPU step not counted)."""
         n = 0
-        for name, _, _, nseg, epi, _, _ in self._plan(M)["launches"]:
+        for name, xin, _, nseg, epi, descs, _ in self._plan(M)["launches"]:
             if name == "gather":
                 continue
-            n += 1 if M <= 16 else (nseg + nseg // 2 if epi == _lib.EPI_SILU_MUL else nseg)
+            if M <= 16:
+                n += 1
+                continue
+            K = xin.shape[1]
+            if epi == _lib.EPI_SILU_MUL:     # per pair: merged (1) or separate (2) GEMMs + SiLU*mul
+                for i in range(0, nseg, 2):
+                    merged = self.merge_prefill and _lib.gemm_multi_ok(descs[i:i + 2], K)
+                    n += (1 if merged else 2) + 1
+            else:
+                i = 0
+                while i < nseg:
+                    j = min(nseg, i + _lib.GEMM_MULTI_MAX) if self.merge_prefill else i + 1
+                    if not (j - i > 1 and _lib.gemm_multi_ok(descs[i:j], K)):
+                        j = i + 1
+                    n += 1
+                    i = j
         return n
 
 

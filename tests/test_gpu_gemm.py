@@ -211,3 +211,66 @@ def test_stack_prefill_step_matches_module_forwards():
     mlp = stack.layers[0].mlp
     want = mlp.down_proj(torch.nn.functional.silu(mlp.gate_proj(x).float()).to(torch.bfloat16) * mlp.up_proj(x))
     assert rel_err(y, want) <= TOL
+
+
+@pytest.mark.parametrize("M,Ns,K,gs,bits,dtype,bias", (
+    (64, (256, 128, 512), 512, 128, 4, torch.bfloat16, True),       # Q/K/V-like, 7 row tiles
+    (300, (1024, 1024), 1024, 64, 4, torch.float16, False),         # gate/up-like, token tail
+    (40, (128, 128, 128, 256), 256, 128, 3, torch.bfloat16, True),  # four projections, 3-bit
+    (2048, (2048, 512), 512, 128, 4, torch.bfloat16, False),        # 160 tiles: one round + cut tiles
+    (17, (128, 384), 128, 128, 2, torch.float16, True),
+))
+def test_merged_prefill_launch_equals_the_separate_launches(M, Ns, K, gs, bits, dtype, bias):
+    cases = [Case(N, K, gs, bits, dtype, seed=100 * i + N + M, bias=bias) for i, N in enumerate(Ns)]
+    mods = [c.module() for c in cases]
+    x = cases[0].x(M)
+    xd = x.cuda()
+    sep = [m(xd) for m in mods]
+    total = sum(Ns)
+    out = torch.full((M, total + 8), 5.0, dtype=dtype, device="cuda")
+    descs, off = [], 0
+    for m in mods:
+        descs.append(m._segment_desc(out[:, off:], ldo=total + 8))
+        off += m.N
+    assert L.gemm_multi_ok(descs, K)
+    for split in (True, False):
+        out[:, :total] = 0
+        L.gemm_multi(xd, L.make_segments(descs), len(descs), split=split)
+        off = 0
+        for c, m, y in zip(cases, mods, sep):
+            got = out[:, off:off + m.N]
+            assert rel_err(got, y) <= 2.0 ** -7, (split, off)       # same products, other split of K
+            assert rel_err(got, c.oracle(x)) <= TOL
+            off += m.N
+        assert (out[:, total:] == 5.0).all()
+
+
+def test_merged_prefill_launch_refuses_mixed_projections():
+    a = Case(128, 128, 128, 4, torch.bfloat16, seed=1)
+    b = Case(128, 128, 128, 3, torch.bfloat16, seed=2)
+    ma, mb = a.module(), b.module()
+    x = a.x(32).cuda()
+    out = torch.empty(32, 256, dtype=torch.bfloat16, device="cuda")
+    descs = [ma._segment_desc(out, ldo=256), mb._segment_desc(out[:, 128:], ldo=256)]
+    assert not L.gemm_multi_ok(descs, 128)
+    with pytest.raises(RuntimeError, match="share one code width"):
+        L.gemm_multi(x, L.make_segments(descs), 2)
+    with pytest.raises(RuntimeError, match="nseg"):
+        L.gemm_multi(x, L.make_segments(descs * 3), 6)
+
+
+def test_split_qkv_and_mlp_take_the_merged_prefill_route():
+    K, M = 256, 48
+    q, k, v = (Case(N, K, 128, 4, torch.bfloat16, seed=N, bias=True) for N in (256, 128, 384))
+    qkv = pkg.SplitQKV(q.module(), k.module(), v.module())
+    x = q.x(M)
+    assert pkg.palettized_modules._prefill_mergeable((qkv.q_proj, qkv.k_proj, qkv.v_proj), x.cuda())
+    got = qkv(x.cuda().view(2, 24, K))
+    want = torch.cat([c.oracle(x) for c in (q, k, v)], dim=-1)
+    assert got.shape == (2, 24, 768) and rel_err(got.reshape(M, -1), want) <= TOL
+    g, u, d = (Case(512, K, 128, 4, torch.bfloat16, seed=7), Case(512, K, 128, 4, torch.bfloat16, seed=8),
+               Case(K, 512, 128, 4, torch.bfloat16, seed=9))
+    mlp = pkg.FusedPalettizedMLP(g.module(), u.module(), d.module(), torch.nn.SiLU())
+    y = mlp(x.cuda())
+    h = (torch.nn.functional.silu(g.oracle(x).float()) * u.oracle(x).float()).to(torch.bfloat16)
+    assert rel_err(y, d.oracle(h)) <= 2 * TOL

@@ -81,6 +81,10 @@ def test_validation_errors_carry_a_message():
     assert rc == 2 and b"M=17" in L.b200lut_last_error()
     rc = L.b200lut_residual_project(x, 64, 1, 64, 0, None, 8, x, 8, 0, None)
     assert rc == 1 and b"null" in L.b200lut_last_error()
+    rc = L.b200lut_gemm_multi(x, 64, 32, 128, 0, ctypes.byref(seg), 5, 0, None, 0, None)
+    assert rc == 2 and b"nseg" in L.b200lut_last_error()
+    rc = L.b200lut_gemm_multi(x, 64, 32, 64, 0, ctypes.byref(seg), 1, 0, None, 0, None)
+    assert rc == 1 and b"at least 128" in L.b200lut_last_error()
     rc = L.b200lut_embed_gather(x, 4, 60, 0, ctypes.byref(seg), None, 0, None)
     assert rc == 1 and b"K %% 64" in L.b200lut_last_error() or b"64" in L.b200lut_last_error()
     rc = L.b200lut_embed_gather(x, -1, 64, 0, ctypes.byref(seg), None, 0, None)
