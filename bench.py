@@ -349,7 +349,7 @@ def embedding_gather_gbs(pkg, N: int, K: int, n_ids: int, iters: int):
 def run_case(args) -> int:
     """A few eager launches of one kernel on a profiling-sized case. gemv: 12288 x 4096
     4-bit projection at M = 1 over 8 distinct weight sets (192 MB of codes, larger than L2);
-    gemm: M = 2048, K = 4096, N = 12288."""
+    gemm: M = 2048, K = 4096, N = 12288; embed: 2048 rows of an lm_head-sized table."""
     import torch
     torch.cuda.set_device(0)
     pkg = importlib.import_module(PKG)
@@ -358,6 +358,10 @@ def run_case(args) -> int:
         gbs, us = single_projection_gbs(pkg, args.batch, 12288, 4096, 8, max(args.steps, 1), 0)
         print(json.dumps({"case": "gemv 12288x4096 M=%d, 8 weight sets" % args.batch, "GB/s": gbs,
                           "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}))
+    elif args.case == "embed":
+        gbs, us = embedding_gather_gbs(pkg, 248320, 4096, 2048, max(args.steps, 1))
+        print(json.dumps({"case": "embedding gather, 2048 rows of a 248320 x 4096 4-bit table",
+                          "GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}))
     else:
         tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, max(args.steps, 1), False)
         print(json.dumps({"case": "gemm M=2048 K=4096 N=12288", "TFLOP/s": tf, "us": us,
@@ -380,7 +384,7 @@ def main() -> int:
                     help="N > 1: how the sharded MLP activation is recombined (push: peer stores "
                          "from the GEMV epilogue; nccl: an all-gather call between the launches)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
-    ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemm"),
+    ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemm", "embed"),
                     help="stack: the benchmark; gemv / gemm: a few launches of one kernel on a "
                          "small case (the workloads the ncu captures in profiles/ use)")
     ap.add_argument("--executor", default="graph", choices=("plan", "graph"),
