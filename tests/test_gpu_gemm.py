@@ -274,3 +274,24 @@ def test_split_qkv_and_mlp_take_the_merged_prefill_route():
     y = mlp(x.cuda())
     h = (torch.nn.functional.silu(g.oracle(x).float()) * u.oracle(x).float()).to(torch.bfloat16)
     assert rel_err(y, d.oracle(h)) <= 2 * TOL
+
+
+@pytest.mark.parametrize("bits", (1, 2, 3, 4))
+def test_shapes_and_seeds_of_the_reference_gpu_gate(bits):
+    # the reference's standalone GPU gate (src/flute_extended/test_flute.py:133-223): M = 256,
+    # K = 512, N = 256, group 32, fp16, A ~ N(0,1), palette ~ N(0,1), codes uniform, seeds 42 and
+    # 43 + b; its own kernels are compared bit for bit with each other there — here the result
+    # is compared with the oracle (max rel err <= 1e-2, cosine >= 0.999)
+    M, K, N, gs = 256, 512, 256, 32
+    torch.manual_seed(42 if bits == 4 else 43 + bits)
+    A = torch.randn(M, K).half()
+    codes = torch.randint(0, 1 << bits, (N, K), dtype=torch.uint8).numpy()
+    lut = torch.randn(N // gs, 1 << bits).half()
+    mod = pkg.PalettizedLinear(torch.from_numpy(orc.pack_idxn(codes, bits)), lut, bits, gs, N, K).cuda()
+    got = mod(A.cuda()).cpu()
+    want = orc.linear_forward(A, orc.dequant_indices(codes, lut, gs, bits))
+    assert rel_err(got, want) <= TOL
+    assert orc.cosine(got.float(), want.float()) >= 0.999
+    # the dequantised weights themselves, bit for bit, through the same module
+    W = mod(torch.eye(K, dtype=torch.float16, device="cuda")).cpu().t()
+    assert torch.equal(W.float(), orc.dequant_indices(codes, lut, gs, bits).float())
