@@ -323,6 +323,38 @@ def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool):
     return 2.0 * M * N * K / us / 1e6, us
 
 
+def kgrouped_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int):
+    """Extra: the K-grouped palette variant of one projection (one 16-entry palette per 128
+    input columns and output row: N*K/4 bytes of palettes beside N*K/2 of codes), launched
+    back to back over `sets` distinct weight sets; returns (GB/s, us per launch)."""
+    import torch
+    L = pkg._lib
+    bits, dt = 4, torch.bfloat16
+    x = torch.randn(M, K, device="cuda").to(dt)
+    out = torch.empty(M, N, dtype=dt, device="cuda")
+    keep = []
+    for i in range(sets):
+        packed = L.repack_from_idxn(pkg.synthetic.random_blob_on_device(N, K, bits, 950 + i, "cuda"), N, K, bits)
+        lut_k = (0.02 * torch.randn(K // 128, N, 16, device="cuda",
+                                    generator=torch.Generator("cuda").manual_seed(950 + i))).sort(dim=-1).values.to(dt)
+        keep.append((packed, lut_k))
+
+    def run():
+        for packed, lut_k in keep:
+            L.gemv_kgrouped(x, packed, lut_k, N, bits, out=out)
+    run()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run()
+    for _ in range(3):
+        g.replay()
+    ms = time_steps(g.replay, iters, 1)
+    us = ms * 1e3 / (iters * sets)
+    byts = N * K * bits // 8 + (K // 128) * N * 16 * 2 + M * K * 2 + M * N * 2
+    return byts / us / 1e3, us
+
+
 def embedding_gather_gbs(pkg, N: int, K: int, n_ids: int, iters: int):
     """Extra: the embedding gather over an lm_head-sized 4-bit table (0.51 GB of codes, far
     beyond L2), `n_ids` random rows per launch; returns (GB/s of algorithmic bytes, us).
@@ -545,6 +577,10 @@ def main() -> int:
             gbs, us = single_projection_gbs(pkg, 1, 248320, 4096, 1, 10, flags)
             extras["gemv_248320x4096_m1_lm_head"] = {"GB/s": gbs, "us_per_launch": us,
                                                      "frac_of_hbm": gbs / peaks["hbm_gbs"]}
+            gbs, us = kgrouped_projection_gbs(pkg, 1, 4096, 4096, 16, 20)
+            extras["gemv_kgrouped_4096x4096_m1"] = {"GB/s": gbs, "us_per_launch": us,
+                                                    "frac_of_hbm": gbs / peaks["hbm_gbs"],
+                                                    "bytes_per_launch": 12599296}
             gbs, us = embedding_gather_gbs(pkg, 248320, 4096, 2048, 20)
             extras["embedding_gather_248320x4096_2048_ids"] = {
                 "GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}

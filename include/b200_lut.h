@@ -306,6 +306,24 @@ int b200lut_gemm_multi(const void* x, int64_t ldx, int M, int K, int dtype,
                        const b200lut_segment* segs, int nseg, int flags,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- K-grouped palettes ---------------------------------------------------------------------
+ *
+ * out[m, n] = sum_k x[m, k] * lut_k[k / 128][n][code(n, k)] (+ bias[n]), M <= 16: one
+ * 2^bits-entry palette per (block of 128 input columns, output row); lut_k is
+ * [K / 128][N][2^bits] in dtype, the codes are in the slab layout. fp32 sums, one rounding.
+ * The reference groups palettes along the output rows and has no kernel of this form; its
+ * reference route expresses it as K / 128 modules of 128 columns with group_size = 1
+ * (src/scripts/palettized_modules.py:125-162), summed in fp32. split = 0 lets the library pick
+ * the number of K ranges (b200lut_gemv_kgrouped_split); with split > 1 the caller passes a
+ * zero-initialised workspace of b200lut_gemv_kgrouped_workspace_bytes(N, M, split) bytes
+ * (fp32 partial sums folded in range order by the last block; the tickets reset themselves). */
+int b200lut_gemv_kgrouped_split(int N, int K);
+size_t b200lut_gemv_kgrouped_workspace_bytes(int N, int M, int split);
+int b200lut_gemv_kgrouped(const void* x, int64_t ldx, int M, int K, int dtype,
+                          const void* packed, const void* lut_k, const void* bias,
+                          int N, int bits, void* out, int64_t ldo, int split,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- embedding gather ----------------------------------------------------------------------
  *
  * out[t, :] = W[ids[t], :] for n_ids int64 ids on the device, W the palettized [N, K] table

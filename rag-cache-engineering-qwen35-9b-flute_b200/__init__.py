@@ -6,7 +6,8 @@ behind a C ABI, see include/b200_lut.h). Import of this package does not load
 the library; the first compute call does, and fails loudly if it is not built.
 """
 from . import _lib, fht, idxN, synthetic                                    # noqa: F401
-from .palettized_modules import (FusedPalettizedMLP, PalettizedEmbedding, PalettizedLinear,  # noqa: F401
+from .palettized_modules import (FusedPalettizedMLP, KGroupedPalettizedLinear,  # noqa: F401
+                                 PalettizedEmbedding, PalettizedLinear,
                                  SplitQKV,
                                  reference_dequant, set_programmatic_launch)
 from .artifacts import (load_metadata, load_palettized_embedding, load_palettized_weight,  # noqa: F401
@@ -16,5 +17,5 @@ from .loader import load_quant_model                                            
 
 __all__ = ["load_quant_model", "load_palettized_weight", "replace_linear_with_palettized",
            "load_palettized_embedding", "load_tied_pair", "export_luts", "import_luts",
-           "iter_palettized_linears", "load_metadata", "PalettizedLinear", "PalettizedEmbedding", "SplitQKV", "FusedPalettizedMLP", "reference_dequant",
+           "iter_palettized_linears", "load_metadata", "PalettizedLinear", "PalettizedEmbedding", "KGroupedPalettizedLinear", "SplitQKV", "FusedPalettizedMLP", "reference_dequant",
            "set_programmatic_launch", "fht", "idxN", "synthetic"]

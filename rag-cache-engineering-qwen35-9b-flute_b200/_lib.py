@@ -28,7 +28,8 @@ EXPORTS = (
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
     "b200lut_residual_project", "b200lut_silu_mul", "b200lut_gemm_workspace_bytes", "b200lut_gemm_ws", "b200lut_gemm_multi",
-    "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
+    "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_kgrouped",
+    "b200lut_gemv_kgrouped_split", "b200lut_gemv_kgrouped_workspace_bytes", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
     "b200lut_gemv_noalloc", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
@@ -116,6 +117,12 @@ def lib() -> ctypes.CDLL:
     L.b200lut_gemm_ws.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32, vp, sz, vp]
     L.b200lut_gemm_multi.restype = i32
     L.b200lut_gemm_multi.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32, vp, sz, vp]
+    L.b200lut_gemv_kgrouped_split.restype = i32
+    L.b200lut_gemv_kgrouped_split.argtypes = [i32, i32]
+    L.b200lut_gemv_kgrouped_workspace_bytes.restype = sz
+    L.b200lut_gemv_kgrouped_workspace_bytes.argtypes = [i32, i32, i32]
+    L.b200lut_gemv_kgrouped.restype = i32
+    L.b200lut_gemv_kgrouped.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, i32, i32, vp, i64, i32, vp, sz, vp]
     L.b200lut_embed_gather.restype = i32
     L.b200lut_embed_gather.argtypes = [vp, i64, i32, i32, ctypes.POINTER(Segment), vp, i32, vp]
     L.b200lut_round_rows.restype = i32
@@ -405,6 +412,36 @@ def gemm(x: torch.Tensor, seg, epilogue: int = EPI_NONE, flags: int = 0, split: 
         else:
             check(lib().b200lut_gemm(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), seg,
                                      epilogue, flags, _stream(x)))
+
+
+_kg_scratch = {}
+
+
+def gemv_kgrouped(x: torch.Tensor, packed: torch.Tensor, lut_k: torch.Tensor, N: int, bits: int,
+                  bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                  split: int = 0) -> torch.Tensor:
+    """Decode GEMV with K-grouped palettes: x [M <= 16, K], codes in the slab layout,
+    lut_k [K / 128, N, 2**bits] in x's dtype -> [M, N]."""
+    _need_cuda(x, "x")
+    M, K = x.shape
+    if out is None:
+        out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        if split <= 0:
+            split = lib().b200lut_gemv_kgrouped_split(N, K)
+        need = lib().b200lut_gemv_kgrouped_workspace_bytes(N, M, split)
+        ws = None
+        if need:
+            key = (x.device, int(_stream(x) or 0))
+            ws = _kg_scratch.get(key)
+            if ws is None or ws.numel() < need:
+                ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=x.device)
+                _kg_scratch[key] = ws
+        check(lib().b200lut_gemv_kgrouped(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype),
+                                          packed.data_ptr(), lut_k.data_ptr(), ptr(bias), N, bits,
+                                          out.data_ptr(), out.stride(0), split, ptr(ws),
+                                          ws.numel() if ws is not None else 0, _stream(x)))
+    return out
 
 
 GEMM_MULTI_MAX = 4

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libb200lut.so")
-SOURCES = ("api.cu", "layout.cu", "gemv.cu", "fht.cu", "gemm_tc.cu", "peer.cu", "residual.cu", "elementwise.cu", "embed.cu")
+SOURCES = ("api.cu", "layout.cu", "gemv.cu", "fht.cu", "gemm_tc.cu", "peer.cu", "residual.cu", "elementwise.cu", "embed.cu", "gemv_kgrouped.cu")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

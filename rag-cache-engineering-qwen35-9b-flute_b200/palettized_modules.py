@@ -747,3 +747,66 @@ class PalettizedEmbedding(nn.Module):
                 w = _lib.fht(w, self._signs_on(w.device), _lib.FHT_ADJOINT, out=w)
             out = _lib.round_rows(w, dtype)
         return out.view(*ids.shape, self.K)
+
+
+class KGroupedPalettizedLinear(nn.Module):
+    """Linear layer whose palettes are grouped along the INPUT axis: one 2**bitwidth-entry
+    palette per (block of 128 input columns, output row),
+        W[n, k] = lut_k[k // 128][n][idx[n, k]],   y = x @ W^T (+ bias), fp32 sums, one rounding.
+    The reference has no module of this form (its groups run along the output rows); in its
+    terms this is K/128 PalettizedLinear(group_size=1, K=128) modules summed in fp32
+    (src/scripts/palettized_modules.py:125-162). indices: the idxN blob of the [N, K] codes;
+    lut_k: [K // 128, N, 2**bitwidth] float16 / bfloat16. Decode kernel only: rows are served
+    16 at a time by b200lut_gemv_kgrouped (no tensor-core form)."""
+
+    GROUP_K = 128
+
+    def __init__(self, indices, lut_k, bitwidth, N, K, bias=None):
+        super().__init__()
+        self.bitwidth, self.N, self.K = int(bitwidth), int(N), int(K)
+        if self.bitwidth not in (1, 2, 3, 4):
+            raise ValueError(f"KGroupedPalettizedLinear: bitwidth must be 1-4, got {self.bitwidth}")
+        if self.N % 128 != 0 or self.K % 128 != 0:
+            raise ValueError(f"KGroupedPalettizedLinear needs N%128==0 and K%128==0, got N={self.N}, "
+                             f"K={self.K}")
+        indices = torch.as_tensor(indices)
+        expected = (self.N * self.K * self.bitwidth) // 8
+        if indices.numel() != expected:
+            raise ValueError(f"idx{self.bitwidth} blob numel {indices.numel()} != N*K*{self.bitwidth}/8 "
+                             f"{expected} (N={self.N}, K={self.K})")
+        lut_k = torch.as_tensor(lut_k)
+        want = (self.K // self.GROUP_K, self.N, 1 << self.bitwidth)
+        if tuple(lut_k.shape) != want:
+            raise ValueError(f"lut_k shape {tuple(lut_k.shape)} != (K/128, N, 2**bitwidth) = {want}")
+        self.register_buffer("indices", indices, persistent=False)
+        self.register_buffer("lut_k", lut_k.contiguous(), persistent=False)
+        self.register_parameter("bias", None if bias is None else nn.Parameter(bias, requires_grad=False))
+        self._packed = None
+
+    def _ensure_packed(self):
+        dev = self.lut_k.device
+        if not self.lut_k.is_cuda:
+            raise RuntimeError("KGroupedPalettizedLinear: move the module to a CUDA device first "
+                               "(this package has no CPU compute route)")
+        if self.lut_k.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError(f"KGroupedPalettizedLinear: palette dtype must be float16 or bfloat16, "
+                             f"got {self.lut_k.dtype}")
+        if self._packed is None or self._packed.device != dev:
+            self._packed = _lib.repack_from_idxn(self.indices.to(dev), self.N, self.K, self.bitwidth)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape[-1] != self.K:
+            raise ValueError(f"KGroupedPalettizedLinear: input feature dim {x.shape[-1]} != K {self.K}")
+        if not x.is_cuda:
+            raise RuntimeError("KGroupedPalettizedLinear: x must be a CUDA tensor")
+        self._ensure_packed()
+        cd = self.lut_k.dtype
+        x2 = x.reshape(-1, self.K).to(cd).contiguous()
+        M = x2.shape[0]
+        out = torch.empty(M, self.N, dtype=cd, device=x.device)
+        bias = None if self.bias is None else self.bias.data.to(cd)
+        for m0 in range(0, M, GEMV_MAX_M):
+            m1 = min(M, m0 + GEMV_MAX_M)
+            _lib.gemv_kgrouped(x2[m0:m1], self._packed, self.lut_k, self.N, self.bitwidth, bias=bias,
+                               out=out[m0:m1])
+        return out.to(x.dtype).reshape(*x.shape[:-1], self.N)

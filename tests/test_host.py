@@ -85,6 +85,14 @@ def test_validation_errors_carry_a_message():
     assert rc == 2 and b"nseg" in L.b200lut_last_error()
     rc = L.b200lut_gemm_multi(x, 64, 32, 64, 0, ctypes.byref(seg), 1, 0, None, 0, None)
     assert rc == 1 and b"at least 128" in L.b200lut_last_error()
+    rc = L.b200lut_gemv_kgrouped(x, 128, 17, 128, 0, x, x, None, 128, 4, x, 128, 1, None, 0, None)
+    assert rc == 2 and b"M=17" in L.b200lut_last_error()
+    rc = L.b200lut_gemv_kgrouped(x, 128, 1, 192, 0, x, x, None, 128, 4, x, 128, 1, None, 0, None)
+    assert rc == 1 and b"multiples of 128" in L.b200lut_last_error()
+    rc = L.b200lut_gemv_kgrouped(x, 256, 1, 256, 0, x, x, None, 128, 4, x, 128, 2, None, 0, None)
+    assert rc == 4 and b"workspace" in L.b200lut_last_error()
+    assert L.b200lut_gemv_kgrouped_workspace_bytes(256, 4, 1) == 0
+    assert L.b200lut_gemv_kgrouped_workspace_bytes(256, 4, 3) == 2 * 4 + 256 + 3 * 4 * 256 * 4
     rc = L.b200lut_embed_gather(x, 4, 60, 0, ctypes.byref(seg), None, 0, None)
     assert rc == 1 and b"K %% 64" in L.b200lut_last_error() or b"64" in L.b200lut_last_error()
     rc = L.b200lut_embed_gather(x, -1, 64, 0, ctypes.byref(seg), None, 0, None)
