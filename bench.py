@@ -390,6 +390,10 @@ def run_case(args) -> int:
         gbs, us = single_projection_gbs(pkg, args.batch, 12288, 4096, 8, max(args.steps, 1), 0)
         print(json.dumps({"case": "gemv 12288x4096 M=%d, 8 weight sets" % args.batch, "GB/s": gbs,
                           "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}))
+    elif args.case == "kgrouped":
+        gbs, us = kgrouped_projection_gbs(pkg, args.batch, 4096, 4096, 16, max(args.steps, 1))
+        print(json.dumps({"case": "K-grouped gemv 4096x4096 M=%d, 16 weight sets" % args.batch, "GB/s": gbs,
+                          "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}))
     elif args.case == "embed":
         gbs, us = embedding_gather_gbs(pkg, 248320, 4096, 2048, max(args.steps, 1))
         print(json.dumps({"case": "embedding gather, 2048 rows of a 248320 x 4096 4-bit table",
@@ -416,7 +420,7 @@ def main() -> int:
                     help="N > 1: how the sharded MLP activation is recombined (push: peer stores "
                          "from the GEMV epilogue; nccl: an all-gather call between the launches)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
-    ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemm", "embed"),
+    ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemm", "embed", "kgrouped"),
                     help="stack: the benchmark; gemv / gemm: a few launches of one kernel on a "
                          "small case (the workloads the ncu captures in profiles/ use)")
     ap.add_argument("--executor", default="graph", choices=("plan", "graph"),
