@@ -45,3 +45,40 @@ def test_random_module_forward_matches_oracle(N, K, gs, bits, dtype, M, opts):
     assert got.shape == (M, N)
     assert rel_err(got, case.oracle(x)) <= TOL
     assert pkg._lib.lib().b200lut_device_status() == 0
+
+
+def _merged_cases(n, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(n):
+        M = int(rng.integers(17, 700))
+        K = int(rng.choice([128, 192, 256, 512, 1024, 2048]))
+        bits = int(rng.choice([1, 2, 3, 4]))
+        gs = int(rng.choice([64, 128, 256]))
+        Ns = tuple(256 * int(rng.integers(1, 5)) for _ in range(int(rng.integers(2, 5))))
+        dtype = torch.bfloat16 if i % 2 == 0 else torch.float16
+        out.append(pytest.param(M, K, bits, gs, Ns, dtype, bool(rng.integers(0, 2)),
+                                id=f"{i}-M{M}-K{K}-b{bits}-gs{gs}-N{'+'.join(map(str, Ns))}"))
+    return out
+
+
+@pytest.mark.parametrize("M,K,bits,gs,Ns,dtype,bias", _merged_cases(16, 77))
+def test_random_merged_prefill_launch_matches_oracle(M, K, bits, gs, Ns, dtype, bias):
+    L = pkg._lib
+    cases = [Case(N, K, gs, bits, dtype, seed=M + 7 * i, bias=bias) for i, N in enumerate(Ns)]
+    mods = [c.module() for c in cases]
+    x = cases[0].x(M)
+    total = sum(Ns)
+    out = torch.zeros(M, total, dtype=dtype, device="cuda")
+    descs, off = [], 0
+    for m in mods:
+        descs.append(m._segment_desc(out[:, off:], ldo=total))
+        off += m.N
+    assert L.gemm_multi_ok(descs, K)
+    L.gemm_multi(x.cuda(), L.make_segments(descs), len(descs))
+    off = 0
+    for c, m in zip(cases, mods):
+        assert rel_err(out[:, off:off + m.N], c.oracle(x)) <= TOL
+        off += m.N
+    torch.cuda.synchronize()
+    assert L.lib().b200lut_device_status() == 0
