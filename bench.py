@@ -323,6 +323,22 @@ def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool):
     return 2.0 * M * N * K / us / 1e6, us
 
 
+def dense_matmul_tflops(M: int, N: int, K: int, iters: int):
+    """Extra: the dense bf16 baseline of the same shape (torch.matmul = cuBLAS on a random
+    [N, K] bf16 matrix), the comparison the reference's benchmark_kernel.py:171-177 makes."""
+    import torch
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    w = (0.02 * torch.randn(N, K, device="cuda")).to(torch.bfloat16)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+
+    def run():
+        torch.matmul(x, w.t(), out=out)
+    for _ in range(3):
+        run()
+    us = time_steps(run, iters, 1) * 1e3 / iters
+    return 2.0 * M * N * K / us / 1e6, us
+
+
 def kgrouped_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int):
     """Extra: the K-grouped palette variant of one projection (one 16-entry palette per 128
     input columns and output row: N*K/4 bytes of palettes beside N*K/2 of codes), launched
@@ -567,6 +583,9 @@ def main() -> int:
             extras["prefill_gemm_m2048_k4096_n12288"] = {
                 "TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"],
                 "peak": peaks["bf16_tflops"], "peak_kind": "burst, " + peaks["source"]}
+            dtf, dus = dense_matmul_tflops(2048, 12288, 4096, 20)
+            extras["dense_bf16_matmul_m2048_k4096_n12288"] = {"TFLOP/s": dtf, "us": dus,
+                                                              "lut_gemm_over_dense": tf / dtf}
             tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, 20, True)
             extras["prefill_gemm_with_block128_fht"] = {
                 "TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
