@@ -306,6 +306,19 @@ int b200lut_gemm_multi(const void* x, int64_t ldx, int M, int K, int dtype,
                        const b200lut_segment* segs, int nseg, int flags,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* Prefill GEMM of ONE projection with two code streams of any widths (the mixed-radix recipes,
+ * e.g. 4 + 2 bits): out = x @ (W1 + W2)^T + bias with fp32 sums and ONE rounding, as two
+ * tensor-core launches — the first leaves its fp32 sums in `scratch` ([M][N] floats,
+ * b200lut_gemm_two_stream_bytes), the second adds them to its own before bias and rounding
+ * (stream 1 first, the reference's order, src/scripts/palettized_modules.py:1241-1251).
+ * group_size >= 64, K >= 128; b200lut_gemm serves the 4 + 4 bit pair and group size 32 in one
+ * launch. Replaces the second-stream branch of the reference's streaming GEMM
+ * (src/flute_extended/src/kernel_streaming.cu:1246-). */
+size_t b200lut_gemm_two_stream_bytes(int M, int N);
+int b200lut_gemm_two_stream(const void* x, int64_t ldx, int M, int K, int dtype,
+                            const b200lut_segment* seg, int flags, void* scratch,
+                            size_t scratch_bytes, void* stream);
+
 /* ---- K-grouped palettes ---------------------------------------------------------------------
  *
  * out[m, n] = sum_k x[m, k] * lut_k[k / 128][n][code(n, k)] (+ bias[n]), M <= 16: one

@@ -28,6 +28,7 @@ EXPORTS = (
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
     "b200lut_residual_project", "b200lut_silu_mul", "b200lut_gemm_workspace_bytes", "b200lut_gemm_ws", "b200lut_gemm_multi",
+    "b200lut_gemm_two_stream", "b200lut_gemm_two_stream_bytes",
     "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_kgrouped",
     "b200lut_gemv_kgrouped_split", "b200lut_gemv_kgrouped_workspace_bytes", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
     "b200lut_gemv_noalloc", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
@@ -123,6 +124,10 @@ def lib() -> ctypes.CDLL:
     L.b200lut_gemv_kgrouped_workspace_bytes.argtypes = [i32, i32, i32]
     L.b200lut_gemv_kgrouped.restype = i32
     L.b200lut_gemv_kgrouped.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, i32, i32, vp, i64, i32, vp, sz, vp]
+    L.b200lut_gemm_two_stream_bytes.restype = sz
+    L.b200lut_gemm_two_stream_bytes.argtypes = [i32, i32]
+    L.b200lut_gemm_two_stream.restype = i32
+    L.b200lut_gemm_two_stream.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, vp, sz, vp]
     L.b200lut_embed_gather.restype = i32
     L.b200lut_embed_gather.argtypes = [vp, i64, i32, i32, ctypes.POINTER(Segment), vp, i32, vp]
     L.b200lut_round_rows.restype = i32
@@ -442,6 +447,23 @@ def gemv_kgrouped(x: torch.Tensor, packed: torch.Tensor, lut_k: torch.Tensor, N:
                                           out.data_ptr(), out.stride(0), split, ptr(ws),
                                           ws.numel() if ws is not None else 0, _stream(x)))
     return out
+
+
+def gemm_two_stream(x: torch.Tensor, seg, flags: int = 0) -> None:
+    """Prefill GEMM of one projection with two code streams of any widths: two tensor-core
+    launches that share fp32 sums through a scratch buffer, one rounding."""
+    _need_cuda(x, "x")
+    M, K = x.shape
+    with torch.cuda.device(x.device):
+        need = lib().b200lut_gemm_two_stream_bytes(M, int(seg[0].N))
+        key = (x.device, int(_stream(x) or 0), "two")
+        buf = _gemm_scratch.get(key)
+        if buf is None or buf.numel() < need:
+            buf = torch.empty(max(need, 2 * buf.numel() if buf is not None else 0), dtype=torch.uint8,
+                              device=x.device)
+            _gemm_scratch[key] = buf
+        check(lib().b200lut_gemm_two_stream(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), seg, flags,
+                                            buf.data_ptr(), buf.numel(), _stream(x)))
 
 
 GEMM_MULTI_MAX = 4

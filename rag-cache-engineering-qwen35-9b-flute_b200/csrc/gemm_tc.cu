@@ -399,6 +399,12 @@ struct PersistParams {
   // tiles through the workspace and each finishes its share of the tile's 16-column chunks,
   // adding the partial sums in ascending-k order.
   int split, full, left;
+  // Two code streams of different widths: the first launch leaves its fp32 sums in acc_out
+  // ([token][row], ld_acc floats per token) instead of rounding them, the second adds acc_in to
+  // its own sums before bias and the single rounding.
+  float* acc_out;
+  const float* acc_in;
+  long long ld_acc;
   float* ws;               // [left tile][part < split][column 256][row 128] fp32
   int* tickets;            // [left tile][2]: partial tiles stored, shares finished; zero between launches
 };
@@ -769,6 +775,29 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
                 __stcg(mine + size_t(col0 + s0 + 16 * ch + j) * kTileRows, __uint_as_float(r[ch][j]));
           continue;
         }
+        if (p.acc_out) {   // first stream of two: raw fp32 sums, no bias, no rounding
+          float* dst = p.acc_out + size_t(m0 + col0 + s0) * p.ld_acc + n0 + 32 * q + lane;
+#pragma unroll
+          for (int ch = 0; ch < 3; ++ch)
+            if (16 * ch < sn)
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (m0 + col0 + s0 + 16 * ch + j < p.M)
+                  __stcg(dst + size_t(16 * ch + j) * p.ld_acc, __uint_as_float(r[ch][j]));
+          continue;
+        }
+        if (p.acc_in) {    // second stream: the first stream's sums join before bias and rounding
+          const float* src = p.acc_in + size_t(m0 + col0 + s0) * p.ld_acc + n0 + 32 * q + lane;
+#pragma unroll
+          for (int ch = 0; ch < 3; ++ch)
+            if (16 * ch < sn)
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float a = m0 + col0 + s0 + 16 * ch + j < p.M
+                                    ? __ldcg(src + size_t(16 * ch + j) * p.ld_acc) : 0.f;
+                r[ch][j] = __float_as_uint(a + __uint_as_float(r[ch][j]));
+              }
+        }
 #pragma unroll
         for (int ch = 0; ch < 3; ++ch) {
           if (16 * ch < sn) {
@@ -1002,8 +1031,10 @@ namespace {
 // whose row tiles are the concatenation of the projections' row tiles.
 int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b200lut_segment* segs,
                     int nseg, bool pdl, int debug, void* workspace, size_t workspace_bytes,
-                    void* stream) {
+                    void* stream, float* acc_out = nullptr, const float* acc_in = nullptr,
+                    long long ld_acc = 0) {
   PersistParams pp = {};
+  pp.acc_out = acc_out; pp.acc_in = acc_in; pp.ld_acc = ld_acc;
   int rows = 0;
   for (int i = 0; i < nseg; ++i) {
     const b200lut_segment& s = segs[i];
@@ -1049,7 +1080,8 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
   const long long tiles = (long long)pp.n_tiles * pp.m_tiles;
   int grid = int(tiles < sms ? tiles : sms);
   const SplitPlan sp = plan_split(tiles, pp.G, sms);
-  if (sp.split && workspace && workspace_bytes >= sp.bytes && aligned16(workspace) && !(debug & 32)) {
+  if (sp.split && workspace && workspace_bytes >= sp.bytes && aligned16(workspace) && !(debug & 32) &&
+      !acc_out && !acc_in) {
     pp.split = sp.split; pp.full = sp.full; pp.left = sp.left;
     pp.tickets = static_cast<int*>(workspace);
     pp.ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kTicketBytes);
@@ -1129,6 +1161,49 @@ extern "C" int b200lut_gemm_multi(const void* x, int64_t ldx, int M, int K, int 
   { const char* e = getenv("B200LUT_GEMM_DEBUG"); debug = e ? atoi(e) : 0; }
   return persistent_gemm(x, ldx, M, K, dtype, segs, nseg, (flags & 1) != 0, debug, workspace,
                          workspace_bytes, stream);
+}
+
+extern "C" size_t b200lut_gemm_two_stream_bytes(int M, int N) {
+  if (M < 1 || N < 1) return 0;
+  return size_t(M) * size_t(N) * sizeof(float);
+}
+
+extern "C" int b200lut_gemm_two_stream(const void* x, int64_t ldx, int M, int K, int dtype,
+                                       const b200lut_segment* seg, int flags, void* scratch,
+                                       size_t scratch_bytes, void* stream) {
+  B200LUT_REQUIRE(x && seg, B200LUT_ERR_INVALID, "null x or segment");
+  B200LUT_REQUIRE(M >= 1, B200LUT_ERR_INVALID, "M must be >= 1, got %d", M);
+  B200LUT_REQUIRE(K >= 2 * kChunkK && K % kChunkK == 0, B200LUT_ERR_INVALID,
+                  "K must be a multiple of 64 and at least 128, got %d", K);
+  B200LUT_REQUIRE(dtype == B200LUT_BF16 || dtype == B200LUT_F16, B200LUT_ERR_INVALID,
+                  "dtype must be B200LUT_BF16 or B200LUT_F16");
+  B200LUT_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K, B200LUT_ERR_ALIGN,
+                  "x must be 16-byte aligned with a row stride that is a multiple of 8 and >= K");
+  const b200lut_segment& s = *seg;
+  if (int rc = check_gemm_segment(s)) return rc;
+  B200LUT_REQUIRE(s.packed2 && s.lut2, B200LUT_ERR_INVALID, "the second stream (packed2 / lut2) is missing");
+  B200LUT_REQUIRE(s.bits >= 1 && s.bits <= 4 && s.bits2 >= 1 && s.bits2 <= 4 && s.group_size >= 64,
+                  B200LUT_ERR_UNSUPPORTED,
+                  "code widths must be 1..4 and the group size >= 64 (got %d / %d bits, group %d)",
+                  s.bits, s.bits2, s.group_size);
+  B200LUT_REQUIRE(aligned16(s.packed) && aligned16(s.packed2), B200LUT_ERR_ALIGN,
+                  "code buffers must be 16-byte aligned");
+  B200LUT_REQUIRE(scratch && scratch_bytes >= b200lut_gemm_two_stream_bytes(M, s.N) && aligned16(scratch),
+                  B200LUT_ERR_WORKSPACE, "the two-stream GEMM needs a 16-byte aligned scratch of %zu bytes",
+                  b200lut_gemm_two_stream_bytes(M, s.N));
+  int debug = 0;
+  { const char* e = getenv("B200LUT_GEMM_DEBUG"); debug = e ? atoi(e) : 0; }
+  float* acc = static_cast<float*>(scratch);
+  b200lut_segment first = s, second = s;
+  first.packed2 = first.lut2 = nullptr; first.bits2 = 0; first.bias = nullptr;
+  second.packed = s.packed2; second.lut = s.lut2; second.bits = s.bits2;
+  second.packed2 = second.lut2 = nullptr; second.bits2 = 0;
+  const bool pdl = (flags & 1) != 0;
+  if (int rc = persistent_gemm(x, ldx, M, K, dtype, &first, 1, pdl, debug, nullptr, 0, stream, acc,
+                               nullptr, s.N))
+    return rc;
+  return persistent_gemm(x, ldx, M, K, dtype, &second, 1, pdl, debug, nullptr, 0, stream, nullptr, acc,
+                         s.N);
 }
 
 extern "C" int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dtype,

@@ -297,6 +297,10 @@ class PalettizedLinear(nn.Module):
             # tensor-core GEMM: any width for one code stream with at most two palettes per
             # tile; 4-bit codes for the two-stream and group-size-32 forms
             _lib.gemm(x2, segs, flags=_flags())
+        elif self.has_stream2 and self.group_size >= 64 and self.K >= 128:
+            # two streams of different widths: one tensor-core launch per stream, fp32 sums
+            # carried from the first to the second, one rounding
+            _lib.gemm_two_stream(x2, segs, flags=_flags())
         else:
             # what the tensor-core GEMM does not serve: decode kernel, 16 rows at a time
             for r0 in range(0, M, GEMV_MAX_M):

@@ -295,3 +295,35 @@ def test_shapes_and_seeds_of_the_reference_gpu_gate(bits):
     # the dequantised weights themselves, bit for bit, through the same module
     W = mod(torch.eye(K, dtype=torch.float16, device="cuda")).cpu().t()
     assert torch.equal(W.float(), orc.dequant_indices(codes, lut, gs, bits).float())
+
+
+@pytest.mark.parametrize("bits,bits2,gs,dtype,N,K,M,bias", (
+    (4, 2, 128, torch.bfloat16, 512, 1024, 300, True),     # the deployed mixed-radix pair
+    (3, 1, 64, torch.float16, 256, 256, 40, False),
+    (2, 4, 128, torch.bfloat16, 384, 512, 129, True),
+    (4, 3, 256, torch.bfloat16, 1024, 2048, 2048, False),  # full prefill width
+))
+def test_two_streams_of_different_widths_on_the_tensor_cores(bits, bits2, gs, dtype, N, K, M, bias):
+    case = Case(N, K, gs, bits, dtype, seed=bits * 10 + bits2, bits2=bits2, bias=bias)
+    mod = case.module()
+    x = case.x(M)
+    got = mod(x.cuda())
+    want = case.oracle(x)
+    assert rel_err(got, want) <= TOL
+    # the same module through the decode kernel, 16 rows at a time: one rounding in both routes
+    rows = slice(0, 16)
+    assert rel_err(got[rows], mod(x[rows].cuda())) <= 2.0 ** -7
+
+
+def test_two_stream_entry_refuses_a_missing_stream_and_a_small_scratch():
+    case = Case(128, 128, 128, 4, torch.bfloat16, seed=3)
+    mod = case.module()
+    x = case.x(32).cuda()
+    out = torch.empty(32, 128, dtype=torch.bfloat16, device="cuda")
+    seg = L.make_segments([mod._segment_desc(out)])
+    with pytest.raises(RuntimeError, match="second stream"):
+        L.gemm_two_stream(x, seg)
+    two = Case(128, 128, 128, 4, torch.bfloat16, seed=4, bits2=2).module()
+    seg = L.make_segments([two._segment_desc(out)])
+    rc = L.lib().b200lut_gemm_two_stream(x.data_ptr(), 128, 32, 128, 0, seg, 0, out.data_ptr(), 64, None)
+    assert rc == 4

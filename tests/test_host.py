@@ -93,6 +93,9 @@ def test_validation_errors_carry_a_message():
     assert rc == 4 and b"workspace" in L.b200lut_last_error()
     assert L.b200lut_gemv_kgrouped_workspace_bytes(256, 4, 1) == 0
     assert L.b200lut_gemv_kgrouped_workspace_bytes(256, 4, 3) == 2 * 4 + 256 + 3 * 4 * 256 * 4
+    rc = L.b200lut_gemm_two_stream(x, 128, 32, 128, 0, ctypes.byref(seg), 0, x, 1 << 20, None)
+    assert rc == 1 and b"second stream" in L.b200lut_last_error()
+    assert L.b200lut_gemm_two_stream_bytes(32, 128) == 32 * 128 * 4
     rc = L.b200lut_embed_gather(x, 4, 60, 0, ctypes.byref(seg), None, 0, None)
     assert rc == 1 and b"K %% 64" in L.b200lut_last_error() or b"64" in L.b200lut_last_error()
     rc = L.b200lut_embed_gather(x, -1, 64, 0, ctypes.byref(seg), None, 0, None)
