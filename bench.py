@@ -576,6 +576,16 @@ def main() -> int:
                      "us_per_launch": ms_step * 1e3 / kernel_launches,
                      "projection_groups_per_step": launches},
     }
+    if M > 64:
+        # beyond the crossover the step is bound by the tensor cores: report it against the
+        # sustained bf16 peak (the kernel is timed inside a long step)
+        tf = stack.flops(M) / (ms_step * 1e-3) / 1e12
+        line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc_persistent_kernel", "achieved": tf,
+                            "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                            "frac": tf / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"],
+                            "traffic": None, "flops_per_step": stack.flops(M),
+                            "us_per_launch": ms_step * 1e3 / kernel_launches,
+                            "projection_groups_per_step": launches}
     if rank == 0 and world == 1 and not args.no_extras:
         extras = {}
         try:
