@@ -41,9 +41,6 @@ constexpr uint32_t kACol = 256;        // operand stage s at columns [256 + 32 s
 constexpr size_t kMaxDynSmem = 232448 - 1024;
 
 __device__ int g_gemm_status = 0;
-#ifdef B200LUT_GEMM_TIMING
-__device__ long long g_gemm_timing[64];
-#endif
 
 struct GemmParams {
   const uint8_t* packed[2];
@@ -58,7 +55,6 @@ struct GemmParams {
   int NT;           // token tile (multiple of 16, <= 256; <= 128 with two planes)
   int m_tiles;
   uint32_t smem_bytes;
-  int debug;
   int out_aligned;   // out rows are 16-byte aligned: staged, vectorised epilogue
 };
 
@@ -101,9 +97,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     *nxs_slot = n;
   }
 
-#ifdef B200LUT_GEMM_TIMING
-  const long long t_kernel0 = clock64();
-#endif
   const int n_tile = blockIdx.x / p.m_tiles, m_tile = blockIdx.x % p.m_tiles;
   const int m0 = m_tile * p.NT, n0 = n_tile * kTileRows;
   const int total = p.G * p.npass;     // k-blocks streamed, pass-major
@@ -146,9 +139,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-#ifdef B200LUT_GEMM_TIMING
-  if (threadIdx.x == 0 && blockIdx.x == 0) g_gemm_timing[48] = clock64() - t_kernel0;
-#endif
   const uint32_t tmem = *tmem_slot;
   const int nst = *nxs_slot > 0 ? *nxs_slot : 1;   // pipeline depth: 2..4 stages of both operands
 
@@ -157,9 +147,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     uint32_t token;
     asm volatile("mov.u32 %0, 0;" : "=r"(token));
     const uint32_t lane_base = tbl_addr + lane * 4 + token;
-#ifdef B200LUT_GEMM_TIMING
-    long long t_wait = 0, t_all = clock64();
-#endif
     for (int i0 = grp; i0 < total; i0 += 2 * kRing) {
 #pragma unroll
       for (int u = 0; u < kRing; ++u) {
@@ -167,15 +154,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
         if (i < total) {
           const int stage = i % nst, use = i / nst;
           const int pass = i >= p.G ? 1 : 0;
-#ifdef B200LUT_GEMM_TIMING
-          long long ta = clock64();
-#endif
           if (use > 0)
             tc::mbar_wait(bar_empty + 8 * stage, uint32_t(use - 1) & 1u, abort_flag,
                           &g_gemm_status, tc::kStatusWaitEmpty);
-#ifdef B200LUT_GEMM_TIMING
-          t_wait += clock64() - ta;
-#endif
           tc::fence_after_sync();
 #pragma unroll
           for (int sl = 0; sl < 2; ++sl) {
@@ -186,9 +167,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
 #pragma unroll
             for (int kt = 0; kt < 4; ++kt) {
               const uint32_t word = w[u][4 * sl + kt];
-#ifdef B200LUT_GEMM_TIMING
-              if (p.debug & 1) { r[4 * kt] = word; r[4 * kt + 1] = word; r[4 * kt + 2] = word; r[4 * kt + 3] = word; continue; }
-#endif
               // slab fields (row g, k 0-1), (g+8, k 0-1), (g, k 2-3), (g+8, k 2-3); the store
               // shape wants (g, c), (g, c+1), (g+8, c), (g+8, c+1): fields 0, 2, 1, 3
               r[4 * kt + 0] = lds32(__byte_perm(word, tb, 0x7604u));
@@ -206,9 +184,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
         }
       }
     }
-#ifdef B200LUT_GEMM_TIMING
-    if (blockIdx.x == 0 && lane == 0) { g_gemm_timing[warp * 2] = t_wait; g_gemm_timing[warp * 2 + 1] = clock64() - t_all; }
-#endif
   } else if (warp == kLookupWarps) {
     // ---- TMA producer: activations of k-block c, tokens m0 .. m0 + NT ---------------------------
     for (int i = 0; i < total; ++i) {
@@ -217,9 +192,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
       if (use > 0)
         tc::mbar_wait(bar_empty + 8 * xs, uint32_t(use - 1) & 1u, abort_flag, &g_gemm_status,
                       tc::kStatusWaitEmpty);
-#ifdef B200LUT_GEMM_TIMING
-      if (lane == 0 && (p.debug & 2) && use > 0) { tc::mbar_arrive(bar_xfull + 8 * xs); } else
-#endif
       if (lane == 0 && !*abort_flag) {
         tc::mbar_expect_tx(bar_xfull + 8 * xs, stage_bytes);
         tma_load_2d(xaddr[xs], &xmap, bar_xfull + 8 * xs, c * kChunkK, m0);
@@ -230,9 +202,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     // ---- MMA issuer ---------------------------------------------------------------------------
     constexpr uint32_t kFmt = DType<T>::id == B200LUT_BF16 ? 1u : 0u;
     const uint32_t idesc = tc::instr_desc(kFmt, 128, uint32_t(p.NT));
-#ifdef B200LUT_GEMM_TIMING
-    long long t_x = 0, t_a = 0, t_all = clock64();
-#endif
     // One thread issues; its instruction stream is the limit (an MMA must leave every 128
     // cycles), so nothing is computed per MMA: stage descriptors sit in registers, stage
     // and phase advance by increment, a K step is a 64-bit add, one commit per k-block.
@@ -246,17 +215,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     auto block = [&](int i, int stage, uint32_t phase, uint64_t bdesc0) {
       const int pass = i >= G ? 1 : 0;
       const bool first = (i == 0) || (two_planes && i == G);
-#ifdef B200LUT_GEMM_TIMING
-      long long ta = clock64();
-#endif
       tc::mbar_wait(bar_xfull + 8 * stage, phase, abort_flag, &g_gemm_status, tc::kStatusWaitLoad);
-#ifdef B200LUT_GEMM_TIMING
-      long long tb = clock64(); t_x += tb - ta;
-#endif
       tc::mbar_wait(bar_afull + 8 * stage, phase, abort_flag, &g_gemm_status, tc::kStatusWaitFull);
-#ifdef B200LUT_GEMM_TIMING
-      t_a += clock64() - tb;
-#endif
       tc::fence_after_sync();
       if (lane == 0) {
         const uint32_t a0 = tmem + kACol + 32u * uint32_t(stage), d0 = pass ? dcol[1] : dcol[0];
@@ -284,18 +244,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
         if (++stage == nst) { stage = 0; phase ^= 1u; }
       }
     }
-#ifdef B200LUT_GEMM_TIMING
-    if (blockIdx.x == 0 && lane == 0) { g_gemm_timing[40] = t_x; g_gemm_timing[41] = t_a; g_gemm_timing[42] = clock64() - t_all; g_gemm_timing[43] = nst; }
-#endif
   }
 
   // ---- epilogue: TMEM -> bias / SiLU*mul -> one rounding -> global -----------------------------
   if (warp < kLookupWarps) {
     tc::mbar_wait(bar_done, 0u, abort_flag, &g_gemm_status, tc::kStatusWaitDone);
     tc::fence_after_sync();
-#ifdef B200LUT_GEMM_TIMING
-    if (threadIdx.x == 0 && blockIdx.x == 0) g_gemm_timing[49] = clock64() - t_kernel0;
-#endif
     const int n = n0 + 32 * q + lane;
     const float b0 = p.bias[0] ? DType<T>::to_float(p.bias[0][n]) : 0.f;
     const float b1 = (p.npass > 1 && p.bias[1]) ? DType<T>::to_float(p.bias[1][n]) : 0.f;
@@ -336,9 +290,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     tc::fence_before_sync();
   }
   __syncthreads();
-#ifdef B200LUT_GEMM_TIMING
-  if (threadIdx.x == 0 && blockIdx.x == 0) g_gemm_timing[50] = clock64() - t_kernel0;
-#endif
   if (warp == kLookupWarps) {
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem, kTmemCols);
@@ -390,7 +341,6 @@ struct PersistParams {
   int n_tiles;       // row tiles
   int W;             // token columns of a row of tiles (the last tile rounded up to 32)
   uint32_t smem_bytes;
-  int debug;
   long long wait_cycles;   // bound of every in-kernel wait, in SM clock cycles
   // Split mode (a workspace was given and the tile count leaves a partly filled last round):
   // every block takes `full` whole tiles; each of the `left` tiles behind them is cut along K
@@ -480,18 +430,6 @@ __global__ void __launch_bounds__(kPThreads, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const PersistParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef B200LUT_GEMM_TIMING
-#define PT_DECL long long pt_acc[4] = {0, 0, 0, 0}; const long long pt_start = clock64(); long long pt_t0 = 0;
-#define PT_BEGIN pt_t0 = clock64();
-#define PT_END(k) pt_acc[k] += clock64() - pt_t0;
-#define PT_STORE(slot) if (blockIdx.x == 0 && lane == 0) { for (int z = 0; z < 4; ++z) g_gemm_timing[slot + z] = pt_acc[z]; g_gemm_timing[slot + 4] = clock64() - pt_start; }
-#else
-#define PT_DECL
-#define PT_BEGIN
-#define PT_END(k)
-#define PT_STORE(slot)
-#endif
-  PT_DECL
   const uint32_t base = smem_u32(smem);
   const uint32_t bar_full = base, bar_done = base + 64, bar_dfull = base + 128,
                  bar_dempty = base + 144;
@@ -611,7 +549,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
             // and rebuild the pair table together when the row tile has changed
             const int row = use.row;
             if (row != table_row) {
-              PT_BEGIN
               asm volatile("bar.sync 1, %0;" ::"r"(kLookupWarps * 32) : "memory");
               const PersistSeg sd = segment_of_row(p, row);
               build_tables(tbl_ptr, sd.lut, BITS, sd.n_groups, (row - sd.row0) * kTileRows, p.gs, nl,
@@ -621,18 +558,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
               asm volatile("mov.u32 %0, 0;" : "=r"(token));
               lane_base = tbl_addr + lane * 4 + token;
               table_row = row;
-              PT_END(1)
             }
             table_seg = use.s;
           }
           const int i = it + 2 * u;
           const int stage = i % kPStages;
-          PT_BEGIN
           if (i >= kPStages)        // the k-block that last used this operand stage has been consumed
             tc::mbar_wait(bar_done + 8 * stage, uint32_t(i / kPStages - 1) & 1u, abort_flag,
                           &g_gemm_status, tc::kStatusWaitEmpty, p.wait_cycles);
-          PT_END(0)
-          PT_BEGIN
           tc::fence_after_sync();
 #pragma unroll
           for (int sl = 0; sl < 2; ++sl) {
@@ -656,17 +589,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
             load_slab_pair<BITS>(w[u], on ? code_ptr(ld) : p.seg[0].packed, q, on ? 1u : 0u);
             if (on) advance(ld);
           }
-          PT_END(2)
-          PT_BEGIN
           tc::wait_st();
-          PT_END(3)
           tc::fence_before_sync();
           if (lane == 0) tc::mbar_arrive(bar_full + 8 * stage);
           advance(use);
         }
       }
     }
-    PT_STORE(warp * 5)
   } else if (warp == kLookupWarps) {
     // ---- TMA producer ---------------------------------------------------------------------------
     int i = 0;
@@ -710,15 +639,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
               int nt = p.M - m0;                          // the row's last tile may be narrower
               nt = nt >= p.NT ? p.NT : ((nt + 31) & ~31);
               idesc = tc::instr_desc(kFmt, 128, uint32_t(nt));
-              PT_BEGIN
               if (t >= 1)
                 tc::mbar_wait(bar_dempty, uint32_t(t - 1) & 1u, abort_flag, &g_gemm_status,
                               tc::kStatusWaitDone, p.wait_cycles);
-              PT_END(2)
             }
-            PT_BEGIN
             tc::mbar_wait(bar_full + 8 * u, phase, abort_flag, &g_gemm_status, tc::kStatusWaitFull, p.wait_cycles);
-            PT_END(0)
             tc::fence_after_sync();
             tc::mma_ts_kblock(d0, tmem + kPACol + 32u * uint32_t(u), xlo[u], xhi, idesc,
                               c == c_first ? 0u : 1u);   // a segment's first k-block overwrites
@@ -727,7 +652,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
           }
         }
       }
-      PT_STORE(45)
     }
     __syncwarp();
   } else {
@@ -747,9 +671,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
       const int half = nt >> 1, col0 = h * half;
       const int n = n0 + 32 * q + lane;
       const float b0 = sd.bias ? DType<T>::to_float(sd.bias[n]) : 0.f;
-      PT_BEGIN
       tc::mbar_wait(bar_dfull, uint32_t(t) & 1u, abort_flag, &g_gemm_status, tc::kStatusWaitDone, p.wait_cycles);
-      PT_END(0)
       tc::fence_after_sync();
       const uint32_t d0 = tmem + (uint32_t(32 * q) << 16) + uint32_t(col0);
       float* wt = cut ? p.ws + size_t(tile - int(gridDim.x) * p.full) * p.split * (256 * kTileRows) : nullptr;
@@ -873,21 +795,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
       }
     }
   }
-
-  if (warp == kLookupWarps + 2) { PT_STORE(52) }
   tc::fence_before_sync();
   __syncthreads();
   if (warp == kLookupWarps) {
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem, kTmemCols);
   }
-#ifdef B200LUT_GEMM_TIMING
-  if (threadIdx.x == 0 && blockIdx.x == 0) { g_gemm_timing[60] = clock64() - pt_start; g_gemm_timing[61] = ntile; }
-#endif
-#undef PT_DECL
-#undef PT_BEGIN
-#undef PT_END
-#undef PT_STORE
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -1007,11 +920,6 @@ int encode_x_map(CUtensorMap* map, const void* x, int64_t ldx, int M, int K, int
 
 using namespace b200lut;
 
-#ifdef B200LUT_GEMM_TIMING
-extern "C" int b200lut_gemm_timing(long long* out64) {
-  return cudaMemcpyFromSymbol(out64, g_gemm_timing, sizeof(long long) * 64) == cudaSuccess ? 0 : 3;
-}
-#endif
 
 // Device-side status of the library's kernels on the current device (0 = none). A
 // non-zero value means a bounded wait ran out inside a kernel (tensor-core pipeline codes,
@@ -1030,7 +938,7 @@ namespace {
 // the same code width and group size, at most two palettes per 128-row tile) as one launch
 // whose row tiles are the concatenation of the projections' row tiles.
 int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b200lut_segment* segs,
-                    int nseg, bool pdl, int debug, void* workspace, size_t workspace_bytes,
+                    int nseg, bool pdl, void* workspace, size_t workspace_bytes,
                     void* stream, float* acc_out = nullptr, const float* acc_in = nullptr,
                     long long ld_acc = 0) {
   PersistParams pp = {};
@@ -1058,7 +966,6 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
   pp.n_tiles = rows;
   pp.W = (pp.m_tiles - 1) * pp.NT + ((M - (pp.m_tiles - 1) * pp.NT + 31) / 32) * 32;
   pp.smem_bytes = uint32_t(kMaxDynSmem);
-  pp.debug = debug;
   // Waits inside the kernel give up after ~10 ms. A profiler that replays the kernel with
   // heavy instrumentation can stretch a healthy wait beyond that; B200LUT_WAIT_MS raises the
   // bound for such runs (capped at one second).
@@ -1080,7 +987,7 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
   const long long tiles = (long long)pp.n_tiles * pp.m_tiles;
   int grid = int(tiles < sms ? tiles : sms);
   const SplitPlan sp = plan_split(tiles, pp.G, sms);
-  if (sp.split && workspace && workspace_bytes >= sp.bytes && aligned16(workspace) && !(debug & 32) &&
+  if (sp.split && workspace && workspace_bytes >= sp.bytes && aligned16(workspace) &&
       !acc_out && !acc_in) {
     pp.split = sp.split; pp.full = sp.full; pp.left = sp.left;
     pp.tickets = static_cast<int*>(workspace);
@@ -1157,9 +1064,7 @@ extern "C" int b200lut_gemm_multi(const void* x, int64_t ldx, int M, int K, int 
                     "one group size >= 64 (segment %d: %d bits, group %d)", i, s.bits, s.group_size);
     B200LUT_REQUIRE(aligned16(s.packed), B200LUT_ERR_ALIGN, "code buffers must be 16-byte aligned");
   }
-  int debug = 0;
-  { const char* e = getenv("B200LUT_GEMM_DEBUG"); debug = e ? atoi(e) : 0; }
-  return persistent_gemm(x, ldx, M, K, dtype, segs, nseg, (flags & 1) != 0, debug, workspace,
+  return persistent_gemm(x, ldx, M, K, dtype, segs, nseg, (flags & 1) != 0, workspace,
                          workspace_bytes, stream);
 }
 
@@ -1191,18 +1096,16 @@ extern "C" int b200lut_gemm_two_stream(const void* x, int64_t ldx, int M, int K,
   B200LUT_REQUIRE(scratch && scratch_bytes >= b200lut_gemm_two_stream_bytes(M, s.N) && aligned16(scratch),
                   B200LUT_ERR_WORKSPACE, "the two-stream GEMM needs a 16-byte aligned scratch of %zu bytes",
                   b200lut_gemm_two_stream_bytes(M, s.N));
-  int debug = 0;
-  { const char* e = getenv("B200LUT_GEMM_DEBUG"); debug = e ? atoi(e) : 0; }
   float* acc = static_cast<float*>(scratch);
   b200lut_segment first = s, second = s;
   first.packed2 = first.lut2 = nullptr; first.bits2 = 0; first.bias = nullptr;
   second.packed = s.packed2; second.lut = s.lut2; second.bits = s.bits2;
   second.packed2 = second.lut2 = nullptr; second.bits2 = 0;
   const bool pdl = (flags & 1) != 0;
-  if (int rc = persistent_gemm(x, ldx, M, K, dtype, &first, 1, pdl, debug, nullptr, 0, stream, acc,
+  if (int rc = persistent_gemm(x, ldx, M, K, dtype, &first, 1, pdl, nullptr, 0, stream, acc,
                                nullptr, s.N))
     return rc;
-  return persistent_gemm(x, ldx, M, K, dtype, &second, 1, pdl, debug, nullptr, 0, stream, nullptr, acc,
+  return persistent_gemm(x, ldx, M, K, dtype, &second, 1, pdl, nullptr, 0, stream, nullptr, acc,
                          s.N);
 }
 
@@ -1231,11 +1134,9 @@ extern "C" int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dty
                   "code buffers must be 16-byte aligned");
 
   const bool pdl = (flags & 1) != 0;
-  int debug = 0;
-  { const char* e = getenv("B200LUT_GEMM_DEBUG"); debug = e ? atoi(e) : 0; }
   const int nl = s.group_size >= 128 ? 1 : 128 / s.group_size;
-  if (!two && nl <= 2 && K / kChunkK >= 2 && !(debug & 4)) {
-    return persistent_gemm(x, ldx, M, K, dtype, seg, 1, pdl, debug, workspace, workspace_bytes, stream);
+  if (!two && nl <= 2 && K / kChunkK >= 2) {
+    return persistent_gemm(x, ldx, M, K, dtype, seg, 1, pdl, workspace, workspace_bytes, stream);
   }
 
   // what is left for the one-tile kernel: two code streams, the fused gate/up form, four
@@ -1278,7 +1179,6 @@ extern "C" int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dty
                     "stages in shared memory", s.group_size, p.npass);
   }
   p.smem_bytes = uint32_t(kMaxDynSmem);
-  p.debug = debug;
 
   CUtensorMap map;
   if (int rc = encode_x_map(&map, x, ldx, M, K, dtype, NT)) return rc;

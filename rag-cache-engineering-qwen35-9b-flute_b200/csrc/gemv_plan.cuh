@@ -234,14 +234,8 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
     }
   };
 
-#ifdef B200LUT_PLAN_TIMING
-  long long tm_head = 0, tm_loop = 0, tm_fold = 0, tm_tile = 0, tm_total0 = clock64(), tm_mark;
-#define TM_MARK() tm_mark = clock64()
-#define TM_ADD(v) v += clock64() - tm_mark
-#else
 #define TM_MARK()
 #define TM_ADD(v)
-#endif
   PassDesc cur, nxt;
   uint32_t w[32];
 #pragma unroll
@@ -271,9 +265,6 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
     __syncthreads();                       // table of this pass is complete; dependency met
     TM_ADD(tm_head);
     TM_MARK();
-#ifdef B200LUT_PLAN_TIMING
-    if (threadIdx.x == 0 && b == 0 && cur.first_of_job) reinterpret_cast<long long*>(misc + 64)[4 * cur.j + 0] = clock64() - tm_total0;
-#endif
     float acc[P::kAcc][4];
 #pragma unroll
     for (int a = 0; a < P::kAcc; ++a)
@@ -296,9 +287,6 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
 
     TM_ADD(tm_loop);
     TM_MARK();
-#ifdef B200LUT_PLAN_TIMING
-    if (threadIdx.x == 0 && b == 0) reinterpret_cast<long long*>(misc + 64)[4 * cur.j + 1] = clock64() - tm_total0;
-#endif
     // codes and table of the next pass go out before this pass folds
     if (nxt.valid) {
       first_chunk(w, nxt.packed, nxt.bits, nxt.tile, jobbuf[nxt.slot].G, nxt.c0 + warp, nxt.c1, lane);
@@ -366,22 +354,9 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_plan_kernel(uint8_t* plan
       }
     }
     TM_ADD(tm_tile);
-#ifdef B200LUT_PLAN_TIMING
-    if (threadIdx.x == 0 && b == 0) reinterpret_cast<long long*>(misc + 64)[4 * cur.j + 2] = clock64() - tm_total0;
-    if (threadIdx.x == 0 && cur.j >= 8 && cur.j < 12) {
-      long long* q = reinterpret_cast<long long*>(misc + 2048) + ((cur.j - 8) * 160 + b) * 4;
-      q[0] = clock64(); q[1] = tm_mark; q[2] = cur.last_of_tile ? 1 : 0; q[3] = cur.c1 - cur.c0;
-    }
-#endif
     cur = nxt;
     region ^= 1;
   }
-#ifdef B200LUT_PLAN_TIMING
-  if (threadIdx.x == 0 && b < 4) {
-    long long* t = reinterpret_cast<long long*>(misc + 16) + b * 5;
-    t[0] = tm_head; t[1] = tm_loop; t[2] = tm_fold; t[3] = tm_tile; t[4] = clock64() - tm_total0;
-  }
-#endif
 
   // the last block out resets the completion counters for the next launch
   __syncthreads();

@@ -8,13 +8,14 @@ fuse MLPs → move to the device. `forward="kernel"` serves through
 libb200lut.so; `forward="reference"` keeps every module on the torch dequant
 route (on CUDA that is this package's dequant kernel + a torch matmul).
 
-Difference from the reference: the model comes from the caller. `model` is an
-`nn.Module` (any module tree with `model.layers[i].<path>` Linear members) or
-a zero-argument callable that builds one; a string is handed to
+Same positional arguments and defaults as the reference. `model_name` may also be an
+`nn.Module` (any module tree with `model.layers[i].<path>` Linear members) or a
+zero-argument callable that builds one; a string is handed to
 `transformers.AutoModelForCausalLM.from_pretrained` (needs a local checkpoint).
-The reference's vendored Qwen3.5 classes and their M1/M2 memories are model
-code outside the linear path; `use_m1m2` and its companions are accepted for
-signature compatibility and must be left at "off" values.
+The reference's vendored Qwen3.5 classes and their M1/M2 memories are model code
+outside the linear path: the default `use_m1m2=True` without a gates file leaves
+outputs unchanged in the reference and is served without the memories; a gates
+file is refused.
 """
 from __future__ import annotations
 
@@ -121,15 +122,28 @@ def recover_awq_scales(model, artifacts_dir: str, metadata: Dict, verify_sha: bo
     return out
 
 
-def load_quant_model(artifacts_dir, model, device, residual=False, dtype=None, forward="kernel",
-                     awq_compensation=True, heads_dir=None, use_m1m2=False, m1m2_mem_size=128,
-                     m1m2_gates_path=None, verify_sha=True):
-    """Returns (model, metadata). See the module docstring for `model`."""
+def load_quant_model(artifacts_dir, model_name, device, residual=False, dtype=None, forward="kernel",
+                     awq_compensation=True, heads_dir=None, use_m1m2=True, m1m2_mem_size=128,
+                     m1m2_gates_path=None, *, verify_sha=True):
+    """Returns (model, metadata). Positional order and defaults are those of the reference's
+    loader (src/scripts/loader.py:17-21); `verify_sha` is an added keyword.
+
+    model_name: a checkpoint name or path (handed to transformers' AutoModelForCausalLM), or —
+    since no checkpoint travels with this package — an nn.Module, or a zero-argument callable
+    that builds one.
+
+    use_m1m2 / m1m2_mem_size / m1m2_gates_path: the M1/M2 memories live in the reference's
+    vendored model classes, which this package does not carry. With the reference's default
+    (use_m1m2=True, no gates file) those memories start from zero-initialised gates and leave
+    the model's outputs bit-unchanged, so the default is served by not attaching them. A gates
+    file would change the outputs and cannot be honoured: it is refused."""
     if forward not in ("kernel", "reference"):
         raise ValueError(f"forward must be 'kernel' or 'reference', got {forward!r}")
-    if use_m1m2 or m1m2_gates_path:
-        raise NotImplementedError("the M1/M2 memories belong to the reference's vendored model code, "
-                                  "which this package does not carry; pass use_m1m2=False")
+    if m1m2_gates_path:
+        raise NotImplementedError(
+            "m1m2_gates_path: trained M1/M2 gates need the reference's vendored model classes, "
+            "which this package does not carry; load without a gates file")
+    model = model_name
     if dtype is None:
         dtype = torch.float16
     metadata = artifacts.load_metadata(artifacts_dir)

@@ -37,7 +37,7 @@ def sha(path):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (its own Python modules are imported from it)")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src", "scripts"))
     sys.path.insert(0, os.path.join(args.reference, "src", "flute_extended"))

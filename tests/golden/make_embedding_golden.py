@@ -45,7 +45,7 @@ def _store(out, key, t):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (its own Python modules are imported from it)")
     ap.add_argument("--out", default=os.path.join(os.path.dirname(os.path.abspath(__file__)),
                                                   "embedding_vectors.npz"))
     args = ap.parse_args()

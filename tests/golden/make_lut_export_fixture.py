@@ -34,7 +34,7 @@ sys.path.insert(0, ROOT)
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (its own Python modules are imported from it)")
     args = ap.parse_args()
     for sub in ("scripts", "flute_extended", "rag"):
         sys.path.insert(0, os.path.join(args.reference, "src", sub))
