@@ -37,6 +37,16 @@ enum {
 
 enum { B200LUT_BF16 = 0, B200LUT_F16 = 1 };
 
+/* Launch flags of the compute entry points (`flags` argument). */
+enum {
+  B200LUT_FLAG_PDL = 1,          /* programmatic dependent launch: everything that does not depend
+                                    on the previous kernel of the stream (code prefetch, palette
+                                    fetch, table build) runs before the launch waits for it */
+  B200LUT_FLAG_TILE_KERNEL = 2,  /* decode GEMV: run the tile x K-split kernel */
+  B200LUT_FLAG_ROWS_KERNEL = 4   /* decode GEMV: run the row-range kernel where it serves the shapes
+                                    (4-bit codes, one stream, M <= 8, split = 0) */
+};
+
 /* Epilogue selector of b200lut_gemv_multi / b200lut_gemm. */
 enum {
   B200LUT_EPI_NONE = 0,
@@ -178,6 +188,15 @@ int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out,
 int b200lut_gemv_noalloc(const void* x, const void* packed, const void* lut, void* out,
                          int M, int N, int K, int bits, int group_size, int n_groups, int dtype,
                          int split, void* stream);
+
+/* Stream-ordered reset of the tickets of the built-in scratch of b200lut_gemv_noalloc (a
+ * cudaMemsetAsync over its first 4 KiB; allocates nothing). The tickets return to zero at the end
+ * of every healthy launch, so ordinary use never needs this. A launch that did not finish (a
+ * sticky CUDA error on its stream, a lost context that the host recovered from) can leave some
+ * set, and later calls on those tiles would then fold their partial sums too early; a caller-
+ * owned workspace is re-zeroed with a memset in that situation, the built-in array with this
+ * call. This entry point has no counterpart in the reference. */
+int b200lut_gemv_noalloc_reset(void* stream);
 
 /* ---- column-parallel exchange: the all-gather folded into the GEMV ---------------------
  *

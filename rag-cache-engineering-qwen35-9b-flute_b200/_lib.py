@@ -21,6 +21,8 @@ BF16, F16, F32 = 0, 1, 2
 EPI_NONE, EPI_SILU_MUL = 0, 1
 FHT_FORWARD, FHT_ADJOINT, FHT_AWQ = 0, 1, 2
 FLAG_PDL = 1
+FLAG_TILE_KERNEL = 2     # decode GEMV: force the tile x K-split kernel
+FLAG_ROWS_KERNEL = 4     # decode GEMV: the row-range kernel where it serves the shapes
 
 EXPORTS = (
     "b200lut_version", "b200lut_last_error", "b200lut_sm_count", "b200lut_device_status", "b200lut_packed_bytes",
@@ -31,7 +33,7 @@ EXPORTS = (
     "b200lut_gemm_two_stream", "b200lut_gemm_two_stream_bytes",
     "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_kgrouped",
     "b200lut_gemv_kgrouped_split", "b200lut_gemv_kgrouped_workspace_bytes", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
-    "b200lut_gemv_noalloc", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
+    "b200lut_gemv_noalloc", "b200lut_gemv_noalloc_reset", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
 
@@ -153,6 +155,8 @@ def lib() -> ctypes.CDLL:
     L.b200lut_fht.argtypes = [vp, vp, vp, vp, i32, i32, i64, i64, i32, i32, i32, vp]
     L.b200lut_gemv_noalloc.restype = i32
     L.b200lut_gemv_noalloc.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+    L.b200lut_gemv_noalloc_reset.restype = i32
+    L.b200lut_gemv_noalloc_reset.argtypes = [vp]
     L.b200lut_plan_bytes.restype = sz
     L.b200lut_plan_bytes.argtypes = [ctypes.POINTER(Job), i32, i32, i32]
     L.b200lut_plan_build.restype = i32

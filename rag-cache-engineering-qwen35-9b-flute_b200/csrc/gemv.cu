@@ -30,6 +30,7 @@
 #include <cooperative_groups.h>
 
 #include <cstdlib>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -41,21 +42,6 @@ namespace b200lut {
 namespace {
 
 __device__ int g_exchange_status = 0;
-
-#ifdef B200LUT_GEMV_TRACE
-// Debug build only: wall-clock stamps (ns) of the first and the last block of each launch.
-__device__ unsigned long long g_trace[8192 * 8];
-__device__ unsigned int g_trace_launch = 0;
-__device__ __forceinline__ unsigned long long trace_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define TRACE_STAMP(k)                                                             \
-  if (trace_row && threadIdx.x == 0) trace_row[k] = trace_now();
-#else
-#define TRACE_STAMP(k)
-#endif
 
 constexpr int kMaxSeg = 8;
 constexpr int kMaxM = 16;
@@ -158,9 +144,6 @@ struct DepWait {
   int target;               // mode 2: proceed when *counter >= target
   int* abort_word;          // mode 2: global word set when any block gave up waiting
   const ExchangeDev* ex;    // mode 1: also wait for the peers' pushes (null: no exchange)
-#ifdef B200LUT_GEMV_TRACE
-  unsigned long long* trace;
-#endif
 };
 
 constexpr long long kDepWaitCycles = 40000000;   // ~20 ms: far beyond any healthy wait
@@ -291,9 +274,6 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
   constexpr int NT = NWARPS * 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
-#ifdef B200LUT_GEMV_TRACE
-  unsigned long long* trace_row = dep.trace;
-#endif
   const size_t chunk_bytes = size_t(1024) * BITS;
   const size_t hop = chunk_bytes * NWARPS;            // bytes between a warp's consecutive chunks
   const uint8_t* lane_base = packed + (size_t(tile) * G) * chunk_bytes + lane * 32;
@@ -336,9 +316,7 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
         peer_poll(*dep.ex, i);
       __syncthreads();
     } else {
-      TRACE_STAMP(1)
       asm volatile("griddepcontrol.wait;" ::: "memory");
-      TRACE_STAMP(2)
     }
   }
   // x fragments ride the code ring: the rows of a chunk are requested RC chunks ahead of their
@@ -349,8 +327,6 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
     load_x<CP>(xf[u], x, ldx, (c + u * NWARPS < c1) ? M : 0, (c + u * NWARPS) * kChunkK, gid, tig);
   if (split_build) table_store_shfl<NT>(tbl_ptr, lutv, BITS, nl);
   __syncthreads();
-  TRACE_STAMP(3)
-
   float acc[P::kAcc][4];
 #pragma unroll
   for (int a = 0; a < P::kAcc; ++a)
@@ -376,10 +352,7 @@ __device__ __forceinline__ void stream_pass(float* part_plane, bool accumulate, 
   for (int a = 0; a < P::kAcc; ++a)
 #pragma unroll
     for (int r = 0; r < 4; ++r) asm volatile("" ::"f"(acc[a][r]));   // lookups end here
-  if (warp == 0) { TRACE_STAMP(4) }
   __syncthreads();   // all warps are done with the tables
-  TRACE_STAMP(5)
-
   // cross-warp fold, 8 batch columns at a time: red[warp][m & 7][row], fixed warp order
 #pragma unroll
   for (int nb = 0; nb < P::kNB; ++nb) {
@@ -558,22 +531,6 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
   const int nplanes = silu ? 2 : 1;
 
   asm volatile("griddepcontrol.launch_dependents;");
-#ifdef B200LUT_GEMV_TRACE
-  __shared__ unsigned long long* trace_row_s;
-  if (threadIdx.x == 0) {
-    trace_row_s = nullptr;
-    if (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) {
-      unsigned int id = 0;
-      if (blockIdx.x == 0) id = atomicAdd(&g_trace_launch, 1u);
-      else id = *reinterpret_cast<volatile unsigned int*>(&g_trace_launch);   // approximate pairing
-      const unsigned int slot = (blockIdx.x == 0 ? 2 * id : 2 * id + 1) % 8192;
-      trace_row_s = g_trace + size_t(slot) * 8;
-      trace_row_s[0] = trace_now();
-    }
-  }
-  __syncthreads();
-  unsigned long long* trace_row = trace_row_s;
-#endif
 
   const int M = p.M;
   bool first = true;
@@ -585,15 +542,10 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
       const uint16_t* lut = pass ? sg.lut2 : sg.lut;
       const int bits = pass ? sg.bits2 : sg.bits;
       float* dst = part + plane * kMaxM * kTileRows;
-#ifdef B200LUT_GEMV_TRACE
-#define TRACE_ARG , (first ? trace_row : nullptr)
-#else
-#define TRACE_ARG
-#endif
 #define B200LUT_PASS(B)                                                                       \
   stream_pass<T, B, CP, NWARPS, RC>(dst, pass != 0, tbl_ptr, tbl_addr, packed, lut, sg.n_groups,  \
                                     sg.gs, tile, p.G, c0, c1, p.x, p.ldx, M, !first,              \
-                                    DepWait{first ? 1 : 0, nullptr, 0, nullptr, (first && p.ex.wait) ? &p.ex : nullptr TRACE_ARG})
+                                    DepWait{first ? 1 : 0, nullptr, 0, nullptr, (first && p.ex.wait) ? &p.ex : nullptr})
       switch (bits) {   // block-uniform
         case 4: B200LUT_PASS(4); break;
         case 3: B200LUT_PASS(3); break;
@@ -604,10 +556,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) gemv_kernel(const GemvParams p
       first = false;
     }
   }
-  TRACE_STAMP(6)
   fold_and_store<T, NT>(p, part, si, tile, tile_g, sp);
-  TRACE_STAMP(7)
-
   if (p.ex.wait) {
     // The last block of a waiting grid counts the wait as done (every block read the count
     // when it polled, before it came here).
@@ -650,6 +599,7 @@ constexpr int kWarpsM8 = 16, kWarpsM16 = 8;
 }  // namespace b200lut
 
 #include "gemv_plan.cuh"
+#include "gemv_rows.cuh"
 
 namespace b200lut {
 namespace {
@@ -774,6 +724,140 @@ int dispatch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t st) {
   return launch<T, 16, kWarpsM16, 1>(p, max_tables, pdl, st);
 }
 
+
+template <typename T>
+int launch_rows(const RowsParams& p, const RowsGeom& g, bool pdl, cudaStream_t stream) {
+  auto kern = gemv_rows_kernel<T>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  B200LUT_REQUIRE(dev >= 0 && dev < 64, B200LUT_ERR_UNSUPPORTED, "device index %d not served", dev);
+  if (!configured[dev]) {
+    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared));
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(g.row_blocks * g.split), 1, 1);
+  cfg.blockDim = dim3(kRowsThreads, 1, 1);
+  cfg.dynamicSmemBytes = g.end_abs;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (g.split > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = unsigned(g.split);
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = unsigned(na);
+  B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
+  return B200LUT_OK;
+}
+
+int sm_count_cached();
+
+// Device address of the library's status word on the current device (looked up once per device).
+int* device_status_addr(int* rc) {
+  static int* status_addr[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    *rc = fail(B200LUT_ERR_UNSUPPORTED, "device index %d not served", dev);
+    return nullptr;
+  }
+  if (!status_addr[dev]) {
+    void* a = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&a, g_exchange_status);
+    if (e != cudaSuccess) {
+      *rc = fail(B200LUT_ERR_CUDA, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    status_addr[dev] = static_cast<int*>(a);
+  }
+  return status_addr[dev];
+}
+
+// Which decode kernel the library policy picks: the flag bits decide when set, else the
+// process-wide default (B200LUT_GEMV_KERNEL=rows|tile in the environment, read once).
+bool rows_kernel_wanted(int flags) {
+  if (flags & B200LUT_FLAG_TILE_KERNEL) return false;
+  if (flags & B200LUT_FLAG_ROWS_KERNEL) return true;
+  static const bool dflt = [] {
+    const char* e = getenv("B200LUT_GEMV_KERNEL");
+    return e != nullptr && e[0] == 'r';
+  }();
+  return dflt;
+}
+
+// The row-range kernel when it serves the launch (4-bit, one stream, M <= 8).
+template <typename T>
+int try_rows(const GemvParams& gp, const uint16_t* x2, int tiles, bool pdl, cudaStream_t st, bool* served) {
+  *served = false;
+  RowsGeom g;
+  const bool silu = gp.epilogue == B200LUT_EPI_SILU_MUL;
+  {
+    // The layout depends only on the segment geometry; it is planned once per distinct launch
+    // shape (the planner walks every 32-row unit) and looked up afterwards.
+    struct Entry { unsigned long long key; bool ok; RowsGeom g; };
+    static Entry cache[64];
+    static int used = 0;
+    static std::mutex mu;
+    unsigned long long h = 1469598103934665603ull;
+    auto mix = [&](unsigned long long v) { h = (h ^ v) * 1099511628211ull; };
+    mix(unsigned(gp.nseg)); mix(unsigned(gp.epilogue)); mix(unsigned(gp.M)); mix(unsigned(gp.K));
+    mix(unsigned(tiles)); mix(unsigned(sm_count_cached()));
+    for (int i = 0; i < gp.nseg; ++i) {
+      mix(unsigned(gp.seg[i].N)); mix(unsigned(gp.seg[i].gs)); mix(unsigned(gp.seg[i].n_groups));
+      mix(unsigned(gp.seg[i].bits)); mix(gp.seg[i].packed2 ? 1u : 0u);
+      mix(reinterpret_cast<unsigned long long>(gp.seg[i].lut));
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    int hit = -1;
+    for (int i = 0; i < used; ++i)
+      if (cache[i].key == h) { hit = i; break; }
+    if (hit < 0) {
+      hit = used < 64 ? used++ : int(h % 64);
+      cache[hit].key = h;
+      cache[hit].ok = rows_plan(gp.seg, gp.nseg, silu, tiles, gp.M, gp.K, sm_count_cached(), &cache[hit].g);
+    }
+    if (!cache[hit].ok) return B200LUT_OK;
+    g = cache[hit].g;
+  }
+  RowsParams p = {};
+  p.x = gp.x;
+  p.x2 = x2;
+  p.ldx = gp.ldx;
+  p.M = gp.M;
+  p.Mp = g.Mp;
+  p.K = gp.K;
+  p.G = gp.G;
+  p.nseg = gp.nseg;
+  p.epilogue = gp.epilogue;
+  p.units_total = g.units_total;
+  p.row_blocks = g.row_blocks;
+  p.split = g.split;
+  p.ntables = g.ntables;
+  p.red_planes = g.red_planes;
+  p.xs_abs = g.xs_abs;
+  p.red_abs = g.red_abs;
+  p.part_abs = g.part_abs;
+  int rc = B200LUT_OK;
+  p.status = device_status_addr(&rc);
+  if (rc) return rc;
+  for (int i = 0; i < gp.nseg; ++i) p.seg[i] = gp.seg[i];
+  p.ex = gp.ex;
+  *served = true;
+  return launch_rows<T>(p, g, pdl, st);
+}
+
 int sm_count_cached() {
   static int cached[64] = {0};
   int dev = 0;
@@ -817,15 +901,6 @@ using namespace b200lut;
 
 extern "C" int b200lut_sm_count(void) { return sm_count_cached(); }
 
-#ifdef B200LUT_GEMV_TRACE
-extern "C" int b200lut_gemv_trace(unsigned long long* out, int rows, unsigned int* launches) {
-  if (cudaMemcpyFromSymbol(out, g_trace, size_t(rows) * 64) != cudaSuccess) return 3;
-  if (cudaMemcpyFromSymbol(launches, g_trace_launch, 4) != cudaSuccess) return 3;
-  unsigned int zero = 0;
-  cudaMemcpyToSymbol(g_trace_launch, &zero, 4);
-  return 0;
-}
-#endif
 
 extern "C" int b200lut_gemv_pick_split(int tiles, int K) {
   if (tiles <= 0 || K <= 0) return 1;
@@ -889,16 +964,9 @@ int convert_exchange(const b200lut_exchange* ex, ExchangeDev* out) {
     out->wait_count = static_cast<uint32_t*>(ex->wait_count);
     out->wait = 1;
   }
-  static int* status_addr[64] = {nullptr};
-  int dev = 0;
-  B200LUT_CUDA_OK(cudaGetDevice(&dev));
-  B200LUT_REQUIRE(dev < 64, B200LUT_ERR_UNSUPPORTED, "device index %d not served", dev);
-  if (!status_addr[dev]) {
-    void* a = nullptr;
-    B200LUT_CUDA_OK(cudaGetSymbolAddress(&a, g_exchange_status));
-    status_addr[dev] = static_cast<int*>(a);
-  }
-  out->status = status_addr[dev];
+  int rc = B200LUT_OK;
+  out->status = b200lut::device_status_addr(&rc);
+  if (rc) return rc;
   return B200LUT_OK;
 }
 
@@ -945,6 +1013,17 @@ extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, i
   int tiles = 0, max_tables = 1;
   if (int rc = convert_segments(segs, nseg, silu, p.seg, &tiles, &max_tables)) return rc;
   p.tiles_total = tiles;
+  const bool pdl = (flags & B200LUT_FLAG_PDL) != 0;
+  cudaStream_t st = cudaStream_t(stream);
+  // Library policy (split == 0): the row-range kernel when it serves the shapes. An explicit
+  // split, B200LUT_FLAG_TILE_KERNEL or an exchange descriptor selects the tile x split kernel.
+  if (split <= 0 && rows_kernel_wanted(flags) && !p.ex.push && !p.ex.wait) {
+    bool served = false;
+    const int rc = dtype == B200LUT_BF16
+                       ? try_rows<__nv_bfloat16>(p, nullptr, tiles, pdl, st, &served)
+                       : try_rows<__half>(p, nullptr, tiles, pdl, st, &served);
+    if (rc || served) return rc;
+  }
   const int warps = M <= 8 ? kWarpsM8 : kWarpsM16;
   if (split <= 0) split = pick_split(tiles, p.G, sm_count_cached(), warps);
   B200LUT_REQUIRE(split >= 1 && split <= 16 && split <= p.G, B200LUT_ERR_INVALID,
@@ -964,11 +1043,10 @@ extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, i
   B200LUT_REQUIRE(!p.ex.push || p.ex.blocks == tiles * split, B200LUT_ERR_INVALID,
                   "exchange: producer_blocks is %d but this launch has %d tiles x split %d blocks",
                   p.ex.blocks, tiles, split);
-  const bool pdl = (flags & 1) != 0;
-  cudaStream_t st = cudaStream_t(stream);
   if (dtype == B200LUT_BF16) return dispatch<__nv_bfloat16>(p, max_tables, pdl, st);
   return dispatch<__half>(p, max_tables, pdl, st);
 }
+
 
 extern "C" int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out, int M,
                             int N, int K, int bits, int group_size, int n_groups, int dtype,
@@ -1151,6 +1229,38 @@ constexpr size_t kNoAllocTicketBytes = 4096;   // 1024 tiles
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 }  // namespace
 
+namespace {
+// Device address of the built-in scratch on the current device. The array's name is only a
+// host-side handle; kernels and memsets need the address behind it, looked up once per device
+// with that device current. Concurrent first calls from several host threads all store the same
+// value.
+int noalloc_scratch(unsigned char** out) {
+  static unsigned char* scratch_addr[64] = {nullptr};
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  B200LUT_REQUIRE(dev >= 0 && dev < 64, B200LUT_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  if (!scratch_addr[dev]) {
+    void* ptr = nullptr;
+    B200LUT_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    B200LUT_REQUIRE(ptr != nullptr, B200LUT_ERR_CUDA, "no device address for the built-in scratch");
+    scratch_addr[dev] = static_cast<unsigned char*>(ptr);
+  }
+  *out = scratch_addr[dev];
+  return B200LUT_OK;
+}
+}  // namespace
+
+// Zero the tickets of the built-in scratch (its first 4 KiB), stream-ordered. The tickets return to
+// zero by themselves at the end of every healthy launch; a launch that never finished (a sticky
+// CUDA error on the stream, a lost context) can leave some set, and every later call on those
+// tiles would then fold early. A host that has recovered from such an error calls this once.
+extern "C" int b200lut_gemv_noalloc_reset(void* stream) {
+  unsigned char* base = nullptr;
+  if (int rc = noalloc_scratch(&base)) return rc;
+  B200LUT_CUDA_OK(cudaMemsetAsync(base, 0, kNoAllocTicketBytes, cudaStream_t(stream)));
+  return B200LUT_OK;
+}
+
 extern "C" int b200lut_gemv_noalloc(const void* x, const void* packed, const void* lut, void* out,
                                     int M, int N, int K, int bits, int group_size, int n_groups,
                                     int dtype, int split, void* stream) {
@@ -1195,22 +1305,13 @@ extern "C" int b200lut_gemv_noalloc(const void* x, const void* packed, const voi
                   "has %zu (lower split, or use b200lut_gemv with a caller workspace)",
                   N, M, split, need, kNoAllocScratchBytes - kNoAllocTicketBytes);
 
-  // set-up, once per device, with that device current: the array's name is only a host-side
-  // handle; the kernel needs the device address behind it
-  static unsigned char* scratch_addr[64] = {nullptr};
-  int dev = 0;
-  B200LUT_CUDA_OK(cudaGetDevice(&dev));
-  B200LUT_REQUIRE(dev >= 0 && dev < 64, B200LUT_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-  if (!scratch_addr[dev]) {
-    void* ptr = nullptr;
-    B200LUT_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
-    B200LUT_REQUIRE(ptr != nullptr, B200LUT_ERR_CUDA, "no device address for the built-in scratch");
-    scratch_addr[dev] = static_cast<unsigned char*>(ptr);
-  }
+  // set-up, once per device, with that device current (see noalloc_scratch)
+  unsigned char* scratch = nullptr;
+  if (int rc = noalloc_scratch(&scratch)) return rc;
   p.split = split;
   p.cluster = 0;     // always the scratch fold: partials to the array, last arrival sums them
-  p.tickets = reinterpret_cast<int*>(scratch_addr[dev]);            // zero at load, self-resetting
-  p.ws = reinterpret_cast<float*>(scratch_addr[dev] + kNoAllocTicketBytes);   // fully rewritten per call
+  p.tickets = reinterpret_cast<int*>(scratch);            // zero at load, self-resetting
+  p.ws = reinterpret_cast<float*>(scratch + kNoAllocTicketBytes);   // fully rewritten per call
   cudaStream_t st = cudaStream_t(stream);
   if (dtype == B200LUT_BF16) return dispatch<__nv_bfloat16>(p, max_tables, false, st);
   return dispatch<__half>(p, max_tables, false, st);

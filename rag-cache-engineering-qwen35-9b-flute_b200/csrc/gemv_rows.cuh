@@ -1,0 +1,515 @@
+// Row-range decode GEMV (M <= 8, 4-bit codes, one code stream) for sm_100a.
+// Included by gemv.cu (shares the segment structs, the epilogue pieces and the exchange).
+//
+// Replaces, for the shapes it serves, the tile x K-split form of the kernel above (reference:
+// src/flute_extended/src/kernel_gemv.cu:92-253, kernel_gemv_splitk.cu:135-409,
+// kernel_gemv_multi.cu:101-334, kernel_gemv_mlp.cu:92-450).
+//
+// Why a second form. At 4 bits one 1 KB plane of a chunk holds 32 output rows x 64 k, so 32
+// rows over ALL of K are a stream of 1 KB pieces, 4 KB apart. A block here owns a contiguous
+// range of such 32-row units over the whole of K: nothing is folded across blocks, a launch
+// of N rows fills min(N / 32, SMs) SMs whatever N / 128 is, and the work per block is even
+// to within one unit. (K is only split, across a thread-block cluster folded through
+// distributed shared memory, when a launch has fewer units than half the SMs.)
+//
+// The block is small on purpose: 8 warps x 128 registers and about 80-95 KB of shared
+// memory, so TWO blocks fit on an SM. With programmatic dependent launch the blocks of the
+// next projection become resident while this one still computes, request their first 8 KB
+// of codes per warp, fetch their palettes and build their pair table, and only then wait for
+// this launch to finish: weight bytes stay in flight across the dependency.
+//
+// Per warp: a ring of eight 1 KB pieces in registers (one 256-bit load per lane each), refilled
+// piece by piece as soon as a piece's 32 lookups are done. A piece is 2 slabs x 4 k-steps:
+// 32 pair-table lookups (one byte permute + one ld.shared each) feed 8 mma.m16n8k16. The
+// activation rows are staged once per block in shared memory in B-fragment order; every n8
+// column of the accumulator carries batch row (column mod M'), M' = M rounded up to 1, 2, 4, 8,
+// so no select is spent on columns. Warps take k-chunks round-robin; their sums meet in shared
+// memory in warp order (deterministic), then bias / residual / SiLU*mul and ONE rounding.
+//
+// The pair table sits at a fixed shared-window address (kRowsTableAbs), so a lookup address is
+// the byte permute plus an immediate offset in the load — no 64 KB alignment of the block's
+// window is needed, which is what lets two blocks share an SM.
+#pragma once
+
+namespace b200lut {
+namespace {
+
+constexpr int kRowsWarps = 8;
+constexpr int kRowsThreads = kRowsWarps * 32;
+constexpr int kRowsRing = 8;            // 1 KB pieces in flight per warp
+constexpr int kUnitRows = 32;           // output rows of one 1 KB plane at 4 bits
+constexpr int kRowsMaxPlanes = 16;      // planes (units x streams) per block: one lane each
+constexpr int kRowsMaxSlots = 4;        // palettes a block can hold (two 64 KB tables)
+constexpr uint32_t kRowsTableAbs = 2048;   // offset of the first pair table inside the block's shared window
+constexpr uint32_t kRowsWindowMask = 0x3FFFFu;   // a block's shared window is smaller than 256 KB
+constexpr int kRowsStatusBadWindow = 0x5000;
+
+struct RowsParams {
+  const uint16_t* x;
+  const uint16_t* x2;      // non-null: the activation is silu(x) * x2 (both [M, ldx])
+  long long ldx;
+  int M, Mp, K, G, nseg, epilogue;
+  int units_total;         // 32-row units (pairs of units under the SiLU*mul epilogue)
+  int row_blocks, split, ntables, red_planes;
+  uint32_t xs_abs, red_abs, part_abs;    // offsets inside the block's shared window
+  int* status;
+  SegDev seg[kMaxSeg];
+  ExchangeDev ex;
+};
+
+__device__ __forceinline__ uint32_t lds32_tbl(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1+2048];" : "=r"(v) : "r"(addr));
+  return v;
+}
+static_assert(kRowsTableAbs == 2048, "the immediate in lds32_tbl is the table address");
+
+// Activation fragments out of shared memory. Not volatile (the scheduler may hoist it across
+// lookups); ordered against the staging barrier by the token every address carries.
+__device__ __forceinline__ void lds128(uint32_t (&r)[4], uint32_t addr) {
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+      : "r"(addr));
+}
+
+__device__ __forceinline__ unsigned long long shfl_u64(unsigned long long v, int src) {
+  return __shfl_sync(0xffffffffu, v, src);
+}
+
+// out = silu(g) * u on 8 packed 16-bit values, fp32 inside, one rounding
+template <typename T>
+__device__ __forceinline__ uint4 silu_mul8(uint4 g, uint4 u) {
+  uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w}, o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float g0 = DType<T>::to_float(uint16_t(gw[i] & 0xFFFFu)), g1 = DType<T>::to_float(uint16_t(gw[i] >> 16));
+    const float u0 = DType<T>::to_float(uint16_t(uw[i] & 0xFFFFu)), u1 = DType<T>::to_float(uint16_t(uw[i] >> 16));
+    const uint32_t lo = DType<T>::from_float(g0 / (1.f + __expf(-g0)) * u0);
+    const uint32_t hi = DType<T>::from_float(g1 / (1.f + __expf(-g1)) * u1);
+    o[i] = lo | (hi << 16);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Bias, residual, SiLU*mul, the one rounding, the store (and its mirrors on the peers).
+template <typename T>
+__device__ __forceinline__ void rows_finish(const RowsParams& p, int u, int m, int row, float a,
+                                            float b) {
+  const bool silu = p.epilogue == B200LUT_EPI_SILU_MUL;
+  const int step = silu ? 2 : 1;
+  int si = 0;
+  for (int s = 0; s < p.nseg; s += step)
+    if ((u >> 2) >= p.seg[s].tile_begin) si = s;
+  const SegDev& s0 = p.seg[si];
+  const int n = (u - 4 * s0.tile_begin) * kUnitRows + row;
+  if (s0.res_rank) a += residual_dot<T>(s0, m, n);
+  if (s0.bias) a += DType<T>::to_float(s0.bias[n]);
+  float v = a;
+  if (silu) {
+    const SegDev& s1 = p.seg[si + 1];
+    if (s1.res_rank) b += residual_dot<T>(s1, m, n);
+    if (s1.bias) b += DType<T>::to_float(s1.bias[n]);
+    v = a / (1.f + __expf(-a)) * b;
+  }
+  uint16_t* dst = s0.out + size_t(m) * s0.ldo + n;
+  const uint16_t bits16 = DType<T>::from_float(v);
+  *dst = bits16;
+  if (p.ex.push) {
+    for (int q = 0; q < p.ex.world; ++q)
+      if (q != p.ex.rank)
+        *reinterpret_cast<uint16_t*>(reinterpret_cast<char*>(dst) + p.ex.delta[q]) = bits16;
+  }
+}
+
+// One 1 KB piece: 2 slabs x 4 k-steps. The 16 lookups of a slab are issued before its four
+// mma so that the shared-memory latency is paid once per slab, not once per k-step.
+template <typename T>
+__device__ __forceinline__ void rows_item(float (&acc)[2][4], const uint32_t (&w)[8], uint32_t base,
+                                          uint32_t xs_addr) {
+  uint32_t xb[2][4];
+  lds128(xb[0], xs_addr);
+  lds128(xb[1], xs_addr + 16);
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    uint32_t a[4][4];
+#pragma unroll
+    for (int kt = 0; kt < 4; ++kt)
+#pragma unroll
+      for (int f = 0; f < 4; ++f)
+        a[kt][f] = lds32_tbl(__byte_perm(w[4 * s + kt], base, 0x7604u | (uint32_t(f) << 4)));
+#pragma unroll
+    for (int kt = 0; kt < 4; ++kt)
+      mma16816<T>(acc[s], a[kt], xb[kt >> 1][2 * (kt & 1)], xb[kt >> 1][2 * (kt & 1) + 1]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowsThreads, 2) gemv_rows_kernel(const __grid_constant__ RowsParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  constexpr int NW = kRowsWarps, NT = kRowsThreads, R = kRowsRing;
+  constexpr uint32_t kFull = 0xffffffffu;
+  constexpr unsigned long long kHop = (unsigned long long)(NW) * 4096ull;   // a warp's next chunk
+  // Shared-state-space addresses of this block: `win` is the start of its window (zero for a
+  // plain launch, the block's slice of the cluster window otherwise), `low` where the dynamic
+  // array starts inside it. Everything below sits at fixed offsets from `win`.
+  const uint32_t smem_abs = smem_u32(smem);
+  const uint32_t low = smem_abs & kRowsWindowMask, win = smem_abs - low;
+  // Never seen; reported instead of trusted. A block in this state does no work but still meets
+  // its cluster at the barriers below.
+  const bool bad_window = low > kRowsTableAbs;
+  if (bad_window && threadIdx.x == 0) atomicExch(p.status, kRowsStatusBadWindow);
+  auto generic = [&](uint32_t off) { return smem + (off - low); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int split = p.split;
+  const int rb = blockIdx.x / split, sp = blockIdx.x % split;
+  const int c0 = (p.G * sp) / split, c1 = (p.G * (sp + 1)) / split;
+  const int kc = c1 - c0;
+  const bool silu = p.epilogue == B200LUT_EPI_SILU_MUL;
+  const int ppu = silu ? 2 : 1;
+  const int u0 = int((long long)p.units_total * rb / p.row_blocks);
+  const int u1 = int((long long)p.units_total * (rb + 1) / p.row_blocks);
+  const int nplanes = bad_window ? 0 : (u1 - u0) * ppu;
+  const int M = p.M, Mp = p.Mp;
+
+  asm volatile("griddepcontrol.launch_dependents;");
+
+  // ---- plane j of the block lives in lane j of every warp -----------------------------------
+  unsigned long long my_ptr = 0, my_lut = 0;
+  const int which = silu ? (lane & 1) : 0;
+  if (lane < nplanes) {
+    const int u = u0 + lane / ppu;
+    int si = 0;
+    for (int s = 0; s < p.nseg; s += ppu)
+      if ((u >> 2) >= p.seg[s].tile_begin) si = s;
+    const SegDev& sg = p.seg[si + which];
+    const int lu = u - 4 * p.seg[si].tile_begin;
+    my_ptr = reinterpret_cast<unsigned long long>(
+        sg.packed + (size_t(lu >> 2) * p.G + c0 + warp) * 4096 + size_t(lu & 3) * 1024);
+    int grp = (lu * kUnitRows) / sg.gs;
+    if (grp > sg.n_groups - 1) grp = sg.n_groups - 1;
+    my_lut = reinterpret_cast<unsigned long long>(sg.lut + size_t(grp) * 16);
+  }
+
+  // ---- rounds: up to R consecutive chunks of one plane. The first round is requested now,
+  //      before anything else; afterwards slot j of the next round is requested as soon as
+  //      slot j of the current one has been looked up. -------------------------------------------
+  const int cnt = kc > warp ? (kc - warp + NW - 1) / NW : 0;    // this warp's chunks per plane
+  const unsigned long long lane_off = (unsigned long long)(lane) * 32ull;
+  uint32_t w[R][8];
+  int cur_plane = 0, cur_k = 0;
+  int cur_n = (cnt > 0 && nplanes > 0) ? (cnt < R ? cnt : R) : 0;
+  {
+    const uint8_t* first = reinterpret_cast<const uint8_t*>(shfl_u64(my_ptr, 0) + lane_off);
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[j][i] = 0u;
+      ldg_stream256_if(w[j], first + j * kHop, j < cur_n ? 1u : 0u);
+    }
+  }
+
+  // ---- palettes: one slot per run of planes that share a palette -------------------------------
+  const unsigned long long prev_lut = __shfl_up_sync(kFull, my_lut, ppu);
+  const bool change = lane < nplanes && (lane < ppu || prev_lut != my_lut);
+  const uint32_t m0 = __ballot_sync(kFull, change && which == 0);
+  const uint32_t m1 = __ballot_sync(kFull, change && which == 1);
+  const uint32_t upto = (2u << lane) - 1u;
+  const int my_slot = which ? __popc(m0) + __popc(m1 & upto) - 1 : __popc(m0 & upto) - 1;
+  const int nslots = __popc(m0) + __popc(m1);
+  uint32_t lutv[2] = {0u, 0u};
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int want = 2 * t + (lane >> 4);
+    unsigned long long lp = 0;
+#pragma unroll
+    for (int s = 2 * t; s < 2 * t + 2; ++s) {
+      const uint32_t owner = __ballot_sync(kFull, change && my_slot == s);
+      const unsigned long long v = shfl_u64(my_lut, owner ? __ffs(owner) - 1 : 0);
+      if (want == s) lp = v;
+    }
+    if (want < nslots) lutv[t] = uint32_t(__ldg(reinterpret_cast<const uint16_t*>(lp) + (lane & 15)));
+  }
+  // pair tables: entry e of slot s at table(s >> 1) + e * 256 + (s & 1) * 128 + 4 * lane
+  if (!bad_window) {
+    uint8_t* tbl = generic(kRowsTableAbs);
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int nsl = nslots - 2 * t < 2 ? nslots - 2 * t : 2;
+      if (nsl > 0) {   // block-uniform
+#pragma unroll
+        for (int k = 0; k < 4096 / NT; ++k) {
+          const int idx = threadIdx.x + k * NT;
+          if (idx < nsl * 2048) {   // warp-uniform
+            const int q = idx & 7, e = (idx >> 3) & 255, sl = idx >> 11;
+            const uint32_t lo = __shfl_sync(kFull, lutv[t], 16 * sl + (e & 15));
+            const uint32_t hi = __shfl_sync(kFull, lutv[t], 16 * sl + (e >> 4));
+            const uint32_t v = lo | (hi << 16);
+            *reinterpret_cast<uint4*>(tbl + size_t(t) * kTableBytes + e * 256 + sl * 128 + q * 16) =
+                make_uint4(v, v, v, v);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- the dependency: the previous kernel of the stream, or the peers' pushes ----------------
+  if (p.ex.wait) {
+    for (int i = int(threadIdx.x); i < p.ex.world * p.ex.blocks; i += NT) peer_poll(p.ex, i);
+    __syncthreads();
+  } else {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
+
+  // ---- activation rows of this block's K range into shared memory, B-fragment order:
+  //      element (chunk g, tig, kt, j) at g*128 + tig*32 + kt*8 + 2j bytes = x[64g + 16kt + 4tig + j]
+  if (!bad_window) {
+    uint8_t* xs = generic(p.xs_abs);
+    const int per_row = kc * 8;   // 16-byte pieces of one row
+    const int total = Mp * per_row;
+#pragma unroll 4
+    for (int idx = threadIdx.x; idx < total; idx += NT) {
+      const int m = idx / per_row, pc = idx - m * per_row;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (m < M) {
+        const size_t off = size_t(m) * p.ldx + size_t(c0) * kChunkK + size_t(pc) * 8;
+        v = __ldcg(reinterpret_cast<const uint4*>(p.x + off));
+        if (p.x2) v = silu_mul8<T>(v, __ldcg(reinterpret_cast<const uint4*>(p.x2 + off)));
+      }
+      const int g = pc >> 3, o = pc & 7, kt = o >> 1, tg = (o & 1) * 2;
+      uint8_t* dst = xs + (size_t(m) * kc + g) * 128 + tg * 32 + kt * 8;
+      *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
+      *reinterpret_cast<uint2*>(dst + 32) = make_uint2(v.z, v.w);
+    }
+  }
+  __syncthreads();   // tables and activation rows are in place
+
+  // ---- main loop ------------------------------------------------------------------------------
+  uint32_t token;   // defined after the barrier; part of every shared-memory address below
+  asm volatile("mov.u32 %0, 0;" : "=r"(token));
+  float acc[2][4];
+#pragma unroll
+  for (int s = 0; s < 2; ++s)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) acc[s][r] = 0.f;
+  float* red = reinterpret_cast<float*>(generic(p.red_abs));
+  const uint32_t xs_lane = token + win + p.xs_abs + uint32_t(gid & (Mp - 1)) * uint32_t(kc) * 128u +
+                           uint32_t(tig) * 32u + uint32_t(warp) * 128u;
+  auto slot_base = [&](int plane) {
+    const int sl = __shfl_sync(kFull, my_slot, plane & 31);
+    return token + win + uint32_t(lane) * 4u + uint32_t(sl & 1) * 128u + uint32_t(sl >> 1) * kTableBytes;
+  };
+  uint32_t base = slot_base(0);
+
+  while (cur_n > 0) {   // warp-uniform
+    // the round after this one
+    int nxt_plane = cur_plane, nxt_k = cur_k + cur_n;
+    if (nxt_k >= cnt) { nxt_k = 0; ++nxt_plane; }
+    int nxt_n = cnt - nxt_k < R ? cnt - nxt_k : R;
+    if (nxt_plane >= nplanes) nxt_n = 0;
+    const uint8_t* nxt_ptr = reinterpret_cast<const uint8_t*>(
+        shfl_u64(my_ptr, nxt_plane & 31) + lane_off + (unsigned long long)(nxt_k) * kHop);
+    const uint32_t xs_cur = xs_lane + uint32_t(cur_k) * uint32_t(NW * 128);
+    if (cur_n == R && nxt_n == R) {
+#pragma unroll
+      for (int j = 0; j < R; ++j) {
+        rows_item<T>(acc, w[j], base, xs_cur + uint32_t(j) * uint32_t(NW * 128));
+        ldg_stream256(w[j], nxt_ptr + j * kHop);
+      }
+    } else if (cur_n == R) {
+#pragma unroll
+      for (int j = 0; j < R; ++j) {
+        rows_item<T>(acc, w[j], base, xs_cur + uint32_t(j) * uint32_t(NW * 128));
+        ldg_stream256_if(w[j], nxt_ptr + j * kHop, j < nxt_n ? 1u : 0u);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < R; ++j) {
+        if (j < cur_n) rows_item<T>(acc, w[j], base, xs_cur + uint32_t(j) * uint32_t(NW * 128));
+        ldg_stream256_if(w[j], nxt_ptr + j * kHop, j < nxt_n ? 1u : 0u);
+      }
+    }
+    if (nxt_plane != cur_plane) {   // this warp's share of the plane is done
+#pragma unroll
+      for (int s = 0; s < 2; ++s)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int col = 2 * tig + (r & 1);
+          if (col < Mp)
+            red[((warp * p.red_planes + cur_plane) * Mp + col) * kUnitRows + 16 * s + gid + 8 * (r >> 1)] =
+                acc[s][r];
+          acc[s][r] = 0.f;
+        }
+      base = slot_base(nxt_plane);
+    }
+    cur_plane = nxt_plane;
+    cur_k = nxt_k;
+    cur_n = nxt_n;
+  }
+  __syncthreads();
+
+  // ---- fold the warps' sums (warp order), then the K parts of a cluster (rank order) -----------
+  const int nwa = kc < NW ? kc : NW;   // warps that held chunks
+  const int nu = nplanes / ppu;
+  const int total_out = nu * M * kUnitRows;
+  auto warp_sum = [&](int plane, int m, int row) {
+    float v = 0.f;
+    for (int wi = 0; wi < nwa; ++wi)
+      v += red[((wi * p.red_planes + plane) * Mp + m) * kUnitRows + row];
+    return v;
+  };
+  if (split == 1) {
+    for (int idx = threadIdx.x; idx < total_out; idx += NT) {
+      const int row = idx & 31, m = (idx >> 5) % M, ul = (idx >> 5) / M;
+      const float a = warp_sum(ul * ppu, m, row);
+      const float b = silu ? warp_sum(ul * ppu + 1, m, row) : 0.f;
+      rows_finish<T>(p, u0 + ul, m, row, a, b);
+    }
+  } else {
+    float* part = reinterpret_cast<float*>(generic(p.part_abs));   // [plane][m][row]
+    for (int idx = threadIdx.x; idx < nplanes * M * kUnitRows; idx += NT) {
+      const int row = idx & 31, m = (idx >> 5) % M, pl = (idx >> 5) / M;
+      part[idx] = warp_sum(pl, m, row);
+    }
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int rank = int(cluster.block_rank());
+    const int i0 = (total_out * rank) / split, i1 = (total_out * (rank + 1)) / split;
+    for (int idx = i0 + int(threadIdx.x); idx < i1; idx += NT) {
+      const int row = idx & 31, m = (idx >> 5) % M, ul = (idx >> 5) / M;
+      float a = 0.f, b = 0.f;
+      for (int q = 0; q < split; ++q) {   // fixed rank order = ascending k
+        const float* peer = cluster.map_shared_rank(part, q);
+        a += peer[((ul * ppu) * M + m) * kUnitRows + row];
+        if (silu) b += peer[((ul * ppu + 1) * M + m) * kUnitRows + row];
+      }
+      rows_finish<T>(p, u0 + ul, m, row, a, b);
+    }
+    cluster.sync();   // keep shared memory alive until every peer has read it
+  }
+
+  if (p.ex.wait) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t old = atomicAdd(p.ex.wait_ticket, 1u);
+      if (old == gridDim.x - 1) {
+        *reinterpret_cast<volatile uint32_t*>(p.ex.wait_ticket) = 0u;
+        *reinterpret_cast<volatile uint32_t*>(p.ex.wait_count) += 1u;
+      }
+    }
+  }
+  if (p.ex.push) {
+    // one system-wide fence per block, then this block's flag in every rank's flag array
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t e = *reinterpret_cast<volatile uint32_t*>(p.ex.epoch) + 1u;
+      __threadfence_system();
+      const uint32_t slot = uint32_t(p.ex.rank) * gridDim.x + blockIdx.x;
+      for (int q = 0; q < p.ex.world; ++q)
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.ex.peer_flag[q] + slot), "r"(e)
+                     : "memory");
+      const uint32_t old = atomicAdd(p.ex.ticket, 1u);
+      if (old == gridDim.x - 1) {
+        *reinterpret_cast<volatile uint32_t*>(p.ex.ticket) = 0u;
+        *reinterpret_cast<volatile uint32_t*>(p.ex.epoch) = e;
+      }
+    }
+  }
+}
+
+// ---- host side: geometry of a launch ------------------------------------------------------------
+
+struct RowsGeom {
+  int units_total, row_blocks, split, ntables, red_planes, Mp;
+  uint32_t xs_abs, red_abs, part_abs, end_abs;
+};
+
+// Palette slots the busiest block needs when `units` units are cut into `row_blocks` ranges
+// (the device assigns one slot per run of consecutive planes with the same palette, per stream).
+int rows_max_slots(const SegDev* seg, int nseg, bool silu, int units, int row_blocks) {
+  const int ppu = silu ? 2 : 1;
+  int worst = 0;
+  for (int rb = 0; rb < row_blocks; ++rb) {
+    const int u0 = int((long long)units * rb / row_blocks), u1 = int((long long)units * (rb + 1) / row_blocks);
+    int slots = 0;
+    for (int wh = 0; wh < ppu; ++wh) {
+      const void* prev = nullptr;
+      for (int u = u0; u < u1; ++u) {
+        int si = 0;
+        for (int s = 0; s < nseg; s += ppu)
+          if ((u >> 2) >= seg[s].tile_begin) si = s;
+        const SegDev& sg = seg[si + wh];
+        const int lu = u - 4 * seg[si].tile_begin;
+        int grp = (lu * kUnitRows) / sg.gs;
+        if (grp > sg.n_groups - 1) grp = sg.n_groups - 1;
+        const void* key = sg.lut + size_t(grp) * 16;
+        if (u == u0 || key != prev) ++slots;
+        prev = key;
+      }
+    }
+    if (slots > worst) worst = slots;
+  }
+  return worst;
+}
+
+// Decide whether the row-range kernel serves this launch and lay it out. Returns false when the
+// tile x split kernel has to run (other code widths, a second stream, M > 8, a K range whose
+// activation rows do not fit in shared memory).
+bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, int K, int sms,
+               RowsGeom* g) {
+  if (M < 1 || M > 8) return false;
+  for (int i = 0; i < nseg; ++i)
+    if (seg[i].bits != 4 || seg[i].packed2 != nullptr || seg[i].gs < kUnitRows) return false;
+  const int ppu = silu ? 2 : 1;
+  const int Mp = M == 1 ? 1 : (M == 2 ? 2 : (M <= 4 ? 4 : 8));
+  const int G = K / kChunkK;
+  const int U = tiles_total * 4;
+  int cap_planes = 32 / Mp;                       // fold buffer <= 32 KB
+  if (cap_planes > kRowsMaxPlanes) cap_planes = kRowsMaxPlanes;
+  const int upb_max = cap_planes / ppu;
+  if (upb_max < 1) return false;
+  int split = 1, row_blocks, slots;
+  if (U > sms) {
+    // One block per SM, or a multiple of that when a block would otherwise span more than two
+    // palettes (one 64 KB table; two such blocks fit on an SM) or more planes than the fold
+    // buffer holds.
+    row_blocks = 0;
+    slots = 0;
+    int fallback = 0, fallback_slots = 0;
+    for (int k = 1; k * sms <= U; ++k) {
+      const int rbk = k * sms;
+      if ((U + rbk - 1) / rbk > upb_max) continue;
+      const int sl = rows_max_slots(seg, nseg, silu, U, rbk);
+      if (!fallback && sl <= kRowsMaxSlots) { fallback = rbk; fallback_slots = sl; }
+      if (sl <= 2) { row_blocks = rbk; slots = sl; break; }
+    }
+    if (!row_blocks) { row_blocks = fallback; slots = fallback_slots; }
+    if (!row_blocks) { row_blocks = U; slots = ppu; }
+  } else if (2 * U > sms) {
+    row_blocks = U;
+    slots = ppu;
+  } else {
+    row_blocks = U;
+    slots = ppu;
+    split = sms / U;
+    if (split > kMaxClusterSplit) split = kMaxClusterSplit;
+    if (split > G) split = G;
+    if (split < 1) split = 1;
+  }
+  g->units_total = U;
+  g->row_blocks = row_blocks;
+  g->split = split;
+  g->ntables = slots > 2 ? 2 : 1;
+  g->Mp = Mp;
+  g->red_planes = ((U + row_blocks - 1) / row_blocks) * ppu;
+  const int kc_max = (G + split - 1) / split;
+  g->xs_abs = kRowsTableAbs + uint32_t(g->ntables) * kTableBytes;
+  g->red_abs = g->xs_abs + uint32_t(Mp) * uint32_t(kc_max) * 128u;
+  g->part_abs = g->red_abs + uint32_t(kRowsWarps) * uint32_t(g->red_planes) * uint32_t(Mp) * 128u;
+  g->end_abs = g->part_abs + (split > 1 ? uint32_t(g->red_planes) * uint32_t(Mp) * 128u : 0u);
+  return g->end_abs <= 227u * 1024u;
+}
+
+}  // namespace
+}  // namespace b200lut

@@ -51,6 +51,45 @@ def test_noalloc_matches_the_ordinary_entry_twice(N, K, bits, M, split):
     assert torch.equal(first, second)
 
 
+def test_noalloc_different_shapes_back_to_back_and_reset():
+    """Calls of different shapes share the one built-in array: tickets of the first shape must
+    be back at zero when the second shape uses the same words, un-split calls (split 1) use no
+    scratch at all, a side stream works like the default one, and the reset entry (what a host
+    calls after it has recovered from a launch that never finished) leaves the array usable."""
+    cases = [(Case(1024, 2048, 128, 4, torch.bfloat16, seed=11), 1, 4),
+             (Case(512, 1024, 64, 4, torch.float16, seed=12), 3, 8),
+             (Case(2048, 1024, 128, 4, torch.bfloat16, seed=13), 2, 1),
+             (Case(1024, 2048, 128, 4, torch.bfloat16, seed=11), 1, 16)]
+    prepared = []
+    for case, M, split in cases:
+        mod = case.module()
+        mod._ensure_packed()
+        x = case.x(M).cuda()
+        ws = None
+        if L.gemv_workspace_bytes(case.N, M, split):
+            ws = torch.zeros(L.gemv_workspace_bytes(case.N, M, split), dtype=torch.uint8, device="cuda")
+        want = torch.empty(M, case.N, dtype=x.dtype, device="cuda")
+        L.check(L.lib().b200lut_gemv(x.data_ptr(), mod._packed.data_ptr(), mod.lut.data_ptr(),
+                                     want.data_ptr(), M, case.N, case.K, case.bits, case.gs,
+                                     mod.lut.shape[0], L.dtype_id(x.dtype), split,
+                                     None if ws is None else ws.data_ptr(),
+                                     0 if ws is None else ws.numel(), None))
+        prepared.append((case, mod, x, split, want))
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    for rounds in range(2):
+        for case, mod, x, split, want in prepared:
+            got = _call(True, case, mod, x, split)
+            assert rel_err(got, case.oracle(x.cpu())) <= TOL
+            assert rel_err(got, want) <= TOL
+        with torch.cuda.stream(side):
+            case, mod, x, split, want = prepared[rounds]
+            got = _call(True, case, mod, x, split)
+            assert rel_err(got, want) <= TOL
+        L.check(L.lib().b200lut_gemv_noalloc_reset(None))
+        torch.cuda.synchronize()
+
+
 def test_noalloc_refuses_what_its_scratch_cannot_hold():
     case = Case(128, 64, 128, 4, torch.bfloat16, seed=1)
     mod = case.module()
