@@ -44,7 +44,9 @@ enum {
                                     fetch, table build) runs before the launch waits for it */
   B200LUT_FLAG_TILE_KERNEL = 2,  /* decode GEMV: run the tile x K-split kernel */
   B200LUT_FLAG_ROWS_KERNEL = 4   /* decode GEMV: run the row-range kernel where it serves the shapes
-                                    (4-bit codes, one stream, M <= 8, split = 0) */
+                                    (4-bit codes, one stream, M <= 8, split = 0, no exchange). It
+                                    is the library's choice for those shapes anyway, unless the
+                                    process runs with B200LUT_GEMV_KERNEL=tile */
 };
 
 /* Epilogue selector of b200lut_gemv_multi / b200lut_gemm. */

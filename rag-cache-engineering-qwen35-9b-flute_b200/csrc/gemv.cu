@@ -725,17 +725,15 @@ int dispatch(const GemvParams& p, int max_tables, bool pdl, cudaStream_t st) {
 }
 
 
-template <typename T>
-int launch_rows(const RowsParams& p, const RowsGeom& g, bool pdl, cudaStream_t stream) {
-  auto kern = gemv_rows_kernel<T>;
+template <typename T, bool XREG>
+int launch_rows_as(const RowsParams& p, const RowsGeom& g, bool pdl, cudaStream_t stream) {
+  auto kern = gemv_rows_kernel<T, XREG>;
   static bool configured[64] = {false};
   int dev = 0;
   B200LUT_CUDA_OK(cudaGetDevice(&dev));
   B200LUT_REQUIRE(dev >= 0 && dev < 64, B200LUT_ERR_UNSUPPORTED, "device index %d not served", dev);
   if (!configured[dev]) {
     B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                         cudaSharedmemCarveoutMaxShared));
     configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -763,6 +761,11 @@ int launch_rows(const RowsParams& p, const RowsGeom& g, bool pdl, cudaStream_t s
   return B200LUT_OK;
 }
 
+template <typename T>
+int launch_rows(const RowsParams& p, const RowsGeom& g, bool pdl, cudaStream_t stream) {
+  return g.xreg ? launch_rows_as<T, true>(p, g, pdl, stream) : launch_rows_as<T, false>(p, g, pdl, stream);
+}
+
 int sm_count_cached();
 
 // Device address of the library's status word on the current device (looked up once per device).
@@ -786,13 +789,14 @@ int* device_status_addr(int* rc) {
 }
 
 // Which decode kernel the library policy picks: the flag bits decide when set, else the
-// process-wide default (B200LUT_GEMV_KERNEL=rows|tile in the environment, read once).
+// process-wide default — the row-range kernel, unless B200LUT_GEMV_KERNEL=tile is in the
+// environment (read once).
 bool rows_kernel_wanted(int flags) {
   if (flags & B200LUT_FLAG_TILE_KERNEL) return false;
   if (flags & B200LUT_FLAG_ROWS_KERNEL) return true;
   static const bool dflt = [] {
     const char* e = getenv("B200LUT_GEMV_KERNEL");
-    return e != nullptr && e[0] == 'r';
+    return !(e != nullptr && e[0] == 't');
   }();
   return dflt;
 }

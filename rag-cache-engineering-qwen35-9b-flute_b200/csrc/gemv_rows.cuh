@@ -12,31 +12,32 @@
 // to within one unit. (K is only split, across a thread-block cluster folded through
 // distributed shared memory, when a launch has fewer units than half the SMs.)
 //
-// The block is small on purpose: 8 warps x 128 registers and about 80-95 KB of shared
-// memory, so TWO blocks fit on an SM. With programmatic dependent launch the blocks of the
-// next projection become resident while this one still computes, request their first 8 KB
-// of codes per warp, fetch their palettes and build their pair table, and only then wait for
-// this launch to finish: weight bytes stay in flight across the dependency.
+// One block of 16 warps per SM. Per warp: a ring of four 1 KB pieces in registers (one 256-bit
+// load per lane each); slot j of the next round is requested as soon as slot j of the current one
+// has been looked up. A piece is 2 slabs x 4 k-steps: 32 pair-table lookups (one byte permute +
+// one ld.shared each, the 16 of a slab issued back to back) feed 8 mma.m16n8k16. Warps take
+// k-chunks round-robin, so when the block's K range is 64 chunks (K = 4096) a warp's slot j is
+// always its chunk j and its activation fragments stay in registers for the whole launch;
+// otherwise they are read per piece from the rows staged in shared memory. Every n8 column of the
+// accumulator carries batch row (column mod M'), M' = M rounded up to 1, 2, 4, 8, so no select
+// is spent on columns. The warps' sums meet in shared memory in warp order (deterministic), then
+// bias / residual / SiLU*mul and ONE rounding.
 //
-// Per warp: a ring of eight 1 KB pieces in registers (one 256-bit load per lane each), refilled
-// piece by piece as soon as a piece's 32 lookups are done. A piece is 2 slabs x 4 k-steps:
-// 32 pair-table lookups (one byte permute + one ld.shared each) feed 8 mma.m16n8k16. The
-// activation rows are staged once per block in shared memory in B-fragment order; every n8
-// column of the accumulator carries batch row (column mod M'), M' = M rounded up to 1, 2, 4, 8,
-// so no select is spent on columns. Warps take k-chunks round-robin; their sums meet in shared
-// memory in warp order (deterministic), then bias / residual / SiLU*mul and ONE rounding.
+// Prologue, in the order that matters under programmatic dependent launch: every warp requests
+// its first round of codes; then half of the warps fetch the palettes and write the pair tables
+// while the other half waits for the previous kernel and stages the activation rows, so the two
+// memory round trips overlap each other and the code fetch.
 //
-// The pair table sits at a fixed shared-window address (kRowsTableAbs), so a lookup address is
-// the byte permute plus an immediate offset in the load — no 64 KB alignment of the block's
-// window is needed, which is what lets two blocks share an SM.
+// The pair table sits at a fixed offset of the block's shared window (kRowsTableAbs), so a lookup
+// address is the byte permute plus an immediate offset in the load; no 64 KB alignment is needed.
 #pragma once
 
 namespace b200lut {
 namespace {
 
-constexpr int kRowsWarps = 8;
+constexpr int kRowsWarps = 16;
 constexpr int kRowsThreads = kRowsWarps * 32;
-constexpr int kRowsRing = 8;            // 1 KB pieces in flight per warp
+constexpr int kRowsRing = 4;            // 1 KB pieces in flight per warp
 constexpr int kUnitRows = 32;           // output rows of one 1 KB plane at 4 bits
 constexpr int kRowsMaxPlanes = 16;      // planes (units x streams) per block: one lane each
 constexpr int kRowsMaxSlots = 4;        // palettes a block can hold (two 64 KB tables)
@@ -125,10 +126,7 @@ __device__ __forceinline__ void rows_finish(const RowsParams& p, int u, int m, i
 // mma so that the shared-memory latency is paid once per slab, not once per k-step.
 template <typename T>
 __device__ __forceinline__ void rows_item(float (&acc)[2][4], const uint32_t (&w)[8], uint32_t base,
-                                          uint32_t xs_addr) {
-  uint32_t xb[2][4];
-  lds128(xb[0], xs_addr);
-  lds128(xb[1], xs_addr + 16);
+                                          const uint32_t (&xb)[2][4]) {
 #pragma unroll
   for (int s = 0; s < 2; ++s) {
     uint32_t a[4][4];
@@ -143,8 +141,20 @@ __device__ __forceinline__ void rows_item(float (&acc)[2][4], const uint32_t (&w
   }
 }
 
+// The same with the activation fragments fetched from the staged rows in shared memory.
 template <typename T>
-__global__ void __launch_bounds__(kRowsThreads, 2) gemv_rows_kernel(const __grid_constant__ RowsParams p) {
+__device__ __forceinline__ void rows_item_smem(float (&acc)[2][4], const uint32_t (&w)[8],
+                                               uint32_t base, uint32_t xs_addr) {
+  uint32_t xb[2][4];
+  lds128(xb[0], xs_addr);
+  lds128(xb[1], xs_addr + 16);
+  rows_item<T>(acc, w, base, xb);
+}
+
+// XREG: the block's K range is exactly kRowsWarps * kRowsRing chunks, so a warp's ring slot j is
+// always its chunk j and the warp keeps the activation fragments of its chunks in registers.
+template <typename T, bool XREG>
+__global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid_constant__ RowsParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   constexpr int NW = kRowsWarps, NT = kRowsThreads, R = kRowsRing;
   constexpr uint32_t kFull = 0xffffffffu;
@@ -218,69 +228,77 @@ __global__ void __launch_bounds__(kRowsThreads, 2) gemv_rows_kernel(const __grid
   const uint32_t upto = (2u << lane) - 1u;
   const int my_slot = which ? __popc(m0) + __popc(m1 & upto) - 1 : __popc(m0 & upto) - 1;
   const int nslots = __popc(m0) + __popc(m1);
-  uint32_t lutv[2] = {0u, 0u};
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int want = 2 * t + (lane >> 4);
-    unsigned long long lp = 0;
-#pragma unroll
-    for (int s = 2 * t; s < 2 * t + 2; ++s) {
-      const uint32_t owner = __ballot_sync(kFull, change && my_slot == s);
-      const unsigned long long v = shfl_u64(my_lut, owner ? __ffs(owner) - 1 : 0);
-      if (want == s) lp = v;
-    }
-    if (want < nslots) lutv[t] = uint32_t(__ldg(reinterpret_cast<const uint16_t*>(lp) + (lane & 15)));
-  }
-  // pair tables: entry e of slot s at table(s >> 1) + e * 256 + (s & 1) * 128 + 4 * lane
-  if (!bad_window) {
-    uint8_t* tbl = generic(kRowsTableAbs);
+
+  // The lower half of the warps fetches the palettes and writes the pair tables while the upper
+  // half waits for the producer of the activation rows and stages them: the two round trips
+  // (palette entries from DRAM, activations from L2) run side by side.
+  if (warp < NW / 2) {
+    constexpr int NTB = NT / 2;   // threads that build
+    uint32_t lutv[2] = {0u, 0u};
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
-      const int nsl = nslots - 2 * t < 2 ? nslots - 2 * t : 2;
-      if (nsl > 0) {   // block-uniform
+      const int want = 2 * t + (lane >> 4);
+      unsigned long long lp = 0;
 #pragma unroll
-        for (int k = 0; k < 4096 / NT; ++k) {
-          const int idx = threadIdx.x + k * NT;
-          if (idx < nsl * 2048) {   // warp-uniform
-            const int q = idx & 7, e = (idx >> 3) & 255, sl = idx >> 11;
-            const uint32_t lo = __shfl_sync(kFull, lutv[t], 16 * sl + (e & 15));
-            const uint32_t hi = __shfl_sync(kFull, lutv[t], 16 * sl + (e >> 4));
-            const uint32_t v = lo | (hi << 16);
-            *reinterpret_cast<uint4*>(tbl + size_t(t) * kTableBytes + e * 256 + sl * 128 + q * 16) =
-                make_uint4(v, v, v, v);
+      for (int s = 2 * t; s < 2 * t + 2; ++s) {
+        const uint32_t owner = __ballot_sync(kFull, change && my_slot == s);
+        const unsigned long long v = shfl_u64(my_lut, owner ? __ffs(owner) - 1 : 0);
+        if (want == s) lp = v;
+      }
+      if (want < nslots) lutv[t] = uint32_t(__ldg(reinterpret_cast<const uint16_t*>(lp) + (lane & 15)));
+    }
+    // pair tables: entry e of slot s at table(s >> 1) + e * 256 + (s & 1) * 128 + 4 * lane
+    if (!bad_window) {
+      uint8_t* tbl = generic(kRowsTableAbs);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int nsl = nslots - 2 * t < 2 ? nslots - 2 * t : 2;
+        if (nsl > 0) {   // block-uniform
+#pragma unroll
+          for (int k = 0; k < 4096 / NTB; ++k) {
+            const int idx = threadIdx.x + k * NTB;
+            if (idx < nsl * 2048) {   // warp-uniform
+              const int q = idx & 7, e = (idx >> 3) & 255, sl = idx >> 11;
+              const uint32_t lo = __shfl_sync(kFull, lutv[t], 16 * sl + (e & 15));
+              const uint32_t hi = __shfl_sync(kFull, lutv[t], 16 * sl + (e >> 4));
+              const uint32_t v = lo | (hi << 16);
+              *reinterpret_cast<uint4*>(tbl + size_t(t) * kTableBytes + e * 256 + sl * 128 + q * 16) =
+                  make_uint4(v, v, v, v);
+            }
           }
         }
       }
     }
-  }
-
-  // ---- the dependency: the previous kernel of the stream, or the peers' pushes ----------------
-  if (p.ex.wait) {
-    for (int i = int(threadIdx.x); i < p.ex.world * p.ex.blocks; i += NT) peer_poll(p.ex, i);
-    __syncthreads();
   } else {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-  }
-
-  // ---- activation rows of this block's K range into shared memory, B-fragment order:
-  //      element (chunk g, tig, kt, j) at g*128 + tig*32 + kt*8 + 2j bytes = x[64g + 16kt + 4tig + j]
-  if (!bad_window) {
-    uint8_t* xs = generic(p.xs_abs);
-    const int per_row = kc * 8;   // 16-byte pieces of one row
-    const int total = Mp * per_row;
+    constexpr int NTS = NT / 2;   // threads that stage
+    const int tid = int(threadIdx.x) - NTS;
+    // the dependency: the previous kernel of the stream, or the peers' pushes
+    if (p.ex.wait) {
+      for (int i = tid; i < p.ex.world * p.ex.blocks; i += NTS) peer_poll(p.ex, i);
+      asm volatile("bar.sync 1, %0;" ::"n"(NTS) : "memory");
+    } else {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+    // activation rows of this block's K range into shared memory, B-fragment order:
+    // element (chunk g, tig, kt, j) at g*128 + tig*32 + kt*8 + 2j bytes = x[64g + 16kt + 4tig + j]
+    if (!bad_window) {
+      uint8_t* xs = generic(p.xs_abs);
+      const int per_row = kc * 8;   // 16-byte pieces of one row
+      const int total = Mp * per_row;
 #pragma unroll 4
-    for (int idx = threadIdx.x; idx < total; idx += NT) {
-      const int m = idx / per_row, pc = idx - m * per_row;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (m < M) {
-        const size_t off = size_t(m) * p.ldx + size_t(c0) * kChunkK + size_t(pc) * 8;
-        v = __ldcg(reinterpret_cast<const uint4*>(p.x + off));
-        if (p.x2) v = silu_mul8<T>(v, __ldcg(reinterpret_cast<const uint4*>(p.x2 + off)));
+      for (int idx = tid; idx < total; idx += NTS) {
+        const int m = idx / per_row, pc = idx - m * per_row;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (m < M) {
+          const size_t off = size_t(m) * p.ldx + size_t(c0) * kChunkK + size_t(pc) * 8;
+          v = __ldcg(reinterpret_cast<const uint4*>(p.x + off));
+          if (p.x2) v = silu_mul8<T>(v, __ldcg(reinterpret_cast<const uint4*>(p.x2 + off)));
+        }
+        const int g = pc >> 3, o = pc & 7, kt = o >> 1, tg = (o & 1) * 2;
+        uint8_t* dst = xs + (size_t(m) * kc + g) * 128 + tg * 32 + kt * 8;
+        *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
+        *reinterpret_cast<uint2*>(dst + 32) = make_uint2(v.z, v.w);
       }
-      const int g = pc >> 3, o = pc & 7, kt = o >> 1, tg = (o & 1) * 2;
-      uint8_t* dst = xs + (size_t(m) * kc + g) * 128 + tg * 32 + kt * 8;
-      *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
-      *reinterpret_cast<uint2*>(dst + 32) = make_uint2(v.z, v.w);
     }
   }
   __syncthreads();   // tables and activation rows are in place
@@ -301,6 +319,14 @@ __global__ void __launch_bounds__(kRowsThreads, 2) gemv_rows_kernel(const __grid
     return token + win + uint32_t(lane) * 4u + uint32_t(sl & 1) * 128u + uint32_t(sl >> 1) * kTableBytes;
   };
   uint32_t base = slot_base(0);
+  uint32_t xr[XREG ? R : 1][2][4];
+  if (XREG) {
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      lds128(xr[j][0], xs_lane + uint32_t(j) * uint32_t(NW * 128));
+      lds128(xr[j][1], xs_lane + uint32_t(j) * uint32_t(NW * 128) + 16);
+    }
+  }
 
   while (cur_n > 0) {   // warp-uniform
     // the round after this one
@@ -311,22 +337,33 @@ __global__ void __launch_bounds__(kRowsThreads, 2) gemv_rows_kernel(const __grid
     const uint8_t* nxt_ptr = reinterpret_cast<const uint8_t*>(
         shfl_u64(my_ptr, nxt_plane & 31) + lane_off + (unsigned long long)(nxt_k) * kHop);
     const uint32_t xs_cur = xs_lane + uint32_t(cur_k) * uint32_t(NW * 128);
-    if (cur_n == R && nxt_n == R) {
+    if (XREG) {   // every round is a whole plane: cur_n == R
+      if (nxt_n == R) {
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+          rows_item<T>(acc, w[j], base, xr[j]);
+          ldg_stream256(w[j], nxt_ptr + j * kHop);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < R; ++j) rows_item<T>(acc, w[j], base, xr[j]);
+      }
+    } else if (cur_n == R && nxt_n == R) {
 #pragma unroll
       for (int j = 0; j < R; ++j) {
-        rows_item<T>(acc, w[j], base, xs_cur + uint32_t(j) * uint32_t(NW * 128));
+        rows_item_smem<T>(acc, w[j], base, xs_cur + uint32_t(j) * uint32_t(NW * 128));
         ldg_stream256(w[j], nxt_ptr + j * kHop);
       }
     } else if (cur_n == R) {
 #pragma unroll
       for (int j = 0; j < R; ++j) {
-        rows_item<T>(acc, w[j], base, xs_cur + uint32_t(j) * uint32_t(NW * 128));
+        rows_item_smem<T>(acc, w[j], base, xs_cur + uint32_t(j) * uint32_t(NW * 128));
         ldg_stream256_if(w[j], nxt_ptr + j * kHop, j < nxt_n ? 1u : 0u);
       }
     } else {
 #pragma unroll
       for (int j = 0; j < R; ++j) {
-        if (j < cur_n) rows_item<T>(acc, w[j], base, xs_cur + uint32_t(j) * uint32_t(NW * 128));
+        if (j < cur_n) rows_item_smem<T>(acc, w[j], base, xs_cur + uint32_t(j) * uint32_t(NW * 128));
         ldg_stream256_if(w[j], nxt_ptr + j * kHop, j < nxt_n ? 1u : 0u);
       }
     }
@@ -421,7 +458,7 @@ __global__ void __launch_bounds__(kRowsThreads, 2) gemv_rows_kernel(const __grid
 // ---- host side: geometry of a launch ------------------------------------------------------------
 
 struct RowsGeom {
-  int units_total, row_blocks, split, ntables, red_planes, Mp;
+  int units_total, row_blocks, split, ntables, red_planes, Mp, xreg;
   uint32_t xs_abs, red_abs, part_abs, end_abs;
 };
 
@@ -471,20 +508,16 @@ bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, i
   if (upb_max < 1) return false;
   int split = 1, row_blocks, slots;
   if (U > sms) {
-    // One block per SM, or a multiple of that when a block would otherwise span more than two
-    // palettes (one 64 KB table; two such blocks fit on an SM) or more planes than the fold
-    // buffer holds.
+    // One block per SM, or the next multiple of that whose blocks fit the palette slots and
+    // the fold buffer.
     row_blocks = 0;
     slots = 0;
-    int fallback = 0, fallback_slots = 0;
-    for (int k = 1; k * sms <= U; ++k) {
+    for (int k = 1; k * sms <= U && !row_blocks; ++k) {
       const int rbk = k * sms;
       if ((U + rbk - 1) / rbk > upb_max) continue;
       const int sl = rows_max_slots(seg, nseg, silu, U, rbk);
-      if (!fallback && sl <= kRowsMaxSlots) { fallback = rbk; fallback_slots = sl; }
-      if (sl <= 2) { row_blocks = rbk; slots = sl; break; }
+      if (sl <= kRowsMaxSlots) { row_blocks = rbk; slots = sl; }
     }
-    if (!row_blocks) { row_blocks = fallback; slots = fallback_slots; }
     if (!row_blocks) { row_blocks = U; slots = ppu; }
   } else if (2 * U > sms) {
     row_blocks = U;
@@ -502,6 +535,7 @@ bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, i
   g->split = split;
   g->ntables = slots > 2 ? 2 : 1;
   g->Mp = Mp;
+  g->xreg = (G % split == 0 && G / split == kRowsWarps * kRowsRing) ? 1 : 0;
   g->red_planes = ((U + row_blocks - 1) / row_blocks) * ppu;
   const int kc_max = (G + split - 1) / split;
   g->xs_abs = kRowsTableAbs + uint32_t(g->ntables) * kTableBytes;

@@ -1,0 +1,125 @@
+"""GPU parity of the row-range decode GEMV (4-bit codes, M <= 8), selected with
+B200LUT_FLAG_ROWS_KERNEL, against the CPU oracle and against the tile x K-split kernel.
+
+Same bar as test_gpu_gemv: outputs within max |got - want| / max |want| <= 1e-2 (16-bit output,
+fp32 accumulate); dequantised weights BIT-EXACT through one-hot activations; results
+deterministic run to run. Shapes cover: one unit per block, several units and two palettes per
+block, ranges that cross a segment boundary of a merged launch, the K split over a thread-block
+cluster (few rows), K ranges that are and are not 64 chunks long (activation fragments in
+registers / read from shared memory), ragged chunk counts, every batch size 1..8, both dtypes."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, Case, pkg, rel_err
+from oracle import lut_linear_oracle as orc
+
+pytestmark = pytest.mark.gpu
+L = pkg._lib
+ROWS, TILE = L.FLAG_ROWS_KERNEL, L.FLAG_TILE_KERNEL
+
+
+def _run(case, x, flags, mod=None):
+    mod = mod or case.module()
+    mod._ensure_packed()
+    out = torch.full((x.shape[0], case.N), float("nan"), dtype=x.dtype, device="cuda")
+    segs = L.make_segments([mod._segment_desc(out)])
+    L.gemv_multi(x.cuda(), segs, 1, flags=flags)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("N,K,gs,dtype,M", (
+    (128, 64, 128, torch.bfloat16, 1),          # one chunk: fifteen idle warps
+    (256, 256, 128, torch.bfloat16, 1),         # K split over a cluster of four
+    (512, 1024, 32, torch.float16, 5),          # one palette per unit
+    (1024, 4096, 64, torch.bfloat16, 8),        # 64 chunks: fragments in registers, M' = 8
+    (4096, 4096, 128, torch.bfloat16, 1),       # the single-projection configuration
+    (4096, 4096, 128, torch.float16, 1),
+    (12288, 4096, 128, torch.bfloat16, 1),      # two or three units per block
+    (12288, 4096, 64, torch.bfloat16, 2),       # up to three palettes per block
+    (2048, 12288, 128, torch.bfloat16, 1),      # down-projection K: three rounds per unit
+    (4096, 12288, 128, torch.bfloat16, 4),
+    (640, 1856, 128, torch.bfloat16, 3),        # 29 chunks: ragged rounds, idle ring slots
+    (9600, 2048, 128, torch.float16, 7),        # 32 chunks: half rounds
+    (1024, 8192, 128, torch.bfloat16, 6),       # two full rounds per unit
+))
+def test_rows_kernel_matches_oracle(N, K, gs, dtype, M):
+    case = Case(N, K, gs, 4, dtype, seed=N + K + M)
+    x = case.x(M)
+    got = _run(case, x, ROWS)
+    assert not torch.isnan(got.float()).any()
+    err = rel_err(got, case.oracle(x))
+    print(f"rows kernel N={N} K={K} gs={gs} M={M}: max rel err {err:.2e}")
+    assert err <= TOL
+    assert torch.equal(got, _run(case, x, ROWS))            # deterministic, run to run
+    assert rel_err(got, _run(case, x, TILE)) <= TOL           # the other kernel agrees
+    assert L.lib().b200lut_device_status() == 0
+
+
+@pytest.mark.parametrize("N,K,gs,dtype", ((256, 128, 128, torch.bfloat16), (4096, 256, 64, torch.float16),
+                                          (12288, 64, 128, torch.bfloat16), (640, 4096, 32, torch.bfloat16)))
+def test_rows_kernel_weights_are_bit_exact(N, K, gs, dtype):
+    # x = e_k (one-hot rows): y[m, n] = W[n, k_m] exactly (1.0 * w + zeros in fp32, one rounding)
+    case = Case(N, K, gs, 4, dtype, seed=3 * N + K)
+    mod = case.module()
+    ks = torch.tensor([0, 1, K // 2 + 3, K - 1, 17 % K, 63 % K, (K // 64 - 1) * 64, 5])
+    x = torch.zeros(8, K, dtype=dtype)
+    x[torch.arange(8), ks] = 1.0
+    got = _run(case, x, ROWS, mod)
+    want = case.w1[:, ks].t().to(dtype)
+    assert torch.equal(got.cpu(), want)
+
+
+def test_rows_kernel_merged_segments_bias_and_residual():
+    # Q/K/V-like merge: three projections of different group sizes share x; unit ranges of the
+    # blocks cross the segment boundaries; one segment carries a bias, one a fused residual
+    K, M, dt = 4096, 3, torch.bfloat16
+    cases = [Case(2048, K, 128, 4, dt, seed=1, bias=True), Case(1024, K, 64, 4, dt, seed=2),
+             Case(4096, K, 128, 4, dt, seed=3, residual=16)]
+    mods = [c.module() for c in cases]
+    x = cases[0].x(M).cuda()
+    total = sum(c.N for c in cases)
+    for variant in (ROWS, TILE):
+        out = torch.full((M, total), float("nan"), dtype=dt, device="cuda")
+        descs, off = [], 0
+        for c, m in zip(cases, mods):
+            res_t = L.residual_project(x, m.resB) if m.has_residual() else None
+            descs.append(m._segment_desc(out[:, off:], ldo=total, res_t=res_t))
+            off += c.N
+        L.gemv_multi(x, L.make_segments(descs), len(descs), flags=variant)
+        torch.cuda.synchronize()
+        off = 0
+        for c in cases:
+            assert rel_err(out[:, off:off + c.N], c.oracle(x.cpu())) <= TOL, (variant, c.N)
+            off += c.N
+
+
+@pytest.mark.parametrize("N,K,M", ((12288, 4096, 1), (12288, 4096, 8), (1024, 2048, 2), (256, 512, 1)))
+def test_rows_kernel_fused_gate_up(N, K, M):
+    dt = torch.bfloat16
+    gate, up = Case(N, K, 128, 4, dt, seed=N + 1, bias=True), Case(N, K, 128, 4, dt, seed=N + 2)
+    mg, mu = gate.module(), up.module()
+    x = gate.x(M)
+    want = orc.silu_mul_fused(x.float() @ gate.w1.t() + gate.bias.float(), x.float() @ up.w1.t(), dt)
+    outs = []
+    for variant in (ROWS, TILE):
+        out = torch.full((M, N), float("nan"), dtype=dt, device="cuda")
+        descs = [mg._segment_desc(out), mu._segment_desc(None)]
+        L.gemv_multi(x.cuda(), L.make_segments(descs), 2, epilogue=L.EPI_SILU_MUL, flags=variant)
+        torch.cuda.synchronize()
+        assert rel_err(out, want) <= TOL, variant
+        outs.append(out)
+    assert rel_err(outs[0], outs[1]) <= TOL
+
+
+def test_rows_kernel_leaves_other_widths_to_the_tile_kernel():
+    # 3-bit codes and second streams are not served: the flag must not change their results
+    case = Case(512, 1024, 128, 3, torch.bfloat16, seed=9)
+    x = case.x(2)
+    assert torch.equal(_run(case, x, ROWS), _run(case, x, TILE))
+    two = Case(256, 512, 128, 4, torch.bfloat16, seed=10, bits2=2)
+    x = two.x(1)
+    assert torch.equal(_run(two, x, ROWS), _run(two, x, TILE))
