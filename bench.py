@@ -35,6 +35,13 @@ if ROOT not in sys.path:
 PKG = "rag-cache-engineering-qwen35-9b-flute_b200"
 METRIC = "9B linear-stack decode tok/s (LUT-GEMV, M=1 unless --batch)"
 FALLBACK_HBM_GBS = 6650.0
+DECODE_KERNEL = "gemv_rows_kernel"
+TRAFFIC_RATIO = 1.0003
+TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one gemv_rows_kernel launch over a "
+                  "248320 x 4096 4-bit projection (508.7 MB for 508.6 MB of algorithmic bytes), ratio scaled "
+                  "to the average launch of the step")
+WORKLOAD = ("qwen3.5-9b linear stack: 32 layers, 248 projections, 6912212992 4-bit weights, "
+            "group 128, bf16 palettes")
 
 
 def measured_peaks():
@@ -162,10 +169,13 @@ def time_steps(fn, steps: int, world: int) -> float:
     return max_over_ranks(e0.elapsed_time(e1), world)
 
 
-def cpu_sample(pkg, stack, M: int, gpu_check: bool, threads: int):
+def cpu_sample(pkg, stack, M: int, gpu_check: bool, threads: int, timed: bool = True, stepped: bool = False):
     """Time the CPU oracle on layers 0 (linear attention) and 3 (full attention) and
     scale to the 24 + 8 layer stack; when gpu_check, compare the GPU outputs of those
-    layers with it (max relative error <= 1e-2)."""
+    layers with it (max relative error <= 1e-2). On a column-parallel shard (world > 1) the
+    oracle computes this rank's rows of every projection; the down projection is checked on the
+    activation row the GPU exchange assembled, whose own slice is checked against the oracle.
+    timed = False skips the second (cached-indices) timing pass."""
     import numpy as np
     import torch
     from oracle import lut_linear_oracle as orc
@@ -174,12 +184,12 @@ def cpu_sample(pkg, stack, M: int, gpu_check: bool, threads: int):
     plan = stack._plan(M) if gpu_check else None
     g = torch.Generator().manual_seed(7)
     x = torch.randn(M, st.HIDDEN, generator=g).to(stack.dtype)
-    if gpu_check:
+    if gpu_check and not stepped:     # stepped: the caller already ran the step on check_input()
         plan["x"].copy_(x)
         stack.step(M)
         torch.cuda.synchronize()
     per_kind, worst = {}, 0.0
-    for li in (0, 3):
+    for li in [i for i in (0, 3) if i < len(stack.layers)]:
         L = stack.layers[li]
         mods = L.heads() + [L.out(), L.mlp.gate_proj, L.mlp.up_proj, L.mlp.down_proj]
         blobs = [pkg._lib.repack_to_idxn(m._packed, m.N, m.K, m.bitwidth).cpu().numpy() for m in mods]
@@ -192,81 +202,196 @@ def cpu_sample(pkg, stack, M: int, gpu_check: bool, threads: int):
                       for m, b, l in zip(mods[-3:], blobs[-3:], luts[-3:]))
         xf = x.float()
         act = orc.silu_mul_fused(xf @ wg.t(), xf @ wu.t(), x.dtype)
-        y = orc.linear_forward(act, wd)
+        n_loc = act.shape[1]
+        down_in = act
+        if stack.world > 1 and gpu_check:      # the full row as the exchange assembled it
+            down_in = plan["buffers"][4 * li + 2].cpu()
+        y = orc.linear_forward(down_in, wd)
         per_kind[L.kind] = time.perf_counter() - t0
+        if not timed:
+            per_kind[L.kind + "_cached"] = per_kind[L.kind]
         # the reference's second mode: logical indices cached once, palette gather per call
-        codes = [orc.unpack_idxn(b, m.N, m.K, m.bitwidth) for m, b in zip(mods, blobs)]
+        codes = [orc.unpack_idxn(b, m.N, m.K, m.bitwidth) for m, b in zip(mods, blobs)] if timed else None
         t0 = time.perf_counter()
-        for m, c, lut in zip(mods[:-3], codes, luts):
-            orc.linear_forward(x, orc.dequant_indices(c, lut, m.group_size, m.bitwidth))
-        wg2, wu2, wd2 = (orc.dequant_indices(c, l, m.group_size, m.bitwidth)
-                         for m, c, l in zip(mods[-3:], codes[-3:], luts[-3:]))
-        act2 = orc.silu_mul_fused(xf @ wg2.t(), xf @ wu2.t(), x.dtype)
-        orc.linear_forward(act2, wd2)
-        per_kind[L.kind + "_cached"] = time.perf_counter() - t0
-        del codes, wg2, wu2, wd2
+        if timed:
+            for m, c, lut in zip(mods[:-3], codes, luts):
+                orc.linear_forward(x, orc.dequant_indices(c, lut, m.group_size, m.bitwidth))
+            wg2, wu2, wd2 = (orc.dequant_indices(c, l, m.group_size, m.bitwidth)
+                             for m, c, l in zip(mods[-3:], codes[-3:], luts[-3:]))
+            act2 = orc.silu_mul_fused(xf @ wg2.t(), xf @ wu2.t(), x.dtype)
+            orc.linear_forward(act2, wd2)
+            per_kind[L.kind + "_cached"] = time.perf_counter() - t0
+            del codes, wg2, wu2, wd2
         if gpu_check:
             bufs = plan["buffers"][4 * li:4 * li + 4]
             want_heads = torch.cat(ys[:-1], dim=1)
-            for got, want in ((bufs[0], want_heads), (bufs[1], ys[-1]), (bufs[2], act), (bufs[3], y)):
+            act_gpu = bufs[2][:, stack.rank * n_loc:(stack.rank + 1) * n_loc]
+            for got, want in ((bufs[0], want_heads), (bufs[1], ys[-1]), (act_gpu, act), (bufs[3], y)):
                 worst = max(worst, orc.max_rel_err(got.cpu().float(), want.float()))
     n_lin = sum(1 for L in stack.layers if L.kind == "linear")
     n_full = len(stack.layers) - n_lin
+    per_kind.setdefault("full", per_kind["linear"])
+    per_kind.setdefault("full_cached", per_kind["linear_cached"])
     step_s = n_lin * per_kind["linear"] + n_full * per_kind["full"]
     per_kind["step_cached"] = n_lin * per_kind["linear_cached"] + n_full * per_kind["full_cached"]
     return step_s, worst, per_kind
 
 
-def run_reference(args, rank: int):
-    """The reference arm: the CPU oracle (port of the reference's forward="reference"
-    route: numpy unpack of the idxN blob on every call, fp32 torch matmul) timed on
-    the host cores. One step = one 4096 x 4096 projection; tok/s is scaled to the
-    stack by the weight ratio."""
-    if rank != 0:
-        return
+def check_input(stack, M: int):
+    """The seeded activation rows the inline correctness gate of the stack runs on."""
+    import torch
+    st = importlib.import_module(PKG + ".stack")
+    return torch.randn(M, st.HIDDEN, generator=torch.Generator().manual_seed(7)).to(stack.dtype)
+
+
+def exchange_equals_gather(stack, M: int, world: int) -> bool:
+    """Multi-GPU gate: after a step, every layer's assembled activation row (filled by the peers'
+    stores, or by the NCCL gather) must equal, bit for bit, an NCCL all-gather of the ranks' own
+    slices taken now. True only if it holds on every rank."""
+    import torch
+    import torch.distributed as dist
+    plan = stack._plan(M)
+    ok = True
+    for li in range(len(stack.layers)):
+        act = plan["buffers"][4 * li + 2]
+        n = act.shape[1] // world
+        mine = act[:, stack.rank * n:(stack.rank + 1) * n].contiguous()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        ok = ok and bool(torch.equal(torch.cat(parts, dim=1), act))
+    flag = torch.tensor([1 if ok else 0], device=act.device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(flag.item())
+
+
+GROUPS = ("heads", "out", "gate_up", "down")
+
+
+def cpu_group_samples(M: int, seed: int):
+    """The four projection groups of a linear-attention decoder layer on the CPU oracle (the
+    reference's forward="reference" route: numpy unpack of every idxN blob on every call, fp32
+    torch matmul): seeded synthetic blobs and palettes drawn on the host. Returns
+    {group: (closure that runs the group once, weights of the group)}."""
     import numpy as np
     import torch
     from oracle import lut_linear_oracle as orc
-    pkg = importlib.import_module(PKG)
+    st = importlib.import_module(PKG + ".stack")
+    rng = np.random.default_rng(seed)
+    bits, gs = 4, 128
+
+    def make(N, K):
+        blob = rng.integers(0, 256, size=N * K * bits // 8, dtype=np.uint8)   # uniform bytes = uniform codes
+        g = torch.Generator().manual_seed(int(rng.integers(1 << 30)))
+        lut = (0.02 * torch.randn(N // gs, 1 << bits, generator=g)).sort(dim=1).values.to(torch.bfloat16)
+        return blob, lut, N, K
+
+    def weight(t):
+        return orc.dequant(t[0], t[1], t[2], t[3], gs, bits)
+    heads = [make(n, st.HIDDEN) for _, n in st.LINEAR_ATTN]
+    out = make(st.HIDDEN, st.HIDDEN)
+    gate, up = make(st.INTERMEDIATE, st.HIDDEN), make(st.INTERMEDIATE, st.HIDDEN)
+    down = make(st.HIDDEN, st.INTERMEDIATE)
+    x = torch.randn(M, st.HIDDEN, generator=torch.Generator().manual_seed(seed)).to(torch.bfloat16)
+    act = torch.randn(M, st.INTERMEDIATE, generator=torch.Generator().manual_seed(seed + 1)).to(torch.bfloat16)
+
+    def run_heads():
+        for t in heads:
+            orc.linear_forward(x, weight(t))
+
+    def run_gate_up():
+        xf = x.float()
+        return orc.silu_mul_fused(xf @ weight(gate).t(), xf @ weight(up).t(), x.dtype)
+    return {"heads": (run_heads, sum(t[2] * t[3] for t in heads)),
+            "out": (lambda: orc.linear_forward(x, weight(out)), out[2] * out[3]),
+            "gate_up": (run_gate_up, 2 * gate[2] * gate[3]),
+            "down": (lambda: orc.linear_forward(act, weight(down)), down[2] * down[3])}
+
+
+def run_reference(args, rank: int):
+    """The reference arm: the CPU oracle (port of the reference's forward="reference" route)
+    timed on the host cores with all the threads torch can use. One timed step = ONE projection
+    group of a decoder layer (Q/K/V/z heads, out projection, gate + up + SiLU*mul, down
+    projection, in turn), so that K steps stay within minutes; the step time of the whole stack
+    is the sum over the 128 groups of the 32 layers, each at its group's mean time (the heads of
+    the 8 full-attention layers, 10240 rows instead of 12288, by row count)."""
+    if rank != 0:
+        return
+    import torch
     st = importlib.import_module(PKG + ".stack")
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    M, N, K, bits, gs = args.batch, 4096, 4096, 4, 128
-    codes, blob = pkg.synthetic.make_blob(N, K, bits, pkg.synthetic.BASE_SEED)
-    lut = pkg.synthetic.make_lut(N // gs, bits, torch.bfloat16, pkg.synthetic.BASE_SEED)
-    x = pkg.synthetic.make_x(M, K, torch.bfloat16, pkg.synthetic.BASE_SEED)
-    blob = blob.numpy()
-
-    def step():
-        return orc.linear_forward(x, orc.dequant(blob, lut, N, K, gs, bits))
-    for _ in range(args.warmup):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step()
-    dt = (time.perf_counter() - t0) / args.steps
-    scale = st.census()["weights"] / (N * K)
-    value = M / (dt * scale)
+    M = args.batch
+    groups = cpu_group_samples(M, 11)
+    for i in range(args.warmup):
+        groups[GROUPS[i % 4]][0]()
+    spent = {g: [] for g in GROUPS}
+    t_all = time.perf_counter()
+    for i in range(args.steps):
+        g = GROUPS[i % 4]
+        t0 = time.perf_counter()
+        groups[g][0]()
+        spent[g].append(time.perf_counter() - t0)
+    wall = time.perf_counter() - t_all
+    seen = [g for g in GROUPS if spent[g]]
+    per_weight = sum(statistics.mean(spent[g]) for g in seen) / sum(groups[g][1] for g in seen)
+    mean = {g: statistics.mean(spent[g]) if spent[g] else per_weight * groups[g][1] for g in GROUPS}
+    n_lin = sum(1 for i in range(st.N_LAYERS) if st.layer_kind(i) == "linear")
+    n_full = st.N_LAYERS - n_lin
+    full_heads = sum(n for _, n in st.FULL_ATTN) / sum(n for _, n in st.LINEAR_ATTN)
+    step_s = (n_lin + n_full * full_heads) * mean["heads"] + st.N_LAYERS * (mean["out"] + mean["gate_up"] + mean["down"])
+    value = M / step_s
+    sample = ("each timed step is ONE projection group of a decoder layer on the CPU, in turn: " +
+              ", ".join(f"{g} {mean[g]:.2f} s" for g in GROUPS) +
+              f"; ms_per_step and value are the 32-layer step = {n_lin} + {n_full} x {full_heads:.3f} heads "
+              f"+ {st.N_LAYERS} x (out + gate_up + down)")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": dt * scale * 1e3, "higher_is_better": True, "scaling": "strong",
+            "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "qwen3.5-9b linear stack: 32 layers, 248 projections, 6912212992 4-bit weights, group 128, bf16 palettes",
-                       "batch": M},
+            "config": {"workload": WORKLOAD, "batch": M, "sample": sample, "timed_wall_s": wall},
             "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port",
-                             "sample": f"one 4096x4096 projection per step ({dt * 1e3:.0f} ms), "
-                                       f"scaled x{scale:.0f} by weight count"},
+                             "sample": f"{args.steps} single-group steps ({wall:.0f} s of CPU work); " + sample +
+                                       "; blob unpacked on every call as the reference route does"},
             "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
-def single_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int, flags: int):
+def sampled_gate(pkg, packed, lut, N, K, bits, gs, x, got, rows=None):
+    """Inline correctness gate of one data point (the reference's benchmark does the same per
+    point, src/flute_extended/benchmark_kernel.py:95-107): the outputs of 256 weight rows
+    spread over the matrix are recomputed on the CPU with the reference route's arithmetic
+    (palette lookup of the exported codes, fp32 matmul, one rounding) and compared. Returns
+    {"rel_max": max|got - want| / max|want|, "cos": cosine}; a point with rel_max > 1e-2 or
+    cos < 0.999 is not reported."""
+    import numpy as np
+    import torch
+    from oracle import lut_linear_oracle as orc
+    if rows is None:
+        tiles = sorted({0, (N // 128) // 3, (N // 128) - 1})
+        rows = torch.cat([torch.arange(t * 128, min(N, t * 128 + 86)) for t in tiles])[:256]
+    codes = pkg._lib.unpack_codes(packed, N, K, bits)[rows.to(packed.device)].cpu().numpy().astype(np.int64)
+    lut_c = lut.cpu()
+    w = torch.empty(len(rows), K)
+    for j, r in enumerate(rows.tolist()):
+        w[j] = lut_c[min(r // gs, lut_c.shape[0] - 1)].float()[torch.from_numpy(codes[j])]
+    xc = x.detach().cpu()
+    want = (xc.float() @ w.t()).to(xc.dtype)
+    g = got[:, rows.to(got.device)].detach().cpu()
+    return {"rel_max": orc.max_rel_err(g.float(), want.float()), "cos": orc.cosine(g.float(), want.float())}
+
+
+def gate_ok(g) -> bool:
+    return g["rel_max"] <= 1e-2 and g["cos"] >= 0.999
+
+
+def single_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int, flags: int,
+                          bits: int = 4, gs: int = 128, gate: bool = False):
     """Extra: one projection launched back to back over `sets` distinct weight sets
-    (their total exceeds L2), CUDA-graph replay; returns (GB/s, us per launch)."""
+    (their total exceeds L2), CUDA-graph replay; returns (GB/s, us per launch[, gate])."""
     import torch
     L = pkg._lib
-    bits, gs, dt = 4, 128, torch.bfloat16
+    dt = torch.bfloat16
     x = torch.randn(M, K, device="cuda").to(dt)
     out = torch.empty(M, N, dtype=dt, device="cuda")
     keep, segs = [], []
@@ -289,11 +414,14 @@ def single_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int, fl
         g.replay()
     ms = time_steps(g.replay, iters, 1)
     us = ms * 1e3 / (iters * sets)
-    byts = N * K * bits // 8 + (N // gs) * 32 + M * K * 2 + M * N * 2
-    return byts / us / 1e3, us
+    byts = N * K * bits // 8 + (N // gs) * (2 << bits) + M * K * 2 + M * N * 2
+    if not gate:
+        return byts / us / 1e3, us
+    # the graph's last launch used the last weight set: `out` holds its result
+    return byts / us / 1e3, us, sampled_gate(pkg, keep[-1][0], keep[-1][1], N, K, bits, gs, x, out)
 
 
-def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool):
+def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool, gate: bool = False):
     """Extra: the M=2048 prefill GEMM (optionally behind the 128-point block Hadamard of the
     activations, timed together), CUDA events, inputs 16 MB + 24 MB + 48 MB out per call."""
     import torch
@@ -320,7 +448,14 @@ def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool):
     if status != 0:
         raise RuntimeError(f"a bounded wait ran out inside the GEMM kernel (device status {status})")
     us = ms * 1e3 / iters
-    return 2.0 * M * N * K / us / 1e6, us
+    if not gate:
+        return 2.0 * M * N * K / us / 1e6, us
+    if rotate:
+        from oracle import lut_linear_oracle as orc
+        xin = orc.fht_block(x.cpu(), 128).to(dt)
+    else:
+        xin = x
+    return 2.0 * M * N * K / us / 1e6, us, sampled_gate(pkg, packed, lut, N, K, bits, gs, xin[:64], out[:64])
 
 
 def dense_matmul_tflops(M: int, N: int, K: int, iters: int):
@@ -339,7 +474,7 @@ def dense_matmul_tflops(M: int, N: int, K: int, iters: int):
     return 2.0 * M * N * K / us / 1e6, us
 
 
-def kgrouped_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int):
+def kgrouped_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int, gate: bool = False):
     """Extra: the K-grouped palette variant of one projection (one 16-entry palette per 128
     input columns and output row: N*K/4 bytes of palettes beside N*K/2 of codes), launched
     back to back over `sets` distinct weight sets; returns (GB/s, us per launch)."""
@@ -368,10 +503,26 @@ def kgrouped_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int):
     ms = time_steps(g.replay, iters, 1)
     us = ms * 1e3 / (iters * sets)
     byts = N * K * bits // 8 + (K // 128) * N * 16 * 2 + M * K * 2 + M * N * 2
-    return byts / us / 1e3, us
+    if not gate:
+        return byts / us / 1e3, us
+    # gate: 128 sampled rows of the last weight set, palette per (128-column block, row)
+    import numpy as np
+    from oracle import lut_linear_oracle as orc
+    packed, lut_k = keep[-1]
+    rows = torch.arange(0, N, N // 128)[:128]
+    codes = L.unpack_codes(packed, N, K, bits)[rows.cuda()].cpu().numpy().astype(np.int64)
+    pal = lut_k[:, rows.cuda()].cpu().float()                     # [K/128, rows, 16]
+    w = torch.empty(len(rows), K)
+    for j in range(len(rows)):
+        c = torch.from_numpy(codes[j]).view(K // 128, 128)
+        w[j] = pal[:, j].gather(1, c).reshape(K)
+    want = (x.cpu().float() @ w.t()).to(dt)
+    got = out[:, rows.cuda()].cpu()
+    return byts / us / 1e3, us, {"rel_max": orc.max_rel_err(got.float(), want.float()),
+                                 "cos": orc.cosine(got.float(), want.float())}
 
 
-def embedding_gather_gbs(pkg, N: int, K: int, n_ids: int, iters: int):
+def embedding_gather_gbs(pkg, N: int, K: int, n_ids: int, iters: int, gate: bool = False):
     """Extra: the embedding gather over an lm_head-sized 4-bit table (0.51 GB of codes, far
     beyond L2), `n_ids` random rows per launch; returns (GB/s of algorithmic bytes, us).
     Algorithmic bytes per row: K/2 of codes + 2K of output."""
@@ -391,7 +542,224 @@ def embedding_gather_gbs(pkg, N: int, K: int, n_ids: int, iters: int):
     if L.lib().b200lut_device_status() != 0:
         raise RuntimeError("the embedding gather met an id outside its table")
     us = ms * 1e3 / iters
-    return n_ids * (K * bits // 8 + 2 * K) / us / 1e3, us
+    if not gate:
+        return n_ids * (K * bits // 8 + 2 * K) / us / 1e3, us
+    # gate: the gathered rows equal the palette lookup of the exported codes, bit for bit
+    # (the weight rows come from the dequant export of the 128-row tiles that hold them)
+    rows = L.embed_gather(ids[:8].contiguous(), table, K, dt)
+    tile_bytes = 128 * K * bits // 8
+    exact = True
+    for j, i in enumerate(ids[:8].tolist()):
+        t = i // 128
+        w = L.dequant(packed[t * tile_bytes:(t + 1) * tile_bytes], lut[t * 128 // gs:(t + 1) * 128 // gs].contiguous(),
+                      128, K, bits, gs)
+        exact = exact and bool(torch.equal(rows[j], w[i % 128]))
+    return n_ids * (K * bits // 8 + 2 * K) / us / 1e3, us, {"bit_exact": exact}
+
+
+def graph_time(run, iters: int):
+    """us per call of `run` under CUDA-graph replay (one eager call first)."""
+    import torch
+    run()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run()
+    for _ in range(3):
+        g.replay()
+    return time_steps(g.replay, iters, 1) * 1e3 / iters
+
+
+def projection_point(pkg, M: int, N: int, K: int, bits: int, gs: int, iters: int, flags: int):
+    """One point of the hybrid-palettization grid: the module forward of one projection (decode
+    GEMV at M <= 16, tensor-core GEMM above) over enough distinct weight sets to exceed L2,
+    CUDA-graph replay. Returns (us per forward, algorithmic bytes, gate)."""
+    import torch
+    dt = torch.bfloat16
+    sets = max(2, -(-160_000_000 // (N * K * bits // 8)))
+    x = torch.randn(M, K, device="cuda").to(dt)
+    mods = []
+    for i in range(sets):
+        packed = pkg._lib.repack_from_idxn(pkg.synthetic.random_blob_on_device(N, K, bits, 300 + i, "cuda"), N, K, bits)
+        lut = pkg.synthetic.make_lut(N // gs, bits, dt, 300 + i).cuda()
+        mods.append(pkg.PalettizedLinear.from_packed(packed, lut, bits, gs, N, K))
+    outs = [None]
+
+    def run():
+        for m in mods:
+            outs[0] = m(x)
+    pkg.set_programmatic_launch(bool(flags & pkg._lib.FLAG_PDL))
+    us = graph_time(run, iters) / sets
+    byts = N * K * bits // 8 + (N // gs) * (2 << bits) + M * K * 2 + M * N * 2
+    last = mods[-1]
+    return us, byts, sampled_gate(pkg, last._packed, last.lut, N, K, bits, gs, x, outs[0])
+
+
+def mlp_block_point(pkg, M: int, form: str, iters: int, flags: int):
+    """The decode MLP block (gate, up 4096 -> 12288; SiLU*mul; down 12288 -> 4096) in one of three
+    forms over 4 weight sets (300 MB of codes): "plain" = gate, up, one SiLU*mul pass, down as
+    four launches with the library's launch shapes; "split" = the same with the K split of the
+    tile kernel set by hand (2 for gate / up, 8 for down: the reference's split-K form);
+    "fused" = gate + up + SiLU*mul in one launch, then down. Returns (us per block, gate)."""
+    import torch
+    L = pkg._lib
+    dt, H, I, bits, gs = torch.bfloat16, 4096, 12288, 4, 128
+    x = torch.randn(M, H, device="cuda").to(dt)
+    sets = []
+    for i in range(4):
+        mk = lambda N, K, sd: (L.repack_from_idxn(pkg.synthetic.random_blob_on_device(N, K, bits, sd, "cuda"), N, K, bits),
+                               pkg.synthetic.make_lut(N // gs, bits, dt, sd).cuda())
+        sets.append((mk(I, H, 500 + 3 * i), mk(I, H, 501 + 3 * i), mk(H, I, 502 + 3 * i)))
+    g_out = torch.empty(M, I, dtype=dt, device="cuda")
+    u_out = torch.empty(M, I, dtype=dt, device="cuda")
+    y = torch.empty(M, H, dtype=dt, device="cuda")
+
+    def seg(w, N, out):
+        return dict(packed=w[0], lut=w[1], N=N, group_size=gs, n_groups=N // gs, bits=bits, out=out)
+    prepared = []
+    for g, u, d in sets:
+        prepared.append((L.make_segments([seg(g, I, g_out)]), L.make_segments([seg(u, I, u_out)]),
+                         L.make_segments([seg(g, I, g_out), seg(u, I, None)]), L.make_segments([seg(d, H, y)])))
+
+    def run():
+        for sg, su, sgu, sd in prepared:
+            if form == "fused":
+                L.gemv_multi(x, sgu, 2, epilogue=L.EPI_SILU_MUL, flags=flags)
+            else:
+                kw = dict(split=2, flags=flags | L.FLAG_TILE_KERNEL) if form == "split" else dict(flags=flags)
+                L.gemv_multi(x, sg, 1, **kw)
+                L.gemv_multi(x, su, 1, **kw)
+                L.silu_mul(g_out, u_out)
+            kw = dict(split=8, flags=flags | L.FLAG_TILE_KERNEL) if form == "split" else dict(flags=flags)
+            L.gemv_multi(g_out, sd, 1, **kw)
+    us = graph_time(run, iters) / len(sets)
+    # gate: the activation row on sampled gate / up rows, then down on the GPU's own activation row
+    from oracle import lut_linear_oracle as orc
+    g, u, d = sets[-1]
+    rows = torch.arange(0, I, I // 128)[:128]
+    import numpy as np
+
+    def wrows(w, N, K, r):
+        codes = L.unpack_codes(w[0], N, K, bits)[r.cuda()].cpu().numpy().astype(np.int64)
+        lut = w[1].cpu().float()
+        return torch.stack([lut[rr // gs][torch.from_numpy(codes[j])] for j, rr in enumerate(r.tolist())])
+    xf = x.cpu().float()
+    act_want = orc.silu_mul_fused(xf @ wrows(g, I, H, rows).t(), xf @ wrows(u, I, H, rows).t(), dt)
+    act_got = g_out[:, rows.cuda()].cpu()
+    gate_act = {"rel_max": orc.max_rel_err(act_got.float(), act_want.float()),
+                "cos": orc.cosine(act_got.float(), act_want.float())}
+    gate_y = sampled_gate(pkg, d[0], d[1], H, I, bits, gs, g_out, y)
+    return us, {"rel_max": max(gate_act["rel_max"], gate_y["rel_max"]), "cos": min(gate_act["cos"], gate_y["cos"])}
+
+
+def stack_point(pkg, stack, M: int, flags: int, iters: int):
+    """The stack at batch M under CUDA-graph replay: (ms per step, gate on layer 0's Q rows)."""
+    import torch
+    plan = stack._plan(M)
+    x = torch.randn(M, plan["x"].shape[1], generator=torch.Generator().manual_seed(40 + M)).to(stack.dtype)
+    plan["x"].copy_(x)
+    ms = graph_time(lambda: stack.step(M, flags=flags), iters) / 1e3
+    q = stack.layers[0].heads()[0]
+    xin = x
+    if stack.rotate:
+        from oracle import lut_linear_oracle as orc
+        signs = plan["launches"][0][3].cpu()
+        xin = orc.fht_forward(x, signs)
+    got = plan["buffers"][0][:, :q.N]
+    return ms, sampled_gate(pkg, q._packed, q.lut, q.N, q.K, q.bitwidth, q.group_size, xin, got)
+
+
+def run_extras(pkg, st, stack, peaks, flags):
+    """Driver-run numbers beside the headline, each behind its own inline correctness gate (a
+    point that fails its gate is reported as failed, without a number)."""
+    import torch
+    extras = {}
+    hbm = peaks["hbm_gbs"]
+
+    def put(name, entry, gate):
+        if gate is not None and not (gate.get("bit_exact") if "bit_exact" in gate else gate_ok(gate)):
+            extras[name] = {"failed_gate": gate}
+        else:
+            if gate is not None:
+                entry["gate"] = gate
+            extras[name] = entry
+    try:
+        tf, us, g = prefill_gemm_tflops(pkg, 2048, 12288, 4096, 20, False, gate=True)
+        put("prefill_gemm_m2048_k4096_n12288", {
+            "TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"],
+            "peak": peaks["bf16_tflops"], "peak_kind": "burst, " + peaks["source"]}, g)
+        dtf, dus = dense_matmul_tflops(2048, 12288, 4096, 20)
+        extras["dense_bf16_matmul_m2048_k4096_n12288"] = {"TFLOP/s": dtf, "us": dus, "lut_gemm_over_dense": tf / dtf}
+        tf, us, g = prefill_gemm_tflops(pkg, 2048, 12288, 4096, 20, True, gate=True)
+        put("prefill_gemm_with_block128_fht", {"TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}, g)
+        for name, N, K, sets, it in (("gemv_4096x4096_m1", 4096, 4096, 40, 20), ("gemv_12288x4096_m1", 12288, 4096, 16, 20),
+                                     ("gemv_4096x12288_m1", 4096, 12288, 16, 20),
+                                     # the model's lm_head (0.51 GB of codes): the kernel's steady-state rate
+                                     ("gemv_248320x4096_m1_lm_head", 248320, 4096, 1, 10)):
+            gbs, us, g = single_projection_gbs(pkg, 1, N, K, sets, it, flags, gate=True)
+            put(name, {"GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / hbm}, g)
+        gbs, us, g = kgrouped_projection_gbs(pkg, 1, 4096, 4096, 16, 20, gate=True)
+        put("gemv_kgrouped_4096x4096_m1", {"GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / hbm,
+                                            "bytes_per_launch": 12599296}, g)
+        gbs, us, g = embedding_gather_gbs(pkg, 248320, 4096, 2048, 20, gate=True)
+        put("embedding_gather_248320x4096_2048_ids", {"GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / hbm}, g)
+
+        # the decode MLP block: 75.5 MB of algorithmic bytes per block
+        mlp_bytes = 3 * (12288 * 4096 // 2) + 2 * (12288 // 128) * 32 + (4096 // 128) * 32
+        for M in (1, 8):
+            for form in ("plain", "split", "fused"):
+                us, g = mlp_block_point(pkg, M, form, 10, flags)
+                byts = mlp_bytes + M * (2 * 4096 + 2 * 12288 * 2 + 2 * 4096)
+                put(f"mlp_block_m{M}_{form}", {"us_per_block": us, "GB/s": byts / us / 1e3,
+                                               "frac_of_hbm": byts / us / 1e3 / hbm}, g)
+
+        # the hybrid-palettization grid: code width x group size x batch on the two projection shapes
+        grid = {}
+        for N in (4096, 12288):
+            for bits in (3, 4):
+                for gs in (64, 128):
+                    for M in (1, 16, 128):
+                        us, byts, g = projection_point(pkg, M, N, 4096, bits, gs, 10, flags)
+                        key = f"{N}x4096_b{bits}_gs{gs}_m{M}"
+                        if gate_ok(g):
+                            grid[key] = {"us": round(us, 2), "frac_of_hbm": round(byts / us / 1e3 / hbm, 3),
+                                         "TFLOP/s": round(2.0 * M * N * 4096 / us / 1e6, 1), "rel_max": g["rel_max"]}
+                        else:
+                            grid[key] = {"failed_gate": g}
+        extras["hybrid_grid"] = grid
+
+        # the stack at the other decode widths, and behind a Hadamard rotation of every group's input
+        for M in (16, 64):
+            ms, g = stack_point(pkg, stack, M, flags, 10)
+            byts = stack.algorithmic_bytes(M)
+            put(f"stack_m{M}", {"ms_per_step": ms, "tok/s": M * 1e3 / ms, "frac_of_hbm": byts / (ms * 1e-3) / 1e9 / hbm,
+                                "launches_per_step": stack.launches_per_step(M)}, g)
+        rot = st.LinearStack(device=stack.device, n_layers=len(stack.layers), rotate=True)
+        ms, g = stack_point(pkg, rot, 1, flags, 10)
+        put("stack_m1_rotated", {"ms_per_step": ms, "tok/s": 1e3 / ms, "launches_per_step": rot.launches_per_step(1),
+                                 "note": "one FHT launch (segments + signs) in front of each of the 128 projection groups"}, g)
+        del rot
+        torch.cuda.empty_cache()
+
+        # the whole stack at prefill width: every projection as a tensor-core GEMM, eager launches
+        Mp = 2048
+        ms_p, g = None, None
+        stack._plan(Mp)["x"].copy_(torch.randn(Mp, 4096, generator=torch.Generator().manual_seed(77)).to(stack.dtype))
+        stack.step(Mp)
+        torch.cuda.synchronize()
+        ms_p = time_steps(lambda: stack.step(Mp), 5, 1) / 5
+        tf_p = stack.flops(Mp) / (ms_p * 1e-3) / 1e12
+        q = stack.layers[0].heads()[0]
+        plan = stack._plan(Mp)
+        g = sampled_gate(pkg, q._packed, q.lut, q.N, q.K, q.bitwidth, q.group_size, plan["x"][:64], plan["buffers"][0][:64, :q.N])
+        put("prefill_stack_m2048", {"tok/s": Mp * 1e3 / ms_p, "ms_per_step": ms_p, "TFLOP/s": tf_p,
+                                    "frac_of_bf16_peak_sustained": tf_p / peaks["bf16_tflops_sustained"],
+                                    "peak_sustained": peaks["bf16_tflops_sustained"]}, g)
+        if pkg._lib.lib().b200lut_device_status() != 0:
+            raise RuntimeError("a bounded wait ran out inside an extra")
+    except Exception as e:       # an extra must not lose the main line
+        extras["error"] = repr(e)
+    return extras
 
 
 def run_case(args) -> int:
@@ -437,8 +805,8 @@ def main() -> int:
                          "from the GEMV epilogue; nccl: an all-gather call between the launches)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
     ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemm", "embed", "kgrouped"),
-                    help="stack: the benchmark; gemv / gemm: a few launches of one kernel on a "
-                         "small case (the workloads the ncu captures in profiles/ use)")
+                    help="stack: the benchmark; gemv / gemm / embed / kgrouped: a few launches of one "
+                         "kernel on a profiling-sized case")
     ap.add_argument("--executor", default="graph", choices=("plan", "graph"),
                     help="plan: persistent cooperative launch(es) per step; graph: one kernel per "
                          "projection group under CUDA-graph replay")
@@ -459,10 +827,6 @@ def main() -> int:
     flags = pkg._lib.FLAG_PDL if args.pdl else 0
     peaks = measured_peaks()
 
-    def trace(msg):
-        if os.environ.get("B200LUT_BENCH_TRACE"):
-            print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
-    trace("building the stack")
     push = world > 1 and args.gather == "push" and M <= 16 and args.executor != "plan"
     stack = st.LinearStack(device=f"cuda:{local}", rank=rank, world=world, n_layers=args.layers,
                            gather="push" if push else "nccl")
@@ -486,23 +850,35 @@ def main() -> int:
         import torch.distributed as dist
         torch.cuda.synchronize()
         dist.barrier()
-    trace("first eager step")
     run_step()
     torch.cuda.synchronize()
-    trace("eager step done")
+    # Inline correctness gate of the timed configuration, on every rank count: one eager step on
+    # seeded rows; rank 0 compares its rows of layers 0 and 3 with the CPU oracle below, and with
+    # several ranks the assembled activation rows must equal an NCCL all-gather bit for bit.
+    plan["x"].copy_(check_input(stack, M))
+    run_step()
+    torch.cuda.synchronize()
+    multi_gpu_check = None
+    if world > 1:
+        multi_gpu_check = {"assembled_rows_equal_nccl_all_gather": exchange_equals_gather(stack, M, world)}
+    gate_worst = None
+    if rank == 0 and not args.no_cpu and world > 1:
+        _, gate_worst, _ = cpu_sample(pkg, stack, M, True, os.cpu_count() or 1, timed=False, stepped=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    plan["x"].copy_(x_host)
     graph = None
     if not args.no_graph:
         side = torch.cuda.Stream()
         with torch.cuda.stream(side):
             run_step()
             torch.cuda.synchronize()
-            trace("capturing")
             graph = torch.cuda.CUDAGraph()
             # thread-local capture: the NCCL watchdog thread keeps making CUDA calls of its own
             with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
                 run_step()
         torch.cuda.synchronize()
-        trace("captured")
 
     def step_resident():
         if graph is not None:
@@ -518,7 +894,6 @@ def main() -> int:
 
     for _ in range(args.warmup):
         step_resident()
-    trace("warm-up done")
     with ClockSampler(local) as clk:
         # run under load for ~1.5 s first so that the 200 ms sampler sees the timed state,
         # then time exactly K steps
@@ -528,7 +903,6 @@ def main() -> int:
                 step_resident()
         ms = time_steps(step_resident, args.steps, world)
     clocks = clk.summary()
-    trace("timed")
     for _ in range(args.warmup):
         step_e2e()
     ms_e2e = time_steps(step_e2e, args.steps, world)
@@ -547,8 +921,7 @@ def main() -> int:
         "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "qwen3.5-9b linear stack: 32 layers, 248 projections, "
-                               "6912212992 4-bit weights, group 128, bf16 palettes",
+        "config": {"workload": WORKLOAD,
                    "batch": M,
                    "parallelism": f"column-parallel x{world}, all-gather per layer" + (
                        "" if world == 1 else
@@ -563,15 +936,14 @@ def main() -> int:
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
         "gpu_launches": kernel_launches * args.steps,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "gemv_plan_kernel" if use_plan else "gemv_kernel", "achieved": achieved,
+        "roofline": {"bound": "hbm", "kernel": "gemv_plan_kernel" if use_plan else DECODE_KERNEL, "achieved": achieved,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                      "peak_source": peaks["source"],
-                     # DRAM bytes per launch: the ncu capture of this kernel on the 12288 x 4096
-                     # projection read 25.25 MB for 25.20 MB of algorithmic bytes and wrote none
-                     # (profiles/gemv_kernel_12288x4096_m1.md); traffic grows with the codes, so
-                     # the ratio is applied to the average launch of the step
-                     "traffic": None if use_plan else 1.002 * bytes_rank / kernel_launches,
-                     "traffic_source": "ncu dram__bytes ratio 1.002 of the 12288x4096 capture, scaled",
+                     # DRAM bytes per launch: the ncu capture of this kernel read TRAFFIC_RATIO times
+                     # the algorithmic bytes of its launch and wrote none; traffic grows with the
+                     # codes, so the ratio is applied to the average launch of the step
+                     "traffic": None if use_plan else TRAFFIC_RATIO * bytes_rank / kernel_launches,
+                     "traffic_source": TRAFFIC_SOURCE,
                      "bytes_per_launch": bytes_rank / kernel_launches,
                      "us_per_launch": ms_step * 1e3 / kernel_launches,
                      "projection_groups_per_step": launches},
@@ -587,52 +959,14 @@ def main() -> int:
                             "us_per_launch": ms_step * 1e3 / kernel_launches,
                             "projection_groups_per_step": launches}
     if rank == 0 and world == 1 and not args.no_extras:
-        extras = {}
-        try:
-            tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, 20, False)
-            extras["prefill_gemm_m2048_k4096_n12288"] = {
-                "TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"],
-                "peak": peaks["bf16_tflops"], "peak_kind": "burst, " + peaks["source"]}
-            dtf, dus = dense_matmul_tflops(2048, 12288, 4096, 20)
-            extras["dense_bf16_matmul_m2048_k4096_n12288"] = {"TFLOP/s": dtf, "us": dus,
-                                                              "lut_gemm_over_dense": tf / dtf}
-            tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, 20, True)
-            extras["prefill_gemm_with_block128_fht"] = {
-                "TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
-            gbs, us = single_projection_gbs(pkg, 1, 4096, 4096, 40, 20, flags)
-            extras["gemv_4096x4096_m1"] = {"GB/s": gbs, "us_per_launch": us,
-                                           "frac_of_hbm": gbs / peaks["hbm_gbs"]}
-            gbs, us = single_projection_gbs(pkg, 1, 12288, 4096, 16, 20, flags)
-            extras["gemv_12288x4096_m1"] = {"GB/s": gbs, "us_per_launch": us,
-                                            "frac_of_hbm": gbs / peaks["hbm_gbs"]}
-            # the model's lm_head (248 320 x 4096, 1940 tiles, 0.51 GB of codes): the steady-state
-            # streaming rate of the kernel, with the per-launch cost amortised over 13 waves
-            gbs, us = single_projection_gbs(pkg, 1, 248320, 4096, 1, 10, flags)
-            extras["gemv_248320x4096_m1_lm_head"] = {"GB/s": gbs, "us_per_launch": us,
-                                                     "frac_of_hbm": gbs / peaks["hbm_gbs"]}
-            gbs, us = kgrouped_projection_gbs(pkg, 1, 4096, 4096, 16, 20)
-            extras["gemv_kgrouped_4096x4096_m1"] = {"GB/s": gbs, "us_per_launch": us,
-                                                    "frac_of_hbm": gbs / peaks["hbm_gbs"],
-                                                    "bytes_per_launch": 12599296}
-            gbs, us = embedding_gather_gbs(pkg, 248320, 4096, 2048, 20)
-            extras["embedding_gather_248320x4096_2048_ids"] = {
-                "GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}
-            # the whole stack at prefill width: every projection as a tensor-core GEMM
-            # (gate, then up multiplying silu of the gate's output), eager launches
-            Mp = 2048
-            stack.step(Mp)
-            torch.cuda.synchronize()
-            ms_p = time_steps(lambda: stack.step(Mp), 5, 1) / 5
-            tf_p = stack.flops(Mp) / (ms_p * 1e-3) / 1e12
-            extras["prefill_stack_m2048"] = {
-                "tok/s": Mp * 1e3 / ms_p, "ms_per_step": ms_p, "TFLOP/s": tf_p,
-                "frac_of_bf16_peak_sustained": tf_p / peaks["bf16_tflops_sustained"],
-                "peak_sustained": peaks["bf16_tflops_sustained"]}
-            if pkg._lib.lib().b200lut_device_status() != 0:
-                raise RuntimeError("a bounded wait ran out inside the prefill stack")
-        except Exception as e:       # an extra must not lose the main line
-            extras["error"] = repr(e)
-        line["extras"] = extras
+        line["extras"] = run_extras(pkg, st, stack, peaks, flags)
+    if multi_gpu_check is not None:
+        line["multi_gpu_check"] = multi_gpu_check
+        if gate_worst is not None:
+            line["multi_gpu_check"]["gpu_max_rel_err_vs_cpu"] = gate_worst
+            line["multi_gpu_check"]["checked"] = "rank 0's rows of layers 0 and 3 against the CPU oracle"
+        if not multi_gpu_check["assembled_rows_equal_nccl_all_gather"] or (gate_worst or 0.0) > 1e-2:
+            line["invalid"] = "multi-GPU outputs differ from the NCCL gather or from the CPU oracle"
     if rank == 0 and world == 1 and not args.no_cpu:
         threads = os.cpu_count() or 1
         step_s, worst, per_kind = cpu_sample(pkg, stack, M, True, threads)

@@ -227,9 +227,9 @@ typedef struct b200lut_exchange {
   int world, rank;        /* 1 <= world <= 8 */
   int push;               /* nonzero: mirror outputs to the peers and signal them */
   int wait;               /* nonzero: wait for all ranks' signals before reading x */
-  int producer_blocks;    /* blocks of the pushing launch (tiles x split: pass an explicit split,
-                             b200lut_gemv_pick_split gives the library's choice); the same on
-                             every rank; push: checked against the launch; wait: flags per rank */
+  int producer_blocks;    /* blocks of the pushing launch (b200lut_gemv_launch_blocks for split = 0,
+                             tiles x split for an explicit split); the same on every rank;
+                             push: checked against the launch; wait: flags per rank */
   int reserved;
   int64_t peer_delta[B200LUT_MAX_PEERS];  /* bytes from a local output address to the same
                                              element of rank q's buffer (entry `rank` unused) */
@@ -241,6 +241,13 @@ typedef struct b200lut_exchange {
   void* wait_ticket;      /* local u32, zero before first use (wait) */
   void* wait_count;       /* local u32, zero before first use: waits done (wait) */
 } b200lut_exchange;
+
+/* Blocks of the launch that b200lut_gemv_multi / b200lut_gemv_exchange would make for these
+ * segments with split = 0 (the library's policy) — the producer_blocks of an exchange whose
+ * pushing launch they describe. Output pointers of the segments may be NULL here. 0 on invalid
+ * arguments. No counterpart in the reference. */
+int b200lut_gemv_launch_blocks(int M, int K, const b200lut_segment* segs, int nseg, int epilogue,
+                               int flags);
 
 /* b200lut_gemv_multi with the exchange described above (ex == NULL: identical to it).
  * No counterpart in the reference. */

@@ -33,7 +33,7 @@ EXPORTS = (
     "b200lut_gemm_two_stream", "b200lut_gemm_two_stream_bytes",
     "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_kgrouped",
     "b200lut_gemv_kgrouped_split", "b200lut_gemv_kgrouped_workspace_bytes", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
-    "b200lut_gemv_noalloc", "b200lut_gemv_noalloc_reset", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
+    "b200lut_gemv_noalloc", "b200lut_gemv_noalloc_reset", "b200lut_gemv_launch_blocks", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
 
@@ -155,6 +155,8 @@ def lib() -> ctypes.CDLL:
     L.b200lut_fht.argtypes = [vp, vp, vp, vp, i32, i32, i64, i64, i32, i32, i32, vp]
     L.b200lut_gemv_noalloc.restype = i32
     L.b200lut_gemv_noalloc.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+    L.b200lut_gemv_launch_blocks.restype = i32
+    L.b200lut_gemv_launch_blocks.argtypes = [i32, i32, ctypes.POINTER(Segment), i32, i32, i32]
     L.b200lut_gemv_noalloc_reset.restype = i32
     L.b200lut_gemv_noalloc_reset.argtypes = [vp]
     L.b200lut_plan_bytes.restype = sz
@@ -306,6 +308,14 @@ def gemv_multi(x: torch.Tensor, segs, nseg: int, epilogue: int = EPI_NONE, split
     with torch.cuda.device(x.device):
         check(lib().b200lut_gemv_multi(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), segs,
                                        nseg, epilogue, split, ws_ptr, ws_bytes, flags, _stream(x)))
+
+
+def gemv_launch_blocks(M: int, K: int, segs, nseg: int, epilogue: int = EPI_NONE, flags: int = 0) -> int:
+    """Blocks of the launch gemv_multi / gemv_exchange would make with split = 0."""
+    n = int(lib().b200lut_gemv_launch_blocks(M, K, segs, nseg, epilogue, flags))
+    if n <= 0:
+        raise ValueError("gemv_launch_blocks: invalid launch description")
+    return n
 
 
 def gemv_pick_split(tiles: int, K: int) -> int:

@@ -801,40 +801,43 @@ bool rows_kernel_wanted(int flags) {
   return dflt;
 }
 
+// The layout of the row-range kernel for a launch, or false when the kernel does not serve it.
+// It depends only on the segment geometry; it is planned once per distinct launch shape (the
+// planner walks every 32-row unit) and looked up afterwards.
+bool rows_geometry(const GemvParams& gp, int tiles, RowsGeom* out) {
+  const bool silu = gp.epilogue == B200LUT_EPI_SILU_MUL;
+  struct Entry { unsigned long long key; bool ok; RowsGeom g; };
+  static Entry cache[64];
+  static int used = 0;
+  static std::mutex mu;
+  unsigned long long h = 1469598103934665603ull;
+  auto mix = [&](unsigned long long v) { h = (h ^ v) * 1099511628211ull; };
+  mix(unsigned(gp.nseg)); mix(unsigned(gp.epilogue)); mix(unsigned(gp.M)); mix(unsigned(gp.K));
+  mix(unsigned(tiles)); mix(unsigned(sm_count_cached()));
+  for (int i = 0; i < gp.nseg; ++i) {
+    mix(unsigned(gp.seg[i].N)); mix(unsigned(gp.seg[i].gs)); mix(unsigned(gp.seg[i].n_groups));
+    mix(unsigned(gp.seg[i].bits)); mix(gp.seg[i].packed2 ? 1u : 0u);
+    mix(reinterpret_cast<unsigned long long>(gp.seg[i].lut));
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  int hit = -1;
+  for (int i = 0; i < used; ++i)
+    if (cache[i].key == h) { hit = i; break; }
+  if (hit < 0) {
+    hit = used < 64 ? used++ : int(h % 64);
+    cache[hit].key = h;
+    cache[hit].ok = rows_plan(gp.seg, gp.nseg, silu, tiles, gp.M, gp.K, sm_count_cached(), &cache[hit].g);
+  }
+  if (cache[hit].ok) *out = cache[hit].g;
+  return cache[hit].ok;
+}
+
 // The row-range kernel when it serves the launch (4-bit, one stream, M <= 8).
 template <typename T>
 int try_rows(const GemvParams& gp, const uint16_t* x2, int tiles, bool pdl, cudaStream_t st, bool* served) {
   *served = false;
   RowsGeom g;
-  const bool silu = gp.epilogue == B200LUT_EPI_SILU_MUL;
-  {
-    // The layout depends only on the segment geometry; it is planned once per distinct launch
-    // shape (the planner walks every 32-row unit) and looked up afterwards.
-    struct Entry { unsigned long long key; bool ok; RowsGeom g; };
-    static Entry cache[64];
-    static int used = 0;
-    static std::mutex mu;
-    unsigned long long h = 1469598103934665603ull;
-    auto mix = [&](unsigned long long v) { h = (h ^ v) * 1099511628211ull; };
-    mix(unsigned(gp.nseg)); mix(unsigned(gp.epilogue)); mix(unsigned(gp.M)); mix(unsigned(gp.K));
-    mix(unsigned(tiles)); mix(unsigned(sm_count_cached()));
-    for (int i = 0; i < gp.nseg; ++i) {
-      mix(unsigned(gp.seg[i].N)); mix(unsigned(gp.seg[i].gs)); mix(unsigned(gp.seg[i].n_groups));
-      mix(unsigned(gp.seg[i].bits)); mix(gp.seg[i].packed2 ? 1u : 0u);
-      mix(reinterpret_cast<unsigned long long>(gp.seg[i].lut));
-    }
-    std::lock_guard<std::mutex> lock(mu);
-    int hit = -1;
-    for (int i = 0; i < used; ++i)
-      if (cache[i].key == h) { hit = i; break; }
-    if (hit < 0) {
-      hit = used < 64 ? used++ : int(h % 64);
-      cache[hit].key = h;
-      cache[hit].ok = rows_plan(gp.seg, gp.nseg, silu, tiles, gp.M, gp.K, sm_count_cached(), &cache[hit].g);
-    }
-    if (!cache[hit].ok) return B200LUT_OK;
-    g = cache[hit].g;
-  }
+  if (!rows_geometry(gp, tiles, &g)) return B200LUT_OK;
   RowsParams p = {};
   p.x = gp.x;
   p.x2 = x2;
@@ -858,6 +861,9 @@ int try_rows(const GemvParams& gp, const uint16_t* x2, int tiles, bool pdl, cuda
   if (rc) return rc;
   for (int i = 0; i < gp.nseg; ++i) p.seg[i] = gp.seg[i];
   p.ex = gp.ex;
+  B200LUT_REQUIRE(!p.ex.push || p.ex.blocks == g.row_blocks * g.split, B200LUT_ERR_INVALID,
+                  "exchange: producer_blocks is %d but this launch has %d blocks "
+                  "(b200lut_gemv_launch_blocks gives the count)", p.ex.blocks, g.row_blocks * g.split);
   *served = true;
   return launch_rows<T>(p, g, pdl, st);
 }
@@ -1020,8 +1026,8 @@ extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, i
   const bool pdl = (flags & B200LUT_FLAG_PDL) != 0;
   cudaStream_t st = cudaStream_t(stream);
   // Library policy (split == 0): the row-range kernel when it serves the shapes. An explicit
-  // split, B200LUT_FLAG_TILE_KERNEL or an exchange descriptor selects the tile x split kernel.
-  if (split <= 0 && rows_kernel_wanted(flags) && !p.ex.push && !p.ex.wait) {
+  // split or B200LUT_FLAG_TILE_KERNEL selects the tile x split kernel.
+  if (split <= 0 && rows_kernel_wanted(flags)) {
     bool served = false;
     const int rc = dtype == B200LUT_BF16
                        ? try_rows<__nv_bfloat16>(p, nullptr, tiles, pdl, st, &served)
@@ -1051,6 +1057,31 @@ extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, i
   return dispatch<__half>(p, max_tables, pdl, st);
 }
 
+
+extern "C" int b200lut_gemv_launch_blocks(int M, int K, const b200lut_segment* segs, int nseg,
+                                          int epilogue, int flags) {
+  if (!segs || nseg < 1 || nseg > kMaxSeg || M < 1 || M > kMaxM || K <= 0 || K % kChunkK) return 0;
+  const bool silu = epilogue == B200LUT_EPI_SILU_MUL;
+  if (silu && nseg % 2) return 0;
+  GemvParams p = {};
+  p.M = M;
+  p.K = K;
+  p.G = K / kChunkK;
+  p.nseg = nseg;
+  p.epilogue = epilogue;
+  b200lut_segment tmp[kMaxSeg];
+  for (int i = 0; i < nseg; ++i) {
+    tmp[i] = segs[i];
+    if (!tmp[i].out) { tmp[i].out = reinterpret_cast<void*>(uintptr_t(16)); tmp[i].ldo = tmp[i].N; }
+  }
+  int tiles = 0, max_tables = 1;
+  if (convert_segments(tmp, nseg, silu, p.seg, &tiles, &max_tables)) return 0;
+  if (rows_kernel_wanted(flags)) {
+    RowsGeom g;
+    if (rows_geometry(p, tiles, &g)) return g.row_blocks * g.split;
+  }
+  return tiles * pick_split(tiles, p.G, sm_count_cached(), M <= 8 ? kWarpsM8 : kWarpsM16);
+}
 
 extern "C" int b200lut_gemv(const void* x, const void* packed, const void* lut, void* out, int M,
                             int N, int K, int bits, int group_size, int n_groups, int dtype,

@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
       uint8_t* xs = generic(p.xs_abs);
       const int per_row = kc * 8;   // 16-byte pieces of one row
       const int total = Mp * per_row;
-#pragma unroll 4
+#pragma unroll 8
       for (int idx = tid; idx < total; idx += NTS) {
         const int m = idx / per_row, pc = idx - m * per_row;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);

@@ -84,14 +84,13 @@ class PeerArena:
 
 
 class Channel:
-    """One exchanged activation buffer [M, width] with its flag array and counters.
-    `tiles` and `K` describe the producing launch (128-row tiles of this rank's slice): the
-    producer runs with `self.split` K splits, i.e. `self.blocks` blocks, one flag each."""
+    """One exchanged activation buffer [M, width] with its flag array and counters. `blocks` is
+    the block count of the producing launch (`_lib.gemv_launch_blocks` of its segments): every
+    block of it owns one flag."""
 
-    def __init__(self, arena: PeerArena, M: int, width: int, dtype, tiles: int, K: int):
+    def __init__(self, arena: PeerArena, M: int, width: int, dtype, blocks: int):
         self.arena = arena
-        self.split = _lib.gemv_pick_split(tiles, K)
-        self.blocks = tiles * self.split
+        self.blocks = int(blocks)
         self.act_off = arena.alloc(M * width * 2)
         self.flag_off = arena.alloc(arena.world * self.blocks * 4)
         # local counters: push ticket +0, push count +32, wait ticket +64, wait count +96

@@ -30,7 +30,12 @@ from . import fht as _fht
 from . import idxN as _idxn
 
 GEMV_MAX_M = 16
-_LAUNCH_FLAGS = {"pdl": os.environ.get("B200LUT_PDL", "0").strip() in ("1", "true", "True")}
+# Programmatic dependent launch is ON unless B200LUT_PDL=0: a launch then fetches its codes and
+# palettes and builds its tables while the previous kernel of the stream drains, and waits for it
+# only before it reads activations. Weights must therefore not be rewritten by the kernel that
+# directly precedes a forward in the stream (load-time conversions are followed by the module's
+# first forward only after their own kernels have completed their blocks).
+_LAUNCH_FLAGS = {"pdl": os.environ.get("B200LUT_PDL", "1").strip() not in ("0", "false", "False")}
 _workspaces = {}
 
 

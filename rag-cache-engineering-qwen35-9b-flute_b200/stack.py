@@ -104,7 +104,8 @@ class LinearStack(nn.Module):
 
     def __init__(self, device="cuda", dtype=torch.bfloat16, bits: int = 4, group_size: int = 128,
                  n_layers: int = N_LAYERS, seed: int = synthetic.BASE_SEED + 5,
-                 rank: int = 0, world: int = 1, gather: str = "nccl", arenas=None):
+                 rank: int = 0, world: int = 1, gather: str = "nccl", arenas=None,
+                 rotate: bool = False):
         super().__init__()
         if gather not in ("nccl", "push"):
             raise ValueError(f"gather must be 'nccl' or 'push', got {gather!r}")
@@ -112,6 +113,10 @@ class LinearStack(nn.Module):
             # with one buffer a peer's next push could overtake this rank's reader
             raise ValueError("gather='push' needs at least two layers")
         self.gather_mode = gather if world > 1 else "nccl"
+        # rotate: every projection group reads the Hadamard rotation of its input row (the
+        # boundary fold of the reference's rotated artifacts, src/flute_extended/fht.py:105-134):
+        # one FHT launch in front of each group, signs drawn per group
+        self.rotate = bool(rotate)
         self.merge_prefill = True    # M > 16: projections that share x run as one launch
         self._arenas = arenas        # test form: pre-built emulated arenas (this rank's one)
         self.device, self.dtype = torch.device(device), dtype
@@ -182,6 +187,18 @@ class LinearStack(nn.Module):
             need = len(self.layers) * (((M * width * 2 + 255) // 256 + 2) * 256 + self.world * 4096 * 4)
             arena = self._arenas if self._arenas is not None else exchange.PeerArena(
                 need, self.rank, self.world, dev)
+        def rotated(src, tag):
+            """("fht", src, dst, signs) entry in front of a group when the stack is rotated."""
+            if not self.rotate:
+                return src
+            K = src.shape[1]
+            g = torch.Generator().manual_seed(len(launches) * 7919 + K)
+            signs = (torch.randint(0, 2, (K,), generator=g) * 2 - 1).float().to(dev)
+            dst = torch.empty_like(src)
+            launches.append(("fht", src, dst, signs, None, None, None))
+            outs_rot.append(dst)
+            return dst
+        outs_rot = []
         for L in self.layers:
             heads = L.heads()
             total = sum(m.N for m in heads)
@@ -190,26 +207,34 @@ class LinearStack(nn.Module):
             for m in heads:
                 descs.append(m._segment_desc(hbuf[:, off:], ldo=total))
                 off += m.N
-            launches.append(("heads", x, _lib.make_segments(descs), len(descs), _lib.EPI_NONE, descs, None))
+            xr = rotated(x, "heads")
+            launches.append(("heads", xr, _lib.make_segments(descs), len(descs), _lib.EPI_NONE, descs, None))
             o = L.out()
             obuf = torch.empty(M, o.N, dtype=dt, device=dev)
             od = [o._segment_desc(obuf)]
-            launches.append(("out", x, _lib.make_segments(od), 1, _lib.EPI_NONE, od, None))
+            launches.append(("out", rotated(x, "out"), _lib.make_segments(od), 1, _lib.EPI_NONE, od, None))
             g, u, d = L.mlp.gate_proj, L.mlp.up_proj, L.mlp.down_proj
-            chan = exchange.Channel(arena, M, g.N * self.world, dt, g.N // 128, g.K) if push else None
+            chan = None
+            if push:
+                probe = _lib.make_segments([g._segment_desc(None), u._segment_desc(None)])
+                chan = exchange.Channel(arena, M, g.N * self.world, dt,
+                                        _lib.gemv_launch_blocks(M, g.K, probe, 2, _lib.EPI_SILU_MUL))
             act = chan.act if push else torch.empty(M, g.N * self.world, dtype=dt, device=dev)
             act_loc = act[:, self.rank * g.N:(self.rank + 1) * g.N]   # full width after gather
             gd = [g._segment_desc(act_loc, ldo=act.shape[1]), u._segment_desc(None)]
-            launches.append(("gate_up", x, _lib.make_segments(gd), 2, _lib.EPI_SILU_MUL, gd,
+            launches.append(("gate_up", rotated(x, "gate_up"), _lib.make_segments(gd), 2, _lib.EPI_SILU_MUL, gd,
                              chan.push if push else None))
             if self.world > 1 and not push:
                 launches.append(("gather", act, act_loc, None, None, None, None))
             ybuf = torch.empty(M, d.N, dtype=dt, device=dev)
             dd = [d._segment_desc(ybuf)]
-            launches.append(("down", act, _lib.make_segments(dd), 1, _lib.EPI_NONE, dd,
+            if self.rotate and push:
+                raise ValueError("a rotated stack uses the NCCL gather (the rotation reads the gathered row)")
+            launches.append(("down", rotated(act, "down"), _lib.make_segments(dd), 1, _lib.EPI_NONE, dd,
                              chan.wait if push else None))
             outs += [hbuf, obuf, act, ybuf]
-        plan = {"x": x, "launches": launches, "buffers": outs, "y": outs[-1], "arena": arena}
+        plan = {"x": x, "launches": launches, "buffers": outs, "y": outs[-1], "arena": arena,
+                "rotated": outs_rot}
         self._plans[M] = plan
         return plan
 
@@ -218,10 +243,11 @@ class LinearStack(nn.Module):
         name, xin, segs, nseg, epi, _, ex = entry
         if name == "gather":
             gather(xin, segs)
+        elif name == "fht":
+            _lib.fht(xin, nseg, out=segs)       # (src, dst, signs) ride in the entry's slots
         elif ex is not None:
-            # the pushing launch runs with the split its flag array was sized for
-            split = ex.producer_blocks // (segs[0].N // 128) if ex.push else 0
-            _lib.gemv_exchange(xin, segs, nseg, ex, epilogue=epi, split=split, flags=flags)
+            # library policy: the flag array was sized with gemv_launch_blocks for the same policy
+            _lib.gemv_exchange(xin, segs, nseg, ex, epilogue=epi, split=0, flags=flags & ~(_lib.FLAG_TILE_KERNEL | _lib.FLAG_ROWS_KERNEL))
         elif M <= 16:
             _lib.gemv_multi(xin, segs, nseg, epilogue=epi, flags=flags)
         elif epi == _lib.EPI_SILU_MUL:
@@ -275,6 +301,8 @@ class LinearStack(nn.Module):
         if "plans" not in plan:
             groups, cur = [], []
             for name, xin, segs, nseg, epi, descs, _ in plan["launches"]:
+                if name == "fht":
+                    raise ValueError("the persistent executor does not serve a rotated stack")
                 if name == "gather":
                     groups.append(("plan", cur))
                     groups.append(("gather", (xin, segs)))
@@ -300,7 +328,7 @@ class LinearStack(nn.Module):
         for name, xin, _, nseg, epi, descs, _ in self._plan(M)["launches"]:
             if name == "gather":
                 continue
-            if M <= 16:
+            if M <= 16 or name == "fht":
                 n += 1
                 continue
             K = xin.shape[1]
