@@ -14,8 +14,9 @@ from .artifacts import (load_metadata, load_palettized_embedding, load_palettize
                         load_tied_pair, replace_linear_with_palettized)
 from .lut_export import export_luts, import_luts, iter_palettized_linears      # noqa: F401
 from .loader import load_quant_model                                             # noqa: F401
+from . import flute_extended                                                     # noqa: F401
 
 __all__ = ["load_quant_model", "load_palettized_weight", "replace_linear_with_palettized",
            "load_palettized_embedding", "load_tied_pair", "export_luts", "import_luts",
            "iter_palettized_linears", "load_metadata", "PalettizedLinear", "PalettizedEmbedding", "KGroupedPalettizedLinear", "SplitQKV", "FusedPalettizedMLP", "reference_dequant",
-           "set_programmatic_launch", "fht", "idxN", "synthetic"]
+           "set_programmatic_launch", "fht", "idxN", "synthetic", "flute_extended"]

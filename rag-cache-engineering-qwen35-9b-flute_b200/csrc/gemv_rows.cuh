@@ -525,9 +525,12 @@ bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, i
   } else {
     row_blocks = U;
     slots = ppu;
+    // K is split over a cluster only down to 64 chunks per part: a part then still streams
+    // 64 KB per unit (about as long as the cluster fold costs) and keeps its activation
+    // fragments in registers.
     split = sms / U;
     if (split > kMaxClusterSplit) split = kMaxClusterSplit;
-    if (split > G) split = G;
+    if (split > G / (kRowsWarps * kRowsRing)) split = G / (kRowsWarps * kRowsRing);
     if (split < 1) split = 1;
   }
   g->units_total = U;

@@ -99,78 +99,85 @@ class PalettizedLinear(nn.Module):
                  rotation_seed: int = None, rotation_k: int = None,
                  awq_scale=None, fold_order: str = None):
         super().__init__()
-        self.bitwidth = int(bitwidth)
-        self.group_size = int(group_size)
-        self.bitwidth2 = int(bitwidth2) if bitwidth2 is not None else self.bitwidth
         self.N, self.K = int(N), int(K)
+        self.bitwidth = int(bitwidth)
+        self.bitwidth2 = self.bitwidth if bitwidth2 is None else int(bitwidth2)
+        self.group_size = int(group_size)
         self.reference = bool(reference)
-        if self.N % 128 != 0 or self.K % 64 != 0:
-            raise ValueError(f"idxN layout requires N%128==0 and K%64==0, got N={self.N}, K={self.K}")
-        for name, b in (("stream-1", self.bitwidth), ("stream-2", self.bitwidth2)):
-            if b not in (1, 2, 3, 4):
-                raise ValueError(f"PalettizedLinear: {name} bitwidth must be 1-4, got {b}")
-        indices = torch.as_tensor(indices)
-        expected = (self.N * self.K * self.bitwidth) // 8
-        if indices.numel() != expected:
-            raise ValueError(f"idx{self.bitwidth} blob numel {indices.numel()} != "
-                             f"N*K*{self.bitwidth}/8 {expected} (N={self.N}, K={self.K})")
-        self.register_buffer("indices", indices, persistent=False)
+        self._dev_cache = {}
+        self._packed = self._packed2 = None
+
+        # --- geometry the slab / idxN layouts can express
+        if self.N % 128 or self.K % 64:
+            raise ValueError(f"PalettizedLinear: the code layout tiles 128 rows x 64 columns, so N%128 and "
+                             f"K%64 must be 0 (N={self.N}, K={self.K})")
+        for label, width in (("bitwidth", self.bitwidth), ("bitwidth2", self.bitwidth2)):
+            if not 1 <= width <= 4:
+                raise ValueError(f"PalettizedLinear: {label}={width}; code widths are 1, 2, 3 or 4 bits")
+
+        # --- code streams: stream 1 always, stream 2 as a complete pair or not at all
+        self.register_buffer("indices", self._checked_blob(indices, self.bitwidth, "stream 1"), persistent=False)
         self.register_buffer("lut", self._lut2d(lut, self.bitwidth), persistent=False)
-        if resA is not None and resB is not None:
-            if resA.shape != (self.N, resB.shape[0]) or resB.shape[1] != self.K:
-                raise ValueError(f"residual factors shape mismatch: A {tuple(resA.shape)}, "
-                                 f"B {tuple(resB.shape)} for N={self.N}, K={self.K}")
+        if (indices2 is None) != (lut2 is None):
+            raise ValueError("PalettizedLinear: a second code stream is given by BOTH indices2 and lut2 "
+                             "(one of them is missing)")
+        if indices2 is None:
+            self.indices2 = self.lut2 = None
+        else:
+            palette2 = self._lut2d(lut2, self.bitwidth2)
+            if palette2.shape[0] != self.lut.shape[0]:
+                raise ValueError(f"PalettizedLinear: the two streams must share one row-group grid; "
+                                 f"stream 1 has {self.lut.shape[0]} palettes, stream 2 has {palette2.shape[0]}")
+            self.register_buffer("indices2", self._checked_blob(indices2, self.bitwidth2, "stream 2"),
+                                 persistent=False)
+            self.register_buffer("lut2", palette2, persistent=False)
+
+        # --- low-rank residual (both factors) and bias
+        if resA is None or resB is None:
+            self.resA = self.resB = None
+        else:
+            rank = resB.shape[0]
+            if tuple(resA.shape) != (self.N, rank) or resB.shape[1] != self.K:
+                raise ValueError(f"PalettizedLinear: residual factors must be resA [N, R] and resB [R, K]; got "
+                                 f"{tuple(resA.shape)} and {tuple(resB.shape)} for N={self.N}, K={self.K}")
             self.register_buffer("resA", resA, persistent=False)
             self.register_buffer("resB", resB, persistent=False)
-        else:
-            self.resA = self.resB = None
-        if indices2 is None and lut2 is None:
-            self.indices2 = self.lut2 = None
-        elif indices2 is None or lut2 is None:
-            raise ValueError("PalettizedLinear: a second stream needs BOTH indices2 and lut2; "
-                             "refusing a half-constructed two-stream module")
-        else:
-            indices2 = torch.as_tensor(indices2)
-            expected2 = (self.N * self.K * self.bitwidth2) // 8
-            if indices2.numel() != expected2:
-                raise ValueError(f"idx{self.bitwidth2} stream-2 blob numel {indices2.numel()} != "
-                                 f"N*K*{self.bitwidth2}/8 {expected2} (N={self.N}, K={self.K})")
-            lut2_t = self._lut2d(lut2, self.bitwidth2)
-            if lut2_t.shape[0] != self.lut.shape[0]:
-                raise ValueError(f"stream-2 LUT groups {lut2_t.shape[0]} != stream-1 "
-                                 f"{self.lut.shape[0]}; both streams must share the group grid")
-            self.register_buffer("indices2", indices2, persistent=False)
-            self.register_buffer("lut2", lut2_t, persistent=False)
-        if bias is not None:
-            self.bias = nn.Parameter(bias, requires_grad=False)
-        else:
+        if bias is None:
             self.register_parameter("bias", None)
-        # rotation (Hadamard boundary fold; None = unrotated)
-        self.rotation_seed = int(rotation_seed) if rotation_seed is not None else None
-        self.rotation_k = int(rotation_k) if rotation_k is not None else None
+        else:
+            self.bias = nn.Parameter(bias, requires_grad=False)
+
+        # --- input rotation: the signs are a pure function of (K, seed); an AWQ scale only makes
+        #     sense on a rotated module
+        self.rotation_seed = None if rotation_seed is None else int(rotation_seed)
+        self.rotation_k = None if rotation_k is None else int(rotation_k)
         self.fold_order = fold_order if fold_order in ("awq_then_rotate", "rotate_then_awq") else None
-        self.rot_signs = None
-        self.awq_scale = None
-        self._dev_cache = {}
-        if self.rotation_seed is not None and self.rotation_k is not None:
-            if self.rotation_k != self.K:
-                raise ValueError(f"PalettizedLinear: rotation_k {self.rotation_k} != the input "
-                                 f"dim K {self.K} — the boundary fold is defined on the input axis")
+        self.rot_signs = self.awq_scale = None
+        rotated = self.rotation_seed is not None and self.rotation_k is not None
+        if rotated and self.rotation_k != self.K:
+            raise ValueError(f"PalettizedLinear: rotation_k={self.rotation_k} but the rotation acts on the "
+                             f"input axis, K={self.K}")
+        if awq_scale is not None and not rotated:
+            raise ValueError("PalettizedLinear: awq_scale without rotation metadata (rotation_seed, rotation_k)")
+        if rotated:
             self.rot_signs = _fht.rotation_signs(self.rotation_k, self.rotation_seed)
-            if awq_scale is not None:
-                st = torch.as_tensor(awq_scale, dtype=torch.float32).detach().cpu()
-                if st.dim() != 1 or st.numel() != self.K:
-                    raise ValueError(f"PalettizedLinear: awq_scale must be a (K,) vector for "
-                                     f"K={self.K}, got {tuple(st.shape)}")
-                if not torch.isfinite(st).all() or bool((st <= 0).any()):
-                    raise ValueError("PalettizedLinear: awq_scale must be finite and > 0 per channel")
-                self.awq_scale = st
-                if self.fold_order is None:
-                    self.fold_order = "rotate_then_awq"
-        elif awq_scale is not None:
-            raise ValueError("PalettizedLinear: awq_scale passed without rotation metadata")
-        self._packed = None
-        self._packed2 = None
+        if awq_scale is not None:
+            scale = torch.as_tensor(awq_scale, dtype=torch.float32).detach().cpu()
+            if scale.dim() != 1 or scale.numel() != self.K:
+                raise ValueError(f"PalettizedLinear: awq_scale has shape {tuple(scale.shape)}; one value per "
+                                 f"input channel (K={self.K}) is expected")
+            if not bool(torch.isfinite(scale).all()) or bool((scale <= 0).any()):
+                raise ValueError("PalettizedLinear: every awq_scale entry must be finite and positive")
+            self.awq_scale = scale
+            self.fold_order = self.fold_order or "rotate_then_awq"
+
+    def _checked_blob(self, blob, width: int, label: str) -> torch.Tensor:
+        blob = torch.as_tensor(blob)
+        want = self.N * self.K * width // 8
+        if blob.numel() != want:
+            raise ValueError(f"PalettizedLinear: {label}: idx{width} blob numel is {blob.numel()}, "
+                             f"N*K*{width}/8 = {want} bytes are needed (N={self.N}, K={self.K})")
+        return blob
 
     @staticmethod
     def _lut2d(lut, bits):
@@ -648,6 +655,7 @@ class PalettizedEmbedding(nn.Module):
         self._packed = None
         self._packed2 = None
         self._tied = []          # [PalettizedLinear] whose slab copies serve this table
+        self._bad_ids = None     # device flag: a forward met a CUDA id outside [0, N)
 
     @classmethod
     def tied_to(cls, lm: PalettizedLinear) -> "PalettizedEmbedding":
@@ -673,6 +681,7 @@ class PalettizedEmbedding(nn.Module):
             emb.rotation_seed, emb.rotation_k = lm.rotation_seed, lm.rotation_k
             emb.rot_signs, emb._signs_cache = lm.rot_signs, {}
             emb._packed = emb._packed2 = None
+            emb._bad_ids = None
         emb._tied = [lm]
         return emb
 
@@ -747,6 +756,13 @@ class PalettizedEmbedding(nn.Module):
                              f"{int(ids.min())}, max {int(ids.max())}); refusing a silent wrap")
         table = self._table()
         flat = ids.to(device=self.lut.device, dtype=torch.int64).reshape(-1).contiguous()
+        if ids.is_cuda and flat.numel():
+            # Device-resident ids cannot be refused here without a host sync (the reference
+            # asserts on the device, which would lose the context). The kernel writes zeros for
+            # such an id; the module remembers that it happened, without a sync, and
+            # check_ids() raises at a moment the host chooses.
+            bad = ((flat < 0) | (flat >= self.N)).any()
+            self._bad_ids = bad if self._bad_ids is None else (self._bad_ids | bad)
         dtype = self.lut.dtype
         if self.rot_signs is None:
             out = _lib.embed_gather(flat, table, self.K, dtype)
@@ -756,6 +772,17 @@ class PalettizedEmbedding(nn.Module):
                 w = _lib.fht(w, self._signs_on(w.device), _lib.FHT_ADJOINT, out=w)
             out = _lib.round_rows(w, dtype)
         return out.view(*ids.shape, self.K)
+
+
+    def check_ids(self) -> None:
+        """Raise if any forward since the last check met a CUDA id outside [0, N) (those rows
+        were gathered as zeros). Synchronises once; clears the record and the library's device
+        status word (0x6000) that the gather kernel raised."""
+        bad, self._bad_ids = self._bad_ids, None
+        if bad is not None and bool(bad.item()):
+            _lib.lib().b200lut_device_status()
+            raise ValueError(f"PalettizedEmbedding: ids out of range [0, {self.N}) were gathered as "
+                             f"zero rows since the last check")
 
 
 class KGroupedPalettizedLinear(nn.Module):

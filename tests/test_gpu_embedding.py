@@ -155,3 +155,26 @@ def test_c_entry_with_a_strided_unaligned_output():
                                          L._stream(ids)))
     assert torch.equal(w.cpu(), want.float())
     assert torch.equal(L.round_rows(w, torch.float16).cpu(), want)
+
+
+def test_cuda_ids_out_of_range_are_zero_rows_and_reported():
+    """Ids that live on the device cannot be refused before the launch without a host sync: the
+    kernel writes zero rows for them (the reference asserts on the device and loses the context,
+    src/scripts/palettized_modules.py:1957-1976, 2300-2306); the module records it and check_ids()
+    raises. Ids on the host are refused up front, as the reference does."""
+    N, K = 256, 128
+    codes, blob = pkg.synthetic.make_blob(N, K, 4, 5)
+    lut = pkg.synthetic.make_lut(N // 128, 4, torch.bfloat16, 5)
+    emb = pkg.PalettizedEmbedding(blob, lut, 4, 128, N, K).cuda()
+    good = torch.tensor([0, 5, 255], device="cuda")
+    emb(good)
+    emb.check_ids()                                   # nothing recorded
+    rows = emb(torch.tensor([3, N, -1, 7], device="cuda"))
+    assert bool((rows[1] == 0).all()) and bool((rows[2] == 0).all())
+    assert torch.equal(rows[0], emb(torch.tensor([3], device="cuda"))[0])
+    with pytest.raises(ValueError, match="out of range"):
+        emb.check_ids()
+    emb.check_ids()                                   # the record is cleared
+    assert pkg._lib.lib().b200lut_device_status() == 0
+    with pytest.raises(ValueError, match="out of range"):
+        emb(torch.tensor([N]))

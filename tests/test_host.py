@@ -202,7 +202,7 @@ def test_constructor_contracts():
         PL(blob, lut, 4, 128, 128, 64, rotation_seed=1, rotation_k=128)
     with pytest.raises(ValueError, match="without rotation"):
         PL(blob, lut, 4, 128, 128, 64, awq_scale=torch.ones(64))
-    with pytest.raises(ValueError, match="finite"):
+    with pytest.raises(ValueError, match="finite and positive"):
         PL(blob, lut, 4, 128, 128, 64, rotation_seed=1, rotation_k=64, awq_scale=torch.zeros(64))
     r = PL(blob, lut, 4, 128, 128, 64, rotation_seed=3, rotation_k=64, awq_scale=torch.ones(64))
     assert r.fold_order == "rotate_then_awq"
