@@ -663,7 +663,7 @@ def stack_point(pkg, stack, M: int, flags: int, iters: int):
     xin = x
     if stack.rotate:
         from oracle import lut_linear_oracle as orc
-        signs = plan["launches"][0][3].cpu()
+        signs = plan["rotated"][0].cpu()
         xin = orc.fht_forward(x, signs)
     got = plan["buffers"][0][:, :q.N]
     return ms, sampled_gate(pkg, q._packed, q.lut, q.N, q.K, q.bitwidth, q.group_size, xin, got)
@@ -738,6 +738,11 @@ def run_extras(pkg, st, stack, peaks, flags):
         ms, g = stack_point(pkg, rot, 1, flags, 10)
         put("stack_m1_rotated", {"ms_per_step": ms, "tok/s": 1e3 / ms, "launches_per_step": rot.launches_per_step(1),
                                  "note": "one FHT launch (segments + signs) in front of each of the 128 projection groups"}, g)
+        del rot
+        rot = st.LinearStack(device=stack.device, n_layers=len(stack.layers), rotate="fused")
+        ms, g = stack_point(pkg, rot, 1, flags, 10)
+        put("stack_m1_rotated_fused", {"ms_per_step": ms, "tok/s": 1e3 / ms, "launches_per_step": rot.launches_per_step(1),
+                                       "note": "the rotation runs inside each decode launch (b200lut_gemv_input)"}, g)
         del rot
         torch.cuda.empty_cache()
 

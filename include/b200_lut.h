@@ -256,6 +256,32 @@ int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, int dtype,
                           void* workspace, size_t workspace_bytes, int flags,
                           const b200lut_exchange* ex, void* stream);
 
+/* What a decode launch does to its activation rows before it multiplies, inside the launch
+ * (every block transforms the rows it stages; no extra kernel, no round trip through memory):
+ *   x_mul      non-NULL: x := silu(x) * x_mul, element-wise, fp32 inside, one rounding — the
+ *              act_fn(gate) * up in front of down_proj (src/scripts/modeling.py:1001-1003) when
+ *              gate and up were left as two plain outputs; x_mul has x's shape and row stride;
+ *   rot_signs  non-NULL: x := Hadamard rotation of x, descending power-of-two segments of K,
+ *              signs on the output, 1/sqrt(b) — bit-identical to b200lut_fht(FORWARD). Replaces
+ *              the reference's fused prologue gemv_fht_prologue
+ *              (src/flute_extended/include/flute/gemv.cuh:305-351; kernel_gemv.cu:579-776);
+ *   awq_scale  with rot_signs: the compensated form ((x * s) H * signs / sqrt(b)) / s
+ *              (b200lut_fht mode AWQ). (K,) fp32 each.
+ * x_mul is applied first. Served for 4-bit single-stream segments, M <= 8, split = 0 (the
+ * row-range kernel); other requests return B200LUT_ERR_UNSUPPORTED and the caller transforms the
+ * rows with b200lut_silu_mul / b200lut_fht first. */
+typedef struct b200lut_input {
+  const void* x_mul;
+  const float* rot_signs;
+  const float* awq_scale;
+} b200lut_input;
+
+/* b200lut_gemv_exchange with an input transform (in == NULL: identical to it). */
+int b200lut_gemv_input(const void* x, int64_t ldx, int M, int K, int dtype,
+                       const b200lut_segment* segs, int nseg, int epilogue, int split,
+                       void* workspace, size_t workspace_bytes, int flags,
+                       const b200lut_exchange* ex, const b200lut_input* in, void* stream);
+
 /* Sharing a device buffer between the ranks (processes) of one box. export: fills a 64-byte
  * handle for the allocation that contains ptr and the offset of ptr inside it (the buffer
  * must come from cudaMalloc, directly or through a caching allocator). open: maps another

@@ -33,7 +33,7 @@ EXPORTS = (
     "b200lut_gemm_two_stream", "b200lut_gemm_two_stream_bytes",
     "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_kgrouped",
     "b200lut_gemv_kgrouped_split", "b200lut_gemv_kgrouped_workspace_bytes", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
-    "b200lut_gemv_noalloc", "b200lut_gemv_noalloc_reset", "b200lut_gemv_launch_blocks", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
+    "b200lut_gemv_noalloc", "b200lut_gemv_noalloc_reset", "b200lut_gemv_launch_blocks", "b200lut_gemv_input", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
 
@@ -72,6 +72,11 @@ class Exchange(ctypes.Structure):
         ("ticket", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("flags", ctypes.c_void_p),
         ("wait_ticket", ctypes.c_void_p), ("wait_count", ctypes.c_void_p),
     ]
+
+
+class Input(ctypes.Structure):
+    """struct b200lut_input: what a decode launch does to its activation rows first."""
+    _fields_ = [("x_mul", ctypes.c_void_p), ("rot_signs", ctypes.c_void_p), ("awq_scale", ctypes.c_void_p)]
 
 
 class LibraryError(RuntimeError):
@@ -155,6 +160,9 @@ def lib() -> ctypes.CDLL:
     L.b200lut_fht.argtypes = [vp, vp, vp, vp, i32, i32, i64, i64, i32, i32, i32, vp]
     L.b200lut_gemv_noalloc.restype = i32
     L.b200lut_gemv_noalloc.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+    L.b200lut_gemv_input.restype = i32
+    L.b200lut_gemv_input.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32,
+                                     i32, vp, sz, i32, ctypes.POINTER(Exchange), ctypes.POINTER(Input), vp]
     L.b200lut_gemv_launch_blocks.restype = i32
     L.b200lut_gemv_launch_blocks.argtypes = [i32, i32, ctypes.POINTER(Segment), i32, i32, i32]
     L.b200lut_gemv_noalloc_reset.restype = i32
@@ -331,6 +339,29 @@ def gemv_exchange(x: torch.Tensor, segs, nseg: int, ex: "Exchange", epilogue: in
         check(lib().b200lut_gemv_exchange(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), segs,
                                           nseg, epilogue, split, None, 0, flags,
                                           ctypes.byref(ex), _stream(x)))
+
+
+def make_input(x_mul: Optional[torch.Tensor] = None, rot_signs: Optional[torch.Tensor] = None,
+               awq_scale: Optional[torch.Tensor] = None) -> Input:
+    """An input transform for gemv_input (tensors must stay alive while it is used)."""
+    for name, v in (("rot_signs", rot_signs), ("awq_scale", awq_scale)):
+        if v is not None and (v.dtype != torch.float32 or not v.is_contiguous() or not v.is_cuda):
+            raise ValueError(f"{name} must be a contiguous float32 CUDA tensor")
+    inp = Input()
+    inp.x_mul, inp.rot_signs, inp.awq_scale = ptr(x_mul), ptr(rot_signs), ptr(awq_scale)
+    return inp
+
+
+def gemv_input(x: torch.Tensor, segs, nseg: int, inp: Input, epilogue: int = EPI_NONE, flags: int = 0,
+               ex: Optional["Exchange"] = None) -> None:
+    """gemv_multi whose launch first transforms the activation rows (silu(x) * x_mul, Hadamard
+    rotation); raises LibraryError (code 2) when the shapes are not served in fused form."""
+    _need_cuda(x, "x")
+    M, K = x.shape
+    with torch.cuda.device(x.device):
+        check(lib().b200lut_gemv_input(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype), segs, nseg,
+                                       epilogue, 0, None, 0, flags,
+                                       None if ex is None else ctypes.byref(ex), ctypes.byref(inp), _stream(x)))
 
 
 def peer_export(t: torch.Tensor):

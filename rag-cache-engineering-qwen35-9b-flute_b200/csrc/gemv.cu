@@ -29,6 +29,7 @@
 //    kernel's tail; only x depends on the predecessor.
 #include <cooperative_groups.h>
 
+#include <cmath>
 #include <cstdlib>
 #include <mutex>
 #include <vector>
@@ -86,6 +87,10 @@ struct GemvParams {
   int* tickets;    // workspace fold: [tiles_total]
   SegDev seg[kMaxSeg];
   ExchangeDev ex;
+  // what the launch does to the activation rows first (row-range kernel only)
+  const uint16_t* x_mul;     // x := silu(x) * x_mul
+  const float* rot_signs;    // x := Hadamard rotation of x (segments + signs)
+  const float* awq_scale;    // ... in the AWQ-compensated form
 };
 
 template <typename T>
@@ -814,6 +819,13 @@ bool rows_geometry(const GemvParams& gp, int tiles, RowsGeom* out) {
   auto mix = [&](unsigned long long v) { h = (h ^ v) * 1099511628211ull; };
   mix(unsigned(gp.nseg)); mix(unsigned(gp.epilogue)); mix(unsigned(gp.M)); mix(unsigned(gp.K));
   mix(unsigned(tiles)); mix(unsigned(sm_count_cached()));
+  uint32_t fht_bytes = 0;
+  if (gp.rot_signs) {   // fp32 scratch of the largest power-of-two segment of K
+    int b = 1;
+    while (b * 2 <= gp.K) b *= 2;
+    fht_bytes = uint32_t(b) * 4u;
+  }
+  mix(fht_bytes);
   for (int i = 0; i < gp.nseg; ++i) {
     mix(unsigned(gp.seg[i].N)); mix(unsigned(gp.seg[i].gs)); mix(unsigned(gp.seg[i].n_groups));
     mix(unsigned(gp.seg[i].bits)); mix(gp.seg[i].packed2 ? 1u : 0u);
@@ -826,7 +838,7 @@ bool rows_geometry(const GemvParams& gp, int tiles, RowsGeom* out) {
   if (hit < 0) {
     hit = used < 64 ? used++ : int(h % 64);
     cache[hit].key = h;
-    cache[hit].ok = rows_plan(gp.seg, gp.nseg, silu, tiles, gp.M, gp.K, sm_count_cached(), &cache[hit].g);
+    cache[hit].ok = rows_plan(gp.seg, gp.nseg, silu, tiles, gp.M, gp.K, sm_count_cached(), fht_bytes, &cache[hit].g);
   }
   if (cache[hit].ok) *out = cache[hit].g;
   return cache[hit].ok;
@@ -840,7 +852,27 @@ int try_rows(const GemvParams& gp, const uint16_t* x2, int tiles, bool pdl, cuda
   if (!rows_geometry(gp, tiles, &g)) return B200LUT_OK;
   RowsParams p = {};
   p.x = gp.x;
-  p.x2 = x2;
+  p.x2 = x2 ? x2 : gp.x_mul;
+  if (gp.rot_signs) {
+    p.rot_signs = gp.rot_signs;
+    p.awq_scale = gp.awq_scale;
+    p.fht_abs = g.fht_abs;
+    int off = 0;
+    while (off < gp.K) {
+      int b = 1, stages = 0;
+      while (b * 2 <= gp.K - off) b *= 2;
+      while ((1 << stages) < b) ++stages;
+      B200LUT_REQUIRE(p.fht_nseg < kRowsMaxFhtSegs, B200LUT_ERR_UNSUPPORTED,
+                      "K=%d splits into more than %d power-of-two segments: rotate with b200lut_fht first",
+                      gp.K, kRowsMaxFhtSegs);
+      p.fht_off[p.fht_nseg] = off;
+      p.fht_len[p.fht_nseg] = b;
+      p.fht_stages[p.fht_nseg] = stages;
+      p.fht_inv[p.fht_nseg] = float(1.0 / sqrt(double(b)));
+      ++p.fht_nseg;
+      off += b;
+    }
+  }
   p.ldx = gp.ldx;
   p.M = gp.M;
   p.Mp = g.Mp;
@@ -994,6 +1026,14 @@ extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, i
                                      const b200lut_segment* segs, int nseg, int epilogue,
                                      int split, void* workspace, size_t workspace_bytes, int flags,
                                      const b200lut_exchange* ex, void* stream) {
+  return b200lut_gemv_input(x, ldx, M, K, dtype, segs, nseg, epilogue, split, workspace,
+                            workspace_bytes, flags, ex, nullptr, stream);
+}
+
+extern "C" int b200lut_gemv_input(const void* x, int64_t ldx, int M, int K, int dtype,
+                                  const b200lut_segment* segs, int nseg, int epilogue, int split,
+                                  void* workspace, size_t workspace_bytes, int flags,
+                                  const b200lut_exchange* ex, const b200lut_input* in, void* stream) {
   B200LUT_REQUIRE(x && segs, B200LUT_ERR_INVALID, "null x or segment table");
   B200LUT_REQUIRE(M >= 1 && M <= kMaxM, B200LUT_ERR_UNSUPPORTED,
                   "decode GEMV serves 1 <= M <= 16, got M=%d (use b200lut_gemm)", M);
@@ -1023,6 +1063,18 @@ extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, i
   int tiles = 0, max_tables = 1;
   if (int rc = convert_segments(segs, nseg, silu, p.seg, &tiles, &max_tables)) return rc;
   p.tiles_total = tiles;
+  const bool transformed = in && (in->x_mul || in->rot_signs || in->awq_scale);
+  if (transformed) {
+    B200LUT_REQUIRE(!in->awq_scale || in->rot_signs, B200LUT_ERR_INVALID,
+                    "input transform: an AWQ scale needs the rotation signs");
+    B200LUT_REQUIRE(!in->x_mul || aligned16(in->x_mul), B200LUT_ERR_ALIGN,
+                    "input transform: x_mul must be 16-byte aligned");
+    B200LUT_REQUIRE(split <= 0 && !(flags & B200LUT_FLAG_TILE_KERNEL), B200LUT_ERR_UNSUPPORTED,
+                    "an input transform is served by the row-range kernel only (split = 0, no tile-kernel flag)");
+    p.x_mul = static_cast<const uint16_t*>(in->x_mul);
+    p.rot_signs = in->rot_signs;
+    p.awq_scale = in->awq_scale;
+  }
   const bool pdl = (flags & B200LUT_FLAG_PDL) != 0;
   cudaStream_t st = cudaStream_t(stream);
   // Library policy (split == 0): the row-range kernel when it serves the shapes. An explicit
@@ -1034,6 +1086,9 @@ extern "C" int b200lut_gemv_exchange(const void* x, int64_t ldx, int M, int K, i
                        : try_rows<__half>(p, nullptr, tiles, pdl, st, &served);
     if (rc || served) return rc;
   }
+  B200LUT_REQUIRE(!transformed, B200LUT_ERR_UNSUPPORTED,
+                  "an input transform needs 4-bit single-stream segments and M <= 8 (the row-range "
+                  "kernel); transform the rows with b200lut_fht / b200lut_silu_mul first");
   const int warps = M <= 8 ? kWarpsM8 : kWarpsM16;
   if (split <= 0) split = pick_split(tiles, p.G, sm_count_cached(), warps);
   B200LUT_REQUIRE(split >= 1 && split <= 16 && split <= p.G, B200LUT_ERR_INVALID,

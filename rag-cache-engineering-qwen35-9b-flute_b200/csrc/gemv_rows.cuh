@@ -44,6 +44,7 @@ constexpr int kRowsMaxSlots = 4;        // palettes a block can hold (two 64 KB 
 constexpr uint32_t kRowsTableAbs = 2048;   // offset of the first pair table inside the block's shared window
 constexpr uint32_t kRowsWindowMask = 0x3FFFFu;   // a block's shared window is smaller than 256 KB
 constexpr int kRowsStatusBadWindow = 0x5000;
+constexpr int kRowsMaxFhtSegs = 8;
 
 struct RowsParams {
   const uint16_t* x;
@@ -53,6 +54,14 @@ struct RowsParams {
   int units_total;         // 32-row units (pairs of units under the SiLU*mul epilogue)
   int row_blocks, split, ntables, red_planes;
   uint32_t xs_abs, red_abs, part_abs;    // offsets inside the block's shared window
+  // Hadamard rotation of the activation rows inside the launch (rot_signs != null): descending
+  // power-of-two segments of K, as b200lut_fht runs them; fht_abs: fp32 scratch of one segment
+  const float* rot_signs;
+  const float* awq_scale;
+  uint32_t fht_abs;
+  int fht_nseg;
+  int fht_off[kRowsMaxFhtSegs], fht_len[kRowsMaxFhtSegs], fht_stages[kRowsMaxFhtSegs];
+  float fht_inv[kRowsMaxFhtSegs];
   int* status;
   SegDev seg[kMaxSeg];
   ExchangeDev ex;
@@ -281,7 +290,66 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
     }
     // activation rows of this block's K range into shared memory, B-fragment order:
     // element (chunk g, tig, kt, j) at g*128 + tig*32 + kt*8 + 2j bytes = x[64g + 16kt + 4tig + j]
-    if (!bad_window) {
+    if (!bad_window && p.rot_signs) {
+      // Rotated rows (the boundary fold of the reference's rotated artifacts, fused like its
+      // gemv_fht_prologue, src/flute_extended/include/flute/gemv.cuh:305-351): per row and
+      // segment, fp32 butterfly in shared memory in the stage order of b200lut_fht (same
+      // expression tree, same bits), then signs, 1/sqrt(b) (and the AWQ scale on both sides),
+      // ONE rounding to the activation dtype, written in B-fragment order. K is never split here.
+      uint8_t* xs = generic(p.xs_abs);
+      float* buf = reinterpret_cast<float*>(generic(p.fht_abs));
+      for (int m = 0; m < Mp; ++m) {
+        for (int sg = 0; sg < p.fht_nseg; ++sg) {
+          const int off = p.fht_off[sg], n = p.fht_len[sg], stages = p.fht_stages[sg];
+          const float inv = p.fht_inv[sg];
+          for (int i = tid * 8; i < n; i += NTS * 8) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (m < M) {
+              const size_t at = size_t(m) * p.ldx + size_t(off + i);
+              v = __ldcg(reinterpret_cast<const uint4*>(p.x + at));
+              if (p.x2) v = silu_mul8<T>(v, __ldcg(reinterpret_cast<const uint4*>(p.x2 + at)));
+            }
+            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float f = DType<T>::to_float(uint16_t(wv[j >> 1] >> (16 * (j & 1))));
+              if (p.awq_scale) f = f * p.awq_scale[off + i + j];
+              buf[i + j] = f;
+            }
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(NTS) : "memory");
+          for (int st = 0; st < stages; ++st) {
+            const int len = 1 << st;
+            for (int i = tid; i < n / 2; i += NTS) {
+              const int lo = ((i >> st) << (st + 1)) + (i & (len - 1));
+              const float a = buf[lo], b = buf[lo + len];
+              buf[lo] = a + b;
+              buf[lo + len] = a - b;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(NTS) : "memory");
+          }
+          for (int i = tid * 4; i < n; i += NTS * 4) {
+            uint32_t o[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t pair = 0;
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int k = off + i + 2 * h + e;
+                float r = buf[i + 2 * h + e] * p.rot_signs[k];
+                r = r * inv;
+                if (p.awq_scale) r = __fdiv_rn(r, p.awq_scale[k]);
+                pair |= uint32_t(DType<T>::from_float(r)) << (16 * e);
+              }
+              o[h] = pair;
+            }
+            const int k = off + i, g = k >> 6, w64 = k & 63, kt = w64 >> 4, tg = (w64 & 15) >> 2;
+            *reinterpret_cast<uint2*>(xs + (size_t(m) * kc + g) * 128 + tg * 32 + kt * 8) = make_uint2(o[0], o[1]);
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(NTS) : "memory");
+        }
+      }
+    } else if (!bad_window) {
       uint8_t* xs = generic(p.xs_abs);
       const int per_row = kc * 8;   // 16-byte pieces of one row
       const int total = Mp * per_row;
@@ -459,7 +527,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
 
 struct RowsGeom {
   int units_total, row_blocks, split, ntables, red_planes, Mp, xreg;
-  uint32_t xs_abs, red_abs, part_abs, end_abs;
+  uint32_t xs_abs, red_abs, part_abs, fht_abs, end_abs;
 };
 
 // Palette slots the busiest block needs when `units` units are cut into `row_blocks` ranges
@@ -494,7 +562,7 @@ int rows_max_slots(const SegDev* seg, int nseg, bool silu, int units, int row_bl
 // tile x split kernel has to run (other code widths, a second stream, M > 8, a K range whose
 // activation rows do not fit in shared memory).
 bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, int K, int sms,
-               RowsGeom* g) {
+               uint32_t fht_bytes, RowsGeom* g) {
   if (M < 1 || M > 8) return false;
   for (int i = 0; i < nseg; ++i)
     if (seg[i].bits != 4 || seg[i].packed2 != nullptr || seg[i].gs < kUnitRows) return false;
@@ -531,7 +599,7 @@ bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, i
     split = sms / U;
     if (split > kMaxClusterSplit) split = kMaxClusterSplit;
     if (split > G / (kRowsWarps * kRowsRing)) split = G / (kRowsWarps * kRowsRing);
-    if (split < 1) split = 1;
+    if (split < 1 || fht_bytes) split = 1;
   }
   g->units_total = U;
   g->row_blocks = row_blocks;
@@ -544,7 +612,8 @@ bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, i
   g->xs_abs = kRowsTableAbs + uint32_t(g->ntables) * kTableBytes;
   g->red_abs = g->xs_abs + uint32_t(Mp) * uint32_t(kc_max) * 128u;
   g->part_abs = g->red_abs + uint32_t(kRowsWarps) * uint32_t(g->red_planes) * uint32_t(Mp) * 128u;
-  g->end_abs = g->part_abs + (split > 1 ? uint32_t(g->red_planes) * uint32_t(Mp) * 128u : 0u);
+  g->fht_abs = g->part_abs + (split > 1 ? uint32_t(g->red_planes) * uint32_t(Mp) * 128u : 0u);
+  g->end_abs = g->fht_abs + fht_bytes;
   return g->end_abs <= 227u * 1024u;
 }
 

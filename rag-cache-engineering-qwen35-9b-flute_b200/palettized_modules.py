@@ -293,16 +293,37 @@ class PalettizedLinear(nn.Module):
                 and self.resB.is_contiguous() and self.resA.data_ptr() % 16 == 0
                 and self.resB.data_ptr() % 16 == 0)
 
-    def _kernel_matmul(self, x2: torch.Tensor, fuse_residual: bool = False) -> torch.Tensor:
+    def _rotation_fuses(self, M: int, dtype=None) -> bool:
+        """The input rotation can run inside the decode launch: 4-bit single stream, at most 8
+        rows, no low-rank residual (its projection needs the rotated row in memory), K made of
+        at most 8 power-of-two segments."""
+        return (self.rot_signs is not None and not self.reference and 0 < M <= 8 and self.bitwidth == 4
+                and (dtype is None or dtype == self.lut.dtype)      # else the rotation rounds in x's dtype
+                and not self.has_stream2 and not self.has_residual() and self.group_size >= 32
+                and bin(self.K).count("1") <= 8
+                and os.environ.get("FLUTE_NO_FHT_FUSE", "").strip() not in ("1", "true", "True"))
+
+    def _input_transform(self, device):
+        signs = self._on("signs", self.rot_signs, device)
+        awq = None
+        if self.awq_scale is not None and self.fold_order == "rotate_then_awq":
+            awq = self._on("awq", self.awq_scale, device)
+        return _lib.make_input(rot_signs=signs, awq_scale=awq)
+
+    def _kernel_matmul(self, x2: torch.Tensor, fuse_residual: bool = False,
+                       fuse_rotation: bool = False) -> torch.Tensor:
         """x2 [M, K] in the compute dtype -> [M, N] (streams + bias, and the low-rank
-        residual when fuse_residual)."""
+        residual when fuse_residual; fuse_rotation: x2 is the UNROTATED row and the launch
+        rotates it)."""
         M = x2.shape[0]
         out = torch.empty(M, self.N, dtype=x2.dtype, device=x2.device)
         if M == 0:
             return out
         res_t = _lib.residual_project(x2, self.resB, flags=_flags()) if fuse_residual else None
         segs = _lib.make_segments([self._segment_desc(out, res_t=res_t)])
-        if M <= GEMV_MAX_M:
+        if fuse_rotation:
+            _lib.gemv_input(x2, segs, 1, self._input_transform(x2.device), flags=_flags())
+        elif M <= GEMV_MAX_M:
             _lib.gemv_multi(x2, segs, 1, flags=_flags())
         elif (self.bitwidth == 4 and (not self.has_stream2 or self.bitwidth2 == 4)) or \
                 (not self.has_stream2 and self.group_size >= 64 and self.K >= 128):
@@ -366,7 +387,8 @@ class PalettizedLinear(nn.Module):
             out = torch.zeros(*shape[:-1], self.N, dtype=x.dtype, device=x.device)
             return out + self.bias.to(x.dtype) if self.bias is not None and self.N else out
         x2 = x.reshape(-1, self.K)
-        if self.rot_signs is not None:
+        fuse_rotation = self._rotation_fuses(x2.shape[0], x2.dtype)
+        if self.rot_signs is not None and not fuse_rotation:
             x2 = self._rotate_input(x2)
         if self.reference:
             out = self._reference_matmul(x2)
@@ -377,7 +399,7 @@ class PalettizedLinear(nn.Module):
             if xc.stride(-1) != 1 or xc.stride(0) % 8 or xc.data_ptr() % 16:
                 xc = xc.contiguous().clone() if xc.data_ptr() % 16 else xc.contiguous()
             residual_done = self._fusable_residual(xc)
-            out = self._kernel_matmul(xc, fuse_residual=residual_done).to(x.dtype)
+            out = self._kernel_matmul(xc, fuse_residual=residual_done, fuse_rotation=fuse_rotation).to(x.dtype)
             bias_done = True
         if self.has_residual() and not (not self.reference and residual_done):
             xr = x2.to(self.resA.dtype)

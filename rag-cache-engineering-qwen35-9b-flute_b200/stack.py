@@ -114,9 +114,12 @@ class LinearStack(nn.Module):
             raise ValueError("gather='push' needs at least two layers")
         self.gather_mode = gather if world > 1 else "nccl"
         # rotate: every projection group reads the Hadamard rotation of its input row (the
-        # boundary fold of the reference's rotated artifacts, src/flute_extended/fht.py:105-134):
-        # one FHT launch in front of each group, signs drawn per group
-        self.rotate = bool(rotate)
+        # boundary fold of the reference's rotated artifacts, src/flute_extended/fht.py:105-134),
+        # signs drawn per group. True / "launch": one FHT launch in front of each group;
+        # "fused": the rotation runs inside the decode launch (M <= 8)
+        if rotate not in (False, True, "launch", "fused"):
+            raise ValueError(f"rotate must be False, True, 'launch' or 'fused', got {rotate!r}")
+        self.rotate = "launch" if rotate is True else rotate
         self.merge_prefill = True    # M > 16: projections that share x run as one launch
         self._arenas = arenas        # test form: pre-built emulated arenas (this rank's one)
         self.device, self.dtype = torch.device(device), dtype
@@ -187,17 +190,24 @@ class LinearStack(nn.Module):
             need = len(self.layers) * (((M * width * 2 + 255) // 256 + 2) * 256 + self.world * 4096 * 4)
             arena = self._arenas if self._arenas is not None else exchange.PeerArena(
                 need, self.rank, self.world, dev)
+        fused_rot = self.rotate == "fused" and M <= 8
+
         def rotated(src, tag):
-            """("fht", src, dst, signs) entry in front of a group when the stack is rotated."""
+            """The group's input and its input transform: with launch rotation an ("fht", src,
+            dst, signs) entry goes in front and the group reads dst; fused, the group reads src
+            through an input transform."""
             if not self.rotate:
-                return src
+                return src, None
             K = src.shape[1]
             g = torch.Generator().manual_seed(len(launches) * 7919 + K)
             signs = (torch.randint(0, 2, (K,), generator=g) * 2 - 1).float().to(dev)
+            outs_rot.append(signs)
+            if fused_rot:
+                return src, _lib.make_input(rot_signs=signs)
             dst = torch.empty_like(src)
-            launches.append(("fht", src, dst, signs, None, None, None))
+            launches.append(("fht", src, dst, signs, None, None, None, None))
             outs_rot.append(dst)
-            return dst
+            return dst, None
         outs_rot = []
         for L in self.layers:
             heads = L.heads()
@@ -207,12 +217,13 @@ class LinearStack(nn.Module):
             for m in heads:
                 descs.append(m._segment_desc(hbuf[:, off:], ldo=total))
                 off += m.N
-            xr = rotated(x, "heads")
-            launches.append(("heads", xr, _lib.make_segments(descs), len(descs), _lib.EPI_NONE, descs, None))
+            xr, inp = rotated(x, "heads")
+            launches.append(("heads", xr, _lib.make_segments(descs), len(descs), _lib.EPI_NONE, descs, None, inp))
             o = L.out()
             obuf = torch.empty(M, o.N, dtype=dt, device=dev)
             od = [o._segment_desc(obuf)]
-            launches.append(("out", rotated(x, "out"), _lib.make_segments(od), 1, _lib.EPI_NONE, od, None))
+            xr, inp = rotated(x, "out")
+            launches.append(("out", xr, _lib.make_segments(od), 1, _lib.EPI_NONE, od, None, inp))
             g, u, d = L.mlp.gate_proj, L.mlp.up_proj, L.mlp.down_proj
             chan = None
             if push:
@@ -222,16 +233,18 @@ class LinearStack(nn.Module):
             act = chan.act if push else torch.empty(M, g.N * self.world, dtype=dt, device=dev)
             act_loc = act[:, self.rank * g.N:(self.rank + 1) * g.N]   # full width after gather
             gd = [g._segment_desc(act_loc, ldo=act.shape[1]), u._segment_desc(None)]
-            launches.append(("gate_up", rotated(x, "gate_up"), _lib.make_segments(gd), 2, _lib.EPI_SILU_MUL, gd,
-                             chan.push if push else None))
+            xr, inp = rotated(x, "gate_up")
+            launches.append(("gate_up", xr, _lib.make_segments(gd), 2, _lib.EPI_SILU_MUL, gd,
+                             chan.push if push else None, inp))
             if self.world > 1 and not push:
-                launches.append(("gather", act, act_loc, None, None, None, None))
+                launches.append(("gather", act, act_loc, None, None, None, None, None))
             ybuf = torch.empty(M, d.N, dtype=dt, device=dev)
             dd = [d._segment_desc(ybuf)]
             if self.rotate and push:
                 raise ValueError("a rotated stack uses the NCCL gather (the rotation reads the gathered row)")
-            launches.append(("down", rotated(act, "down"), _lib.make_segments(dd), 1, _lib.EPI_NONE, dd,
-                             chan.wait if push else None))
+            xr, inp = rotated(act, "down")
+            launches.append(("down", xr, _lib.make_segments(dd), 1, _lib.EPI_NONE, dd,
+                             chan.wait if push else None, inp))
             outs += [hbuf, obuf, act, ybuf]
         plan = {"x": x, "launches": launches, "buffers": outs, "y": outs[-1], "arena": arena,
                 "rotated": outs_rot}
@@ -240,9 +253,12 @@ class LinearStack(nn.Module):
 
     def run_launch(self, entry, M: int, flags: int = 0, gather=None) -> None:
         """Issue one entry of the plan's launch list on the current stream."""
-        name, xin, segs, nseg, epi, _, ex = entry
+        name, xin, segs, nseg, epi, _, ex, inp = entry
         if name == "gather":
             gather(xin, segs)
+        elif inp is not None and M <= 16:
+            _lib.gemv_input(xin, segs, nseg, inp, epilogue=epi, flags=flags & ~(_lib.FLAG_TILE_KERNEL | _lib.FLAG_ROWS_KERNEL),
+                            ex=ex)
         elif name == "fht":
             _lib.fht(xin, nseg, out=segs)       # (src, dst, signs) ride in the entry's slots
         elif ex is not None:
@@ -300,8 +316,8 @@ class LinearStack(nn.Module):
         plan = self._plan(M)
         if "plans" not in plan:
             groups, cur = [], []
-            for name, xin, segs, nseg, epi, descs, _ in plan["launches"]:
-                if name == "fht":
+            for name, xin, segs, nseg, epi, descs, _, inp in plan["launches"]:
+                if name == "fht" or inp is not None:
                     raise ValueError("the persistent executor does not serve a rotated stack")
                 if name == "gather":
                     groups.append(("plan", cur))
@@ -325,7 +341,7 @@ class LinearStack(nn.Module):
     def launches_per_step(self, M: int) -> int:
         """Kernel launches of one step (the all-gathers of a multi-GPU step not counted)."""
         n = 0
-        for name, xin, _, nseg, epi, descs, _ in self._plan(M)["launches"]:
+        for name, xin, _, nseg, epi, descs, _, _ in self._plan(M)["launches"]:
             if name == "gather":
                 continue
             if M <= 16 or name == "fht":

@@ -33,14 +33,14 @@ def _run(case, x, flags, mod=None):
 
 @pytest.mark.parametrize("N,K,gs,dtype,M", (
     (128, 64, 128, torch.bfloat16, 1),          # one chunk: fifteen idle warps
-    (256, 256, 128, torch.bfloat16, 1),         # K split over a cluster of four
+    (256, 256, 128, torch.bfloat16, 1),         # four chunks: twelve idle warps
     (512, 1024, 32, torch.float16, 5),          # one palette per unit
     (1024, 4096, 64, torch.bfloat16, 8),        # 64 chunks: fragments in registers, M' = 8
     (4096, 4096, 128, torch.bfloat16, 1),       # the single-projection configuration
     (4096, 4096, 128, torch.float16, 1),
     (12288, 4096, 128, torch.bfloat16, 1),      # two or three units per block
     (12288, 4096, 64, torch.bfloat16, 2),       # up to three palettes per block
-    (2048, 12288, 128, torch.bfloat16, 1),      # down-projection K: three rounds per unit
+    (2048, 12288, 128, torch.bfloat16, 1),      # down-projection K, few rows: K split over a cluster of two
     (4096, 12288, 128, torch.bfloat16, 4),
     (640, 1856, 128, torch.bfloat16, 3),        # 29 chunks: ragged rounds, idle ring slots
     (9600, 2048, 128, torch.float16, 7),        # 32 chunks: half rounds
@@ -123,3 +123,53 @@ def test_rows_kernel_leaves_other_widths_to_the_tile_kernel():
     two = Case(256, 512, 128, 4, torch.bfloat16, seed=10, bits2=2)
     x = two.x(1)
     assert torch.equal(_run(two, x, ROWS), _run(two, x, TILE))
+
+
+@pytest.mark.parametrize("N,K,M,dtype,awq", ((4096, 4096, 1, torch.bfloat16, False), (4096, 12288, 3, torch.float16, True),
+                                              (12288, 4096, 8, torch.bfloat16, True), (256, 192, 2, torch.float16, False)))
+def test_rotation_inside_the_launch_equals_the_separate_transform(N, K, M, dtype, awq):
+    """The module rotates its input inside the decode launch when it can (the reference's fused
+    prologue, src/flute_extended/include/flute/gemv.cuh:305-351). Same butterfly, same rounding
+    point: the outputs equal those behind a separate b200lut_fht launch bit for bit."""
+    import os
+    case = Case(N, K, 128, 4, dtype, seed=N + K, rotation_seed=5, awq=awq)
+    mod = case.module()
+    x = case.x(M).cuda()
+    assert mod._rotation_fuses(M, x.dtype)
+    fused = mod(x)
+    os.environ["FLUTE_NO_FHT_FUSE"] = "1"
+    try:
+        assert not mod._rotation_fuses(M, x.dtype)
+        separate = mod(x)
+    finally:
+        del os.environ["FLUTE_NO_FHT_FUSE"]
+    assert torch.equal(fused, separate)
+    assert rel_err(fused, case.oracle(x.cpu())) <= TOL
+    assert L.lib().b200lut_device_status() == 0
+
+
+def test_gated_input_inside_the_launch():
+    # down(silu(g) * u) with the product formed while the launch stages its rows
+    dt, M, I, H = torch.bfloat16, 2, 12288, 4096
+    case = Case(H, I, 128, 4, dt, seed=77)
+    mod = case.module()
+    mod._ensure_packed()
+    g = torch.randn(M, I, generator=torch.Generator().manual_seed(1)).to(dt).cuda()
+    u = torch.randn(M, I, generator=torch.Generator().manual_seed(2)).to(dt).cuda()
+    out = torch.empty(M, H, dtype=dt, device="cuda")
+    segs = L.make_segments([mod._segment_desc(out)])
+    L.gemv_input(g, segs, 1, L.make_input(x_mul=u))
+    act = L.silu_mul(g.clone(), u)
+    want = torch.empty_like(out)
+    L.gemv_multi(act, L.make_segments([mod._segment_desc(want)]), 1, flags=ROWS)
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    assert rel_err(out, case.oracle(act.cpu())) <= TOL
+    # shapes the fused form does not serve are refused, not silently served another way
+    three = Case(256, 256, 128, 3, dt, seed=3).module()
+    three._ensure_packed()
+    o = torch.empty(1, 256, dtype=dt, device="cuda")
+    with pytest.raises(L.LibraryError) as e:
+        L.gemv_input(torch.zeros(1, 256, dtype=dt, device="cuda"), L.make_segments([three._segment_desc(o)]), 1,
+                     L.make_input(x_mul=torch.zeros(1, 256, dtype=dt, device="cuda")))
+    assert e.value.code == 2
