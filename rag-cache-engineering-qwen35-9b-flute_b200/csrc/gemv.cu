@@ -888,6 +888,7 @@ int try_rows(const GemvParams& gp, const uint16_t* x2, int tiles, bool pdl, cuda
   p.xs_abs = g.xs_abs;
   p.red_abs = g.red_abs;
   p.part_abs = g.part_abs;
+  p.meta_abs = g.meta_abs;
   int rc = B200LUT_OK;
   p.status = device_status_addr(&rc);
   if (rc) return rc;

@@ -54,6 +54,7 @@ struct RowsParams {
   int units_total;         // 32-row units (pairs of units under the SiLU*mul epilogue)
   int row_blocks, split, ntables, red_planes;
   uint32_t xs_abs, red_abs, part_abs;    // offsets inside the block's shared window
+  uint32_t meta_abs;                     // RowsUnitMeta[units of the block]
   // Hadamard rotation of the activation rows inside the launch (rot_signs != null): descending
   // power-of-two segments of K, as b200lut_fht runs them; fht_abs: fp32 scratch of one segment
   const float* rot_signs;
@@ -101,27 +102,32 @@ __device__ __forceinline__ uint4 silu_mul8(uint4 g, uint4 u) {
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// What the epilogue needs to know about one 32-row unit of the block, worked out once in the
+// prologue (segment search and parameter loads off the tail of the launch) and kept in shared memory.
+struct RowsUnitMeta {
+  uint16_t* out;            // &out[0][n0] of the unit (gate segment under SiLU*mul)
+  const uint16_t* bias;     // &bias[n0] or null
+  const uint16_t* bias2;    // up segment's, under SiLU*mul
+  long long ldo;
+  int seg;                  // segment index (gate segment under SiLU*mul)
+  int n0;                   // first row of the unit inside its segment
+  int has_res;              // bit 0: segment has a fused residual; bit 1: the up segment has one
+  int pad;
+};
+
 // Bias, residual, SiLU*mul, the one rounding, the store (and its mirrors on the peers).
 template <typename T>
-__device__ __forceinline__ void rows_finish(const RowsParams& p, int u, int m, int row, float a,
-                                            float b) {
-  const bool silu = p.epilogue == B200LUT_EPI_SILU_MUL;
-  const int step = silu ? 2 : 1;
-  int si = 0;
-  for (int s = 0; s < p.nseg; s += step)
-    if ((u >> 2) >= p.seg[s].tile_begin) si = s;
-  const SegDev& s0 = p.seg[si];
-  const int n = (u - 4 * s0.tile_begin) * kUnitRows + row;
-  if (s0.res_rank) a += residual_dot<T>(s0, m, n);
-  if (s0.bias) a += DType<T>::to_float(s0.bias[n]);
+__device__ __forceinline__ void rows_finish(const RowsParams& p, const RowsUnitMeta& um, bool silu,
+                                            int m, int row, float a, float b) {
+  if (um.has_res & 1) a += residual_dot<T>(p.seg[um.seg], m, um.n0 + row);
+  if (um.bias) a += DType<T>::to_float(um.bias[row]);
   float v = a;
   if (silu) {
-    const SegDev& s1 = p.seg[si + 1];
-    if (s1.res_rank) b += residual_dot<T>(s1, m, n);
-    if (s1.bias) b += DType<T>::to_float(s1.bias[n]);
+    if (um.has_res & 2) b += residual_dot<T>(p.seg[um.seg + 1], m, um.n0 + row);
+    if (um.bias2) b += DType<T>::to_float(um.bias2[row]);
     v = a / (1.f + __expf(-a)) * b;
   }
-  uint16_t* dst = s0.out + size_t(m) * s0.ldo + n;
+  uint16_t* dst = um.out + size_t(m) * um.ldo + row;
   const uint16_t bits16 = DType<T>::from_float(v);
   *dst = bits16;
   if (p.ex.push) {
@@ -209,6 +215,19 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
     int grp = (lu * kUnitRows) / sg.gs;
     if (grp > sg.n_groups - 1) grp = sg.n_groups - 1;
     my_lut = reinterpret_cast<unsigned long long>(sg.lut + size_t(grp) * 16);
+    if (warp == 0 && which == 0) {
+      const SegDev& s0 = p.seg[si];
+      RowsUnitMeta um;
+      um.n0 = lu * kUnitRows;
+      um.out = s0.out + um.n0;
+      um.bias = s0.bias ? s0.bias + um.n0 : nullptr;
+      um.bias2 = (silu && p.seg[si + 1].bias) ? p.seg[si + 1].bias + um.n0 : nullptr;
+      um.ldo = s0.ldo;
+      um.seg = si;
+      um.has_res = (s0.res_rank ? 1 : 0) | ((silu && p.seg[si + 1].res_rank) ? 2 : 0);
+      um.pad = 0;
+      reinterpret_cast<RowsUnitMeta*>(generic(p.meta_abs))[lane / ppu] = um;
+    }
   }
 
   // ---- rounds: up to R consecutive chunks of one plane. The first round is requested now,
@@ -458,10 +477,16 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
   const int nwa = kc < NW ? kc : NW;   // warps that held chunks
   const int nu = nplanes / ppu;
   const int total_out = nu * M * kUnitRows;
+  const RowsUnitMeta* meta = reinterpret_cast<const RowsUnitMeta*>(generic(p.meta_abs));
   auto warp_sum = [&](int plane, int m, int row) {
+    const float* r0 = red + (plane * Mp + m) * kUnitRows + row;
+    const int stride = p.red_planes * Mp * kUnitRows;
+    float part_v[NW];
+#pragma unroll
+    for (int wi = 0; wi < NW; ++wi) part_v[wi] = wi < nwa ? r0[wi * stride] : 0.f;   // loads first,
     float v = 0.f;
-    for (int wi = 0; wi < nwa; ++wi)
-      v += red[((wi * p.red_planes + plane) * Mp + m) * kUnitRows + row];
+#pragma unroll
+    for (int wi = 0; wi < NW; ++wi) v += part_v[wi];                               // adds in warp order
     return v;
   };
   if (split == 1) {
@@ -469,7 +494,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
       const int row = idx & 31, m = (idx >> 5) % M, ul = (idx >> 5) / M;
       const float a = warp_sum(ul * ppu, m, row);
       const float b = silu ? warp_sum(ul * ppu + 1, m, row) : 0.f;
-      rows_finish<T>(p, u0 + ul, m, row, a, b);
+      rows_finish<T>(p, meta[ul], silu, m, row, a, b);
     }
   } else {
     float* part = reinterpret_cast<float*>(generic(p.part_abs));   // [plane][m][row]
@@ -489,7 +514,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
         a += peer[((ul * ppu) * M + m) * kUnitRows + row];
         if (silu) b += peer[((ul * ppu + 1) * M + m) * kUnitRows + row];
       }
-      rows_finish<T>(p, u0 + ul, m, row, a, b);
+      rows_finish<T>(p, meta[ul], silu, m, row, a, b);
     }
     cluster.sync();   // keep shared memory alive until every peer has read it
   }
@@ -527,7 +552,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
 
 struct RowsGeom {
   int units_total, row_blocks, split, ntables, red_planes, Mp, xreg;
-  uint32_t xs_abs, red_abs, part_abs, fht_abs, end_abs;
+  uint32_t xs_abs, red_abs, part_abs, fht_abs, meta_abs, end_abs;
 };
 
 // Palette slots the busiest block needs when `units` units are cut into `row_blocks` ranges
@@ -613,7 +638,8 @@ bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, i
   g->red_abs = g->xs_abs + uint32_t(Mp) * uint32_t(kc_max) * 128u;
   g->part_abs = g->red_abs + uint32_t(kRowsWarps) * uint32_t(g->red_planes) * uint32_t(Mp) * 128u;
   g->fht_abs = g->part_abs + (split > 1 ? uint32_t(g->red_planes) * uint32_t(Mp) * 128u : 0u);
-  g->end_abs = g->fht_abs + fht_bytes;
+  g->meta_abs = g->fht_abs + ((fht_bytes + 15u) & ~15u);
+  g->end_abs = g->meta_abs + uint32_t((U + row_blocks - 1) / row_blocks) * uint32_t(sizeof(RowsUnitMeta));
   return g->end_abs <= 227u * 1024u;
 }
 
