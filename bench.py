@@ -357,7 +357,7 @@ def run_reference(args, rank: int):
     print(json.dumps(line), flush=True)
 
 
-def sampled_gate(pkg, packed, lut, N, K, bits, gs, x, got, rows=None):
+def sampled_gate(pkg, packed, lut, N, K, bits, gs, x, got, rows=None, residual=None):
     """Inline correctness gate of one data point (the reference's benchmark does the same per
     point, src/flute_extended/benchmark_kernel.py:95-107): the outputs of 256 weight rows
     spread over the matrix are recomputed on the CPU with the reference route's arithmetic
@@ -377,6 +377,9 @@ def sampled_gate(pkg, packed, lut, N, K, bits, gs, x, got, rows=None):
         w[j] = lut_c[min(r // gs, lut_c.shape[0] - 1)].float()[torch.from_numpy(codes[j])]
     xc = x.detach().cpu()
     want = (xc.float() @ w.t()).to(xc.dtype)
+    if residual is not None:      # (resA [N, R], resB [R, K]): the reference route adds it to the rounded sums
+        resA, resB = (t.detach().cpu() for t in residual)
+        want = want + ((xc @ resB.t()) @ resA[rows].t()).to(want.dtype)
     g = got[:, rows.to(got.device)].detach().cpu()
     return {"rel_max": orc.max_rel_err(g.float(), want.float()), "cos": orc.cosine(g.float(), want.float())}
 
@@ -421,9 +424,12 @@ def single_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int, fl
     return byts / us / 1e3, us, sampled_gate(pkg, keep[-1][0], keep[-1][1], N, K, bits, gs, x, out)
 
 
-def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool, gate: bool = False):
+def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool, gate: bool = False,
+                        rank: int = 0):
     """Extra: the M=2048 prefill GEMM (optionally behind the 128-point block Hadamard of the
-    activations, timed together), CUDA events, inputs 16 MB + 24 MB + 48 MB out per call."""
+    activations, or with a rank-`rank` residual: its projection launch and the extra k-block,
+    timed together), CUDA events, inputs 16 MB + 24 MB + 48 MB out per call. The FLOP count is
+    the code streams' only."""
     import torch
     L = pkg._lib
     bits, gs, dt = 4, 128, torch.bfloat16
@@ -432,10 +438,19 @@ def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool, g
     x = torch.randn(M, K, device="cuda").to(dt)
     xr = torch.empty_like(x)
     out = torch.empty(M, N, dtype=dt, device="cuda")
-    seg = L.make_segments([dict(packed=packed, lut=lut, N=N, group_size=gs, n_groups=N // gs,
-                                bits=bits, out=out)])
+    desc = dict(packed=packed, lut=lut, N=N, group_size=gs, n_groups=N // gs, bits=bits, out=out)
+    residual = None
+    if rank:
+        resA = (0.05 * torch.randn(N, rank, device="cuda")).to(dt)
+        resB = (0.05 * torch.randn(rank, K, device="cuda")).to(dt)
+        t = torch.empty(M, L.residual_block_cols(rank), dtype=dt, device="cuda")
+        desc.update(resA=resA, res_t=t)
+        residual = (resA, resB)
+    seg = L.make_segments([desc])
 
     def run():
+        if rank:
+            L.residual_project_rows(x, resB, out=t)
         if rotate:
             L.fht(x, None, block=128, out=xr)
             L.gemm(xr, seg)
@@ -455,7 +470,8 @@ def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool, g
         xin = orc.fht_block(x.cpu(), 128).to(dt)
     else:
         xin = x
-    return 2.0 * M * N * K / us / 1e6, us, sampled_gate(pkg, packed, lut, N, K, bits, gs, xin[:64], out[:64])
+    return 2.0 * M * N * K / us / 1e6, us, sampled_gate(pkg, packed, lut, N, K, bits, gs, xin[:64], out[:64],
+                                                        residual=residual)
 
 
 def dense_matmul_tflops(M: int, N: int, K: int, iters: int):
@@ -692,6 +708,9 @@ def run_extras(pkg, st, stack, peaks, flags):
         extras["dense_bf16_matmul_m2048_k4096_n12288"] = {"TFLOP/s": dtf, "us": dus, "lut_gemm_over_dense": tf / dtf}
         tf, us, g = prefill_gemm_tflops(pkg, 2048, 12288, 4096, 20, True, gate=True)
         put("prefill_gemm_with_block128_fht", {"TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}, g)
+        tf, us, g = prefill_gemm_tflops(pkg, 2048, 12288, 4096, 20, False, gate=True, rank=32)
+        put("prefill_gemm_with_rank32_residual", {"TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"],
+                                                   "launches": "residual_rows_kernel + gemm_tc_persistent_kernel"}, g)
         for name, N, K, sets, it in (("gemv_4096x4096_m1", 4096, 4096, 40, 20), ("gemv_12288x4096_m1", 12288, 4096, 16, 20),
                                      ("gemv_4096x12288_m1", 4096, 12288, 16, 20),
                                      # the model's lm_head (0.51 GB of codes): the kernel's steady-state rate

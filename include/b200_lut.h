@@ -126,9 +126,13 @@ typedef struct b200lut_segment {
   int n_groups;          /* palette rows actually present (row-group index is clamped) */
   int bits;              /* stream-1 width (1..4) */
   int bits2;             /* stream-2 width, 0 if absent */
-  int res_rank;          /* R of the fused low-rank residual, 0 if absent (decode GEMV only) */
+  int res_rank;          /* R of the fused low-rank residual (a multiple of 8), 0 if absent */
   const void* resA;      /* [N, R] dtype, row-major: out[m, n] += sum_r res_t[m, r] * resA[n, r] */
-  const float* res_t;    /* [M, res_ldt] fp32 = x @ resB^T, from b200lut_residual_project */
+  const void* res_t;     /* x @ resB^T. Decode GEMV: fp32 [M, res_ldt] from
+                            b200lut_residual_project. Prefill GEMM: dtype [M, res_ldt] from
+                            b200lut_residual_project_rows, a block of 64 * ceil(R / 64) columns
+                            whose columns beyond R are zero; the blocks of the projections of a
+                            merged launch lie side by side in one matrix (one res_ldt). */
   int64_t res_ldt;       /* elements between consecutive rows of res_t */
 } b200lut_segment;
 
@@ -143,6 +147,20 @@ typedef struct b200lut_segment {
 int b200lut_residual_project(const void* x, int64_t ldx, int M, int K, int dtype,
                              const void* resB, int R, float* t, int64_t ldt, int flags,
                              void* stream);
+
+/* The same first factor for the prefill GEMM, any M: t[m, c] = round_dtype(sum_k x[m, k] *
+ * resB[c, k]) for c < R and 0 for R <= c < cols, t a [M, ldt] dtype matrix; cols is a multiple
+ * of 64, ldt >= cols a multiple of 8. The rounding of t to the factors' dtype is the
+ * reference route's (src/scripts/palettized_modules.py:1363-1364). The prefill GEMM then
+ * feeds t and the projection's resA rows to its accumulator as extra k-blocks
+ * (segment fields res_rank / resA / res_t / res_ldt), so the residual, the bias and the code
+ * streams are rounded once, together — the reference's streaming kernel accumulates the
+ * residual inside its launch the same way
+ * (src/flute_extended/src/kernel_streaming.cu:1438-1463). flags bit 0: programmatic
+ * dependent launch. */
+int b200lut_residual_project_rows(const void* x, int64_t ldx, int M, int K, int dtype,
+                                  const void* resB, int R, void* t, int64_t ldt, int cols,
+                                  int flags, void* stream);
 
 /* Scratch bytes b200lut_gemv_multi needs for (segments, M, split): zero when the
  * split is reduced through thread-block-cluster shared memory (split <= 8),

@@ -29,7 +29,7 @@ EXPORTS = (
     "b200lut_repack_from_idxn", "b200lut_repack_to_idxn", "b200lut_unpack_codes",
     "b200lut_dequant", "b200lut_gemv_workspace_bytes", "b200lut_gemv_pick_split",
     "b200lut_gemv_multi", "b200lut_gemv", "b200lut_gemm", "b200lut_fht",
-    "b200lut_residual_project", "b200lut_silu_mul", "b200lut_gemm_workspace_bytes", "b200lut_gemm_ws", "b200lut_gemm_multi",
+    "b200lut_residual_project", "b200lut_residual_project_rows", "b200lut_silu_mul", "b200lut_gemm_workspace_bytes", "b200lut_gemm_ws", "b200lut_gemm_multi",
     "b200lut_gemm_two_stream", "b200lut_gemm_two_stream_bytes",
     "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_kgrouped",
     "b200lut_gemv_kgrouped_split", "b200lut_gemv_kgrouped_workspace_bytes", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
@@ -143,6 +143,8 @@ def lib() -> ctypes.CDLL:
     L.b200lut_silu_mul.argtypes = [vp, vp, i32, i32, i64, i64, i32, vp]
     L.b200lut_residual_project.restype = i32
     L.b200lut_residual_project.argtypes = [vp, i64, i32, i32, i32, vp, i32, vp, i64, i32, vp]
+    L.b200lut_residual_project_rows.restype = i32
+    L.b200lut_residual_project_rows.argtypes = [vp, i64, i32, i32, i32, vp, i32, vp, i64, i32, i32, vp]
     L.b200lut_gemv_exchange.restype = i32
     L.b200lut_gemv_exchange.argtypes = [vp, i64, i32, i32, i32, ctypes.POINTER(Segment), i32, i32,
                                         i32, vp, sz, i32, ctypes.POINTER(Exchange), vp]
@@ -298,6 +300,30 @@ def residual_project(x: torch.Tensor, resB: torch.Tensor, flags: int = 0,
         check(lib().b200lut_residual_project(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype),
                                              resB.data_ptr(), R, out.data_ptr(), out.stride(0),
                                              flags, _stream(x)))
+    return out
+
+
+def residual_block_cols(rank: int) -> int:
+    """Columns of a projection's block of the prefill t matrix: 64 * ceil(rank / 64)."""
+    return 64 * ((int(rank) + 63) // 64)
+
+
+def residual_project_rows(x: torch.Tensor, resB: torch.Tensor, flags: int = 0,
+                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """t = round(x @ resB^T) in x's dtype for the prefill GEMM: [M, 64 * ceil(R / 64)], zero
+    beyond column R. `out` may be a column block of a wider matrix (merged launches)."""
+    _need_cuda(x, "x")
+    M, K = x.shape
+    R = resB.shape[0]
+    cols = residual_block_cols(R)
+    if out is None:
+        out = torch.empty(M, cols, dtype=x.dtype, device=x.device)
+    if out.shape[1] != cols or out.dtype != x.dtype or out.stride(1) != 1:
+        raise ValueError("residual_project_rows: out must be [M, 64 * ceil(R / 64)] in x's dtype")
+    with torch.cuda.device(x.device):
+        check(lib().b200lut_residual_project_rows(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype),
+                                                  resB.data_ptr(), R, out.data_ptr(), out.stride(0),
+                                                  cols, flags, _stream(x)))
     return out
 
 

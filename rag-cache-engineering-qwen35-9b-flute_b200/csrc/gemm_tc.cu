@@ -329,7 +329,10 @@ struct PersistSeg {
   const uint16_t* bias;
   uint16_t* out;
   long long ldo;
-  int row0, n_groups, out_aligned, pad;
+  int row0, n_groups, out_aligned;
+  int res_rank;            // rank of the low-rank residual, 0 if the projection has none
+  const uint16_t* resA;    // [N, res_rank], row-major
+  int t_col0, pad;         // first column of this projection's block of the t matrix
 };
 
 struct PersistParams {
@@ -349,6 +352,11 @@ struct PersistParams {
   // tiles through the workspace and each finishes its share of the tile's 16-column chunks,
   // adding the partial sums in ascending-k order.
   int split, full, left;
+  // Low-rank residual: E extra k-blocks close every tile. Their weight operand is 64 columns of
+  // the projection's resA rows (zero beyond the rank), written to the operand stage as they
+  // are; their activation operand is the matching 64-column block of t = x @ resB^T, fetched
+  // through the second tensor map. The sums, the bias and the single rounding are the tile's.
+  int E;
   // Two code streams of different widths: the first launch leaves its fp32 sums in acc_out
   // ([token][row], ld_acc floats per token) instead of rounding them, the second adds acc_in to
   // its own sums before bias and the single rounding.
@@ -427,7 +435,8 @@ __device__ __forceinline__ int persist_first_tile(const PersistParams& p, long l
 
 template <typename T, int BITS>
 __global__ void __launch_bounds__(kPThreads, 1)
-gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const PersistParams p) {
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
+                          const __grid_constant__ CUtensorMap tmap, const PersistParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t base = smem_u32(smem);
@@ -453,7 +462,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
   // The block's work is a list of segments (tile, k-blocks [c0, c1)). Plain mode: the whole
   // tiles of a cost-balanced contiguous range. Split mode: first the block's k-range of a cut
   // tile (if it has one), then `full` whole tiles.
-  const int G = p.G;
+  const int G = p.G;           // k-blocks of codes
+  const int Gx = p.G + p.E;    // k-blocks of a tile, the residual's included
   const int bid = int(blockIdx.x);
   int t0, ntile, has_cut = 0, cut_tile = 0, cut_c0 = 0, cut_c1 = 0, cut_part = 0;
   if (p.split) {
@@ -463,19 +473,19 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
       has_cut = 1;
       cut_part = bid % p.split;
       cut_tile = int(gridDim.x) * p.full + bid / p.split;
-      cut_c0 = (G * cut_part) / p.split;
-      cut_c1 = (G * (cut_part + 1)) / p.split;
+      cut_c0 = (Gx * cut_part) / p.split;
+      cut_c1 = (Gx * (cut_part + 1)) / p.split;
     }
   } else {
     t0 = persist_first_tile(p, bid, gridDim.x);
     ntile = persist_first_tile(p, bid + 1, gridDim.x) - t0;
   }
   const int nseg = ntile + has_cut;
-  const int iters = ntile * G + (cut_c1 - cut_c0);
+  const int iters = ntile * Gx + (cut_c1 - cut_c0);
   // segment s of this block
   auto seg_tile = [&](int sg) { return (has_cut && sg == 0) ? cut_tile : t0 + sg - has_cut; };
   auto seg_c0 = [&](int sg) { return (has_cut && sg == 0) ? cut_c0 : 0; };
-  auto seg_c1 = [&](int sg) { return (has_cut && sg == 0) ? cut_c1 : G; };
+  auto seg_c1 = [&](int sg) { return (has_cut && sg == 0) ? cut_c1 : Gx; };
 
   asm volatile("griddepcontrol.launch_dependents;");
 
@@ -535,7 +545,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
 #pragma unroll
       for (int i = 0; i < 2 * BITS; ++i) w[u][i] = 0u;
       const bool on = ld.s < nseg;
-      load_slab_pair<BITS>(w[u], on ? code_ptr(ld) : p.seg[0].packed, q, on ? 1u : 0u);
+      const bool codes = on && ld.c < G;      // a residual k-block has no codes to fetch
+      load_slab_pair<BITS>(w[u], codes ? code_ptr(ld) : p.seg[0].packed, q, codes ? 1u : 0u);
       if (on) advance(ld);
     }
     int table_row = -1, table_seg = -1;
@@ -567,8 +578,35 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
             tc::mbar_wait(bar_done + 8 * stage, uint32_t(i / kPStages - 1) & 1u, abort_flag,
                           &g_gemm_status, tc::kStatusWaitEmpty, p.wait_cycles);
           tc::fence_after_sync();
+          const bool residual = use.c >= G;
+          if (residual) {
+            // 64 columns of the tile's resA rows as they are. Register 4 kt + i of the store is
+            // 32-bit column 8 kt + 2 (lane & 3) + (i & 1) of row (lane >> 2) + 8 (i >> 1): four
+            // consecutive 16-bit values of each of the lane's two rows per 16-column block.
+            const PersistSeg sd = segment_of_row(p, use.row);
+            const int kk = (use.c - G) * kChunkK + 4 * (lane & 3);
+#pragma unroll
+            for (int sl = 0; sl < 2; ++sl) {
+              const int n = (use.row - sd.row0) * kTileRows + 32 * q + 16 * sl + (lane >> 2);
+              const uint16_t* ra = sd.resA + size_t(n) * sd.res_rank + kk;
+              const uint16_t* rb = ra + size_t(8) * sd.res_rank;
+              uint32_t r[16];
+#pragma unroll
+              for (int kt = 0; kt < 4; ++kt) {
+                uint2 lo = make_uint2(0u, 0u), hi = make_uint2(0u, 0u);
+                if (sd.resA != nullptr && kk + 16 * kt < sd.res_rank) {   // the rank is a multiple of 8
+                  lo = __ldg(reinterpret_cast<const uint2*>(ra + 16 * kt));
+                  hi = __ldg(reinterpret_cast<const uint2*>(rb + 16 * kt));
+                }
+                r[4 * kt + 0] = lo.x; r[4 * kt + 1] = lo.y;
+                r[4 * kt + 2] = hi.x; r[4 * kt + 3] = hi.y;
+              }
+              tc::tmem_st_16x256b_x4(tmem + (uint32_t(32 * q + 16 * sl) << 16) + kPACol + 32u * stage, r);
+            }
+          }
 #pragma unroll
           for (int sl = 0; sl < 2; ++sl) {
+            if (residual) continue;
             const int rowslab = 2 * q + sl;
             const int pal = nl == 1 ? 0 : (nl == 2 ? rowslab >> 2 : rowslab >> 1);
             const uint32_t tb = lane_base + uint32_t(pal >> 1) * kTableBytes + uint32_t(pal & 1) * 128u;
@@ -586,7 +624,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
           }
           {
             const bool on = ld.s < nseg;
-            load_slab_pair<BITS>(w[u], on ? code_ptr(ld) : p.seg[0].packed, q, on ? 1u : 0u);
+            const bool codes = on && ld.c < G;
+            load_slab_pair<BITS>(w[u], codes ? code_ptr(ld) : p.seg[0].packed, q, codes ? 1u : 0u);
             if (on) advance(ld);
           }
           tc::wait_st();
@@ -602,6 +641,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
     for (int sg = 0; sg < nseg; ++sg) {
       const int m0 = (seg_tile(sg) % p.m_tiles) * p.NT;
       const int c_hi = seg_c1(sg);
+      const int tcol = p.E ? segment_of_row(p, seg_tile(sg) / p.m_tiles).t_col0 - G * kChunkK : 0;
       for (int c = seg_c0(sg); c < c_hi; ++c, ++i) {
         const int xs = i % kPStages;
         if (i >= kPStages)
@@ -609,7 +649,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap, const Persis
                         &g_gemm_status, tc::kStatusWaitEmpty, p.wait_cycles);
         if (lane == 0 && !*abort_flag) {
           tc::mbar_expect_tx(bar_full + 8 * xs, stage_bytes);
-          tma_load_2d(xstage(xs), &xmap, bar_full + 8 * xs, c * kChunkK, m0);
+          if (c < G) tma_load_2d(xstage(xs), &xmap, bar_full + 8 * xs, c * kChunkK, m0);
+          else tma_load_2d(xstage(xs), &tmap, bar_full + 8 * xs, tcol + c * kChunkK, m0);
         }
         __syncwarp();
       }
@@ -869,8 +910,8 @@ SplitPlan plan_split(long long tiles, int G, int sms) {
 }
 
 template <typename T, int BITS>
-int launch_persistent(const CUtensorMap& map, const PersistParams& p, int grid, bool pdl,
-                      cudaStream_t stream) {
+int launch_persistent(const CUtensorMap& map, const CUtensorMap& tmap, const PersistParams& p,
+                      int grid, bool pdl, cudaStream_t stream) {
   auto kern = gemm_tc_persistent_kernel<T, BITS>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -894,7 +935,7 @@ int launch_persistent(const CUtensorMap& map, const PersistParams& p, int grid, 
   }
   cfg.attrs = attr;
   cfg.numAttrs = unsigned(na);
-  B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map, p));
+  B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map, tmap, p));
   return B200LUT_OK;
 }
 
@@ -943,7 +984,9 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
                     long long ld_acc = 0) {
   PersistParams pp = {};
   pp.acc_out = acc_out; pp.acc_in = acc_in; pp.ld_acc = ld_acc;
-  int rows = 0;
+  int rows = 0, extra = 0;
+  const uint16_t* t_base = nullptr;
+  long long t_ld = 0;
   for (int i = 0; i < nseg; ++i) {
     const b200lut_segment& s = segs[i];
     PersistSeg& d = pp.seg[i];
@@ -956,7 +999,23 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
     d.row0 = rows;
     d.n_groups = s.n_groups;
     rows += s.N / kTileRows;
+    if (s.res_rank > 0) {
+      // all residual projections of a launch read column blocks of ONE t matrix
+      if (!t_base) { t_base = static_cast<const uint16_t*>(s.res_t); t_ld = s.res_ldt; }
+      const long long col0 = static_cast<const uint16_t*>(s.res_t) - t_base;
+      const int blocks = (s.res_rank + kChunkK - 1) / kChunkK;
+      B200LUT_REQUIRE(s.res_ldt == t_ld && col0 >= 0 && col0 % 8 == 0 &&
+                          col0 + (long long)blocks * kChunkK <= t_ld,
+                      B200LUT_ERR_INVALID,
+                      "the res_t blocks of a merged prefill launch must lie in one [M, res_ldt] matrix, "
+                      "16-byte aligned and 64 * ceil(rank / 64) columns wide each (segment %d)", i);
+      d.resA = static_cast<const uint16_t*>(s.resA);
+      d.res_rank = s.res_rank;
+      d.t_col0 = int(col0);
+      if (blocks > extra) extra = blocks;
+    }
   }
+  pp.E = extra;
   pp.nsegs = nseg;
   const b200lut_segment& s = segs[0];
   pp.M = M; pp.K = K; pp.G = K / kChunkK;
@@ -976,8 +1035,13 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
     if (ms > 1000) ms = 1000;
     pp.wait_cycles = (long long)ms * 2000000ll;
   }
-  CUtensorMap pmap;
+  CUtensorMap pmap, tmap;
   if (int rc = encode_x_map(&pmap, x, ldx, M, K, dtype, pp.NT)) return rc;
+  if (extra) {
+    if (int rc = encode_x_map(&tmap, t_base, t_ld, M, int(t_ld), dtype, pp.NT)) return rc;
+  } else {
+    tmap = pmap;
+  }
   int sms = 148;
   {
     int dev = 0;
@@ -986,7 +1050,7 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
   }
   const long long tiles = (long long)pp.n_tiles * pp.m_tiles;
   int grid = int(tiles < sms ? tiles : sms);
-  const SplitPlan sp = plan_split(tiles, pp.G, sms);
+  const SplitPlan sp = plan_split(tiles, pp.G + pp.E, sms);
   if (sp.split && workspace && workspace_bytes >= sp.bytes && aligned16(workspace) &&
       !acc_out && !acc_in) {
     pp.split = sp.split; pp.full = sp.full; pp.left = sp.left;
@@ -996,8 +1060,8 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
   }
 #define B200LUT_PERSIST(B)                                                                      \
   (dtype == B200LUT_BF16                                                                          \
-       ? launch_persistent<__nv_bfloat16, B>(pmap, pp, grid, pdl, cudaStream_t(stream))          \
-       : launch_persistent<__half, B>(pmap, pp, grid, pdl, cudaStream_t(stream)))
+       ? launch_persistent<__nv_bfloat16, B>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream))    \
+       : launch_persistent<__half, B>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)))
   switch (s.bits) {
     case 4: return B200LUT_PERSIST(4);
     case 3: return B200LUT_PERSIST(3);
@@ -1012,8 +1076,14 @@ int check_gemm_segment(const b200lut_segment& s) {
   B200LUT_REQUIRE(s.packed && s.lut && s.out, B200LUT_ERR_INVALID, "null codes, palette or output");
   B200LUT_REQUIRE(s.N > 0 && s.N % kTileRows == 0 && s.ldo >= s.N, B200LUT_ERR_INVALID,
                   "N must be a positive multiple of 128 and ldo >= N (N=%d)", s.N);
-  B200LUT_REQUIRE(s.res_rank == 0, B200LUT_ERR_UNSUPPORTED,
-                  "the prefill GEMM does not fuse the low-rank residual (two dense GEMMs do it)");
+  B200LUT_REQUIRE(s.res_rank >= 0 && s.res_rank <= 1024 && s.res_rank % 8 == 0, B200LUT_ERR_UNSUPPORTED,
+                  "the rank of a fused low-rank residual is a multiple of 8, at most 1024 (got %d)",
+                  s.res_rank);
+  B200LUT_REQUIRE(s.res_rank == 0 || (s.resA && s.res_t && aligned16(s.resA) && aligned16(s.res_t) &&
+                                      s.res_ldt % 8 == 0),
+                  B200LUT_ERR_INVALID,
+                  "a fused low-rank residual needs resA and res_t (from b200lut_residual_project_rows), "
+                  "16-byte aligned, and a res_ldt that is a multiple of 8");
   B200LUT_REQUIRE(s.group_size >= 32 && s.n_groups >= 1 &&
                       ((s.group_size < 128 && (s.group_size & (s.group_size - 1)) == 0) ||
                        s.group_size % 128 == 0),
@@ -1099,6 +1169,7 @@ extern "C" int b200lut_gemm_two_stream(const void* x, int64_t ldx, int M, int K,
   float* acc = static_cast<float*>(scratch);
   b200lut_segment first = s, second = s;
   first.packed2 = first.lut2 = nullptr; first.bits2 = 0; first.bias = nullptr;
+  first.res_rank = 0; first.resA = nullptr; first.res_t = nullptr;   // the second launch carries it
   second.packed = s.packed2; second.lut = s.lut2; second.bits = s.bits2;
   second.packed2 = second.lut2 = nullptr; second.bits2 = 0;
   const bool pdl = (flags & 1) != 0;
@@ -1141,6 +1212,9 @@ extern "C" int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dty
 
   // what is left for the one-tile kernel: two code streams, the fused gate/up form, four
   // palettes per tile — it looks 4-bit codes up
+  B200LUT_REQUIRE(s.res_rank == 0, B200LUT_ERR_UNSUPPORTED,
+                  "the low-rank residual is fused into one-stream prefill launches with at most two "
+                  "palettes per tile, and into b200lut_gemm_two_stream");
   B200LUT_REQUIRE(s.bits == 4 && (!two || s.bits2 == 4), B200LUT_ERR_UNSUPPORTED,
                   "two-stream, gate/up-fused and group-size-32 prefill GEMMs serve 4-bit codes "
                   "(got %d / %d)", s.bits, s.bits2);

@@ -704,7 +704,7 @@ int convert_segments(const b200lut_segment* segs, int nseg, bool silu, SegDev* o
                       "segment %d: resA and res_t must be 16-byte aligned, res_ldt a multiple of 4", i);
     }
     d.resA = static_cast<const uint16_t*>(s.resA);
-    d.res_t = s.res_t;
+    d.res_t = static_cast<const float*>(s.res_t);
     d.res_ldt = s.res_ldt;
     d.res_rank = s.res_rank;
     d.pad = 0;

@@ -83,6 +83,101 @@ __global__ void __launch_bounds__(kProjThreads) residual_project_kernel(
   }
 }
 
+
+// Prefill form of the same first factor, for any number of activation rows: t[m, c] rounded
+// once to the compute dtype (the reference route rounds x @ resB^T to the factors' dtype before
+// the second product, src/scripts/palettized_modules.py:1363-1364), written as a [M, ldt]
+// matrix whose columns [R, cols) are zero so that the prefill GEMM can take 64-column blocks
+// of it as extra k-blocks of its accumulator.
+//
+// One block per (16 activation rows, 64 columns of t): eight warps take the 32-wide k steps
+// round-robin and run mma.sync m16n8k16 (bf16 / f16, fp32 sums) with the SAME permutation of
+// k inside a step on both operands — lane (g, c) reads 16 contiguous bytes of its rows at
+// k0 + 8 c and feeds elements (0,1) / (2,3) to the first instruction and (4,5) / (6,7) to the
+// second — so every global load is a full 16-byte one and no shuffle is needed. The warps'
+// partial sums meet in shared memory in warp order (the result does not depend on the
+// schedule), then one rounding and the store.
+constexpr int kRowsProjWarps = 8;
+constexpr int kRowsProjCols = 64;
+constexpr int kRowsProjPitch = kRowsProjCols + 4;   // floats per staged row
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  if constexpr (DType<T>::id == B200LUT_BF16) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+                 "{%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+                 "{%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowsProjWarps * 32) residual_rows_kernel(
+    const uint16_t* __restrict__ x, long long ldx, int M, int K, const uint16_t* __restrict__ resB,
+    int R, uint16_t* __restrict__ t, long long ldt, int cols) {
+  __shared__ float red[kRowsProjWarps][16][kRowsProjPitch];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  const int m0 = blockIdx.x * 16, c0 = blockIdx.y * kRowsProjCols;
+  // residual rows of this column block that exist, in 8-wide tiles
+  int tiles = (R - c0 + 7) / 8;
+  tiles = tiles < 0 ? 0 : (tiles > 8 ? 8 : tiles);
+  asm volatile("griddepcontrol.launch_dependents;");
+
+  float acc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+  const bool row_lo = m0 + g < M, row_hi = m0 + g + 8 < M;
+  const uint16_t* xlo = x + size_t(row_lo ? m0 + g : 0) * ldx + 8 * c;
+  const uint16_t* xhi = x + size_t(row_hi ? m0 + g + 8 : 0) * ldx + 8 * c;
+  const uint16_t* brow = resB + size_t(c0 + g) * K + 8 * c;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int steps = K / 32;
+#pragma unroll 2
+  for (int s = warp; s < steps; s += kRowsProjWarps) {
+    const int k0 = 32 * s;
+    const uint4 a = row_lo ? __ldcg(reinterpret_cast<const uint4*>(xlo + k0)) : zero;
+    const uint4 b = row_hi ? __ldcg(reinterpret_cast<const uint4*>(xhi + k0)) : zero;
+    uint4 w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      w[j] = (j < tiles && c0 + 8 * j + g < R)
+                 ? __ldg(reinterpret_cast<const uint4*>(brow + size_t(8 * j) * K + k0)) : zero;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j < tiles) {   // block-uniform
+        mma16816<T>(acc[j], a.x, b.x, a.y, b.y, w[j].x, w[j].y);
+        mma16816<T>(acc[j], a.z, b.z, a.w, b.w, w[j].z, w[j].w);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    red[warp][g][8 * j + 2 * c] = acc[j][0];
+    red[warp][g][8 * j + 2 * c + 1] = acc[j][1];
+    red[warp][g + 8][8 * j + 2 * c] = acc[j][2];
+    red[warp][g + 8][8 * j + 2 * c + 1] = acc[j][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < 16 * kRowsProjCols; idx += kRowsProjWarps * 32) {
+    const int r = idx / kRowsProjCols, col = idx % kRowsProjCols;
+    if (m0 + r < M && c0 + col < cols) {
+      float v = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < kRowsProjWarps; ++w2) v += red[w2][r][col];
+      t[size_t(m0 + r) * ldt + c0 + col] = DType<T>::from_float(v);
+    }
+  }
+}
+
 }  // namespace
 }  // namespace b200lut
 
@@ -123,5 +218,47 @@ extern "C" int b200lut_residual_project(const void* x, int64_t ldx, int M, int K
     B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, residual_project_kernel<__nv_bfloat16>, xp, ldx_, M, K, bp, t, ldt_));
   else
     B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, residual_project_kernel<__half>, xp, ldx_, M, K, bp, t, ldt_));
+  return B200LUT_OK;
+}
+
+extern "C" int b200lut_residual_project_rows(const void* x, int64_t ldx, int M, int K, int dtype,
+                                             const void* resB, int R, void* t, int64_t ldt,
+                                             int cols, int flags, void* stream) {
+  B200LUT_REQUIRE(x && resB && t, B200LUT_ERR_INVALID, "null x, resB or t");
+  B200LUT_REQUIRE(M >= 1, B200LUT_ERR_INVALID, "M must be >= 1, got %d", M);
+  B200LUT_REQUIRE(K > 0 && K % kChunkK == 0, B200LUT_ERR_INVALID,
+                  "K must be a positive multiple of 64, got %d", K);
+  B200LUT_REQUIRE(R >= 1 && cols >= R && cols % kRowsProjCols == 0 && ldt >= cols && ldt % 8 == 0,
+                  B200LUT_ERR_INVALID,
+                  "need 1 <= R <= cols, cols a multiple of 64 and ldt >= cols, a multiple of 8 "
+                  "(got R=%d, cols=%d, ldt=%lld)", R, cols, (long long)ldt);
+  B200LUT_REQUIRE(dtype == B200LUT_BF16 || dtype == B200LUT_F16, B200LUT_ERR_INVALID,
+                  "dtype must be B200LUT_BF16 or B200LUT_F16");
+  B200LUT_REQUIRE(aligned16(x) && aligned16(resB) && aligned16(t) && ldx % 8 == 0 && ldx >= K,
+                  B200LUT_ERR_ALIGN,
+                  "x, resB and t must be 16-byte aligned, the x row stride a multiple of 8 and >= K");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned((M + 15) / 16), unsigned(cols / kRowsProjCols), 1);
+  cfg.blockDim = dim3(kRowsProjWarps * 32, 1, 1);
+  cfg.stream = cudaStream_t(stream);
+  cudaLaunchAttribute attr[1];
+  int na = 0;
+  if (flags & 1) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = unsigned(na);
+  const uint16_t* xp = static_cast<const uint16_t*>(x);
+  const uint16_t* bp = static_cast<const uint16_t*>(resB);
+  uint16_t* tp = static_cast<uint16_t*>(t);
+  const long long ldx_ = ldx, ldt_ = ldt;
+  if (dtype == B200LUT_BF16)
+    B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, residual_rows_kernel<__nv_bfloat16>, xp, ldx_, M, K, bp,
+                                       R, tp, ldt_, cols));
+  else
+    B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, residual_rows_kernel<__half>, xp, ldx_, M, K, bp, R,
+                                       tp, ldt_, cols));
   return B200LUT_OK;
 }

@@ -284,14 +284,27 @@ class PalettizedLinear(nn.Module):
             return _fht.fht_apply_awq(x, signs, self._on("awq", self.awq_scale, x.device))
         return _fht.fht_apply(x, signs)
 
-    def _fusable_residual(self, x2: torch.Tensor) -> bool:
-        """Decode rows, rank a multiple of 8, factors in the compute dtype and 16-byte aligned:
-        the residual rides the GEMV (one projection launch + the epilogue)."""
-        return (self.has_residual() and 0 < x2.shape[0] <= GEMV_MAX_M
-                and self.resA.shape[1] % 8 == 0 and self.resA.dtype == x2.dtype
-                and self.resB.dtype == x2.dtype and self.resA.is_contiguous()
+    def _fusable_residual(self, M: int, dtype: torch.dtype) -> bool:
+        """Rank a multiple of 8, factors in the compute dtype and 16-byte aligned: the residual
+        rides the projection launch. At decode (M <= 16) a projection launch computes
+        t = x @ resB^T in fp32 and the GEMV epilogue adds t @ resA^T; at prefill t is rounded to
+        the compute dtype (as the reference route does) and enters the tensor-core GEMM's
+        accumulator as extra k-blocks — one-stream launches with at most two palettes per
+        128-row tile, and the two-stream launch pair."""
+        if M > GEMV_MAX_M and not self._prefill_residual_served():
+            return False
+        return (self.has_residual() and M > 0 and self.resA.shape[1] <= 1024
+                and self.resA.shape[1] % 8 == 0 and self.resA.dtype == dtype
+                and self.resB.dtype == dtype and self.resA.is_contiguous()
                 and self.resB.is_contiguous() and self.resA.data_ptr() % 16 == 0
                 and self.resB.data_ptr() % 16 == 0)
+
+    def _prefill_residual_served(self) -> bool:
+        if self.group_size < 64 or self.K < 128:
+            return False
+        if not self.has_stream2:
+            return True
+        return not (self.bitwidth == 4 and self.bitwidth2 == 4)   # the 4 + 4 pair is one one-tile launch
 
     def _rotation_fuses(self, M: int, dtype=None) -> bool:
         """The input rotation can run inside the decode launch: 4-bit single stream, at most 8
@@ -319,7 +332,10 @@ class PalettizedLinear(nn.Module):
         out = torch.empty(M, self.N, dtype=x2.dtype, device=x2.device)
         if M == 0:
             return out
-        res_t = _lib.residual_project(x2, self.resB, flags=_flags()) if fuse_residual else None
+        res_t = None
+        if fuse_residual:
+            project = _lib.residual_project if M <= GEMV_MAX_M else _lib.residual_project_rows
+            res_t = project(x2, self.resB, flags=_flags())
         segs = _lib.make_segments([self._segment_desc(out, res_t=res_t)])
         if fuse_rotation:
             _lib.gemv_input(x2, segs, 1, self._input_transform(x2.device), flags=_flags())
@@ -398,7 +414,7 @@ class PalettizedLinear(nn.Module):
             xc = x2 if x2.dtype == cd else x2.to(cd)
             if xc.stride(-1) != 1 or xc.stride(0) % 8 or xc.data_ptr() % 16:
                 xc = xc.contiguous().clone() if xc.data_ptr() % 16 else xc.contiguous()
-            residual_done = self._fusable_residual(xc)
+            residual_done = self._fusable_residual(xc.shape[0], xc.dtype)
             out = self._kernel_matmul(xc, fuse_residual=residual_done, fuse_rotation=fuse_rotation).to(x.dtype)
             bias_done = True
         if self.has_residual() and not (not self.reference and residual_done):
@@ -423,15 +439,15 @@ def _mergeable(mods, x: torch.Tensor) -> bool:
             return False
         if m.lut.dtype not in (torch.float16, torch.bfloat16):
             return False
-        if m.has_residual() and not m._fusable_residual(x2.to(m.lut.dtype)):
+        if m.has_residual() and not m._fusable_residual(x2.shape[0], m.lut.dtype):
             return False
     return True
 
 
 def _prefill_mergeable(mods, x: torch.Tensor) -> bool:
     """Prefill-merge verdict (M > 16): projections that share x run as ONE tensor-core launch
-    when they have one code stream each, one code width, one group size >= 64, one dtype, no
-    low-rank residual, and are unrotated or share one rotation."""
+    when they have one code stream each, one code width, one group size >= 64, one dtype, only
+    low-rank residuals the launch can carry, and are unrotated or share one rotation."""
     x2 = x.reshape(-1, x.shape[-1])
     if x2.shape[0] <= GEMV_MAX_M or not x.is_cuda or len(mods) > _lib.GEMM_MULTI_MAX:
         return False
@@ -443,7 +459,9 @@ def _prefill_mergeable(mods, x: torch.Tensor) -> bool:
             return False
         if m.lut.dtype != m0.lut.dtype or m.lut.dtype not in (torch.float16, torch.bfloat16):
             return False
-        if m.has_stream2 or m.has_residual() or not _same_rotation(m0, m):
+        if m.has_stream2 or not _same_rotation(m0, m):
+            return False
+        if m.has_residual() and not m._fusable_residual(x2.shape[0], m.lut.dtype):
             return False
         if m.bitwidth != m0.bitwidth or m.group_size != m0.group_size or m.group_size < 64:
             return False
@@ -460,7 +478,16 @@ def _prefill_merged(mods, x: torch.Tensor, outs) -> None:
     if m0.rot_signs is not None:
         x2 = m0._rotate_input(x2)
     x2 = x2.to(m0.lut.dtype).contiguous()
-    descs = [m._segment_desc(o, ldo=o.stride(0)) for m, o in zip(mods, outs)]
+    # the residual projections' t blocks lie side by side in one matrix
+    widths = [_lib.residual_block_cols(m.resB.shape[0]) if m.has_residual() else 0 for m in mods]
+    t_all = torch.empty(x2.shape[0], sum(widths), dtype=x2.dtype, device=x2.device) if any(widths) else None
+    descs, col = [], 0
+    for m, o, w in zip(mods, outs, widths):
+        res_t = None
+        if w:
+            res_t = _lib.residual_project_rows(x2, m.resB, flags=_flags(), out=t_all[:, col:col + w])
+            col += w
+        descs.append(m._segment_desc(o, ldo=o.stride(0), res_t=res_t))
     _lib.gemm_multi(x2, _lib.make_segments(descs), len(descs), flags=_flags())
 
 

@@ -68,7 +68,12 @@ def test_validation_errors_carry_a_message():
     rc = L.b200lut_gemv_multi(x, 64, 1, 64, 0, ctypes.byref(seg), 1, 0, 0, None, 0, 0, None)
     assert rc == 1 and b"resA" in L.b200lut_last_error()
     rc = L.b200lut_gemm(x, 64, 32, 64, 0, ctypes.byref(seg), 0, 0, None)
-    assert rc == 2 and b"residual" in L.b200lut_last_error()
+    assert rc == 1 and b"b200lut_residual_project_rows" in L.b200lut_last_error()
+    seg.res_rank = 12                                   # the prefill GEMM wants a multiple of 8 too
+    rc = L.b200lut_gemm(x, 64, 32, 64, 0, ctypes.byref(seg), 0, 0, None)
+    assert rc == 2 and b"multiple of 8" in L.b200lut_last_error()
+    rc = L.b200lut_residual_project_rows(x, 64, 32, 64, 0, x, 8, x, 64, 32, 0, None)
+    assert rc == 1 and b"multiple of 64" in L.b200lut_last_error()
     seg.res_rank = 0
     # the split schedule's workspace: sized without a device (148 SMs assumed), validated like
     # the plain entry
