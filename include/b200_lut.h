@@ -292,6 +292,15 @@ typedef struct b200lut_input {
   const void* x_mul;
   const float* rot_signs;
   const float* awq_scale;
+  /* Non-zero: every segment of the launch has its own fold — seg_rot_signs[i] (NULL: segment
+   * i takes the rows as they are) and seg_awq_scale[i] — as the segment table of the
+   * reference's merged kernels carries a rotation per segment
+   * (src/flute_extended/include/flute/gemv.cuh:112-133,
+   * src/flute_extended/src/kernel_gemv_multi.cu:101-334). rot_signs / awq_scale must then be
+   * NULL and the epilogue B200LUT_EPI_NONE; a launch block never crosses a segment. */
+  int per_segment;
+  const float* seg_rot_signs[8];
+  const float* seg_awq_scale[8];
 } b200lut_input;
 
 /* b200lut_gemv_exchange with an input transform (in == NULL: identical to it). */

@@ -76,7 +76,9 @@ class Exchange(ctypes.Structure):
 
 class Input(ctypes.Structure):
     """struct b200lut_input: what a decode launch does to its activation rows first."""
-    _fields_ = [("x_mul", ctypes.c_void_p), ("rot_signs", ctypes.c_void_p), ("awq_scale", ctypes.c_void_p)]
+    _fields_ = [("x_mul", ctypes.c_void_p), ("rot_signs", ctypes.c_void_p), ("awq_scale", ctypes.c_void_p),
+                ("per_segment", ctypes.c_int), ("seg_rot_signs", ctypes.c_void_p * 8),
+                ("seg_awq_scale", ctypes.c_void_p * 8)]
 
 
 class LibraryError(RuntimeError):
@@ -368,13 +370,26 @@ def gemv_exchange(x: torch.Tensor, segs, nseg: int, ex: "Exchange", epilogue: in
 
 
 def make_input(x_mul: Optional[torch.Tensor] = None, rot_signs: Optional[torch.Tensor] = None,
-               awq_scale: Optional[torch.Tensor] = None) -> Input:
-    """An input transform for gemv_input (tensors must stay alive while it is used)."""
-    for name, v in (("rot_signs", rot_signs), ("awq_scale", awq_scale)):
+               awq_scale: Optional[torch.Tensor] = None, seg_folds=None) -> Input:
+    """An input transform for gemv_input (tensors must stay alive while it is used).
+    seg_folds: one (rot_signs or None, awq_scale or None) pair per segment of the launch — every
+    segment rotates the shared rows with its own fold (excludes rot_signs / awq_scale)."""
+    folds = list(seg_folds) if seg_folds is not None else []
+    if folds and (rot_signs is not None or awq_scale is not None):
+        raise ValueError("per-segment folds exclude a launch-wide fold")
+    if len(folds) > 8:
+        raise ValueError("at most 8 segments per launch")
+    flat = [("rot_signs", rot_signs), ("awq_scale", awq_scale)]
+    flat += [(f"seg_folds[{i}]", v) for i, pair in enumerate(folds) for v in pair]
+    for name, v in flat:
         if v is not None and (v.dtype != torch.float32 or not v.is_contiguous() or not v.is_cuda):
             raise ValueError(f"{name} must be a contiguous float32 CUDA tensor")
     inp = Input()
     inp.x_mul, inp.rot_signs, inp.awq_scale = ptr(x_mul), ptr(rot_signs), ptr(awq_scale)
+    if folds:
+        inp.per_segment = 1
+        for i, (sg, aw) in enumerate(folds):
+            inp.seg_rot_signs[i], inp.seg_awq_scale[i] = ptr(sg), ptr(aw)
     return inp
 
 

@@ -91,6 +91,9 @@ struct GemvParams {
   const uint16_t* x_mul;     // x := silu(x) * x_mul
   const float* rot_signs;    // x := Hadamard rotation of x (segments + signs)
   const float* awq_scale;    // ... in the AWQ-compensated form
+  int per_seg;               // every segment has its own fold (seg_signs / seg_awq, null = none)
+  const float* seg_signs[kMaxSeg];
+  const float* seg_awq[kMaxSeg];
 };
 
 template <typename T>
@@ -820,12 +823,13 @@ bool rows_geometry(const GemvParams& gp, int tiles, RowsGeom* out) {
   mix(unsigned(gp.nseg)); mix(unsigned(gp.epilogue)); mix(unsigned(gp.M)); mix(unsigned(gp.K));
   mix(unsigned(tiles)); mix(unsigned(sm_count_cached()));
   uint32_t fht_bytes = 0;
-  if (gp.rot_signs) {   // fp32 scratch of the largest power-of-two segment of K
+  if (gp.rot_signs || gp.per_seg) {   // fp32 scratch of the largest power-of-two segment of K
     int b = 1;
     while (b * 2 <= gp.K) b *= 2;
     fht_bytes = uint32_t(b) * 4u;
   }
   mix(fht_bytes);
+  mix(unsigned(gp.per_seg));
   for (int i = 0; i < gp.nseg; ++i) {
     mix(unsigned(gp.seg[i].N)); mix(unsigned(gp.seg[i].gs)); mix(unsigned(gp.seg[i].n_groups));
     mix(unsigned(gp.seg[i].bits)); mix(gp.seg[i].packed2 ? 1u : 0u);
@@ -838,7 +842,8 @@ bool rows_geometry(const GemvParams& gp, int tiles, RowsGeom* out) {
   if (hit < 0) {
     hit = used < 64 ? used++ : int(h % 64);
     cache[hit].key = h;
-    cache[hit].ok = rows_plan(gp.seg, gp.nseg, silu, tiles, gp.M, gp.K, sm_count_cached(), fht_bytes, &cache[hit].g);
+    cache[hit].ok = rows_plan(gp.seg, gp.nseg, silu, tiles, gp.M, gp.K, sm_count_cached(), fht_bytes,
+                              gp.per_seg, &cache[hit].g);
   }
   if (cache[hit].ok) *out = cache[hit].g;
   return cache[hit].ok;
@@ -853,9 +858,15 @@ int try_rows(const GemvParams& gp, const uint16_t* x2, int tiles, bool pdl, cuda
   RowsParams p = {};
   p.x = gp.x;
   p.x2 = x2 ? x2 : gp.x_mul;
-  if (gp.rot_signs) {
+  if (gp.rot_signs || gp.per_seg) {
     p.rot_signs = gp.rot_signs;
     p.awq_scale = gp.awq_scale;
+    p.per_seg = g.per_seg;
+    for (int i = 0; i <= kMaxSeg; ++i) p.blk0[i] = g.blk0[i];
+    for (int i = 0; i < kMaxSeg; ++i) {
+      p.seg_signs[i] = gp.seg_signs[i];
+      p.seg_awq[i] = gp.seg_awq[i];
+    }
     p.fht_abs = g.fht_abs;
     int off = 0;
     while (off < gp.K) {
@@ -1064,10 +1075,22 @@ extern "C" int b200lut_gemv_input(const void* x, int64_t ldx, int M, int K, int 
   int tiles = 0, max_tables = 1;
   if (int rc = convert_segments(segs, nseg, silu, p.seg, &tiles, &max_tables)) return rc;
   p.tiles_total = tiles;
-  const bool transformed = in && (in->x_mul || in->rot_signs || in->awq_scale);
+  const bool transformed = in && (in->x_mul || in->rot_signs || in->awq_scale || in->per_segment);
   if (transformed) {
     B200LUT_REQUIRE(!in->awq_scale || in->rot_signs, B200LUT_ERR_INVALID,
                     "input transform: an AWQ scale needs the rotation signs");
+    if (in->per_segment) {
+      B200LUT_REQUIRE(!in->rot_signs && !silu, B200LUT_ERR_INVALID,
+                      "input transform: per-segment folds exclude a launch-wide fold and the silu-mul "
+                      "epilogue (a gate/up pair shares its input)");
+      p.per_seg = 1;
+      for (int i = 0; i < nseg; ++i) {
+        B200LUT_REQUIRE(!in->seg_awq_scale[i] || in->seg_rot_signs[i], B200LUT_ERR_INVALID,
+                        "input transform: segment %d has an AWQ scale but no rotation signs", i);
+        p.seg_signs[i] = in->seg_rot_signs[i];
+        p.seg_awq[i] = in->seg_awq_scale[i];
+      }
+    }
     B200LUT_REQUIRE(!in->x_mul || aligned16(in->x_mul), B200LUT_ERR_ALIGN,
                     "input transform: x_mul must be 16-byte aligned");
     B200LUT_REQUIRE(split <= 0 && !(flags & B200LUT_FLAG_TILE_KERNEL), B200LUT_ERR_UNSUPPORTED,

@@ -59,6 +59,12 @@ struct RowsParams {
   // power-of-two segments of K, as b200lut_fht runs them; fht_abs: fp32 scratch of one segment
   const float* rot_signs;
   const float* awq_scale;
+  // per_seg: every segment has its own fold (seg_signs[i] null = that segment's input is used
+  // as it is); blocks then never cross a segment: segment i owns blocks [blk0[i], blk0[i + 1])
+  int per_seg;
+  int blk0[kMaxSeg + 1];
+  const float* seg_signs[kMaxSeg];
+  const float* seg_awq[kMaxSeg];
   uint32_t fht_abs;
   int fht_nseg;
   int fht_off[kRowsMaxFhtSegs], fht_len[kRowsMaxFhtSegs], fht_stages[kRowsMaxFhtSegs];
@@ -100,6 +106,69 @@ __device__ __forceinline__ uint4 silu_mul8(uint4 g, uint4 u) {
     o[i] = lo | (hi << 16);
   }
   return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// 4096-point Hadamard butterfly (no scaling) by 256 threads, 16 values per thread, the stages
+// in the order len = 1, 2, 4, ... 2048 — the order of b200lut_fht, so every value goes through
+// the same additions and subtractions and has the same bits. Stages 0-3, 4-7 and 8-11 each run
+// on 16 registers; between them the values are regrouped through `buf` (4096 floats; value i
+// lives in the 16-byte piece (i >> 2) ^ ((i >> 5) & 3), which keeps the 16-byte stores of the
+// first pass and the strided reads of the last one free of bank conflicts).
+// In: v[j] = value 16 t + j. Out: v[j] = value 256 j + t. `bar` = barrier id of the 256 threads.
+__device__ __forceinline__ void fht16_regs(float (&v)[16]) {
+#pragma unroll
+  for (int len = 1; len < 16; len <<= 1)
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (!(i & len)) {
+        const float a = v[i], b = v[i + len];
+        v[i] = a + b;
+        v[i + len] = a - b;
+      }
+}
+
+__device__ __forceinline__ int fht4096_slot(int i) { return (((i >> 2) ^ ((i >> 5) & 3)) << 2) | (i & 3); }
+
+__device__ __forceinline__ void fht4096_regs(float (&v)[16], float* buf, int t) {
+  fht16_regs(v);                                                   // stages 0-3
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    *reinterpret_cast<float4*>(buf + fht4096_slot(16 * t + 4 * c)) =
+        make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  const int mid = ((t >> 4) << 8) | (t & 15);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = buf[fht4096_slot(mid + 16 * j)];
+  fht16_regs(v);                                                   // stages 4-7
+#pragma unroll
+  for (int j = 0; j < 16; ++j) buf[fht4096_slot(mid + 16 * j)] = v[j];
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = buf[fht4096_slot(256 * j + t)];
+  fht16_regs(v);                                                   // stages 8-11
+  asm volatile("bar.sync 1, 256;" ::: "memory");                   // buf may be written again
+}
+
+// The 32-row units [u0, u1) of row block rb. Plain: `row_blocks` even ranges of the launch's
+// units. Per-segment folds: even ranges of the units of the segment that owns the block.
+__host__ __device__ inline void rows_block_units(int per_seg, const int* blk0, const SegDev* seg, int nseg,
+                                                 int units_total, int row_blocks, int rb, int* u0, int* u1,
+                                                 int* owner) {
+  if (!per_seg) {
+    *u0 = int((long long)units_total * rb / row_blocks);
+    *u1 = int((long long)units_total * (rb + 1) / row_blocks);
+    *owner = 0;
+    return;
+  }
+  int s = 0;
+  for (int i = 1; i < nseg; ++i)
+    if (rb >= blk0[i]) s = i;
+  const int ub = 4 * seg[s].tile_begin;
+  const int ue = s + 1 < nseg ? 4 * seg[s + 1].tile_begin : units_total;
+  const int nb = blk0[s + 1] - blk0[s], lb = rb - blk0[s];
+  *u0 = ub + int((long long)(ue - ub) * lb / nb);
+  *u1 = ub + int((long long)(ue - ub) * (lb + 1) / nb);
+  *owner = s;
 }
 
 // What the epilogue needs to know about one 32-row unit of the block, worked out once in the
@@ -193,8 +262,10 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
   const int kc = c1 - c0;
   const bool silu = p.epilogue == B200LUT_EPI_SILU_MUL;
   const int ppu = silu ? 2 : 1;
-  const int u0 = int((long long)p.units_total * rb / p.row_blocks);
-  const int u1 = int((long long)p.units_total * (rb + 1) / p.row_blocks);
+  int u0, u1, owner;
+  rows_block_units(p.per_seg, p.blk0, p.seg, p.nseg, p.units_total, p.row_blocks, rb, &u0, &u1, &owner);
+  const float* rot_signs = p.per_seg ? p.seg_signs[owner] : p.rot_signs;
+  const float* awq_scale = p.per_seg ? p.seg_awq[owner] : p.awq_scale;
   const int nplanes = bad_window ? 0 : (u1 - u0) * ppu;
   const int M = p.M, Mp = p.Mp;
 
@@ -300,6 +371,14 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
   } else {
     constexpr int NTS = NT / 2;   // threads that stage
     const int tid = int(threadIdx.x) - NTS;
+    // the rotation's signs (and scales) do not depend on the previous kernel: pull their lines
+    // into L1 while waiting for it
+    if (rot_signs) {
+      for (int i = tid * 32; i < p.K; i += NTS * 32) {
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(rot_signs + i));
+        if (awq_scale) asm volatile("prefetch.global.L1 [%0];" ::"l"(awq_scale + i));
+      }
+    }
     // the dependency: the previous kernel of the stream, or the peers' pushes
     if (p.ex.wait) {
       for (int i = tid; i < p.ex.world * p.ex.blocks; i += NTS) peer_poll(p.ex, i);
@@ -309,7 +388,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
     }
     // activation rows of this block's K range into shared memory, B-fragment order:
     // element (chunk g, tig, kt, j) at g*128 + tig*32 + kt*8 + 2j bytes = x[64g + 16kt + 4tig + j]
-    if (!bad_window && p.rot_signs) {
+    if (!bad_window && rot_signs) {
       // Rotated rows (the boundary fold of the reference's rotated artifacts, fused like its
       // gemv_fht_prologue, src/flute_extended/include/flute/gemv.cuh:305-351): per row and
       // segment, fp32 butterfly in shared memory in the stage order of b200lut_fht (same
@@ -321,6 +400,58 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
         for (int sg = 0; sg < p.fht_nseg; ++sg) {
           const int off = p.fht_off[sg], n = p.fht_len[sg], stages = p.fht_stages[sg];
           const float inv = p.fht_inv[sg];
+          if (n == 4096 || n == 8192) {
+            // register form: one or two 4096-point transforms; for 8192 values the first half
+            // waits in the upper part of the scratch (every thread reads back its own slots) and
+            // the last stage (len = 4096) joins the two halves on the way out
+            static_assert(NTS == 256, "fht4096_regs is written for 256 threads");
+            const int halves = n >> 12;
+            float v[16];
+            for (int h = 0; h < halves; ++h) {
+              uint4 raw[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+              const int i0 = 4096 * h + 16 * tid;
+              if (m < M) {
+                const size_t at = size_t(m) * p.ldx + size_t(off + i0);
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                  raw[c] = __ldcg(reinterpret_cast<const uint4*>(p.x + at + 8 * c));
+                  if (p.x2) raw[c] = silu_mul8<T>(raw[c], __ldcg(reinterpret_cast<const uint4*>(p.x2 + at + 8 * c)));
+                }
+              }
+              const uint32_t wv[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float f = DType<T>::to_float(uint16_t(wv[j >> 1] >> (16 * (j & 1))));
+                if (awq_scale) f = f * awq_scale[off + i0 + j];
+                v[j] = f;
+              }
+              fht4096_regs(v, buf, tid);
+              if (h + 1 < halves) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) buf[4096 + 256 * j + tid] = v[j];
+              }
+            }
+            auto emit = [&](int k, float val) {
+              float r = val * rot_signs[k];
+              r = r * inv;
+              if (awq_scale) r = __fdiv_rn(r, awq_scale[k]);
+              const int g = k >> 6, w64 = k & 63;
+              *reinterpret_cast<uint16_t*>(xs + (size_t(m) * kc + g) * 128 + ((w64 & 15) >> 2) * 32 +
+                                           (w64 >> 4) * 8 + (w64 & 3) * 2) = DType<T>::from_float(r);
+            };
+            if (halves == 2) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float a = buf[4096 + 256 * j + tid], b = v[j];
+                emit(off + 256 * j + tid, a + b);
+                emit(off + 4096 + 256 * j + tid, a - b);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) emit(off + 256 * j + tid, v[j]);
+            }
+            continue;
+          }
           for (int i = tid * 8; i < n; i += NTS * 8) {
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (m < M) {
@@ -332,7 +463,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               float f = DType<T>::to_float(uint16_t(wv[j >> 1] >> (16 * (j & 1))));
-              if (p.awq_scale) f = f * p.awq_scale[off + i + j];
+              if (awq_scale) f = f * awq_scale[off + i + j];
               buf[i + j] = f;
             }
           }
@@ -355,9 +486,9 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
                 const int k = off + i + 2 * h + e;
-                float r = buf[i + 2 * h + e] * p.rot_signs[k];
+                float r = buf[i + 2 * h + e] * rot_signs[k];
                 r = r * inv;
-                if (p.awq_scale) r = __fdiv_rn(r, p.awq_scale[k]);
+                if (awq_scale) r = __fdiv_rn(r, awq_scale[k]);
                 pair |= uint32_t(DType<T>::from_float(r)) << (16 * e);
               }
               o[h] = pair;
@@ -552,16 +683,20 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
 
 struct RowsGeom {
   int units_total, row_blocks, split, ntables, red_planes, Mp, xreg;
+  int per_seg, blk0[kMaxSeg + 1];
   uint32_t xs_abs, red_abs, part_abs, fht_abs, meta_abs, end_abs;
 };
 
 // Palette slots the busiest block needs when `units` units are cut into `row_blocks` ranges
 // (the device assigns one slot per run of consecutive planes with the same palette, per stream).
-int rows_max_slots(const SegDev* seg, int nseg, bool silu, int units, int row_blocks) {
+int rows_max_slots(const SegDev* seg, int nseg, bool silu, int units, int row_blocks, int per_seg = 0,
+                   const int* blk0 = nullptr, int* most_units = nullptr) {
   const int ppu = silu ? 2 : 1;
-  int worst = 0;
+  int worst = 0, widest = 0;
   for (int rb = 0; rb < row_blocks; ++rb) {
-    const int u0 = int((long long)units * rb / row_blocks), u1 = int((long long)units * (rb + 1) / row_blocks);
+    int u0, u1, owner;
+    rows_block_units(per_seg, blk0, seg, nseg, units, row_blocks, rb, &u0, &u1, &owner);
+    if (u1 - u0 > widest) widest = u1 - u0;
     int slots = 0;
     for (int wh = 0; wh < ppu; ++wh) {
       const void* prev = nullptr;
@@ -580,15 +715,39 @@ int rows_max_slots(const SegDev* seg, int nseg, bool silu, int units, int row_bl
     }
     if (slots > worst) worst = slots;
   }
+  if (most_units) *most_units = widest;
   return worst;
+}
+
+// Per-segment folds: `blocks` row blocks dealt to the segments in proportion to their units
+// (at least one each, never more than a segment has units). Returns the blocks dealt.
+int rows_deal_blocks(const SegDev* seg, int nseg, int units, int blocks, int* blk0) {
+  int nb[kMaxSeg], us[kMaxSeg], dealt = 0;
+  for (int i = 0; i < nseg; ++i) {
+    us[i] = (i + 1 < nseg ? 4 * seg[i + 1].tile_begin : units) - 4 * seg[i].tile_begin;
+    nb[i] = 1;
+    ++dealt;
+  }
+  while (dealt < blocks) {
+    int best = -1;
+    for (int i = 0; i < nseg; ++i)
+      if (nb[i] < us[i] && (best < 0 || (long long)us[i] * nb[best] > (long long)us[best] * nb[i])) best = i;
+    if (best < 0) break;
+    ++nb[best];
+    ++dealt;
+  }
+  blk0[0] = 0;
+  for (int i = 0; i < nseg; ++i) blk0[i + 1] = blk0[i] + nb[i];
+  return dealt;
 }
 
 // Decide whether the row-range kernel serves this launch and lay it out. Returns false when the
 // tile x split kernel has to run (other code widths, a second stream, M > 8, a K range whose
 // activation rows do not fit in shared memory).
 bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, int K, int sms,
-               uint32_t fht_bytes, RowsGeom* g) {
+               uint32_t fht_bytes, int per_seg, RowsGeom* g) {
   if (M < 1 || M > 8) return false;
+  if (per_seg && silu) return false;    // a (gate, up) pair is one unit and has one input
   for (int i = 0; i < nseg; ++i)
     if (seg[i].bits != 4 || seg[i].packed2 != nullptr || seg[i].gs < kUnitRows) return false;
   const int ppu = silu ? 2 : 1;
@@ -600,7 +759,21 @@ bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, i
   const int upb_max = cap_planes / ppu;
   if (upb_max < 1) return false;
   int split = 1, row_blocks, slots;
-  if (U > sms) {
+  g->per_seg = per_seg;
+  for (int i = 0; i <= kMaxSeg; ++i) g->blk0[i] = 0;
+  int widest = 0;
+  if (per_seg) {
+    // blocks never cross a segment: one block per SM dealt over the segments (or the next
+    // multiple that fits the palette slots and the fold buffer), one unit per block at most
+    row_blocks = 0;
+    slots = 0;
+    for (int k = 1; !row_blocks; ++k) {
+      const int want = k * sms < U ? k * sms : U;
+      const int got = rows_deal_blocks(seg, nseg, U, want, g->blk0);
+      const int sl = rows_max_slots(seg, nseg, silu, U, got, 1, g->blk0, &widest);
+      if ((widest <= upb_max && sl <= kRowsMaxSlots) || want == U) { row_blocks = got; slots = sl; }
+    }
+  } else if (U > sms) {
     // One block per SM, or the next multiple of that whose blocks fit the palette slots and
     // the fold buffer.
     row_blocks = 0;
@@ -632,14 +805,15 @@ bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, i
   g->ntables = slots > 2 ? 2 : 1;
   g->Mp = Mp;
   g->xreg = (G % split == 0 && G / split == kRowsWarps * kRowsRing) ? 1 : 0;
-  g->red_planes = ((U + row_blocks - 1) / row_blocks) * ppu;
+  if (!per_seg) widest = (U + row_blocks - 1) / row_blocks;
+  g->red_planes = widest * ppu;
   const int kc_max = (G + split - 1) / split;
   g->xs_abs = kRowsTableAbs + uint32_t(g->ntables) * kTableBytes;
   g->red_abs = g->xs_abs + uint32_t(Mp) * uint32_t(kc_max) * 128u;
   g->part_abs = g->red_abs + uint32_t(kRowsWarps) * uint32_t(g->red_planes) * uint32_t(Mp) * 128u;
   g->fht_abs = g->part_abs + (split > 1 ? uint32_t(g->red_planes) * uint32_t(Mp) * 128u : 0u);
   g->meta_abs = g->fht_abs + ((fht_bytes + 15u) & ~15u);
-  g->end_abs = g->meta_abs + uint32_t((U + row_blocks - 1) / row_blocks) * uint32_t(sizeof(RowsUnitMeta));
+  g->end_abs = g->meta_abs + uint32_t(widest) * uint32_t(sizeof(RowsUnitMeta));
   return g->end_abs <= 227u * 1024u;
 }
 

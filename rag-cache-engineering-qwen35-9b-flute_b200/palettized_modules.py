@@ -316,6 +316,39 @@ class PalettizedLinear(nn.Module):
                 and bin(self.K).count("1") <= 8
                 and os.environ.get("FLUTE_NO_FHT_FUSE", "").strip() not in ("1", "true", "True"))
 
+    def _rows_kernel_shape(self, M: int, dtype) -> bool:
+        """What the row-range decode kernel serves (and with it every input transform)."""
+        return (not self.reference and 0 < M <= 8 and self.bitwidth == 4 and not self.has_stream2
+                and self.group_size >= 32 and dtype == self.lut.dtype
+                and self.lut.dtype in (torch.float16, torch.bfloat16))
+
+    def _fold(self, device):
+        """(rot_signs, awq_scale) of this module's input fold on `device`, (None, None) if unrotated."""
+        if self.rot_signs is None:
+            return None, None
+        awq = None
+        if self.awq_scale is not None and self.fold_order == "rotate_then_awq":
+            awq = self._on("awq", self.awq_scale, device)
+        return self._on("signs", self.rot_signs, device), awq
+
+    def forward_gated(self, g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
+        """self(silu(g) * u) for 2-D g, u of one shape: at decode the product (and this module's
+        rotation) runs in the prologue of the projection launch; otherwise one elementwise pass
+        over g and the ordinary forward."""
+        M = g.shape[0]
+        strided = (g.stride(1) == 1 and u.stride(1) == 1 and g.stride(0) == u.stride(0) and g.stride(0) % 8 == 0)
+        if (g.dtype == u.dtype and strided and self._rows_kernel_shape(M, g.dtype)
+                and not self.has_residual() and g.data_ptr() % 16 == 0 and u.data_ptr() % 16 == 0
+                and (self.rot_signs is None or self._rotation_fuses(M, g.dtype))):
+            out = torch.empty(M, self.N, dtype=g.dtype, device=g.device)
+            signs, awq = self._fold(g.device)
+            inp = _lib.make_input(x_mul=u, rot_signs=signs, awq_scale=awq)
+            _lib.gemv_input(g, _lib.make_segments([self._segment_desc(out)]), 1, inp, flags=_flags())
+            return out
+        g = g.contiguous()
+        _lib.silu_mul(g, u)
+        return self(g)
+
     def _input_transform(self, device):
         signs = self._on("signs", self.rot_signs, device)
         awq = None
@@ -425,17 +458,38 @@ class PalettizedLinear(nn.Module):
         return out.reshape(*shape[:-1], self.N)
 
 
-def _mergeable(mods, x: torch.Tensor) -> bool:
-    """Decode-merge verdict: M <= 16, same K, one dtype, unrotated or one shared rotation,
-    and every low-rank residual of a kind the GEMV epilogue serves."""
+def _per_segment_folds(mods, M: int) -> bool:
+    """The projections carry different folds, yet one launch can serve them: each block of the
+    row-range kernel rotates the shared rows with the fold of the segment it works on (the
+    reference's merged kernels carry a fold per segment the same way,
+    src/flute_extended/src/kernel_gemv_multi.cu:101-334)."""
+    dt = mods[0].lut.dtype
+    for m in mods:
+        if not m._rows_kernel_shape(M, dt):
+            return False
+        if m.rot_signs is not None and not m._rotation_fuses(M, dt):
+            return False
+    return True
+
+
+def _mergeable(mods, x: torch.Tensor, per_segment: bool = False) -> bool:
+    """Decode-merge verdict: M <= 16, same K, one dtype, unrotated or one shared rotation (or,
+    with per_segment, folds the launch can apply per segment), and every low-rank residual of
+    a kind the GEMV epilogue serves."""
     x2 = x.reshape(-1, x.shape[-1])
     if x2.shape[0] > GEMV_MAX_M or x2.shape[0] == 0 or not x.is_cuda:
         return False
     m0 = mods[0]
+    if not all(isinstance(m, PalettizedLinear) for m in mods):
+        return False
+    one_fold = all(_same_rotation(m0, m) for m in mods)
+    if not one_fold and not (per_segment and all(m.K == m0.K and m.lut.dtype == m0.lut.dtype for m in mods)
+                             and _per_segment_folds(mods, x2.shape[0])):
+        return False
     for m in mods:
         if not isinstance(m, PalettizedLinear) or m.reference or m.K != m0.K:
             return False
-        if m.lut.dtype != m0.lut.dtype or not _same_rotation(m0, m):
+        if m.lut.dtype != m0.lut.dtype:
             return False
         if m.lut.dtype not in (torch.float16, torch.bfloat16):
             return False
@@ -493,9 +547,8 @@ def _prefill_merged(mods, x: torch.Tensor, outs) -> None:
 
 def _same_rotation(a: "PalettizedLinear", b: "PalettizedLinear") -> bool:
     """Both unrotated, or both rotated by the same fold (seed, length, order, AWQ scale): a
-    merged launch rotates the shared input row once. (The reference's merged kernels carry a
-    per-segment FHT prologue and so also merge different folds; here the rotation is a
-    launch of its own and only a shared fold can be merged.)"""
+    merged launch rotates the shared input row once. Different folds merge only where the
+    launch itself can rotate per segment (_per_segment_folds)."""
     if a.rot_signs is None or b.rot_signs is None:
         return a.rot_signs is None and b.rot_signs is None
     if (a.rotation_seed, a.rotation_k, a.fold_order) != (b.rotation_seed, b.rotation_k, b.fold_order):
@@ -525,6 +578,44 @@ def _stacked_residual(owner: nn.Module, mods, x2: torch.Tensor):
     return out
 
 
+def _merged_decode(owner: nn.Module, mods, x: torch.Tensor, epilogue: int = None) -> torch.Tensor:
+    """One decode launch for projections that share x (their outputs side by side in one
+    [M, sum N] buffer; under the SiLU*mul epilogue only the gate's). One shared fold runs as a
+    transform launch in front — or inside the launch where the row-range kernel serves it;
+    different folds always run inside the launch, one per segment."""
+    epi = _lib.EPI_NONE if epilogue is None else epilogue
+    cd = mods[0].lut.dtype
+    x2 = x.reshape(-1, x.shape[-1])
+    M = x2.shape[0]
+    m0 = mods[0]
+    one_fold = all(_same_rotation(m0, m) for m in mods)
+    inp = None
+    if not one_fold:
+        inp = _lib.make_input(seg_folds=[m._fold(x.device) for m in mods])
+    elif m0.rot_signs is not None:
+        if all(m._rows_kernel_shape(M, cd) and m._rotation_fuses(M, x2.dtype) for m in mods):
+            inp = m0._input_transform(x.device)
+        else:
+            x2 = m0._rotate_input(x2)
+    x2 = x2.to(cd).contiguous()
+    silu = epi == _lib.EPI_SILU_MUL
+    total = mods[0].N if silu else sum(m.N for m in mods)
+    out = torch.empty(M, total, dtype=cd, device=x.device)
+    res = _stacked_residual(owner, mods, x2) if inp is None or not one_fold else {}
+    descs, off = [], 0
+    for i, m in enumerate(mods):
+        dst = None if (silu and i % 2) else out[:, off:]
+        descs.append(m._segment_desc(dst, ldo=total, res_t=res.get(id(m))))
+        if dst is not None:
+            off += m.N
+    segs = _lib.make_segments(descs)
+    if inp is not None:
+        _lib.gemv_input(x2, segs, len(descs), inp, epilogue=epi, flags=_flags())
+    else:
+        _lib.gemv_multi(x2, segs, len(descs), epilogue=epi, flags=_flags())
+    return out
+
+
 class SplitQKV(nn.Module):
     """q/k/v projections sharing one input: one merged decode launch when
     M <= 16, else the three modules (reference palettized_modules.py:1390-1466)."""
@@ -543,22 +634,10 @@ class SplitQKV(nn.Module):
             _prefill_merged(mods, x, [out[:, o:] for o in offs])
             return out.to(x.dtype).reshape(*x.shape[:-1], total)
         if os.environ.get("FLUTE_NO_MERGE", "").strip() in ("1", "true", "True") \
-                or not _mergeable(mods, x):
+                or not _mergeable(mods, x, per_segment=True):
             return torch.cat([m(x) for m in mods], dim=-1)
-        cd = mods[0].lut.dtype
-        x2 = x.reshape(-1, x.shape[-1])
-        if mods[0].rot_signs is not None:          # one shared fold (see _same_rotation)
-            x2 = mods[0]._rotate_input(x2)
-        x2 = x2.to(cd).contiguous()
-        total = sum(m.N for m in mods)
-        out = torch.empty(x2.shape[0], total, dtype=cd, device=x.device)
-        res = _stacked_residual(self, mods, x2)
-        descs, off = [], 0
-        for m in mods:
-            descs.append(m._segment_desc(out[:, off:], ldo=total, res_t=res.get(id(m))))
-            off += m.N
-        _lib.gemv_multi(x2, _lib.make_segments(descs), len(descs), flags=_flags())
-        return out.to(x.dtype).reshape(*x.shape[:-1], total)
+        out = _merged_decode(self, mods, x)
+        return out.to(x.dtype).reshape(*x.shape[:-1], out.shape[1])
 
 
 class FusedPalettizedMLP(nn.Module):
@@ -575,6 +654,7 @@ class FusedPalettizedMLP(nn.Module):
         return isinstance(self.act_fn, nn.SiLU) or self.act_fn in (torch.nn.functional.silu,)
 
     def fused_gate_up(self, x2: torch.Tensor) -> torch.Tensor:
+        """silu(gate(x2)) * up(x2) for rows already in the projections' basis, one launch."""
         g, u = self.gate_proj, self.up_proj
         out = torch.empty(x2.shape[0], g.N, dtype=x2.dtype, device=x2.device)
         res = _stacked_residual(self, (g, u), x2)
@@ -588,8 +668,16 @@ class FusedPalettizedMLP(nn.Module):
 
     def forward(self, x):
         mods = (self.gate_proj, self.up_proj)
-        fusable = (self._is_silu() and _mergeable(mods, x) and mods[0].N == mods[1].N
-                   and os.environ.get("FLUTE_NO_MERGE", "").strip() not in ("1", "true", "True"))
+        merge = (self._is_silu() and mods[0].N == mods[1].N
+                 and os.environ.get("FLUTE_NO_MERGE", "").strip() not in ("1", "true", "True"))
+        fusable = merge and _mergeable(mods, x)
+        if not fusable and merge and _mergeable(mods, x, per_segment=True):
+            # gate and up carry different folds: one launch rotates the shared rows per segment
+            # and leaves g | u side by side; SiLU*mul then runs in the prologue of the down launch
+            gu = _merged_decode(self, mods, x)
+            n = mods[0].N
+            y = self.down_proj.forward_gated(gu[:, :n], gu[:, n:])
+            return y.to(x.dtype).reshape(*x.shape[:-1], self.down_proj.N)
         if not fusable:
             if self._is_silu() and mods[0].N == mods[1].N and _prefill_mergeable(mods, x):
                 # prefill: gate and up as one tensor-core launch, one SiLU*mul pass, down
@@ -608,12 +696,7 @@ class FusedPalettizedMLP(nn.Module):
                 _lib.silu_mul(g.view(-1, g.shape[-1]), u.view(-1, u.shape[-1]))
                 return self.down_proj(g)
             return self.down_proj(self.act_fn(g) * u)
-        cd = mods[0].lut.dtype
-        x2 = x.reshape(-1, x.shape[-1])
-        if mods[0].rot_signs is not None:          # one shared fold (see _same_rotation)
-            x2 = mods[0]._rotate_input(x2)
-        x2 = x2.to(cd).contiguous()
-        y = self.fused_gate_up(x2).to(x.dtype)
+        y = _merged_decode(self, mods, x, epilogue=_lib.EPI_SILU_MUL).to(x.dtype)
         return self.down_proj(y).reshape(*x.shape[:-1], self.down_proj.N)
 
 

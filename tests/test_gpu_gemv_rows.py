@@ -173,3 +173,66 @@ def test_gated_input_inside_the_launch():
         L.gemv_input(torch.zeros(1, 256, dtype=dt, device="cuda"), L.make_segments([three._segment_desc(o)]), 1,
                      L.make_input(x_mul=torch.zeros(1, 256, dtype=dt, device="cuda")))
     assert e.value.code == 2
+
+
+# ---- a fold per segment ----------------------------------------------------------------------------
+@pytest.mark.parametrize("Ns,K,M,dtype", (
+    ((512, 256, 256), 4096, 1, torch.bfloat16),          # fewer units than SMs: one block per unit
+    ((4096, 1024, 1024), 4096, 4, torch.float16),        # 192 units: the blocks are dealt to the segments
+    ((2048, 4096, 512, 128), 12288, 2, torch.bfloat16),  # K = 8192 + 4096 values per fold
+    ((256, 128), 192, 8, torch.bfloat16),                # K = 128 + 64: the butterfly in shared memory
+))
+def test_merged_launch_with_a_fold_per_segment(Ns, K, M, dtype):
+    """Projections that share x but carry different folds run as ONE launch: every block
+    rotates the rows with the fold of its segment (reference: the per-segment rotation of the
+    merged kernels, src/flute_extended/src/kernel_gemv_multi.cu:101-334). Each segment's outputs
+    equal those of its own launch behind its own transform, bit for bit when K is not split."""
+    cases = []
+    for i, n in enumerate(Ns):
+        kind = i % 3          # rotated, rotated + AWQ scale, unrotated
+        cases.append(Case(n, K, 128, 4, dtype, seed=300 + i + K, bias=bool(i & 1),
+                          rotation_seed=None if kind == 2 else 11 + i, awq=kind == 1))
+    mods = [c.module() for c in cases]
+    x = cases[0].x(M).cuda()
+    total = sum(Ns)
+    out = torch.full((M, total), float("nan"), dtype=dtype, device="cuda")
+    descs, off = [], 0
+    for m in mods:
+        m._ensure_packed()
+        descs.append(m._segment_desc(out[:, off:], ldo=total))
+        off += m.N
+    inp = L.make_input(seg_folds=[m._fold(x.device) for m in mods])
+    L.gemv_input(x, L.make_segments(descs), len(descs), inp)
+    torch.cuda.synchronize()
+    assert L.lib().b200lut_device_status() == 0
+    off = 0
+    for c, m in zip(cases, mods):
+        got = out[:, off:off + c.N]
+        off += c.N
+        assert rel_err(got, c.oracle(x.cpu())) <= TOL
+        if K == 4096:
+            assert torch.equal(got, m(x))
+    # the SiLU*mul epilogue shares one input between gate and up: refused with per-segment folds
+    with pytest.raises(L.LibraryError):
+        L.gemv_input(x, L.make_segments(descs[:2]), 2, inp, epilogue=L.EPI_SILU_MUL)
+
+
+def test_module_layer_merges_projections_with_different_folds():
+    K, M, dt = 4096, 1, torch.bfloat16
+    q, k, v = (Case(n, K, 128, 4, dt, seed=400 + i, rotation_seed=21 + i, awq=i == 1)
+               for i, n in enumerate((1024, 256, 256)))
+    x = q.x(M)
+    qkv = pkg.SplitQKV(q.module(), k.module(), v.module())
+    assert pkg.palettized_modules._mergeable((qkv.q_proj, qkv.k_proj, qkv.v_proj), x.cuda(), per_segment=True)
+    assert not pkg.palettized_modules._mergeable((qkv.q_proj, qkv.k_proj, qkv.v_proj), x.cuda())
+    got = qkv(x.cuda())
+    want = torch.cat([c.oracle(x) for c in (q, k, v)], dim=-1)
+    assert rel_err(got, want) <= TOL
+    gate, up, down = (Case(n, kk, 128, 4, dt, seed=410 + i, rotation_seed=31 + i)
+                      for i, (n, kk) in enumerate(((1024, K), (1024, K), (K, 1024))))
+    mlp = pkg.FusedPalettizedMLP(gate.module(), up.module(), down.module(), torch.nn.SiLU())
+    got = mlp(x.cuda())
+    act = (torch.nn.functional.silu(gate.oracle(x).float()) * up.oracle(x).float()).to(dt)
+    assert rel_err(got, down.oracle(act)) <= 2 * TOL
+    torch.cuda.synchronize()
+    assert L.lib().b200lut_device_status() == 0

@@ -86,6 +86,14 @@ def test_validation_errors_carry_a_message():
     assert rc == 2 and b"M=17" in L.b200lut_last_error()
     rc = L.b200lut_residual_project(x, 64, 1, 64, 0, None, 8, x, 8, 0, None)
     assert rc == 1 and b"null" in L.b200lut_last_error()
+    inp = pkg._lib.Input()
+    inp.per_segment, inp.rot_signs = 1, x                   # a launch-wide fold next to per-segment ones
+    rc = L.b200lut_gemv_input(x, 64, 1, 64, 0, ctypes.byref(seg), 1, 0, 0, None, 0, 0, None, ctypes.byref(inp), None)
+    assert rc == 1 and b"per-segment folds" in L.b200lut_last_error()
+    inp.rot_signs = None
+    inp.seg_awq_scale[0] = x                                 # a scale without signs
+    rc = L.b200lut_gemv_input(x, 64, 1, 64, 0, ctypes.byref(seg), 1, 0, 0, None, 0, 0, None, ctypes.byref(inp), None)
+    assert rc == 1 and b"segment 0" in L.b200lut_last_error()
     rc = L.b200lut_gemm_multi(x, 64, 32, 128, 0, ctypes.byref(seg), 5, 0, None, 0, None)
     assert rc == 2 and b"nseg" in L.b200lut_last_error()
     rc = L.b200lut_gemm_multi(x, 64, 32, 64, 0, ctypes.byref(seg), 1, 0, None, 0, None)
