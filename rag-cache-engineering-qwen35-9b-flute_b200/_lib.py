@@ -562,7 +562,7 @@ def gemm_multi_ok(descs: Sequence[dict], K: int) -> bool:
     if not 1 <= len(descs) <= GEMM_MULTI_MAX or K < 128:
         return False
     d0 = descs[0]
-    return all(d.get("packed2") is None and d.get("resA") is None and d["bits"] == d0["bits"]
+    return all(d.get("packed2") is None and d["bits"] == d0["bits"]
                and d["group_size"] == d0["group_size"] and d["group_size"] >= 64 for d in descs)
 
 

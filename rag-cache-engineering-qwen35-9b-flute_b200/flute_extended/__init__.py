@@ -323,12 +323,44 @@ def _check_table(A, seg_table, count, what):
         raise ValueError(f"{what}: A must be a contiguous [1, K] tensor")
 
 
+def _table_segments(rows, members, x, K, dev, dt, out_override, keep):
+    """b200lut_segment array of the table rows `members`; residual projections run on `x`."""
+    segs = (_lib.Segment * len(members))()
+    for sg, i in zip(segs, members):
+        r = rows[i]
+        N, b1, b2, gs = r["N"], r["b1"], r["b2"], r["gs"]
+        if N <= 0 or N % 128 or not r["q1"] or not r["lut1"]:
+            raise ValueError(f"seg_table row {i}: N must be a positive multiple of 128 and q1 / lut1 non-zero")
+        sg.packed = _slab_of(r["q1"], N, K, b1, dev).data_ptr()
+        sg.lut = r["lut1"]
+        if r["q2"]:
+            sg.packed2 = _slab_of(r["q2"], N, K, b2, dev).data_ptr()
+            sg.lut2, sg.bits2 = r["lut2"], b2
+        sg.bias = r["bias"] or None
+        out = r["C"]
+        if out_override is not None:
+            out = out_override.get(i, 0)
+        sg.out = out or None
+        sg.ldo, sg.N, sg.group_size, sg.n_groups, sg.bits = N, N, gs, -(-N // gs), b1
+        if r["R"]:
+            R = r["R"]
+            resB = _view(r["resB"], R * K * 2, dev).view(dt).view(R, K)
+            t = _lib.residual_project(x, resB, flags=_flags())
+            keep.append(t)
+            sg.resA, sg.res_t, sg.res_rank, sg.res_ldt = r["resA"], t.data_ptr(), R, t.stride(0)
+    return segs
+
+
 def _table_launch(A, seg_table, epilogue, out_override=None):
     """Run the segments of a [count, 15] address table. Segments that share one fold (signs, s) —
-    or carry none — run as ONE launch on the (rotated) row; different folds give one launch per
-    fold, each behind its own transform (the reference rotates per segment inside one launch)."""
+    or carry none — run as ONE launch on the (rotated) row. Different folds also run as one
+    launch where the row-range kernel can rotate per segment (4-bit single-stream segments,
+    group size >= 32, no low-rank residual, K of at most 8 power-of-two pieces), as the
+    reference does; otherwise one launch per fold, each behind its own transform. Under the
+    SiLU*mul epilogue gate and up share one input, so different folds there give one launch
+    that leaves gate and up side by side and one SiLU*mul pass (two roundings more than the
+    reference's fused kernel)."""
     dev, K, dt = A.device, A.shape[1], A.dtype
-    esize = 2
     rows = [dict(zip(_COLS, (int(v) for v in r))) for r in seg_table.tolist()]
     rotated = [r["signs"] != 0 for r in rows]
     if any(rotated) and not all(rotated):
@@ -336,41 +368,39 @@ def _table_launch(A, seg_table, epilogue, out_override=None):
     folds = {}
     for i, r in enumerate(rows):
         folds.setdefault((r["signs"], r["s"]), []).append(i)
+    keep = []
+    override = None if out_override is None else {0: out_override}
+
+    def fold_tensors(signs_ptr, s_ptr):
+        signs = _view(signs_ptr, 4 * K, dev).view(torch.float32) if signs_ptr else None
+        scale = _view(s_ptr, 4 * K, dev).view(torch.float32) if s_ptr else None
+        return signs, scale
+
+    per_segment = (len(folds) > 1 and bin(K).count("1") <= 8
+                   and all(r["b1"] == 4 and not r["q2"] and r["gs"] >= 32 and not r["R"] for r in rows))
+    if per_segment:
+        members = list(range(len(rows)))
+        silu = epilogue == _lib.EPI_SILU_MUL
+        up = None
+        if silu:     # gate lands in C, up beside it, then C <- silu(C) * up
+            up = torch.empty(1, rows[1]["N"], dtype=dt, device=dev)
+            override = {0: out_override, 1: up.data_ptr()}
+        segs = _table_segments(rows, members, A, K, dev, dt, override, keep)
+        inp = _lib.make_input(seg_folds=[fold_tensors(r["signs"], r["s"]) for r in rows])
+        _lib.gemv_input(A, segs, len(members), inp, flags=_flags())
+        if silu:
+            gate = _view(out_override, 2 * rows[0]["N"], dev).view(dt).view(1, rows[0]["N"])
+            _lib.silu_mul(gate, up)
+        return
     if epilogue == _lib.EPI_SILU_MUL and len(folds) > 1:
-        # gate and up with different folds: two plain launches, then the SiLU*mul pass
-        raise ValueError("qgemm_gemv_mlp: gate and up must share one rotation fold in this library")
+        raise ValueError("qgemm_gemv_mlp: gate and up with different rotation folds are served for 4-bit "
+                         "single-stream segments without a low-rank residual only")
     for (signs_ptr, s_ptr), members in folds.items():
         x = A
         if signs_ptr:
-            signs = _view(signs_ptr, 4 * K, dev).view(torch.float32)
-            if s_ptr:
-                x = _lib.fht(A, signs, mode=_lib.FHT_AWQ, scale=_view(s_ptr, 4 * K, dev).view(torch.float32))
-            else:
-                x = _lib.fht(A, signs)
-        segs = (_lib.Segment * len(members))()
-        keep = []
-        for sg, i in zip(segs, members):
-            r = rows[i]
-            N, b1, b2, gs = r["N"], r["b1"], r["b2"], r["gs"]
-            if N <= 0 or N % 128 or not r["q1"] or not r["lut1"]:
-                raise ValueError(f"seg_table row {i}: N must be a positive multiple of 128 and q1 / lut1 non-zero")
-            sg.packed = _slab_of(r["q1"], N, K, b1, dev).data_ptr()
-            sg.lut = r["lut1"]
-            if r["q2"]:
-                sg.packed2 = _slab_of(r["q2"], N, K, b2, dev).data_ptr()
-                sg.lut2, sg.bits2 = r["lut2"], b2
-            sg.bias = r["bias"] or None
-            out = r["C"]
-            if out_override is not None:
-                out = out_override if i == 0 else 0
-            sg.out = out or None
-            sg.ldo, sg.N, sg.group_size, sg.n_groups, sg.bits = N, N, gs, -(-N // gs), b1
-            if r["R"]:
-                R = r["R"]
-                resB = _view(r["resB"], R * K * esize, dev).view(dt).view(R, K)
-                t = _lib.residual_project(x, resB, flags=_flags())
-                keep.append(t)
-                sg.resA, sg.res_t, sg.res_rank, sg.res_ldt = r["resA"], t.data_ptr(), R, t.stride(0)
+            signs, scale = fold_tensors(signs_ptr, s_ptr)
+            x = _lib.fht(A, signs, mode=_lib.FHT_AWQ, scale=scale) if scale is not None else _lib.fht(A, signs)
+        segs = _table_segments(rows, members, x, K, dev, dt, override, keep)
         _lib.gemv_multi(x, segs, len(members), epilogue=epilogue, flags=_flags())
 
 

@@ -163,3 +163,36 @@ def test_multi_and_mlp_tables():
     assert fx.qgemm_gemv_mlp(x, t, C) is C
     want = orc.silu_mul_fused(x.cpu().float() @ g.w1.t(), x.cpu().float() @ u.w1.t(), dt)
     assert rel_err(C, want) <= TOL
+
+
+@gpu
+def test_tables_whose_segments_carry_different_folds():
+    K, dt = 4096, torch.bfloat16
+    cases = [Case(n, K, 128, 4, dt, seed=40 + i, rotation_seed=7 + i, awq=i == 1) for i, n in enumerate((512, 256, 128))]
+    x = cases[0].x(1).cuda()
+    out = torch.full((1, sum(c.N for c in cases)), float("nan"), dtype=dt, device="cuda")
+    keep, rows, off = [], [], 0
+    for c in cases:
+        d = dict(q1=c.blob.cuda(), lut1=c.lut.cuda(), signs=c.signs.cuda())
+        if c.awq is not None:
+            d["s"] = c.awq.cuda()
+        keep.append(d)
+        r = {k: v.data_ptr() for k, v in d.items()}
+        r.update(C=out.data_ptr() + 2 * off, N=c.N, b1=4, gs=128)
+        rows.append(r)
+        off += c.N
+    fx.qgemm_gemv_multi(x, _table(rows))
+    torch.cuda.synchronize()
+    off = 0
+    for c in cases:
+        assert rel_err(out[:, off:off + c.N], c.oracle(x.cpu())) <= TOL, c.N
+        off += c.N
+    # gate and up with different folds, then SiLU*mul
+    g, u = cases[1], Case(256, K, 128, 4, dt, seed=50, rotation_seed=19)
+    dg, du = keep[1], dict(q1=u.blob.cuda(), lut1=u.lut.cuda(), signs=u.signs.cuda())
+    C = torch.empty(1, 256, dtype=dt, device="cuda")
+    t = _table([dict({k: v.data_ptr() for k, v in dg.items()}, N=256, b1=4, gs=128),
+                dict({k: v.data_ptr() for k, v in du.items()}, N=256, b1=4, gs=128)])
+    assert fx.qgemm_gemv_mlp(x, t, C) is C
+    want = orc.silu_mul_fused(g.oracle(x.cpu()).float(), u.oracle(x.cpu()).float(), dt)
+    assert rel_err(C, want) <= 2 * TOL
