@@ -433,7 +433,9 @@ __device__ __forceinline__ int persist_first_tile(const PersistParams& p, long l
   return int(r * p.m_tiles + j);
 }
 
-template <typename T, int BITS>
+// RES: the launch carries low-rank residual k-blocks (a separate instantiation, so that launches
+// without a residual run exactly the loop they ran before it existed).
+template <typename T, int BITS, bool RES>
 __global__ void __launch_bounds__(kPThreads, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
                           const __grid_constant__ CUtensorMap tmap, const PersistParams p) {
@@ -463,7 +465,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
   // tiles of a cost-balanced contiguous range. Split mode: first the block's k-range of a cut
   // tile (if it has one), then `full` whole tiles.
   const int G = p.G;           // k-blocks of codes
-  const int Gx = p.G + p.E;    // k-blocks of a tile, the residual's included
+  const int Gx = RES ? p.G + p.E : p.G;    // k-blocks of a tile, the residual's included
   const int bid = int(blockIdx.x);
   int t0, ntile, has_cut = 0, cut_tile = 0, cut_c0 = 0, cut_c1 = 0, cut_part = 0;
   if (p.split) {
@@ -545,7 +547,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
 #pragma unroll
       for (int i = 0; i < 2 * BITS; ++i) w[u][i] = 0u;
       const bool on = ld.s < nseg;
-      const bool codes = on && ld.c < G;      // a residual k-block has no codes to fetch
+      const bool codes = on && (!RES || ld.c < G);      // a residual k-block has no codes to fetch
       load_slab_pair<BITS>(w[u], codes ? code_ptr(ld) : p.seg[0].packed, q, codes ? 1u : 0u);
       if (on) advance(ld);
     }
@@ -578,8 +580,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
             tc::mbar_wait(bar_done + 8 * stage, uint32_t(i / kPStages - 1) & 1u, abort_flag,
                           &g_gemm_status, tc::kStatusWaitEmpty, p.wait_cycles);
           tc::fence_after_sync();
-          const bool residual = use.c >= G;
-          if (residual) {
+          const bool residual = RES && use.c >= G;
+          if (RES && residual) {
             // 64 columns of the tile's resA rows as they are. Register 4 kt + i of the store is
             // 32-bit column 8 kt + 2 (lane & 3) + (i & 1) of row (lane >> 2) + 8 (i >> 1): four
             // consecutive 16-bit values of each of the lane's two rows per 16-column block.
@@ -624,7 +626,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
           }
           {
             const bool on = ld.s < nseg;
-            const bool codes = on && ld.c < G;
+            const bool codes = on && (!RES || ld.c < G);
             load_slab_pair<BITS>(w[u], codes ? code_ptr(ld) : p.seg[0].packed, q, codes ? 1u : 0u);
             if (on) advance(ld);
           }
@@ -641,7 +643,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
     for (int sg = 0; sg < nseg; ++sg) {
       const int m0 = (seg_tile(sg) % p.m_tiles) * p.NT;
       const int c_hi = seg_c1(sg);
-      const int tcol = p.E ? segment_of_row(p, seg_tile(sg) / p.m_tiles).t_col0 - G * kChunkK : 0;
+      const int tcol = RES ? segment_of_row(p, seg_tile(sg) / p.m_tiles).t_col0 - G * kChunkK : 0;
       for (int c = seg_c0(sg); c < c_hi; ++c, ++i) {
         const int xs = i % kPStages;
         if (i >= kPStages)
@@ -649,7 +651,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
                         &g_gemm_status, tc::kStatusWaitEmpty, p.wait_cycles);
         if (lane == 0 && !*abort_flag) {
           tc::mbar_expect_tx(bar_full + 8 * xs, stage_bytes);
-          if (c < G) tma_load_2d(xstage(xs), &xmap, bar_full + 8 * xs, c * kChunkK, m0);
+          if (!RES || c < G) tma_load_2d(xstage(xs), &xmap, bar_full + 8 * xs, c * kChunkK, m0);
           else tma_load_2d(xstage(xs), &tmap, bar_full + 8 * xs, tcol + c * kChunkK, m0);
         }
         __syncwarp();
@@ -909,10 +911,10 @@ SplitPlan plan_split(long long tiles, int G, int sms) {
   return sp;
 }
 
-template <typename T, int BITS>
+template <typename T, int BITS, bool RES>
 int launch_persistent(const CUtensorMap& map, const CUtensorMap& tmap, const PersistParams& p,
                       int grid, bool pdl, cudaStream_t stream) {
-  auto kern = gemm_tc_persistent_kernel<T, BITS>;
+  auto kern = gemm_tc_persistent_kernel<T, BITS, RES>;
   static bool configured[64] = {false};
   int dev = 0;
   B200LUT_CUDA_OK(cudaGetDevice(&dev));
@@ -1058,10 +1060,11 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
     pp.ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kTicketBytes);
     grid = sms;
   }
-#define B200LUT_PERSIST(B)                                                                      \
-  (dtype == B200LUT_BF16                                                                          \
-       ? launch_persistent<__nv_bfloat16, B>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream))    \
-       : launch_persistent<__half, B>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)))
+#define B200LUT_PERSIST_AS(B, RES)                                                                 \
+  (dtype == B200LUT_BF16                                                                            \
+       ? launch_persistent<__nv_bfloat16, B, RES>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)) \
+       : launch_persistent<__half, B, RES>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)))
+#define B200LUT_PERSIST(B) (extra ? B200LUT_PERSIST_AS(B, true) : B200LUT_PERSIST_AS(B, false))
   switch (s.bits) {
     case 4: return B200LUT_PERSIST(4);
     case 3: return B200LUT_PERSIST(3);
@@ -1069,6 +1072,7 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
     default: return B200LUT_PERSIST(1);
   }
 #undef B200LUT_PERSIST
+#undef B200LUT_PERSIST_AS
 }
 
 // the checks every projection of a prefill GEMM passes, whichever kernel serves it
