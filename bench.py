@@ -36,10 +36,11 @@ PKG = "rag-cache-engineering-qwen35-9b-flute_b200"
 METRIC = "9B linear-stack decode tok/s (LUT-GEMV, M=1 unless --batch)"
 FALLBACK_HBM_GBS = 6650.0
 DECODE_KERNEL = "gemv_rows_kernel"
-TRAFFIC_RATIO = 1.0003
+TRAFFIC_RATIO = 1.0026
 TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one gemv_rows_kernel launch over a "
-                  "248320 x 4096 4-bit projection (508.7 MB for 508.6 MB of algorithmic bytes), ratio scaled "
-                  "to the average launch of the step")
+                  "12288 x 4096 4-bit projection (25.267 MB for 25.202 MB of algorithmic bytes; the "
+                  "lm_head-sized launch reads 508.75 MB for 509.13 MB), ratio scaled to the average "
+                  "launch of the step")
 WORKLOAD = ("qwen3.5-9b linear stack: 32 layers, 248 projections, 6912212992 4-bit weights, "
             "group 128, bf16 palettes")
 
@@ -789,6 +790,7 @@ def run_extras(pkg, st, stack, peaks, flags):
 def run_case(args) -> int:
     """A few eager launches of one kernel on a profiling-sized case. gemv: 12288 x 4096
     4-bit projection at M = 1 over 8 distinct weight sets (192 MB of codes, larger than L2);
+    gemv_head: one 248320 x 4096 projection (the kernel's steady state);
     gemm: M = 2048, K = 4096, N = 12288; embed: 2048 rows of an lm_head-sized table."""
     import torch
     torch.cuda.set_device(0)
@@ -798,6 +800,10 @@ def run_case(args) -> int:
         gbs, us = single_projection_gbs(pkg, args.batch, 12288, 4096, 8, max(args.steps, 1), 0)
         print(json.dumps({"case": "gemv 12288x4096 M=%d, 8 weight sets" % args.batch, "GB/s": gbs,
                           "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}))
+    elif args.case == "gemv_head":
+        gbs, us = single_projection_gbs(pkg, args.batch, 248320, 4096, 1, max(args.steps, 1), 0)
+        print(json.dumps({"case": "gemv 248320x4096 (lm_head size, 0.51 GB of codes) M=%d" % args.batch,
+                          "GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}))
     elif args.case == "kgrouped":
         gbs, us = kgrouped_projection_gbs(pkg, args.batch, 4096, 4096, 16, max(args.steps, 1))
         print(json.dumps({"case": "K-grouped gemv 4096x4096 M=%d, 16 weight sets" % args.batch, "GB/s": gbs,
@@ -828,9 +834,9 @@ def main() -> int:
                     help="N > 1: how the sharded MLP activation is recombined (push: peer stores "
                          "from the GEMV epilogue; nccl: an all-gather call between the launches)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
-    ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemm", "embed", "kgrouped"),
-                    help="stack: the benchmark; gemv / gemm / embed / kgrouped: a few launches of one "
-                         "kernel on a profiling-sized case")
+    ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemv_head", "gemm", "embed", "kgrouped"),
+                    help="stack: the benchmark; gemv / gemv_head / gemm / embed / kgrouped: a few launches "
+                         "of one kernel on a profiling-sized case")
     ap.add_argument("--executor", default="graph", choices=("plan", "graph"),
                     help="plan: persistent cooperative launch(es) per step; graph: one kernel per "
                          "projection group under CUDA-graph replay")
@@ -947,10 +953,13 @@ def main() -> int:
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD,
                    "batch": M,
-                   "parallelism": f"column-parallel x{world}, all-gather per layer" + (
+                   "parallelism": f"column-parallel x{world}, all-gather of the MLP activation per layer" + (
                        "" if world == 1 else
                        " folded into the GEMV launches (peer stores over NVLink + flag wait)" if push
-                       else " (NCCL)"),
+                       else " (NCCL)") + (
+                       "" if world == 1 else
+                       "; the other sharded outputs (heads, out, down) have no full-K consumer in the "
+                       "stack and stay sharded, so the result read back is this rank's 1/N of y"),
                    "l2": "inputs (3.46 GB of codes per step) exceed the 126 MB L2",
                    "launch": ("persistent cooperative launch per step (jobs chained by completion counters), "
                               "CUDA graph replay" if use_plan else
