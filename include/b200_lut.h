@@ -248,7 +248,13 @@ typedef struct b200lut_exchange {
   int producer_blocks;    /* blocks of the pushing launch (b200lut_gemv_launch_blocks for split = 0,
                              tiles x split for an explicit split); the same on every rank;
                              push: checked against the launch; wait: flags per rank */
-  int reserved;
+  int wait_ms;            /* wait: bound of the flag wait in milliseconds, 1..1000; 0 = the default
+                             (about one second). When it runs out the launch carries on with
+                             whatever its activation buffer holds, b200lut_device_status()
+                             returns 0x7000 + the rank whose flag was missing, and every later
+                             wait on the device returns at once until that call has cleared the
+                             word: outputs are undefined from the first expiry until the host
+                             has read the status and re-zeroed the exchange words. */
   int64_t peer_delta[B200LUT_MAX_PEERS];  /* bytes from a local output address to the same
                                              element of rank q's buffer (entry `rank` unused) */
   void* peer_flag[B200LUT_MAX_PEERS];     /* rank q's flag array u32[world][producer_blocks]

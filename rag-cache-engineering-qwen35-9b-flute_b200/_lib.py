@@ -67,7 +67,7 @@ class Exchange(ctypes.Structure):
     _fields_ = [
         ("world", ctypes.c_int), ("rank", ctypes.c_int),
         ("push", ctypes.c_int), ("wait", ctypes.c_int),
-        ("producer_blocks", ctypes.c_int), ("reserved", ctypes.c_int),
+        ("producer_blocks", ctypes.c_int), ("wait_ms", ctypes.c_int),
         ("peer_delta", ctypes.c_int64 * MAX_PEERS), ("peer_flag", ctypes.c_void_p * MAX_PEERS),
         ("ticket", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("flags", ctypes.c_void_p),
         ("wait_ticket", ctypes.c_void_p), ("wait_count", ctypes.c_void_p),

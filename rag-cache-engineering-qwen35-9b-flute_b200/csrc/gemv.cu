@@ -77,6 +77,7 @@ struct ExchangeDev {
   uint32_t* wait_ticket;
   uint32_t* wait_count;
   int* status;          // device status word of the library (set when a wait runs out)
+  long long wait_cycles;   // bound of the flag wait in SM clock cycles
 };
 
 struct GemvParams {
@@ -199,7 +200,7 @@ __device__ __forceinline__ void peer_poll(const ExchangeDev& ex, int idx) {
     if (arrived()) return;
     if ((i & 15u) == 0u) {
       if (*reinterpret_cast<volatile int*>(ex.status) != 0) return;
-      if (clock64() - t0 > kPeerWaitCycles) break;
+      if (clock64() - t0 > ex.wait_cycles) break;
     }
   }
   atomicExch(ex.status, 0x7000 + idx / ex.blocks);
@@ -1017,6 +1018,9 @@ int convert_exchange(const b200lut_exchange* ex, ExchangeDev* out) {
     out->wait_ticket = static_cast<uint32_t*>(ex->wait_ticket);
     out->wait_count = static_cast<uint32_t*>(ex->wait_count);
     out->wait = 1;
+    B200LUT_REQUIRE(ex->wait_ms >= 0 && ex->wait_ms <= 1000, B200LUT_ERR_INVALID,
+                    "exchange: wait_ms must be 0 (default) or 1..1000, got %d", ex->wait_ms);
+    out->wait_cycles = ex->wait_ms ? (long long)ex->wait_ms * 2000000ll : kPeerWaitCycles;
   }
   int rc = B200LUT_OK;
   out->status = b200lut::device_status_addr(&rc);

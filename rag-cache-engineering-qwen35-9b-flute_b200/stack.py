@@ -309,6 +309,16 @@ class LinearStack(nn.Module):
             self.run_launch(entry, M, flags, gather)
         return plan["y"]
 
+    def check_status(self) -> None:
+        """Call after a host sync (it reads a device word): raises when a bounded wait ran out in
+        any kernel since the last call — a peer's push that never came (0x7000 + rank), a
+        tensor-core pipeline wait, an embedding id out of range. From the first expiry until this
+        call the step's outputs are undefined; after an exchange expiry re-zero the arenas
+        (every rank) before the next step."""
+        status = _lib.lib().b200lut_device_status()
+        if status != 0:
+            raise RuntimeError(f"LinearStack: a bounded device wait ran out (device status {status:#x})")
+
     def decode_plans(self, M: int):
         """Persistent-launch form of the step (M <= 16): the launches between two
         all-gathers become one plan each (a single plan on one GPU). Inside a plan every

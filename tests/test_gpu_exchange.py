@@ -119,3 +119,46 @@ def test_two_gpu_push_equals_nccl_gather():
     ok = mp.get_context("spawn").Array("i", [0] * world)
     mp.spawn(_two_gpu_worker, args=(world, 29531, ok), nprocs=world, join=True)
     assert list(ok) == [1] * world
+
+
+def test_a_wait_that_runs_out_returns_reports_the_rank_and_the_channel_recovers():
+    """Nothing pushes, so the consumer's flag wait runs out at its (here 1 ms) bound: the launch
+    still returns, the device status names the rank whose flag was missing, later waits do not
+    block, and after the host has read the status and re-zeroed the exchange words a complete
+    push / wait round gives the plain result."""
+    from helpers import Case
+    L = pkg._lib
+    dt, M, world = torch.bfloat16, 1, 2
+    arenas = exchange.PeerArena.emulated(1 << 16, world, "cuda")
+    prods = [Case(128, 256, 128, 4, dt, seed=90 + r) for r in range(world)]
+    cons = Case(128, 256, 128, 4, dt, seed=95)
+    pmods = [c.module() for c in prods]
+    cmod = cons.module()
+    for m in pmods + [cmod]:
+        m._ensure_packed()
+    x = prods[0].x(M).cuda()
+    blocks = L.gemv_launch_blocks(M, 256, L.make_segments([pmods[0]._segment_desc(None)]), 1)
+    chans = [exchange.Channel(arenas[r], M, 256, dt, blocks) for r in range(world)]
+    out = torch.zeros(M, cons.N, dtype=dt, device="cuda")
+    csegs = L.make_segments([cmod._segment_desc(out)])
+
+    chans[0].wait.wait_ms = 1
+    L.gemv_exchange(chans[0].act, csegs, 1, chans[0].wait)      # no producer has run
+    L.gemv_exchange(chans[0].act, csegs, 1, chans[0].wait)      # the status is sticky: returns at once
+    torch.cuda.synchronize()
+    status = L.lib().b200lut_device_status()
+    assert status in (0x7000, 0x7001), hex(status)              # 0x7000 + a rank whose flag was missing
+    assert L.lib().b200lut_device_status() == 0                 # reading it cleared it
+
+    for a in arenas:                                            # recovery: counters and flags back to zero
+        a.buf.zero_()
+    for rep in range(2):
+        for r in range(world):
+            dst = chans[r].act[:, r * 128:(r + 1) * 128]
+            L.gemv_exchange(x, L.make_segments([pmods[r]._segment_desc(dst, ldo=256)]), 1, chans[r].push)
+        L.gemv_exchange(chans[0].act, csegs, 1, chans[0].wait)
+        torch.cuda.synchronize()
+        assert L.lib().b200lut_device_status() == 0
+        act = torch.cat([m(x) for m in pmods], dim=1)
+        assert torch.equal(chans[0].act, act) and torch.equal(chans[1].act, act)
+        assert torch.equal(out, cmod(act))
