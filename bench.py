@@ -539,6 +539,39 @@ def kgrouped_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int, 
                                  "cos": orc.cosine(got.float(), want.float())}
 
 
+def kgrouped_gemm_tflops(pkg, M: int, N: int, K: int, iters: int):
+    """Extra: the K-grouped palette variant at prefill width on the tensor cores
+    (b200lut_gemm_kgrouped); returns (TFLOP/s, us, gate on 128 sampled weight rows x 64 tokens)."""
+    import numpy as np
+    import torch
+    from oracle import lut_linear_oracle as orc
+    L = pkg._lib
+    bits, dt = 4, torch.bfloat16
+    packed = L.repack_from_idxn(pkg.synthetic.random_blob_on_device(N, K, bits, 970, "cuda"), N, K, bits)
+    lut_k = (0.02 * torch.randn(K // 128, N, 16, device="cuda",
+                                generator=torch.Generator("cuda").manual_seed(970))).sort(dim=-1).values.to(dt)
+    x = torch.randn(M, K, device="cuda").to(dt)
+    out = torch.empty(M, N, dtype=dt, device="cuda")
+
+    def run():
+        L.gemm_kgrouped(x, packed, lut_k, N, bits, out=out)
+    for _ in range(3):
+        run()
+    us = time_steps(run, iters, 1) * 1e3 / iters
+    if L.lib().b200lut_device_status() != 0:
+        raise RuntimeError("a bounded wait ran out inside the K-grouped GEMM")
+    rows = torch.arange(0, N, N // 128)[:128]
+    codes = L.unpack_codes(packed, N, K, bits)[rows.cuda()].cpu().numpy().astype(np.int64)
+    pal = lut_k[:, rows.cuda()].cpu().float()
+    w = torch.empty(len(rows), K)
+    for j in range(len(rows)):
+        w[j] = pal[:, j].gather(1, torch.from_numpy(codes[j]).view(K // 128, 128)).reshape(K)
+    want = (x[:64].cpu().float() @ w.t()).to(dt)
+    got = out[:64][:, rows.cuda()].cpu()
+    return 2.0 * M * N * K / us / 1e6, us, {"rel_max": orc.max_rel_err(got.float(), want.float()),
+                                            "cos": orc.cosine(got.float(), want.float())}
+
+
 def embedding_gather_gbs(pkg, N: int, K: int, n_ids: int, iters: int, gate: bool = False):
     """Extra: the embedding gather over an lm_head-sized 4-bit table (0.51 GB of codes, far
     beyond L2), `n_ids` random rows per launch; returns (GB/s of algorithmic bytes, us).
@@ -721,6 +754,9 @@ def run_extras(pkg, st, stack, peaks, flags):
         gbs, us, g = kgrouped_projection_gbs(pkg, 1, 4096, 4096, 16, 20, gate=True)
         put("gemv_kgrouped_4096x4096_m1", {"GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / hbm,
                                             "bytes_per_launch": 12599296}, g)
+        tf, us, g = kgrouped_gemm_tflops(pkg, 2048, 12288, 4096, 20)
+        put("prefill_gemm_kgrouped_m2048_k4096_n12288", {"TFLOP/s": tf, "us": us,
+                                                          "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}, g)
         gbs, us, g = embedding_gather_gbs(pkg, 248320, 4096, 2048, 20, gate=True)
         put("embedding_gather_248320x4096_2048_ids", {"GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / hbm}, g)
 

@@ -424,6 +424,17 @@ int b200lut_gemv_kgrouped(const void* x, int64_t ldx, int M, int K, int dtype,
                           int N, int bits, void* out, int64_t ldo, int split,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same projection at any M on the tensor cores (the prefill form): the persistent tcgen05
+ * kernel of b200lut_gemm with a lookup that reads every weight out of its row's palette — the
+ * palettes of a lookup warp's 32 rows travel with the codes through a shared-memory ring. fp32
+ * sums, one rounding. workspace: optional scratch of the split schedule, as b200lut_gemm_ws takes
+ * it (b200lut_gemm_workspace_bytes(M, N, K) bytes, zero-filled once); NULL runs whole tiles.
+ * flags bit 0: programmatic dependent launch. */
+int b200lut_gemm_kgrouped(const void* x, int64_t ldx, int M, int K, int dtype,
+                          const void* packed, const void* lut_k, const void* bias, int N,
+                          int bits, void* out, int64_t ldo, int flags, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
 /* ---- embedding gather ----------------------------------------------------------------------
  *
  * out[t, :] = W[ids[t], :] for n_ids int64 ids on the device, W the palettized [N, K] table

@@ -32,7 +32,7 @@ EXPORTS = (
     "b200lut_residual_project", "b200lut_residual_project_rows", "b200lut_silu_mul", "b200lut_gemm_workspace_bytes", "b200lut_gemm_ws", "b200lut_gemm_multi",
     "b200lut_gemm_two_stream", "b200lut_gemm_two_stream_bytes",
     "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_kgrouped",
-    "b200lut_gemv_kgrouped_split", "b200lut_gemv_kgrouped_workspace_bytes", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
+    "b200lut_gemv_kgrouped_split", "b200lut_gemv_kgrouped_workspace_bytes", "b200lut_gemm_kgrouped", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
     "b200lut_gemv_noalloc", "b200lut_gemv_noalloc_reset", "b200lut_gemv_launch_blocks", "b200lut_gemv_input", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
 )
 
@@ -133,6 +133,8 @@ def lib() -> ctypes.CDLL:
     L.b200lut_gemv_kgrouped_workspace_bytes.argtypes = [i32, i32, i32]
     L.b200lut_gemv_kgrouped.restype = i32
     L.b200lut_gemv_kgrouped.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, i32, i32, vp, i64, i32, vp, sz, vp]
+    L.b200lut_gemm_kgrouped.restype = i32
+    L.b200lut_gemm_kgrouped.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, i32, i32, vp, i64, i32, vp, sz, vp]
     L.b200lut_gemm_two_stream_bytes.restype = sz
     L.b200lut_gemm_two_stream_bytes.argtypes = [i32, i32]
     L.b200lut_gemm_two_stream.restype = i32
@@ -531,6 +533,25 @@ def gemv_kgrouped(x: torch.Tensor, packed: torch.Tensor, lut_k: torch.Tensor, N:
         check(lib().b200lut_gemv_kgrouped(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype),
                                           packed.data_ptr(), lut_k.data_ptr(), ptr(bias), N, bits,
                                           out.data_ptr(), out.stride(0), split, ptr(ws),
+                                          ws.numel() if ws is not None else 0, _stream(x)))
+    return out
+
+
+def gemm_kgrouped(x: torch.Tensor, packed: torch.Tensor, lut_k: torch.Tensor, N: int, bits: int,
+                  bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                  flags: int = 0, split: bool = True) -> torch.Tensor:
+    """Tensor-core GEMM with K-grouped palettes, any M: x [M, K], codes in the slab layout,
+    lut_k [K / 128, N, 2**bits] in x's dtype -> [M, N] (split=False: whole-tile schedule)."""
+    _need_cuda(x, "x")
+    M, K = x.shape
+    if out is None:
+        out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        need = lib().b200lut_gemm_workspace_bytes(M, N, K) if split else 0
+        ws = _gemm_workspace(x.device, int(_stream(x) or 0), need) if need else None
+        check(lib().b200lut_gemm_kgrouped(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype),
+                                          packed.data_ptr(), lut_k.data_ptr(), ptr(bias), N, bits,
+                                          out.data_ptr(), out.stride(0), flags, ptr(ws),
                                           ws.numel() if ws is not None else 0, _stream(x)))
     return out
 

@@ -357,6 +357,7 @@ struct PersistParams {
   // are; their activation operand is the matching 64-column block of t = x @ resB^T, fetched
   // through the second tensor map. The sums, the bias and the single rounding are the tile's.
   int E;
+  int kg_N;                // K-grouped palettes: output rows of the projection (rows of lut_k per k-group)
   // Two code streams of different widths: the first launch leaves its fp32 sums in acc_out
   // ([token][row], ld_acc floats per token) instead of rounding them, the second adds acc_in to
   // its own sums before bias and the single rounding.
@@ -433,12 +434,44 @@ __device__ __forceinline__ int persist_first_tile(const PersistParams& p, long l
   return int(r * p.m_tiles + j);
 }
 
-// RES: the launch carries low-rank residual k-blocks (a separate instantiation, so that launches
-// without a residual run exactly the loop they ran before it existed).
-template <typename T, int BITS, bool RES>
+// MODE (separate instantiations, so that a plain launch runs exactly the loop it always ran):
+//   kModePlain     palettes shared by groups of output rows, looked up through the pair table;
+//   kModeResidual  the same, and every tile ends with low-rank residual k-blocks;
+//   kModeKGrouped  one palette per (128 input columns, output row): `lut` of the one segment is
+//                  lut_k [K / 128][N][2^BITS]. A pair table per palette cannot pay off for 128
+//                  weights, so a lookup warp keeps the palettes of its 32 rows for the k-blocks
+//                  it has in flight in a private shared-memory ring (cp.async, requested together
+//                  with the codes) and reads every weight with one 16-bit load; the rest of the
+//                  pipeline does not know the difference.
+constexpr int kModePlain = 0, kModeResidual = 1, kModeKGrouped = 2;
+
+// The 2 * BITS bits of field i (0..15) of local slab sl (0, 1): two codes, the lower one first.
+template <int BITS>
+__device__ __forceinline__ uint32_t slab_field(const uint32_t (&w)[2 * BITS], int sl, int i) {
+  constexpr uint32_t kMask = (1u << (2 * BITS)) - 1u;
+  const int pos = 32 * BITS * sl + 2 * BITS * i, m = pos >> 5, sh = pos & 31;
+  if (sh + 2 * BITS > 32) return __funnelshift_r(w[m], w[(m + 1) % (2 * BITS)], sh) & kMask;
+  return (w[m] >> sh) & kMask;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+
+template <typename T, int BITS, int MODE>
 __global__ void __launch_bounds__(kPThreads, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
                           const __grid_constant__ CUtensorMap tmap, const PersistParams p) {
+  constexpr bool RES = MODE == kModeResidual, KG = MODE == kModeKGrouped;
   extern __shared__ __align__(16) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t base = smem_u32(smem);
@@ -541,6 +574,21 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
     advance(ld);
     enter(use, grp - 2);
     advance(use);
+    // K-grouped: the palettes of this warp's 32 rows for k-block `cu` go to slot u of the warp's
+    // ring (where the pair tables of the other modes live); one commit group per slot and
+    // iteration, issued or not, so that the group count tells which slot has landed.
+    constexpr int kPal = 1 << BITS;
+    constexpr uint32_t kPalSlot = 1024;          // 32 rows x 16 entries x 2 bytes at 4 bits
+    const uint32_t pal_ring = tbl_addr + uint32_t(warp) * (kRing * kPalSlot);
+    auto load_palette = [&](int u, const Cursor& cu, bool on) {
+      if (on) {
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.seg[0].lut) +
+                             ((size_t(cu.c >> 1) * p.kg_N + size_t(cu.row) * kTileRows + 32 * q) * kPal) * 2;
+        for (int i = lane; i < 4 * kPal; i += 32)      // 64 * kPal bytes in 16-byte pieces
+          cp_async16(pal_ring + uint32_t(u) * kPalSlot + uint32_t(i) * 16u, src + size_t(i) * 16);
+      }
+      cp_async_commit();
+    };
     uint32_t w[kRing][2 * BITS];
 #pragma unroll
     for (int u = 0; u < kRing; ++u) {
@@ -549,6 +597,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
       const bool on = ld.s < nseg;
       const bool codes = on && (!RES || ld.c < G);      // a residual k-block has no codes to fetch
       load_slab_pair<BITS>(w[u], codes ? code_ptr(ld) : p.seg[0].packed, q, codes ? 1u : 0u);
+      if (KG) load_palette(u, ld, on);
       if (on) advance(ld);
     }
     int table_row = -1, table_seg = -1;
@@ -557,7 +606,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
 #pragma unroll
       for (int u = 0; u < kRing; ++u) {
         if (it + 2 * u < iters) {     // warp-uniform
-          if (use.s != table_seg) {
+          if (!KG && use.s != table_seg) {
             // a new segment: all eight lookup warps pass here once per segment (block-uniform),
             // and rebuild the pair table together when the row tile has changed
             const int row = use.row;
@@ -606,9 +655,32 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
               tc::tmem_st_16x256b_x4(tmem + (uint32_t(32 * q + 16 * sl) << 16) + kPACol + 32u * stage, r);
             }
           }
+          if (KG) {
+            cp_async_wait<kRing - 1>();      // the group of this slot (and every older one) has landed
+            __syncwarp();
+            const uint32_t slot = pal_ring + uint32_t(u) * kPalSlot;
+#pragma unroll
+            for (int sl = 0; sl < 2; ++sl) {
+              const uint32_t row_lo = slot + uint32_t(16 * sl + (lane >> 2)) * (2 * kPal);
+              const uint32_t row_hi = row_lo + 8u * (2 * kPal);
+              uint32_t r[16];
+#pragma unroll
+              for (int kt = 0; kt < 4; ++kt) {
+                uint32_t v[4];
+#pragma unroll
+                for (int f = 0; f < 4; ++f) {   // fields (g, k 0-1), (g+8, k 0-1), (g, k 2-3), (g+8, k 2-3)
+                  const uint32_t pair = slab_field<BITS>(w[u], sl, 4 * kt + f);
+                  const uint32_t rowb = (f & 1) ? row_hi : row_lo;
+                  v[f] = lds16(rowb + 2u * (pair & (kPal - 1))) | (lds16(rowb + 2u * (pair >> BITS)) << 16);
+                }
+                r[4 * kt + 0] = v[0]; r[4 * kt + 1] = v[2]; r[4 * kt + 2] = v[1]; r[4 * kt + 3] = v[3];
+              }
+              tc::tmem_st_16x256b_x4(tmem + (uint32_t(32 * q + 16 * sl) << 16) + kPACol + 32u * stage, r);
+            }
+          }
 #pragma unroll
           for (int sl = 0; sl < 2; ++sl) {
-            if (residual) continue;
+            if (residual || KG) continue;
             const int rowslab = 2 * q + sl;
             const int pal = nl == 1 ? 0 : (nl == 2 ? rowslab >> 2 : rowslab >> 1);
             const uint32_t tb = lane_base + uint32_t(pal >> 1) * kTableBytes + uint32_t(pal & 1) * 128u;
@@ -628,6 +700,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
             const bool on = ld.s < nseg;
             const bool codes = on && (!RES || ld.c < G);
             load_slab_pair<BITS>(w[u], codes ? code_ptr(ld) : p.seg[0].packed, q, codes ? 1u : 0u);
+            if (KG) load_palette(u, ld, on);
             if (on) advance(ld);
           }
           tc::wait_st();
@@ -911,10 +984,10 @@ SplitPlan plan_split(long long tiles, int G, int sms) {
   return sp;
 }
 
-template <typename T, int BITS, bool RES>
+template <typename T, int BITS, int MODE>
 int launch_persistent(const CUtensorMap& map, const CUtensorMap& tmap, const PersistParams& p,
                       int grid, bool pdl, cudaStream_t stream) {
-  auto kern = gemm_tc_persistent_kernel<T, BITS, RES>;
+  auto kern = gemm_tc_persistent_kernel<T, BITS, MODE>;
   static bool configured[64] = {false};
   int dev = 0;
   B200LUT_CUDA_OK(cudaGetDevice(&dev));
@@ -983,9 +1056,11 @@ namespace {
 int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b200lut_segment* segs,
                     int nseg, bool pdl, void* workspace, size_t workspace_bytes,
                     void* stream, float* acc_out = nullptr, const float* acc_in = nullptr,
-                    long long ld_acc = 0) {
+                    long long ld_acc = 0, int kg_rows = 0) {
   PersistParams pp = {};
   pp.acc_out = acc_out; pp.acc_in = acc_in; pp.ld_acc = ld_acc;
+  const bool kgrouped = kg_rows > 0;     // segs[0].lut is lut_k [K / 128][kg_rows][2^bits]
+  pp.kg_N = kg_rows;
   int rows = 0, extra = 0;
   const uint16_t* t_base = nullptr;
   long long t_ld = 0;
@@ -1060,11 +1135,13 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
     pp.ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kTicketBytes);
     grid = sms;
   }
-#define B200LUT_PERSIST_AS(B, RES)                                                                 \
-  (dtype == B200LUT_BF16                                                                            \
-       ? launch_persistent<__nv_bfloat16, B, RES>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)) \
-       : launch_persistent<__half, B, RES>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)))
-#define B200LUT_PERSIST(B) (extra ? B200LUT_PERSIST_AS(B, true) : B200LUT_PERSIST_AS(B, false))
+#define B200LUT_PERSIST_AS(B, MODE)                                                                 \
+  (dtype == B200LUT_BF16                                                                             \
+       ? launch_persistent<__nv_bfloat16, B, MODE>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)) \
+       : launch_persistent<__half, B, MODE>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)))
+#define B200LUT_PERSIST(B)                                                  \
+  (kgrouped ? B200LUT_PERSIST_AS(B, kModeKGrouped)                          \
+            : (extra ? B200LUT_PERSIST_AS(B, kModeResidual) : B200LUT_PERSIST_AS(B, kModePlain)))
   switch (s.bits) {
     case 4: return B200LUT_PERSIST(4);
     case 3: return B200LUT_PERSIST(3);
@@ -1140,6 +1217,36 @@ extern "C" int b200lut_gemm_multi(const void* x, int64_t ldx, int M, int K, int 
   }
   return persistent_gemm(x, ldx, M, K, dtype, segs, nseg, (flags & 1) != 0, workspace,
                          workspace_bytes, stream);
+}
+
+extern "C" int b200lut_gemm_kgrouped(const void* x, int64_t ldx, int M, int K, int dtype,
+                                     const void* packed, const void* lut_k, const void* bias, int N,
+                                     int bits, void* out, int64_t ldo, int flags, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+  B200LUT_REQUIRE(x && packed && lut_k && out, B200LUT_ERR_INVALID, "null x, codes, palettes or output");
+  B200LUT_REQUIRE(M >= 1, B200LUT_ERR_INVALID, "M must be >= 1, got %d", M);
+  B200LUT_REQUIRE(K >= 128 && K % 128 == 0, B200LUT_ERR_INVALID,
+                  "K must be a positive multiple of 128 (one palette per 128 input columns), got %d", K);
+  B200LUT_REQUIRE(N > 0 && N % kTileRows == 0 && ldo >= N, B200LUT_ERR_INVALID,
+                  "N must be a positive multiple of 128 and ldo >= N (N=%d)", N);
+  B200LUT_REQUIRE(bits >= 1 && bits <= 4, B200LUT_ERR_INVALID, "code width must be 1..4, got %d", bits);
+  B200LUT_REQUIRE(dtype == B200LUT_BF16 || dtype == B200LUT_F16, B200LUT_ERR_INVALID,
+                  "dtype must be B200LUT_BF16 or B200LUT_F16");
+  B200LUT_REQUIRE(aligned16(x) && aligned16(packed) && aligned16(lut_k) && ldx % 8 == 0 && ldx >= K,
+                  B200LUT_ERR_ALIGN,
+                  "x, codes and palettes must be 16-byte aligned, the x row stride a multiple of 8 and >= K");
+  b200lut_segment s = {};
+  s.packed = packed;
+  s.lut = lut_k;
+  s.bias = bias;
+  s.out = out;
+  s.ldo = ldo;
+  s.N = N;
+  s.group_size = kTileRows;     // not used by the K-grouped lookup
+  s.n_groups = N / kTileRows;
+  s.bits = bits;
+  return persistent_gemm(x, ldx, M, K, dtype, &s, 1, (flags & 1) != 0, workspace, workspace_bytes, stream,
+                         nullptr, nullptr, 0, N);
 }
 
 extern "C" size_t b200lut_gemm_two_stream_bytes(int M, int N) {

@@ -924,8 +924,8 @@ class KGroupedPalettizedLinear(nn.Module):
     The reference has no module of this form (its groups run along the output rows); in its
     terms this is K/128 PalettizedLinear(group_size=1, K=128) modules summed in fp32
     (src/scripts/palettized_modules.py:125-162). indices: the idxN blob of the [N, K] codes;
-    lut_k: [K // 128, N, 2**bitwidth] float16 / bfloat16. Decode kernel only: rows are served
-    16 at a time by b200lut_gemv_kgrouped (no tensor-core form)."""
+    lut_k: [K // 128, N, 2**bitwidth] float16 / bfloat16. Up to 16 rows run the decode kernel
+    (b200lut_gemv_kgrouped), more the tensor-core GEMM (b200lut_gemm_kgrouped)."""
 
     GROUP_K = 128
 
@@ -973,8 +973,11 @@ class KGroupedPalettizedLinear(nn.Module):
         M = x2.shape[0]
         out = torch.empty(M, self.N, dtype=cd, device=x.device)
         bias = None if self.bias is None else self.bias.data.to(cd)
-        for m0 in range(0, M, GEMV_MAX_M):
-            m1 = min(M, m0 + GEMV_MAX_M)
-            _lib.gemv_kgrouped(x2[m0:m1], self._packed, self.lut_k, self.N, self.bitwidth, bias=bias,
-                               out=out[m0:m1])
+        if M == 0:
+            return out.to(x.dtype).reshape(*x.shape[:-1], self.N)
+        if M <= GEMV_MAX_M:
+            _lib.gemv_kgrouped(x2, self._packed, self.lut_k, self.N, self.bitwidth, bias=bias, out=out)
+        else:
+            _lib.gemm_kgrouped(x2, self._packed, self.lut_k, self.N, self.bitwidth, bias=bias, out=out,
+                               flags=_flags())
         return out.to(x.dtype).reshape(*x.shape[:-1], self.N)

@@ -34,7 +34,11 @@ def _case(N, K, bits, dtype, seed, bias=False):
     (384, 1024, 3, torch.bfloat16, 8, False),
     (128, 512, 2, torch.float16, 16, True),
     (512, 256, 1, torch.bfloat16, 5, False),
-    (1024, 2048, 4, torch.bfloat16, 40, True),     # more than 16 rows: served 16 at a time
+    (1024, 2048, 4, torch.bfloat16, 40, True),     # more than 16 rows: the tensor-core form
+    (4096, 4096, 4, torch.bfloat16, 300, True),    # 64 tiles: cut in two along K over the idle SMs
+    (512, 1024, 3, torch.float16, 128, False),
+    (256, 256, 2, torch.bfloat16, 257, True),      # a second token tile of one row
+    (128, 128, 1, torch.float16, 17, False),       # one tile, two k-blocks, one palette block
 ))
 def test_outputs_match_the_oracle_composition(N, K, bits, dtype, M, bias):
     codes, lut_k, b, mod = _case(N, K, bits, dtype, N + K + M, bias)
@@ -53,6 +57,35 @@ def test_dequantised_weights_are_bit_exact(bits, dtype):
     codes, lut_k, _, mod = _case(N, K, bits, dtype, 10 + bits)
     W = mod(torch.eye(K, dtype=dtype, device="cuda")).cpu().t()      # [N, K]
     assert torch.equal(W.float(), orc.dequant_kgrouped(codes, lut_k, 128).float())
+
+
+@pytest.mark.parametrize("bits,dtype", ((4, torch.bfloat16), (3, torch.float16), (2, torch.bfloat16),
+                                        (1, torch.float16)))
+def test_weights_through_the_tensor_core_form_are_bit_exact(bits, dtype):
+    N, K = 384, 256
+    codes, lut_k, _, mod = _case(N, K, bits, dtype, 20 + bits)
+    mod._ensure_packed()
+    W = L.gemm_kgrouped(torch.eye(K, dtype=dtype, device="cuda"), mod._packed, mod.lut_k, N, bits).cpu().t()
+    assert torch.equal(W.float(), orc.dequant_kgrouped(codes, lut_k, 128).float())
+    torch.cuda.synchronize()
+    assert L.lib().b200lut_device_status() == 0
+
+
+def test_tensor_core_form_at_prefill_width_sampled():
+    # M = 2048, K = 4096, N = 4096: every token, 256 sampled weight rows; both schedules agree
+    N, K, M, dt = 4096, 4096, 2048, torch.bfloat16
+    codes, lut_k, _, mod = _case(N, K, 4, dt, 4242)
+    mod._ensure_packed()
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(5)).to(dt).cuda()
+    got = L.gemm_kgrouped(x, mod._packed, mod.lut_k, N, 4)
+    whole = L.gemm_kgrouped(x, mod._packed, mod.lut_k, N, 4, split=False)
+    rows = torch.cat([torch.arange(t * 128, t * 128 + 64) for t in (0, 11, 20, 31)])
+    w = orc.dequant_kgrouped(codes[rows.numpy()], lut_k[:, rows], 128)
+    want = orc.linear_forward(x.cpu(), w)
+    assert rel_err(got[:, rows.cuda()], want) <= TOL
+    assert rel_err(got, whole) <= 4e-3
+    torch.cuda.synchronize()
+    assert L.lib().b200lut_device_status() == 0
 
 
 def test_every_split_gives_the_same_sums_within_rounding():
