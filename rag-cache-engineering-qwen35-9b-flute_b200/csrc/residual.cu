@@ -117,50 +117,106 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
   }
 }
 
-template <typename T>
+// TILES: 8-wide column tiles a block computes (4 when R <= 32 — the deployed rank — else 8).
+// The kernel is a chain of memory round trips (activations from DRAM, residual rows from L2), so
+// a warp fetches UNROLL k steps at a time with cp.async into its own two-stage staging area — no
+// registers held while the loads fly — and multiplies one batch while the next one lands.
+__device__ __forceinline__ void rp_cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint4 rp_lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+template <int TILES> struct RowsProj {
+  static constexpr int kUnroll = TILES <= 4 ? 4 : 2;
+  static constexpr int kRows = 16 + 8 * TILES;                 // staged rows of one k step
+  static constexpr uint32_t kStepBytes = kRows * 64u;          // 32 k = 64 bytes per row
+  static constexpr uint32_t kStageBytes = kUnroll * kStepBytes;
+  static constexpr uint32_t kWarpBytes = 2u * kStageBytes;
+  static constexpr uint32_t kRedBytes = kRowsProjWarps * 16 * kRowsProjPitch * 4;
+  static constexpr uint32_t kSmem = kRowsProjWarps * kWarpBytes > kRedBytes ? kRowsProjWarps * kWarpBytes : kRedBytes;
+};
+
+template <typename T, int TILES>
 __global__ void __launch_bounds__(kRowsProjWarps * 32) residual_rows_kernel(
     const uint16_t* __restrict__ x, long long ldx, int M, int K, const uint16_t* __restrict__ resB,
     int R, uint16_t* __restrict__ t, long long ldt, int cols) {
-  __shared__ float red[kRowsProjWarps][16][kRowsProjPitch];
+  using P = RowsProj<TILES>;
+  extern __shared__ __align__(16) uint8_t rp_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
   const int m0 = blockIdx.x * 16, c0 = blockIdx.y * kRowsProjCols;
-  // residual rows of this column block that exist, in 8-wide tiles
-  int tiles = (R - c0 + 7) / 8;
-  tiles = tiles < 0 ? 0 : (tiles > 8 ? 8 : tiles);
   asm volatile("griddepcontrol.launch_dependents;");
 
-  float acc[8][4];
+  float acc[TILES][4];
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
+  for (int j = 0; j < TILES; ++j)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
-  const bool row_lo = m0 + g < M, row_hi = m0 + g + 8 < M;
-  const uint16_t* xlo = x + size_t(row_lo ? m0 + g : 0) * ldx + 8 * c;
-  const uint16_t* xhi = x + size_t(row_hi ? m0 + g + 8 : 0) * ldx + 8 * c;
-  const uint16_t* brow = resB + size_t(c0 + g) * K + 8 * c;
-  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint32_t mine = uint32_t(__cvta_generic_to_shared(rp_smem)) + uint32_t(warp) * P::kWarpBytes;
   const int steps = K / 32;
-#pragma unroll 2
-  for (int s = warp; s < steps; s += kRowsProjWarps) {
-    const int k0 = 32 * s;
-    const uint4 a = row_lo ? __ldcg(reinterpret_cast<const uint4*>(xlo + k0)) : zero;
-    const uint4 b = row_hi ? __ldcg(reinterpret_cast<const uint4*>(xhi + k0)) : zero;
-    uint4 w[8];
+  const int nb = (steps > warp ? (steps - warp + kRowsProjWarps - 1) / kRowsProjWarps : 0);   // this warp's steps
+  const int batches = (nb + P::kUnroll - 1) / P::kUnroll;
+  // Rows beyond M and residual rows beyond R are read from the last valid row instead (their
+  // products land in outputs that are never stored, or are stored as zero).
+  auto fetch = [&](int batch) {
+    const uint32_t st = mine + uint32_t(batch & 1) * P::kStageBytes;
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      w[j] = (j < tiles && c0 + 8 * j + g < R)
-                 ? __ldg(reinterpret_cast<const uint4*>(brow + size_t(8 * j) * K + k0)) : zero;
+    for (int u = 0; u < P::kUnroll; ++u) {
+      const int i = batch * P::kUnroll + u;
+      if (i < nb) {      // warp-uniform
+        const int k0 = 32 * (warp + i * kRowsProjWarps);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (j < tiles) {   // block-uniform
-        mma16816<T>(acc[j], a.x, b.x, a.y, b.y, w[j].x, w[j].y);
-        mma16816<T>(acc[j], a.z, b.z, a.w, b.w, w[j].z, w[j].w);
+        for (int pc = lane; pc < P::kRows * 4; pc += 32) {
+          const int row = pc >> 2, part = pc & 3;
+          const uint16_t* src;
+          if (row < 16) {
+            int m = m0 + row;
+            m = m < M ? m : M - 1;
+            src = x + size_t(m) * ldx + k0 + 8 * part;
+          } else {
+            int r = c0 + row - 16;
+            r = r < R ? r : R - 1;
+            src = resB + size_t(r) * K + k0 + 8 * part;
+          }
+          rp_cp_async16(st + uint32_t(u) * P::kStepBytes + uint32_t(row) * 64u + uint32_t(part) * 16u, src);
+        }
       }
     }
-  }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (batches > 0) fetch(0);
+  for (int bt = 0; bt < batches; ++bt) {
+    if (bt + 1 < batches) {
+      fetch(bt + 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncwarp();
+    const uint32_t st = mine + uint32_t(bt & 1) * P::kStageBytes;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+    for (int u = 0; u < P::kUnroll; ++u) {
+      if (bt * P::kUnroll + u < nb) {      // warp-uniform
+        const uint32_t sb = st + uint32_t(u) * P::kStepBytes + uint32_t(c) * 16u;
+        const uint4 a = rp_lds128(sb + uint32_t(g) * 64u), b = rp_lds128(sb + uint32_t(g + 8) * 64u);
+#pragma unroll
+        for (int j = 0; j < TILES; ++j) {
+          const uint4 w = rp_lds128(sb + uint32_t(16 + 8 * j + g) * 64u);
+          mma16816<T>(acc[j], a.x, b.x, a.y, b.y, w.x, w.y);
+          mma16816<T>(acc[j], a.z, b.z, a.w, b.w, w.z, w.w);
+        }
+      }
+    }
+    __syncwarp();      // the stage is refilled two batches on
+  }
+  __syncthreads();     // the staging areas are done with: the fold buffer takes their place
+  float (*red)[16][kRowsProjPitch] = reinterpret_cast<float (*)[16][kRowsProjPitch]>(rp_smem);
+#pragma unroll
+  for (int j = 0; j < TILES; ++j) {
     red[warp][g][8 * j + 2 * c] = acc[j][0];
     red[warp][g][8 * j + 2 * c + 1] = acc[j][1];
     red[warp][g + 8][8 * j + 2 * c] = acc[j][2];
@@ -171,8 +227,10 @@ __global__ void __launch_bounds__(kRowsProjWarps * 32) residual_rows_kernel(
     const int r = idx / kRowsProjCols, col = idx % kRowsProjCols;
     if (m0 + r < M && c0 + col < cols) {
       float v = 0.f;
+      if (col < 8 * TILES && c0 + col < R) {
 #pragma unroll
-      for (int w2 = 0; w2 < kRowsProjWarps; ++w2) v += red[w2][r][col];
+        for (int w2 = 0; w2 < kRowsProjWarps; ++w2) v += red[w2][r][col];
+      }
       t[size_t(m0 + r) * ldt + c0 + col] = DType<T>::from_float(v);
     }
   }
@@ -254,11 +312,21 @@ extern "C" int b200lut_residual_project_rows(const void* x, int64_t ldx, int M, 
   const uint16_t* bp = static_cast<const uint16_t*>(resB);
   uint16_t* tp = static_cast<uint16_t*>(t);
   const long long ldx_ = ldx, ldt_ = ldt;
+  const bool narrow = R <= 32;     // four 8-wide column tiles hold every residual row
+  cfg.dynamicSmemBytes = narrow ? RowsProj<4>::kSmem : RowsProj<8>::kSmem;
+  auto go = [&](auto kern, int which) -> int {
+    static bool configured[4][64] = {};     // the four instantiations share this lambda's type
+    int dev = 0;
+    B200LUT_CUDA_OK(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[which][dev]) {
+      B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           int(cfg.dynamicSmemBytes)));
+      if (dev < 64) configured[which][dev] = true;
+    }
+    B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, xp, ldx_, M, K, bp, R, tp, ldt_, cols));
+    return B200LUT_OK;
+  };
   if (dtype == B200LUT_BF16)
-    B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, residual_rows_kernel<__nv_bfloat16>, xp, ldx_, M, K, bp,
-                                       R, tp, ldt_, cols));
-  else
-    B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, residual_rows_kernel<__half>, xp, ldx_, M, K, bp, R,
-                                       tp, ldt_, cols));
-  return B200LUT_OK;
+    return narrow ? go(residual_rows_kernel<__nv_bfloat16, 4>, 0) : go(residual_rows_kernel<__nv_bfloat16, 8>, 1);
+  return narrow ? go(residual_rows_kernel<__half, 4>, 2) : go(residual_rows_kernel<__half, 8>, 3);
 }
