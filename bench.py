@@ -426,7 +426,7 @@ def single_projection_gbs(pkg, M: int, N: int, K: int, sets: int, iters: int, fl
 
 
 def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool, gate: bool = False,
-                        rank: int = 0):
+                        rank: int = 0, flags: int = 0):
     """Extra: the M=2048 prefill GEMM (optionally behind the 128-point block Hadamard of the
     activations, or with a rank-`rank` residual: its projection launch and the extra k-block,
     timed together), CUDA events, inputs 16 MB + 24 MB + 48 MB out per call. The FLOP count is
@@ -454,9 +454,9 @@ def prefill_gemm_tflops(pkg, M: int, N: int, K: int, iters: int, rotate: bool, g
             L.residual_project_rows(x, resB, out=t)
         if rotate:
             L.fht(x, None, block=128, out=xr)
-            L.gemm(xr, seg)
+            L.gemm(xr, seg, flags=flags)
         else:
-            L.gemm(x, seg)
+            L.gemm(x, seg, flags=flags)
     for _ in range(3):
         run()
     ms = time_steps(run, iters, 1)
@@ -849,9 +849,11 @@ def run_case(args) -> int:
         print(json.dumps({"case": "embedding gather, 2048 rows of a 248320 x 4096 4-bit table",
                           "GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}))
     else:
-        tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, max(args.steps, 1), False)
-        print(json.dumps({"case": "gemm M=2048 K=4096 N=12288", "TFLOP/s": tf, "us": us,
-                          "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}))
+        pairs = args.case == "gemm_pairs"
+        tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, max(args.steps, 1), False,
+                                     flags=pkg._lib.FLAG_CTA_PAIRS if pairs else 0)
+        print(json.dumps({"case": "gemm M=2048 K=4096 N=12288" + (", CTA pairs (cta_group::2)" if pairs else ""),
+                          "TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}))
     return 0
 
 
@@ -870,9 +872,9 @@ def main() -> int:
                     help="N > 1: how the sharded MLP activation is recombined (push: peer stores "
                          "from the GEMV epilogue; nccl: an all-gather call between the launches)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
-    ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemv_head", "gemm", "embed", "kgrouped"),
-                    help="stack: the benchmark; gemv / gemv_head / gemm / embed / kgrouped: a few launches "
-                         "of one kernel on a profiling-sized case")
+    ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemv_head", "gemm", "gemm_pairs", "embed", "kgrouped"),
+                    help="stack: the benchmark; gemv / gemv_head / gemm / gemm_pairs / embed / kgrouped: a few "
+                         "launches of one kernel on a profiling-sized case")
     ap.add_argument("--executor", default="graph", choices=("plan", "graph"),
                     help="plan: persistent cooperative launch(es) per step; graph: one kernel per "
                          "projection group under CUDA-graph replay")

@@ -43,10 +43,15 @@ enum {
                                     on the previous kernel of the stream (code prefetch, palette
                                     fetch, table build) runs before the launch waits for it */
   B200LUT_FLAG_TILE_KERNEL = 2,  /* decode GEMV: run the tile x K-split kernel */
-  B200LUT_FLAG_ROWS_KERNEL = 4   /* decode GEMV: run the row-range kernel where it serves the shapes
+  B200LUT_FLAG_ROWS_KERNEL = 4,  /* decode GEMV: run the row-range kernel where it serves the shapes
                                     (4-bit codes, one stream, M <= 8, split = 0, no exchange). It
                                     is the library's choice for those shapes anyway, unless the
                                     process runs with B200LUT_GEMV_KERNEL=tile */
+  B200LUT_FLAG_CTA_PAIRS = 8     /* prefill GEMM: run launches of M >= 256 rows with an even number of
+                                    128-row tiles as pairs of CTAs (tcgen05 cta_group::2: one MMA
+                                    covers 256 weight rows, each CTA fetches half of the activation
+                                    tile; no multicast load). Same results bit for bit, measured
+                                    slower than one CTA per tile, so it is never the default */
 };
 
 /* Epilogue selector of b200lut_gemv_multi / b200lut_gemm. */

@@ -23,6 +23,7 @@ FHT_FORWARD, FHT_ADJOINT, FHT_AWQ = 0, 1, 2
 FLAG_PDL = 1
 FLAG_TILE_KERNEL = 2     # decode GEMV: force the tile x K-split kernel
 FLAG_ROWS_KERNEL = 4     # decode GEMV: the row-range kernel where it serves the shapes
+FLAG_CTA_PAIRS = 8       # prefill GEMM: CTA pairs (tcgen05 cta_group::2); slower, never the default
 
 EXPORTS = (
     "b200lut_version", "b200lut_last_error", "b200lut_sm_count", "b200lut_device_status", "b200lut_packed_bytes",

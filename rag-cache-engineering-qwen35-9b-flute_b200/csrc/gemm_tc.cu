@@ -67,6 +67,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// The same for a CTA of a pair (cta_group::2): the tile lands in this CTA's shared memory, its
+// bytes are reported to `bar`, which may be the other CTA's barrier. Not a multicast load.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
@@ -467,11 +479,25 @@ __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
   return v;
 }
 
-template <typename T, int BITS, int MODE>
+// PAIR: the grid is launched as clusters of two CTAs that work as one MMA unit (cta_group::2) on
+// two row tiles of one token tile: the pair's leader issues MMAs of 256 weight rows (half the
+// issue cost per row — the issuing thread, not the tensor pipe, bounds the one-CTA form) and each
+// CTA fetches only HALF of the activation tile (half the L2 -> shared-memory traffic). Everything
+// a CTA does for its own row tile — codes, lookups, its tensor memory, its epilogue — is as
+// before. The schedule is computed on a virtual grid of pairs over pairs of row tiles; CTA r of
+// a pair serves row tile 2 j + r. No multicast load: each CTA's bulk load lands in its own
+// shared memory and reports its bytes to the leader's barrier.
+template <typename T, int BITS, int MODE, bool PAIR>
 __global__ void __launch_bounds__(kPThreads, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
                           const __grid_constant__ CUtensorMap tmap, const PersistParams p) {
   constexpr bool RES = MODE == kModeResidual, KG = MODE == kModeKGrouped;
+  // Ring depth of both operands. A pair's stages hold half an activation tile each, and its
+  // stage round trip crosses to the other CTA and back, so it runs twice as many: eight operand
+  // stages of 32 columns fill the tensor memory next to the 256-column accumulator.
+  constexpr int NS = PAIR ? 2 * kPStages : kPStages;
+  static_assert(kPACol + 32 * NS <= kTmemCols, "operand stages must fit beside the accumulator");
+  const uint32_t crank = PAIR ? tc::cluster_ctarank() : 0u;      // 0: the pair's leader
   extern __shared__ __align__(16) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t base = smem_u32(smem);
@@ -484,22 +510,27 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
   if (nl < 1) nl = 1;
   const uint32_t tbl_addr = (base + kCtrlBytes + 0xFFFFu) & ~0xFFFFu;
   uint8_t* tbl_ptr = smem + (tbl_addr - base);
-  const uint32_t stage_bytes = uint32_t(p.NT) * 128u;
+  // bytes of one activation stage in THIS CTA (a pair splits the tile's tokens between its CTAs)
+  const uint32_t stage_bytes = uint32_t(PAIR ? p.NT / 2 : p.NT) * 128u;
   // below the table: control block, the epilogue's two staging slices, one activation stage;
   // above it: three more
   uint16_t* stage_out = reinterpret_cast<uint16_t*>(smem + kCtrlBytes);   // 2 x [token][128 rows]
   const uint32_t xlow = (base + kCtrlBytes + 2u * kPStageTokens * 256u + 1023u) & ~1023u;
   const uint32_t xhigh = tbl_addr + kTableBytes;
-  auto xstage = [&](int s) { return s < 1 ? xlow : xhigh + uint32_t(s - 1) * stage_bytes; };
-  const bool fits = xhigh + (kPStages - 1) * stage_bytes <= base + p.smem_bytes &&
-                    xlow + stage_bytes <= tbl_addr;
+  constexpr int kLow = PAIR ? 2 : 1;       // stages that fit below the table
+  auto xstage = [&](int s) {
+    return s < kLow ? xlow + uint32_t(s) * stage_bytes : xhigh + uint32_t(s - kLow) * stage_bytes;
+  };
+  const bool fits = xhigh + (NS - kLow) * stage_bytes <= base + p.smem_bytes &&
+                    xlow + kLow * stage_bytes <= tbl_addr;
 
   // The block's work is a list of segments (tile, k-blocks [c0, c1)). Plain mode: the whole
   // tiles of a cost-balanced contiguous range. Split mode: first the block's k-range of a cut
   // tile (if it has one), then `full` whole tiles.
   const int G = p.G;           // k-blocks of codes
   const int Gx = RES ? p.G + p.E : p.G;    // k-blocks of a tile, the residual's included
-  const int bid = int(blockIdx.x);
+  const int bid = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x);        // block (or pair) of the schedule
+  const int nblk = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
   int t0, ntile, has_cut = 0, cut_tile = 0, cut_c0 = 0, cut_c1 = 0, cut_part = 0;
   if (p.split) {
     t0 = bid * p.full;
@@ -507,13 +538,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
     if (bid < p.left * p.split) {
       has_cut = 1;
       cut_part = bid % p.split;
-      cut_tile = int(gridDim.x) * p.full + bid / p.split;
+      cut_tile = nblk * p.full + bid / p.split;
       cut_c0 = (Gx * cut_part) / p.split;
       cut_c1 = (Gx * (cut_part + 1)) / p.split;
     }
   } else {
-    t0 = persist_first_tile(p, bid, gridDim.x);
-    ntile = persist_first_tile(p, bid + 1, gridDim.x) - t0;
+    t0 = persist_first_tile(p, bid, nblk);
+    ntile = persist_first_tile(p, bid + 1, nblk) - t0;
   }
   const int nseg = ntile + has_cut;
   const int iters = ntile * Gx + (cut_c1 - cut_c0);
@@ -521,24 +552,33 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
   auto seg_tile = [&](int sg) { return (has_cut && sg == 0) ? cut_tile : t0 + sg - has_cut; };
   auto seg_c0 = [&](int sg) { return (has_cut && sg == 0) ? cut_c0 : 0; };
   auto seg_c1 = [&](int sg) { return (has_cut && sg == 0) ? cut_c1 : Gx; };
+  // row tile of a scheduled tile (a pair schedules pairs of row tiles), and the slot of a cut
+  // tile in the workspace and the ticket array
+  auto tile_row = [&](int tile) { return PAIR ? 2 * (tile / p.m_tiles) + int(crank) : tile / p.m_tiles; };
+  auto cut_slot = [&](int tile) { return PAIR ? 2 * (tile - nblk * p.full) + int(crank) : tile - nblk * p.full; };
 
   asm volatile("griddepcontrol.launch_dependents;");
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kPStages; ++s) {
-      tc::mbar_init(bar_full + 8 * s, 5);    // four lookup warps + the TMA producer (and its bytes)
+    for (int s = 0; s < NS; ++s) {
+      // four lookup warps (of each CTA of a pair) + the TMA producer's expect_tx (and the bytes)
+      tc::mbar_init(bar_full + 8 * s, PAIR ? 9 : 5);
       tc::mbar_init(bar_done + 8 * s, 1);    // tcgen05.commit of the k-block that used the stage
     }
     tc::mbar_init(bar_dfull, 1);              // tcgen05.commit: the tile's last MMA
-    tc::mbar_init(bar_dempty, kPEpiWarps);    // the epilogue warps have read the accumulator
+    tc::mbar_init(bar_dempty, PAIR ? 2 * kPEpiWarps : kPEpiWarps);    // the epilogue warps have read the accumulator
     *abort_flag = fits ? 0 : 1;
     if (!fits) atomicCAS(&g_gemm_status, tc::kStatusOk, tc::kStatusWaitLoad);
     tc::mbar_init_fence();
   }
-  if (warp == kLookupWarps) tc::tmem_alloc(base + 264, kTmemCols);
+  if (warp == kLookupWarps) {
+    if constexpr (PAIR) tc::tmem_alloc_pair(base + 264, kTmemCols);
+    else tc::tmem_alloc(base + 264, kTmemCols);
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   tc::fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) tc::cluster_sync();      // both CTAs' barriers exist before anyone signals across
+  else __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
@@ -553,7 +593,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
       if (cu.s < nseg) {
         cu.c = seg_c0(cu.s) + over;
         cu.c1 = seg_c1(cu.s);
-        cu.row = seg_tile(cu.s) / p.m_tiles;
+        cu.row = tile_row(seg_tile(cu.s));
         const PersistSeg sd = segment_of_row(p, cu.row);
         cu.base = sd.packed + size_t(cu.row - sd.row0) * G * (1024 * BITS);
       }
@@ -624,9 +664,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
             table_seg = use.s;
           }
           const int i = it + 2 * u;
-          const int stage = i % kPStages;
-          if (i >= kPStages)        // the k-block that last used this operand stage has been consumed
-            tc::mbar_wait(bar_done + 8 * stage, uint32_t(i / kPStages - 1) & 1u, abort_flag,
+          const int stage = i % NS;
+          if (i >= NS)        // the k-block that last used this operand stage has been consumed
+            tc::mbar_wait(bar_done + 8 * stage, uint32_t(i / NS - 1) & 1u, abort_flag,
                           &g_gemm_status, tc::kStatusWaitEmpty, p.wait_cycles);
           tc::fence_after_sync();
           const bool residual = RES && use.c >= G;
@@ -705,7 +745,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
           }
           tc::wait_st();
           tc::fence_before_sync();
-          if (lane == 0) tc::mbar_arrive(bar_full + 8 * stage);
+          if (lane == 0) {
+            if constexpr (PAIR) tc::mbar_arrive_cluster((bar_full + 8 * stage) & tc::kPeerBitMask);
+            else tc::mbar_arrive(bar_full + 8 * stage);
+          }
           advance(use);
         }
       }
@@ -714,18 +757,33 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
     // ---- TMA producer ---------------------------------------------------------------------------
     int i = 0;
     for (int sg = 0; sg < nseg; ++sg) {
-      const int m0 = (seg_tile(sg) % p.m_tiles) * p.NT;
+      int m0 = (seg_tile(sg) % p.m_tiles) * p.NT;
+      if constexpr (PAIR) {
+        // the pair's second CTA holds the upper half of the tile's tokens: nt / 2 rows on, where
+        // nt is the width the MMA will run this tile at
+        int nt = p.M - m0;
+        nt = nt >= p.NT ? p.NT : ((nt + 31) & ~31);
+        m0 += int(crank) * (nt >> 1);
+      }
       const int c_hi = seg_c1(sg);
-      const int tcol = RES ? segment_of_row(p, seg_tile(sg) / p.m_tiles).t_col0 - G * kChunkK : 0;
+      const int tcol = RES ? segment_of_row(p, tile_row(seg_tile(sg))).t_col0 - G * kChunkK : 0;
       for (int c = seg_c0(sg); c < c_hi; ++c, ++i) {
-        const int xs = i % kPStages;
-        if (i >= kPStages)
-          tc::mbar_wait(bar_done + 8 * xs, uint32_t(i / kPStages - 1) & 1u, abort_flag,
+        const int xs = i % NS;
+        if (i >= NS)
+          tc::mbar_wait(bar_done + 8 * xs, uint32_t(i / NS - 1) & 1u, abort_flag,
                         &g_gemm_status, tc::kStatusWaitEmpty, p.wait_cycles);
         if (lane == 0 && !*abort_flag) {
-          tc::mbar_expect_tx(bar_full + 8 * xs, stage_bytes);
-          if (!RES || c < G) tma_load_2d(xstage(xs), &xmap, bar_full + 8 * xs, c * kChunkK, m0);
-          else tma_load_2d(xstage(xs), &tmap, bar_full + 8 * xs, tcol + c * kChunkK, m0);
+          if constexpr (PAIR) {
+            // both halves report their bytes to the leader's barrier; the leader expects them
+            if (crank == 0) tc::mbar_expect_tx(bar_full + 8 * xs, 2u * stage_bytes);
+            const uint32_t lead = (bar_full + 8 * xs) & tc::kPeerBitMask;
+            if (!RES || c < G) tma_load_2d_pair(xstage(xs), &xmap, lead, c * kChunkK, m0);
+            else tma_load_2d_pair(xstage(xs), &tmap, lead, tcol + c * kChunkK, m0);
+          } else {
+            tc::mbar_expect_tx(bar_full + 8 * xs, stage_bytes);
+            if (!RES || c < G) tma_load_2d(xstage(xs), &xmap, bar_full + 8 * xs, c * kChunkK, m0);
+            else tma_load_2d(xstage(xs), &tmap, bar_full + 8 * xs, tcol + c * kChunkK, m0);
+          }
         }
         __syncwarp();
       }
@@ -734,18 +792,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
     // ---- MMA issuer -----------------------------------------------------------------------------
     constexpr uint32_t kFmt = DType<T>::id == B200LUT_BF16 ? 1u : 0u;
     const uint64_t dtemplate = tc::smem_desc(0u, 16u, 1024u, 2u);
-    uint32_t xlo[kPStages];
+    uint32_t xlo[NS];
 #pragma unroll
-    for (int s = 0; s < kPStages; ++s) xlo[s] = uint32_t(dtemplate) + (xstage(s) >> 4);
+    for (int s = 0; s < NS; ++s) xlo[s] = uint32_t(dtemplate) + (xstage(s) >> 4);
     const uint32_t xhi = uint32_t(dtemplate >> 32);
-    if (lane == 0) {
+    if (lane == 0 && crank == 0) {               // of a pair only the leader issues
       int t = -1, c = 0, c_first = 0, c_end = 0;   // segment, k-block, the segment's k range
       uint32_t idesc = 0;
       const uint32_t d0 = tmem;
       uint32_t phase = 0;            // (i / ring size) & 1
-      for (int i0 = 0; i0 < iters; i0 += kPStages, phase ^= 1u) {
+      for (int i0 = 0; i0 < iters; i0 += NS, phase ^= 1u) {
 #pragma unroll
-        for (int u = 0; u < kPStages; ++u) {
+        for (int u = 0; u < NS; ++u) {
           if (i0 + u < iters) {
             if (c == c_end) {        // a new segment: the accumulator must have been drained
               ++t;
@@ -754,17 +812,24 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
               const int m0 = (seg_tile(t) % p.m_tiles) * p.NT;
               int nt = p.M - m0;                          // the row's last tile may be narrower
               nt = nt >= p.NT ? p.NT : ((nt + 31) & ~31);
-              idesc = tc::instr_desc(kFmt, 128, uint32_t(nt));
+              idesc = tc::instr_desc(kFmt, PAIR ? 256 : 128, uint32_t(nt));
               if (t >= 1)
                 tc::mbar_wait(bar_dempty, uint32_t(t - 1) & 1u, abort_flag, &g_gemm_status,
                               tc::kStatusWaitDone, p.wait_cycles);
             }
             tc::mbar_wait(bar_full + 8 * u, phase, abort_flag, &g_gemm_status, tc::kStatusWaitFull, p.wait_cycles);
             tc::fence_after_sync();
-            tc::mma_ts_kblock(d0, tmem + kPACol + 32u * uint32_t(u), xlo[u], xhi, idesc,
-                              c == c_first ? 0u : 1u);   // a segment's first k-block overwrites
-            tc::mma_commit(bar_done + 8 * u);
-            if (++c == c_end) tc::mma_commit(bar_dfull);
+            if constexpr (PAIR) {
+              tc::mma_ts_kblock_pair(d0, tmem + kPACol + 32u * uint32_t(u), xlo[u], xhi, idesc,
+                                     c == c_first ? 0u : 1u);
+              tc::mma_commit_pair(bar_done + 8 * u);          // frees the stage in both CTAs
+              if (++c == c_end) tc::mma_commit_pair(bar_dfull);
+            } else {
+              tc::mma_ts_kblock(d0, tmem + kPACol + 32u * uint32_t(u), xlo[u], xhi, idesc,
+                                c == c_first ? 0u : 1u);   // a segment's first k-block overwrites
+              tc::mma_commit(bar_done + 8 * u);
+              if (++c == c_end) tc::mma_commit(bar_dfull);
+            }
           }
         }
       }
@@ -780,8 +845,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
     for (int t = 0; t < nseg; ++t) {
       const int tile = seg_tile(t);
       const bool cut = has_cut && t == 0;
-      const PersistSeg sd = segment_of_row(p, tile / p.m_tiles);
-      const int n0 = (tile / p.m_tiles - sd.row0) * kTileRows, m0 = (tile % p.m_tiles) * p.NT;
+      const PersistSeg sd = segment_of_row(p, tile_row(tile));
+      const int n0 = (tile_row(tile) - sd.row0) * kTileRows, m0 = (tile % p.m_tiles) * p.NT;
       int nt = p.M - m0;
       nt = nt >= p.NT ? p.NT : ((nt + 31) & ~31);
       const int half = nt >> 1, col0 = h * half;
@@ -790,7 +855,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
       tc::mbar_wait(bar_dfull, uint32_t(t) & 1u, abort_flag, &g_gemm_status, tc::kStatusWaitDone, p.wait_cycles);
       tc::fence_after_sync();
       const uint32_t d0 = tmem + (uint32_t(32 * q) << 16) + uint32_t(col0);
-      float* wt = cut ? p.ws + size_t(tile - int(gridDim.x) * p.full) * p.split * (256 * kTileRows) : nullptr;
+      float* wt = cut ? p.ws + size_t(cut_slot(tile)) * p.split * (256 * kTileRows) : nullptr;
       // slices of up to 48 tokens: three loads in flight, one wait, staging, 16-byte stores
       for (int s0 = 0; s0 < half; s0 += kPStageTokens) {
         const int sn = half - s0 < kPStageTokens ? half - s0 : kPStageTokens;
@@ -801,7 +866,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
         tc::wait_ld();
         if (s0 + sn >= half) {   // the accumulator is free as soon as it has been read
           tc::fence_before_sync();
-          if (lane == 0) tc::mbar_arrive(bar_dempty);
+          if (lane == 0) {
+            if constexpr (PAIR) tc::mbar_arrive_cluster(bar_dempty & tc::kPeerBitMask);
+            else tc::mbar_arrive(bar_dempty);
+          }
         }
         if (cut) {   // this block's k-range of a cut tile: raw fp32 sums to its workspace slot
           float* mine = wt + size_t(cut_part) * (256 * kTileRows) + 32 * q + lane;
@@ -865,7 +933,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
         // wait: the grid is one block per SM and every block does its cut piece first), and
         // each finishes the token pairs g with g % split == its part: the partial sums are
         // added in part (= ascending k) order, bias, one rounding, element stores.
-        int* cnt = p.tickets + 2 * (tile - int(gridDim.x) * p.full);
+        int* cnt = p.tickets + 2 * cut_slot(tile);
         __threadfence();
         asm volatile("bar.sync 4, %0;" ::"r"(kPEpiWarps * 32) : "memory");
         if (warp == kLookupWarps + 2 && lane == 0) {
@@ -912,10 +980,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
     }
   }
   tc::fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) tc::cluster_sync();      // neither CTA's memories are in use by the other any more
+  else __syncthreads();
   if (warp == kLookupWarps) {
     tc::fence_after_sync();
-    tc::tmem_dealloc(tmem, kTmemCols);
+    if constexpr (PAIR) tc::tmem_dealloc_pair(tmem, kTmemCols);
+    else tc::tmem_dealloc(tmem, kTmemCols);
   }
 }
 
@@ -984,10 +1054,10 @@ SplitPlan plan_split(long long tiles, int G, int sms) {
   return sp;
 }
 
-template <typename T, int BITS, int MODE>
+template <typename T, int BITS, int MODE, bool PAIR>
 int launch_persistent(const CUtensorMap& map, const CUtensorMap& tmap, const PersistParams& p,
                       int grid, bool pdl, cudaStream_t stream) {
-  auto kern = gemm_tc_persistent_kernel<T, BITS, MODE>;
+  auto kern = gemm_tc_persistent_kernel<T, BITS, MODE, PAIR>;
   static bool configured[64] = {false};
   int dev = 0;
   B200LUT_CUDA_OK(cudaGetDevice(&dev));
@@ -1001,11 +1071,18 @@ int launch_persistent(const CUtensorMap& map, const CUtensorMap& tmap, const Per
   cfg.blockDim = dim3(kPThreads, 1, 1);
   cfg.dynamicSmemBytes = p.smem_bytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   int na = 0;
   if (pdl) {
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (PAIR) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 2;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
     ++na;
   }
   cfg.attrs = attr;
@@ -1013,6 +1090,10 @@ int launch_persistent(const CUtensorMap& map, const CUtensorMap& tmap, const Per
   B200LUT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map, tmap, p));
   return B200LUT_OK;
 }
+
+// Whether a launch of `rows` row tiles and M activation rows runs as CTA pairs: whole 256-token
+// tiles are worth it, the row tiles must pair up, and so must the SMs.
+bool pairs_serve(int rows, int M, int sms) { return M >= kPMaxNT && rows >= 2 && rows % 2 == 0 && sms % 2 == 0; }
 
 int encode_x_map(CUtensorMap* map, const void* x, int64_t ldx, int M, int K, int dtype, int NT) {
   EncodeTiledFn enc = encode_fn();
@@ -1056,7 +1137,7 @@ namespace {
 int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b200lut_segment* segs,
                     int nseg, bool pdl, void* workspace, size_t workspace_bytes,
                     void* stream, float* acc_out = nullptr, const float* acc_in = nullptr,
-                    long long ld_acc = 0, int kg_rows = 0) {
+                    long long ld_acc = 0, int kg_rows = 0, bool cta_pairs = false) {
   PersistParams pp = {};
   pp.acc_out = acc_out; pp.acc_in = acc_in; pp.ld_acc = ld_acc;
   const bool kgrouped = kg_rows > 0;     // segs[0].lut is lut_k [K / 128][kg_rows][2^bits]
@@ -1097,9 +1178,19 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
   const b200lut_segment& s = segs[0];
   pp.M = M; pp.K = K; pp.G = K / kChunkK;
   pp.gs = s.group_size;
+  int sms = 148;
+  {
+    int dev = 0;
+    B200LUT_CUDA_OK(cudaGetDevice(&dev));
+    B200LUT_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  // CTA pairs (cta_group::2), on request (B200LUT_FLAG_CTA_PAIRS): the plain lookup mode only.
+  // Measured 1.47x SLOWER than one CTA per tile at every prefill shape (bit-identical results),
+  // so the library never picks it by itself.
+  const bool pair = cta_pairs && pairs_serve(rows, M, sms) && !acc_out && !acc_in && !extra && !kgrouped;
   pp.NT = M >= kPMaxNT ? kPMaxNT : ((M + 31) / 32) * 32;
   pp.m_tiles = (M + pp.NT - 1) / pp.NT;
-  pp.n_tiles = rows;
+  pp.n_tiles = pair ? rows / 2 : rows;      // a pair schedules pairs of row tiles
   pp.W = (pp.m_tiles - 1) * pp.NT + ((M - (pp.m_tiles - 1) * pp.NT + 31) / 32) * 32;
   pp.smem_bytes = uint32_t(kMaxDynSmem);
   // Waits inside the kernel give up after ~10 ms. A profiler that replays the kernel with
@@ -1113,35 +1204,36 @@ int persistent_gemm(const void* x, int64_t ldx, int M, int K, int dtype, const b
     pp.wait_cycles = (long long)ms * 2000000ll;
   }
   CUtensorMap pmap, tmap;
-  if (int rc = encode_x_map(&pmap, x, ldx, M, K, dtype, pp.NT)) return rc;
+  const int box_rows = pair ? pp.NT / 2 : pp.NT;     // each CTA of a pair fetches half of the tile's tokens
+  if (int rc = encode_x_map(&pmap, x, ldx, M, K, dtype, box_rows)) return rc;
   if (extra) {
-    if (int rc = encode_x_map(&tmap, t_base, t_ld, M, int(t_ld), dtype, pp.NT)) return rc;
+    if (int rc = encode_x_map(&tmap, t_base, t_ld, M, int(t_ld), dtype, box_rows)) return rc;
   } else {
     tmap = pmap;
   }
-  int sms = 148;
-  {
-    int dev = 0;
-    B200LUT_CUDA_OK(cudaGetDevice(&dev));
-    B200LUT_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  }
+  // the schedule's blocks: CTAs, or pairs of them over pairs of row tiles
+  const int units = pair ? sms / 2 : sms;
   const long long tiles = (long long)pp.n_tiles * pp.m_tiles;
-  int grid = int(tiles < sms ? tiles : sms);
-  const SplitPlan sp = plan_split(tiles, pp.G + pp.E, sms);
+  int grid = int(tiles < units ? tiles : units);
+  SplitPlan sp = plan_split(tiles, pp.G + pp.E, units);
+  if (pair) sp.bytes = sp.split ? kTicketBytes + 2 * (sp.bytes - kTicketBytes) : 0;   // a slot per CTA
+  if (pair && sp.left > int(kTicketBytes / 16)) sp.split = 0;
   if (sp.split && workspace && workspace_bytes >= sp.bytes && aligned16(workspace) &&
       !acc_out && !acc_in) {
     pp.split = sp.split; pp.full = sp.full; pp.left = sp.left;
     pp.tickets = static_cast<int*>(workspace);
     pp.ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kTicketBytes);
-    grid = sms;
+    grid = units;
   }
-#define B200LUT_PERSIST_AS(B, MODE)                                                                 \
-  (dtype == B200LUT_BF16                                                                             \
-       ? launch_persistent<__nv_bfloat16, B, MODE>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)) \
-       : launch_persistent<__half, B, MODE>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)))
-#define B200LUT_PERSIST(B)                                                  \
-  (kgrouped ? B200LUT_PERSIST_AS(B, kModeKGrouped)                          \
-            : (extra ? B200LUT_PERSIST_AS(B, kModeResidual) : B200LUT_PERSIST_AS(B, kModePlain)))
+  if (pair) grid *= 2;
+#define B200LUT_PERSIST_AS(B, MODE, PAIR)                                                                 \
+  (dtype == B200LUT_BF16                                                                                   \
+       ? launch_persistent<__nv_bfloat16, B, MODE, PAIR>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)) \
+       : launch_persistent<__half, B, MODE, PAIR>(pmap, tmap, pp, grid, pdl, cudaStream_t(stream)))
+#define B200LUT_PERSIST(B)                                                         \
+  (kgrouped ? B200LUT_PERSIST_AS(B, kModeKGrouped, false)                          \
+            : (extra ? B200LUT_PERSIST_AS(B, kModeResidual, false)                 \
+                     : (pair ? B200LUT_PERSIST_AS(B, kModePlain, true) : B200LUT_PERSIST_AS(B, kModePlain, false))))
   switch (s.bits) {
     case 4: return B200LUT_PERSIST(4);
     case 3: return B200LUT_PERSIST(3);
@@ -1182,7 +1274,14 @@ extern "C" size_t b200lut_gemm_workspace_bytes(int M, int N, int K) {
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess)
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  return plan_split(tiles, K / kChunkK, sms).bytes;
+  // what either form of the launch may ask for: single CTAs, or (on request) CTA pairs over pairs of row tiles
+  size_t need = plan_split(tiles, K / kChunkK, sms).bytes;
+  if (pairs_serve(N / kTileRows, M, sms)) {
+    const SplitPlan sp = plan_split(tiles / 2, K / kChunkK, sms / 2);
+    const size_t pair_need = sp.split ? kTicketBytes + 2 * (sp.bytes - kTicketBytes) : 0;
+    if (pair_need > need) need = pair_need;
+  }
+  return need;
 }
 
 extern "C" int b200lut_gemm(const void* x, int64_t ldx, int M, int K, int dtype,
@@ -1216,7 +1315,8 @@ extern "C" int b200lut_gemm_multi(const void* x, int64_t ldx, int M, int K, int 
     B200LUT_REQUIRE(aligned16(s.packed), B200LUT_ERR_ALIGN, "code buffers must be 16-byte aligned");
   }
   return persistent_gemm(x, ldx, M, K, dtype, segs, nseg, (flags & 1) != 0, workspace,
-                         workspace_bytes, stream);
+                         workspace_bytes, stream, nullptr, nullptr, 0, 0,
+                         (flags & B200LUT_FLAG_CTA_PAIRS) != 0);
 }
 
 extern "C" int b200lut_gemm_kgrouped(const void* x, int64_t ldx, int M, int K, int dtype,
@@ -1246,7 +1346,7 @@ extern "C" int b200lut_gemm_kgrouped(const void* x, int64_t ldx, int M, int K, i
   s.n_groups = N / kTileRows;
   s.bits = bits;
   return persistent_gemm(x, ldx, M, K, dtype, &s, 1, (flags & 1) != 0, workspace, workspace_bytes, stream,
-                         nullptr, nullptr, 0, N);
+                         nullptr, nullptr, 0, N, (flags & B200LUT_FLAG_CTA_PAIRS) != 0);
 }
 
 extern "C" size_t b200lut_gemm_two_stream_bytes(int M, int N) {
@@ -1318,7 +1418,8 @@ extern "C" int b200lut_gemm_ws(const void* x, int64_t ldx, int M, int K, int dty
   const bool pdl = (flags & 1) != 0;
   const int nl = s.group_size >= 128 ? 1 : 128 / s.group_size;
   if (!two && nl <= 2 && K / kChunkK >= 2) {
-    return persistent_gemm(x, ldx, M, K, dtype, seg, 1, pdl, workspace, workspace_bytes, stream);
+    return persistent_gemm(x, ldx, M, K, dtype, seg, 1, pdl, workspace, workspace_bytes, stream,
+                           nullptr, nullptr, 0, 0, (flags & B200LUT_FLAG_CTA_PAIRS) != 0);
   }
 
   // what is left for the one-tile kernel: two code streams, the fused gate/up form, four

@@ -191,5 +191,65 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
                : "memory");
 }
 
+// ---- CTA pairs (cta_group::2) ---------------------------------------------------------------------
+// Two CTAs of a cluster work as one MMA unit: each keeps its 128 rows of the A operand in its own
+// tensor memory and HALF of the B tile in its own shared memory; one thread of the leader (cluster
+// rank 0) issues the MMAs, the tensor cores of both CTAs run them, each into its own accumulator.
+// Shared-state addresses carry the CTA's rank in bit 24: clearing it names the leader's copy of a
+// barrier, which is how the peer's arrivals and its bulk loads report to the leader. No load here
+// is a multicast load.
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on a barrier of any CTA of the cluster (shared::cluster address).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// One warp of EACH CTA of the pair executes alloc / dealloc (same warp index, same dst offset).
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+               "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+// The four K = 16 steps of one k-block on a CTA pair: D (256 rows over the two CTAs) (+)=
+// A[a0 + 8 j in each CTA's tensor memory] * B[desc + 32 j bytes, half of its N rows in each CTA].
+__device__ __forceinline__ void mma_ts_kblock_pair(uint32_t tmem_d, uint32_t a0, uint32_t desc_lo,
+                                                   uint32_t desc_hi, uint32_t idesc,
+                                                   uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 b0, b1, b2, b3;\n\t.reg .b32 l1, l2, l3, a1, a2, a3;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 q, %6, %6;\n\t"
+      "add.u32 l1, %2, 2;\n\tadd.u32 l2, %2, 4;\n\tadd.u32 l3, %2, 6;\n\t"
+      "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\t"
+      "mov.b64 b0, {%2, %3};\n\tmov.b64 b1, {l1, %3};\n\tmov.b64 b2, {l2, %3};\n\tmov.b64 b3, {l3, %3};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], b0, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, p;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [a1], b1, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, q;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [a2], b2, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, q;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [a3], b3, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, q;\n\t}"
+      :
+      : "r"(tmem_d), "r"(a0), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// All MMAs issued so far by this thread arrive, when complete, on the barrier at the same offset
+// in both CTAs of the pair.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(uint16_t(3))
+      : "memory");
+}
+
 }  // namespace tc
 }  // namespace b200lut

@@ -327,3 +327,29 @@ def test_two_stream_entry_refuses_a_missing_stream_and_a_small_scratch():
     seg = L.make_segments([two._segment_desc(out)])
     rc = L.lib().b200lut_gemm_two_stream(x.data_ptr(), 128, 32, 128, 0, seg, 0, out.data_ptr(), 64, None)
     assert rc == 4
+
+
+@pytest.mark.parametrize("N,K,gs,bits,dtype,M,bias", (
+    (12288, 1024, 128, 4, torch.bfloat16, 512, True),    # 96 pairs of tiles on 74 pairs of SMs: cut tiles too
+    (1024, 2048, 64, 3, torch.float16, 300, False),      # a second token tile 44 rows wide: the halves meet at 32
+    (256, 256, 128, 2, torch.bfloat16, 256, True),       # one pair, one tile each
+))
+def test_cta_pairs_give_the_same_bits_as_single_ctas(N, K, gs, bits, dtype, M, bias):
+    """tcgen05 cta_group::2: two CTAs of a cluster run one MMA over 256 weight rows, each holding
+    its own 128 rows in tensor memory and half of the activation tile in shared memory. Every
+    output element is the same sum in the same order as with one CTA per tile."""
+    case = Case(N, K, gs, bits, dtype, seed=N + M, bias=bias)
+    mod = case.module()
+    mod._ensure_packed()
+    x = case.x(M).cuda()
+    single = _raw_gemm(case, mod, x, split=False)
+    d = dict(packed=mod._packed, lut=mod.lut, N=case.N, group_size=case.gs, n_groups=mod.lut.shape[0],
+             bits=case.bits, out=torch.full((M, N), float("nan"), dtype=dtype, device="cuda"))
+    if case.bias is not None:
+        d["bias"] = case.bias.cuda()
+    L.gemm(x, L.make_segments([d]), flags=L.FLAG_CTA_PAIRS, split=False)
+    assert torch.equal(d["out"], single)               # whole tiles: the same sums in the same order
+    assert rel_err(single, case.oracle(x.cpu())) <= TOL
+    d["out"].fill_(float("nan"))
+    L.gemm(x, L.make_segments([d]), flags=L.FLAG_CTA_PAIRS)     # cut tiles: other K split points
+    assert rel_err(d["out"], single) <= 4e-3
