@@ -741,6 +741,19 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap xmap,
             const bool codes = on && (!RES || ld.c < G);
             load_slab_pair<BITS>(w[u], codes ? code_ptr(ld) : p.seg[0].packed, q, codes ? 1u : 0u);
             if (KG) load_palette(u, ld, on);
+            if (RES && on && !codes) {
+              // a residual k-block four iterations ahead: pull this lane's resA rows into L1 now
+              const PersistSeg sd = segment_of_row(p, ld.row);
+              if (sd.resA != nullptr) {
+                const int kk = (ld.c - G) * kChunkK;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int n = (ld.row - sd.row0) * kTileRows + 32 * q + 8 * j + (lane >> 2);
+                  if (kk < sd.res_rank)
+                    asm volatile("prefetch.global.L1 [%0];" ::"l"(sd.resA + size_t(n) * sd.res_rank + kk));
+                }
+              }
+            }
             if (on) advance(ld);
           }
           tc::wait_st();
