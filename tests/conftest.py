@@ -74,3 +74,18 @@ def golden():
 @pytest.fixture(scope="session")
 def golden_embedding():
     return Golden(os.path.join(ROOT, "tests", "golden", "embedding_vectors.npz"))
+
+
+def pytest_terminal_summary(terminalreporter):
+    """Observed maxima of the parity checks (bound: 1e-2 unless the test says otherwise), the
+    five largest and the count, so a regression shows before it crosses the bound."""
+    try:
+        from helpers import OBSERVED
+    except Exception:
+        return
+    if not OBSERVED:
+        return
+    worst = sorted(OBSERVED.items(), key=lambda kv: -kv[1])[:5]
+    terminalreporter.write_line(f"observed max-relative errors of {len(OBSERVED)} tests; largest:")
+    for name, e in worst:
+        terminalreporter.write_line(f"  {e:.3e}  {name}")

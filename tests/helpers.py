@@ -61,5 +61,16 @@ class Case:
                                   bias=self.bias, rot_signs=self.signs, awq_scale=self.awq)
 
 
+OBSERVED = {}    # test id -> largest max-relative error it measured (printed at the end of the run)
+
+
 def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
-    return orc.max_rel_err(got.detach().cpu().float(), want.detach().cpu().float())
+    """max |got - want| / max |want| (the reference's rel-max form,
+    src/scripts/test_qwen_weights.py:104-105); the largest value per test is kept so that the
+    run's summary shows how far below the bound the kernels are."""
+    import os
+    e = orc.max_rel_err(got.detach().cpu().float(), want.detach().cpu().float())
+    name = os.environ.get("PYTEST_CURRENT_TEST", "?").split(" ")[0]
+    if e <= 5e-2 and e > OBSERVED.get(name, -1.0):     # larger values are deliberate contrasts
+        OBSERVED[name] = e
+    return e
