@@ -130,8 +130,16 @@ def gemv_mlp_available() -> bool:
 
 
 def gemv_mlp_supported(K, N, specs, fht: bool = False, folds_differ: bool = False) -> bool:
+    """With folds_differ (gate and up rotated by different folds) the pair is served only where
+    one launch can rotate per segment: 4-bit single-stream segments, group size >= 32, K made of
+    at most 8 power-of-two pieces (qgemm_gemv_mlp then leaves gate | up side by side and runs one
+    SiLU*mul pass)."""
     specs = list(specs)
-    return _built() and len(specs) == 2 and all(_shape_ok(b1, b2, gs, N, K) for b1, b2, gs in specs)
+    ok = _built() and len(specs) == 2 and all(_shape_ok(b1, b2, gs, N, K) for b1, b2, gs in specs)
+    if ok and folds_differ:
+        ok = all(int(b1) == 4 and not int(b2 or 0) and int(gs) >= 32 for b1, b2, gs in specs) \
+            and bin(int(K)).count("1") <= 8
+    return ok
 
 
 def gemv_split_hint(N: int, K: int) -> int:

@@ -873,6 +873,15 @@ class PalettizedEmbedding(nn.Module):
         if self.has_stream2:
             d.update(packed2=p2, lut2=self.lut2.to(self.lut.dtype), bits2=self.bitwidth2)
         if self.has_residual():
+            if (self.resA.dtype != self.lut.dtype or self.resB.dtype != self.lut.dtype) \
+                    and not self.__dict__.get("_warned_residual_dtype"):
+                # the reference widens the factors to fp32 in the dtype they are stored in
+                # (src/scripts/palettized_modules.py:2320); the gather kernel reads them in
+                # the palette dtype, so wider factors lose their extra bits here
+                import warnings
+                warnings.warn(f"PalettizedEmbedding: residual factors in {self.resA.dtype} / {self.resB.dtype} are "
+                              f"rounded to the palette dtype {self.lut.dtype} for the gather kernel")
+                self.__dict__["_warned_residual_dtype"] = True
             d.update(resA=self.resA.to(self.lut.dtype).contiguous(),
                      resB=self.resB.to(self.lut.dtype).contiguous())
         return d
