@@ -754,6 +754,8 @@ def run_extras(pkg, st, stack, peaks, flags):
         gbs, us, g = kgrouped_projection_gbs(pkg, 1, 4096, 4096, 16, 20, gate=True)
         put("gemv_kgrouped_4096x4096_m1", {"GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / hbm,
                                             "bytes_per_launch": 12599296}, g)
+        gbs, us, g = kgrouped_projection_gbs(pkg, 8, 4096, 4096, 16, 20, gate=True)
+        put("gemv_kgrouped_4096x4096_m8", {"GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / hbm}, g)
         tf, us, g = kgrouped_gemm_tflops(pkg, 2048, 12288, 4096, 20)
         put("prefill_gemm_kgrouped_m2048_k4096_n12288", {"TFLOP/s": tf, "us": us,
                                                           "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}, g)

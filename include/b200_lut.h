@@ -421,7 +421,11 @@ int b200lut_gemm_two_stream(const void* x, int64_t ldx, int M, int K, int dtype,
  * (src/scripts/palettized_modules.py:125-162), summed in fp32. split = 0 lets the library pick
  * the number of K ranges (b200lut_gemv_kgrouped_split); with split > 1 the caller passes a
  * zero-initialised workspace of b200lut_gemv_kgrouped_workspace_bytes(N, M, split) bytes
- * (fp32 partial sums folded in range order by the last block; the tickets reset themselves). */
+ * (fp32 partial sums folded in range order by the last block; the tickets reset themselves).
+ * The N / 128 tickets sit at the start of the workspace and the partial sums behind them: a
+ * caller that reuses one workspace for different N zeroes its first N / 128 * 4 + 256 bytes when
+ * N grows. With split = 0 and 4-bit codes at M <= 8 the library runs the row-range form of the
+ * kernel instead (one block per range of 32-row units over all of K, no workspace). */
 int b200lut_gemv_kgrouped_split(int N, int K);
 size_t b200lut_gemv_kgrouped_workspace_bytes(int N, int M, int split);
 int b200lut_gemv_kgrouped(const void* x, int64_t ldx, int M, int K, int dtype,

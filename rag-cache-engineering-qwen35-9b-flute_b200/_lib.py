@@ -521,16 +521,23 @@ def gemv_kgrouped(x: torch.Tensor, packed: torch.Tensor, lut_k: torch.Tensor, N:
     if out is None:
         out = torch.empty(M, N, dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
-        if split <= 0:
-            split = lib().b200lut_gemv_kgrouped_split(N, K)
-        need = lib().b200lut_gemv_kgrouped_workspace_bytes(N, M, split)
+        # split = 0 leaves the choice (kernel and split) to the library; the scratch is sized for
+        # the split it would pick for its workspace-folded kernel
+        planned = split if split > 0 else lib().b200lut_gemv_kgrouped_split(N, K)
+        need = lib().b200lut_gemv_kgrouped_workspace_bytes(N, M, planned)
         ws = None
         if need:
+            # One zero-filled scratch per (device, stream). The tickets sit at its start, N / 128
+            # of them, and the partial sums behind them: a call with MORE row tiles than the last
+            # one finds old partial sums where its tickets are, so the head is zeroed again
+            # (stream-ordered) whenever the tile count changes.
             key = (x.device, int(_stream(x) or 0))
-            ws = _kg_scratch.get(key)
+            ws, tiles = _kg_scratch.get(key, (None, 0))
             if ws is None or ws.numel() < need:
                 ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=x.device)
-                _kg_scratch[key] = ws
+            elif tiles != N // 128:
+                ws[:(max(tiles, N // 128) * 4 + 511) // 256 * 256].zero_()
+            _kg_scratch[key] = (ws, N // 128)
         check(lib().b200lut_gemv_kgrouped(x.data_ptr(), x.stride(0), M, K, dtype_id(x.dtype),
                                           packed.data_ptr(), lut_k.data_ptr(), ptr(bias), N, bits,
                                           out.data_ptr(), out.stride(0), split, ptr(ws),

@@ -18,7 +18,11 @@
 // are in flight behind the one being computed. K ranges are folded through an fp32 workspace by
 // the last block to arrive, in range order (deterministic; the ticket resets itself).
 // Bound: HBM (codes N*K*bits/8 + palettes N*K*2^bits/64 bytes per launch).
+#include <cstdlib>
+
 #include "common.cuh"
+#include "pairtable.cuh"
+#include "gemv_kgrouped_rows.cuh"
 
 namespace b200lut {
 namespace {
@@ -277,6 +281,42 @@ extern "C" int b200lut_gemv_kgrouped(const void* x, int64_t ldx, int M, int K, i
                   "x, codes and palettes must be 16-byte aligned, the x row stride a multiple of 8 "
                   "and >= K, ldo >= N");
   const int tiles = N / kTileRows, NG = K / kKgGroup;
+  // Library policy (split == 0): the row-range form for 4-bit codes at M <= 8 where its rows and
+  // fold buffer fit in shared memory (B200LUT_KG_KERNEL=simt keeps the SIMT kernel, for A/B runs).
+  if (split <= 0 && bits == 4 && M <= 8) {
+    static const bool simt_only = [] {
+      const char* e = getenv("B200LUT_KG_KERNEL");
+      return e != nullptr && e[0] == 's';
+    }();
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    KgRowsGeom g;
+    if (!simt_only && kg_rows_plan(M, N, K, sms, &g)) {
+      KgRowsParams rp = {};
+      rp.x = static_cast<const uint16_t*>(x);
+      rp.ldx = ldx;
+      rp.packed = static_cast<const uint8_t*>(packed);
+      rp.lut = static_cast<const uint16_t*>(lut_k);
+      rp.bias = static_cast<const uint16_t*>(bias);
+      rp.out = static_cast<uint16_t*>(out);
+      rp.ldo = ldo;
+      rp.M = M; rp.Mp = g.Mp; rp.N = N; rp.K = K; rp.G = K / kChunkK;
+      rp.units_total = g.units_total; rp.row_blocks = g.row_blocks; rp.red_planes = g.red_planes;
+      rp.xs_off = g.xs_off; rp.red_off = g.red_off;
+      auto go = [&](auto kern, int which) -> int {
+        static bool configured[2][64] = {};
+        if (dev >= 64 || !configured[which][dev]) {
+          B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+          if (dev < 64) configured[which][dev] = true;
+        }
+        kern<<<unsigned(g.row_blocks), kKrThreads, g.bytes, cudaStream_t(stream)>>>(rp);
+        B200LUT_CUDA_OK(cudaGetLastError());
+        return B200LUT_OK;
+      };
+      return dtype == B200LUT_BF16 ? go(gemv_kgrouped_rows_kernel<__nv_bfloat16>, 0)
+                                   : go(gemv_kgrouped_rows_kernel<__half>, 1);
+    }
+  }
   if (split <= 0) split = pick_kg_split(tiles, NG);
   B200LUT_REQUIRE(split <= NG && split <= 65535, B200LUT_ERR_INVALID,
                   "split %d exceeds the %d column groups", split, NG);

@@ -112,3 +112,36 @@ def test_refusals():
         pkg.KGroupedPalettizedLinear(mod.indices.cpu(), lut_k[:, :64], 4, 128, 128)
     with pytest.raises(ValueError, match="K%128"):
         pkg.KGroupedPalettizedLinear(torch.zeros(128 * 64 // 2, dtype=torch.uint8), lut_k, 4, 128, 64)
+
+
+def test_the_shared_scratch_survives_a_change_of_shape():
+    # the wrapper keeps one scratch per stream: its tickets sit where a smaller shape left
+    # partial sums, so a larger shape after a smaller one must still fold correctly
+    dt = torch.bfloat16
+    for N, K, M, bits in ((256, 2048, 2, 3), (1536, 2048, 16, 3), (512, 4096, 9, 4), (2048, 1024, 16, 4)):
+        codes, lut_k, _, mod = _case(N, K, bits, dt, N + K)
+        x = torch.randn(M, K, generator=torch.Generator().manual_seed(N)).to(dt)
+        want = orc.linear_forward(x, orc.dequant_kgrouped(codes, lut_k, 128))
+        for _ in range(2):
+            assert rel_err(mod(x.cuda()), want) <= TOL, (N, K, M, bits)
+
+
+@pytest.mark.parametrize("N,K,M,dtype", ((4096, 4096, 1, torch.bfloat16), (12288, 4096, 3, torch.float16),
+                                         (4096, 12288, 8, torch.bfloat16), (160 * 32, 256, 5, torch.bfloat16),
+                                         (128, 128, 2, torch.float16)))
+def test_row_range_form_of_the_decode_kernel(N, K, M, dtype):
+    """4-bit codes at M <= 8 run the row-range form (split = 0); an explicit split keeps the
+    workspace-folded kernel: both match the oracle composition and each other within rounding."""
+    codes, lut_k, b, mod = _case(N, K, 4, dtype, N + K + M, bias=True)
+    mod._ensure_packed()
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(M)).to(dtype)
+    rows = np.arange(0, N, max(1, N // 256))
+    want = orc.linear_forward(x, orc.dequant_kgrouped(codes[rows], lut_k[:, rows], 128), bias=b[rows])
+    got = L.gemv_kgrouped(x.cuda(), mod._packed, mod.lut_k, N, 4, bias=mod.bias.data)
+    assert rel_err(got[:, rows], want) <= TOL
+    again = L.gemv_kgrouped(x.cuda(), mod._packed, mod.lut_k, N, 4, bias=mod.bias.data)
+    assert torch.equal(got, again)
+    other = L.gemv_kgrouped(x.cuda(), mod._packed, mod.lut_k, N, 4, bias=mod.bias.data, split=2 if K >= 256 else 1)
+    assert rel_err(got, other) <= 4e-3
+    torch.cuda.synchronize()
+    assert L.lib().b200lut_device_status() == 0
