@@ -431,24 +431,28 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
                 for (int j = 0; j < 16; ++j) buf[4096 + 256 * j + tid] = v[j];
               }
             }
-            auto emit = [&](int k, float val) {
-              float r = val * rot_signs[k];
+            // value j of this thread is element 256 j + tid of the segment (and of its upper half):
+            // its place in the staged rows moves by 512 bytes per j, its sign by 256 floats
+            const int k0 = off + tid;
+            uint8_t* dst0 = xs + (size_t(m) * kc + (k0 >> 6)) * 128 + (((k0 & 63) & 15) >> 2) * 32 +
+                            ((k0 & 63) >> 4) * 8 + (k0 & 3) * 2;
+            auto emit = [&](int j, int half, float val) {
+              const int k = k0 + 4096 * half + 256 * j;
+              float r = val * __ldg(rot_signs + k);
               r = r * inv;
-              if (awq_scale) r = __fdiv_rn(r, awq_scale[k]);
-              const int g = k >> 6, w64 = k & 63;
-              *reinterpret_cast<uint16_t*>(xs + (size_t(m) * kc + g) * 128 + ((w64 & 15) >> 2) * 32 +
-                                           (w64 >> 4) * 8 + (w64 & 3) * 2) = DType<T>::from_float(r);
+              if (awq_scale) r = __fdiv_rn(r, __ldg(awq_scale + k));
+              *reinterpret_cast<uint16_t*>(dst0 + size_t(half) * (64 * 128) + size_t(j) * 512) = DType<T>::from_float(r);
             };
             if (halves == 2) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const float a = buf[4096 + 256 * j + tid], b = v[j];
-                emit(off + 256 * j + tid, a + b);
-                emit(off + 4096 + 256 * j + tid, a - b);
+                emit(j, 0, a + b);
+                emit(j, 1, a - b);
               }
             } else {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) emit(off + 256 * j + tid, v[j]);
+              for (int j = 0; j < 16; ++j) emit(j, 0, v[j]);
             }
             continue;
           }
