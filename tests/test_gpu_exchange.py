@@ -34,9 +34,9 @@ def _emulated_step(stacks, M, x):
     return plans
 
 
-@pytest.mark.parametrize("M", (1, 5))
-def test_emulated_two_rank_push_equals_manual_gather(M):
-    world, layers = 2, 2
+@pytest.mark.parametrize("M,world", ((1, 2), (5, 2), (1, 8), (3, 4)))
+def test_emulated_ranks_push_equals_manual_gather(M, world):
+    layers = 2
     arenas = exchange.PeerArena.emulated(1 << 20, world, "cuda")
     pushed = [stack_mod.LinearStack(n_layers=layers, rank=r, world=world, gather="push",
                                     arenas=arenas[r]) for r in range(world)]
