@@ -205,8 +205,11 @@ def cpu_sample(pkg, stack, M: int, gpu_check: bool, threads: int, timed: bool = 
         act = orc.silu_mul_fused(xf @ wg.t(), xf @ wu.t(), x.dtype)
         n_loc = act.shape[1]
         down_in = act
+        # with a flag-less exchange the consumer refills the rows after use: the multi-GPU gate
+        # left its own assembly of them (an NCCL all-gather of the ranks' slices) in the plan
+        assembled = plan.get("assembled")
         if stack.world > 1 and gpu_check:      # the full row as the exchange assembled it
-            down_in = plan["buffers"][4 * li + 2].cpu()
+            down_in = (assembled[li] if assembled else plan["buffers"][4 * li + 2]).cpu()
         y = orc.linear_forward(down_in, wd)
         per_kind[L.kind] = time.perf_counter() - t0
         if not timed:
@@ -226,7 +229,7 @@ def cpu_sample(pkg, stack, M: int, gpu_check: bool, threads: int, timed: bool = 
         if gpu_check:
             bufs = plan["buffers"][4 * li:4 * li + 4]
             want_heads = torch.cat(ys[:-1], dim=1)
-            act_gpu = bufs[2][:, stack.rank * n_loc:(stack.rank + 1) * n_loc]
+            act_gpu = (assembled[li] if assembled else bufs[2])[:, stack.rank * n_loc:(stack.rank + 1) * n_loc]
             for got, want in ((bufs[0], want_heads), (bufs[1], ys[-1]), (act_gpu, act), (bufs[3], y)):
                 worst = max(worst, orc.max_rel_err(got.cpu().float(), want.float()))
     n_lin = sum(1 for L in stack.layers if L.kind == "linear")
@@ -248,18 +251,48 @@ def check_input(stack, M: int):
 def exchange_equals_gather(stack, M: int, world: int) -> bool:
     """Multi-GPU gate: after a step, every layer's assembled activation row (filled by the peers'
     stores, or by the NCCL gather) must equal, bit for bit, an NCCL all-gather of the ranks' own
-    slices taken now. True only if it holds on every rank."""
+    slices taken now — or, when the exchange consumes the rows (no flags), what the step computed
+    from them must equal what it computes from such a gather. True only if it holds on every rank."""
     import torch
     import torch.distributed as dist
+    L = importlib.import_module(PKG)._lib
     plan = stack._plan(M)
     ok = True
-    for li in range(len(stack.layers)):
-        act = plan["buffers"][4 * li + 2]
-        n = act.shape[1] // world
-        mine = act[:, stack.rank * n:(stack.rank + 1) * n].contiguous()
-        parts = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(parts, mine)
-        ok = ok and bool(torch.equal(torch.cat(parts, dim=1), act))
+    if plan.get("sentinel"):
+        # Flag-less exchange: the consumer has refilled the rows it consumed, so the check runs on
+        # what they produced. Per layer: this rank's slice again (the gate/up launch without the
+        # exchange), an NCCL all-gather of the slices, the down launch on the gathered rows without
+        # the exchange: its output must equal, bit for bit, what the step left behind. The rows
+        # are then marked "not arrived" again for the steps that follow.
+        launches = plan["launches"]
+        plan["assembled"] = {}
+        for li in range(len(stack.layers)):
+            _, xin, segs, nseg, epi, _, _, _ = launches[4 * li + 2]
+            _, _, dsegs, dn, depi, _, _, _ = launches[4 * li + 3]
+            act, y = plan["buffers"][4 * li + 2], plan["buffers"][4 * li + 3]
+            y_step = y.clone()
+            L.gemv_multi(xin, segs, nseg, epilogue=epi)
+            n = act.shape[1] // world
+            mine = act[:, stack.rank * n:(stack.rank + 1) * n].contiguous()
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine)
+            full = torch.cat(parts, dim=1)
+            L.gemv_multi(full, dsegs, dn, epilogue=depi)
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(y, y_step))
+            plan["assembled"][li] = full
+            act.view(torch.int16).fill_(-1)
+        torch.cuda.synchronize()
+        dist.barrier()
+    else:
+        for li in range(len(stack.layers)):
+            act = plan["buffers"][4 * li + 2]
+            n = act.shape[1] // world
+            mine = act[:, stack.rank * n:(stack.rank + 1) * n].contiguous()
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine)
+            ok = ok and bool(torch.equal(torch.cat(parts, dim=1), act))
+    act = plan["buffers"][2]
     flag = torch.tensor([1 if ok else 0], device=act.device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     return bool(flag.item())

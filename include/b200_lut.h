@@ -269,6 +269,17 @@ typedef struct b200lut_exchange {
   const void* flags;      /* the local flag array, zero before first use (wait) */
   void* wait_ticket;      /* local u32, zero before first use (wait) */
   void* wait_count;       /* local u32, zero before first use: waits done (wait) */
+  int sentinel;           /* nonzero on BOTH launches of a channel: no flags and no system-wide fence.
+                             The exchanged rows themselves say what has arrived: the buffer starts
+                             filled with 0xFFFF (a pattern no finite value and no converted NaN
+                             has), every rank's producer stores its elements into it with plain
+                             16-bit stores, the waiting launch polls each 16-byte piece it stages
+                             until none of its elements is 0xFFFF (bounded by wait_ms), and its
+                             last block refills the rows with 0xFFFF when every block has staged
+                             them. Served by the row-range kernel only (4-bit single-stream
+                             segments, M <= 8 and rows that fit its shared memory); other launches
+                             return B200LUT_ERR_UNSUPPORTED. */
+  int reserved;
 } b200lut_exchange;
 
 /* Blocks of the launch that b200lut_gemv_multi / b200lut_gemv_exchange would make for these

@@ -72,6 +72,7 @@ class Exchange(ctypes.Structure):
         ("peer_delta", ctypes.c_int64 * MAX_PEERS), ("peer_flag", ctypes.c_void_p * MAX_PEERS),
         ("ticket", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("flags", ctypes.c_void_p),
         ("wait_ticket", ctypes.c_void_p), ("wait_count", ctypes.c_void_p),
+        ("sentinel", ctypes.c_int), ("reserved", ctypes.c_int),
     ]
 
 

@@ -78,6 +78,7 @@ struct ExchangeDev {
   uint32_t* wait_count;
   int* status;          // device status word of the library (set when a wait runs out)
   long long wait_cycles;   // bound of the flag wait in SM clock cycles
+  int sentinel, pad;    // no flags: the waiting launch polls its rows for 0xFFFF (see gemv_rows.cuh)
 };
 
 struct GemvParams {
@@ -1022,6 +1023,8 @@ int convert_exchange(const b200lut_exchange* ex, ExchangeDev* out) {
                     "exchange: wait_ms must be 0 (default) or 1..1000, got %d", ex->wait_ms);
     out->wait_cycles = ex->wait_ms ? (long long)ex->wait_ms * 2000000ll : kPeerWaitCycles;
   }
+  out->sentinel = ex->sentinel ? 1 : 0;
+  if (!out->wait_cycles) out->wait_cycles = kPeerWaitCycles;
   int rc = B200LUT_OK;
   out->status = b200lut::device_status_addr(&rc);
   if (rc) return rc;
@@ -1117,6 +1120,9 @@ extern "C" int b200lut_gemv_input(const void* x, int64_t ldx, int M, int K, int 
   B200LUT_REQUIRE(!transformed, B200LUT_ERR_UNSUPPORTED,
                   "an input transform needs 4-bit single-stream segments and M <= 8 (the row-range "
                   "kernel); transform the rows with b200lut_fht / b200lut_silu_mul first");
+  B200LUT_REQUIRE(!p.ex.sentinel, B200LUT_ERR_UNSUPPORTED,
+                  "an exchange without flags (sentinel) is served by the row-range kernel only: 4-bit "
+                  "single-stream segments, M <= 8, split = 0 and rows that fit its shared memory");
   const int warps = M <= 8 ? kWarpsM8 : kWarpsM16;
   if (split <= 0) split = pick_split(tiles, p.G, sm_count_cached(), warps);
   B200LUT_REQUIRE(split >= 1 && split <= 16 && split <= p.G, B200LUT_ERR_INVALID,

@@ -108,6 +108,42 @@ __device__ __forceinline__ uint4 silu_mul8(uint4 g, uint4 u) {
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// Exchange without flags ("the data is its own flag"): the rows a waiting launch stages live in a
+// buffer that its last block refills with 0xFFFF after use (no finite bf16 / f16 value, nor the
+// NaN a conversion produces, has that pattern), and the producers on every rank store their
+// elements into it with plain 2-byte stores, which are atomic. A 16-byte piece is therefore
+// complete exactly when none of its eight elements is 0xFFFF: the waiting launch polls the piece
+// itself (bounded; on expiry status 0x7000 + the rank that owns the missing column, and the launch
+// carries on). The producer needs no system-wide fence and no flag stores.
+__device__ __forceinline__ bool has_sentinel(const uint4& v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  bool any = false;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) any = any || (w[i] & 0xFFFFu) == 0xFFFFu || (w[i] >> 16) == 0xFFFFu;
+  return any;
+}
+__device__ __forceinline__ uint4 load_rows_piece(const RowsParams& p, const uint16_t* ptr, int col) {
+  uint4 v = __ldcg(reinterpret_cast<const uint4*>(ptr));
+  if (p.ex.wait && p.ex.sentinel && has_sentinel(v)) {
+    const long long t0 = clock64();
+    for (uint32_t i = 1;; ++i) {
+      asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                   : "l"(ptr)
+                   : "memory");
+      if (!has_sentinel(v)) break;
+      if ((i & 15u) == 0u) {
+        if (*reinterpret_cast<volatile int*>(p.ex.status) != 0) break;
+        if (clock64() - t0 > p.ex.wait_cycles) {
+          atomicExch(p.ex.status, 0x7000 + col / (p.K / p.ex.world));
+          break;
+        }
+      }
+    }
+  }
+  return v;
+}
+
 // 4096-point Hadamard butterfly (no scaling) by 256 threads, 16 values per thread, the stages
 // in the order len = 1, 2, 4, ... 2048 — the order of b200lut_fht, so every value goes through
 // the same additions and subtractions and has the same bits. Stages 0-3, 4-7 and 8-11 each run
@@ -380,7 +416,9 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
       }
     }
     // the dependency: the previous kernel of the stream, or the peers' pushes
-    if (p.ex.wait) {
+    if (p.ex.wait && p.ex.sentinel) {
+      // nothing to wait for up front: every staged piece is polled until it is complete
+    } else if (p.ex.wait) {
       for (int i = tid; i < p.ex.world * p.ex.blocks; i += NTS) peer_poll(p.ex, i);
       asm volatile("bar.sync 1, %0;" ::"n"(NTS) : "memory");
     } else {
@@ -414,7 +452,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
                 const size_t at = size_t(m) * p.ldx + size_t(off + i0);
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
-                  raw[c] = __ldcg(reinterpret_cast<const uint4*>(p.x + at + 8 * c));
+                  raw[c] = load_rows_piece(p, p.x + at + 8 * c, off + i0 + 8 * c);
                   if (p.x2) raw[c] = silu_mul8<T>(raw[c], __ldcg(reinterpret_cast<const uint4*>(p.x2 + at + 8 * c)));
                 }
               }
@@ -460,7 +498,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (m < M) {
               const size_t at = size_t(m) * p.ldx + size_t(off + i);
-              v = __ldcg(reinterpret_cast<const uint4*>(p.x + at));
+              v = load_rows_piece(p, p.x + at, off + i);
               if (p.x2) v = silu_mul8<T>(v, __ldcg(reinterpret_cast<const uint4*>(p.x2 + at)));
             }
             const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
@@ -513,7 +551,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (m < M) {
           const size_t off = size_t(m) * p.ldx + size_t(c0) * kChunkK + size_t(pc) * 8;
-          v = __ldcg(reinterpret_cast<const uint4*>(p.x + off));
+          v = load_rows_piece(p, p.x + off, c0 * kChunkK + pc * 8);
           if (p.x2) v = silu_mul8<T>(v, __ldcg(reinterpret_cast<const uint4*>(p.x2 + off)));
         }
         const int g = pc >> 3, o = pc & 7, kt = o >> 1, tg = (o & 1) * 2;
@@ -656,15 +694,30 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
 
   if (p.ex.wait) {
     __syncthreads();
+    // the fold buffer is free by now: its first word tells the block whether it is the last one
+    volatile int& last_block = *reinterpret_cast<volatile int*>(generic(p.red_abs));
     if (threadIdx.x == 0) {
       const uint32_t old = atomicAdd(p.ex.wait_ticket, 1u);
-      if (old == gridDim.x - 1) {
+      last_block = old == gridDim.x - 1 ? 1 : 0;
+      if (last_block) {
         *reinterpret_cast<volatile uint32_t*>(p.ex.wait_ticket) = 0u;
         *reinterpret_cast<volatile uint32_t*>(p.ex.wait_count) += 1u;
       }
     }
+    if (p.ex.sentinel) {
+      // every block has staged its rows: the last one marks them as not yet arrived again
+      __syncthreads();
+      if (last_block) {
+        const uint4 ones = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+        uint16_t* rows = const_cast<uint16_t*>(p.x);
+        for (int idx = threadIdx.x; idx < M * (p.K / 8); idx += NT) {
+          const int m = idx / (p.K / 8), pc = idx - m * (p.K / 8);
+          *reinterpret_cast<uint4*>(rows + size_t(m) * p.ldx + size_t(pc) * 8) = ones;
+        }
+      }
+    }
   }
-  if (p.ex.push) {
+  if (p.ex.push && !p.ex.sentinel) {
     // one system-wide fence per block, then this block's flag in every rank's flag array
     __syncthreads();
     if (threadIdx.x == 0) {

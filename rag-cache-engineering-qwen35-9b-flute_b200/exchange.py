@@ -44,6 +44,8 @@ class PeerArena:
                 self._opened.append(b)
                 self.base.append(b + off)
         self._cursor = 0
+        self.emulated = False
+        self._group = group
         dist.barrier(group=group)      # every rank has zeroed and mapped before anyone pushes
 
     @classmethod
@@ -57,6 +59,7 @@ class PeerArena:
             a = cls.__new__(cls)
             a.rank, a.world, a.nbytes, a.buf = r, world, nbytes, bufs[r]
             a._opened, a._cursor = [], 0
+            a.emulated, a._group = True, None
             a.base = [b.data_ptr() for b in bufs]
             arenas.append(a)
         return arenas
@@ -77,6 +80,16 @@ class PeerArena:
         nbytes = n * torch.empty((), dtype=dtype).element_size()
         return self.buf[off:off + nbytes].view(dtype).view(*shape)
 
+    def ready(self, device) -> None:
+        """After channels have been carved and pre-filled: every rank's fills have landed before
+        any rank pushes (nothing to do for arenas emulated on one device, whose launches are
+        issued in order)."""
+        if self.emulated:
+            return
+        import torch.distributed as dist
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self._group)
+
     def close(self) -> None:
         for b in self._opened:
             _lib.peer_close(b)
@@ -86,9 +99,11 @@ class PeerArena:
 class Channel:
     """One exchanged activation buffer [M, width] with its flag array and counters. `blocks` is
     the block count of the producing launch (`_lib.gemv_launch_blocks` of its segments): every
-    block of it owns one flag."""
+    block of it owns one flag. sentinel=True: no flags — the buffer starts filled with 0xFFFF, the
+    consumer polls the rows themselves and refills them after use (row-range kernel only; the
+    caller synchronises the ranks once after building its channels, before the first push)."""
 
-    def __init__(self, arena: PeerArena, M: int, width: int, dtype, blocks: int):
+    def __init__(self, arena: PeerArena, M: int, width: int, dtype, blocks: int, sentinel: bool = False):
         self.arena = arena
         self.blocks = int(blocks)
         self.act_off = arena.alloc(M * width * 2)
@@ -96,6 +111,9 @@ class Channel:
         # local counters: push ticket +0, push count +32, wait ticket +64, wait count +96
         self.ctl_off = arena.alloc(_ALIGN)
         self.act = arena.view(self.act_off, (M, width), dtype)
+        self.sentinel = bool(sentinel)
+        if self.sentinel:
+            arena.buf[self.act_off:self.act_off + M * width * 2].fill_(0xFF)
         a = arena
         me = a.base[a.rank]
         push = _lib.Exchange()
@@ -112,4 +130,5 @@ class Channel:
         wait.flags = me + self.flag_off
         wait.wait_ticket = me + self.ctl_off + 64
         wait.wait_count = me + self.ctl_off + 96
+        push.sentinel = wait.sentinel = 1 if self.sentinel else 0
         self.push, self.wait = push, wait

@@ -23,6 +23,7 @@ into every rank's buffer over NVLink, the down launch waits for the flags).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import torch
@@ -184,6 +185,7 @@ class LinearStack(nn.Module):
         launches = []
         outs = []
         push = self.gather_mode == "push" and M <= 16
+        sentinel = push and M <= 4 and os.environ.get("B200LUT_EXCHANGE", "").strip() != "flags"
         arena = None
         if push:
             width = self.layers[0].mlp.gate_proj.N * self.world
@@ -228,8 +230,11 @@ class LinearStack(nn.Module):
             chan = None
             if push:
                 probe = _lib.make_segments([g._segment_desc(None), u._segment_desc(None)])
+                # up to four rows both launches run the row-range kernel, which can take the rows
+                # themselves as the arrival signal (no flags, no system-wide fence on the producer)
                 chan = exchange.Channel(arena, M, g.N * self.world, dt,
-                                        _lib.gemv_launch_blocks(M, g.K, probe, 2, _lib.EPI_SILU_MUL))
+                                        _lib.gemv_launch_blocks(M, g.K, probe, 2, _lib.EPI_SILU_MUL),
+                                        sentinel=sentinel)
             act = chan.act if push else torch.empty(M, g.N * self.world, dtype=dt, device=dev)
             act_loc = act[:, self.rank * g.N:(self.rank + 1) * g.N]   # full width after gather
             gd = [g._segment_desc(act_loc, ldo=act.shape[1]), u._segment_desc(None)]
@@ -246,7 +251,10 @@ class LinearStack(nn.Module):
             launches.append(("down", xr, _lib.make_segments(dd), 1, _lib.EPI_NONE, dd,
                              chan.wait if push else None, inp))
             outs += [hbuf, obuf, act, ybuf]
+        if push and sentinel:
+            arena.ready(dev)
         plan = {"x": x, "launches": launches, "buffers": outs, "y": outs[-1], "arena": arena,
+                "sentinel": bool(push and sentinel),
                 "rotated": outs_rot}
         self._plans[M] = plan
         return plan

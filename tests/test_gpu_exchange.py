@@ -64,8 +64,13 @@ def test_emulated_ranks_push_equals_manual_gather(M, world):
                 s.run_launch(e, M)
         torch.cuda.synchronize()
         for r in range(world):
-            for got, want in zip(plans[r]["buffers"], mplans[r]["buffers"]):
-                assert torch.equal(got, want), f"rank {r}, repetition {rep}"
+            for i, (got, want) in enumerate(zip(plans[r]["buffers"], mplans[r]["buffers"])):
+                if plans[r]["sentinel"] and i % 4 == 2:
+                    # a flag-less exchange consumes the rows: the consumer has marked them "not
+                    # arrived" again; what it computed from them is the next buffer
+                    assert bool((got.view(torch.int16) == -1).all())
+                    continue
+                assert torch.equal(got, want), f"rank {r}, repetition {rep}, buffer {i}"
 
     full = stack_mod.LinearStack(n_layers=layers)
     fp = full._plan(M)
@@ -82,12 +87,12 @@ def test_push_needs_two_layers():
         stack_mod.LinearStack(n_layers=1, rank=0, world=2, gather="push")
 
 
-def _two_gpu_worker(rank, world, port, ok):
+def _two_gpu_worker(rank, world, port, ok, M):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-    M, layers = 1, 3
+    layers = 3
     a = stack_mod.LinearStack(device=f"cuda:{rank}", n_layers=layers, rank=rank, world=world, gather="push")
     b = stack_mod.LinearStack(device=f"cuda:{rank}", n_layers=layers, rank=rank, world=world, gather="nccl")
     x = torch.randn(M, stack_mod.HIDDEN, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
@@ -103,7 +108,12 @@ def _two_gpu_worker(rank, world, port, ok):
         ya = a.step(M, flags=pkg._lib.FLAG_PDL)
         yb = b.step(M, gather=gather)
         torch.cuda.synchronize()
-        same = same and all(torch.equal(p, q) for p, q in zip(a._plan(M)["buffers"], b._plan(M)["buffers"]))
+        consumed = a._plan(M)["sentinel"]      # a flag-less exchange refills the rows it has consumed
+        for i, (p, q) in enumerate(zip(a._plan(M)["buffers"], b._plan(M)["buffers"])):
+            if consumed and i % 4 == 2:
+                same = same and bool((p.view(torch.int16) == -1).all())
+            else:
+                same = same and torch.equal(p, q)
         same = same and torch.equal(ya, yb)
     same = same and pkg._lib.lib().b200lut_device_status() == 0
     dist.barrier()
@@ -113,11 +123,12 @@ def _two_gpu_worker(rank, world, port, ok):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs of one box")
-def test_two_gpu_push_equals_nccl_gather():
+@pytest.mark.parametrize("M", (1, 6))      # without flags (the rows are their own signal), with flags
+def test_two_gpu_push_equals_nccl_gather(M):
     import torch.multiprocessing as mp
     world = 2
     ok = mp.get_context("spawn").Array("i", [0] * world)
-    mp.spawn(_two_gpu_worker, args=(world, 29531, ok), nprocs=world, join=True)
+    mp.spawn(_two_gpu_worker, args=(world, 29531 + M, ok, M), nprocs=world, join=True)
     assert list(ok) == [1] * world
 
 
@@ -141,6 +152,26 @@ def test_a_wait_that_runs_out_returns_reports_the_rank_and_the_channel_recovers(
     chans = [exchange.Channel(arenas[r], M, 256, dt, blocks) for r in range(world)]
     out = torch.zeros(M, cons.N, dtype=dt, device="cuda")
     csegs = L.make_segments([cmod._segment_desc(out)])
+
+    # the same without flags: the rows start as 0xFFFF and nothing replaces them
+    sarenas = exchange.PeerArena.emulated(1 << 16, world, "cuda")
+    schans = [exchange.Channel(sarenas[r], M, 256, dt, blocks, sentinel=True) for r in range(world)]
+    schans[0].wait.wait_ms = 1
+    L.gemv_exchange(schans[0].act, csegs, 1, schans[0].wait)
+    torch.cuda.synchronize()
+    status = L.lib().b200lut_device_status()
+    assert status in (0x7000, 0x7001), hex(status)
+    assert bool((schans[0].act.view(torch.int16) == -1).all())   # refilled (it never changed) for the next round
+    for rep in range(2):
+        for r in range(world):
+            dst = schans[r].act[:, r * 128:(r + 1) * 128]
+            L.gemv_exchange(x, L.make_segments([pmods[r]._segment_desc(dst, ldo=256)]), 1, schans[r].push)
+        L.gemv_exchange(schans[0].act, csegs, 1, schans[0].wait)
+        L.gemv_exchange(schans[1].act, csegs, 1, schans[1].wait)
+        torch.cuda.synchronize()
+        assert L.lib().b200lut_device_status() == 0
+        assert torch.equal(out, cmod(torch.cat([m(x) for m in pmods], dim=1)))
+        assert bool((schans[0].act.view(torch.int16) == -1).all())   # the consumer's last block refilled the rows
 
     chans[0].wait.wait_ms = 1
     L.gemv_exchange(chans[0].act, csegs, 1, chans[0].wait)      # no producer has run
