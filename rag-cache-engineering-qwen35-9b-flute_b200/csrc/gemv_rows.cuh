@@ -30,6 +30,11 @@
 //
 // The pair table sits at a fixed offset of the block's shared window (kRowsTableAbs), so a lookup
 // address is the byte permute plus an immediate offset in the load; no 64 KB alignment is needed.
+//
+// What the staging half can do on the way (b200lut_input / b200lut_exchange): multiply the rows
+// into silu(x) * x_mul, rotate them (one fold for the launch, or one per segment — the blocks are
+// then dealt to the segments so that none crosses one), wait for the peers of a column-parallel
+// exchange (flags, or the rows themselves as the arrival signal).
 #pragma once
 
 namespace b200lut {
