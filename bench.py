@@ -885,9 +885,11 @@ def run_case(args) -> int:
                           "GB/s": gbs, "us_per_launch": us, "frac_of_hbm": gbs / peaks["hbm_gbs"]}))
     else:
         pairs = args.case == "gemm_pairs"
-        tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, max(args.steps, 1), False,
+        rank = 32 if args.case == "gemm_res" else 0
+        tf, us = prefill_gemm_tflops(pkg, 2048, 12288, 4096, max(args.steps, 1), False, rank=rank,
                                      flags=pkg._lib.FLAG_CTA_PAIRS if pairs else 0)
-        print(json.dumps({"case": "gemm M=2048 K=4096 N=12288" + (", CTA pairs (cta_group::2)" if pairs else ""),
+        print(json.dumps({"case": "gemm M=2048 K=4096 N=12288" + (", CTA pairs (cta_group::2)" if pairs else "")
+                          + (", rank-32 residual (projection launch + residual k-blocks)" if rank else ""),
                           "TFLOP/s": tf, "us": us, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}))
     return 0
 
@@ -907,9 +909,9 @@ def main() -> int:
                     help="N > 1: how the sharded MLP activation is recombined (push: peer stores "
                          "from the GEMV epilogue; nccl: an all-gather call between the launches)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a graph replay")
-    ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemv_head", "gemm", "gemm_pairs", "embed", "kgrouped"),
-                    help="stack: the benchmark; gemv / gemv_head / gemm / gemm_pairs / embed / kgrouped: a few "
-                         "launches of one kernel on a profiling-sized case")
+    ap.add_argument("--case", default="stack", choices=("stack", "gemv", "gemv_head", "gemm", "gemm_pairs", "gemm_res", "embed", "kgrouped"),
+                    help="stack: the benchmark; gemv / gemv_head / gemm / gemm_pairs / gemm_res / embed / "
+                         "kgrouped: a few launches of one kernel on a profiling-sized case")
     ap.add_argument("--executor", default="graph", choices=("plan", "graph"),
                     help="plan: persistent cooperative launch(es) per step; graph: one kernel per "
                          "projection group under CUDA-graph replay")
