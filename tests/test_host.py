@@ -94,6 +94,20 @@ def test_validation_errors_carry_a_message():
     inp.seg_awq_scale[0] = x                                 # a scale without signs
     rc = L.b200lut_gemv_input(x, 64, 1, 64, 0, ctypes.byref(seg), 1, 0, 0, None, 0, 0, None, ctypes.byref(inp), None)
     assert rc == 1 and b"segment 0" in L.b200lut_last_error()
+    # K-grouped tensor-core form: one palette per 128 input columns
+    L.b200lut_gemm_kgrouped.restype = ctypes.c_int
+    rc = L.b200lut_gemm_kgrouped(x, 64, 32, 64, 0, x, x, None, 128, 4, x, 128, 0, None, 0, None)
+    assert rc == 1 and b"multiple of 128" in L.b200lut_last_error()
+    rc = L.b200lut_gemm_kgrouped(x, 128, 32, 128, 0, x, x, None, 128, 5, x, 128, 0, None, 0, None)
+    assert rc == 1 and b"code width" in L.b200lut_last_error()
+    rc = L.b200lut_gemm_kgrouped(x, 128, 32, 128, 0, x, None, None, 128, 4, x, 128, 0, None, 0, None)
+    assert rc == 1 and b"null" in L.b200lut_last_error()
+    # an exchange's wait bound is 0 (default) or 1..1000 ms
+    ex = pkg._lib.Exchange()
+    ex.world, ex.rank, ex.wait, ex.producer_blocks, ex.wait_ms = 2, 0, 1, 4, 5000
+    ex.flags = ex.wait_ticket = ex.wait_count = x
+    rc = L.b200lut_gemv_exchange(x, 64, 1, 64, 0, ctypes.byref(seg), 1, 0, 0, None, 0, 0, ctypes.byref(ex), None)
+    assert rc == 1 and b"wait_ms" in L.b200lut_last_error()
     rc = L.b200lut_gemm_multi(x, 64, 32, 128, 0, ctypes.byref(seg), 5, 0, None, 0, None)
     assert rc == 2 and b"nseg" in L.b200lut_last_error()
     rc = L.b200lut_gemm_multi(x, 64, 32, 64, 0, ctypes.byref(seg), 1, 0, None, 0, None)
