@@ -473,7 +473,7 @@ def _per_segment_folds(mods, M: int) -> bool:
 
 
 def _mergeable(mods, x: torch.Tensor, per_segment: bool = False) -> bool:
-    """Decode-merge verdict: M <= 16, same K, one dtype, unrotated or one shared rotation (or,
+    """Decode-merge decision: M <= 16, same K, one dtype, unrotated or one shared rotation (or,
     with per_segment, folds the launch can apply per segment), and every low-rank residual of
     a kind the GEMV epilogue serves."""
     x2 = x.reshape(-1, x.shape[-1])
@@ -499,7 +499,7 @@ def _mergeable(mods, x: torch.Tensor, per_segment: bool = False) -> bool:
 
 
 def _prefill_mergeable(mods, x: torch.Tensor) -> bool:
-    """Prefill-merge verdict (M > 16): projections that share x run as ONE tensor-core launch
+    """Prefill-merge decision (M > 16): projections that share x run as ONE tensor-core launch
     when they have one code stream each, one code width, one group size >= 64, one dtype, only
     low-rank residuals the launch can carry, and are unrotated or share one rotation."""
     x2 = x.reshape(-1, x.shape[-1])
