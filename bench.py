@@ -1036,8 +1036,9 @@ def main() -> int:
                        "; the other sharded outputs (heads, out, down) have no full-K consumer in the "
                        "stack and stay sharded, so the result read back is this rank's 1/N of y"),
                    "l2": "inputs (3.46 GB of codes per step) exceed the 126 MB L2",
-                   "launch": ("persistent cooperative launch per step (jobs chained by completion counters), "
-                              "CUDA graph replay" if use_plan else
+                   "launch": ("persistent cooperative launch per step (jobs chained by completion counters; "
+                              + "/".join(sorted({p.form for k, p in stack.decode_plans(M) if k == "plan"}))
+                              + " form), CUDA graph replay" if use_plan else
                               "one kernel per projection group, CUDA graph replay"
                               + (", programmatic dependent launch" if args.pdl else ""))},
         "e2e": {"value": M * 1e3 / (ms_e2e / args.steps), "unit": "tok/s",

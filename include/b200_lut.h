@@ -368,6 +368,10 @@ int b200lut_plan_build(void* plan, size_t plan_bytes, const b200lut_job* jobs, i
                        int dtype, void* stream);
 int b200lut_plan_run(void* plan, int M, int dtype, void* stream);
 int b200lut_plan_status(const void* plan);
+/* Which kernel a built plan runs: 1 = the row-range block body, job after job (every job
+ * 4-bit, single-stream, M <= 8, one block per SM at most); 0 = the tile-share kernel (any other
+ * mix, or B200LUT_PLAN_KERNEL=tile in the environment); negative = not a plan buffer. */
+int b200lut_plan_form(const void* plan);
 
 /* ------------------------------------------------------------------------- *
  * Prefill GEMM (M > 16), tcgen05 / TMEM

@@ -34,7 +34,7 @@ EXPORTS = (
     "b200lut_gemm_two_stream", "b200lut_gemm_two_stream_bytes",
     "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_kgrouped",
     "b200lut_gemv_kgrouped_split", "b200lut_gemv_kgrouped_workspace_bytes", "b200lut_gemm_kgrouped", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
-    "b200lut_gemv_noalloc", "b200lut_gemv_noalloc_reset", "b200lut_gemv_launch_blocks", "b200lut_gemv_input", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status",
+    "b200lut_gemv_noalloc", "b200lut_gemv_noalloc_reset", "b200lut_gemv_launch_blocks", "b200lut_gemv_input", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status", "b200lut_plan_form",
 )
 
 
@@ -183,6 +183,8 @@ def lib() -> ctypes.CDLL:
     L.b200lut_plan_run.argtypes = [vp, i32, i32, vp]
     L.b200lut_plan_status.restype = i32
     L.b200lut_plan_status.argtypes = [vp]
+    L.b200lut_plan_form.restype = i32
+    L.b200lut_plan_form.argtypes = [vp]
     _lib = L
     return L
 
@@ -658,6 +660,8 @@ class DecodePlan:
             check(lib().b200lut_plan_build(self.buffer.data_ptr(), nbytes, arr, len(jobs), self.M, did,
                                            torch.cuda.current_stream(self.device).cuda_stream))
         self.njobs = len(jobs)
+        # "rows": the row-range block body runs job after job; "tiles": the tile-share kernel
+        self.form = "rows" if lib().b200lut_plan_form(self.buffer.data_ptr()) == 1 else "tiles"
 
     def run(self) -> None:
         with torch.cuda.device(self.device):

@@ -31,6 +31,7 @@
 
 #include <cmath>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -814,7 +815,7 @@ bool rows_kernel_wanted(int flags) {
 // The layout of the row-range kernel for a launch, or false when the kernel does not serve it.
 // It depends only on the segment geometry; it is planned once per distinct launch shape (the
 // planner walks every 32-row unit) and looked up afterwards.
-bool rows_geometry(const GemvParams& gp, int tiles, RowsGeom* out) {
+bool rows_geometry(const GemvParams& gp, int tiles, bool may_split, RowsGeom* out) {
   const bool silu = gp.epilogue == B200LUT_EPI_SILU_MUL;
   struct Entry { unsigned long long key; bool ok; RowsGeom g; };
   static Entry cache[64];
@@ -823,7 +824,7 @@ bool rows_geometry(const GemvParams& gp, int tiles, RowsGeom* out) {
   unsigned long long h = 1469598103934665603ull;
   auto mix = [&](unsigned long long v) { h = (h ^ v) * 1099511628211ull; };
   mix(unsigned(gp.nseg)); mix(unsigned(gp.epilogue)); mix(unsigned(gp.M)); mix(unsigned(gp.K));
-  mix(unsigned(tiles)); mix(unsigned(sm_count_cached()));
+  mix(unsigned(tiles)); mix(unsigned(sm_count_cached())); mix(may_split ? 1u : 0u);
   uint32_t fht_bytes = 0;
   if (gp.rot_signs || gp.per_seg) {   // fp32 scratch of the largest power-of-two segment of K
     int b = 1;
@@ -845,19 +846,16 @@ bool rows_geometry(const GemvParams& gp, int tiles, RowsGeom* out) {
     hit = used < 64 ? used++ : int(h % 64);
     cache[hit].key = h;
     cache[hit].ok = rows_plan(gp.seg, gp.nseg, silu, tiles, gp.M, gp.K, sm_count_cached(), fht_bytes,
-                              gp.per_seg, &cache[hit].g);
+                              gp.per_seg, may_split, &cache[hit].g);
   }
   if (cache[hit].ok) *out = cache[hit].g;
   return cache[hit].ok;
 }
 
-// The row-range kernel when it serves the launch (4-bit, one stream, M <= 8).
-template <typename T>
-int try_rows(const GemvParams& gp, const uint16_t* x2, int tiles, bool pdl, cudaStream_t st, bool* served) {
-  *served = false;
-  RowsGeom g;
-  if (!rows_geometry(gp, tiles, &g)) return B200LUT_OK;
-  RowsParams p = {};
+// The kernel parameters of a launch with geometry g.
+int fill_rows_params(const GemvParams& gp, const uint16_t* x2, const RowsGeom& g, RowsParams* out) {
+  RowsParams& p = *out;
+  p = RowsParams{};
   p.x = gp.x;
   p.x2 = x2 ? x2 : gp.x_mul;
   if (gp.rot_signs || gp.per_seg) {
@@ -902,11 +900,23 @@ int try_rows(const GemvParams& gp, const uint16_t* x2, int tiles, bool pdl, cuda
   p.red_abs = g.red_abs;
   p.part_abs = g.part_abs;
   p.meta_abs = g.meta_abs;
+  p.xreg = g.xreg;
   int rc = B200LUT_OK;
   p.status = device_status_addr(&rc);
   if (rc) return rc;
   for (int i = 0; i < gp.nseg; ++i) p.seg[i] = gp.seg[i];
   p.ex = gp.ex;
+  return B200LUT_OK;
+}
+
+// The row-range kernel when it serves the launch (4-bit, one stream, M <= 8).
+template <typename T>
+int try_rows(const GemvParams& gp, const uint16_t* x2, int tiles, bool pdl, cudaStream_t st, bool* served) {
+  *served = false;
+  RowsGeom g;
+  if (!rows_geometry(gp, tiles, true, &g)) return B200LUT_OK;
+  RowsParams p;
+  if (int rc = fill_rows_params(gp, x2, g, &p)) return rc;
   B200LUT_REQUIRE(!p.ex.push || p.ex.blocks == g.row_blocks * g.split, B200LUT_ERR_INVALID,
                   "exchange: producer_blocks is %d but this launch has %d blocks "
                   "(b200lut_gemv_launch_blocks gives the count)", p.ex.blocks, g.row_blocks * g.split);
@@ -1167,7 +1177,7 @@ extern "C" int b200lut_gemv_launch_blocks(int M, int K, const b200lut_segment* s
   if (convert_segments(tmp, nseg, silu, p.seg, &tiles, &max_tables)) return 0;
   if (rows_kernel_wanted(flags)) {
     RowsGeom g;
-    if (rows_geometry(p, tiles, &g)) return g.row_blocks * g.split;
+    if (rows_geometry(p, tiles, true, &g)) return g.row_blocks * g.split;
   }
   return tiles * pick_split(tiles, p.G, sm_count_cached(), M <= 8 ? kWarpsM8 : kWarpsM16);
 }
@@ -1263,6 +1273,113 @@ int plan_layout(const b200lut_job* jobs, int njobs, int M, int dtype, int grid, 
   return B200LUT_OK;
 }
 
+// ---- the row-range form of a plan --------------------------------------------------------------
+// When every job is served by the row-range kernel (4-bit, one stream, M <= 8, rows that fit its
+// shared memory, at most one block per SM) the plan runs gemv_rows_plan_kernel: the same block
+// body as a single launch of that kernel, job after job. B200LUT_PLAN_KERNEL=tile in the
+// environment (read once) keeps the tile-share kernel for every plan.
+struct RowsPlanLayout {
+  RowsPlanHeader hdr;
+  std::vector<uint8_t> jobs;    // njobs slots of kRowsPlanSlot bytes
+};
+
+bool rows_plan_wanted() {
+  static const bool wanted = [] {
+    const char* e = getenv("B200LUT_PLAN_KERNEL");
+    return !(e != nullptr && e[0] == 't');
+  }();
+  return wanted;
+}
+
+// `base`: device address of the plan buffer (null when only the size is asked for). Call after
+// plan_layout has validated the jobs. *served = false: some job needs the tile-share kernel.
+int rows_plan_layout(const b200lut_job* jobs, int njobs, int M, uint8_t* base, RowsPlanLayout* out,
+                     bool* served) {
+  *served = false;
+  if (!rows_plan_wanted() || M > 8) return B200LUT_OK;
+  const int sms = sm_count_cached();
+  RowsPlanHeader& h = out->hdr;
+  h = RowsPlanHeader{};
+  h.magic = kRowsPlanMagic;
+  h.njobs = njobs;
+  long long off = (sizeof(RowsPlanHeader) + 255) & ~255ll;
+  h.jobs_off = off;   off += ((long long)njobs * kRowsPlanSlot + 255) & ~255ll;
+  h.done_off = off;   off += ((long long)njobs * 4 + 255) & ~255ll;
+  h.misc_off = off;   off += 256;
+  h.total_bytes = off;
+  out->jobs.assign(size_t(njobs) * kRowsPlanSlot, uint8_t(0));
+  std::vector<int> blocks(size_t(njobs), 0);
+  int* done = reinterpret_cast<int*>(base + h.done_off);
+  int* misc = reinterpret_cast<int*>(base + h.misc_off);
+  uint32_t max_end = 0;
+  int grid = 1;
+  for (int j = 0; j < njobs; ++j) {
+    const b200lut_job& src = jobs[j];
+    const bool silu = src.epilogue == B200LUT_EPI_SILU_MUL;
+    GemvParams gp = {};
+    gp.x = static_cast<const uint16_t*>(src.x);
+    gp.ldx = src.ldx;
+    gp.M = M;
+    gp.K = src.K;
+    gp.G = src.K / kChunkK;
+    gp.nseg = src.nseg;
+    gp.epilogue = src.epilogue;
+    int tiles = 0, max_tables = 1;
+    if (int rc = convert_segments(src.segs, src.nseg, silu, gp.seg, &tiles, &max_tables)) return rc;
+    gp.tiles_total = tiles;
+    RowsGeom g;
+    if (!rows_geometry(gp, tiles, false, &g) || g.split != 1 || g.row_blocks > sms) return B200LUT_OK;
+    RowsParams p;
+    if (int rc = fill_rows_params(gp, nullptr, g, &p)) return rc;
+    blocks[size_t(j)] = g.row_blocks;
+    if (src.dep >= 0) {
+      p.dep_done = done + src.dep;
+      p.dep_target = blocks[size_t(src.dep)];
+    }
+    p.done = done + j;
+    p.abort_word = misc + 1;
+    memcpy(out->jobs.data() + size_t(j) * kRowsPlanSlot, &p, sizeof(p));
+    if (g.end_abs > max_end) max_end = g.end_abs;
+    if (g.row_blocks > grid) grid = g.row_blocks;
+  }
+  h.grid = grid;
+  h.params_abs = (max_end + 15u) & ~15u;
+  h.smem_bytes = h.params_abs + 2u * kRowsPlanSlot;
+  if (h.smem_bytes > 227u * 1024u) return B200LUT_OK;
+  *served = true;
+  return B200LUT_OK;
+}
+
+// What b200lut_plan_run must know about a row-range plan, kept on the host by the build call
+// (the run call gets the device buffer only).
+struct RowsPlanInfo { const void* plan; int dev, grid; uint32_t smem; };
+std::mutex g_rows_plan_mu;
+RowsPlanInfo g_rows_plans[256];
+int g_rows_plans_used = 0;
+
+void rows_plan_forget(const void* plan, int dev) {
+  for (int i = 0; i < g_rows_plans_used; ++i)
+    if (g_rows_plans[i].plan == plan && g_rows_plans[i].dev == dev)
+      g_rows_plans[i] = g_rows_plans[--g_rows_plans_used];
+}
+
+template <typename T>
+int launch_rows_plan(void* plan, const RowsPlanInfo& info, cudaStream_t stream) {
+  auto kern = gemv_rows_plan_kernel<T>;
+  static bool configured[64] = {false};
+  if (info.dev < 64 && !configured[info.dev]) {
+    B200LUT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured[info.dev] = true;
+  }
+  uint8_t* arg = static_cast<uint8_t*>(plan);
+  void* args[] = {&arg};
+  // cooperative: every block of the grid is resident, so a block that waits for a producer
+  // never holds the SM the producer needs
+  B200LUT_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kern), dim3(unsigned(info.grid)),
+                                              dim3(kRowsThreads), args, info.smem, stream));
+  return B200LUT_OK;
+}
+
 template <typename T, int CP, int NWARPS>
 int launch_plan(void* plan, int grid, cudaStream_t stream) {
   auto kern = gemv_plan_kernel<T, CP, NWARPS>;
@@ -1296,7 +1413,10 @@ int dispatch_plan(void* plan, int M, int grid, cudaStream_t st) {
 extern "C" size_t b200lut_plan_bytes(const b200lut_job* jobs, int njobs, int M, int dtype) {
   PlanLayout lay;
   if (plan_layout(jobs, njobs, M, dtype, sm_count_cached(), &lay) != B200LUT_OK) return 0;
-  return size_t(lay.hdr.total_bytes);
+  RowsPlanLayout rows;
+  bool served = false;
+  if (rows_plan_layout(jobs, njobs, M, nullptr, &rows, &served) != B200LUT_OK) return 0;
+  return served ? size_t(rows.hdr.total_bytes) : size_t(lay.hdr.total_bytes);
 }
 
 extern "C" int b200lut_plan_build(void* plan, size_t plan_bytes, const b200lut_job* jobs, int njobs,
@@ -1304,10 +1424,34 @@ extern "C" int b200lut_plan_build(void* plan, size_t plan_bytes, const b200lut_j
   B200LUT_REQUIRE(plan && aligned16(plan), B200LUT_ERR_ALIGN, "plan buffer must be 16-byte aligned");
   PlanLayout lay;
   if (int rc = plan_layout(jobs, njobs, M, dtype, sm_count_cached(), &lay)) return rc;
-  B200LUT_REQUIRE(plan_bytes >= size_t(lay.hdr.total_bytes), B200LUT_ERR_WORKSPACE,
-                  "plan needs %lld bytes, got %zu", lay.hdr.total_bytes, plan_bytes);
   cudaStream_t st = cudaStream_t(stream);
   uint8_t* base = static_cast<uint8_t*>(plan);
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(g_rows_plan_mu);
+    rows_plan_forget(plan, dev);
+  }
+  RowsPlanLayout rows;
+  bool served = false;
+  if (int rc = rows_plan_layout(jobs, njobs, M, base, &rows, &served)) return rc;
+  if (served) {
+    const RowsPlanHeader& h = rows.hdr;
+    B200LUT_REQUIRE(plan_bytes >= size_t(h.total_bytes), B200LUT_ERR_WORKSPACE,
+                    "plan needs %lld bytes, got %zu", h.total_bytes, plan_bytes);
+    B200LUT_CUDA_OK(cudaMemsetAsync(base, 0, size_t(h.total_bytes), st));
+    B200LUT_CUDA_OK(cudaMemcpyAsync(base, &h, sizeof(h), cudaMemcpyHostToDevice, st));
+    B200LUT_CUDA_OK(cudaMemcpyAsync(base + h.jobs_off, rows.jobs.data(), rows.jobs.size(),
+                                    cudaMemcpyHostToDevice, st));
+    B200LUT_CUDA_OK(cudaStreamSynchronize(st));   // the host staging dies with this call
+    std::lock_guard<std::mutex> lock(g_rows_plan_mu);
+    B200LUT_REQUIRE(g_rows_plans_used < 256, B200LUT_ERR_UNSUPPORTED,
+                    "more than 256 live row-range plans (rebuilding a buffer replaces its entry)");
+    g_rows_plans[g_rows_plans_used++] = RowsPlanInfo{plan, dev, h.grid, h.smem_bytes};
+    return B200LUT_OK;
+  }
+  B200LUT_REQUIRE(plan_bytes >= size_t(lay.hdr.total_bytes), B200LUT_ERR_WORKSPACE,
+                  "plan needs %lld bytes, got %zu", lay.hdr.total_bytes, plan_bytes);
   // counters, tickets and the abort word start at zero; partials need no initial value
   B200LUT_CUDA_OK(cudaMemsetAsync(base, 0, size_t(lay.hdr.ws_off), st));
   B200LUT_CUDA_OK(cudaMemcpyAsync(base, &lay.hdr, sizeof(PlanHeader), cudaMemcpyHostToDevice, st));
@@ -1321,13 +1465,45 @@ extern "C" int b200lut_plan_run(void* plan, int M, int dtype, void* stream) {
   B200LUT_REQUIRE(plan, B200LUT_ERR_INVALID, "null plan");
   B200LUT_REQUIRE(M >= 1 && M <= kMaxM && (dtype == B200LUT_BF16 || dtype == B200LUT_F16),
                   B200LUT_ERR_INVALID, "M and dtype must be those the plan was built with");
+  {
+    int dev = 0;
+    B200LUT_CUDA_OK(cudaGetDevice(&dev));
+    RowsPlanInfo info = {};
+    {
+      std::lock_guard<std::mutex> lock(g_rows_plan_mu);
+      for (int i = 0; i < g_rows_plans_used; ++i)
+        if (g_rows_plans[i].plan == plan && g_rows_plans[i].dev == dev) info = g_rows_plans[i];
+    }
+    if (info.plan) {
+      if (dtype == B200LUT_BF16) return launch_rows_plan<__nv_bfloat16>(plan, info, cudaStream_t(stream));
+      return launch_rows_plan<__half>(plan, info, cudaStream_t(stream));
+    }
+  }
   const int grid = sm_count_cached();
   if (dtype == B200LUT_BF16) return dispatch_plan<__nv_bfloat16>(plan, M, grid, cudaStream_t(stream));
   return dispatch_plan<__half>(plan, M, grid, cudaStream_t(stream));
 }
 
+extern "C" int b200lut_plan_form(const void* plan) {
+  if (!plan) return -1;
+  unsigned long long magic = 0;
+  if (cudaMemcpy(&magic, plan, sizeof(magic), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return magic == kRowsPlanMagic ? 1 : (magic == kPlanMagic ? 0 : -1);
+}
+
 extern "C" int b200lut_plan_status(const void* plan) {
   B200LUT_REQUIRE(plan, B200LUT_ERR_INVALID, "null plan");
+  unsigned long long magic = 0;
+  B200LUT_CUDA_OK(cudaMemcpy(&magic, plan, sizeof(magic), cudaMemcpyDeviceToHost));
+  if (magic == kRowsPlanMagic) {
+    RowsPlanHeader rh;
+    B200LUT_CUDA_OK(cudaMemcpy(&rh, plan, sizeof(rh), cudaMemcpyDeviceToHost));
+    int words[2] = {0, 0};
+    B200LUT_CUDA_OK(cudaMemcpy(words, static_cast<const uint8_t*>(plan) + rh.misc_off, sizeof(words),
+                               cudaMemcpyDeviceToHost));
+    if (words[1] != 0) return fail(B200LUT_ERR_DEVICE, "a dependency wait inside the plan ran out");
+    return B200LUT_OK;
+  }
   PlanHeader h;
   B200LUT_CUDA_OK(cudaMemcpy(&h, plan, sizeof(h), cudaMemcpyDeviceToHost));
   B200LUT_REQUIRE(h.magic == kPlanMagic, B200LUT_ERR_INVALID, "not a plan buffer");

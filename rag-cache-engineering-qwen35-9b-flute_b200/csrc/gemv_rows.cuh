@@ -75,6 +75,14 @@ struct RowsParams {
   int fht_off[kRowsMaxFhtSegs], fht_len[kRowsMaxFhtSegs], fht_stages[kRowsMaxFhtSegs];
   float fht_inv[kRowsMaxFhtSegs];
   int* status;
+  // Inside a persistent plan (gemv_rows_plan_kernel; all null / zero in a plain launch): the
+  // completion counter of the job that produces the activation rows and the value it has when
+  // every block of that job has stored its rows; this job's own counter; the plan's abort word.
+  const int* dep_done;
+  int dep_target;
+  int xreg;                // which instantiation serves the job (see XREG below)
+  int* done;
+  int* abort_word;
   SegDev seg[kMaxSeg];
   ExchangeDev ex;
 };
@@ -278,9 +286,9 @@ __device__ __forceinline__ void rows_item_smem(float (&acc)[2][4], const uint32_
 
 // XREG: the block's K range is exactly kRowsWarps * kRowsRing chunks, so a warp's ring slot j is
 // always its chunk j and the warp keeps the activation fragments of its chunks in registers.
-template <typename T, bool XREG>
-__global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid_constant__ RowsParams p) {
-  extern __shared__ __align__(16) uint8_t smem[];
+// `bid` of `nblk`: the block's place in the launch (its place among the job's blocks inside a plan).
+template <typename T, bool XREG, bool PLAN>
+__device__ __forceinline__ void rows_block(const RowsParams& p, uint8_t* smem, const int bid, const int nblk) {
   constexpr int NW = kRowsWarps, NT = kRowsThreads, R = kRowsRing;
   constexpr uint32_t kFull = 0xffffffffu;
   constexpr unsigned long long kHop = (unsigned long long)(NW) * 4096ull;   // a warp's next chunk
@@ -298,7 +306,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   const int split = p.split;
-  const int rb = blockIdx.x / split, sp = blockIdx.x % split;
+  const int rb = bid / split, sp = bid % split;
   const int c0 = (p.G * sp) / split, c1 = (p.G * (sp + 1)) / split;
   const int kc = c1 - c0;
   const bool silu = p.epilogue == B200LUT_EPI_SILU_MUL;
@@ -421,7 +429,11 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
       }
     }
     // the dependency: the previous kernel of the stream, or the peers' pushes
-    if (p.ex.wait && p.ex.sentinel) {
+    if (PLAN && p.dep_done) {
+      // every block of the producing job has stored its rows and bumped the job's counter
+      if (tid == 0) dep_poll(DepWait{2, p.dep_done, p.dep_target, p.abort_word, nullptr});
+      asm volatile("bar.sync 1, %0;" ::"n"(NTS) : "memory");
+    } else if (p.ex.wait && p.ex.sentinel) {
       // nothing to wait for up front: every staged piece is polled until it is complete
     } else if (p.ex.wait) {
       for (int i = tid; i < p.ex.world * p.ex.blocks; i += NTS) peer_poll(p.ex, i);
@@ -667,7 +679,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
     for (int wi = 0; wi < NW; ++wi) v += part_v[wi];                               // adds in warp order
     return v;
   };
-  if (split == 1) {
+  if (PLAN || split == 1) {   // (a plan never splits K)
     for (int idx = threadIdx.x; idx < total_out; idx += NT) {
       const int row = idx & 31, m = (idx >> 5) % M, ul = (idx >> 5) / M;
       const float a = warp_sum(ul * ppu, m, row);
@@ -703,7 +715,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
     volatile int& last_block = *reinterpret_cast<volatile int*>(generic(p.red_abs));
     if (threadIdx.x == 0) {
       const uint32_t old = atomicAdd(p.ex.wait_ticket, 1u);
-      last_block = old == gridDim.x - 1 ? 1 : 0;
+      last_block = old == uint32_t(nblk) - 1u ? 1 : 0;
       if (last_block) {
         *reinterpret_cast<volatile uint32_t*>(p.ex.wait_ticket) = 0u;
         *reinterpret_cast<volatile uint32_t*>(p.ex.wait_count) += 1u;
@@ -728,15 +740,88 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid
     if (threadIdx.x == 0) {
       const uint32_t e = *reinterpret_cast<volatile uint32_t*>(p.ex.epoch) + 1u;
       __threadfence_system();
-      const uint32_t slot = uint32_t(p.ex.rank) * gridDim.x + blockIdx.x;
+      const uint32_t slot = uint32_t(p.ex.rank) * uint32_t(nblk) + uint32_t(bid);
       for (int q = 0; q < p.ex.world; ++q)
         asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.ex.peer_flag[q] + slot), "r"(e)
                      : "memory");
       const uint32_t old = atomicAdd(p.ex.ticket, 1u);
-      if (old == gridDim.x - 1) {
+      if (old == uint32_t(nblk) - 1u) {
         *reinterpret_cast<volatile uint32_t*>(p.ex.ticket) = 0u;
         *reinterpret_cast<volatile uint32_t*>(p.ex.epoch) = e;
       }
+    }
+  }
+  if (PLAN && p.done) {
+    // the rows of this block are stored: one fence for the block, then the job's counter
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      atomicAdd(p.done, 1);
+    }
+  }
+}
+
+template <typename T, bool XREG>
+__global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const __grid_constant__ RowsParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  rows_block<T, XREG, false>(p, smem, int(blockIdx.x), int(gridDim.x));
+}
+
+// Persistent form: a list of jobs (the projections of a model step, each depending on the one
+// before it or on none) in ONE launch of one block per SM. Every block walks the list; a job's
+// parameters sit in shared memory (the next job's are copied in while this one runs), and block b
+// works on job j when b is below the job's block count. Because the body requests its first
+// round of codes and builds its pair tables BEFORE it looks at the producer's counter, code
+// bytes are in flight across every dependency, and no launch, drain or ramp separates two jobs.
+// The only waits are the bounded polls of a producer's counter; when one runs out the plan's
+// abort word is set, every later poll returns at once and the launch ends.
+struct RowsPlanHeader {
+  unsigned long long magic;
+  int njobs, grid;
+  uint32_t smem_bytes, params_abs;     // dynamic shared memory of the launch; where the two job slots sit
+  long long jobs_off, done_off, misc_off, total_bytes;
+};
+constexpr unsigned long long kRowsPlanMagic = 0xB200'1A7E'D0C0'DE02ull;
+constexpr uint32_t kRowsPlanSlot = (uint32_t(sizeof(RowsParams)) + 15u) & ~15u;
+
+template <typename T>
+__global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_plan_kernel(uint8_t* plan_bytes) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const RowsPlanHeader& hdr = *reinterpret_cast<const RowsPlanHeader*>(plan_bytes);
+  const uint8_t* jobs = plan_bytes + hdr.jobs_off;
+  int* done = reinterpret_cast<int*>(plan_bytes + hdr.done_off);
+  int* misc = reinterpret_cast<int*>(plan_bytes + hdr.misc_off);   // [0] exit count, [1] abort
+  const int njobs = hdr.njobs;
+  const uint32_t low = smem_u32(smem) & kRowsWindowMask;
+  uint8_t* slots = smem + (hdr.params_abs - low);
+  auto fetch = [&](int j) {   // 16 bytes per thread, no register round trip
+    const uint32_t dst = smem_u32(slots) + uint32_t(j & 1) * kRowsPlanSlot;
+    const uint8_t* src = jobs + size_t(j) * kRowsPlanSlot;
+    for (uint32_t o = threadIdx.x * 16u; o < kRowsPlanSlot; o += kRowsThreads * 16u)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + o), "l"(src + o) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch(0);
+  for (int j = 0; j < njobs; ++j) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();             // job j's parameters are in; nobody still works on job j - 1
+    if (j + 1 < njobs) fetch(j + 1);
+    const RowsParams& p = *reinterpret_cast<const RowsParams*>(slots + size_t(j & 1) * kRowsPlanSlot);
+    const int nblk = p.row_blocks;
+    if (int(blockIdx.x) < nblk) {
+      if (p.xreg) rows_block<T, true, true>(p, smem, int(blockIdx.x), nblk);
+      else rows_block<T, false, true>(p, smem, int(blockIdx.x), nblk);
+    }
+  }
+  // the last block out resets the completion counters for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int old = atomicAdd(misc, 1);
+    if (old == int(gridDim.x) - 1) {
+      for (int j = 0; j < njobs; ++j) done[j] = 0;
+      misc[0] = 0;
+      __threadfence();
     }
   }
 }
@@ -807,7 +892,7 @@ int rows_deal_blocks(const SegDev* seg, int nseg, int units, int blocks, int* bl
 // tile x split kernel has to run (other code widths, a second stream, M > 8, a K range whose
 // activation rows do not fit in shared memory).
 bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, int K, int sms,
-               uint32_t fht_bytes, int per_seg, RowsGeom* g) {
+               uint32_t fht_bytes, int per_seg, bool may_split, RowsGeom* g) {
   if (M < 1 || M > 8) return false;
   if (per_seg && silu) return false;    // a (gate, up) pair is one unit and has one input
   for (int i = 0; i < nseg; ++i)
@@ -859,7 +944,7 @@ bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, i
     split = sms / U;
     if (split > kMaxClusterSplit) split = kMaxClusterSplit;
     if (split > G / (kRowsWarps * kRowsRing)) split = G / (kRowsWarps * kRowsRing);
-    if (split < 1 || fht_bytes) split = 1;
+    if (split < 1 || fht_bytes || !may_split) split = 1;
   }
   g->units_total = U;
   g->row_blocks = row_blocks;

@@ -190,6 +190,57 @@ def test_persistent_plan_matches_per_launch_results():
         assert rel_err(y, down.oracle(act.cpu())) <= TOL
 
 
+@pytest.mark.parametrize("M", (1, 3, 8))
+def test_persistent_plan_of_row_range_jobs(M):
+    # every job 4-bit and single-stream: the plan runs the row-range block body job after job.
+    # Jobs wide enough to fill the SMs without a K split are laid out exactly as their single
+    # launches, so their results are equal bit for bit; the narrow ones (a single launch splits
+    # K over a cluster, a plan never does) agree to an output ulp.
+    dt = torch.bfloat16
+    q, k, o = (Case(n, 4096, 128, 4, dt, seed=s) for n, s in ((4096, 11), (1024, 12), (4096, 13)))
+    gate, up = Case(4096, 4096, 128, 4, dt, seed=14, bias=True), Case(4096, 4096, 64, 4, dt, seed=15)
+    down = Case(4096, 4096, 128, 4, dt, seed=16)
+    small = Case(256, 1024, 64, 4, dt, seed=17)
+    mods = {n: c.module() for n, c in dict(q=q, k=k, o=o, gate=gate, up=up, down=down, small=small).items()}
+    for m in mods.values():
+        m._ensure_packed()
+    x = q.x(M).cuda()
+    heads = torch.empty(M, 5120, dtype=dt, device="cuda")
+    obuf = torch.empty(M, 4096, dtype=dt, device="cuda")
+    act = torch.empty(M, 4096, dtype=dt, device="cuda")
+    y = torch.empty(M, 4096, dtype=dt, device="cuda")
+    tail = torch.empty(M, 256, dtype=dt, device="cuda")
+    jobs = [
+        dict(x=x, segs=[mods["q"]._segment_desc(heads, ldo=5120), mods["k"]._segment_desc(heads[:, 4096:], ldo=5120)], dep=-1),
+        dict(x=x, segs=[mods["o"]._segment_desc(obuf)], dep=0),
+        dict(x=x, segs=[mods["gate"]._segment_desc(act), mods["up"]._segment_desc(None)],
+             epilogue=L.EPI_SILU_MUL, dep=1),
+        dict(x=act, segs=[mods["down"]._segment_desc(y)], dep=2),
+        dict(x=y[:, :1024], segs=[mods["small"]._segment_desc(tail)], dep=3),
+    ]
+    bufs = (heads, obuf, act, y, tail)
+    for j in jobs:
+        L.gemv_multi(j["x"], L.make_segments(j["segs"]), len(j["segs"]), epilogue=j.get("epilogue", 0))
+    torch.cuda.synchronize()
+    want = [t.clone() for t in bufs]
+    plan = L.DecodePlan(jobs, M, dt, "cuda")
+    assert plan.form == "rows"
+    for rep in range(4):        # the counters return to zero by themselves
+        for t in bufs:
+            t.fill_(float("nan"))
+        plan.run()
+        torch.cuda.synchronize()
+        plan.check_status()
+        for i, (got, w) in enumerate(zip(bufs, want)):
+            if i < 4:
+                assert torch.equal(got, w), (rep, i)
+            else:
+                assert rel_err(got, w) <= 5e-3, (rep, i)
+    assert rel_err(obuf, o.oracle(x.cpu())) <= TOL
+    assert rel_err(y, down.oracle(act.cpu())) <= TOL
+    assert L.lib().b200lut_device_status() == 0
+
+
 # ---- fused low-rank residual ------------------------------------------------------------------
 @pytest.mark.parametrize("M,K,R,dtype", ((1, 4096, 32, torch.bfloat16), (16, 1024, 256, torch.float16),
                                           (5, 192, 8, torch.bfloat16)))

@@ -45,6 +45,8 @@ def _run(case, x, flags, mod=None):
     (640, 1856, 128, torch.bfloat16, 3),        # 29 chunks: ragged rounds, idle ring slots
     (9600, 2048, 128, torch.float16, 7),        # 32 chunks: half rounds
     (1024, 8192, 128, torch.bfloat16, 6),       # two full rounds per unit
+    (32768, 1024, 128, torch.bfloat16, 8),      # seven units per block, each folded behind its last plane
+    (20480, 1024, 64, torch.float16, 4),        # the same at M' = 4 with a palette per two units
 ))
 def test_rows_kernel_matches_oracle(N, K, gs, dtype, M):
     case = Case(N, K, gs, 4, dtype, seed=N + K + M)
@@ -97,7 +99,8 @@ def test_rows_kernel_merged_segments_bias_and_residual():
             off += c.N
 
 
-@pytest.mark.parametrize("N,K,M", ((12288, 4096, 1), (12288, 4096, 8), (1024, 2048, 2), (256, 512, 1)))
+@pytest.mark.parametrize("N,K,M", ((12288, 4096, 1), (12288, 4096, 8), (1024, 2048, 2), (256, 512, 1),
+                                   (24576, 1024, 5), (12288, 4096, 3)))
 def test_rows_kernel_fused_gate_up(N, K, M):
     dt = torch.bfloat16
     gate, up = Case(N, K, 128, 4, dt, seed=N + 1, bias=True), Case(N, K, 128, 4, dt, seed=N + 2)
