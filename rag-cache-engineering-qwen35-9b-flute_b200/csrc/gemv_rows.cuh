@@ -754,10 +754,8 @@ __device__ __forceinline__ void rows_block(const RowsParams& p, uint8_t* smem, c
   if (PLAN && p.done) {
     // the rows of this block are stored: one fence for the block, then the job's counter
     __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      atomicAdd(p.done, 1);
-    }
+    if (threadIdx.x == 0)
+      asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.done) : "memory");
   }
 }
 
