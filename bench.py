@@ -271,13 +271,14 @@ def exchange_equals_gather(stack, M: int, world: int) -> bool:
             _, _, dsegs, dn, depi, _, _, _ = launches[4 * li + 3]
             act, y = plan["buffers"][4 * li + 2], plan["buffers"][4 * li + 3]
             y_step = y.clone()
-            L.gemv_multi(xin, segs, nseg, epilogue=epi)
+            # (a flag-less exchange always runs the row-range kernel: so do the launches repeated here)
+            L.gemv_multi(xin, segs, nseg, epilogue=epi, flags=L.FLAG_ROWS_KERNEL)
             n = act.shape[1] // world
             mine = act[:, stack.rank * n:(stack.rank + 1) * n].contiguous()
             parts = [torch.empty_like(mine) for _ in range(world)]
             dist.all_gather(parts, mine)
             full = torch.cat(parts, dim=1)
-            L.gemv_multi(full, dsegs, dn, epilogue=depi)
+            L.gemv_multi(full, dsegs, dn, epilogue=depi, flags=L.FLAG_ROWS_KERNEL)
             torch.cuda.synchronize()
             ok = ok and bool(torch.equal(y, y_step))
             plan["assembled"][li] = full

@@ -285,7 +285,10 @@ typedef struct b200lut_exchange {
 /* Blocks of the launch that b200lut_gemv_multi / b200lut_gemv_exchange would make for these
  * segments with split = 0 (the library's policy) — the producer_blocks of an exchange whose
  * pushing launch they describe. Output pointers of the segments may be NULL here. 0 on invalid
- * arguments. No counterpart in the reference. */
+ * arguments. The policy picks between the two decode kernels by shape and M; a launch that
+ * carries an input transform or a flag-less (sentinel) exchange always runs the row-range
+ * kernel, so pass B200LUT_FLAG_ROWS_KERNEL here for such a launch. No counterpart in the
+ * reference. */
 int b200lut_gemv_launch_blocks(int M, int K, const b200lut_segment* segs, int nseg, int epilogue,
                                int flags);
 

@@ -812,6 +812,21 @@ bool rows_kernel_wanted(int flags) {
   return dflt;
 }
 
+// Library policy between the two decode kernels for a launch both serve (no kernel flag, no
+// input transform, no flag-less exchange). The row-range kernel stages all M rows of its K range
+// in shared memory before its first lookup. With ONE unit per block and a K range whose
+// fragments cannot stay in registers (K != 4096) nothing amortises that from two rows on, and
+// the tile kernel (activation fragments straight from L2, chunk by chunk) is faster. Measured,
+// rows / tile: 4096 x 12288 per launch, M=1 10.2 / 10.2 us, M=2 12.9 / 11.5, M=3 14.5 / 11.6,
+// M=4 15.2 / 11.8; the 9B stack per step with this rule off / on, M=2 1.50 / 1.39 ms, M=3
+// 1.81 / 1.64, M=4 1.89 / 1.69. (The same rule for one-unit launches of K = 4096 from three
+// rows on wins per launch, 7.4 / 6.7 us at M=4, but loses in the stack, 1.69 -> 1.78 ms: the
+// launch chain then alternates between the two kernels four times per layer instead of twice.)
+bool rows_kernel_faster(const RowsGeom& g, int M) {
+  if (g.split != 1 || g.per_seg || g.units_total > g.row_blocks) return true;
+  return g.xreg || M < 2;
+}
+
 // The layout of the row-range kernel for a launch, or false when the kernel does not serve it.
 // It depends only on the segment geometry; it is planned once per distinct launch shape (the
 // planner walks every 32-row unit) and looked up afterwards.
@@ -896,6 +911,7 @@ int fill_rows_params(const GemvParams& gp, const uint16_t* x2, const RowsGeom& g
   p.split = g.split;
   p.ntables = g.ntables;
   p.red_planes = g.red_planes;
+  p.incr = g.incr;
   p.xs_abs = g.xs_abs;
   p.red_abs = g.red_abs;
   p.part_abs = g.part_abs;
@@ -911,13 +927,16 @@ int fill_rows_params(const GemvParams& gp, const uint16_t* x2, const RowsGeom& g
 
 // The row-range kernel when it serves the launch (4-bit, one stream, M <= 8).
 template <typename T>
-int try_rows(const GemvParams& gp, const uint16_t* x2, int tiles, bool pdl, cudaStream_t st, bool* served) {
+int try_rows(const GemvParams& gp, const uint16_t* x2, int tiles, bool pdl, bool must, cudaStream_t st,
+             bool* served) {
   *served = false;
   RowsGeom g;
   if (!rows_geometry(gp, tiles, true, &g)) return B200LUT_OK;
+  if (!must && !rows_kernel_faster(g, gp.M)) return B200LUT_OK;
   RowsParams p;
   if (int rc = fill_rows_params(gp, x2, g, &p)) return rc;
-  B200LUT_REQUIRE(!p.ex.push || p.ex.blocks == g.row_blocks * g.split, B200LUT_ERR_INVALID,
+  // (a flag-less exchange has no flags to count)
+  B200LUT_REQUIRE(!p.ex.push || p.ex.sentinel || p.ex.blocks == g.row_blocks * g.split, B200LUT_ERR_INVALID,
                   "exchange: producer_blocks is %d but this launch has %d blocks "
                   "(b200lut_gemv_launch_blocks gives the count)", p.ex.blocks, g.row_blocks * g.split);
   *served = true;
@@ -1122,9 +1141,10 @@ extern "C" int b200lut_gemv_input(const void* x, int64_t ldx, int M, int K, int 
   // split or B200LUT_FLAG_TILE_KERNEL selects the tile x split kernel.
   if (split <= 0 && rows_kernel_wanted(flags)) {
     bool served = false;
+    const bool must = transformed || p.ex.sentinel || (flags & B200LUT_FLAG_ROWS_KERNEL);
     const int rc = dtype == B200LUT_BF16
-                       ? try_rows<__nv_bfloat16>(p, nullptr, tiles, pdl, st, &served)
-                       : try_rows<__half>(p, nullptr, tiles, pdl, st, &served);
+                       ? try_rows<__nv_bfloat16>(p, nullptr, tiles, pdl, must, st, &served)
+                       : try_rows<__half>(p, nullptr, tiles, pdl, must, st, &served);
     if (rc || served) return rc;
   }
   B200LUT_REQUIRE(!transformed, B200LUT_ERR_UNSUPPORTED,
@@ -1177,7 +1197,9 @@ extern "C" int b200lut_gemv_launch_blocks(int M, int K, const b200lut_segment* s
   if (convert_segments(tmp, nseg, silu, p.seg, &tiles, &max_tables)) return 0;
   if (rows_kernel_wanted(flags)) {
     RowsGeom g;
-    if (rows_geometry(p, tiles, true, &g)) return g.row_blocks * g.split;
+    if (rows_geometry(p, tiles, true, &g) &&
+        ((flags & B200LUT_FLAG_ROWS_KERNEL) || rows_kernel_faster(g, M)))
+      return g.row_blocks * g.split;
   }
   return tiles * pick_split(tiles, p.G, sm_count_cached(), M <= 8 ? kWarpsM8 : kWarpsM16);
 }

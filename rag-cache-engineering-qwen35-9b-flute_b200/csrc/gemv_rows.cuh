@@ -58,6 +58,12 @@ struct RowsParams {
   int M, Mp, K, G, nseg, epilogue;
   int units_total;         // 32-row units (pairs of units under the SiLU*mul epilogue)
   int row_blocks, split, ntables, red_planes;
+  // incr (M' = 8, K of exactly 64 chunks): the warps' sums of a unit are folded as soon as its
+  // last plane is done (one block barrier per plane) out of 2 (4 under SiLU*mul) rotating plane
+  // buffers that take the place of the staged rows (which live in registers by then), instead of
+  // all planes after the loop out of a buffer of their own: eight rows of K = 4096 then fit next
+  // to four palettes, and a block's planes are bounded only by the lanes that hold their metadata
+  int incr;
   uint32_t xs_abs, red_abs, part_abs;    // offsets inside the block's shared window
   uint32_t meta_abs;                     // RowsUnitMeta[units of the block]
   // Hadamard rotation of the activation rows inside the launch (rot_signs != null): descending
@@ -589,6 +595,20 @@ __device__ __forceinline__ void rows_block(const RowsParams& p, uint8_t* smem, c
 #pragma unroll
     for (int r = 0; r < 4; ++r) acc[s][r] = 0.f;
   float* red = reinterpret_cast<float*>(generic(p.red_abs));
+  const int nwa = kc < NW ? kc : NW;   // warps that held chunks
+  const RowsUnitMeta* meta = reinterpret_cast<const RowsUnitMeta*>(generic(p.meta_abs));
+  // sum of the 16 warps' partial results of one (plane buffer, batch row, row): loads first, adds in warp order
+  auto warp_sum = [&](int plane, int m, int row) {
+    const float* r0 = red + (plane * Mp + m) * kUnitRows + row;
+    const int stride = p.red_planes * Mp * kUnitRows;
+    float part_v[NW];
+#pragma unroll
+    for (int wi = 0; wi < NW; ++wi) part_v[wi] = wi < nwa ? r0[wi * stride] : 0.f;
+    float v = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < NW; ++wi) v += part_v[wi];
+    return v;
+  };
   const uint32_t xs_lane = token + win + p.xs_abs + uint32_t(gid & (Mp - 1)) * uint32_t(kc) * 128u +
                            uint32_t(tig) * 32u + uint32_t(warp) * 128u;
   auto slot_base = [&](int plane) {
@@ -602,6 +622,17 @@ __device__ __forceinline__ void rows_block(const RowsParams& p, uint8_t* smem, c
     for (int j = 0; j < R; ++j) {
       lds128(xr[j][0], xs_lane + uint32_t(j) * uint32_t(NW * 128));
       lds128(xr[j][1], xs_lane + uint32_t(j) * uint32_t(NW * 128) + 16);
+    }
+    if (p.incr) {
+      // the plane buffers take the place of the staged rows: nobody may write a sum before
+      // every warp holds its fragments (the values are pinned here, ahead of the barrier)
+#pragma unroll
+      for (int j = 0; j < R; ++j)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) asm volatile("" : "+r"(xr[j][h][i]));
+      __syncthreads();
     }
   }
 
@@ -645,17 +676,34 @@ __device__ __forceinline__ void rows_block(const RowsParams& p, uint8_t* smem, c
       }
     }
     if (nxt_plane != cur_plane) {   // this warp's share of the plane is done
+      const int buf = (XREG && p.incr) ? (cur_plane & (p.red_planes - 1)) : cur_plane;
 #pragma unroll
       for (int s = 0; s < 2; ++s)
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           const int col = 2 * tig + (r & 1);
           if (col < Mp)
-            red[((warp * p.red_planes + cur_plane) * Mp + col) * kUnitRows + 16 * s + gid + 8 * (r >> 1)] =
+            red[((warp * p.red_planes + buf) * Mp + col) * kUnitRows + 16 * s + gid + 8 * (r >> 1)] =
                 acc[s][r];
           acc[s][r] = 0.f;
         }
       base = slot_base(nxt_plane);
+      if (XREG && p.incr) {
+        // Every warp passes here once per plane (all sixteen hold chunks). After the barrier the
+        // plane's sums are complete; when it closes a unit, the unit is finished right away. A
+        // buffer is written again two (four) planes later, i.e. behind the next barrier, which
+        // the folding threads reach only after this fold.
+        asm volatile("bar.sync 3, %0;" ::"n"(NT) : "memory");
+        if ((cur_plane % ppu) == ppu - 1) {
+          const int ul = cur_plane / ppu, b0 = (cur_plane - (ppu - 1)) & (p.red_planes - 1);
+          for (int idx = threadIdx.x; idx < M * kUnitRows; idx += NT) {
+            const int row = idx & 31, m = idx >> 5;
+            const float a = warp_sum(b0, m, row);
+            const float b = silu ? warp_sum(b0 + 1, m, row) : 0.f;
+            rows_finish<T>(p, meta[ul], silu, m, row, a, b);
+          }
+        }
+      }
     }
     cur_plane = nxt_plane;
     cur_k = nxt_k;
@@ -664,22 +712,11 @@ __device__ __forceinline__ void rows_block(const RowsParams& p, uint8_t* smem, c
   __syncthreads();
 
   // ---- fold the warps' sums (warp order), then the K parts of a cluster (rank order) -----------
-  const int nwa = kc < NW ? kc : NW;   // warps that held chunks
   const int nu = nplanes / ppu;
   const int total_out = nu * M * kUnitRows;
-  const RowsUnitMeta* meta = reinterpret_cast<const RowsUnitMeta*>(generic(p.meta_abs));
-  auto warp_sum = [&](int plane, int m, int row) {
-    const float* r0 = red + (plane * Mp + m) * kUnitRows + row;
-    const int stride = p.red_planes * Mp * kUnitRows;
-    float part_v[NW];
-#pragma unroll
-    for (int wi = 0; wi < NW; ++wi) part_v[wi] = wi < nwa ? r0[wi * stride] : 0.f;   // loads first,
-    float v = 0.f;
-#pragma unroll
-    for (int wi = 0; wi < NW; ++wi) v += part_v[wi];                               // adds in warp order
-    return v;
-  };
-  if (PLAN || split == 1) {   // (a plan never splits K)
+  if (XREG && p.incr) {
+    // every unit was finished behind its last plane
+  } else if (PLAN || split == 1) {   // (a plan never splits K)
     for (int idx = threadIdx.x; idx < total_out; idx += NT) {
       const int row = idx & 31, m = (idx >> 5) % M, ul = (idx >> 5) / M;
       const float a = warp_sum(ul * ppu, m, row);
@@ -827,7 +864,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_plan_kernel(uint8_t
 // ---- host side: geometry of a launch ------------------------------------------------------------
 
 struct RowsGeom {
-  int units_total, row_blocks, split, ntables, red_planes, Mp, xreg;
+  int units_total, row_blocks, split, ntables, red_planes, Mp, xreg, incr;
   int per_seg, blk0[kMaxSeg + 1];
   uint32_t xs_abs, red_abs, part_abs, fht_abs, meta_abs, end_abs;
 };
@@ -901,7 +938,11 @@ bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, i
   const int U = tiles_total * 4;
   int cap_planes = 32 / Mp;                       // fold buffer <= 32 KB
   if (cap_planes > kRowsMaxPlanes) cap_planes = kRowsMaxPlanes;
-  const int upb_max = cap_planes / ppu;
+  // Eight rows of a K of exactly 64 chunks: the units are folded as they finish out of 2 * ppu
+  // rotating plane buffers in the place of the staged rows (see RowsParams::incr), so the fold
+  // buffer neither caps the planes of a block nor takes shared memory of its own.
+  const bool incr_ok = Mp == 8 && G == kRowsWarps * kRowsRing;
+  const int upb_max = (incr_ok ? kRowsMaxPlanes : cap_planes) / ppu;
   if (upb_max < 1) return false;
   int split = 1, row_blocks, slots;
   g->per_seg = per_seg;
@@ -951,11 +992,17 @@ bool rows_plan(const SegDev* seg, int nseg, bool silu, int tiles_total, int M, i
   g->Mp = Mp;
   g->xreg = (G % split == 0 && G / split == kRowsWarps * kRowsRing) ? 1 : 0;
   if (!per_seg) widest = (U + row_blocks - 1) / row_blocks;
-  g->red_planes = widest * ppu;
+  g->incr = (incr_ok && split == 1) ? 1 : 0;
+  if (!g->incr && widest * ppu > cap_planes) return false;
+  g->red_planes = g->incr ? 2 * ppu : widest * ppu;
   const int kc_max = (G + split - 1) / split;
   g->xs_abs = kRowsTableAbs + uint32_t(g->ntables) * kTableBytes;
   g->red_abs = g->xs_abs + uint32_t(Mp) * uint32_t(kc_max) * 128u;
   g->part_abs = g->red_abs + uint32_t(kRowsWarps) * uint32_t(g->red_planes) * uint32_t(Mp) * 128u;
+  if (g->incr) {   // 16 warps x 2 ppu planes x M' x 128 bytes <= M' x 64 chunks x 128 bytes
+    g->part_abs = g->red_abs;
+    g->red_abs = g->xs_abs;
+  }
   g->fht_abs = g->part_abs + (split > 1 ? uint32_t(g->red_planes) * uint32_t(Mp) * 128u : 0u);
   g->meta_abs = g->fht_abs + ((fht_bytes + 15u) & ~15u);
   g->end_abs = g->meta_abs + uint32_t(widest) * uint32_t(sizeof(RowsUnitMeta));

@@ -61,7 +61,9 @@ def test_emulated_ranks_push_equals_manual_gather(M, world):
                             entries[q][1][:, r * n:(r + 1) * n].copy_(e[2])
                 continue
             for s, e in zip(manual, entries):
-                s.run_launch(e, M)
+                # a flag-less exchange always runs the row-range kernel; the launches it is
+                # compared with, bit for bit, must run the same one
+                s.run_launch(e, M, pkg._lib.FLAG_ROWS_KERNEL if plans[0]["sentinel"] else 0)
         torch.cuda.synchronize()
         for r in range(world):
             for i, (got, want) in enumerate(zip(plans[r]["buffers"], mplans[r]["buffers"])):
@@ -106,7 +108,7 @@ def _two_gpu_worker(rank, world, port, ok, M):
         a._plan(M)["x"].copy_(x)
         b._plan(M)["x"].copy_(x)
         ya = a.step(M, flags=pkg._lib.FLAG_PDL)
-        yb = b.step(M, gather=gather)
+        yb = b.step(M, flags=pkg._lib.FLAG_ROWS_KERNEL if a._plan(M)["sentinel"] else 0, gather=gather)
         torch.cuda.synchronize()
         consumed = a._plan(M)["sentinel"]      # a flag-less exchange refills the rows it has consumed
         for i, (p, q) in enumerate(zip(a._plan(M)["buffers"], b._plan(M)["buffers"])):

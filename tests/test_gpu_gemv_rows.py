@@ -128,12 +128,17 @@ def test_rows_kernel_leaves_other_widths_to_the_tile_kernel():
     assert torch.equal(_run(two, x, ROWS), _run(two, x, TILE))
 
 
-@pytest.mark.parametrize("N,K,M,dtype,awq", ((4096, 4096, 1, torch.bfloat16, False), (4096, 12288, 3, torch.float16, True),
-                                              (12288, 4096, 8, torch.bfloat16, True), (256, 192, 2, torch.float16, False)))
-def test_rotation_inside_the_launch_equals_the_separate_transform(N, K, M, dtype, awq):
+@pytest.mark.parametrize("N,K,M,dtype,awq,exact", (
+    (4096, 4096, 1, torch.bfloat16, False, True), (4096, 12288, 1, torch.float16, True, True),
+    (12288, 4096, 8, torch.bfloat16, True, True), (256, 192, 2, torch.float16, False, True),
+    # behind a separate transform the library policy gives this shape to the tile kernel (one unit
+    # per block, K != 4096, M >= 2): same rotated rows, another summation order
+    (4096, 12288, 3, torch.float16, True, False)))
+def test_rotation_inside_the_launch_equals_the_separate_transform(N, K, M, dtype, awq, exact):
     """The module rotates its input inside the decode launch when it can (the reference's fused
     prologue, src/flute_extended/include/flute/gemv.cuh:305-351). Same butterfly, same rounding
-    point: the outputs equal those behind a separate b200lut_fht launch bit for bit."""
+    point: the outputs equal those behind a separate b200lut_fht launch bit for bit whenever the
+    same decode kernel runs behind it."""
     import os
     case = Case(N, K, 128, 4, dtype, seed=N + K, rotation_seed=5, awq=awq)
     mod = case.module()
@@ -146,7 +151,10 @@ def test_rotation_inside_the_launch_equals_the_separate_transform(N, K, M, dtype
         separate = mod(x)
     finally:
         del os.environ["FLUTE_NO_FHT_FUSE"]
-    assert torch.equal(fused, separate)
+    if exact:
+        assert torch.equal(fused, separate)
+    else:
+        assert rel_err(fused, separate) <= 5e-3
     assert rel_err(fused, case.oracle(x.cpu())) <= TOL
     assert L.lib().b200lut_device_status() == 0
 
