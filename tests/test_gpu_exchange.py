@@ -103,7 +103,7 @@ def _two_gpu_worker(rank, world, port, ok, M):
         parts = [torch.empty_like(local.contiguous()) for _ in range(world)]
         dist.all_gather(parts, local.contiguous())
         full.copy_(torch.cat(parts, dim=1))
-    same = True
+    bad = 0     # bit 0: a buffer differs, 1: consumed rows not refilled, 2: y differs, 3: device status
     for _ in range(4):
         a._plan(M)["x"].copy_(x)
         b._plan(M)["x"].copy_(x)
@@ -113,13 +113,15 @@ def _two_gpu_worker(rank, world, port, ok, M):
         consumed = a._plan(M)["sentinel"]      # a flag-less exchange refills the rows it has consumed
         for i, (p, q) in enumerate(zip(a._plan(M)["buffers"], b._plan(M)["buffers"])):
             if consumed and i % 4 == 2:
-                same = same and bool((p.view(torch.int16) == -1).all())
+                bad |= 0 if bool((p.view(torch.int16) == -1).all()) else 2
             else:
-                same = same and torch.equal(p, q)
-        same = same and torch.equal(ya, yb)
-    same = same and pkg._lib.lib().b200lut_device_status() == 0
+                bad |= 0 if torch.equal(p, q) else 1
+        bad |= 0 if torch.equal(ya, yb) else 4
+        torch.cuda.synchronize()
+        dist.barrier()       # the peer's next push must not land while this rank still looks at its rows
+    bad |= 0 if pkg._lib.lib().b200lut_device_status() == 0 else 8
     dist.barrier()
-    ok[rank] = 1 if same else 0
+    ok[rank] = 1 if bad == 0 else -bad
     a._plan(M)["arena"].close()
     dist.destroy_process_group()
 
