@@ -210,8 +210,11 @@ __host__ __device__ inline void rows_block_units(int per_seg, const int* blk0, c
                                                  int units_total, int row_blocks, int rb, int* u0, int* u1,
                                                  int* owner) {
   if (!per_seg) {
-    *u0 = int((long long)units_total * rb / row_blocks);
-    *u1 = int((long long)units_total * (rb + 1) / row_blocks);
+    // floor(units * rb / blocks); a 32-bit division whenever the product allows (same quotient)
+    const unsigned long long a = (unsigned long long)(units_total) * unsigned(rb);
+    const unsigned long long b = a + (unsigned long long)(units_total);
+    *u0 = (b >> 32) == 0 ? int(uint32_t(a) / uint32_t(row_blocks)) : int(a / unsigned(row_blocks));
+    *u1 = (b >> 32) == 0 ? int(uint32_t(b) / uint32_t(row_blocks)) : int(b / unsigned(row_blocks));
     *owner = 0;
     return;
   }
@@ -329,32 +332,16 @@ __device__ __forceinline__ void rows_block(const RowsParams& p, uint8_t* smem, c
   // ---- plane j of the block lives in lane j of every warp -----------------------------------
   unsigned long long my_ptr = 0, my_lut = 0;
   const int which = silu ? (lane & 1) : 0;
-  if (lane < nplanes) {
+  int si = 0, lu = 0;
+  if (lane < nplanes) {   // where the plane's codes start: all the first loads need
     const int u = u0 + lane / ppu;
-    int si = 0;
     for (int s = 0; s < p.nseg; s += ppu)
       if ((u >> 2) >= p.seg[s].tile_begin) si = s;
-    const SegDev& sg = p.seg[si + which];
-    const int lu = u - 4 * p.seg[si].tile_begin;
+    lu = u - 4 * p.seg[si].tile_begin;
     my_ptr = reinterpret_cast<unsigned long long>(
-        sg.packed + (size_t(lu >> 2) * p.G + c0 + warp) * 4096 + size_t(lu & 3) * 1024);
-    int grp = (lu * kUnitRows) / sg.gs;
-    if (grp > sg.n_groups - 1) grp = sg.n_groups - 1;
-    my_lut = reinterpret_cast<unsigned long long>(sg.lut + size_t(grp) * 16);
-    if (warp == 0 && which == 0) {
-      const SegDev& s0 = p.seg[si];
-      RowsUnitMeta um;
-      um.n0 = lu * kUnitRows;
-      um.out = s0.out + um.n0;
-      um.bias = s0.bias ? s0.bias + um.n0 : nullptr;
-      um.bias2 = (silu && p.seg[si + 1].bias) ? p.seg[si + 1].bias + um.n0 : nullptr;
-      um.ldo = s0.ldo;
-      um.seg = si;
-      um.has_res = (s0.res_rank ? 1 : 0) | ((silu && p.seg[si + 1].res_rank) ? 2 : 0);
-      um.pad = 0;
-      reinterpret_cast<RowsUnitMeta*>(generic(p.meta_abs))[lane / ppu] = um;
-    }
+        p.seg[si + which].packed + (size_t(lu >> 2) * p.G + c0 + warp) * 4096 + size_t(lu & 3) * 1024);
   }
+
 
   // ---- rounds: up to R consecutive chunks of one plane. The first round is requested now,
   //      before anything else; afterwards slot j of the next round is requested as soon as
@@ -371,6 +358,27 @@ __device__ __forceinline__ void rows_block(const RowsParams& p, uint8_t* smem, c
 #pragma unroll
       for (int i = 0; i < 8; ++i) w[j][i] = 0u;
       ldg_stream256_if(w[j], first + j * kHop, j < cur_n ? 1u : 0u);
+    }
+  }
+
+  // ---- the plane's palette and what the epilogue needs to know about its unit ------------------
+  if (lane < nplanes) {
+    const SegDev& sg = p.seg[si + which];
+    int grp = (lu * kUnitRows) / sg.gs;
+    if (grp > sg.n_groups - 1) grp = sg.n_groups - 1;
+    my_lut = reinterpret_cast<unsigned long long>(sg.lut + size_t(grp) * 16);
+    if (warp == 0 && which == 0) {
+      const SegDev& s0 = p.seg[si];
+      RowsUnitMeta um;
+      um.n0 = lu * kUnitRows;
+      um.out = s0.out + um.n0;
+      um.bias = s0.bias ? s0.bias + um.n0 : nullptr;
+      um.bias2 = (silu && p.seg[si + 1].bias) ? p.seg[si + 1].bias + um.n0 : nullptr;
+      um.ldo = s0.ldo;
+      um.seg = si;
+      um.has_res = (s0.res_rank ? 1 : 0) | ((silu && p.seg[si + 1].res_rank) ? 2 : 0);
+      um.pad = 0;
+      reinterpret_cast<RowsUnitMeta*>(generic(p.meta_abs))[lane / ppu] = um;
     }
   }
 
