@@ -375,6 +375,11 @@ int b200lut_plan_status(const void* plan);
  * 4-bit, single-stream, M <= 8, one block per SM at most); 0 = the tile-share kernel (any other
  * mix, or B200LUT_PLAN_KERNEL=tile in the environment); negative = not a plan buffer. */
 int b200lut_plan_form(const void* plan);
+/* Call before the buffer of a built plan is freed or reused for something else (with the
+ * buffer's device current): the library keeps one small host-side record per row-range plan
+ * (what b200lut_plan_run must know to launch it) and drops it here. Rebuilding a plan in the
+ * same buffer replaces the record by itself. NULL is accepted. */
+int b200lut_plan_release(const void* plan);
 
 /* ------------------------------------------------------------------------- *
  * Prefill GEMM (M > 16), tcgen05 / TMEM

@@ -34,7 +34,7 @@ EXPORTS = (
     "b200lut_gemm_two_stream", "b200lut_gemm_two_stream_bytes",
     "b200lut_embed_gather", "b200lut_round_rows", "b200lut_gemv_kgrouped",
     "b200lut_gemv_kgrouped_split", "b200lut_gemv_kgrouped_workspace_bytes", "b200lut_gemm_kgrouped", "b200lut_gemv_exchange", "b200lut_peer_export", "b200lut_peer_open", "b200lut_peer_close",
-    "b200lut_gemv_noalloc", "b200lut_gemv_noalloc_reset", "b200lut_gemv_launch_blocks", "b200lut_gemv_input", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status", "b200lut_plan_form",
+    "b200lut_gemv_noalloc", "b200lut_gemv_noalloc_reset", "b200lut_gemv_launch_blocks", "b200lut_gemv_input", "b200lut_plan_bytes", "b200lut_plan_build", "b200lut_plan_run", "b200lut_plan_status", "b200lut_plan_form", "b200lut_plan_release",
 )
 
 
@@ -185,6 +185,8 @@ def lib() -> ctypes.CDLL:
     L.b200lut_plan_status.argtypes = [vp]
     L.b200lut_plan_form.restype = i32
     L.b200lut_plan_form.argtypes = [vp]
+    L.b200lut_plan_release.restype = i32
+    L.b200lut_plan_release.argtypes = [vp]
     _lib = L
     return L
 
@@ -671,3 +673,16 @@ class DecodePlan:
     def check_status(self) -> None:
         with torch.cuda.device(self.device):
             check(lib().b200lut_plan_status(self.buffer.data_ptr()))
+
+    def close(self) -> None:
+        """Drop the library's record of this plan (before its buffer goes back to the allocator)."""
+        buf = self.__dict__.get("buffer")
+        if buf is not None and _lib is not None:
+            with torch.cuda.device(self.device):
+                lib().b200lut_plan_release(buf.data_ptr())
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

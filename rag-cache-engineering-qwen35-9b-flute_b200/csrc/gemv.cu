@@ -1376,13 +1376,16 @@ int rows_plan_layout(const b200lut_job* jobs, int njobs, int M, uint8_t* base, R
 // (the run call gets the device buffer only).
 struct RowsPlanInfo { const void* plan; int dev, grid; uint32_t smem; };
 std::mutex g_rows_plan_mu;
-RowsPlanInfo g_rows_plans[256];
-int g_rows_plans_used = 0;
+std::vector<RowsPlanInfo> g_rows_plans;     // one entry per live row-range plan buffer
 
 void rows_plan_forget(const void* plan, int dev) {
-  for (int i = 0; i < g_rows_plans_used; ++i)
-    if (g_rows_plans[i].plan == plan && g_rows_plans[i].dev == dev)
-      g_rows_plans[i] = g_rows_plans[--g_rows_plans_used];
+  for (size_t i = 0; i < g_rows_plans.size();)
+    if (g_rows_plans[i].plan == plan && g_rows_plans[i].dev == dev) {
+      g_rows_plans[i] = g_rows_plans.back();
+      g_rows_plans.pop_back();
+    } else {
+      ++i;
+    }
 }
 
 template <typename T>
@@ -1467,9 +1470,7 @@ extern "C" int b200lut_plan_build(void* plan, size_t plan_bytes, const b200lut_j
                                     cudaMemcpyHostToDevice, st));
     B200LUT_CUDA_OK(cudaStreamSynchronize(st));   // the host staging dies with this call
     std::lock_guard<std::mutex> lock(g_rows_plan_mu);
-    B200LUT_REQUIRE(g_rows_plans_used < 256, B200LUT_ERR_UNSUPPORTED,
-                    "more than 256 live row-range plans (rebuilding a buffer replaces its entry)");
-    g_rows_plans[g_rows_plans_used++] = RowsPlanInfo{plan, dev, h.grid, h.smem_bytes};
+    g_rows_plans.push_back(RowsPlanInfo{plan, dev, h.grid, h.smem_bytes});
     return B200LUT_OK;
   }
   B200LUT_REQUIRE(plan_bytes >= size_t(lay.hdr.total_bytes), B200LUT_ERR_WORKSPACE,
@@ -1493,8 +1494,8 @@ extern "C" int b200lut_plan_run(void* plan, int M, int dtype, void* stream) {
     RowsPlanInfo info = {};
     {
       std::lock_guard<std::mutex> lock(g_rows_plan_mu);
-      for (int i = 0; i < g_rows_plans_used; ++i)
-        if (g_rows_plans[i].plan == plan && g_rows_plans[i].dev == dev) info = g_rows_plans[i];
+      for (const RowsPlanInfo& e : g_rows_plans)
+        if (e.plan == plan && e.dev == dev) info = e;
     }
     if (info.plan) {
       if (dtype == B200LUT_BF16) return launch_rows_plan<__nv_bfloat16>(plan, info, cudaStream_t(stream));
@@ -1504,6 +1505,15 @@ extern "C" int b200lut_plan_run(void* plan, int M, int dtype, void* stream) {
   const int grid = sm_count_cached();
   if (dtype == B200LUT_BF16) return dispatch_plan<__nv_bfloat16>(plan, M, grid, cudaStream_t(stream));
   return dispatch_plan<__half>(plan, M, grid, cudaStream_t(stream));
+}
+
+extern "C" int b200lut_plan_release(const void* plan) {
+  if (!plan) return B200LUT_OK;
+  int dev = 0;
+  B200LUT_CUDA_OK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_rows_plan_mu);
+  rows_plan_forget(plan, dev);
+  return B200LUT_OK;
 }
 
 extern "C" int b200lut_plan_form(const void* plan) {

@@ -245,6 +245,7 @@ def test_plan_entries_refuse_null_buffers_before_any_cuda_call():
     L = pkg._lib
     lib = L.lib()
     assert lib.b200lut_plan_form(None) < 0                      # not a plan buffer
+    assert lib.b200lut_plan_release(None) == 0                  # nothing to drop
     assert lib.b200lut_plan_status(None) == L.ERR_INVALID if hasattr(L, "ERR_INVALID") else lib.b200lut_plan_status(None) != 0
     assert lib.b200lut_plan_run(None, 1, L.dtype_id(torch.bfloat16), None) != 0
     assert lib.b200lut_plan_bytes(None, 0, 1, L.dtype_id(torch.bfloat16)) == 0
