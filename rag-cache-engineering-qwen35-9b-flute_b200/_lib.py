@@ -444,15 +444,21 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 def embed_gather(ids: torch.Tensor, table: dict, K: int, dtype: torch.dtype,
-                 out_fp32: bool = False) -> torch.Tensor:
+                 out_fp32: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rows ids (1-D int64 CUDA tensor) of a palettized [N, K] table -> [n, K] in `dtype`
     (fp32 with out_fp32). table: packed, lut, bits, N, group_size, n_groups and optionally
-    packed2 / lut2 / bits2 and resA + resB (both or neither)."""
+    packed2 / lut2 / bits2 and resA + resB (both or neither). out: a contiguous [n, K] tensor of
+    the result type to write into (nothing is allocated then)."""
     _need_cuda(ids, "ids")
     if ids.dim() != 1 or ids.dtype != torch.int64 or not ids.is_contiguous():
         raise ValueError("embed_gather expects a contiguous 1-D int64 id tensor")
     n = ids.numel()
-    out = torch.empty(n, K, dtype=torch.float32 if out_fp32 else dtype, device=ids.device)
+    want = torch.float32 if out_fp32 else dtype
+    if out is None:
+        out = torch.empty(n, K, dtype=want, device=ids.device)
+    elif (tuple(out.shape) != (n, K) or out.dtype != want or not out.is_contiguous()
+          or out.device != ids.device):
+        raise ValueError(f"out must be a contiguous [{n}, {K}] {want} tensor on the ids' device")
     seg = (Segment * 1)()
     s = seg[0]
     s.packed, s.lut = ptr(table["packed"]), ptr(table["lut"])

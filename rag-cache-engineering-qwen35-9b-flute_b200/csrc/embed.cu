@@ -152,6 +152,53 @@ __global__ void __launch_bounds__(kEmbedThreads) embed_gather_kernel(const Embed
   }
 }
 
+// The common case on its own path: 4-bit codes, one stream, no residual, 16-bit output rows that
+// take 8-byte stores. One block per token. The row's palette becomes a 256-entry pair table in
+// shared memory (entry e = palette[e & 15] | palette[e >> 4] << 16: two consecutive k in one
+// word; 1 KB, every bank holds whole words of it, so a warp's lookups never conflict). A thread
+// owns (chunk g, tig): ONE 16-byte load fetches the four words of the row's slab in lane
+// 4 * (r & 7) + tig — 16 codes of this row, interleaved with 16 of row r ^ 8 —, eight table
+// lookups turn them into four 8-byte pieces (k = 64 g + 16 kt + 4 tig .. + 3), and the four
+// threads of a chunk's k-step fill whole 32-byte sectors. Against the generic kernel above: an
+// eighth of the load instructions and half of the lookups per output.
+template <typename T>
+__global__ void __launch_bounds__(kEmbedThreads) embed_gather4_kernel(const EmbedParams p) {
+  __shared__ uint32_t pair[256];
+  const long long tok = blockIdx.x;
+  const long long id = p.ids[tok];
+  uint16_t* orow = static_cast<uint16_t*>(p.out) + tok * p.ldo;
+  const int G = p.K / kChunkK;
+  if (id < 0 || id >= p.N) {
+    if (threadIdx.x == 0) atomicExch(&g_embed_status, kBadId);
+    for (int item = threadIdx.x; item < G * 16; item += kEmbedThreads)
+      *reinterpret_cast<uint2*>(orow + item * 4) = make_uint2(0u, 0u);
+    return;
+  }
+  const int n = int(id), t = n >> 7, r = n & 127;
+  int grp = n / p.group_size;
+  if (grp > p.n_groups - 1) grp = p.n_groups - 1;
+  {
+    const uint16_t* l1 = p.lut[0] + size_t(grp) * 16;
+    const int e = threadIdx.x;
+    pair[e] = uint32_t(__ldg(l1 + (e & 15))) | (uint32_t(__ldg(l1 + (e >> 4))) << 16);
+  }
+  __syncthreads();
+  const int s = r >> 4, gid = r & 7, half = (r >> 3) & 1;
+  // chunk g of the tile, plane s >> 1, lane 4 gid + tig, the slab's four words
+  const uint8_t* base = p.packed[0] + size_t(t) * G * 4096 + (s >> 1) * 1024 + gid * 128 + (s & 1) * 16;
+  const int sh0 = 8 * half, sh1 = 8 * (half + 2);
+  for (int item = threadIdx.x; item < G * 4; item += kEmbedThreads) {
+    const int g = item >> 2, tig = item & 3;
+    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(base + size_t(g) * 4096 + tig * 32));
+    const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
+    uint16_t* o = orow + g * kChunkK + 4 * tig;
+#pragma unroll
+    for (int kt = 0; kt < 4; ++kt)
+      *reinterpret_cast<uint2*>(o + 16 * kt) =
+          make_uint2(pair[(w[kt] >> sh0) & 0xFFu], pair[(w[kt] >> sh1) & 0xFFu]);
+  }
+}
+
 // fp32 rows -> 16-bit rows, one rounding (the cast after the un-rotation of tied rows)
 template <typename T>
 __global__ void __launch_bounds__(256) round_rows_kernel(const float* __restrict__ in,
@@ -214,6 +261,14 @@ extern "C" int b200lut_embed_gather(const int64_t* ids, int64_t n_ids, int K, in
   const int esz = out_fp32 ? 4 : 2;
   p.vec_ok = aligned16(s.out) && (s.ldo * esz) % 16 == 0;
   p.N = s.N; p.K = K; p.group_size = s.group_size; p.n_groups = s.n_groups;
+  if (p.bits[0] == 4 && !p.packed[1] && p.R == 0 && !p.out_f32 && p.vec_ok && aligned16(p.packed[0])) {
+    if (dtype == B200LUT_BF16)
+      embed_gather4_kernel<__nv_bfloat16><<<unsigned(n_ids), kEmbedThreads, 0, cudaStream_t(stream)>>>(p);
+    else
+      embed_gather4_kernel<__half><<<unsigned(n_ids), kEmbedThreads, 0, cudaStream_t(stream)>>>(p);
+    B200LUT_CUDA_OK(cudaGetLastError());
+    return B200LUT_OK;
+  }
   const dim3 grid(unsigned(n_ids), unsigned((K / 8 + kEmbedThreads - 1) / kEmbedThreads), 1);
   if (dtype == B200LUT_BF16)
     embed_gather_kernel<__nv_bfloat16><<<grid, kEmbedThreads, 0, cudaStream_t(stream)>>>(p);

@@ -67,6 +67,8 @@ def test_reference_vectors(golden_embedding, name):
     (384, 320, 32, 2, 1, 0, None, torch.bfloat16, (1,)),
     (1280, 2048, 256, 4, 4, 32, None, torch.float16, (65,)),         # deployed recipe: rank 32
     (256, 512, 128, 1, None, 8, 4, torch.bfloat16, (19,)),
+    (640, 192, 32, 4, None, 0, None, torch.float16, (300,)),         # fewer (chunk, lane) items than threads
+    (1024, 8192, 512, 4, None, 0, None, torch.bfloat16, (3, 7)),     # two items per thread, a group of four tiles
 ))
 def test_seeded_tables_against_the_oracle(N, K, gs, bits, bits2, rank, rot, dtype, n_ids):
     rng = np.random.default_rng(N + K)
