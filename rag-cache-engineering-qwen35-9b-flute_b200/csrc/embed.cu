@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(kEmbedThreads) embed_gather_kernel(const Embed
 // The common case on its own path: 4-bit codes, one stream, no residual, 16-bit output rows that
 // take 8-byte stores. One block per token. The row's palette becomes a 256-entry pair table in
 // shared memory (entry e = palette[e & 15] | palette[e >> 4] << 16: two consecutive k in one
-// word; 1 KB, every bank holds whole words of it, so a warp's lookups never conflict). A thread
+// word; 1 KB, eight words per bank, so a warp's lookups take a few wavefronts each). A thread
 // owns (chunk g, tig): ONE 16-byte load fetches the four words of the row's slab in lane
 // 4 * (r & 7) + tig — 16 codes of this row, interleaved with 16 of row r ^ 8 —, eight table
 // lookups turn them into four 8-byte pieces (k = 64 g + 16 kt + 4 tig .. + 3), and the four
