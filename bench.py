@@ -826,7 +826,7 @@ def run_extras(pkg, st, stack, peaks, flags):
         extras["hybrid_grid"] = grid
 
         # the stack at the other decode widths, and behind a Hadamard rotation of every group's input
-        for M in (16, 64):
+        for M in (4, 8, 16, 64):
             ms, g = stack_point(pkg, stack, M, flags, 10)
             byts = stack.algorithmic_bytes(M)
             put(f"stack_m{M}", {"ms_per_step": ms, "tok/s": M * 1e3 / ms, "frac_of_hbm": byts / (ms * 1e-3) / 1e9 / hbm,
